@@ -1,0 +1,294 @@
+"""Benchmark of the EXL3 quantized-linear path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (N = 1): the quantized projections of a Llama-3-8B-shaped decoder at 4.0 bits per weight
+(32 layers x {q, k, v, o, gate, up, down}; hidden 4096, FFN 14336, 8 KV heads), batch-1 decode
+(QMV): one step is one activation row through all 224 projections, each with its own weights,
+3.49 GB of packed trellis in total, so every step streams far more than the 126 MB L2.  The o
+projection of every layer is the single-layer 4096 x 4096 K=4 configuration.  Inputs are seeded
+synthetic data: uniform random trellis words (any bit string is a valid EXL3 tile), +-1 fp16 sign
+vectors, x ~ N(0, 1) fp16.
+
+Metric: effective HBM GB/s = algorithmic bytes / device time, where the algorithmic bytes of one
+projection are in*out*K/8 (trellis) + 2*(in+out) (sign vectors) + 2*M*(in+out) (x read, y write).
+
+With N > 1 (launched under torch.distributed.run) every projection is tensor-parallel: q/k/v/gate/up
+are split by output columns, o/down by input rows with an all-reduce of the fp32 partial sums, and
+the total work is fixed (strong scaling).
+
+``--impl reference`` times the CPU oracle (the C restatement of the reference's arithmetic) on the
+host cores, on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+HIDDEN, FFN, KV, LAYERS, K_BITS, CB = 4096, 14336, 1024, 32, 4, 0
+# name, in, out, tensor-parallel kind
+PROJECTIONS = [("q", HIDDEN, HIDDEN, "col"), ("k", HIDDEN, KV, "col"), ("v", HIDDEN, KV, "col"),
+               ("o", HIDDEN, HIDDEN, "row"), ("gate", HIDDEN, FFN, "col"), ("up", HIDDEN, FFN, "col"),
+               ("down", FFN, HIDDEN, "row")]
+WORKLOAD = "llama3-8b-shaped EXL3 4.0bpw projections (32 layers x q,k,v,o,gate,up,down), batch-1 decode QMV"
+
+
+def algorithmic_bytes(n_in: int, n_out: int, k: int, rows: int) -> int:
+    return n_in * n_out * k // 8 + 2 * (n_in + n_out) + 2 * rows * (n_in + n_out)
+
+
+def measured_peak_gbs() -> tuple[float, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100", "-i",
+                 str(device_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        clocks, max_clock, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) != 6:
+                continue
+            try:
+                clocks.append(float(parts[0]))
+                max_clock = float(parts[1])
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[2:]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        if not clocks:
+            return {"sm_mhz": None, "sm_max_mhz": max_clock, "reasons": ["no samples"]}
+        return {"sm_mhz": float(np.median(clocks)), "sm_max_mhz": max_clock, "reasons": sorted(reasons),
+                "samples": len(clocks)}
+
+
+# ------------------------------------------------------------------------------------------------ ours
+
+def shard(kind: str, n_in: int, n_out: int, world: int) -> tuple[int, int]:
+    if world == 1:
+        return n_in, n_out
+    if kind == "col":
+        assert n_out % (128 * world) == 0
+        return n_in, n_out // world
+    assert n_in % (128 * world) == 0
+    return n_in // world, n_out
+
+
+def run_ours(args) -> dict:
+    import mlxl3_b200 as ex
+    from mlxl3_b200.runtime import DeviceBuffer, Event, PinnedBuffer, Stream
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    ex.init(local_rank)
+    rows = 1
+
+    # ---- build the sharded projections, each with its own seeded weights -------------------------
+    layers = []
+    total_bytes = 0
+    rng_x = np.random.default_rng(4242)
+    for layer in range(LAYERS):
+        for j, (name, n_in, n_out, kind) in enumerate(PROJECTIONS):
+            s_in, s_out = shard(kind, n_in, n_out, world)
+            rng = np.random.default_rng([1001, layer, j, rank])
+            trellis = rng.integers(0, 65536, (s_in // 16, s_out // 16, 16 * K_BITS), dtype=np.uint16)
+            suh = np.where(rng.random(s_in) > 0.5, -1, 1).astype(np.float16)
+            svh = np.where(rng.random(s_out) > 0.5, -1, 1).astype(np.float16)
+            layers.append((kind, s_in, s_out, ex.Exl3Linear(trellis, suh, svh, None, K_BITS, CB)))
+            total_bytes += algorithmic_bytes(n_in, n_out, K_BITS, rows)   # whole-job bytes, counted once
+    x_host = {n: PinnedBuffer((rows, n), np.float16) for n in {l[1] for l in layers}}
+    for n, buf in x_host.items():
+        buf.array[...] = rng_x.standard_normal((rows, n)).astype(np.float16)
+    d_x = {n: DeviceBuffer.from_numpy(buf.array) for n, buf in x_host.items()}
+    d_y = {n: DeviceBuffer(rows * n * 2) for n in {l[2] for l in layers}}
+    y_host = PinnedBuffer((rows, layers[-1][2]), np.float16)
+    ws = DeviceBuffer(max(l[3].workspace_bytes(rows) for l in layers))
+
+    if world > 1:
+        import torch
+        stream = Stream(handle=torch.cuda.current_stream().cuda_stream)
+        yhat = {n: torch.empty((rows, n), dtype=torch.float32, device="cuda") for n in {l[2] for l in layers}}
+    else:
+        stream = Stream()
+
+    from ctypes import c_void_p
+    from mlxl3_b200 import _lib
+
+    def step(host_io: bool) -> None:
+        if host_io:
+            first = layers[0][1]
+            d_x[first].upload(x_host[first].array, stream)
+        for kind, s_in, s_out, lin in layers:
+            if world > 1 and kind == "row":
+                # row-parallel: fp32 partial sums -> all-reduce over NVLink -> output rotation
+                buf = yhat[s_out]
+                lin.forward_partial_device(d_x[s_in].ptr, ex.F16, rows, buf.data_ptr(), ws, stream)
+                dist.all_reduce(buf)
+                lin.finish_device(buf.data_ptr(), rows, ex.F16, d_y[s_out].ptr, stream)
+            else:
+                lin.forward_device(d_x[s_in].ptr, ex.F16, rows, d_y[s_out].ptr, ws, stream)
+        if host_io:
+            last = layers[-1][2]
+            _lib.call("b200exl3_memcpy_d2h", c_void_p(y_host.ptr), c_void_p(d_y[last].ptr), y_host.nbytes,
+                      c_void_p(stream.handle))
+            stream.sync()
+
+    def barrier() -> None:
+        stream.sync()
+        if dist is not None:
+            dist.barrier()
+            import torch
+            torch.cuda.synchronize()
+
+    def timed(host_io: bool) -> float:
+        for _ in range(args.warmup):
+            step(host_io)
+        barrier()
+        start, stop = Event(), Event()
+        start.record(stream)
+        for _ in range(args.steps):
+            step(host_io)
+        stop.record(stream)
+        ms = start.elapsed_ms(stop)
+        barrier()
+        if dist is not None:
+            import torch
+            t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    ms_device = timed(host_io=False)
+    clocks = sampler.stop() if sampler else None
+    ms_e2e = timed(host_io=True)
+
+    launches_per_step = 3 * len(layers)
+    ms_per_step = ms_device / args.steps
+    value = total_bytes / (ms_per_step * 1e-3) / 1e9
+    e2e_value = total_bytes / (ms_e2e / args.steps * 1e-3) / 1e9
+    peak, peak_kind = measured_peak_gbs()
+    per_gpu = value / world
+    result = {
+        "metric": "exl3_qmv_effective_hbm_gbs", "value": round(value, 2), "unit": "GB/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f16 x 4-bit trellis, f32 accumulate", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "k_bits": K_BITS, "codebook": CB, "rows": rows,
+                   "bytes_per_step": total_bytes, "l2_policy": "inputs larger than L2 (3.49 GB of weights per step)",
+                   "parallelism": f"tp{world}"},
+        "linear_stack_tok_s": round(1e3 / ms_per_step, 1),
+        "roofline": {"bound": "hbm", "achieved": round(per_gpu, 2), "peak": peak, "unit": "GB/s",
+                     "frac": round(per_gpu / peak, 4), "traffic": None, "peak_kind": f"of {peak_kind}",
+                     "note": "achieved = algorithmic bytes of all projections / device time of the whole step "
+                             "(product kernel plus both rotations), per GPU"},
+        "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": rows * layers[0][1] * 2,
+                "d2h_bytes_per_step": rows * layers[-1][2] * 2},
+        "gpu_launches": launches_per_step * args.steps,
+        "clocks": clocks,
+    }
+    if rank == 0 and world == 1:
+        result["cpu_baseline"] = cpu_baseline(budget_s=12.0)
+    if dist is not None:
+        dist.destroy_process_group()
+    return result if rank == 0 else {}
+
+
+# ------------------------------------------------------------------------------------------- reference
+
+def cpu_baseline(budget_s: float) -> dict:
+    """Times the CPU oracle on the o projection (4096 x 4096, K = 4, one row) with every host core."""
+    import oracle
+    rng = np.random.default_rng(1001)
+    n = HIDDEN
+    trellis = rng.integers(0, 65536, (n // 16, n // 16, 16 * K_BITS), dtype=np.uint16)
+    suh = np.where(rng.random(n) > 0.5, -1, 1).astype(np.float16)
+    svh = np.where(rng.random(n) > 0.5, -1, 1).astype(np.float16)
+    x = rng.standard_normal((1, n)).astype(np.float16)
+    threads = oracle.default_threads()
+    oracle.linear_forward(trellis, K_BITS, CB, suh, svh, None, x, threads=threads)
+    t0, reps = time.perf_counter(), 0
+    while time.perf_counter() - t0 < budget_s or reps < 3:
+        oracle.linear_forward(trellis, K_BITS, CB, suh, svh, None, x, threads=threads)
+        reps += 1
+    dt = (time.perf_counter() - t0) / reps
+    return {"value": round(algorithmic_bytes(n, n, K_BITS, 1) / dt / 1e9, 3), "unit": "GB/s", "cores": threads,
+            "kind": "port", "ms_per_layer": round(dt * 1e3, 3),
+            "sample": f"{reps} calls of the 4096x4096 K=4 o projection, one row (1/224 of a step each)"}
+
+
+def run_reference(args) -> dict:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return {}
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    base = cpu_baseline(budget_s=max(2.0, min(60.0, 2.0 * (args.steps + args.warmup))))
+    return {
+        "impl": "reference", "metric": "exl3_qmv_effective_hbm_gbs", "value": base["value"], "unit": "GB/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_layer"] * 224,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16 x 4-bit trellis, f32 accumulate",
+        "data": "synthetic", "config": {"workload": WORKLOAD, "k_bits": K_BITS, "codebook": CB, "rows": 1},
+        "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    result = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if result:
+        print(json.dumps(result), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,135 @@
+/*
+ * b200exl3 -- C ABI of the B200 (sm_100a) implementation of the EXL3 quantized-linear path.
+ *
+ * Conventions (they mirror the reference's FFI, native/ffi/mlx_bridge.cpp:49-66 and
+ * native/src/array.rs:319-369):
+ *   - every function returns 0 on success and -1 on error; it never throws or aborts;
+ *   - after an error, b200exl3_last_error() returns a NUL-terminated message that stays valid
+ *     until the next call of this library on the same thread;
+ *   - objects are opaque handles created by *_create and released by *_free;
+ *   - dtype codes are the reference's (native/src/array.rs:21-36): 2 = u16, 3 = u32, 9 = f16,
+ *     10 = f32, 12 = bf16.
+ * Differences forced by CUDA: tensors are caller-owned DEVICE pointers with explicit shapes
+ * (the reference passes opaque lazy MLX arrays), every launch takes a cudaStream_t (passed as
+ * void*), and forward calls allocate nothing: scratch memory is a caller-provided workspace.
+ * All device pointers must be 16-byte aligned.  Handles are immutable after creation, so one
+ * handle may be used from several threads and streams at once, each with its own workspace.
+ */
+#ifndef B200EXL3_H
+#define B200EXL3_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200EXL3_U16 2
+#define B200EXL3_U32 3
+#define B200EXL3_F16 9
+#define B200EXL3_F32 10
+#define B200EXL3_BF16 12
+
+/* flags of b200exl3_linear_create */
+#define B200EXL3_COPY_TRELLIS 1u   /* copy the trellis into library-owned memory (default: borrow the pointer) */
+#define B200EXL3_EXACT_WEIGHTS 2u  /* multiply with the bit-exact fp16 weight instead of its two fp16 halves */
+
+typedef struct b200exl3_linear b200exl3_linear;
+typedef void* b200exl3_stream;     /* cudaStream_t */
+
+/* ---- runtime (replaces mlxl3_mlx_init / mlxl3_mlx_error, native/ffi/mlx_bridge.cpp:176, 222-232) ---- */
+
+/* Selects `device` for the calling thread and checks that it is an sm_100 part.  Idempotent. */
+int b200exl3_init(int device);
+const char* b200exl3_last_error(void);
+/* major*10000 + minor*100 + patch */
+int b200exl3_version(void);
+/* Tuning knobs for experiments: "qmv_ctas_per_sm", "qmv_force_splits" (0 = heuristic). */
+int b200exl3_set_option(const char* name, int64_t value);
+
+/* Plain device-memory plumbing for hosts that have no CUDA binding of their own (replaces
+ * mlxl3_array_from_bytes, mlxl3_array_copy_bytes, mlxl3_array_free and mlxl3_synchronize,
+ * native/ffi/mlx_bridge.cpp:337, 610, 233, 192).  Streams are created non-blocking. */
+int b200exl3_malloc(size_t bytes, void** out_device_ptr);
+int b200exl3_free(void* device_ptr);
+int b200exl3_host_alloc(size_t bytes, void** out_pinned_ptr);
+int b200exl3_host_free(void* pinned_ptr);
+int b200exl3_memcpy_h2d(void* dst_device, const void* src_host, size_t bytes, b200exl3_stream stream);
+int b200exl3_memcpy_d2h(void* dst_host, const void* src_device, size_t bytes, b200exl3_stream stream);
+int b200exl3_memset(void* dst_device, int value, size_t bytes, b200exl3_stream stream);
+int b200exl3_stream_create(b200exl3_stream* out);
+int b200exl3_stream_destroy(b200exl3_stream stream);
+int b200exl3_stream_sync(b200exl3_stream stream);
+int b200exl3_event_create(void** out_event);
+int b200exl3_event_destroy(void* event);
+int b200exl3_event_record(void* event, b200exl3_stream stream);
+/* Waits for `stop`, then returns the device time between the two events in milliseconds. */
+int b200exl3_event_elapsed_ms(void* start, void* stop, float* out_ms);
+
+/* ---- codec (replaces exl3_decode / exl3_codebook of native/shaders/exl3.metal:102-114 and
+ *      codec::unpack / decode_codeword / reconstruct_inner of native/src/codec.rs:52-71, 102-124, 159-190) ---- */
+
+/* packed [tiles, 16k] u16 -> states [tiles, 256] u16 (kernel order) and/or fp16 values [tiles, 256];
+ * either output may be NULL. */
+int b200exl3_unpack_states(const uint16_t* d_packed, int64_t tiles, int k, int codebook, uint16_t* d_states,
+                           uint16_t* d_values_f16, b200exl3_stream stream);
+/* states [n] u16 -> fp16 weights [n]; d_states == NULL enumerates the states 0..n-1. */
+int b200exl3_codebook(const uint16_t* d_states, int64_t n, int codebook, uint16_t* d_values_f16,
+                      b200exl3_stream stream);
+/* trellis [in/16, out/16, 16k] u16 -> inner matrix W [in, out] fp16 row-major, bit-exact with
+ * codec::reconstruct_inner.  in and out are multiples of 16. */
+int b200exl3_reconstruct(const uint16_t* d_trellis, int in, int out, int k, int codebook, uint16_t* d_w_f16,
+                         b200exl3_stream stream);
+
+/* ---- rotations (replace the MLX chains of native/src/linear.rs:855-861 and 978-996, the fused
+ *      glue_prologue / glue_epilogue of native/src/linear.rs:1452-1600, mlxl3_flash_prepare128 of
+ *      native/ffi/mlx_bridge.cpp:237 and exl3_prepare128 / flash_finish128 of
+ *      native/shaders/exl3.metal:204-235) ---- */
+
+/* xhat[r, :] = H128(half(half(x[r, :]) * suh)) as fp16.  d_suh_f16 holds [in] (scale_rows == 1) or
+ * [rows, in] (scale_rows == rows).  Bit-exact with MLX's fp16 hadamard_transform. */
+int b200exl3_prepare(const void* d_x, int x_dtype, const uint16_t* d_suh_f16, int64_t scale_rows, int64_t rows, int in,
+                     uint16_t* d_xhat_f16, b200exl3_stream stream);
+/* y[r, :] = half(H128(half(sum_s partials[s, r, :]))) * svh (+ bias) written as y_dtype.
+ * partials is fp32 [splits, rows, out]; d_bias_f16 may be NULL. */
+int b200exl3_finish(const float* d_partials, int splits, const uint16_t* d_svh_f16, int64_t scale_rows,
+                    const uint16_t* d_bias_f16, int64_t rows, int out, int y_dtype, void* d_y, b200exl3_stream stream);
+
+/* ---- Exl3Linear (replaces native/src/linear.rs:424-1236) ---- */
+
+/* Same validation as Exl3Linear::new (native/src/linear.rs:577-639): k in 1..8, codebook in 0..2
+ * (0 default, 1 MCG, 2 MUL1), in and out positive multiples of 128, trellis [in/16, out/16, 16k]
+ * 16-bit integers.  suh [in], svh [out] and the optional bias [out] are given in `scale_dtype`
+ * (f16, bf16 or f32) and converted once to fp16, as the reference does at load. */
+int b200exl3_linear_create(const uint16_t* d_trellis, const void* d_suh, const void* d_svh, const void* d_bias_or_null,
+                           int scale_dtype, int in, int out, int k, int codebook, uint32_t flags,
+                           b200exl3_linear** out_handle);
+void b200exl3_linear_free(b200exl3_linear* handle);
+int b200exl3_linear_input_dims(const b200exl3_linear* handle);    /* Exl3Linear::input_dims  */
+int b200exl3_linear_output_dims(const b200exl3_linear* handle);   /* Exl3Linear::output_dims */
+int b200exl3_linear_workspace_bytes(const b200exl3_linear* handle, int64_t rows, size_t* out_bytes);
+/* Exl3Linear::forward (native/src/linear.rs:731-997): x [rows, in] in x_dtype -> y [rows, out] in
+ * the same dtype.  rows >= 1.  The workspace must hold b200exl3_linear_workspace_bytes(rows). */
+int b200exl3_linear_forward(const b200exl3_linear* handle, const void* d_x, int x_dtype, int64_t rows, void* d_y,
+                            void* d_workspace, size_t workspace_bytes, b200exl3_stream stream);
+/* The middle of forward alone: fp32 yhat [rows, out] = xhat [rows, in] (fp16, already rotated) times
+ * the inner matrix -- what the reference's QMV/QMM kernels return before the output rotation. */
+int b200exl3_linear_forward_raw(const b200exl3_linear* handle, const uint16_t* d_xhat_f16, int64_t rows, float* d_yhat,
+                                void* d_workspace, size_t workspace_bytes, b200exl3_stream stream);
+/* Row-parallel tensor parallelism.  The reference sums split-K partials in fp32 before the output
+ * rotation (native/src/linear.rs:978-982); a layer whose input rows are sharded over GPUs is the same
+ * thing with the partials on different devices.  forward_partial = input rotation + product, giving
+ * this shard's fp32 yhat [rows, out]; the caller all-reduces yhat and then calls linear_finish, which
+ * applies the output rotation, svh and bias of the handle. */
+int b200exl3_linear_forward_partial(const b200exl3_linear* handle, const void* d_x, int x_dtype, int64_t rows,
+                                    float* d_yhat, void* d_workspace, size_t workspace_bytes, b200exl3_stream stream);
+int b200exl3_linear_finish(const b200exl3_linear* handle, const float* d_yhat, int64_t rows, int y_dtype, void* d_y,
+                           b200exl3_stream stream);
+/* Inner matrix W [in, out] fp16 of this layer (the bit-exact deliverable). */
+int b200exl3_linear_decode(const b200exl3_linear* handle, uint16_t* d_w_f16, b200exl3_stream stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200EXL3_H */

@@ -1,0 +1,14 @@
+"""B200-native EXL3 quantized-linear path: hand-written sm_100a CUDA kernels behind a C ABI
+(``include/b200exl3.h``), with this package as the Python host-side mirror of the reference's
+operator interface.  Importing the package does not load the CUDA library; the first call does,
+and it raises if the library is not built -- there is no CPU fallback.
+"""
+from ._lib import BF16, F16, F32, B200Exl3Error, LIB_PATH
+from .linear import DEFAULT, MCG, MUL1, Exl3Linear
+from .runtime import DEFAULT_STREAM, DeviceBuffer, Event, PinnedBuffer, Stream, init, set_option
+from . import codec
+
+__all__ = [
+    "BF16", "F16", "F32", "B200Exl3Error", "LIB_PATH", "DEFAULT", "MCG", "MUL1", "Exl3Linear", "DEFAULT_STREAM",
+    "DeviceBuffer", "Event", "PinnedBuffer", "Stream", "init", "set_option", "codec",
+]

@@ -1,0 +1,356 @@
+// C ABI of the library: argument validation, handle ownership, workspace carving and kernel dispatch.
+// Error convention of the reference's FFI (native/ffi/mlx_bridge.cpp:49-66): int status plus a
+// thread-local message; nothing throws across the boundary.
+#include "../../include/b200exl3.h"
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+
+#include "common.cuh"
+#include "kernels.h"
+
+using namespace b200exl3;
+
+namespace {
+
+thread_local std::string g_error;
+
+int fail(const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    g_error = buf;
+    return -1;
+}
+
+int check(cudaError_t e, const char* what) {
+    if (e == cudaSuccess) return 0;
+    return fail("%s: %s", what, cudaGetErrorString(e));
+}
+
+#define B200_TRY(expr, what)                      \
+    do {                                          \
+        if (check((expr), (what)) != 0) return -1; \
+    } while (0)
+
+cudaStream_t as_stream(b200exl3_stream s) { return static_cast<cudaStream_t>(s); }
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+__global__ void to_half_kernel(const void* src, int dtype, int64_t n, __half* dst) {
+    int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < n) dst[i] = load_as_half(src, dtype, i);
+}
+
+__global__ void sum_partials_kernel(const float* partials, int splits, int64_t stride, int64_t n, float* out) {
+    int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float acc = partials[i];
+    for (int s = 1; s < splits; ++s) acc = __fadd_rn(acc, partials[s * stride + i]);
+    out[i] = acc;
+}
+
+int valid_format(int k, int cb) {
+    if (k < 1 || k > 8) return fail("K must be in 1..=8, got %d", k);
+    if (cb < 0 || cb > 2) return fail("invalid EXL3 codebook %d", cb);
+    return 0;
+}
+
+constexpr int kMaxBatchRows = 32;   // rows handled by one launch of the fused product kernel
+
+}  // namespace
+
+struct b200exl3_linear {
+    int in, out, k, cb, device;
+    uint32_t flags;
+    const uint16_t* trellis;
+    uint16_t* owned_trellis;
+    __half* suh;
+    __half* svh;
+    __half* bias;
+};
+
+extern "C" {
+
+const char* b200exl3_last_error(void) { return g_error.c_str(); }
+
+int b200exl3_version(void) { return 100; }
+
+int b200exl3_init(int device) {
+    int count = 0;
+    B200_TRY(cudaGetDeviceCount(&count), "cudaGetDeviceCount");
+    if (device < 0 || device >= count) return fail("device %d out of range (%d visible)", device, count);
+    B200_TRY(cudaSetDevice(device), "cudaSetDevice");
+    cudaDeviceProp prop{};
+    B200_TRY(cudaGetDeviceProperties(&prop, device), "cudaGetDeviceProperties");
+    if (prop.major != 10) return fail("device %d is sm_%d%d; this library contains sm_100a code only", device, prop.major, prop.minor);
+    return 0;
+}
+
+int b200exl3_set_option(const char* name, int64_t value) {
+    static int ctas = 0, splits = 0;
+    if (!name) return fail("option name is NULL");
+    if (!strcmp(name, "qmv_ctas_per_sm")) ctas = static_cast<int>(value);
+    else if (!strcmp(name, "qmv_force_splits")) splits = static_cast<int>(value);
+    else return fail("unknown option %s", name);
+    qmv_set_tuning(ctas, splits);
+    return 0;
+}
+
+/* ---- memory / stream plumbing ---------------------------------------------------------------- */
+
+int b200exl3_malloc(size_t bytes, void** out) {
+    if (!out) return fail("out pointer is NULL");
+    *out = nullptr;
+    if (bytes == 0) return 0;
+    return check(cudaMalloc(out, bytes), "cudaMalloc");
+}
+int b200exl3_free(void* p) { return p ? check(cudaFree(p), "cudaFree") : 0; }
+int b200exl3_host_alloc(size_t bytes, void** out) {
+    if (!out) return fail("out pointer is NULL");
+    *out = nullptr;
+    if (bytes == 0) return 0;
+    return check(cudaMallocHost(out, bytes), "cudaMallocHost");
+}
+int b200exl3_host_free(void* p) { return p ? check(cudaFreeHost(p), "cudaFreeHost") : 0; }
+int b200exl3_memcpy_h2d(void* dst, const void* src, size_t bytes, b200exl3_stream s) {
+    if (bytes == 0) return 0;
+    return check(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, as_stream(s)), "cudaMemcpyAsync(h2d)");
+}
+int b200exl3_memcpy_d2h(void* dst, const void* src, size_t bytes, b200exl3_stream s) {
+    if (bytes == 0) return 0;
+    return check(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, as_stream(s)), "cudaMemcpyAsync(d2h)");
+}
+int b200exl3_memset(void* dst, int value, size_t bytes, b200exl3_stream s) {
+    if (bytes == 0) return 0;
+    return check(cudaMemsetAsync(dst, value, bytes, as_stream(s)), "cudaMemsetAsync");
+}
+int b200exl3_stream_create(b200exl3_stream* out) {
+    if (!out) return fail("out pointer is NULL");
+    cudaStream_t s;
+    B200_TRY(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking), "cudaStreamCreate");
+    *out = s;
+    return 0;
+}
+int b200exl3_stream_destroy(b200exl3_stream s) { return s ? check(cudaStreamDestroy(as_stream(s)), "cudaStreamDestroy") : 0; }
+int b200exl3_stream_sync(b200exl3_stream s) { return check(cudaStreamSynchronize(as_stream(s)), "cudaStreamSynchronize"); }
+int b200exl3_event_create(void** out) {
+    if (!out) return fail("out pointer is NULL");
+    cudaEvent_t e;
+    B200_TRY(cudaEventCreate(&e), "cudaEventCreate");
+    *out = e;
+    return 0;
+}
+int b200exl3_event_destroy(void* e) { return e ? check(cudaEventDestroy(static_cast<cudaEvent_t>(e)), "cudaEventDestroy") : 0; }
+int b200exl3_event_record(void* e, b200exl3_stream s) {
+    return check(cudaEventRecord(static_cast<cudaEvent_t>(e), as_stream(s)), "cudaEventRecord");
+}
+int b200exl3_event_elapsed_ms(void* start, void* stop, float* out_ms) {
+    if (!out_ms) return fail("out pointer is NULL");
+    B200_TRY(cudaEventSynchronize(static_cast<cudaEvent_t>(stop)), "cudaEventSynchronize");
+    return check(cudaEventElapsedTime(out_ms, static_cast<cudaEvent_t>(start), static_cast<cudaEvent_t>(stop)),
+                 "cudaEventElapsedTime");
+}
+
+/* ---- codec ------------------------------------------------------------------------------------- */
+
+int b200exl3_unpack_states(const uint16_t* d_packed, int64_t tiles, int k, int cb, uint16_t* d_states,
+                           uint16_t* d_values, b200exl3_stream s) {
+    if (valid_format(k, cb)) return -1;
+    if (tiles < 0) return fail("packed length is not a whole tile");
+    if (tiles > 0 && (!d_packed || (!d_states && !d_values))) return fail("NULL buffer");
+    return check(launch_unpack_states(d_packed, tiles, k, cb, d_states, reinterpret_cast<__half*>(d_values), as_stream(s)),
+                 "unpack_states");
+}
+
+int b200exl3_codebook(const uint16_t* d_states, int64_t n, int cb, uint16_t* d_values, b200exl3_stream s) {
+    if (valid_format(1, cb)) return -1;
+    if (n < 0 || (n > 0 && !d_values)) return fail("invalid codebook request");
+    return check(launch_codebook(d_states, n, cb, reinterpret_cast<__half*>(d_values), as_stream(s)), "codebook");
+}
+
+int b200exl3_reconstruct(const uint16_t* d_trellis, int in, int out, int k, int cb, uint16_t* d_w, b200exl3_stream s) {
+    if (valid_format(k, cb)) return -1;
+    if (in <= 0 || out <= 0 || in % 16 || out % 16) return fail("dimensions must be positive multiples of 16");
+    if (!d_trellis || !d_w) return fail("NULL buffer");
+    if (!aligned16(d_trellis) || !aligned16(d_w)) return fail("device pointers must be 16-byte aligned");
+    return check(launch_reconstruct(d_trellis, in / 16, out / 16, k, cb, reinterpret_cast<__half*>(d_w), as_stream(s)),
+                 "reconstruct");
+}
+
+/* ---- rotations ------------------------------------------------------------------------------- */
+
+int b200exl3_prepare(const void* d_x, int x_dtype, const uint16_t* d_suh, int64_t scale_rows, int64_t rows, int in,
+                     uint16_t* d_xhat, b200exl3_stream s) {
+    if (in <= 0 || in % 128) return fail("expected complete 128-aligned rows");
+    if (rows < 0) return fail("negative row count");
+    if (!dtype_is_float(x_dtype)) return fail("unsupported input dtype %d", x_dtype);
+    if (scale_rows != 1 && scale_rows != rows) return fail("scales must have one row or one per input row");
+    if (rows == 0) return 0;
+    if (!d_x || !d_suh || !d_xhat) return fail("NULL buffer");
+    if (!aligned16(d_xhat)) return fail("device pointers must be 16-byte aligned");
+    return check(launch_prepare(d_x, x_dtype, reinterpret_cast<const __half*>(d_suh), scale_rows, rows, in,
+                                reinterpret_cast<__half*>(d_xhat), as_stream(s)), "prepare");
+}
+
+int b200exl3_finish(const float* d_partials, int splits, const uint16_t* d_svh, int64_t scale_rows,
+                    const uint16_t* d_bias, int64_t rows, int out, int y_dtype, void* d_y, b200exl3_stream s) {
+    if (out <= 0 || out % 128) return fail("expected complete 128-aligned rows");
+    if (rows < 0 || splits < 1) return fail("invalid finish request");
+    if (!dtype_is_float(y_dtype)) return fail("unsupported output dtype %d", y_dtype);
+    if (scale_rows != 1 && scale_rows != rows) return fail("scales must have one row or one per input row");
+    if (rows == 0) return 0;
+    if (!d_partials || !d_svh || !d_y) return fail("NULL buffer");
+    if (!aligned16(d_partials)) return fail("device pointers must be 16-byte aligned");
+    return check(launch_finish(d_partials, splits, rows * out, reinterpret_cast<const __half*>(d_svh), scale_rows,
+                               reinterpret_cast<const __half*>(d_bias), rows, out, y_dtype, d_y, as_stream(s)), "finish");
+}
+
+/* ---- Exl3Linear ------------------------------------------------------------------------------ */
+
+int b200exl3_linear_create(const uint16_t* d_trellis, const void* d_suh, const void* d_svh, const void* d_bias,
+                           int scale_dtype, int in, int out, int k, int cb, uint32_t flags, b200exl3_linear** out_handle) {
+    if (!out_handle) return fail("out pointer is NULL");
+    *out_handle = nullptr;
+    if (valid_format(k, cb)) return -1;
+    if (in <= 0 || out <= 0) return fail("invalid trellis shape");
+    if (in % 128 || out % 128) return fail("public EXL3 projections require 128-aligned dimensions");
+    if (!d_trellis) return fail("invalid trellis shape");
+    if (!d_suh || !d_svh) return fail("EXL3 scales have wrong dimensions");
+    if (!dtype_is_float(scale_dtype)) return fail("unsupported scale dtype %d", scale_dtype);
+    if (!aligned16(d_trellis)) return fail("device pointers must be 16-byte aligned");
+    b200exl3_linear* h = new (std::nothrow) b200exl3_linear{};
+    if (!h) return fail("out of host memory");
+    h->in = in; h->out = out; h->k = k; h->cb = cb; h->flags = flags;
+    cudaGetDevice(&h->device);
+    auto convert = [&](const void* src, int n, __half** dst) -> int {
+        B200_TRY(cudaMalloc(dst, static_cast<size_t>(n) * sizeof(__half)), "cudaMalloc(scales)");
+        to_half_kernel<<<(n + 255) / 256, 256>>>(src, scale_dtype, n, *dst);
+        return check(cudaGetLastError(), "convert scales");
+    };
+    int rc = convert(d_suh, in, &h->suh);
+    if (!rc) rc = convert(d_svh, out, &h->svh);
+    if (!rc && d_bias) rc = convert(d_bias, out, &h->bias);
+    if (!rc && (flags & B200EXL3_COPY_TRELLIS)) {
+        size_t bytes = static_cast<size_t>(in / 16) * (out / 16) * 16 * k * sizeof(uint16_t);
+        rc = check(cudaMalloc(&h->owned_trellis, bytes), "cudaMalloc(trellis)");
+        if (!rc) rc = check(cudaMemcpy(h->owned_trellis, d_trellis, bytes, cudaMemcpyDeviceToDevice), "copy trellis");
+        h->trellis = h->owned_trellis;
+    } else {
+        h->trellis = d_trellis;
+    }
+    if (!rc) rc = check(cudaDeviceSynchronize(), "linear_create");
+    if (rc) {
+        b200exl3_linear_free(h);
+        return -1;
+    }
+    *out_handle = h;
+    return 0;
+}
+
+void b200exl3_linear_free(b200exl3_linear* h) {
+    if (!h) return;
+    cudaFree(h->suh);
+    cudaFree(h->svh);
+    cudaFree(h->bias);
+    cudaFree(h->owned_trellis);
+    delete h;
+}
+
+int b200exl3_linear_input_dims(const b200exl3_linear* h) { return h ? h->in : fail("NULL handle"); }
+int b200exl3_linear_output_dims(const b200exl3_linear* h) { return h ? h->out : fail("NULL handle"); }
+
+static size_t xhat_bytes(const b200exl3_linear* h, int64_t rows) {
+    return round_up(static_cast<size_t>(rows) * h->in * sizeof(__half), 256);
+}
+
+int b200exl3_linear_workspace_bytes(const b200exl3_linear* h, int64_t rows, size_t* out_bytes) {
+    if (!h || !out_bytes) return fail("NULL argument");
+    if (rows <= 0) return fail("EXL3 linear input cannot be empty");
+    int64_t batch = rows < kMaxBatchRows ? rows : kMaxBatchRows;
+    QmvPlan plan = plan_qmv(h->in, h->out, h->k, batch);
+    *out_bytes = xhat_bytes(h, rows) + round_up(static_cast<size_t>(plan.splits) * batch * h->out * sizeof(float), 256);
+    return 0;
+}
+
+static int forward_common(const b200exl3_linear* h, const void* d_x, int x_dtype, const uint16_t* d_xhat_in, int64_t rows,
+                          void* d_y, float* d_yhat, void* ws, size_t ws_bytes, cudaStream_t stream) {
+    if (!h) return fail("NULL handle");
+    if (rows <= 0) return fail("EXL3 linear input cannot be empty");
+    size_t need = 0;
+    if (b200exl3_linear_workspace_bytes(h, rows, &need)) return -1;
+    if (!ws || ws_bytes < need) return fail("workspace too small: %zu bytes given, %zu needed", ws_bytes, need);
+    if (!aligned16(ws)) return fail("device pointers must be 16-byte aligned");
+    char* base = static_cast<char*>(ws);
+    const __half* xhat = reinterpret_cast<const __half*>(d_xhat_in);
+    if (!xhat) {
+        __half* buf = reinterpret_cast<__half*>(base);
+        B200_TRY(launch_prepare(d_x, x_dtype, h->suh, 1, rows, h->in, buf, stream), "prepare");
+        xhat = buf;
+    }
+    float* partials = reinterpret_cast<float*>(base + xhat_bytes(h, rows));
+    const bool exact = (h->flags & B200EXL3_EXACT_WEIGHTS) != 0;
+    for (int64_t r0 = 0; r0 < rows; r0 += kMaxBatchRows) {
+        int64_t n = rows - r0 < kMaxBatchRows ? rows - r0 : kMaxBatchRows;
+        QmvPlan plan = plan_qmv(h->in, h->out, h->k, n);
+        B200_TRY(launch_qmv(h->trellis, h->in, h->out, h->k, h->cb, xhat + r0 * h->in, n, exact, plan, partials, stream),
+                 "qmv");
+        if (d_yhat) {
+            int64_t count = n * h->out;
+            sum_partials_kernel<<<static_cast<unsigned>((count + 255) / 256), 256, 0, stream>>>(
+                partials, plan.splits, count, count, d_yhat + r0 * h->out);
+            B200_TRY(cudaGetLastError(), "sum partials");
+        } else {
+            char* y = static_cast<char*>(d_y) + static_cast<size_t>(r0) * h->out * dtype_size(x_dtype);
+            B200_TRY(launch_finish(partials, plan.splits, n * h->out, h->svh, 1, h->bias, n, h->out, x_dtype, y, stream),
+                     "finish");
+        }
+    }
+    return 0;
+}
+
+int b200exl3_linear_forward(const b200exl3_linear* h, const void* d_x, int x_dtype, int64_t rows, void* d_y, void* ws,
+                            size_t ws_bytes, b200exl3_stream s) {
+    if (!dtype_is_float(x_dtype)) return fail("unsupported input dtype %d", x_dtype);
+    if (!d_x || !d_y) return fail("NULL buffer");
+    return forward_common(h, d_x, x_dtype, nullptr, rows, d_y, nullptr, ws, ws_bytes, as_stream(s));
+}
+
+int b200exl3_linear_forward_raw(const b200exl3_linear* h, const uint16_t* d_xhat, int64_t rows, float* d_yhat, void* ws,
+                                size_t ws_bytes, b200exl3_stream s) {
+    if (!d_xhat || !d_yhat) return fail("NULL buffer");
+    if (!aligned16(d_xhat)) return fail("device pointers must be 16-byte aligned");
+    return forward_common(h, nullptr, kF16, d_xhat, rows, nullptr, d_yhat, ws, ws_bytes, as_stream(s));
+}
+
+int b200exl3_linear_forward_partial(const b200exl3_linear* h, const void* d_x, int x_dtype, int64_t rows, float* d_yhat,
+                                    void* ws, size_t ws_bytes, b200exl3_stream s) {
+    if (!dtype_is_float(x_dtype)) return fail("unsupported input dtype %d", x_dtype);
+    if (!d_x || !d_yhat) return fail("NULL buffer");
+    return forward_common(h, d_x, x_dtype, nullptr, rows, nullptr, d_yhat, ws, ws_bytes, as_stream(s));
+}
+
+int b200exl3_linear_finish(const b200exl3_linear* h, const float* d_yhat, int64_t rows, int y_dtype, void* d_y,
+                           b200exl3_stream s) {
+    if (!h) return fail("NULL handle");
+    if (rows <= 0) return fail("EXL3 linear input cannot be empty");
+    if (!dtype_is_float(y_dtype)) return fail("unsupported output dtype %d", y_dtype);
+    if (!d_yhat || !d_y) return fail("NULL buffer");
+    if (!aligned16(d_yhat)) return fail("device pointers must be 16-byte aligned");
+    return check(launch_finish(d_yhat, 1, rows * h->out, h->svh, 1, h->bias, rows, h->out, y_dtype, d_y, as_stream(s)),
+                 "finish");
+}
+
+int b200exl3_linear_decode(const b200exl3_linear* h, uint16_t* d_w, b200exl3_stream s) {
+    if (!h) return fail("NULL handle");
+    return b200exl3_reconstruct(h->trellis, h->in, h->out, h->k, h->cb, d_w, s);
+}
+
+}  // extern "C"

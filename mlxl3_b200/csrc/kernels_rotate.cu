@@ -1,0 +1,75 @@
+// Input and output rotations of the EXL3 linear layer as stand-alone kernels
+// (reference: native/src/linear.rs:855-861 and 978-996; native/shaders/_lane_prologue.metal,
+// _lane_epilogue.metal, exl3.metal:204-235).  One warp per 128-block of one row.
+#include "hadamard.cuh"
+#include "kernels.h"
+
+namespace b200exl3 {
+
+__global__ void __launch_bounds__(256)
+prepare_kernel(const void* __restrict__ x, int x_dtype, const __half* __restrict__ suh, int64_t scale_rows,
+               int64_t rows, int in, __half* __restrict__ xhat) {
+    const int lane = threadIdx.x & 31;
+    const int blocks_per_row = in >> 7;
+    const int64_t total = rows * blocks_per_row;
+    for (int64_t unit = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); unit < total;
+         unit += static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5)) {
+        const int64_t row = unit / blocks_per_row;
+        const int col = static_cast<int>(unit % blocks_per_row) * 128 + lane * 4;
+        const __half* s = suh + (scale_rows == 1 ? 0 : row * in) + col;
+        __half h[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) h[j] = __hmul(load_as_half(x, x_dtype, row * in + col + j), s[j]);
+        warp_hadamard128_f16(h, lane);
+        *reinterpret_cast<uint2*>(xhat + row * in + col) = *reinterpret_cast<uint2*>(h);
+    }
+}
+
+__global__ void __launch_bounds__(256)
+finish_kernel(const float* __restrict__ partials, int splits, int64_t split_stride, const __half* __restrict__ svh,
+              int64_t scale_rows, const __half* __restrict__ bias, int64_t rows, int out, int y_dtype,
+              void* __restrict__ y) {
+    const int lane = threadIdx.x & 31;
+    const int blocks_per_row = out >> 7;
+    const int64_t total = rows * blocks_per_row;
+    for (int64_t unit = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); unit < total;
+         unit += static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5)) {
+        const int64_t row = unit / blocks_per_row;
+        const int col = static_cast<int>(unit % blocks_per_row) * 128 + lane * 4;
+        float4 acc = *reinterpret_cast<const float4*>(partials + row * out + col);
+        for (int s = 1; s < splits; ++s) {               // splits are added in order, in fp32
+            float4 p = *reinterpret_cast<const float4*>(partials + s * split_stride + row * out + col);
+            acc.x = __fadd_rn(acc.x, p.x); acc.y = __fadd_rn(acc.y, p.y);
+            acc.z = __fadd_rn(acc.z, p.z); acc.w = __fadd_rn(acc.w, p.w);
+        }
+        __half h[4] = {__float2half_rn(acc.x), __float2half_rn(acc.y), __float2half_rn(acc.z), __float2half_rn(acc.w)};
+        warp_hadamard128_f16(h, lane);
+        const __half* s = svh + (scale_rows == 1 ? 0 : row * out) + col;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) store_from_half(y, y_dtype, row * out + col + j, __hmul(h[j], s[j]), bias, col + j);
+    }
+}
+
+static unsigned grid_for(int64_t units) {
+    int64_t blocks = (units + 7) / 8;
+    int64_t cap = static_cast<int64_t>(kSmCount) * 8;
+    return static_cast<unsigned>(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
+}
+
+cudaError_t launch_prepare(const void* x, int x_dtype, const __half* suh, int64_t scale_rows, int64_t rows, int in,
+                           __half* xhat, cudaStream_t stream) {
+    if (rows == 0) return cudaSuccess;
+    prepare_kernel<<<grid_for(rows * (in / 128)), 256, 0, stream>>>(x, x_dtype, suh, scale_rows, rows, in, xhat);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_finish(const float* partials, int splits, int64_t split_stride, const __half* svh,
+                          int64_t scale_rows, const __half* bias, int64_t rows, int out, int y_dtype, void* y,
+                          cudaStream_t stream) {
+    if (rows == 0) return cudaSuccess;
+    finish_kernel<<<grid_for(rows * (out / 128)), 256, 0, stream>>>(partials, splits, split_stride, svh, scale_rows, bias,
+                                                                    rows, out, y_dtype, y);
+    return cudaGetLastError();
+}
+
+}  // namespace b200exl3

@@ -1,0 +1,160 @@
+"""``Exl3Linear`` -- the host-side mirror of the reference's quantized-linear operator
+(native/src/linear.rs:424-1236 of the reference) over the C ABI.
+
+Same construction arguments, the same validation and error wording, the same ``forward``
+contract: ``x`` of any rank with last dimension ``in`` and dtype f16 / f32 (bf16 as uint16 bits with
+``dtype=BF16``) gives ``y`` with the same leading dimensions and the same dtype.  All arithmetic
+runs in the CUDA library; there is no CPU path.
+"""
+from __future__ import annotations
+
+from ctypes import byref, c_size_t, c_void_p
+
+import numpy as np
+
+from . import _lib
+from ._lib import BF16, F16, F32, B200Exl3Error
+from .runtime import DEFAULT_STREAM, DeviceBuffer, Stream
+
+DEFAULT, MCG, MUL1 = 0, 1, 2
+
+
+def dtype_code(array: np.ndarray, dtype: int | None = None) -> int:
+    if dtype is not None:
+        if dtype == BF16 and array.dtype != np.uint16:
+            raise B200Exl3Error("bf16 data is passed as uint16 bit patterns")
+        return dtype
+    if array.dtype == np.float16:
+        return F16
+    if array.dtype == np.float32:
+        return F32
+    raise B200Exl3Error(f"unsupported EXL3 input dtype {array.dtype}")
+
+
+def _np_dtype(code: int):
+    return {F16: np.float16, F32: np.float32, BF16: np.uint16}[code]
+
+
+class Exl3Linear:
+    """One EXL3-quantized linear layer resident on the GPU.
+
+    ``Exl3Linear(trellis, suh, svh, bias, k, cb)`` follows ``Exl3Linear::new``
+    (native/src/linear.rs:577-639): ``trellis`` is ``[in/16, out/16, 16*k]`` int16/uint16, ``suh`` is
+    ``[in]``, ``svh`` and the optional ``bias`` are ``[out]`` (f16 or f32; bf16 as uint16 with
+    ``scale_dtype=BF16``), ``k`` in 1..8 and ``cb`` one of DEFAULT / MCG / MUL1.
+    """
+
+    def __init__(self, trellis: np.ndarray, suh: np.ndarray, svh: np.ndarray, bias: np.ndarray | None, k: int,
+                 cb: int = DEFAULT, *, scale_dtype: int | None = None, exact_weights: bool = False):
+        if not 1 <= k <= 8:
+            raise B200Exl3Error(f"K must be in 1..=8, got {k}")
+        if cb not in (DEFAULT, MCG, MUL1):
+            raise B200Exl3Error(f"invalid EXL3 codebook {cb}")
+        trellis = np.asarray(trellis)
+        if trellis.ndim != 3 or trellis.shape[2] != 16 * k or min(trellis.shape) <= 0:
+            raise B200Exl3Error("invalid trellis shape")
+        rows, cols = trellis.shape[0] * 16, trellis.shape[1] * 16
+        if rows % 128 or cols % 128:
+            raise B200Exl3Error("public EXL3 projections require 128-aligned dimensions")
+        suh, svh = np.asarray(suh), np.asarray(svh)
+        if suh.shape != (rows,) or svh.shape != (cols,):
+            raise B200Exl3Error("EXL3 scales have wrong dimensions")
+        if bias is not None and np.asarray(bias).shape != (cols,):
+            raise B200Exl3Error("EXL3 bias has wrong dimensions")
+        if trellis.dtype not in (np.uint16, np.int16):
+            raise B200Exl3Error("EXL3 trellis must contain 16-bit integers")
+        code = dtype_code(suh, scale_dtype)
+        cast = _np_dtype(code)
+        self.rows, self.cols, self.k, self.cb = rows, cols, k, cb
+        self._trellis = DeviceBuffer.from_numpy(trellis.view(np.uint16))
+        d_suh = DeviceBuffer.from_numpy(suh.astype(cast, copy=False))
+        d_svh = DeviceBuffer.from_numpy(svh.astype(cast, copy=False))
+        d_bias = DeviceBuffer.from_numpy(np.asarray(bias).astype(cast, copy=False)) if bias is not None else None
+        handle = c_void_p()
+        flags = _lib.EXACT_WEIGHTS if exact_weights else 0
+        _lib.call("b200exl3_linear_create", c_void_p(self._trellis.ptr), c_void_p(d_suh.ptr), c_void_p(d_svh.ptr),
+                  c_void_p(d_bias.ptr) if d_bias else None, code, rows, cols, k, cb, flags, byref(handle))
+        self.handle = handle.value
+        self._workspace: DeviceBuffer | None = None
+
+    # ---- reference accessors (native/src/linear.rs:655-660) ---------------------------------------
+    def input_dims(self) -> int:
+        return self.rows
+
+    def output_dims(self) -> int:
+        return self.cols
+
+    def workspace_bytes(self, rows: int) -> int:
+        out = c_size_t()
+        _lib.call("b200exl3_linear_workspace_bytes", c_void_p(self.handle), rows, byref(out))
+        return out.value
+
+    def _ensure_workspace(self, rows: int) -> DeviceBuffer:
+        need = self.workspace_bytes(rows)
+        if self._workspace is None or self._workspace.nbytes < need:
+            self._workspace = DeviceBuffer(need)
+        return self._workspace
+
+    # ---- device-pointer entry points (no host copies) ---------------------------------------------
+    def forward_device(self, d_x: int, dtype: int, rows: int, d_y: int, workspace: DeviceBuffer,
+                       stream: Stream = DEFAULT_STREAM) -> None:
+        _lib.call("b200exl3_linear_forward", c_void_p(self.handle), c_void_p(d_x), dtype, rows, c_void_p(d_y),
+                  c_void_p(workspace.ptr), workspace.nbytes, c_void_p(stream.handle))
+
+    def forward_partial_device(self, d_x: int, dtype: int, rows: int, d_yhat: int, workspace: DeviceBuffer,
+                               stream: Stream = DEFAULT_STREAM) -> None:
+        """Input rotation and product only: fp32 ``yhat[rows, out]`` of this (row-parallel) shard."""
+        _lib.call("b200exl3_linear_forward_partial", c_void_p(self.handle), c_void_p(d_x), dtype, rows, c_void_p(d_yhat),
+                  c_void_p(workspace.ptr), workspace.nbytes, c_void_p(stream.handle))
+
+    def finish_device(self, d_yhat: int, rows: int, dtype: int, d_y: int, stream: Stream = DEFAULT_STREAM) -> None:
+        """Output rotation, ``svh`` and bias applied to an (all-reduced) fp32 ``yhat``."""
+        _lib.call("b200exl3_linear_finish", c_void_p(self.handle), c_void_p(d_yhat), rows, dtype, c_void_p(d_y),
+                  c_void_p(stream.handle))
+
+    # ---- host-buffer entry points (what a caller with numpy arrays uses) --------------------------
+    def forward(self, x: np.ndarray, dtype: int | None = None, stream: Stream = DEFAULT_STREAM) -> np.ndarray:
+        """``Exl3Linear::forward`` (native/src/linear.rs:731-997) with host arrays in and out."""
+        x = np.asarray(x)
+        if x.ndim == 0 or x.shape[-1] != self.rows:
+            raise B200Exl3Error(f"invalid EXL3 linear input for {self.rows} inputs")
+        matrix_rows = x.size // self.rows
+        if matrix_rows <= 0:
+            raise B200Exl3Error("EXL3 linear input cannot be empty")
+        code = dtype_code(x, dtype)
+        x2 = np.ascontiguousarray(x).reshape(matrix_rows, self.rows)
+        d_x = DeviceBuffer.from_numpy(x2, stream)
+        d_y = DeviceBuffer(matrix_rows * self.cols * x2.dtype.itemsize)
+        self.forward_device(d_x.ptr, code, matrix_rows, d_y.ptr, self._ensure_workspace(matrix_rows), stream)
+        y = d_y.download((matrix_rows, self.cols), x2.dtype, stream)
+        return y.reshape(*x.shape[:-1], self.cols)
+
+    def forward_raw(self, xhat: np.ndarray, stream: Stream = DEFAULT_STREAM) -> np.ndarray:
+        """fp32 ``xhat @ W`` for already rotated fp16 inputs ``[rows, in]`` (no rotations, no scales)."""
+        xh = np.ascontiguousarray(xhat, np.float16)
+        if xh.ndim != 2 or xh.shape[1] != self.rows or xh.shape[0] == 0:
+            raise B200Exl3Error(f"invalid EXL3 linear input for {self.rows} inputs")
+        rows = xh.shape[0]
+        d_x = DeviceBuffer.from_numpy(xh, stream)
+        d_y = DeviceBuffer(rows * self.cols * 4)
+        ws = self._ensure_workspace(rows)
+        _lib.call("b200exl3_linear_forward_raw", c_void_p(self.handle), c_void_p(d_x.ptr), rows, c_void_p(d_y.ptr),
+                  c_void_p(ws.ptr), ws.nbytes, c_void_p(stream.handle))
+        return d_y.download((rows, self.cols), np.float32, stream)
+
+    def decode(self, stream: Stream = DEFAULT_STREAM) -> np.ndarray:
+        """Inner matrix ``W[in, out]`` as fp16 (``codec::reconstruct_inner``, native/src/codec.rs:159-190)."""
+        d_w = DeviceBuffer(self.rows * self.cols * 2)
+        _lib.call("b200exl3_linear_decode", c_void_p(self.handle), c_void_p(d_w.ptr), c_void_p(stream.handle))
+        return d_w.download((self.rows, self.cols), np.float16, stream)
+
+    def close(self) -> None:
+        if getattr(self, "handle", None):
+            _lib.load().b200exl3_linear_free(c_void_p(self.handle))
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
