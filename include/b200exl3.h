@@ -11,9 +11,11 @@
  *     10 = f32, 12 = bf16.
  * Differences forced by CUDA: tensors are caller-owned DEVICE pointers with explicit shapes
  * (the reference passes opaque lazy MLX arrays), every launch takes a cudaStream_t (passed as
- * void*), and forward calls allocate nothing: scratch memory is a caller-provided workspace.
- * All device pointers must be 16-byte aligned.  Handles are immutable after creation, so one
- * handle may be used from several threads and streams at once, each with its own workspace.
+ * void*), and forward calls allocate nothing: scratch memory is a caller-provided workspace whose
+ * first B200EXL3_WORKSPACE_HEADER_BYTES bytes were zeroed once.  All device pointers must be
+ * 16-byte aligned.  Handles are immutable after creation, so one handle may be used from several
+ * threads and streams at once, each with its own workspace; calls that share a workspace must be
+ * ordered on one stream.
  */
 #ifndef B200EXL3_H
 #define B200EXL3_H
@@ -32,8 +34,11 @@ extern "C" {
 #define B200EXL3_BF16 12
 
 /* flags of b200exl3_linear_create */
-#define B200EXL3_COPY_TRELLIS 1u   /* copy the trellis into library-owned memory (default: borrow the pointer) */
 #define B200EXL3_EXACT_WEIGHTS 2u  /* multiply with the bit-exact fp16 weight instead of its two fp16 halves */
+
+/* A workspace starts with this many bytes of arrival counters.  They must be zero before the first
+ * call that uses the workspace (b200exl3_memset); every call leaves them zero again. */
+#define B200EXL3_WORKSPACE_HEADER_BYTES 16384
 
 typedef struct b200exl3_linear b200exl3_linear;
 typedef void* b200exl3_stream;     /* cudaStream_t */
@@ -45,7 +50,9 @@ int b200exl3_init(int device);
 const char* b200exl3_last_error(void);
 /* major*10000 + minor*100 + patch */
 int b200exl3_version(void);
-/* Tuning knobs for experiments: "qmv_ctas_per_sm", "qmv_force_splits" (0 = heuristic). */
+/* Process-wide knobs: "qmv_ctas_per_sm" (CTAs per SM the grids are sized for), "qmv_force_splits"
+ * (0 = heuristic), "pdl" (1 = launch layer kernels with programmatic stream serialization, so the
+ * weight prefetch of a layer overlaps the tail of the previous kernel in the stream). */
 int b200exl3_set_option(const char* name, int64_t value);
 
 /* Plain device-memory plumbing for hosts that have no CUDA binding of their own (replaces
@@ -66,6 +73,15 @@ int b200exl3_event_destroy(void* event);
 int b200exl3_event_record(void* event, b200exl3_stream stream);
 /* Waits for `stop`, then returns the device time between the two events in milliseconds. */
 int b200exl3_event_elapsed_ms(void* start, void* stop, float* out_ms);
+
+/* Graph replay (replaces mlxl3_replay_capture / mlxl3_replay_apply / mlxl3_replay_free,
+ * native/ffi/mlx_bridge.cpp:150-175).  Every launch issued on `stream` between begin and end is
+ * recorded instead of run; the returned graph replays them with one launch.  Forward calls allocate
+ * nothing, so whole decode steps can be recorded; run each distinct call once before recording. */
+int b200exl3_graph_begin(b200exl3_stream stream);
+int b200exl3_graph_end(b200exl3_stream stream, void** out_graph);
+int b200exl3_graph_launch(void* graph, b200exl3_stream stream);
+int b200exl3_graph_free(void* graph);
 
 /* ---- codec (replaces exl3_decode / exl3_codebook of native/shaders/exl3.metal:102-114 and
  *      codec::unpack / decode_codeword / reconstruct_inner of native/src/codec.rs:52-71, 102-124, 159-190) ---- */
@@ -101,7 +117,10 @@ int b200exl3_finish(const float* d_partials, int splits, const uint16_t* d_svh_f
 /* Same validation as Exl3Linear::new (native/src/linear.rs:577-639): k in 1..8, codebook in 0..2
  * (0 default, 1 MCG, 2 MUL1), in and out positive multiples of 128, trellis [in/16, out/16, 16k]
  * 16-bit integers.  suh [in], svh [out] and the optional bias [out] are given in `scale_dtype`
- * (f16, bf16 or f32) and converted once to fp16, as the reference does at load. */
+ * (f16, bf16 or f32) and converted once to fp16, as the reference does at load.  The trellis is
+ * re-laid into library-owned memory (four neighbouring tiles interleaved word by word, same size;
+ * this replaces the loader's tile-layout preparation), so none of the caller's buffers is referenced
+ * after the call returns. */
 int b200exl3_linear_create(const uint16_t* d_trellis, const void* d_suh, const void* d_svh, const void* d_bias_or_null,
                            int scale_dtype, int in, int out, int k, int codebook, uint32_t flags,
                            b200exl3_linear** out_handle);

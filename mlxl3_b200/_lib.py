@@ -11,7 +11,8 @@ from pathlib import Path
 LIB_PATH = Path(__file__).resolve().parent / "libb200exl3.so"
 
 U16, U32, F16, F32, BF16 = 2, 3, 9, 10, 12
-COPY_TRELLIS, EXACT_WEIGHTS = 1, 2
+EXACT_WEIGHTS = 2
+WORKSPACE_HEADER_BYTES = 16384
 
 
 class B200Exl3Error(RuntimeError):
@@ -38,6 +39,10 @@ SIGNATURES = {
     "b200exl3_event_destroy": (c_int, [c_void_p]),
     "b200exl3_event_record": (c_int, [c_void_p, c_void_p]),
     "b200exl3_event_elapsed_ms": (c_int, [c_void_p, c_void_p, POINTER(c_float)]),
+    "b200exl3_graph_begin": (c_int, [c_void_p]),
+    "b200exl3_graph_end": (c_int, [c_void_p, POINTER(c_void_p)]),
+    "b200exl3_graph_launch": (c_int, [c_void_p, c_void_p]),
+    "b200exl3_graph_free": (c_int, [c_void_p]),
     "b200exl3_unpack_states": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "b200exl3_codebook": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p]),
     "b200exl3_reconstruct": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),

@@ -63,15 +63,15 @@ int valid_format(int k, int cb) {
     return 0;
 }
 
-constexpr int kMaxBatchRows = 32;   // rows handled by one launch of the fused product kernel
+constexpr int kMaxBatchRows = kQmvMaxRows;              // rows handled by one launch of the fused kernel
+constexpr size_t kCounterBytes = B200EXL3_WORKSPACE_HEADER_BYTES;   // arrival counters at the head of a workspace
 
 }  // namespace
 
 struct b200exl3_linear {
     int in, out, k, cb, device;
     uint32_t flags;
-    const uint16_t* trellis;
-    uint16_t* owned_trellis;
+    uint32_t* wq;       // weights in the quad layout, owned
     __half* suh;
     __half* svh;
     __half* bias;
@@ -95,12 +95,13 @@ int b200exl3_init(int device) {
 }
 
 int b200exl3_set_option(const char* name, int64_t value) {
-    static int ctas = 0, splits = 0;
+    static int ctas = 0, splits = 0, pdl = 0;
     if (!name) return fail("option name is NULL");
     if (!strcmp(name, "qmv_ctas_per_sm")) ctas = static_cast<int>(value);
     else if (!strcmp(name, "qmv_force_splits")) splits = static_cast<int>(value);
+    else if (!strcmp(name, "pdl")) pdl = static_cast<int>(value);
     else return fail("unknown option %s", name);
-    qmv_set_tuning(ctas, splits);
+    qmv_set_tuning(ctas, splits, pdl);
     return 0;
 }
 
@@ -157,6 +158,31 @@ int b200exl3_event_elapsed_ms(void* start, void* stop, float* out_ms) {
     B200_TRY(cudaEventSynchronize(static_cast<cudaEvent_t>(stop)), "cudaEventSynchronize");
     return check(cudaEventElapsedTime(out_ms, static_cast<cudaEvent_t>(start), static_cast<cudaEvent_t>(stop)),
                  "cudaEventElapsedTime");
+}
+
+/* ---- graph replay ------------------------------------------------------------------------------ */
+
+int b200exl3_graph_begin(b200exl3_stream s) {
+    return check(cudaStreamBeginCapture(as_stream(s), cudaStreamCaptureModeThreadLocal), "cudaStreamBeginCapture");
+}
+int b200exl3_graph_end(b200exl3_stream s, void** out_graph) {
+    if (!out_graph) return fail("out pointer is NULL");
+    *out_graph = nullptr;
+    cudaGraph_t graph = nullptr;
+    B200_TRY(cudaStreamEndCapture(as_stream(s), &graph), "cudaStreamEndCapture");
+    cudaGraphExec_t exec = nullptr;
+    cudaError_t e = cudaGraphInstantiate(&exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (check(e, "cudaGraphInstantiate")) return -1;
+    *out_graph = exec;
+    return 0;
+}
+int b200exl3_graph_launch(void* graph, b200exl3_stream s) {
+    if (!graph) return fail("NULL graph");
+    return check(cudaGraphLaunch(static_cast<cudaGraphExec_t>(graph), as_stream(s)), "cudaGraphLaunch");
+}
+int b200exl3_graph_free(void* graph) {
+    return graph ? check(cudaGraphExecDestroy(static_cast<cudaGraphExec_t>(graph)), "cudaGraphExecDestroy") : 0;
 }
 
 /* ---- codec ------------------------------------------------------------------------------------- */
@@ -226,6 +252,7 @@ int b200exl3_linear_create(const uint16_t* d_trellis, const void* d_suh, const v
     if (!d_suh || !d_svh) return fail("EXL3 scales have wrong dimensions");
     if (!dtype_is_float(scale_dtype)) return fail("unsupported scale dtype %d", scale_dtype);
     if (!aligned16(d_trellis)) return fail("device pointers must be 16-byte aligned");
+    if (out / 128 > static_cast<int>(kCounterBytes / sizeof(unsigned int))) return fail("output dimension %d is too large", out);
     b200exl3_linear* h = new (std::nothrow) b200exl3_linear{};
     if (!h) return fail("out of host memory");
     h->in = in; h->out = out; h->k = k; h->cb = cb; h->flags = flags;
@@ -238,13 +265,11 @@ int b200exl3_linear_create(const uint16_t* d_trellis, const void* d_suh, const v
     int rc = convert(d_suh, in, &h->suh);
     if (!rc) rc = convert(d_svh, out, &h->svh);
     if (!rc && d_bias) rc = convert(d_bias, out, &h->bias);
-    if (!rc && (flags & B200EXL3_COPY_TRELLIS)) {
+    if (!rc) {
         size_t bytes = static_cast<size_t>(in / 16) * (out / 16) * 16 * k * sizeof(uint16_t);
-        rc = check(cudaMalloc(&h->owned_trellis, bytes), "cudaMalloc(trellis)");
-        if (!rc) rc = check(cudaMemcpy(h->owned_trellis, d_trellis, bytes, cudaMemcpyDeviceToDevice), "copy trellis");
-        h->trellis = h->owned_trellis;
-    } else {
-        h->trellis = d_trellis;
+        rc = check(cudaMalloc(&h->wq, bytes), "cudaMalloc(weights)");
+        if (!rc) rc = check(launch_repack_quads(reinterpret_cast<const uint32_t*>(d_trellis), in / 16, out / 16, k, h->wq, 0),
+                            "repack weights");
     }
     if (!rc) rc = check(cudaDeviceSynchronize(), "linear_create");
     if (rc) {
@@ -260,27 +285,24 @@ void b200exl3_linear_free(b200exl3_linear* h) {
     cudaFree(h->suh);
     cudaFree(h->svh);
     cudaFree(h->bias);
-    cudaFree(h->owned_trellis);
+    cudaFree(h->wq);
     delete h;
 }
 
 int b200exl3_linear_input_dims(const b200exl3_linear* h) { return h ? h->in : fail("NULL handle"); }
 int b200exl3_linear_output_dims(const b200exl3_linear* h) { return h ? h->out : fail("NULL handle"); }
 
-static size_t xhat_bytes(const b200exl3_linear* h, int64_t rows) {
-    return round_up(static_cast<size_t>(rows) * h->in * sizeof(__half), 256);
-}
-
 int b200exl3_linear_workspace_bytes(const b200exl3_linear* h, int64_t rows, size_t* out_bytes) {
     if (!h || !out_bytes) return fail("NULL argument");
     if (rows <= 0) return fail("EXL3 linear input cannot be empty");
-    int64_t batch = rows < kMaxBatchRows ? rows : kMaxBatchRows;
-    QmvPlan plan = plan_qmv(h->in, h->out, h->k, batch);
-    *out_bytes = xhat_bytes(h, rows) + round_up(static_cast<size_t>(plan.splits) * batch * h->out * sizeof(float), 256);
+    QmvPlan plan = plan_qmv(h->in, h->out, h->k, rows);
+    *out_bytes = kCounterBytes + qmv_partial_bytes(plan, h->out, rows);
     return 0;
 }
 
-static int forward_common(const b200exl3_linear* h, const void* d_x, int x_dtype, const uint16_t* d_xhat_in, int64_t rows,
+// One fused launch per batch of up to kMaxBatchRows rows.  Exactly one of d_x / d_xhat is given;
+// d_y != nullptr selects the rotated output, otherwise the summed fp32 product goes to d_yhat.
+static int forward_common(const b200exl3_linear* h, const void* d_x, int x_dtype, const uint16_t* d_xhat, int64_t rows,
                           void* d_y, float* d_yhat, void* ws, size_t ws_bytes, cudaStream_t stream) {
     if (!h) return fail("NULL handle");
     if (rows <= 0) return fail("EXL3 linear input cannot be empty");
@@ -289,29 +311,26 @@ static int forward_common(const b200exl3_linear* h, const void* d_x, int x_dtype
     if (!ws || ws_bytes < need) return fail("workspace too small: %zu bytes given, %zu needed", ws_bytes, need);
     if (!aligned16(ws)) return fail("device pointers must be 16-byte aligned");
     char* base = static_cast<char*>(ws);
-    const __half* xhat = reinterpret_cast<const __half*>(d_xhat_in);
-    if (!xhat) {
-        __half* buf = reinterpret_cast<__half*>(base);
-        B200_TRY(launch_prepare(d_x, x_dtype, h->suh, 1, rows, h->in, buf, stream), "prepare");
-        xhat = buf;
-    }
-    float* partials = reinterpret_cast<float*>(base + xhat_bytes(h, rows));
     const bool exact = (h->flags & B200EXL3_EXACT_WEIGHTS) != 0;
+    const size_t x_size = dtype_size(x_dtype);
     for (int64_t r0 = 0; r0 < rows; r0 += kMaxBatchRows) {
-        int64_t n = rows - r0 < kMaxBatchRows ? rows - r0 : kMaxBatchRows;
-        QmvPlan plan = plan_qmv(h->in, h->out, h->k, n);
-        B200_TRY(launch_qmv(h->trellis, h->in, h->out, h->k, h->cb, xhat + r0 * h->in, n, exact, plan, partials, stream),
-                 "qmv");
-        if (d_yhat) {
-            int64_t count = n * h->out;
-            sum_partials_kernel<<<static_cast<unsigned>((count + 255) / 256), 256, 0, stream>>>(
-                partials, plan.splits, count, count, d_yhat + r0 * h->out);
-            B200_TRY(cudaGetLastError(), "sum partials");
-        } else {
-            char* y = static_cast<char*>(d_y) + static_cast<size_t>(r0) * h->out * dtype_size(x_dtype);
-            B200_TRY(launch_finish(partials, plan.splits, n * h->out, h->svh, 1, h->bias, n, h->out, x_dtype, y, stream),
-                     "finish");
-        }
+        const int64_t n = rows - r0 < kMaxBatchRows ? rows - r0 : kMaxBatchRows;
+        const QmvPlan plan = plan_qmv(h->in, h->out, h->k, n);
+        QmvArgs a{};
+        a.wq = h->wq;
+        a.x = d_x ? static_cast<const char*>(d_x) + static_cast<size_t>(r0) * h->in * x_size : nullptr;
+        a.suh = h->suh;
+        a.xhat = d_xhat ? reinterpret_cast<const __half*>(d_xhat) + r0 * h->in : nullptr;
+        a.counters = reinterpret_cast<unsigned int*>(base);
+        a.partials = reinterpret_cast<float*>(base + kCounterBytes);
+        a.svh = h->svh;
+        a.bias = h->bias;
+        a.y = d_y ? static_cast<char*>(d_y) + static_cast<size_t>(r0) * h->out * x_size : nullptr;
+        a.yhat = d_yhat ? d_yhat + r0 * h->out : nullptr;
+        a.x_dtype = x_dtype;
+        a.y_dtype = x_dtype;
+        a.in = h->in; a.out = h->out; a.rows = static_cast<int>(n);
+        B200_TRY(launch_qmv(a, h->k, h->cb, exact, plan, stream), "fused linear kernel");
     }
     return 0;
 }
@@ -350,7 +369,9 @@ int b200exl3_linear_finish(const b200exl3_linear* h, const float* d_yhat, int64_
 
 int b200exl3_linear_decode(const b200exl3_linear* h, uint16_t* d_w, b200exl3_stream s) {
     if (!h) return fail("NULL handle");
-    return b200exl3_reconstruct(h->trellis, h->in, h->out, h->k, h->cb, d_w, s);
+    if (!d_w || !aligned16(d_w)) return fail("device pointers must be 16-byte aligned");
+    return check(launch_reconstruct_quads(h->wq, h->in / 16, h->out / 16, h->k, h->cb, reinterpret_cast<__half*>(d_w),
+                                          as_stream(s)), "reconstruct");
 }
 
 }  // extern "C"

@@ -26,6 +26,19 @@ __device__ __forceinline__ uint32_t tile_state(const uint16_t* __restrict__ tile
     return static_cast<uint32_t>(merged >> shift) & 0xffffu;
 }
 
+// Same window with the tile's words `stride` apart (stride 4 = the quad layout of the fused kernels).
+__device__ __forceinline__ uint32_t tile_state_strided(const uint32_t* __restrict__ words, int stride, int k, int t) {
+    int b0 = t * k + k + 256 * k - 16;
+    int b1 = b0 + 16;
+    int nw = 8 * k;
+    int i0 = (b0 >> 5) % nw;
+    int last = (b1 - 1) >> 5;
+    int i1 = last % nw;
+    int shift = ((last + 1) << 5) - b1;
+    uint64_t merged = (static_cast<uint64_t>(words[i0 * stride]) << 32) | words[i1 * stride];
+    return static_cast<uint32_t>(merged >> shift) & 0xffffu;
+}
+
 // ---- codebooks ------------------------------------------------------------------------------------
 
 // Codebooks 0 and 1: the 32-bit pattern whose two fp16 halves add up to the weight.
@@ -51,7 +64,7 @@ __device__ __forceinline__ __half decode_codeword(uint32_t state) {
         return __hfma(h, __ushort_as_half(0x1eee), __ushort_as_half(0xc931));
     } else {
         uint32_t v = codeword_halves<CB>(state);
-        return __hadd(__ushort_as_half(static_cast<unsigned short>(v & 0xffffu)),
+        return __hadd_rn(__ushort_as_half(static_cast<unsigned short>(v & 0xffffu)),
                       __ushort_as_half(static_cast<unsigned short>(v >> 16)));
     }
 }
@@ -60,43 +73,6 @@ __device__ __forceinline__ __half decode_codeword_rt(uint32_t state, int cb) {
     if (cb == 0) return decode_codeword<0>(state);
     if (cb == 1) return decode_codeword<1>(state);
     return decode_codeword<2>(state);
-}
-
-// ---- lane windows: the eight states of lane `lane`, K known at compile time -------------------------
-//
-// The lane's states end at stream bit E = 8K(lane+1); together they span 7K+16 bits.  We take the
-// (up to three) words that end at the word holding bit E-1, shift the lane-dependent slack out
-// once, and then every state sits at a compile-time offset (7-j)*K from bit 0.
-template <int K>
-__device__ __forceinline__ void lane_states(const uint32_t* __restrict__ words, int lane, uint32_t (&st)[8]) {
-    constexpr int NW = 8 * K;
-    const int end = 8 * K * (lane + 1);
-    const int il = (end - 1) >> 5;
-    const int slack = ((il + 1) << 5) - end;          // 0..31, zero for K = 4 and K = 8
-    const uint32_t w2 = words[il];
-    const uint32_t w1 = words[il >= 1 ? il - 1 : il - 1 + NW];
-    uint32_t w0 = 0;
-    if constexpr (K >= 5) w0 = words[il >= 2 ? il - 2 : il - 2 + NW];
-    uint32_t n2, n1, n0;
-    if constexpr (K == 4 || K == 8) {
-        n2 = w2; n1 = w1; n0 = w0;
-    } else {
-        n2 = __funnelshift_r(w2, w1, slack);
-        n1 = __funnelshift_r(w1, w0, slack);
-        n0 = w0 >> slack;
-    }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        constexpr int dummy = 0; (void)dummy;
-        const int c = (7 - j) * K;                      // compile-time after unrolling
-        uint32_t v;
-        if (c + 16 <= 32) v = n2 >> c;
-        else if (c < 32) v = __funnelshift_r(n2, n1, c);
-        else if (c + 16 <= 64) v = n1 >> (c - 32);
-        else if (c < 64) v = __funnelshift_r(n1, n0, c - 32);
-        else v = n0 >> (c - 64);
-        st[j] = v & 0xffffu;
-    }
 }
 
 }  // namespace b200exl3

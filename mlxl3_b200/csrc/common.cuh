@@ -32,7 +32,7 @@ __device__ __forceinline__ __half load_as_half(const void* p, int dtype, int64_t
 // y.astype(x.dtype) then + bias, as native/src/linear.rs:990-996 orders it.
 __device__ __forceinline__ void store_from_half(void* p, int dtype, int64_t i, __half v, const __half* bias, int col) {
     if (dtype == kF16) {
-        reinterpret_cast<__half*>(p)[i] = bias ? __hadd(v, bias[col]) : v;
+        reinterpret_cast<__half*>(p)[i] = bias ? __hadd_rn(v, bias[col]) : v;
     } else if (dtype == kF32) {
         float f = __half2float(v);
         reinterpret_cast<float*>(p)[i] = bias ? __fadd_rn(f, __half2float(bias[col])) : f;

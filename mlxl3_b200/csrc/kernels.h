@@ -23,19 +23,52 @@ cudaError_t launch_finish(const float* partials, int splits, int64_t split_strid
                           int64_t scale_rows, const __half* bias, int64_t rows, int out, int y_dtype, void* y,
                           cudaStream_t stream);
 
-// ---- fused product (kernels_qmv.cu) ---------------------------------------------------------------
+// ---- fused linear layer (kernels_qmv*.cu) ----------------------------------------------------------
+constexpr int kQmvWarps = 8;         // warps per CTA
+constexpr int kQmvRedStride = 132;   // floats per reduced row: 128 + 4 keeps the fragment stores conflict-free
+constexpr int kQmvMaxRows = 32;      // activation rows one launch can take
+constexpr int kQmvMaxSmemBytes = 200 * 1024;
+
+// rows of 8 tiles kept in flight per warp
+__host__ __device__ constexpr int qmv_depth(int k) { return k <= 2 ? 8 : 4; }
+
+struct QmvArgs {
+    const uint32_t* wq;        // quad layout [tiles_k, tiles_n/4, 8K, 4] words
+    const void* x;             // [rows, in] activations in x_dtype (used when xhat == nullptr)
+    const __half* suh;         // [in]
+    const __half* xhat;        // [rows, in] already rotated activations, or nullptr
+    float* partials;           // [splits, rows, out] scratch (unused when splits == 1)
+    unsigned int* counters;    // [out/128] arrival counters, zero on entry and on exit
+    const __half* svh;         // [out]   (output rotation; used when y != nullptr)
+    const __half* bias;        // [out] or nullptr
+    void* y;                   // [rows, out] in y_dtype, or nullptr for raw output
+    float* yhat;               // [rows, out] summed fp32 product, written when y == nullptr
+    int x_dtype, y_dtype;
+    int in, out, rows, tiles_k, tiles_n, splits;
+    int xs_stride;             // halves per activation row in shared memory
+};
+
 struct QmvPlan {
-    int splits;          // split-K factor: partial sums per output element
-    int warps;           // warps per CTA
+    int splits;          // split-K factor: CTAs per 128-column block
     int col_blocks;      // out / 128
+    int xs_stride;       // halves per activation row in shared memory
     size_t smem_bytes;   // dynamic shared memory per CTA
+    bool pdl;            // launch with programmatic stream serialization (overlap with the previous kernel's tail)
 };
 QmvPlan plan_qmv(int in, int out, int k, int64_t rows);
-// partials[s, r, n] (fp32, r < rows <= 32) = sum over split s of xhat[r, :] . W[:, n]
+// Scratch a launch needs: counters first (zero-initialised once by the owner), then the partial sums.
+size_t qmv_counter_bytes(int out);
+size_t qmv_partial_bytes(const QmvPlan& plan, int out, int64_t rows);
 // exact: decode the reference's fp16 weight bit for bit before multiplying (codebooks 0/1 default to
 // feeding the two fp16 halves of a weight as two products, which differs by fp16 rounding of the weight).
-cudaError_t launch_qmv(const uint16_t* trellis, int in, int out, int k, int cb, const __half* xhat, int64_t rows,
-                       bool exact, const QmvPlan& plan, float* partials, cudaStream_t stream);
-void qmv_set_tuning(int ctas_per_sm, int force_splits);
+cudaError_t launch_qmv(QmvArgs args, int k, int cb, bool exact, const QmvPlan& plan, cudaStream_t stream);
+void qmv_set_tuning(int ctas_per_sm, int force_splits, int pdl);
+
+// ---- weight layout (kernels_codec.cu) -----------------------------------------------------------------
+// checkpoint layout [tiles_k, tiles_n, 8K] words -> quad layout [tiles_k, tiles_n/4, 8K, 4]
+cudaError_t launch_repack_quads(const uint32_t* trellis, int tiles_k, int tiles_n, int k, uint32_t* wq, cudaStream_t stream);
+// inner matrix from the quad layout, bit-exact
+cudaError_t launch_reconstruct_quads(const uint32_t* wq, int tiles_k, int tiles_n, int k, int cb, __half* w,
+                                     cudaStream_t stream);
 
 }  // namespace b200exl3

@@ -24,9 +24,11 @@ __global__ void codebook_kernel(const uint16_t* __restrict__ states, int64_t n, 
 
 // One CTA of 256 threads reconstructs a strip of 8 tiles: 16 rows x 128 columns of W.  Each warp
 // decodes one tile into shared memory in row-major order; the CTA then writes 16-byte pieces so
-// that every row segment (256 bytes) leaves as whole sectors.
+// that every row segment (256 bytes) leaves as whole sectors.  QUADS selects the weight layout:
+// false = checkpoint layout [tiles_k, tiles_n, 8K] words, true = quad layout [tiles_k, tiles_n/4, 8K, 4].
+template <bool QUADS>
 __global__ void __launch_bounds__(256)
-reconstruct_kernel(const uint16_t* __restrict__ trellis, int tiles_k, int tiles_n, int k, int cb,
+reconstruct_kernel(const uint32_t* __restrict__ trellis, int tiles_k, int tiles_n, int k, int cb,
                    __half* __restrict__ w) {
     __shared__ __align__(16) __half strip[16][128 + 8];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -35,11 +37,12 @@ reconstruct_kernel(const uint16_t* __restrict__ trellis, int tiles_k, int tiles_
     const int tn0 = (blockIdx.x % strips_n) * 8;
     const int tn = tn0 + warp;
     if (tn < tiles_n) {
-        const uint16_t* tile = trellis + (static_cast<int64_t>(tk) * tiles_n + tn) * 16 * k;
+        const int64_t tile = static_cast<int64_t>(tk) * tiles_n + tn;
+        const uint32_t* words = QUADS ? trellis + (tile >> 2) * (32 * k) + (tile & 3) : trellis + tile * (8 * k);
         const int r = (lane & 3) * 2, c = lane >> 2;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            uint32_t s = tile_state(tile, k, lane * 8 + j);
+            uint32_t s = tile_state_strided(words, QUADS ? 4 : 1, k, lane * 8 + j);
             int row = r + (j & 1) + ((j & 2) ? 8 : 0);
             int col = c + ((j & 4) ? 8 : 0);
             strip[row][warp * 16 + col] = decode_codeword_rt(s, cb);
@@ -53,6 +56,18 @@ reconstruct_kernel(const uint16_t* __restrict__ trellis, int tiles_k, int tiles_
         uint4 v = *reinterpret_cast<const uint4*>(&strip[row][piece * 8]);
         *reinterpret_cast<uint4*>(w + (static_cast<int64_t>(tk) * 16 + row) * out + col) = v;
     }
+}
+
+// One thread per 16-byte chunk of the quad layout: word w of four neighbouring tiles.
+__global__ void repack_quads_kernel(const uint32_t* __restrict__ trellis, int64_t quads, int k, uint32_t* __restrict__ wq) {
+    const int64_t chunk = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const int nw = 8 * k;
+    if (chunk >= quads * nw) return;
+    const int64_t quad = chunk / nw;
+    const int wi = static_cast<int>(chunk % nw);
+    const uint32_t* src = trellis + quad * 4 * nw + wi;
+    uint4 v = make_uint4(src[0], src[nw], src[2 * nw], src[3 * nw]);
+    reinterpret_cast<uint4*>(wq)[chunk] = v;
 }
 
 cudaError_t launch_unpack_states(const uint16_t* packed, int64_t tiles, int k, int cb, uint16_t* states, __half* values,
@@ -73,7 +88,24 @@ cudaError_t launch_reconstruct(const uint16_t* trellis, int tiles_k, int tiles_n
                                cudaStream_t stream) {
     int64_t blocks = static_cast<int64_t>(tiles_k) * ((tiles_n + 7) / 8);
     if (blocks == 0) return cudaSuccess;
-    reconstruct_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(trellis, tiles_k, tiles_n, k, cb, w);
+    reconstruct_kernel<false><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+        reinterpret_cast<const uint32_t*>(trellis), tiles_k, tiles_n, k, cb, w);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_reconstruct_quads(const uint32_t* wq, int tiles_k, int tiles_n, int k, int cb, __half* w,
+                                     cudaStream_t stream) {
+    int64_t blocks = static_cast<int64_t>(tiles_k) * ((tiles_n + 7) / 8);
+    if (blocks == 0) return cudaSuccess;
+    reconstruct_kernel<true><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(wq, tiles_k, tiles_n, k, cb, w);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_repack_quads(const uint32_t* trellis, int tiles_k, int tiles_n, int k, uint32_t* wq, cudaStream_t stream) {
+    const int64_t quads = static_cast<int64_t>(tiles_k) * (tiles_n / 4);
+    const int64_t chunks = quads * 8 * k;
+    if (chunks == 0) return cudaSuccess;
+    repack_quads_kernel<<<static_cast<unsigned>((chunks + 255) / 256), 256, 0, stream>>>(trellis, quads, k, wq);
     return cudaGetLastError();
 }
 

@@ -1,187 +1,304 @@
-// Fused trellis-decode x activation product for up to 32 activation rows (QMV and small-batch QMM).
+// Fused EXL3 linear layer for up to 32 activation rows (QMV and small-batch QMM) in ONE launch:
+// input rotation -> trellis decode x activation product -> split reduction -> output rotation.
 //
 // Reference behaviour replaced: native/shaders/_qmv_tile_kernel.metal (M = 1 and the MB row-sharing
-// layouts) driven by native/src/linear.rs:934-955 and 1138-1175.  Output: fp32 partial sums
-// partials[split, row, n] = sum_{k in split} float(xhat[row, k]) * W[k, n].
+// layouts) with its prologue / epilogue kernels (_lane_prologue.metal, _lane_epilogue.metal), driven
+// by native/src/linear.rs:847-996 and 1024-1216.
 //
-// Design (B200): the kernel is bound by HBM bandwidth and by the integer work of the decode, so
-//  * packed trellis words are staged with 16-byte cp.async copies into a per-warp ring in shared
-//    memory (no registers held by loads in flight, every byte read once);
-//  * each warp decodes a 16x16 tile in registers: lane L owns states 8L..8L+7, which are exactly
-//    the A-fragment of mma.m16n8k16 for W^T (rows = output columns, cols = inputs);
-//  * the multiply by the activations runs on the tensor cores with the activation rows in the
-//    n dimension, so 1..8 rows cost the same and the fp32 accumulators live in the MMA fragment;
-//  * for codebooks 0 and 1 the weight is lo + hi of two fp16 halves; in the default "split" mode
-//    the two halves are fed as two k elements against a duplicated activation, which removes the
-//    fp16 add from the decode (x*(lo+hi) = x*lo + x*hi, accumulated in fp32).  "exact" mode adds
-//    the halves first and reproduces the reference's fp16 weight bit for bit;
-//  * work is cut into units of one tile; a CTA owns one 128-column block and one contiguous slice
-//    of that block's tiles_k*8 units, and its warps own equal contiguous sub-slices, so the load
-//    is balanced to one tile whatever the shape.
+// Design (B200).  The layer is bound by HBM bandwidth and, at low K, by the integer work of the
+// decode (about 30 instructions per 16x16 tile is the floor), so everything that is not decode is
+// kept off the issue slots:
+//  * weights live in a "quad" layout made once at load (4 neighbouring tiles interleaved word by
+//    word), so one 16-byte shared-memory load gives a lane its stream word for four tiles;
+//  * packed words are staged with 16-byte cp.async copies into a per-warp ring in shared memory,
+//    issued before anything that depends on the activations;
+//  * lane L owns states 8L..8L+7 of a tile, which are exactly the A-fragment of mma.m16n8k16 for
+//    W^T; the product runs on the tensor cores with the activation rows in the n dimension, so
+//    1..8 rows cost the same and the fp32 accumulators are the MMA fragment;
+//  * codebooks 0/1: the weight is lo + hi of two fp16 halves of a 32-bit hash.  In the default
+//    "split" mode the halves are fed as two k elements against a duplicated activation
+//    (x*lo + x*hi in fp32), which removes the fp16 add; "exact" mode adds the halves first and
+//    reproduces the reference's fp16 weight bit for bit;
+//  * for K = 4 and K = 8 two states 16 bits apart share a register P = lo | hi << 16; then
+//    b_hi = (P >> 16) * M + C,  T = P * M + (C + (C << 16)),  b_lo = T - (b_hi << 16)
+//    hashes both without masking the low state (integer multiply-add pipe instead of the ALU pipe);
+//  * a CTA owns one 128-column block and a contiguous slice of that block's tiles; its warps own
+//    equal contiguous sub-slices (balanced to one tile).  The activations of the slice are rotated
+//    into shared memory by the CTA itself; the last CTA to finish a column block sums the split
+//    partials in a fixed order and applies the output rotation.
 //
 // Included by one small translation unit per K so the eight K values compile in parallel.
 #pragma once
 
 #include "codec.cuh"
+#include "hadamard.cuh"
 #include "kernels.h"
 
 namespace b200exl3 {
 
-// rows of 8 tiles kept in flight per warp
-__host__ __device__ constexpr int qmv_depth(int k) { return k <= 2 ? 8 : 4; }
+// ---- hash of the eight states of a lane -------------------------------------------------------------
 
-constexpr int kQmvRedStride = 132;   // floats per reduced row: 128 + 4 keeps the fragment stores conflict-free
+template <int CB>
+__device__ __forceinline__ constexpr uint32_t hash_mul() { return CB == 0 ? 89226354u : (CB == 1 ? 0xcbac1fedu : 0x83dcd12du); }
+template <int CB>
+__device__ __forceinline__ constexpr uint32_t hash_add() { return CB == 0 ? 64248484u : 0u; }
 
-struct QmvParams {
-    const uint32_t* trellis;   // [tiles_k, tiles_n, 8K] words
-    const __half* xhat;        // [rows, in]
-    float* partials;           // [splits, rows, out]
-    int in, out, rows, tiles_k, tiles_n, splits;
-};
-
-template <int K>
-__device__ __forceinline__ void qmv_issue_row(const uint32_t* __restrict__ trellis, int tiles_n, int tk, int tn0,
-                                              int lo, int hi, uint32_t* slot, int lane) {
-    constexpr int kChunksPerTile = 2 * K;                  // 16-byte chunks
-    const char* src = reinterpret_cast<const char*>(trellis + (static_cast<int64_t>(tk) * tiles_n + tn0) * (8 * K));
-    char* dst = reinterpret_cast<char*>(slot);
+// b[j] = state_j * M + C for the lane's states j = 0..7 (32-bit wrap-around).  (w0:w1:w2) are the
+// stream words that end at the word holding the lane's last bit; `slack` bits of w2 lie past it.
+template <int K, int CB>
+__device__ __forceinline__ void lane_hashes(uint32_t w2, uint32_t w1, uint32_t w0, int slack, uint32_t (&b)[8]) {
+    constexpr uint32_t M = hash_mul<CB>(), C = hash_add<CB>();
+    if constexpr (K == 4 || K == 8) {
+        uint32_t P[4];
+        if constexpr (K == 4) {
+            // states at bit offsets 0,4,...,28: P[p] = {offset 4p (state 7-p), offset 4p+16 (state 3-p)}
+            P[0] = w2; P[1] = __funnelshift_r(w2, w1, 4); P[2] = __funnelshift_r(w2, w1, 8); P[3] = __funnelshift_r(w2, w1, 12);
+        } else {
+            // states at bit offsets 0,8,...,56: {0,16} {8,24} {32,48} {40,56} = states {7,5} {6,4} {3,1} {2,0}
+            P[0] = w2; P[1] = __funnelshift_r(w2, w1, 8);
+            P[2] = w1; P[3] = __funnelshift_r(w1, w0, 8);
+        }
+        constexpr uint32_t C2 = C + (C << 16);
 #pragma unroll
-    for (int c = lane; c < 8 * kChunksPerTile; c += 32) {
-        int tile = c / kChunksPerTile;
-        if (tile >= lo && tile < hi) cp_async_16(dst + c * 16, src + c * 16);
+        for (int p = 0; p < 4; ++p) {
+            const uint32_t hi = P[p] >> 16;
+            const uint32_t bh = hi * M + C;
+            const uint32_t t = P[p] * M + C2;
+            const uint32_t bl = bh * 0xffff0000u + t;
+            if constexpr (K == 4) {
+                b[7 - p] = bl; b[3 - p] = bh;
+            } else {
+                const int jl = p == 0 ? 7 : (p == 1 ? 6 : (p == 2 ? 3 : 2));
+                b[jl] = bl; b[jl - 2] = bh;
+            }
+        }
+    } else {
+        const uint32_t n2 = __funnelshift_r(w2, w1, slack);
+        const uint32_t n1 = __funnelshift_r(w1, w0, slack);
+        const uint32_t n0 = w0 >> slack;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int c = (7 - j) * K;
+            uint32_t v;
+            if (c + 16 <= 32) v = n2 >> c;
+            else if (c < 32) v = __funnelshift_r(n2, n1, c);
+            else if (c + 16 <= 64) v = n1 >> (c - 32);
+            else if (c < 64) v = __funnelshift_r(n1, n0, c - 32);
+            else v = n0 >> (c - 64);
+            b[j] = (v & 0xffffu) * M + C;
+        }
     }
 }
 
-// MODE 0: codebook 0/1, split halves.  MODE 1: exact fp16 weights (all codebooks).
-template <int K, int CB, int NB, int MODE, int WARPS>
-__global__ void __launch_bounds__(WARPS * 32)
-qmv_kernel(const QmvParams p) {
+// Per-lane geometry of the stream words, constant for the whole kernel.
+template <int K>
+struct LaneGeom {
+    int i2, i1, i0, slack;     // word indices inside a tile; bits of word i2 that lie past the lane's last bit
+    __device__ __forceinline__ explicit LaneGeom(int lane) {
+        constexpr int NW = 8 * K;
+        const int end = 8 * K * (lane + 1);
+        i2 = (end - 1) >> 5;
+        slack = ((i2 + 1) << 5) - end;
+        i1 = i2 >= 1 ? i2 - 1 : i2 - 1 + NW;
+        i0 = i2 >= 2 ? i2 - 2 : i2 - 2 + NW;
+    }
+};
+
+// One tile: decode the lane's eight weights and issue the MMAs against the activation fragments.
+// MODE 0: codebook 0/1, split halves (2 MMAs per 8 rows).  MODE 1: exact fp16 weights (1 MMA per 8 rows).
+template <int K, int CB, int NB, int MODE>
+__device__ __forceinline__ void tile_mma(uint32_t w2, uint32_t w1, uint32_t w0, int slack, const uint32_t (&bx)[NB][4],
+                                         float (&acc)[NB][4]) {
+    uint32_t b[8];
+    lane_hashes<K, CB>(w2, w1, w0, slack, b);
+    if constexpr (MODE == 0) {
+        uint32_t a[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a[j] = lop3_and_xor(b[j], 0x8fff8fffu, 0x3b603b60u);
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+            mma_16816(acc[nb], a[0], a[4], a[1], a[5], bx[nb][0], bx[nb][1]);
+            mma_16816(acc[nb], a[2], a[6], a[3], a[7], bx[nb][2], bx[nb][3]);
+        }
+    } else {
+        uint32_t a0, a1, a2, a3;
+        if constexpr (CB == 2) {
+            const __half2 inv = __half2half2(__ushort_as_half(0x1eee));
+            const __half2 bias = __half2half2(__ushort_as_half(0xc931));
+            auto pair = [&](uint32_t x, uint32_t y) {
+                uint32_t v = prmt(__dp4a(x, 0x01010101u, 0x6400u), __dp4a(y, 0x01010101u, 0x6400u), 0x5410);
+                __half2 w = __hfma2(*reinterpret_cast<__half2*>(&v), inv, bias);
+                return *reinterpret_cast<uint32_t*>(&w);
+            };
+            a0 = pair(b[0], b[1]); a1 = pair(b[4], b[5]); a2 = pair(b[2], b[3]); a3 = pair(b[6], b[7]);
+        } else {
+            auto pair = [&](uint32_t x, uint32_t y) {
+                x = lop3_and_xor(x, 0x8fff8fffu, 0x3b603b60u);
+                y = lop3_and_xor(y, 0x8fff8fffu, 0x3b603b60u);
+                uint32_t lo2 = prmt(x, y, 0x5410), hi2 = prmt(x, y, 0x7632);
+                __half2 w = __hadd2_rn(*reinterpret_cast<__half2*>(&lo2), *reinterpret_cast<__half2*>(&hi2));
+                return *reinterpret_cast<uint32_t*>(&w);
+            };
+            a0 = pair(b[0], b[1]); a1 = pair(b[4], b[5]); a2 = pair(b[2], b[3]); a3 = pair(b[6], b[7]);
+        }
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) mma_16816(acc[nb], a0, a1, a2, a3, bx[nb][0], bx[nb][1]);
+    }
+}
+
+// Copies the needed quads (those touching tiles [lo, hi) of the row) of one 8-tile row into a ring slot.
+template <int K>
+__device__ __forceinline__ void qmv_issue_row(const uint32_t* __restrict__ wq, int tiles_n, int tk, int tn0, int lo,
+                                              int hi, uint32_t* slot, int lane) {
+    constexpr int kChunksPerQuad = 8 * K;                   // 16-byte chunks: one per stream word
+    const char* src = reinterpret_cast<const char*>(wq + (static_cast<int64_t>(tk) * tiles_n + tn0) * (8 * K));
+    char* dst = reinterpret_cast<char*>(slot);
+#pragma unroll
+    for (int c = lane; c < 2 * kChunksPerQuad; c += 32) {
+        const int quad = c / kChunksPerQuad;
+        if (lo < 4 * quad + 4 && hi > 4 * quad) cp_async_16(dst + c * 16, src + c * 16);
+    }
+}
+
+template <int K, int CB, int NB, int MODE>
+__global__ void __launch_bounds__(kQmvWarps * 32)
+qmv_kernel(const QmvArgs p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    constexpr int kRowWords = 64 * K;                      // 8 tiles x 8K words
+    constexpr int WARPS = kQmvWarps;
+    constexpr int DEPTH = qmv_depth(K);
+    constexpr int kRowWords = 64 * K;                       // 2 quads x 8K words x 4 tiles
+    constexpr int kRingBytes = WARPS * DEPTH * kRowWords * 4;
+    __shared__ int s_last;
+
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, q = lane & 3;
     const int col_blocks = p.out >> 7;
     const int cblock = blockIdx.x % col_blocks;
     const int split = blockIdx.x / col_blocks;
     const int tn0 = cblock * 8;
-    constexpr int DEPTH = qmv_depth(K);
+    const int rows = p.rows;
 
-    // unit range of this CTA, then of this warp
+    // unit (= tile) range of this CTA inside its column block, then of this warp
     const int units = p.tiles_k * 8;
     const int cta_u0 = static_cast<int>(static_cast<int64_t>(units) * split / p.splits);
     const int cta_u1 = static_cast<int>(static_cast<int64_t>(units) * (split + 1) / p.splits);
     const int cta_n = cta_u1 - cta_u0;
     const int u0 = cta_u0 + static_cast<int>(static_cast<int64_t>(cta_n) * warp / WARPS);
     const int u1 = cta_u0 + static_cast<int>(static_cast<int64_t>(cta_n) * (warp + 1) / WARPS);
-
-    float acc[NB][8][4];
-#pragma unroll
-    for (int nb = 0; nb < NB; ++nb)
-#pragma unroll
-        for (int t = 0; t < 8; ++t)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) acc[nb][t][i] = 0.0f;
+    const int tk_first = u0 >> 3;
+    const int nrows = u1 > u0 ? ((u1 - 1) >> 3) - tk_first + 1 : 0;
 
     uint32_t* ring = reinterpret_cast<uint32_t*>(smem_raw) + static_cast<size_t>(warp) * DEPTH * kRowWords;
+    __half* xs = reinterpret_cast<__half*>(smem_raw + kRingBytes);     // [rows][xs_stride]
 
-    if (u1 > u0) {
-        const int tk_first = u0 >> 3, tk_last = (u1 - 1) >> 3;
-        const int nrows = tk_last - tk_first + 1;
-        for (int i = 0; i < DEPTH; ++i) {
-            if (i < nrows) {
-                int tk = tk_first + i;
-                qmv_issue_row<K>(p.trellis, p.tiles_n, tk, tn0, max(u0 - 8 * tk, 0), min(u1 - 8 * tk, 8),
-                                 ring + i * kRowWords, lane);
-            }
-            cp_async_commit();
+    // ---- phase 0: start streaming weights (they do not depend on the previous kernel) ----------------
+#pragma unroll
+    for (int i = 0; i < DEPTH; ++i) {
+        if (i < nrows) {
+            const int tk = tk_first + i;
+            qmv_issue_row<K>(p.wq, p.tiles_n, tk, tn0, max(u0 - 8 * tk, 0), min(u1 - 8 * tk, 8), ring + i * kRowWords, lane);
         }
-        int slot = 0;
-        for (int r = 0; r < nrows; ++r) {
-            const int tk = tk_first + r;
-            // activation fragments for this input tile: rows nb*8+g, inputs 16tk + {2q,2q+1,2q+8,2q+9}
-            uint32_t bx[NB][4];
-#pragma unroll
-            for (int nb = 0; nb < NB; ++nb) {
-                const int row = nb * 8 + g;
-                uint32_t p0 = 0, p1 = 0;
-                if (row < p.rows) {
-                    const uint32_t* xr = reinterpret_cast<const uint32_t*>(p.xhat + static_cast<int64_t>(row) * p.in + tk * 16);
-                    p0 = __ldg(xr + q);
-                    p1 = __ldg(xr + q + 4);
-                }
-                if constexpr (MODE == 0) {
-                    bx[nb][0] = prmt(p0, p0, 0x1010); bx[nb][1] = prmt(p0, p0, 0x3232);
-                    bx[nb][2] = prmt(p1, p1, 0x1010); bx[nb][3] = prmt(p1, p1, 0x3232);
-                } else {
-                    bx[nb][0] = p0; bx[nb][1] = p1; bx[nb][2] = 0; bx[nb][3] = 0;
-                }
-            }
-            // every iteration commits one group, so row r's group is complete once at most
-            // DEPTH-1 newer groups are pending
-            cp_async_wait<DEPTH - 1>();
-            __syncwarp();
-            const uint32_t* row_words = ring + slot * kRowWords;
-            const int lo = max(u0 - 8 * tk, 0), hi = min(u1 - 8 * tk, 8);
-#pragma unroll
-            for (int t = 0; t < 8; ++t) {
-                if (t >= lo && t < hi) {
-                    uint32_t st[8];
-                    lane_states<K>(row_words + t * (8 * K), lane, st);
-                    if constexpr (MODE == 0) {
-                        uint32_t a[8];
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) a[j] = codeword_halves<CB>(st[j]);
-#pragma unroll
-                        for (int nb = 0; nb < NB; ++nb) {
-                            mma_16816(acc[nb][t], a[0], a[4], a[1], a[5], bx[nb][0], bx[nb][1]);
-                            mma_16816(acc[nb][t], a[2], a[6], a[3], a[7], bx[nb][2], bx[nb][3]);
-                        }
-                    } else {
-                        uint32_t a0, a1, a2, a3;
-                        if constexpr (CB == 2) {
-                            uint32_t s[8];
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) s[j] = mul1_sum_bits(st[j]);
-                            const __half2 inv = __half2half2(__ushort_as_half(0x1eee));
-                            const __half2 bias = __half2half2(__ushort_as_half(0xc931));
-                            auto pair = [&](uint32_t x, uint32_t y) {
-                                uint32_t v = prmt(x, y, 0x5410);
-                                __half2 w = __hfma2(*reinterpret_cast<__half2*>(&v), inv, bias);
-                                return *reinterpret_cast<uint32_t*>(&w);
-                            };
-                            a0 = pair(s[0], s[1]); a1 = pair(s[4], s[5]); a2 = pair(s[2], s[3]); a3 = pair(s[6], s[7]);
-                        } else {
-                            uint32_t v[8];
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) v[j] = codeword_halves<CB>(st[j]);
-                            auto pair = [&](uint32_t x, uint32_t y) {
-                                uint32_t lo2 = prmt(x, y, 0x5410), hi2 = prmt(x, y, 0x7632);
-                                __half2 w = __hadd2(*reinterpret_cast<__half2*>(&lo2), *reinterpret_cast<__half2*>(&hi2));
-                                return *reinterpret_cast<uint32_t*>(&w);
-                            };
-                            a0 = pair(v[0], v[1]); a1 = pair(v[4], v[5]); a2 = pair(v[2], v[3]); a3 = pair(v[6], v[7]);
-                        }
-#pragma unroll
-                        for (int nb = 0; nb < NB; ++nb) mma_16816(acc[nb][t], a0, a1, a2, a3, bx[nb][0], bx[nb][1]);
-                    }
-                }
-            }
-            __syncwarp();
-            if (r + DEPTH < nrows) {
-                int tkn = tk + DEPTH;
-                qmv_issue_row<K>(p.trellis, p.tiles_n, tkn, tn0, max(u0 - 8 * tkn, 0), min(u1 - 8 * tkn, 8),
-                                 ring + slot * kRowWords, lane);
-            }
-            cp_async_commit();
-            slot = slot + 1 == DEPTH ? 0 : slot + 1;
-        }
-        cp_async_wait<0>();
+        cp_async_commit();
     }
+    pdl_launch_dependents();
+    pdl_wait();
 
-    // ---- deterministic tree reduction over the warps, then coalesced store of the partial sums ----
-    __syncthreads();                                        // the ring is dead from here on
+    // ---- phase 1: rotate (or fetch) the activations of this CTA's input range into shared memory ---
+    const int kb0 = cta_n > 0 ? (cta_u0 >> 3) >> 3 : 0;                         // first 128-block
+    const int kb1 = cta_n > 0 ? ((((cta_u1 - 1) >> 3) >> 3) + 1) : 0;           // one past the last
+    {
+        const int nblk = kb1 - kb0;
+        for (int unit = warp; unit < rows * nblk; unit += WARPS) {
+            const int row = unit / nblk, blk = unit % nblk;
+            const int col = (kb0 + blk) * 128 + lane * 4;
+            __align__(8) __half h[4];
+            if (p.xhat) {
+                *reinterpret_cast<uint2*>(h) = *reinterpret_cast<const uint2*>(p.xhat + static_cast<int64_t>(row) * p.in + col);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    h[j] = __hmul_rn(load_as_half(p.x, p.x_dtype, static_cast<int64_t>(row) * p.in + col + j), p.suh[col + j]);
+                warp_hadamard128_f16(h, lane);
+            }
+            *reinterpret_cast<uint2*>(xs + row * p.xs_stride + blk * 128 + lane * 4) = *reinterpret_cast<uint2*>(h);
+        }
+    }
+    __syncthreads();
+
+    // ---- phase 2: decode x activations ----------------------------------------------------------------
+    float acc[8][NB][4];
+#pragma unroll
+    for (int t = 0; t < 8; ++t)
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[t][nb][i] = 0.0f;
+
+    const LaneGeom<K> geom(lane);
+    int slot = 0;
+    for (int r = 0; r < nrows; ++r) {
+        const int tk = tk_first + r;
+        // activation fragments: rows nb*8+g, inputs 16tk + {2q, 2q+1, 2q+8, 2q+9}
+        uint32_t bx[NB][4];
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+            const int row = nb * 8 + g;
+            uint32_t p0 = 0, p1 = 0;
+            if (row < rows) {
+                const uint32_t* xr = reinterpret_cast<const uint32_t*>(xs + row * p.xs_stride + (tk * 16 - kb0 * 128));
+                p0 = xr[q];
+                p1 = xr[q + 4];
+            }
+            if constexpr (MODE == 0) {
+                bx[nb][0] = prmt(p0, p0, 0x1010); bx[nb][1] = prmt(p0, p0, 0x3232);
+                bx[nb][2] = prmt(p1, p1, 0x1010); bx[nb][3] = prmt(p1, p1, 0x3232);
+            } else {
+                bx[nb][0] = p0; bx[nb][1] = p1; bx[nb][2] = 0; bx[nb][3] = 0;
+            }
+        }
+        // every iteration commits one group, so row r's group is complete once at most DEPTH-1 newer
+        // groups are pending
+        cp_async_wait<DEPTH - 1>();
+        __syncwarp();
+        const uint32_t* row_words = ring + slot * kRowWords;
+        const int lo = max(u0 - 8 * tk, 0), hi = min(u1 - 8 * tk, 8);
+        const bool full = lo == 0 && hi == 8;
+#pragma unroll
+        for (int quad = 0; quad < 2; ++quad) {
+            if (full || (lo < 4 * quad + 4 && hi > 4 * quad)) {
+                const uint4* qw = reinterpret_cast<const uint4*>(row_words + quad * (32 * K));
+                const uint4 W2 = qw[geom.i2];
+                const uint4 W1 = qw[geom.i1];
+                uint4 W0 = make_uint4(0, 0, 0, 0);
+                if constexpr (K >= 5) W0 = qw[geom.i0];
+                const uint32_t w2[4] = {W2.x, W2.y, W2.z, W2.w}, w1[4] = {W1.x, W1.y, W1.z, W1.w},
+                               w0[4] = {W0.x, W0.y, W0.z, W0.w};
+                if (full) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        tile_mma<K, CB, NB, MODE>(w2[j], w1[j], w0[j], geom.slack, bx, acc[quad * 4 + j]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        if (quad * 4 + j >= lo && quad * 4 + j < hi)
+                            tile_mma<K, CB, NB, MODE>(w2[j], w1[j], w0[j], geom.slack, bx, acc[quad * 4 + j]);
+                }
+            }
+        }
+        __syncwarp();
+        if (r + DEPTH < nrows) {
+            const int tkn = tk + DEPTH;
+            qmv_issue_row<K>(p.wq, p.tiles_n, tkn, tn0, max(u0 - 8 * tkn, 0), min(u1 - 8 * tkn, 8),
+                             ring + slot * kRowWords, lane);
+        }
+        cp_async_commit();
+        slot = slot + 1 == DEPTH ? 0 : slot + 1;
+    }
+    cp_async_wait<0>();
+
+    // ---- phase 3: deterministic tree reduction over the warps -------------------------------------------
+    __syncthreads();                                        // ring and activations are dead from here on
     float* red = reinterpret_cast<float*>(smem_raw);
-    const int rows = p.rows;
     auto frag_store = [&](float* base) {
 #pragma unroll
         for (int nb = 0; nb < NB; ++nb)
@@ -189,8 +306,8 @@ qmv_kernel(const QmvParams p) {
             for (int t = 0; t < 8; ++t)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    int row = nb * 8 + 2 * q + (i & 1), col = t * 16 + g + ((i & 2) ? 8 : 0);
-                    if (row < rows) base[row * kQmvRedStride + col] = acc[nb][t][i];
+                    const int row = nb * 8 + 2 * q + (i & 1), col = t * 16 + g + ((i & 2) ? 8 : 0);
+                    if (row < rows) base[row * kQmvRedStride + col] = acc[t][nb][i];
                 }
     };
     auto frag_add = [&](const float* base) {
@@ -200,8 +317,8 @@ qmv_kernel(const QmvParams p) {
             for (int t = 0; t < 8; ++t)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    int row = nb * 8 + 2 * q + (i & 1), col = t * 16 + g + ((i & 2) ? 8 : 0);
-                    if (row < rows) acc[nb][t][i] = __fadd_rn(acc[nb][t][i], base[row * kQmvRedStride + col]);
+                    const int row = nb * 8 + 2 * q + (i & 1), col = t * 16 + g + ((i & 2) ? 8 : 0);
+                    if (row < rows) acc[t][nb][i] = __fadd_rn(acc[t][nb][i], base[row * kQmvRedStride + col]);
                 }
     };
     const int slab = rows * kQmvRedStride;
@@ -214,36 +331,94 @@ qmv_kernel(const QmvParams p) {
     }
     if (warp == 0) frag_store(red);
     __syncthreads();
-    float* dst = p.partials + static_cast<int64_t>(split) * rows * p.out + cblock * 128;
-    for (int i = threadIdx.x; i < rows * 128; i += WARPS * 32) {
-        int row = i >> 7, col = i & 127;
-        dst[static_cast<int64_t>(row) * p.out + col] = red[row * kQmvRedStride + col];
+
+    // ---- phase 4: split reduction across CTAs; the last CTA of a column block finishes it -------------
+    const int64_t plane = static_cast<int64_t>(rows) * p.out;
+    if (p.splits > 1) {
+        float* dst = p.partials + split * plane + cblock * 128;
+        for (int i = threadIdx.x; i < rows * 128; i += WARPS * 32) {
+            const int row = i >> 7, col = i & 127;
+            __stcg(dst + static_cast<int64_t>(row) * p.out + col, red[row * kQmvRedStride + col]);
+        }
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const unsigned int prev = atomicAdd(p.counters + cblock, 1u);
+            s_last = prev == static_cast<unsigned int>(p.splits - 1);
+        }
+        __syncthreads();
+        if (!s_last) return;
+        __threadfence();
+        if (threadIdx.x == 0) p.counters[cblock] = 0;       // leave the scratch ready for the next call
+    }
+    // one warp per activation row: sum the splits in order, rotate, scale, store
+    for (int row = warp; row < rows; row += WARPS) {
+        float v[4];
+        if (p.splits > 1) {
+            const float* src = p.partials + static_cast<int64_t>(row) * p.out + cblock * 128 + lane * 4;
+            float4 a = __ldcg(reinterpret_cast<const float4*>(src));
+            for (int s0 = 1; s0 < p.splits; s0 += 8) {
+                float4 part[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (s0 + j < p.splits) part[j] = __ldcg(reinterpret_cast<const float4*>(src + (s0 + j) * plane));
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (s0 + j < p.splits) {
+                        a.x = __fadd_rn(a.x, part[j].x); a.y = __fadd_rn(a.y, part[j].y);
+                        a.z = __fadd_rn(a.z, part[j].z); a.w = __fadd_rn(a.w, part[j].w);
+                    }
+            }
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = red[row * kQmvRedStride + lane * 4 + j];
+        }
+        const int col = cblock * 128 + lane * 4;
+        if (p.y == nullptr) {
+            *reinterpret_cast<float4*>(p.yhat + static_cast<int64_t>(row) * p.out + col) = make_float4(v[0], v[1], v[2], v[3]);
+        } else {
+            __half h[4] = {__float2half_rn(v[0]), __float2half_rn(v[1]), __float2half_rn(v[2]), __float2half_rn(v[3])};
+            warp_hadamard128_f16(h, lane);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                store_from_half(p.y, p.y_dtype, static_cast<int64_t>(row) * p.out + col + j, __hmul_rn(h[j], p.svh[col + j]),
+                                p.bias, col + j);
+        }
     }
 }
 
-constexpr int kQmvWarps = 8;
-
 template <int K, int CB, int NB, int MODE>
-cudaError_t qmv_launch_one(const QmvParams& p, const QmvPlan& plan, cudaStream_t stream) {
-    auto kernel = qmv_kernel<K, CB, NB, MODE, kQmvWarps>;
-    if (plan.smem_bytes > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             static_cast<int>(plan.smem_bytes));
+cudaError_t qmv_launch_one(const QmvArgs& p, const QmvPlan& plan, cudaStream_t stream) {
+    auto kernel = qmv_kernel<K, CB, NB, MODE>;
+    static bool attribute_set = false;                      // once per kernel: allow the largest carve-out
+    if (!attribute_set) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kQmvMaxSmemBytes);
         if (e != cudaSuccess) return e;
+        attribute_set = true;
     }
-    kernel<<<static_cast<unsigned>(plan.col_blocks * plan.splits), kQmvWarps * 32, plan.smem_bytes, stream>>>(p);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>(plan.col_blocks * plan.splits));
+    cfg.blockDim = dim3(kQmvWarps * 32);
+    cfg.dynamicSmemBytes = plan.smem_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = plan.pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, p);
 }
 
 template <int K, int CB, int MODE>
-cudaError_t qmv_launch_nb(const QmvParams& p, const QmvPlan& plan, cudaStream_t stream) {
+cudaError_t qmv_launch_nb(const QmvArgs& p, const QmvPlan& plan, cudaStream_t stream) {
     if (p.rows <= 8) return qmv_launch_one<K, CB, 1, MODE>(p, plan, stream);
     if (p.rows <= 16) return qmv_launch_one<K, CB, 2, MODE>(p, plan, stream);
     return qmv_launch_one<K, CB, 4, MODE>(p, plan, stream);
 }
 
 template <int K>
-cudaError_t qmv_launch_k(const QmvParams& p, int cb, bool exact, const QmvPlan& plan, cudaStream_t stream) {
+cudaError_t qmv_launch_k(const QmvArgs& p, int cb, bool exact, const QmvPlan& plan, cudaStream_t stream) {
     if (cb == 2) return qmv_launch_nb<K, 2, 1>(p, plan, stream);
     if (cb == 0) return exact ? qmv_launch_nb<K, 0, 1>(p, plan, stream) : qmv_launch_nb<K, 0, 0>(p, plan, stream);
     return exact ? qmv_launch_nb<K, 1, 1>(p, plan, stream) : qmv_launch_nb<K, 1, 0>(p, plan, stream);

@@ -1,8 +1,8 @@
-// Instantiates the fused product kernels for K = 6 bits per weight.
+// Instantiates the fused linear-layer kernels for K = 6 bits per weight.
 #include "kernels_qmv_impl.cuh"
 
 namespace b200exl3 {
-cudaError_t qmv_dispatch_k6(const QmvParams& p, int cb, bool exact, const QmvPlan& plan, cudaStream_t stream) {
+cudaError_t qmv_dispatch_k6(const QmvArgs& p, int cb, bool exact, const QmvPlan& plan, cudaStream_t stream) {
     return qmv_launch_k<6>(p, cb, exact, plan, stream);
 }
 }  // namespace b200exl3

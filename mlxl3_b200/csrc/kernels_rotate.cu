@@ -17,9 +17,9 @@ prepare_kernel(const void* __restrict__ x, int x_dtype, const __half* __restrict
         const int64_t row = unit / blocks_per_row;
         const int col = static_cast<int>(unit % blocks_per_row) * 128 + lane * 4;
         const __half* s = suh + (scale_rows == 1 ? 0 : row * in) + col;
-        __half h[4];
+        __align__(8) __half h[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) h[j] = __hmul(load_as_half(x, x_dtype, row * in + col + j), s[j]);
+        for (int j = 0; j < 4; ++j) h[j] = __hmul_rn(load_as_half(x, x_dtype, row * in + col + j), s[j]);
         warp_hadamard128_f16(h, lane);
         *reinterpret_cast<uint2*>(xhat + row * in + col) = *reinterpret_cast<uint2*>(h);
     }
@@ -36,17 +36,25 @@ finish_kernel(const float* __restrict__ partials, int splits, int64_t split_stri
          unit += static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5)) {
         const int64_t row = unit / blocks_per_row;
         const int col = static_cast<int>(unit % blocks_per_row) * 128 + lane * 4;
-        float4 acc = *reinterpret_cast<const float4*>(partials + row * out + col);
-        for (int s = 1; s < splits; ++s) {               // splits are added in order, in fp32
-            float4 p = *reinterpret_cast<const float4*>(partials + s * split_stride + row * out + col);
-            acc.x = __fadd_rn(acc.x, p.x); acc.y = __fadd_rn(acc.y, p.y);
-            acc.z = __fadd_rn(acc.z, p.z); acc.w = __fadd_rn(acc.w, p.w);
+        const float* src = partials + row * out + col;
+        float4 acc = *reinterpret_cast<const float4*>(src);
+        for (int s0 = 1; s0 < splits; s0 += 8) {         // splits are added in order, in fp32; loads go out together
+            float4 part[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (s0 + j < splits) part[j] = *reinterpret_cast<const float4*>(src + (s0 + j) * split_stride);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (s0 + j < splits) {
+                    acc.x = __fadd_rn(acc.x, part[j].x); acc.y = __fadd_rn(acc.y, part[j].y);
+                    acc.z = __fadd_rn(acc.z, part[j].z); acc.w = __fadd_rn(acc.w, part[j].w);
+                }
         }
         __half h[4] = {__float2half_rn(acc.x), __float2half_rn(acc.y), __float2half_rn(acc.z), __float2half_rn(acc.w)};
         warp_hadamard128_f16(h, lane);
         const __half* s = svh + (scale_rows == 1 ? 0 : row * out) + col;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) store_from_half(y, y_dtype, row * out + col + j, __hmul(h[j], s[j]), bias, col + j);
+        for (int j = 0; j < 4; ++j) store_from_half(y, y_dtype, row * out + col + j, __hmul_rn(h[j], s[j]), bias, col + j);
     }
 }
 

@@ -35,6 +35,14 @@ def _np_dtype(code: int):
     return {F16: np.float16, F32: np.float32, BF16: np.uint16}[code]
 
 
+def new_workspace(nbytes: int) -> DeviceBuffer:
+    """Scratch memory for forward calls: its header of arrival counters is zeroed here, once."""
+    buf = DeviceBuffer(max(nbytes, _lib.WORKSPACE_HEADER_BYTES))
+    _lib.call("b200exl3_memset", c_void_p(buf.ptr), 0, _lib.WORKSPACE_HEADER_BYTES, c_void_p(DEFAULT_STREAM.handle))
+    DEFAULT_STREAM.sync()
+    return buf
+
+
 class Exl3Linear:
     """One EXL3-quantized linear layer resident on the GPU.
 
@@ -66,13 +74,13 @@ class Exl3Linear:
         code = dtype_code(suh, scale_dtype)
         cast = _np_dtype(code)
         self.rows, self.cols, self.k, self.cb = rows, cols, k, cb
-        self._trellis = DeviceBuffer.from_numpy(trellis.view(np.uint16))
+        d_trellis = DeviceBuffer.from_numpy(trellis.view(np.uint16))
         d_suh = DeviceBuffer.from_numpy(suh.astype(cast, copy=False))
         d_svh = DeviceBuffer.from_numpy(svh.astype(cast, copy=False))
         d_bias = DeviceBuffer.from_numpy(np.asarray(bias).astype(cast, copy=False)) if bias is not None else None
         handle = c_void_p()
         flags = _lib.EXACT_WEIGHTS if exact_weights else 0
-        _lib.call("b200exl3_linear_create", c_void_p(self._trellis.ptr), c_void_p(d_suh.ptr), c_void_p(d_svh.ptr),
+        _lib.call("b200exl3_linear_create", c_void_p(d_trellis.ptr), c_void_p(d_suh.ptr), c_void_p(d_svh.ptr),
                   c_void_p(d_bias.ptr) if d_bias else None, code, rows, cols, k, cb, flags, byref(handle))
         self.handle = handle.value
         self._workspace: DeviceBuffer | None = None
@@ -92,7 +100,7 @@ class Exl3Linear:
     def _ensure_workspace(self, rows: int) -> DeviceBuffer:
         need = self.workspace_bytes(rows)
         if self._workspace is None or self._workspace.nbytes < need:
-            self._workspace = DeviceBuffer(need)
+            self._workspace = new_workspace(need)
         return self._workspace
 
     # ---- device-pointer entry points (no host copies) ---------------------------------------------

@@ -147,3 +147,44 @@ class PinnedBuffer:
             self.free()
         except Exception:
             pass
+
+
+class Graph:
+    """A recorded sequence of launches (``b200exl3_graph_*``), replayed with one call.
+
+    with Graph.record(stream) as g:
+        ... forward_device calls on `stream` ...
+    g.launch(stream)
+    """
+
+    def __init__(self):
+        self.handle = None
+        self._stream = None
+
+    @classmethod
+    def record(cls, stream: Stream) -> "Graph":
+        g = cls()
+        g._stream = stream
+        return g
+
+    def __enter__(self) -> "Graph":
+        _lib.call("b200exl3_graph_begin", c_void_p(self._stream.handle))
+        return self
+
+    def __exit__(self, exc_type, exc, tb) -> None:
+        h = c_void_p()
+        status = _lib.load().b200exl3_graph_end(c_void_p(self._stream.handle), byref(h))
+        if exc_type is None:
+            _lib.check(status)
+            self.handle = h.value
+
+    def launch(self, stream: Stream) -> None:
+        _lib.call("b200exl3_graph_launch", c_void_p(self.handle), c_void_p(stream.handle))
+
+    def __del__(self):
+        try:
+            if self.handle:
+                _lib.call("b200exl3_graph_free", c_void_p(self.handle))
+                self.handle = None
+        except Exception:
+            pass
