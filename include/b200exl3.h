@@ -50,9 +50,10 @@ int b200exl3_init(int device);
 const char* b200exl3_last_error(void);
 /* major*10000 + minor*100 + patch */
 int b200exl3_version(void);
-/* Process-wide knobs: "qmv_ctas_per_sm" (CTAs per SM the grids are sized for), "qmv_force_splits"
- * (0 = heuristic), "pdl" (1 = launch layer kernels with programmatic stream serialization, so the
- * weight prefetch of a layer overlaps the tail of the previous kernel in the stream). */
+/* Process-wide knobs: "qmv_ctas_per_sm" (CTAs per SM the grids are sized for), "qmv_force_grid"
+ * (CTAs per launch, 0 = heuristic), "pdl" (1 or 2 = launch layer kernels with programmatic stream serialization, so the
+ * weight prefetch of a layer overlaps the tail of the previous kernel in the stream; 1 releases the
+ * next kernel after the main loop, 2 as soon as the first copies are in flight). */
 int b200exl3_set_option(const char* name, int64_t value);
 
 /* Plain device-memory plumbing for hosts that have no CUDA binding of their own (replaces
@@ -128,6 +129,10 @@ void b200exl3_linear_free(b200exl3_linear* handle);
 int b200exl3_linear_input_dims(const b200exl3_linear* handle);    /* Exl3Linear::input_dims  */
 int b200exl3_linear_output_dims(const b200exl3_linear* handle);   /* Exl3Linear::output_dims */
 int b200exl3_linear_workspace_bytes(const b200exl3_linear* handle, int64_t rows, size_t* out_bytes);
+/* Waits for the device and reads the status word of a workspace: 0 = every kernel that used it ran to
+ * completion, 1 = a bounded device-side wait gave up (the results of that call are invalid).  The
+ * kernels never spin without a limit, so a lost copy shows up here instead of as a hung GPU. */
+int b200exl3_workspace_status(const void* d_workspace, int* out_status);
 /* Exl3Linear::forward (native/src/linear.rs:731-997): x [rows, in] in x_dtype -> y [rows, out] in
  * the same dtype.  rows >= 1.  The workspace must hold b200exl3_linear_workspace_bytes(rows). */
 int b200exl3_linear_forward(const b200exl3_linear* handle, const void* d_x, int x_dtype, int64_t rows, void* d_y,

@@ -42,19 +42,9 @@ cudaStream_t as_stream(b200exl3_stream s) { return static_cast<cudaStream_t>(s);
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
-
 __global__ void to_half_kernel(const void* src, int dtype, int64_t n, __half* dst) {
     int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i < n) dst[i] = load_as_half(src, dtype, i);
-}
-
-__global__ void sum_partials_kernel(const float* partials, int splits, int64_t stride, int64_t n, float* out) {
-    int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    float acc = partials[i];
-    for (int s = 1; s < splits; ++s) acc = __fadd_rn(acc, partials[s * stride + i]);
-    out[i] = acc;
 }
 
 int valid_format(int k, int cb) {
@@ -95,13 +85,13 @@ int b200exl3_init(int device) {
 }
 
 int b200exl3_set_option(const char* name, int64_t value) {
-    static int ctas = 0, splits = 0, pdl = 0;
+    static int ctas = 0, grid = 0, pdl = 0;
     if (!name) return fail("option name is NULL");
     if (!strcmp(name, "qmv_ctas_per_sm")) ctas = static_cast<int>(value);
-    else if (!strcmp(name, "qmv_force_splits")) splits = static_cast<int>(value);
+    else if (!strcmp(name, "qmv_force_grid")) grid = static_cast<int>(value);
     else if (!strcmp(name, "pdl")) pdl = static_cast<int>(value);
     else return fail("unknown option %s", name);
-    qmv_set_tuning(ctas, splits, pdl);
+    qmv_set_tuning(ctas, grid, pdl);
     return 0;
 }
 
@@ -163,7 +153,7 @@ int b200exl3_event_elapsed_ms(void* start, void* stop, float* out_ms) {
 /* ---- graph replay ------------------------------------------------------------------------------ */
 
 int b200exl3_graph_begin(b200exl3_stream s) {
-    return check(cudaStreamBeginCapture(as_stream(s), cudaStreamCaptureModeThreadLocal), "cudaStreamBeginCapture");
+    return check(cudaStreamBeginCapture(as_stream(s), cudaStreamCaptureModeRelaxed), "cudaStreamBeginCapture");
 }
 int b200exl3_graph_end(b200exl3_stream s, void** out_graph) {
     if (!out_graph) return fail("out pointer is NULL");
@@ -252,7 +242,7 @@ int b200exl3_linear_create(const uint16_t* d_trellis, const void* d_suh, const v
     if (!d_suh || !d_svh) return fail("EXL3 scales have wrong dimensions");
     if (!dtype_is_float(scale_dtype)) return fail("unsupported scale dtype %d", scale_dtype);
     if (!aligned16(d_trellis)) return fail("device pointers must be 16-byte aligned");
-    if (out / 128 > static_cast<int>(kCounterBytes / sizeof(unsigned int))) return fail("output dimension %d is too large", out);
+    if (out / 128 >= static_cast<int>(kCounterBytes / sizeof(unsigned int))) return fail("output dimension %d is too large", out);
     b200exl3_linear* h = new (std::nothrow) b200exl3_linear{};
     if (!h) return fail("out of host memory");
     h->in = in; h->out = out; h->k = k; h->cb = cb; h->flags = flags;
@@ -322,6 +312,7 @@ static int forward_common(const b200exl3_linear* h, const void* d_x, int x_dtype
         a.suh = h->suh;
         a.xhat = d_xhat ? reinterpret_cast<const __half*>(d_xhat) + r0 * h->in : nullptr;
         a.counters = reinterpret_cast<unsigned int*>(base);
+        a.error = reinterpret_cast<unsigned int*>(base + kCounterBytes - sizeof(unsigned int));
         a.partials = reinterpret_cast<float*>(base + kCounterBytes);
         a.svh = h->svh;
         a.bias = h->bias;
@@ -332,6 +323,15 @@ static int forward_common(const b200exl3_linear* h, const void* d_x, int x_dtype
         a.in = h->in; a.out = h->out; a.rows = static_cast<int>(n);
         B200_TRY(launch_qmv(a, h->k, h->cb, exact, plan, stream), "fused linear kernel");
     }
+    return 0;
+}
+
+int b200exl3_workspace_status(const void* ws, int* out_status) {
+    if (!ws || !out_status) return fail("NULL argument");
+    unsigned int flag = 0;
+    B200_TRY(cudaMemcpy(&flag, static_cast<const char*>(ws) + kCounterBytes - sizeof(unsigned int), sizeof flag,
+                        cudaMemcpyDeviceToHost), "read workspace status");
+    *out_status = static_cast<int>(flag);
     return 0;
 }
 

@@ -37,23 +37,27 @@ struct QmvArgs {
     const void* x;             // [rows, in] activations in x_dtype (used when xhat == nullptr)
     const __half* suh;         // [in]
     const __half* xhat;        // [rows, in] already rotated activations, or nullptr
-    float* partials;           // [splits, rows, out] scratch (unused when splits == 1)
+    float* partials;           // [out/128, max_pieces, rows, 128] scratch for column blocks shared by several CTAs
     unsigned int* counters;    // [out/128] arrival counters, zero on entry and on exit
+    unsigned int* error;       // set to 1 if a weight copy never arrived (bounded wait gave up)
     const __half* svh;         // [out]   (output rotation; used when y != nullptr)
     const __half* bias;        // [out] or nullptr
     void* y;                   // [rows, out] in y_dtype, or nullptr for raw output
     float* yhat;               // [rows, out] summed fp32 product, written when y == nullptr
     int x_dtype, y_dtype;
-    int in, out, rows, tiles_k, tiles_n, splits;
+    int in, out, rows, tiles_k, tiles_n, max_pieces;
     int xs_stride;             // halves per activation row in shared memory
+    int pdl_early;             // 1: let the next kernel start as soon as this one has started its copies
 };
 
 struct QmvPlan {
-    int splits;          // split-K factor: CTAs per 128-column block
+    int grid;            // CTAs: every one gets the same number of tiles (+-1)
+    int max_pieces;      // upper bound on the CTAs that share one 128-column block
     int col_blocks;      // out / 128
     int xs_stride;       // halves per activation row in shared memory
     size_t smem_bytes;   // dynamic shared memory per CTA
     bool pdl;            // launch with programmatic stream serialization (overlap with the previous kernel's tail)
+    bool pdl_early;      // trigger the dependent launch before the main loop instead of after it
 };
 QmvPlan plan_qmv(int in, int out, int k, int64_t rows);
 // Scratch a launch needs: counters first (zero-initialised once by the owner), then the partial sums.
@@ -62,7 +66,7 @@ size_t qmv_partial_bytes(const QmvPlan& plan, int out, int64_t rows);
 // exact: decode the reference's fp16 weight bit for bit before multiplying (codebooks 0/1 default to
 // feeding the two fp16 halves of a weight as two products, which differs by fp16 rounding of the weight).
 cudaError_t launch_qmv(QmvArgs args, int k, int cb, bool exact, const QmvPlan& plan, cudaStream_t stream);
-void qmv_set_tuning(int ctas_per_sm, int force_splits, int pdl);
+void qmv_set_tuning(int ctas_per_sm, int force_grid, int pdl);
 
 // ---- weight layout (kernels_codec.cu) -----------------------------------------------------------------
 // checkpoint layout [tiles_k, tiles_n, 8K] words -> quad layout [tiles_k, tiles_n/4, 8K, 4]

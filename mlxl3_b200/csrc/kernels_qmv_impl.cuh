@@ -64,7 +64,8 @@ __device__ __forceinline__ void lane_hashes(uint32_t w2, uint32_t w1, uint32_t w
             const uint32_t hi = P[p] >> 16;
             const uint32_t bh = hi * M + C;
             const uint32_t t = P[p] * M + C2;
-            const uint32_t bl = bh * 0xffff0000u + t;
+            uint32_t bl;                                   // t - (bh << 16) as one multiply-add
+            asm("mad.lo.u32 %0, %1, %2, %3;" : "=r"(bl) : "r"(bh), "r"(0xffff0000u), "r"(t));
             if constexpr (K == 4) {
                 b[7 - p] = bl; b[3 - p] = bh;
             } else {
@@ -146,17 +147,25 @@ __device__ __forceinline__ void tile_mma(uint32_t w2, uint32_t w1, uint32_t w0, 
     }
 }
 
-// Copies the needed quads (those touching tiles [lo, hi) of the row) of one 8-tile row into a ring slot.
-template <int K>
-__device__ __forceinline__ void qmv_issue_row(const uint32_t* __restrict__ wq, int tiles_n, int tk, int tn0, int lo,
-                                              int hi, uint32_t* slot, int lane) {
-    constexpr int kChunksPerQuad = 8 * K;                   // 16-byte chunks: one per stream word
-    const char* src = reinterpret_cast<const char*>(wq + (static_cast<int64_t>(tk) * tiles_n + tn0) * (8 * K));
-    char* dst = reinterpret_cast<char*>(slot);
+// All tiles [lo, hi) of one staged row.  FULL rows carry no per-tile tests.
+template <int K, int CB, int NB, int MODE, bool FULL>
+__device__ __forceinline__ void qmv_row(const uint32_t* __restrict__ row_words, const LaneGeom<K>& geom, int lo, int hi,
+                                        const uint32_t (&bx)[NB][4], float (&acc)[8][NB][4]) {
 #pragma unroll
-    for (int c = lane; c < 2 * kChunksPerQuad; c += 32) {
-        const int quad = c / kChunksPerQuad;
-        if (lo < 4 * quad + 4 && hi > 4 * quad) cp_async_16(dst + c * 16, src + c * 16);
+    for (int quad = 0; quad < 2; ++quad) {
+        if (FULL || (lo < 4 * quad + 4 && hi > 4 * quad)) {
+            const uint4* qw = reinterpret_cast<const uint4*>(row_words + quad * (32 * K));
+            const uint4 W2 = qw[geom.i2];
+            const uint4 W1 = qw[geom.i1];
+            uint4 W0 = make_uint4(0, 0, 0, 0);
+            if constexpr (K >= 5) W0 = qw[geom.i0];
+            const uint32_t w2[4] = {W2.x, W2.y, W2.z, W2.w}, w1[4] = {W1.x, W1.y, W1.z, W1.w},
+                           w0[4] = {W0.x, W0.y, W0.z, W0.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (FULL || (quad * 4 + j >= lo && quad * 4 + j < hi))
+                    tile_mma<K, CB, NB, MODE>(w2[j], w1[j], w0[j], geom.slack, bx, acc[quad * 4 + j]);
+        }
     }
 }
 
@@ -168,224 +177,245 @@ qmv_kernel(const QmvArgs p) {
     constexpr int DEPTH = qmv_depth(K);
     constexpr int kRowWords = 64 * K;                       // 2 quads x 8K words x 4 tiles
     constexpr int kRingBytes = WARPS * DEPTH * kRowWords * 4;
+    constexpr uint32_t kRowBytes = kRowWords * 4;
     __shared__ int s_last;
+    __shared__ __align__(8) uint64_t s_bar[WARPS][DEPTH];
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, q = lane & 3;
-    const int col_blocks = p.out >> 7;
-    const int cblock = blockIdx.x % col_blocks;
-    const int split = blockIdx.x / col_blocks;
-    const int tn0 = cblock * 8;
     const int rows = p.rows;
+    const int G = static_cast<int>(gridDim.x);
+    const int bid = static_cast<int>(blockIdx.x);
 
-    // unit (= tile) range of this CTA inside its column block, then of this warp
-    const int units = p.tiles_k * 8;
-    const int cta_u0 = static_cast<int>(static_cast<int64_t>(units) * split / p.splits);
-    const int cta_u1 = static_cast<int>(static_cast<int64_t>(units) * (split + 1) / p.splits);
-    const int cta_n = cta_u1 - cta_u0;
-    const int u0 = cta_u0 + static_cast<int>(static_cast<int64_t>(cta_n) * warp / WARPS);
-    const int u1 = cta_u0 + static_cast<int>(static_cast<int64_t>(cta_n) * (warp + 1) / WARPS);
-    const int tk_first = u0 >> 3;
-    const int nrows = u1 > u0 ? ((u1 - 1) >> 3) - tk_first + 1 : 0;
+    // All tiles of the layer in column-block-major order; unit = block * UB + (tk * 8 + tile-in-row).
+    // CTA i owns units [T*i/G, T*(i+1)/G): the same number of tiles (+-1) for every CTA, so the
+    // grid is one balanced wave whatever the shape.  A CTA may touch several column blocks, and a
+    // block may be shared by several CTAs ("pieces").
+    const int64_t UB = static_cast<int64_t>(p.tiles_k) * 8;
+    const int64_t T = UB * (p.out >> 7);
+    const int64_t my0 = T * bid / G, my1 = T * (bid + 1) / G;
 
     uint32_t* ring = reinterpret_cast<uint32_t*>(smem_raw) + static_cast<size_t>(warp) * DEPTH * kRowWords;
     __half* xs = reinterpret_cast<__half*>(smem_raw + kRingBytes);     // [rows][xs_stride]
-
-    // ---- phase 0: start streaming weights (they do not depend on the previous kernel) ----------------
-#pragma unroll
-    for (int i = 0; i < DEPTH; ++i) {
-        if (i < nrows) {
-            const int tk = tk_first + i;
-            qmv_issue_row<K>(p.wq, p.tiles_n, tk, tn0, max(u0 - 8 * tk, 0), min(u1 - 8 * tk, 8), ring + i * kRowWords, lane);
-        }
-        cp_async_commit();
-    }
-    pdl_launch_dependents();
-    pdl_wait();
-
-    // ---- phase 1: rotate (or fetch) the activations of this CTA's input range into shared memory ---
-    const int kb0 = cta_n > 0 ? (cta_u0 >> 3) >> 3 : 0;                         // first 128-block
-    const int kb1 = cta_n > 0 ? ((((cta_u1 - 1) >> 3) >> 3) + 1) : 0;           // one past the last
-    {
-        const int nblk = kb1 - kb0;
-        for (int unit = warp; unit < rows * nblk; unit += WARPS) {
-            const int row = unit / nblk, blk = unit % nblk;
-            const int col = (kb0 + blk) * 128 + lane * 4;
-            __align__(8) __half h[4];
-            if (p.xhat) {
-                *reinterpret_cast<uint2*>(h) = *reinterpret_cast<const uint2*>(p.xhat + static_cast<int64_t>(row) * p.in + col);
-            } else {
-#pragma unroll
-                for (int j = 0; j < 4; ++j)
-                    h[j] = __hmul_rn(load_as_half(p.x, p.x_dtype, static_cast<int64_t>(row) * p.in + col + j), p.suh[col + j]);
-                warp_hadamard128_f16(h, lane);
-            }
-            *reinterpret_cast<uint2*>(xs + row * p.xs_stride + blk * 128 + lane * 4) = *reinterpret_cast<uint2*>(h);
-        }
-    }
-    __syncthreads();
-
-    // ---- phase 2: decode x activations ----------------------------------------------------------------
-    float acc[8][NB][4];
-#pragma unroll
-    for (int t = 0; t < 8; ++t)
-#pragma unroll
-        for (int nb = 0; nb < NB; ++nb)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) acc[t][nb][i] = 0.0f;
-
+    float* red = reinterpret_cast<float*>(smem_raw);                    // reused after the main loop
+    uint64_t* bars = s_bar[warp];
+    const size_t row_stride = static_cast<size_t>(p.tiles_n) * (32 * K);
     const LaneGeom<K> geom(lane);
+    const int64_t tile_floats = static_cast<int64_t>(rows) * 128;
+
+    if (lane == 0) {
+#pragma unroll
+        for (int i = 0; i < DEPTH; ++i) mbar_init(bars + i, 1);
+        mbar_init_fence();
+    }
+    __syncwarp();
     int slot = 0;
-    for (int r = 0; r < nrows; ++r) {
-        const int tk = tk_first + r;
-        // activation fragments: rows nb*8+g, inputs 16tk + {2q, 2q+1, 2q+8, 2q+9}
-        uint32_t bx[NB][4];
+    uint32_t parity = 0;
+    bool copy_lost = false;
+    bool first_block = true;
+
+    for (int64_t cblock = my0 / UB; cblock * UB < my1; ++cblock) {
+        // ---- this CTA's slice [cta_u0, cta_u1) of the block, then this warp's slice -----------------
+        const int cta_u0 = static_cast<int>(max(my0, cblock * UB) - cblock * UB);
+        const int cta_u1 = static_cast<int>(min(my1, (cblock + 1) * UB) - cblock * UB);
+        const int cta_n = cta_u1 - cta_u0;
+        const int u0 = cta_u0 + static_cast<int>(static_cast<int64_t>(cta_n) * warp / WARPS);
+        const int u1 = cta_u0 + static_cast<int>(static_cast<int64_t>(cta_n) * (warp + 1) / WARPS);
+        const int tk_first = u0 >> 3;
+        const int nrows = u1 > u0 ? ((u1 - 1) >> 3) - tk_first + 1 : 0;
+        const int tn0 = static_cast<int>(cblock) * 8;
+        // CTA holding unit x: ceil((x+1)*G/T) - 1
+        const int i_first = static_cast<int>(((cblock * UB + 1) * G - 1) / T);
+        const int i_last = static_cast<int>((((cblock + 1) * UB) * G - 1) / T);
+        const int pieces = i_last - i_first + 1;
+
+        // ---- phase 0: start streaming weights (they do not depend on the previous kernel) ------------
+        // Whole 8-tile rows are copied even when the warp owns only part of the first or last one:
+        // one TMA copy per row, consecutive rows a fixed stride apart.
+        const char* next_src =
+            reinterpret_cast<const char*>(p.wq + (static_cast<int64_t>(tk_first) * p.tiles_n + tn0) * (8 * K));
+        if (lane == 0) {
+            // the slots may hold reduction scratch written through the generic proxy by the previous block
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+#pragma unroll
+            for (int i = 0; i < DEPTH; ++i)
+                if (i < nrows) {
+                    const int sl = slot + i < DEPTH ? slot + i : slot + i - DEPTH;
+                    mbar_expect_tx(bars + sl, kRowBytes);
+                    bulk_copy_g2s(ring + sl * kRowWords, next_src + i * row_stride, kRowBytes, bars + sl);
+                }
+        }
+        next_src += DEPTH * row_stride;
+        if (first_block) {
+            if (p.pdl_early) pdl_launch_dependents();
+            pdl_wait();
+            first_block = false;
+        }
+
+        // ---- phase 1: rotate (or fetch) the activations of this slice's input range into shared memory
+        const int kb0 = (cta_u0 >> 3) >> 3;                              // first 128-block
+        const int kb1 = (((cta_u1 - 1) >> 3) >> 3) + 1;                  // one past the last
+        {
+            const int nblk = kb1 - kb0;
+            for (int unit = warp; unit < rows * nblk; unit += WARPS) {
+                const int row = unit / nblk, blk = unit % nblk;
+                const int col = (kb0 + blk) * 128 + lane * 4;
+                __align__(8) __half h[4];
+                if (p.xhat) {
+                    *reinterpret_cast<uint2*>(h) = *reinterpret_cast<const uint2*>(p.xhat + static_cast<int64_t>(row) * p.in + col);
+                } else {
+                    __align__(8) __half sc[4];
+                    *reinterpret_cast<uint2*>(sc) = *reinterpret_cast<const uint2*>(p.suh + col);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        h[j] = __hmul_rn(load_as_half(p.x, p.x_dtype, static_cast<int64_t>(row) * p.in + col + j), sc[j]);
+                    warp_hadamard128_f16(h, lane);
+                }
+                *reinterpret_cast<uint2*>(xs + row * p.xs_stride + blk * 128 + lane * 4) = *reinterpret_cast<uint2*>(h);
+            }
+        }
+        __syncthreads();
+
+        // ---- phase 2: decode x activations ----------------------------------------------------------------
+        float acc[8][NB][4];
+#pragma unroll
+        for (int t = 0; t < 8; ++t)
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[t][nb][i] = 0.0f;
+
+        // activation fragments of input tile tk: rows nb*8+g, inputs 16tk + {2q, 2q+1, 2q+8, 2q+9}
+        const uint32_t* xfrag[NB];
 #pragma unroll
         for (int nb = 0; nb < NB; ++nb) {
-            const int row = nb * 8 + g;
-            uint32_t p0 = 0, p1 = 0;
-            if (row < rows) {
-                const uint32_t* xr = reinterpret_cast<const uint32_t*>(xs + row * p.xs_stride + (tk * 16 - kb0 * 128));
-                p0 = xr[q];
-                p1 = xr[q + 4];
+            const int row = min(nb * 8 + g, rows - 1);
+            xfrag[nb] = reinterpret_cast<const uint32_t*>(xs + row * p.xs_stride + (tk_first * 16 - kb0 * 128)) + q;
+        }
+        const int lo_first = u0 & 7, hi_last = nrows > 0 ? ((u1 - 1) & 7) + 1 : 8;
+        for (int r = 0; r < nrows; ++r) {
+            uint32_t bx[NB][4];
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) {
+                uint32_t p0 = xfrag[nb][r * 8], p1 = xfrag[nb][r * 8 + 4];
+                if (nb * 8 + g >= rows) { p0 = 0; p1 = 0; }
+                if constexpr (MODE == 0) {
+                    bx[nb][0] = prmt(p0, p0, 0x1010); bx[nb][1] = prmt(p0, p0, 0x3232);
+                    bx[nb][2] = prmt(p1, p1, 0x1010); bx[nb][3] = prmt(p1, p1, 0x3232);
+                } else {
+                    bx[nb][0] = p0; bx[nb][1] = p1; bx[nb][2] = 0; bx[nb][3] = 0;
+                }
             }
-            if constexpr (MODE == 0) {
-                bx[nb][0] = prmt(p0, p0, 0x1010); bx[nb][1] = prmt(p0, p0, 0x3232);
-                bx[nb][2] = prmt(p1, p1, 0x1010); bx[nb][3] = prmt(p1, p1, 0x3232);
-            } else {
-                bx[nb][0] = p0; bx[nb][1] = p1; bx[nb][2] = 0; bx[nb][3] = 0;
+            if (!mbar_wait(bars + slot, parity)) copy_lost = true;
+            const uint32_t* row_words = ring + slot * kRowWords;
+            const int lo = r == 0 ? lo_first : 0, hi = r == nrows - 1 ? hi_last : 8;
+            if (lo == 0 && hi == 8) qmv_row<K, CB, NB, MODE, true>(row_words, geom, 0, 8, bx, acc);
+            else qmv_row<K, CB, NB, MODE, false>(row_words, geom, lo, hi, bx, acc);
+            __syncwarp();                                       // every lane has read the slot
+            if (lane == 0 && r + DEPTH < nrows) {
+                mbar_expect_tx(bars + slot, kRowBytes);
+                bulk_copy_g2s(ring + slot * kRowWords, next_src, kRowBytes, bars + slot);
+            }
+            next_src += row_stride;
+            if (++slot == DEPTH) { slot = 0; parity ^= 1u; }
+        }
+        if (!p.pdl_early && (cblock + 1) * UB >= my1) pdl_launch_dependents();
+
+        // ---- phase 3: deterministic tree reduction over the warps -------------------------------------------
+        __syncthreads();                                        // ring and activations are dead from here on
+        auto frag_store = [&](float* base) {
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                for (int t = 0; t < 8; ++t)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int row = nb * 8 + 2 * q + (i & 1), col = t * 16 + g + ((i & 2) ? 8 : 0);
+                        if (row < rows) base[row * kQmvRedStride + col] = acc[t][nb][i];
+                    }
+        };
+        auto frag_add = [&](const float* base) {
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                for (int t = 0; t < 8; ++t)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int row = nb * 8 + 2 * q + (i & 1), col = t * 16 + g + ((i & 2) ? 8 : 0);
+                        if (row < rows) acc[t][nb][i] = __fadd_rn(acc[t][nb][i], base[row * kQmvRedStride + col]);
+                    }
+        };
+        const int slab = rows * kQmvRedStride;
+#pragma unroll
+        for (int half = WARPS / 2; half >= 1; half >>= 1) {
+            if (warp >= half && warp < 2 * half) frag_store(red + (warp - half) * slab);
+            __syncthreads();
+            if (warp < half) frag_add(red + warp * slab);
+            __syncthreads();
+        }
+        if (warp == 0) frag_store(red);
+        __syncthreads();
+
+        // ---- phase 4: pieces of a block held by different CTAs; the last to arrive finishes the block ----
+        bool finish = true;
+        const float* piece_base = p.partials + cblock * p.max_pieces * tile_floats;
+        if (pieces > 1) {
+            float* dst = p.partials + (cblock * p.max_pieces + (bid - i_first)) * tile_floats;
+            for (int i = threadIdx.x; i < rows * 128; i += WARPS * 32)
+                __stcg(dst + i, red[(i >> 7) * kQmvRedStride + (i & 127)]);
+            __threadfence();
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                const unsigned int prev = atomicAdd(p.counters + cblock, 1u);
+                s_last = prev == static_cast<unsigned int>(pieces - 1);
+            }
+            __syncthreads();
+            finish = s_last != 0;
+            if (finish) {
+                __threadfence();
+                if (threadIdx.x == 0) p.counters[cblock] = 0;   // leave the scratch ready for the next call
             }
         }
-        // every iteration commits one group, so row r's group is complete once at most DEPTH-1 newer
-        // groups are pending
-        cp_async_wait<DEPTH - 1>();
-        __syncwarp();
-        const uint32_t* row_words = ring + slot * kRowWords;
-        const int lo = max(u0 - 8 * tk, 0), hi = min(u1 - 8 * tk, 8);
-        const bool full = lo == 0 && hi == 8;
+        if (finish) {
+            // one warp per activation row: sum the pieces in order, rotate, scale, store
+            for (int row = warp; row < rows; row += WARPS) {
+                float v[4];
+                if (pieces > 1) {
+                    const float* src = piece_base + row * 128 + lane * 4;
+                    float4 a = __ldcg(reinterpret_cast<const float4*>(src));
+                    for (int s0 = 1; s0 < pieces; s0 += 8) {
+                        float4 part[8];
 #pragma unroll
-        for (int quad = 0; quad < 2; ++quad) {
-            if (full || (lo < 4 * quad + 4 && hi > 4 * quad)) {
-                const uint4* qw = reinterpret_cast<const uint4*>(row_words + quad * (32 * K));
-                const uint4 W2 = qw[geom.i2];
-                const uint4 W1 = qw[geom.i1];
-                uint4 W0 = make_uint4(0, 0, 0, 0);
-                if constexpr (K >= 5) W0 = qw[geom.i0];
-                const uint32_t w2[4] = {W2.x, W2.y, W2.z, W2.w}, w1[4] = {W1.x, W1.y, W1.z, W1.w},
-                               w0[4] = {W0.x, W0.y, W0.z, W0.w};
-                if (full) {
+                        for (int j = 0; j < 8; ++j)
+                            if (s0 + j < pieces) part[j] = __ldcg(reinterpret_cast<const float4*>(src + (s0 + j) * tile_floats));
 #pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        tile_mma<K, CB, NB, MODE>(w2[j], w1[j], w0[j], geom.slack, bx, acc[quad * 4 + j]);
+                        for (int j = 0; j < 8; ++j)
+                            if (s0 + j < pieces) {
+                                a.x = __fadd_rn(a.x, part[j].x); a.y = __fadd_rn(a.y, part[j].y);
+                                a.z = __fadd_rn(a.z, part[j].z); a.w = __fadd_rn(a.w, part[j].w);
+                            }
+                    }
+                    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
                 } else {
 #pragma unroll
+                    for (int j = 0; j < 4; ++j) v[j] = red[row * kQmvRedStride + lane * 4 + j];
+                }
+                const int col = static_cast<int>(cblock) * 128 + lane * 4;
+                if (p.y == nullptr) {
+                    *reinterpret_cast<float4*>(p.yhat + static_cast<int64_t>(row) * p.out + col) = make_float4(v[0], v[1], v[2], v[3]);
+                } else {
+                    __half h[4] = {__float2half_rn(v[0]), __float2half_rn(v[1]), __float2half_rn(v[2]), __float2half_rn(v[3])};
+                    warp_hadamard128_f16(h, lane);
+#pragma unroll
                     for (int j = 0; j < 4; ++j)
-                        if (quad * 4 + j >= lo && quad * 4 + j < hi)
-                            tile_mma<K, CB, NB, MODE>(w2[j], w1[j], w0[j], geom.slack, bx, acc[quad * 4 + j]);
+                        store_from_half(p.y, p.y_dtype, static_cast<int64_t>(row) * p.out + col + j,
+                                        __hmul_rn(h[j], p.svh[col + j]), p.bias, col + j);
                 }
             }
         }
-        __syncwarp();
-        if (r + DEPTH < nrows) {
-            const int tkn = tk + DEPTH;
-            qmv_issue_row<K>(p.wq, p.tiles_n, tkn, tn0, max(u0 - 8 * tkn, 0), min(u1 - 8 * tkn, 8),
-                             ring + slot * kRowWords, lane);
-        }
-        cp_async_commit();
-        slot = slot + 1 == DEPTH ? 0 : slot + 1;
+        __syncthreads();                                        // shared memory is reused by the next block
     }
-    cp_async_wait<0>();
-
-    // ---- phase 3: deterministic tree reduction over the warps -------------------------------------------
-    __syncthreads();                                        // ring and activations are dead from here on
-    float* red = reinterpret_cast<float*>(smem_raw);
-    auto frag_store = [&](float* base) {
-#pragma unroll
-        for (int nb = 0; nb < NB; ++nb)
-#pragma unroll
-            for (int t = 0; t < 8; ++t)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int row = nb * 8 + 2 * q + (i & 1), col = t * 16 + g + ((i & 2) ? 8 : 0);
-                    if (row < rows) base[row * kQmvRedStride + col] = acc[t][nb][i];
-                }
-    };
-    auto frag_add = [&](const float* base) {
-#pragma unroll
-        for (int nb = 0; nb < NB; ++nb)
-#pragma unroll
-            for (int t = 0; t < 8; ++t)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int row = nb * 8 + 2 * q + (i & 1), col = t * 16 + g + ((i & 2) ? 8 : 0);
-                    if (row < rows) acc[t][nb][i] = __fadd_rn(acc[t][nb][i], base[row * kQmvRedStride + col]);
-                }
-    };
-    const int slab = rows * kQmvRedStride;
-#pragma unroll
-    for (int half = WARPS / 2; half >= 1; half >>= 1) {
-        if (warp >= half && warp < 2 * half) frag_store(red + (warp - half) * slab);
-        __syncthreads();
-        if (warp < half) frag_add(red + warp * slab);
-        __syncthreads();
-    }
-    if (warp == 0) frag_store(red);
-    __syncthreads();
-
-    // ---- phase 4: split reduction across CTAs; the last CTA of a column block finishes it -------------
-    const int64_t plane = static_cast<int64_t>(rows) * p.out;
-    if (p.splits > 1) {
-        float* dst = p.partials + split * plane + cblock * 128;
-        for (int i = threadIdx.x; i < rows * 128; i += WARPS * 32) {
-            const int row = i >> 7, col = i & 127;
-            __stcg(dst + static_cast<int64_t>(row) * p.out + col, red[row * kQmvRedStride + col]);
-        }
-        __threadfence();
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            const unsigned int prev = atomicAdd(p.counters + cblock, 1u);
-            s_last = prev == static_cast<unsigned int>(p.splits - 1);
-        }
-        __syncthreads();
-        if (!s_last) return;
-        __threadfence();
-        if (threadIdx.x == 0) p.counters[cblock] = 0;       // leave the scratch ready for the next call
-    }
-    // one warp per activation row: sum the splits in order, rotate, scale, store
-    for (int row = warp; row < rows; row += WARPS) {
-        float v[4];
-        if (p.splits > 1) {
-            const float* src = p.partials + static_cast<int64_t>(row) * p.out + cblock * 128 + lane * 4;
-            float4 a = __ldcg(reinterpret_cast<const float4*>(src));
-            for (int s0 = 1; s0 < p.splits; s0 += 8) {
-                float4 part[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                    if (s0 + j < p.splits) part[j] = __ldcg(reinterpret_cast<const float4*>(src + (s0 + j) * plane));
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                    if (s0 + j < p.splits) {
-                        a.x = __fadd_rn(a.x, part[j].x); a.y = __fadd_rn(a.y, part[j].y);
-                        a.z = __fadd_rn(a.z, part[j].z); a.w = __fadd_rn(a.w, part[j].w);
-                    }
-            }
-            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-        } else {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) v[j] = red[row * kQmvRedStride + lane * 4 + j];
-        }
-        const int col = cblock * 128 + lane * 4;
-        if (p.y == nullptr) {
-            *reinterpret_cast<float4*>(p.yhat + static_cast<int64_t>(row) * p.out + col) = make_float4(v[0], v[1], v[2], v[3]);
-        } else {
-            __half h[4] = {__float2half_rn(v[0]), __float2half_rn(v[1]), __float2half_rn(v[2]), __float2half_rn(v[3])};
-            warp_hadamard128_f16(h, lane);
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-                store_from_half(p.y, p.y_dtype, static_cast<int64_t>(row) * p.out + col + j, __hmul_rn(h[j], p.svh[col + j]),
-                                p.bias, col + j);
-        }
-    }
+    if (copy_lost && lane == 0) atomicExch(p.error, 1u);
 }
 
 template <int K, int CB, int NB, int MODE>
@@ -398,7 +428,7 @@ cudaError_t qmv_launch_one(const QmvArgs& p, const QmvPlan& plan, cudaStream_t s
         attribute_set = true;
     }
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(static_cast<unsigned>(plan.col_blocks * plan.splits));
+    cfg.gridDim = dim3(static_cast<unsigned>(plan.grid));
     cfg.blockDim = dim3(kQmvWarps * 32);
     cfg.dynamicSmemBytes = plan.smem_bytes;
     cfg.stream = stream;

@@ -43,6 +43,14 @@ def new_workspace(nbytes: int) -> DeviceBuffer:
     return buf
 
 
+def workspace_status(workspace: DeviceBuffer) -> int:
+    """0 if every kernel that used the workspace completed; 1 if a bounded device-side wait gave up."""
+    from ctypes import c_int
+    out = c_int()
+    _lib.call("b200exl3_workspace_status", c_void_p(workspace.ptr), byref(out))
+    return out.value
+
+
 class Exl3Linear:
     """One EXL3-quantized linear layer resident on the GPU.
 

@@ -109,11 +109,12 @@ def test_rows_are_independent_and_deterministic(gpu):
         assert np.array_equal(bits(layer.forward(x[r:r + 1])), bits(batched[r:r + 1]))
 
 
-@pytest.mark.parametrize("splits", [1, 2, 7, 32])
-def test_split_factor_does_not_change_parity(gpu, splits):
-    rng = np.random.default_rng(5 + splits)
-    trellis, suh, svh = random_layer(rng, 2048, 256, 4)
-    gpu.set_option("qmv_force_splits", splits)
+@pytest.mark.parametrize("grid", [1, 2, 3, 7, 64, 296, 1000])
+def test_work_partition_does_not_change_parity(gpu, grid):
+    # any number of CTAs: slices that span several column blocks, blocks shared by many CTAs
+    rng = np.random.default_rng(5 + grid)
+    trellis, suh, svh = random_layer(rng, 2048, 384, 4)
+    gpu.set_option("qmv_force_grid", grid)
     try:
         layer = gpu.Exl3Linear(trellis, suh, svh, None, 4, 0, exact_weights=True)
         x = rng.standard_normal((5, 2048)).astype(np.float16)
@@ -121,7 +122,7 @@ def test_split_factor_does_not_change_parity(gpu, splits):
         xhat = oracle.prepare(x, suh)
         _check_raw(layer.forward_raw(xhat), oracle.matmul_raw(trellis, 4, 0, xhat, f64acc=True), 2e-4)
     finally:
-        gpu.set_option("qmv_force_splits", 0)
+        gpu.set_option("qmv_force_grid", 0)
 
 
 @pytest.mark.parametrize("n_in,n_out,k,rows", [(4096, 4096, 4, 1), (4096, 14336, 3, 4), (14336, 4096, 3, 16)])
@@ -166,7 +167,7 @@ def test_graph_replay_and_dependent_launch(gpu):
     stream.sync()
     eager = [d.download((2, 1024), np.float16, stream) for d in d_y]
     assert np.isfinite(eager[-1].astype(np.float32)).all()
-    for pdl in (0, 1):
+    for pdl in (0, 1, 2):
         gpu.set_option("pdl", pdl)
         try:
             step()                                         # warm
@@ -179,5 +180,6 @@ def test_graph_replay_and_dependent_launch(gpu):
             stream.sync()
             for want, d in zip(eager, d_y):
                 assert np.array_equal(bits(d.download((2, 1024), np.float16, stream)), bits(want))
+            assert gpu.workspace_status(ws) == 0
         finally:
             gpu.set_option("pdl", 0)
