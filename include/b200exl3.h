@@ -53,7 +53,9 @@ int b200exl3_version(void);
 /* Process-wide knobs: "qmv_ctas_per_sm" (CTAs per SM the grids are sized for), "qmv_force_grid"
  * (CTAs per launch, 0 = heuristic), "pdl" (1 or 2 = launch layer kernels with programmatic stream serialization, so the
  * weight prefetch of a layer overlaps the tail of the previous kernel in the stream; 1 releases the
- * next kernel after the main loop, 2 as soon as the first copies are in flight). */
+ * next kernel after the main loop, 2 as soon as the first copies are in flight), "qmv_trace_buffer"
+ * (device address of a uint64 [grid, 8] array that receives nanosecond stamps of each CTA's phases:
+ * start, activations visible, rotated, main loop done, warps joined, reduced, finished; 0 = off). */
 int b200exl3_set_option(const char* name, int64_t value);
 
 /* Plain device-memory plumbing for hosts that have no CUDA binding of their own (replaces

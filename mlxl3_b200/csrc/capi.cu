@@ -90,6 +90,10 @@ int b200exl3_set_option(const char* name, int64_t value) {
     if (!strcmp(name, "qmv_ctas_per_sm")) ctas = static_cast<int>(value);
     else if (!strcmp(name, "qmv_force_grid")) grid = static_cast<int>(value);
     else if (!strcmp(name, "pdl")) pdl = static_cast<int>(value);
+    else if (!strcmp(name, "qmv_trace_buffer")) {
+        qmv_set_trace(reinterpret_cast<unsigned long long*>(static_cast<uintptr_t>(value)));
+        return 0;
+    }
     else return fail("unknown option %s", name);
     qmv_set_tuning(ctas, grid, pdl);
     return 0;
@@ -282,11 +286,18 @@ void b200exl3_linear_free(b200exl3_linear* h) {
 int b200exl3_linear_input_dims(const b200exl3_linear* h) { return h ? h->in : fail("NULL handle"); }
 int b200exl3_linear_output_dims(const b200exl3_linear* h) { return h ? h->out : fail("NULL handle"); }
 
+static size_t round256(size_t v) { return (v + 255) / 256 * 256; }
+
+// workspace = [counters + status | partial tiles | rotated activations (only when the kernel does not rotate)]
+static size_t xhat_bytes(const b200exl3_linear* h, int64_t rows) {
+    return rows > kQmvFusedRows ? round256(static_cast<size_t>(rows) * h->in * sizeof(__half)) : 0;
+}
+
 int b200exl3_linear_workspace_bytes(const b200exl3_linear* h, int64_t rows, size_t* out_bytes) {
     if (!h || !out_bytes) return fail("NULL argument");
     if (rows <= 0) return fail("EXL3 linear input cannot be empty");
     QmvPlan plan = plan_qmv(h->in, h->out, h->k, rows);
-    *out_bytes = kCounterBytes + qmv_partial_bytes(plan, h->out, rows);
+    *out_bytes = kCounterBytes + qmv_partial_bytes(plan, h->out, rows) + xhat_bytes(h, rows);
     return 0;
 }
 
@@ -303,14 +314,22 @@ static int forward_common(const b200exl3_linear* h, const void* d_x, int x_dtype
     char* base = static_cast<char*>(ws);
     const bool exact = (h->flags & B200EXL3_EXACT_WEIGHTS) != 0;
     const size_t x_size = dtype_size(x_dtype);
+    const __half* xhat = reinterpret_cast<const __half*>(d_xhat);
+    if (!xhat && rows > kQmvFusedRows) {
+        // more than two rows: rotate all of them once, the product kernel reads the rotated rows
+        const QmvPlan first = plan_qmv(h->in, h->out, h->k, rows);
+        __half* buf = reinterpret_cast<__half*>(base + kCounterBytes + qmv_partial_bytes(first, h->out, rows));
+        B200_TRY(launch_prepare(d_x, x_dtype, h->suh, 1, rows, h->in, buf, stream), "prepare");
+        xhat = buf;
+    }
     for (int64_t r0 = 0; r0 < rows; r0 += kMaxBatchRows) {
         const int64_t n = rows - r0 < kMaxBatchRows ? rows - r0 : kMaxBatchRows;
         const QmvPlan plan = plan_qmv(h->in, h->out, h->k, n);
         QmvArgs a{};
         a.wq = h->wq;
-        a.x = d_x ? static_cast<const char*>(d_x) + static_cast<size_t>(r0) * h->in * x_size : nullptr;
+        a.x = !xhat ? static_cast<const char*>(d_x) + static_cast<size_t>(r0) * h->in * x_size : nullptr;
         a.suh = h->suh;
-        a.xhat = d_xhat ? reinterpret_cast<const __half*>(d_xhat) + r0 * h->in : nullptr;
+        a.xhat = xhat ? xhat + r0 * h->in : nullptr;
         a.counters = reinterpret_cast<unsigned int*>(base);
         a.error = reinterpret_cast<unsigned int*>(base + kCounterBytes - sizeof(unsigned int));
         a.partials = reinterpret_cast<float*>(base + kCounterBytes);

@@ -26,8 +26,10 @@ cudaError_t launch_finish(const float* partials, int splits, int64_t split_strid
 // ---- fused linear layer (kernels_qmv*.cu) ----------------------------------------------------------
 constexpr int kQmvWarps = 8;         // warps per CTA
 constexpr int kQmvRedStride = 132;   // floats per reduced row: 128 + 4 keeps the fragment stores conflict-free
-constexpr int kQmvMaxRows = 32;      // activation rows one launch can take
+constexpr int kQmvMaxRows = 16;      // activation rows one launch can take
 constexpr int kQmvMaxSmemBytes = 200 * 1024;
+constexpr int kQmvXBlocks = 6;       // 128-blocks of rotated activations a warp keeps per row
+constexpr int kQmvFusedRows = 2;     // up to this many rows the kernel rotates the activations itself
 
 // rows of 8 tiles kept in flight per warp
 __host__ __device__ constexpr int qmv_depth(int k) { return k <= 2 ? 8 : 4; }
@@ -40,21 +42,27 @@ struct QmvArgs {
     float* partials;           // [out/128, max_pieces, rows, 128] scratch for column blocks shared by several CTAs
     unsigned int* counters;    // [out/128] arrival counters, zero on entry and on exit
     unsigned int* error;       // set to 1 if a weight copy never arrived (bounded wait gave up)
+    unsigned long long* trace; // optional [grid, 8] nanosecond stamps of the phases of each CTA, or nullptr
     const __half* svh;         // [out]   (output rotation; used when y != nullptr)
     const __half* bias;        // [out] or nullptr
     void* y;                   // [rows, out] in y_dtype, or nullptr for raw output
     float* yhat;               // [rows, out] summed fp32 product, written when y == nullptr
     int x_dtype, y_dtype;
     int in, out, rows, tiles_k, tiles_n, max_pieces;
-    int xs_stride;             // halves per activation row in shared memory
+    int warp_smem;             // bytes of shared memory per warp
+    int xs_offset;             // offset of the rotated activations inside a warp's shared memory
+    int stage_offset;          // offset of the staged result tiles inside a warp's shared memory
     int pdl_early;             // 1: let the next kernel start as soon as this one has started its copies
 };
 
 struct QmvPlan {
-    int grid;            // CTAs: every one gets the same number of tiles (+-1)
+    int grid;            // CTAs of 8 warps: every warp gets the same number of tiles (+-1)
     int max_pieces;      // upper bound on the CTAs that share one 128-column block
     int col_blocks;      // out / 128
-    int xs_stride;       // halves per activation row in shared memory
+    int warp_smem;       // bytes of shared memory per warp
+    int xs_offset;       // offset of the rotated activations inside a warp's shared memory
+    int stage_offset;    // offset of the staged result tiles inside a warp's shared memory
+    bool fused_rotation; // the kernel rotates the activations itself (rows <= kQmvFusedRows)
     size_t smem_bytes;   // dynamic shared memory per CTA
     bool pdl;            // launch with programmatic stream serialization (overlap with the previous kernel's tail)
     bool pdl_early;      // trigger the dependent launch before the main loop instead of after it
@@ -67,6 +75,7 @@ size_t qmv_partial_bytes(const QmvPlan& plan, int out, int64_t rows);
 // feeding the two fp16 halves of a weight as two products, which differs by fp16 rounding of the weight).
 cudaError_t launch_qmv(QmvArgs args, int k, int cb, bool exact, const QmvPlan& plan, cudaStream_t stream);
 void qmv_set_tuning(int ctas_per_sm, int force_grid, int pdl);
+void qmv_set_trace(unsigned long long* device_buffer);
 
 // ---- weight layout (kernels_codec.cu) -----------------------------------------------------------------
 // checkpoint layout [tiles_k, tiles_n, 8K] words -> quad layout [tiles_k, tiles_n/4, 8K, 4]

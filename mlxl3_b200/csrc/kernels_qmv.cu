@@ -29,40 +29,35 @@ void qmv_set_tuning(int ctas_per_sm, int force_grid, int pdl) {
     g_pdl = pdl > 0 ? pdl : 0;
 }
 
-// halves per activation row kept in shared memory for a slice of at most `units` tiles of one block
-static int xs_stride_for(int tiles_k, int64_t units) {
-    // `units` tiles -> that many /8 input tiles (+1 for a ragged start) -> 128-blocks (+1 likewise);
-    // 8 halves of padding stagger the rows over the banks
-    const int64_t tks = (units + 7) / 8 + 1;
-    const int blocks = static_cast<int>(std::min<int64_t>((tks + 7) / 8 + 1, (tiles_k + 7) / 8));
-    return blocks * 128 + 8;
-}
+static unsigned long long* g_trace = nullptr;
+void qmv_set_trace(unsigned long long* device_buffer) { g_trace = device_buffer; }
 
 QmvPlan plan_qmv(int in, int out, int k, int64_t rows) {
     QmvPlan plan{};
     plan.col_blocks = out / 128;
     const int tiles_k = in / 16;
-    const int64_t ub = static_cast<int64_t>(tiles_k) * 8;
-    const int64_t total = ub * plan.col_blocks;
+    const int64_t total = static_cast<int64_t>(tiles_k) * 8 * plan.col_blocks;
     const int r = static_cast<int>(std::min<int64_t>(rows, kQmvMaxRows));
-    // register pressure grows with the number of 8-row blocks: 2 and 4 blocks fit 2 and 1 CTAs per SM
-    const int resident = r <= 8 ? g_ctas_per_sm : (r <= 16 ? std::min(g_ctas_per_sm, 2) : 1);
+    // two 8-row blocks need about twice the registers and shared memory: one CTA per SM
+    const int resident = r <= 8 ? g_ctas_per_sm : 1;
     int64_t grid = g_force_grid > 0 ? g_force_grid : static_cast<int64_t>(kSmCount) * resident;
-    // keep at least four tiles per warp so a CTA is not all prologue and epilogue
+    // keep at least four tiles per warp so a warp is not all prologue and epilogue
     grid = std::max<int64_t>(1, std::min(grid, total / (kQmvWarps * 4)));
-    const size_t ring = static_cast<size_t>(kQmvWarps) * qmv_depth(k) * 64 * k * sizeof(uint32_t);
-    // the rotated activations of a slice must fit beside the ring: more CTAs = shorter slices
-    const size_t budget = kQmvMaxSmemBytes - ring;
-    auto slice_units = [&](int64_t gr) { return std::min(ub, (total + gr - 1) / gr); };
-    while (grid < total && static_cast<size_t>(r) * xs_stride_for(tiles_k, slice_units(grid)) * sizeof(__half) > budget)
-        grid += kSmCount;
-    grid = std::min(grid, total);
+    // a warp's range must not exceed one column block (it then touches at most two blocks)
+    const int64_t ub = static_cast<int64_t>(tiles_k) * 8;
+    const int64_t min_warps = (total + ub - 2) / (ub - 1) + 1;
+    grid = std::max(grid, (min_warps + kQmvWarps - 1) / kQmvWarps);
     plan.grid = static_cast<int>(grid);
     plan.max_pieces = static_cast<int>((grid + plan.col_blocks - 1) / plan.col_blocks + 1);
-    plan.xs_stride = xs_stride_for(tiles_k, slice_units(grid));
-    const size_t xs = static_cast<size_t>(r) * plan.xs_stride * sizeof(__half);
-    const size_t red = static_cast<size_t>(kQmvWarps / 2) * r * kQmvRedStride * sizeof(float);
-    plan.smem_bytes = std::max(ring + xs, red);
+    plan.fused_rotation = r <= kQmvFusedRows;
+    // per warp: [ring of packed rows | rotated activations | two staged result tiles]
+    const size_t ring = static_cast<size_t>(qmv_depth(k)) * 64 * k * sizeof(uint32_t);
+    const size_t xs = plan.fused_rotation ? static_cast<size_t>(r) * kQmvXBlocks * 128 * sizeof(__half) : 0;
+    const size_t stage = 2 * static_cast<size_t>(r) * kQmvRedStride * sizeof(float);   // first and second block of a warp
+    plan.xs_offset = static_cast<int>(ring);
+    plan.stage_offset = static_cast<int>(ring + xs);
+    plan.warp_smem = static_cast<int>((ring + xs + stage + 15) / 16 * 16);
+    plan.smem_bytes = static_cast<size_t>(plan.warp_smem) * kQmvWarps;
     plan.pdl = g_pdl != 0;
     plan.pdl_early = g_pdl == 2;
     return plan;
@@ -80,7 +75,10 @@ cudaError_t launch_qmv(QmvArgs args, int k, int cb, bool exact, const QmvPlan& p
     args.tiles_k = args.in / 16;
     args.tiles_n = args.out / 16;
     args.max_pieces = plan.max_pieces;
-    args.xs_stride = plan.xs_stride;
+    args.trace = g_trace;
+    args.warp_smem = plan.warp_smem;
+    args.xs_offset = plan.xs_offset;
+    args.stage_offset = plan.stage_offset;
     args.pdl_early = plan.pdl_early ? 1 : 0;
     switch (k) {
         case 1: return qmv_dispatch_k1(args, cb, exact, plan, stream);

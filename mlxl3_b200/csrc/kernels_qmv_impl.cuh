@@ -1,4 +1,4 @@
-// Fused EXL3 linear layer for up to 32 activation rows (QMV and small-batch QMM) in ONE launch:
+// Fused EXL3 linear layer for up to 16 activation rows (QMV and small-batch QMM) in ONE launch:
 // input rotation -> trellis decode x activation product -> split reduction -> output rotation.
 //
 // Reference behaviour replaced: native/shaders/_qmv_tile_kernel.metal (M = 1 and the MB row-sharing
@@ -22,10 +22,12 @@
 //  * for K = 4 and K = 8 two states 16 bits apart share a register P = lo | hi << 16; then
 //    b_hi = (P >> 16) * M + C,  T = P * M + (C + (C << 16)),  b_lo = T - (b_hi << 16)
 //    hashes both without masking the low state (integer multiply-add pipe instead of the ALU pipe);
-//  * a CTA owns one 128-column block and a contiguous slice of that block's tiles; its warps own
-//    equal contiguous sub-slices (balanced to one tile).  The activations of the slice are rotated
-//    into shared memory by the CTA itself; the last CTA to finish a column block sums the split
-//    partials in a fixed order and applies the output rotation.
+//  * every warp is an independent worker: all tiles of the layer are ordered column-block-major and
+//    split evenly over all warps of the grid (balanced to one tile for any shape, one wave).  A warp
+//    rotates the activations of its own input range into shared memory, accumulates its tiles, and
+//    writes its partial [rows, 128] tile; the last warp to arrive at a column block (arrival counter)
+//    sums the partials in a fixed order and applies the output rotation.  No CTA-wide barrier exists.
+//    With more than two activation rows the rotation is done once by a separate kernel instead.
 //
 // Included by one small translation unit per K so the eight K values compile in parallel.
 #pragma once
@@ -169,161 +171,274 @@ __device__ __forceinline__ void qmv_row(const uint32_t* __restrict__ row_words, 
     }
 }
 
+// ---- the rarely executed parts of the kernel: written small (no unrolling) so that they cost the
+//      decode loop neither registers nor instruction-cache space -----------------------------------------
+
+// Rotates the activations of input 128-blocks [kb0, kb0 + nblk) of every row into the warp's shared
+// memory: xs[row][blk][128] = H128(half(half(x) * suh)).  The loads of the next block are issued before
+// the butterflies of the current one.
+__device__ __forceinline__ void qmv_rotate_chunk(const void* x, int x_dtype, const __half* suh, int in, int rows, int kb0,
+                                                 int nblk, __half* xs, int lane) {
+    constexpr int kXsHalves = kQmvXBlocks * 128;
+    const int total = rows * nblk;
+    auto fetch = [&](int unit, uint2& sv, __half (&xv)[4]) {
+        const int row = unit / nblk, blk = unit - row * nblk;
+        const int col = (kb0 + blk) * 128 + lane * 4;
+        sv = *reinterpret_cast<const uint2*>(suh + col);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) xv[j] = load_as_half(x, x_dtype, static_cast<int64_t>(row) * in + col + j);
+    };
+    uint2 sv_next;
+    __half xv_next[4];
+    fetch(0, sv_next, xv_next);
+#pragma unroll 1
+    for (int unit = 0; unit < total; ++unit) {
+        const uint2 sv = sv_next;
+        __align__(8) __half h[4];
+        const __half* sc = reinterpret_cast<const __half*>(&sv);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) h[j] = __hmul_rn(xv_next[j], sc[j]);
+        if (unit + 1 < total) fetch(unit + 1, sv_next, xv_next);
+        warp_hadamard128_f16(h, lane);
+        const int row = unit / nblk, blk = unit - row * nblk;
+        *reinterpret_cast<uint2*>(xs + row * kXsHalves + blk * 128 + lane * 4) = *reinterpret_cast<uint2*>(h);
+    }
+    __syncwarp();
+}
+
+// The last warp of a CTA to stage its tile of column block `cblock`: adds the tiles of the warps that
+// had work in the block (warp_mask) in warp order; if other CTAs share the block, publishes the
+// sum as this CTA's piece and counts arrivals; the last CTA adds the pieces in piece order.  Whoever
+// holds the complete sum applies the output rotation (or stores the raw sum).
+__device__ __forceinline__ void qmv_finish_block(const QmvArgs& p, int cblock, unsigned int warp_mask, unsigned int second_mask,
+                                              int pieces, int piece, const unsigned char* smem_base, int lane) {
+    const int rows = p.rows;
+    const int tile_floats = rows * 128;
+    const float* piece_base = p.partials + static_cast<int64_t>(cblock) * p.max_pieces * tile_floats;
+    float* piece_dst = p.partials + (static_cast<int64_t>(cblock) * p.max_pieces + piece) * tile_floats;
+    const int stage_floats = rows * kQmvRedStride;
+#pragma unroll 1
+    for (int pass = 0; pass < (pieces > 1 ? 2 : 1); ++pass) {
+        if (pass == 1) {
+            __threadfence();
+            __syncwarp();
+            unsigned int prev = 0;
+            if (lane == 0) prev = atomicAdd(p.counters + cblock, 1u);
+            prev = __shfl_sync(0xffffffffu, prev, 0);
+            if (prev != static_cast<unsigned int>(pieces - 1)) return;       // not the last CTA of this block
+            __threadfence();
+            if (lane == 0) p.counters[cblock] = 0;              // leave the scratch ready for the next call
+        }
+        const bool complete = pass == 1 || pieces == 1;
+#pragma unroll 1
+        for (int row = 0; row < rows; ++row) {
+            float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (pass == 0) {
+                bool any = false;
+#pragma unroll 1
+                for (int w = 0; w < kQmvWarps; ++w) {
+                    if (!((warp_mask >> w) & 1u)) continue;
+                    // a warp stages the tile of its first block in buffer 0 and of its second block in buffer 1
+                    const float4 t4 = *reinterpret_cast<const float4*>(
+                        reinterpret_cast<const float*>(smem_base + static_cast<size_t>(w) * p.warp_smem + p.stage_offset) +
+                        ((second_mask >> w) & 1u) * stage_floats + row * kQmvRedStride + lane * 4);
+                    if (!any) { a = t4; any = true; }
+                    else { a.x = __fadd_rn(a.x, t4.x); a.y = __fadd_rn(a.y, t4.y); a.z = __fadd_rn(a.z, t4.z); a.w = __fadd_rn(a.w, t4.w); }
+                }
+            } else {
+                const float* src = piece_base + row * 128 + lane * 4;
+                a = __ldcg(reinterpret_cast<const float4*>(src));
+#pragma unroll 1
+                for (int s0 = 1; s0 < pieces; s0 += 4) {         // loads of four pieces go out together
+                    float4 part[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        if (s0 + j < pieces) part[j] = __ldcg(reinterpret_cast<const float4*>(src + (s0 + j) * tile_floats));
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        if (s0 + j < pieces) {
+                            a.x = __fadd_rn(a.x, part[j].x); a.y = __fadd_rn(a.y, part[j].y);
+                            a.z = __fadd_rn(a.z, part[j].z); a.w = __fadd_rn(a.w, part[j].w);
+                        }
+                }
+            }
+            if (!complete) {
+                __stcg(reinterpret_cast<float4*>(piece_dst + row * 128 + lane * 4), a);
+                continue;
+            }
+            const int col = cblock * 128 + lane * 4;
+            if (p.y == nullptr) {
+                *reinterpret_cast<float4*>(p.yhat + static_cast<int64_t>(row) * p.out + col) = a;
+            } else {
+                __half h[4] = {__float2half_rn(a.x), __float2half_rn(a.y), __float2half_rn(a.z), __float2half_rn(a.w)};
+                warp_hadamard128_f16(h, lane);
+                __align__(8) __half sv[4];
+                *reinterpret_cast<uint2*>(sv) = *reinterpret_cast<const uint2*>(p.svh + col);
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    store_from_half(p.y, p.y_dtype, static_cast<int64_t>(row) * p.out + col + j, __hmul_rn(h[j], sv[j]), p.bias,
+                                    col + j);
+            }
+        }
+    }
+}
+
 template <int K, int CB, int NB, int MODE>
-__global__ void __launch_bounds__(kQmvWarps * 32)
+__global__ void __launch_bounds__(kQmvWarps * 32, NB == 1 ? 2 : 1)
 qmv_kernel(const QmvArgs p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int WARPS = kQmvWarps;
     constexpr int DEPTH = qmv_depth(K);
     constexpr int kRowWords = 64 * K;                       // 2 quads x 8K words x 4 tiles
-    constexpr int kRingBytes = WARPS * DEPTH * kRowWords * 4;
     constexpr uint32_t kRowBytes = kRowWords * 4;
-    __shared__ int s_last;
+    constexpr int kXsHalves = kQmvXBlocks * 128;            // rotated activations kept per row and warp
     __shared__ __align__(8) uint64_t s_bar[WARPS][DEPTH];
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, q = lane & 3;
     const int rows = p.rows;
-    const int G = static_cast<int>(gridDim.x);
-    const int bid = static_cast<int>(blockIdx.x);
 
-    // All tiles of the layer in column-block-major order; unit = block * UB + (tk * 8 + tile-in-row).
-    // CTA i owns units [T*i/G, T*(i+1)/G): the same number of tiles (+-1) for every CTA, so the
-    // grid is one balanced wave whatever the shape.  A CTA may touch several column blocks, and a
-    // block may be shared by several CTAs ("pieces").
-    const int64_t UB = static_cast<int64_t>(p.tiles_k) * 8;
-    const int64_t T = UB * (p.out >> 7);
-    const int64_t my0 = T * bid / G, my1 = T * (bid + 1) / G;
+    // All tiles of the layer are ordered column-block-major (unit = block * UB + tk * 8 + tile-in-row)
+    // and warp w of W owns units [T*w/W, T*(w+1)/W): the same tile count (+-1) for every warp of the
+    // grid, whatever the shape.  A warp's range may cross into the next 128-column block (it then has
+    // a segment in each).  The eight warps of a CTA walk the same list of blocks, add their tiles up in
+    // shared memory, and CTAs that share a block ("pieces") meet in global memory.
+    // (the layer has fewer than 2^31 tiles; only the products with the warp count need 64 bits)
+    const int W = static_cast<int>(gridDim.x) * WARPS;
+    const int wid = static_cast<int>(blockIdx.x) * WARPS + warp;
+    const int UB = p.tiles_k * 8;
+    const int T = UB * (p.out >> 7);
+    const int w0 = static_cast<int>(static_cast<int64_t>(T) * wid / W);
+    const int w1 = static_cast<int>(static_cast<int64_t>(T) * (wid + 1) / W);
 
-    uint32_t* ring = reinterpret_cast<uint32_t*>(smem_raw) + static_cast<size_t>(warp) * DEPTH * kRowWords;
-    __half* xs = reinterpret_cast<__half*>(smem_raw + kRingBytes);     // [rows][xs_stride]
-    float* red = reinterpret_cast<float*>(smem_raw);                    // reused after the main loop
+    unsigned char* mine = smem_raw + static_cast<size_t>(warp) * p.warp_smem;
+    uint32_t* ring = reinterpret_cast<uint32_t*>(mine);                  // DEPTH rows of packed words
+    __half* xs = reinterpret_cast<__half*>(mine + p.xs_offset);          // [rows][kXsHalves] (fused rotation only)
+    const int stage_floats = rows * kQmvRedStride;                       // one staged [rows][128] tile
     uint64_t* bars = s_bar[warp];
     const size_t row_stride = static_cast<size_t>(p.tiles_n) * (32 * K);
     const LaneGeom<K> geom(lane);
-    const int64_t tile_floats = static_cast<int64_t>(rows) * 128;
+    const bool tracing = p.trace != nullptr && threadIdx.x == 0;
+    if (tracing) p.trace[blockIdx.x * 8 + 0] = global_ns();
 
+    // the unit ranges of the CTA's eight warps, for the block walk and the mask of contributing warps
+    __shared__ int s_begin[WARPS + 1];
+    __shared__ unsigned int s_arrived[WARPS + 2];            // per visited block: warps that staged their tile
+    if (threadIdx.x <= WARPS)
+        s_begin[threadIdx.x] = static_cast<int>(static_cast<int64_t>(T) * (static_cast<int64_t>(blockIdx.x) * WARPS + threadIdx.x) / W);
+    if (threadIdx.x < WARPS + 2) s_arrived[threadIdx.x] = 0;
     if (lane == 0) {
 #pragma unroll
         for (int i = 0; i < DEPTH; ++i) mbar_init(bars + i, 1);
-        mbar_init_fence();
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // barriers visible to the copy engine
     }
-    __syncwarp();
+    __syncthreads();
+    const int cta0 = s_begin[0];
+    // A warp's range is at most one block long (the launch guarantees it), so it touches at most two
+    // blocks and owns two staging buffers: nobody ever waits for anybody inside the CTA.
+    if (w1 - w0 > UB) {
+        if (threadIdx.x == 0) atomicExch(p.error, 2u);
+        return;
+    }
     int slot = 0;
     uint32_t parity = 0;
     bool copy_lost = false;
-    bool first_block = true;
+    bool first_chunk = true;
 
-    for (int64_t cblock = my0 / UB; cblock * UB < my1; ++cblock) {
-        // ---- this CTA's slice [cta_u0, cta_u1) of the block, then this warp's slice -----------------
-        const int cta_u0 = static_cast<int>(max(my0, cblock * UB) - cblock * UB);
-        const int cta_u1 = static_cast<int>(min(my1, (cblock + 1) * UB) - cblock * UB);
-        const int cta_n = cta_u1 - cta_u0;
-        const int u0 = cta_u0 + static_cast<int>(static_cast<int64_t>(cta_n) * warp / WARPS);
-        const int u1 = cta_u0 + static_cast<int>(static_cast<int64_t>(cta_n) * (warp + 1) / WARPS);
-        const int tk_first = u0 >> 3;
-        const int nrows = u1 > u0 ? ((u1 - 1) >> 3) - tk_first + 1 : 0;
-        const int tn0 = static_cast<int>(cblock) * 8;
-        // CTA holding unit x: ceil((x+1)*G/T) - 1
-        const int i_first = static_cast<int>(((cblock * UB + 1) * G - 1) / T);
-        const int i_last = static_cast<int>((((cblock + 1) * UB) * G - 1) / T);
-        const int pieces = i_last - i_first + 1;
-
-        // ---- phase 0: start streaming weights (they do not depend on the previous kernel) ------------
-        // Whole 8-tile rows are copied even when the warp owns only part of the first or last one:
-        // one TMA copy per row, consecutive rows a fixed stride apart.
-        const char* next_src =
-            reinterpret_cast<const char*>(p.wq + (static_cast<int64_t>(tk_first) * p.tiles_n + tn0) * (8 * K));
-        if (lane == 0) {
-            // the slots may hold reduction scratch written through the generic proxy by the previous block
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-#pragma unroll
-            for (int i = 0; i < DEPTH; ++i)
-                if (i < nrows) {
-                    const int sl = slot + i < DEPTH ? slot + i : slot + i - DEPTH;
-                    mbar_expect_tx(bars + sl, kRowBytes);
-                    bulk_copy_g2s(ring + sl * kRowWords, next_src + i * row_stride, kRowBytes, bars + sl);
-                }
-        }
-        next_src += DEPTH * row_stride;
-        if (first_block) {
-            if (p.pdl_early) pdl_launch_dependents();
-            pdl_wait();
-            first_block = false;
-        }
-
-        // ---- phase 1: rotate (or fetch) the activations of this slice's input range into shared memory
-        const int kb0 = (cta_u0 >> 3) >> 3;                              // first 128-block
-        const int kb1 = (((cta_u1 - 1) >> 3) >> 3) + 1;                  // one past the last
+    for (int cblock = w0 / UB; cblock * UB < w1; ++cblock) {
+        // ---- this warp's segment [u0, u1) of the block ----------------------------------------------------
+        const int u0 = max(w0, cblock * UB) - cblock * UB;
+        const int u1 = min(w1, (cblock + 1) * UB) - cblock * UB;
+        float* stage = reinterpret_cast<float*>(mine + p.stage_offset) + (cblock - w0 / UB) * stage_floats;
         {
-            const int nblk = kb1 - kb0;
-            for (int unit = warp; unit < rows * nblk; unit += WARPS) {
-                const int row = unit / nblk, blk = unit % nblk;
-                const int col = (kb0 + blk) * 128 + lane * 4;
-                __align__(8) __half h[4];
-                if (p.xhat) {
-                    *reinterpret_cast<uint2*>(h) = *reinterpret_cast<const uint2*>(p.xhat + static_cast<int64_t>(row) * p.in + col);
-                } else {
-                    __align__(8) __half sc[4];
-                    *reinterpret_cast<uint2*>(sc) = *reinterpret_cast<const uint2*>(p.suh + col);
+            const int tk_first = u0 >> 3, tk_last = (u1 - 1) >> 3;
+            const int lo_first = u0 & 7, hi_last = ((u1 - 1) & 7) + 1;
+            const int tn0 = cblock * 8;
+
+            float acc[8][NB][4];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        h[j] = __hmul_rn(load_as_half(p.x, p.x_dtype, static_cast<int64_t>(row) * p.in + col + j), sc[j]);
-                    warp_hadamard128_f16(h, lane);
+            for (int t = 0; t < 8; ++t)
+#pragma unroll
+                for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) acc[t][nb][i] = 0.0f;
+
+            // The segment is walked in chunks whose inputs span at most kQmvXBlocks 128-blocks, so that
+            // the rotated activations of a chunk fit the warp's shared memory.
+            for (int tk0 = tk_first; tk0 <= tk_last;) {
+                const int kb0 = tk0 >> 3;
+                const int tk_end = min(tk_last + 1, (kb0 + kQmvXBlocks) * 8);
+                const int nrows = tk_end - tk0;
+
+                // ---- phase 0: start streaming weights (they do not depend on the previous kernel) ----
+                // Whole 8-tile rows are copied even when the warp owns only part of the first or last
+                // one: one TMA copy per row, consecutive rows a fixed stride apart.
+                const char* next_src =
+                    reinterpret_cast<const char*>(p.wq + (static_cast<int64_t>(tk0) * p.tiles_n + tn0) * (8 * K));
+                if (lane == 0) {
+#pragma unroll
+                    for (int i = 0; i < DEPTH; ++i)
+                        if (i < nrows) {
+                            const int sl = slot + i < DEPTH ? slot + i : slot + i - DEPTH;
+                            mbar_expect_tx(bars + sl, kRowBytes);
+                            bulk_copy_g2s(ring + sl * kRowWords, next_src + i * row_stride, kRowBytes, bars + sl);
+                        }
                 }
-                *reinterpret_cast<uint2*>(xs + row * p.xs_stride + blk * 128 + lane * 4) = *reinterpret_cast<uint2*>(h);
-            }
-        }
-        __syncthreads();
-
-        // ---- phase 2: decode x activations ----------------------------------------------------------------
-        float acc[8][NB][4];
-#pragma unroll
-        for (int t = 0; t < 8; ++t)
-#pragma unroll
-            for (int nb = 0; nb < NB; ++nb)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) acc[t][nb][i] = 0.0f;
-
-        // activation fragments of input tile tk: rows nb*8+g, inputs 16tk + {2q, 2q+1, 2q+8, 2q+9}
-        const uint32_t* xfrag[NB];
-#pragma unroll
-        for (int nb = 0; nb < NB; ++nb) {
-            const int row = min(nb * 8 + g, rows - 1);
-            xfrag[nb] = reinterpret_cast<const uint32_t*>(xs + row * p.xs_stride + (tk_first * 16 - kb0 * 128)) + q;
-        }
-        const int lo_first = u0 & 7, hi_last = nrows > 0 ? ((u1 - 1) & 7) + 1 : 8;
-        for (int r = 0; r < nrows; ++r) {
-            uint32_t bx[NB][4];
-#pragma unroll
-            for (int nb = 0; nb < NB; ++nb) {
-                uint32_t p0 = xfrag[nb][r * 8], p1 = xfrag[nb][r * 8 + 4];
-                if (nb * 8 + g >= rows) { p0 = 0; p1 = 0; }
-                if constexpr (MODE == 0) {
-                    bx[nb][0] = prmt(p0, p0, 0x1010); bx[nb][1] = prmt(p0, p0, 0x3232);
-                    bx[nb][2] = prmt(p1, p1, 0x1010); bx[nb][3] = prmt(p1, p1, 0x3232);
-                } else {
-                    bx[nb][0] = p0; bx[nb][1] = p1; bx[nb][2] = 0; bx[nb][3] = 0;
+                next_src += DEPTH * row_stride;
+                if (first_chunk) {
+                    if (p.pdl_early) pdl_launch_dependents();
+                    pdl_wait();
+                    first_chunk = false;
+                    if (tracing) p.trace[blockIdx.x * 8 + 1] = global_ns();
                 }
-            }
-            if (!mbar_wait(bars + slot, parity)) copy_lost = true;
-            const uint32_t* row_words = ring + slot * kRowWords;
-            const int lo = r == 0 ? lo_first : 0, hi = r == nrows - 1 ? hi_last : 8;
-            if (lo == 0 && hi == 8) qmv_row<K, CB, NB, MODE, true>(row_words, geom, 0, 8, bx, acc);
-            else qmv_row<K, CB, NB, MODE, false>(row_words, geom, lo, hi, bx, acc);
-            __syncwarp();                                       // every lane has read the slot
-            if (lane == 0 && r + DEPTH < nrows) {
-                mbar_expect_tx(bars + slot, kRowBytes);
-                bulk_copy_g2s(ring + slot * kRowWords, next_src, kRowBytes, bars + slot);
-            }
-            next_src += row_stride;
-            if (++slot == DEPTH) { slot = 0; parity ^= 1u; }
-        }
-        if (!p.pdl_early && (cblock + 1) * UB >= my1) pdl_launch_dependents();
 
-        // ---- phase 3: deterministic tree reduction over the warps -------------------------------------------
-        __syncthreads();                                        // ring and activations are dead from here on
-        auto frag_store = [&](float* base) {
+                // ---- phase 1: rotate this chunk's activations into the warp's shared memory ------------
+                if (p.xhat == nullptr)
+                    qmv_rotate_chunk(p.x, p.x_dtype, p.suh, p.in, rows, kb0, ((tk_end - 1) >> 3) - kb0 + 1, xs, lane);
+                if (tracing && tk0 == tk_first) p.trace[blockIdx.x * 8 + 2] = global_ns();
+
+                // ---- phase 2: decode x activations ----------------------------------------------------------
+                // activation fragments of input tile tk: rows nb*8+g, inputs 16tk + {2q, 2q+1, 2q+8, 2q+9}
+                const uint32_t* xfrag[NB];
+#pragma unroll
+                for (int nb = 0; nb < NB; ++nb) {
+                    const int row = min(nb * 8 + g, rows - 1);
+                    if (p.xhat == nullptr)
+                        xfrag[nb] = reinterpret_cast<const uint32_t*>(xs + row * kXsHalves + (tk0 * 16 - kb0 * 128)) + q;
+                    else
+                        xfrag[nb] = reinterpret_cast<const uint32_t*>(p.xhat + static_cast<int64_t>(row) * p.in + tk0 * 16) + q;
+                }
+                for (int r = 0; r < nrows; ++r) {
+                    const int tk = tk0 + r;
+                    uint32_t bx[NB][4];
+#pragma unroll
+                    for (int nb = 0; nb < NB; ++nb) {
+                        uint32_t p0 = xfrag[nb][r * 8], p1 = xfrag[nb][r * 8 + 4];
+                        if (nb * 8 + g >= rows) { p0 = 0; p1 = 0; }
+                        if constexpr (MODE == 0) {
+                            bx[nb][0] = prmt(p0, p0, 0x1010); bx[nb][1] = prmt(p0, p0, 0x3232);
+                            bx[nb][2] = prmt(p1, p1, 0x1010); bx[nb][3] = prmt(p1, p1, 0x3232);
+                        } else {
+                            bx[nb][0] = p0; bx[nb][1] = p1; bx[nb][2] = 0; bx[nb][3] = 0;
+                        }
+                    }
+                    if (!mbar_wait(bars + slot, parity)) copy_lost = true;
+                    const uint32_t* row_words = ring + slot * kRowWords;
+                    const int lo = tk == tk_first ? lo_first : 0, hi = tk == tk_last ? hi_last : 8;
+                    if (lo == 0 && hi == 8) qmv_row<K, CB, NB, MODE, true>(row_words, geom, 0, 8, bx, acc);
+                    else qmv_row<K, CB, NB, MODE, false>(row_words, geom, lo, hi, bx, acc);
+                    __syncwarp();                               // every lane has read the slot
+                    if (lane == 0 && r + DEPTH < nrows) {
+                        mbar_expect_tx(bars + slot, kRowBytes);
+                        bulk_copy_g2s(ring + slot * kRowWords, next_src, kRowBytes, bars + slot);
+                    }
+                    next_src += row_stride;
+                    if (++slot == DEPTH) { slot = 0; parity ^= 1u; }
+                }
+                tk0 = tk_end;
+            }
+
+            // ---- phase 3: stage the fragment as a [rows][128] tile in this warp's shared memory -----------
 #pragma unroll
             for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
@@ -331,89 +446,38 @@ qmv_kernel(const QmvArgs p) {
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         const int row = nb * 8 + 2 * q + (i & 1), col = t * 16 + g + ((i & 2) ? 8 : 0);
-                        if (row < rows) base[row * kQmvRedStride + col] = acc[t][nb][i];
+                        if (row < rows) stage[row * kQmvRedStride + col] = acc[t][nb][i];
                     }
-        };
-        auto frag_add = [&](const float* base) {
-#pragma unroll
-            for (int nb = 0; nb < NB; ++nb)
-#pragma unroll
-                for (int t = 0; t < 8; ++t)
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const int row = nb * 8 + 2 * q + (i & 1), col = t * 16 + g + ((i & 2) ? 8 : 0);
-                        if (row < rows) acc[t][nb][i] = __fadd_rn(acc[t][nb][i], base[row * kQmvRedStride + col]);
-                    }
-        };
-        const int slab = rows * kQmvRedStride;
-#pragma unroll
-        for (int half = WARPS / 2; half >= 1; half >>= 1) {
-            if (warp >= half && warp < 2 * half) frag_store(red + (warp - half) * slab);
-            __syncthreads();
-            if (warp < half) frag_add(red + warp * slab);
-            __syncthreads();
         }
-        if (warp == 0) frag_store(red);
-        __syncthreads();
+        if (!p.pdl_early && (cblock + 1) * UB >= w1) pdl_launch_dependents();
+        if (tracing) p.trace[blockIdx.x * 8 + 3] = global_ns();
 
-        // ---- phase 4: pieces of a block held by different CTAs; the last to arrive finishes the block ----
-        bool finish = true;
-        const float* piece_base = p.partials + cblock * p.max_pieces * tile_floats;
-        if (pieces > 1) {
-            float* dst = p.partials + (cblock * p.max_pieces + (bid - i_first)) * tile_floats;
-            for (int i = threadIdx.x; i < rows * 128; i += WARPS * 32)
-                __stcg(dst + i, red[(i >> 7) * kQmvRedStride + (i & 127)]);
-            __threadfence();
-            __syncthreads();
-            if (threadIdx.x == 0) {
-                const unsigned int prev = atomicAdd(p.counters + cblock, 1u);
-                s_last = prev == static_cast<unsigned int>(pieces - 1);
+        // ---- phase 4: the last warp of the CTA to arrive at this block adds the CTA's tiles, meets the
+        //      other CTAs of the block, rotates and stores ---------------------------------------------------
+        unsigned int mask = 0, second = 0;                      // warps with a tile here; ... as their 2nd block
+#pragma unroll 1
+        for (int w = 0; w < WARPS; ++w)
+            if (min(s_begin[w + 1], (cblock + 1) * UB) > max(s_begin[w], cblock * UB)) {
+                mask |= 1u << w;
+                if (s_begin[w] / UB != cblock) second |= 1u << w;
             }
-            __syncthreads();
-            finish = s_last != 0;
-            if (finish) {
-                __threadfence();
-                if (threadIdx.x == 0) p.counters[cblock] = 0;   // leave the scratch ready for the next call
-            }
+        __syncwarp();
+        unsigned int prev = 0;
+        if (lane == 0) {
+            __threadfence_block();                              // the staged tile before the arrival
+            prev = atomicAdd(&s_arrived[cblock - cta0 / UB], 1u);
         }
-        if (finish) {
-            // one warp per activation row: sum the pieces in order, rotate, scale, store
-            for (int row = warp; row < rows; row += WARPS) {
-                float v[4];
-                if (pieces > 1) {
-                    const float* src = piece_base + row * 128 + lane * 4;
-                    float4 a = __ldcg(reinterpret_cast<const float4*>(src));
-                    for (int s0 = 1; s0 < pieces; s0 += 8) {
-                        float4 part[8];
-#pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            if (s0 + j < pieces) part[j] = __ldcg(reinterpret_cast<const float4*>(src + (s0 + j) * tile_floats));
-#pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            if (s0 + j < pieces) {
-                                a.x = __fadd_rn(a.x, part[j].x); a.y = __fadd_rn(a.y, part[j].y);
-                                a.z = __fadd_rn(a.z, part[j].z); a.w = __fadd_rn(a.w, part[j].w);
-                            }
-                    }
-                    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) v[j] = red[row * kQmvRedStride + lane * 4 + j];
-                }
-                const int col = static_cast<int>(cblock) * 128 + lane * 4;
-                if (p.y == nullptr) {
-                    *reinterpret_cast<float4*>(p.yhat + static_cast<int64_t>(row) * p.out + col) = make_float4(v[0], v[1], v[2], v[3]);
-                } else {
-                    __half h[4] = {__float2half_rn(v[0]), __float2half_rn(v[1]), __float2half_rn(v[2]), __float2half_rn(v[3])};
-                    warp_hadamard128_f16(h, lane);
-#pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        store_from_half(p.y, p.y_dtype, static_cast<int64_t>(row) * p.out + col + j,
-                                        __hmul_rn(h[j], p.svh[col + j]), p.bias, col + j);
-                }
-            }
+        prev = __shfl_sync(0xffffffffu, prev, 0);
+        if (tracing) p.trace[blockIdx.x * 8 + 4] = global_ns();
+        if (prev + 1 == static_cast<unsigned int>(__popc(mask))) {
+            __threadfence_block();
+            // CTA holding unit x: (ceil((x+1)*W/T) - 1) / WARPS
+            const int i_first = static_cast<int>((((static_cast<int64_t>(cblock) * UB + 1) * W - 1) / T) / WARPS);
+            const int i_last = static_cast<int>(((static_cast<int64_t>(cblock + 1) * UB * W - 1) / T) / WARPS);
+            qmv_finish_block(p, cblock, mask, second, i_last - i_first + 1, static_cast<int>(blockIdx.x) - i_first, smem_raw,
+                             lane);
+            if (tracing) p.trace[blockIdx.x * 8 + 5] = global_ns();
         }
-        __syncthreads();                                        // shared memory is reused by the next block
     }
     if (copy_lost && lane == 0) atomicExch(p.error, 1u);
 }
@@ -443,8 +507,7 @@ cudaError_t qmv_launch_one(const QmvArgs& p, const QmvPlan& plan, cudaStream_t s
 template <int K, int CB, int MODE>
 cudaError_t qmv_launch_nb(const QmvArgs& p, const QmvPlan& plan, cudaStream_t stream) {
     if (p.rows <= 8) return qmv_launch_one<K, CB, 1, MODE>(p, plan, stream);
-    if (p.rows <= 16) return qmv_launch_one<K, CB, 2, MODE>(p, plan, stream);
-    return qmv_launch_one<K, CB, 4, MODE>(p, plan, stream);
+    return qmv_launch_one<K, CB, 2, MODE>(p, plan, stream);
 }
 
 template <int K>
