@@ -5,7 +5,9 @@
 Workload (N = 1): the quantized projections of a Llama-3-8B-shaped decoder at 4.0 bits per weight
 (32 layers x {q, k, v, o, gate, up, down}; hidden 4096, FFN 14336, 8 KV heads), batch-1 decode
 (QMV): one step is one activation row through all 224 projections, each with its own weights,
-3.49 GB of packed trellis in total, so every step streams far more than the 126 MB L2.  The o
+3.49 GB of packed trellis in total, so every step streams far more than the 126 MB L2.  q/k/v and
+gate/up share their input and run as one fused group launch each (128 launches per step), recorded
+once and replayed as a CUDA graph.  The o
 projection of every layer is the single-layer 4096 x 4096 K=4 configuration.  Inputs are seeded
 synthetic data: uniform random trellis words (any bit string is a valid EXL3 tile), +-1 fp16 sign
 vectors, x ~ N(0, 1) fp16.
@@ -36,11 +38,13 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 HIDDEN, FFN, KV, LAYERS, K_BITS, CB = 4096, 14336, 1024, 32, 4, 0
-# name, in, out, tensor-parallel kind
-PROJECTIONS = [("q", HIDDEN, HIDDEN, "col"), ("k", HIDDEN, KV, "col"), ("v", HIDDEN, KV, "col"),
-               ("o", HIDDEN, HIDDEN, "row"), ("gate", HIDDEN, FFN, "col"), ("up", HIDDEN, FFN, "col"),
-               ("down", FFN, HIDDEN, "row")]
-WORKLOAD = "llama3-8b-shaped EXL3 4.0bpw projections (32 layers x q,k,v,o,gate,up,down), batch-1 decode QMV"
+# launch unit: (member names, in, member outs, tensor-parallel kind).  q/k/v and gate/up read the same
+# input and run as one Exl3Group launch each, as the reference's ProjectionBundle fuses them
+# (native/src/qwen35.rs:63-96 of the reference).
+LAUNCHES = [(("q", "k", "v"), HIDDEN, (HIDDEN, KV, KV), "col"), (("o",), HIDDEN, (HIDDEN,), "row"),
+            (("gate", "up"), HIDDEN, (FFN, FFN), "col"), (("down",), FFN, (HIDDEN,), "row")]
+WORKLOAD = ("llama3-8b-shaped EXL3 4.0bpw projections (32 layers x [q|k|v], o, [gate|up], down; 224 projections in "
+            "128 launches), batch-1 decode QMV")
 
 
 def algorithmic_bytes(n_in: int, n_out: int, k: int, rows: int) -> int:
@@ -128,30 +132,39 @@ def run_ours(args) -> dict:
     rows = 1
 
     # ---- build the sharded projections, each with its own seeded weights -------------------------
-    layers = []
+    layers = []            # (kind, in, [outs], operator)
     total_bytes = 0
     rng_x = np.random.default_rng(4242)
     for layer in range(LAYERS):
-        for j, (name, n_in, n_out, kind) in enumerate(PROJECTIONS):
-            s_in, s_out = shard(kind, n_in, n_out, world)
-            rng = np.random.default_rng([1001, layer, j, rank])
-            trellis = rng.integers(0, 65536, (s_in // 16, s_out // 16, 16 * K_BITS), dtype=np.uint16)
-            suh = np.where(rng.random(s_in) > 0.5, -1, 1).astype(np.float16)
-            svh = np.where(rng.random(s_out) > 0.5, -1, 1).astype(np.float16)
-            layers.append((kind, s_in, s_out, ex.Exl3Linear(trellis, suh, svh, None, K_BITS, CB)))
-            total_bytes += algorithmic_bytes(n_in, n_out, K_BITS, rows)   # whole-job bytes, counted once
+        for j, (names, n_in, n_outs, kind) in enumerate(LAUNCHES):
+            members = []
+            for m, n_out in enumerate(n_outs):
+                s_in, s_out = shard(kind, n_in, n_out, world)
+                rng = np.random.default_rng([1001, layer, j, m, rank])
+                trellis = rng.integers(0, 65536, (s_in // 16, s_out // 16, 16 * K_BITS), dtype=np.uint16)
+                suh = np.where(rng.random(s_in) > 0.5, -1, 1).astype(np.float16)
+                svh = np.where(rng.random(s_out) > 0.5, -1, 1).astype(np.float16)
+                members.append(ex.Exl3Linear(trellis, suh, svh, None, K_BITS, CB))
+                total_bytes += algorithmic_bytes(n_in, n_out, K_BITS, rows)   # whole-job bytes, counted once
+            if len(members) > 1:
+                op = ex.Exl3Group(members)
+                for m in members:
+                    m.close()
+            else:
+                op = members[0]
+            layers.append((kind, shard(kind, n_in, n_outs[0], world)[0], [shard(kind, n_in, o, world)[1] for o in n_outs], op))
     x_host = {n: PinnedBuffer((rows, n), np.float16) for n in {l[1] for l in layers}}
     for n, buf in x_host.items():
         buf.array[...] = rng_x.standard_normal((rows, n)).astype(np.float16)
     d_x = {n: DeviceBuffer.from_numpy(buf.array) for n, buf in x_host.items()}
-    d_y = {n: DeviceBuffer(rows * n * 2) for n in {l[2] for l in layers}}
-    y_host = PinnedBuffer((rows, layers[-1][2]), np.float16)
+    d_y = {n: [DeviceBuffer(rows * n * 2) for _ in range(3)] for n in {o for l in layers for o in l[2]}}
+    y_host = PinnedBuffer((rows, layers[-1][2][0]), np.float16)
     ws = ex.new_workspace(max(l[3].workspace_bytes(rows) for l in layers))
 
     if world > 1:
         import torch
         stream = Stream(handle=torch.cuda.current_stream().cuda_stream)
-        yhat = {n: torch.empty((rows, n), dtype=torch.float32, device="cuda") for n in {l[2] for l in layers}}
+        yhat = {n: torch.empty((rows, n), dtype=torch.float32, device="cuda") for n in {o for l in layers for o in l[2]}}
     else:
         stream = Stream()
 
@@ -163,15 +176,17 @@ def run_ours(args) -> dict:
     graph = None
 
     def launch_all() -> None:
-        for kind, s_in, s_out, lin in layers:
+        for kind, s_in, s_outs, op in layers:
             if world > 1 and kind == "row":
                 # row-parallel: fp32 partial sums -> all-reduce over NVLink -> output rotation
-                buf = yhat[s_out]
-                lin.forward_partial_device(d_x[s_in].ptr, ex.F16, rows, buf.data_ptr(), ws, stream)
+                buf = yhat[s_outs[0]]
+                op.forward_partial_device(d_x[s_in].ptr, ex.F16, rows, buf.data_ptr(), ws, stream)
                 dist.all_reduce(buf)
-                lin.finish_device(buf.data_ptr(), rows, ex.F16, d_y[s_out].ptr, stream)
+                op.finish_device(buf.data_ptr(), rows, ex.F16, d_y[s_outs[0]][0].ptr, stream)
+            elif len(s_outs) > 1:
+                op.forward_device(d_x[s_in].ptr, ex.F16, rows, [d_y[o][i].ptr for i, o in enumerate(s_outs)], ws, stream)
             else:
-                lin.forward_device(d_x[s_in].ptr, ex.F16, rows, d_y[s_out].ptr, ws, stream)
+                op.forward_device(d_x[s_in].ptr, ex.F16, rows, d_y[s_outs[0]][0].ptr, ws, stream)
 
     def step(host_io: bool) -> None:
         if host_io:
@@ -182,8 +197,8 @@ def run_ours(args) -> dict:
         else:
             launch_all()
         if host_io:
-            last = layers[-1][2]
-            _lib.call("b200exl3_memcpy_d2h", c_void_p(y_host.ptr), c_void_p(d_y[last].ptr), y_host.nbytes,
+            last = layers[-1][2][0]
+            _lib.call("b200exl3_memcpy_d2h", c_void_p(y_host.ptr), c_void_p(d_y[last][0].ptr), y_host.nbytes,
                       c_void_p(stream.handle))
             stream.sync()
 
@@ -213,7 +228,7 @@ def run_ours(args) -> dict:
         return ms
 
     if world == 1 and not args.no_graph:
-        # one decode step = one graph replay: the 224 launches are recorded once (the reference's
+        # one decode step = one graph replay: the 128 launches are recorded once (the reference's
         # engine does the same with its graph replay, native/ffi/mlx_bridge.cpp:150-175)
         launch_all()
         stream.sync()
@@ -242,10 +257,10 @@ def run_ours(args) -> dict:
         "roofline": {"bound": "hbm", "achieved": round(per_gpu, 2), "peak": peak, "unit": "GB/s",
                      "frac": round(per_gpu / peak, 4), "traffic": None, "peak_kind": f"of {peak_kind}",
                      "note": "achieved = algorithmic bytes of a step / device time of the step, per GPU; the step "
-                             "is 224 launches of the one fused kernel (rotations included), so this is also the "
+                             "is 128 launches of the one fused kernel (rotations included), so this is also the "
                              "per-launch average"},
         "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": rows * layers[0][1] * 2,
-                "d2h_bytes_per_step": rows * layers[-1][2] * 2},
+                "d2h_bytes_per_step": rows * layers[-1][2][0] * 2},
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks,
     }

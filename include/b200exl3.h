@@ -41,6 +41,7 @@ extern "C" {
 #define B200EXL3_WORKSPACE_HEADER_BYTES 16384
 
 typedef struct b200exl3_linear b200exl3_linear;
+typedef struct b200exl3_group b200exl3_group;
 typedef void* b200exl3_stream;     /* cudaStream_t */
 
 /* ---- runtime (replaces mlxl3_mlx_init / mlxl3_mlx_error, native/ffi/mlx_bridge.cpp:176, 222-232) ---- */
@@ -154,6 +155,23 @@ int b200exl3_linear_finish(const b200exl3_linear* handle, const float* d_yhat, i
                            b200exl3_stream stream);
 /* Inner matrix W [in, out] fp16 of this layer (the bit-exact deliverable). */
 int b200exl3_linear_decode(const b200exl3_linear* handle, uint16_t* d_w_f16, b200exl3_stream stream);
+
+/* ---- Exl3Group (replaces native/src/linear.rs:2285-2814 and native/shaders/_qmv_mapped_tile_kernel.metal
+ *      in its identity-map use): projections that read the same input (q/k/v, gate/up), each with its
+ *      own suh, run as ONE launch ---- */
+
+/* Same rule as Exl3Group::compatible (native/src/linear.rs:2303-2311): at least two members with equal
+ * input width, K and codebook (K = 7 is accepted too; the reference excludes it for an Apple-specific
+ * reason).  Weights and scales are copied (concatenated along the output axis, native/src/linear.rs:
+ * 2313-2375), so the members may be freed afterwards.  At most 8 members. */
+int b200exl3_group_create(const b200exl3_linear* const* members, int count, b200exl3_group** out_handle);
+void b200exl3_group_free(b200exl3_group* handle);
+int b200exl3_group_count(const b200exl3_group* handle);
+int b200exl3_group_workspace_bytes(const b200exl3_group* handle, int64_t rows, size_t* out_bytes);
+/* Exl3Group::forward (native/src/linear.rs:2377-2814): x [rows, in] -> count outputs, d_ys[g] is
+ * [rows, out_g] in x's dtype. */
+int b200exl3_group_forward(const b200exl3_group* handle, const void* d_x, int x_dtype, int64_t rows, void* const* d_ys,
+                           void* d_workspace, size_t workspace_bytes, b200exl3_stream stream);
 
 #ifdef __cplusplus
 }

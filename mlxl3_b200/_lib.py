@@ -61,6 +61,11 @@ SIGNATURES = {
                                                 c_void_p]),
     "b200exl3_linear_finish": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p]),
     "b200exl3_linear_decode": (c_int, [c_void_p, c_void_p, c_void_p]),
+    "b200exl3_group_create": (c_int, [POINTER(c_void_p), c_int, POINTER(c_void_p)]),
+    "b200exl3_group_free": (None, [c_void_p]),
+    "b200exl3_group_count": (c_int, [c_void_p]),
+    "b200exl3_group_workspace_bytes": (c_int, [c_void_p, c_int64, POINTER(c_size_t)]),
+    "b200exl3_group_forward": (c_int, [c_void_p, c_void_p, c_int, c_int64, POINTER(c_void_p), c_void_p, c_size_t, c_void_p]),
 }
 
 _lib = None

@@ -58,14 +58,28 @@ constexpr size_t kCounterBytes = B200EXL3_WORKSPACE_HEADER_BYTES;   // arrival c
 
 }  // namespace
 
-struct b200exl3_linear {
-    int in, out, k, cb, device;
+// One launchable layer: a plain Exl3Linear (groups == 1) or several projections that share their
+// input, concatenated along the output axis (Exl3Group).
+struct LayerCore {
+    int in, out, k, cb;
     uint32_t flags;
-    uint32_t* wq;       // weights in the quad layout, owned
-    __half* suh;
-    __half* svh;
-    __half* bias;
+    uint32_t* wq;       // weights in the quad layout [in/16, out/64, 8K, 4], owned
+    __half* suh;        // [groups, in]
+    __half* svh;        // [out]
+    __half* bias;       // [out] or nullptr
+    int groups;
+    int gcol0[kQmvMaxGroups], gout[kQmvMaxGroups];
 };
+
+struct b200exl3_linear { LayerCore c; };
+struct b200exl3_group { LayerCore c; };
+
+static void core_free(LayerCore& c) {
+    cudaFree(c.suh);
+    cudaFree(c.svh);
+    cudaFree(c.bias);
+    cudaFree(c.wq);
+}
 
 extern "C" {
 
@@ -247,10 +261,11 @@ int b200exl3_linear_create(const uint16_t* d_trellis, const void* d_suh, const v
     if (!dtype_is_float(scale_dtype)) return fail("unsupported scale dtype %d", scale_dtype);
     if (!aligned16(d_trellis)) return fail("device pointers must be 16-byte aligned");
     if (out / 128 >= static_cast<int>(kCounterBytes / sizeof(unsigned int))) return fail("output dimension %d is too large", out);
-    b200exl3_linear* h = new (std::nothrow) b200exl3_linear{};
-    if (!h) return fail("out of host memory");
+    b200exl3_linear* handle = new (std::nothrow) b200exl3_linear{};
+    if (!handle) return fail("out of host memory");
+    LayerCore* h = &handle->c;
     h->in = in; h->out = out; h->k = k; h->cb = cb; h->flags = flags;
-    cudaGetDevice(&h->device);
+    h->groups = 1; h->gcol0[0] = 0; h->gout[0] = out;
     auto convert = [&](const void* src, int n, __half** dst) -> int {
         B200_TRY(cudaMalloc(dst, static_cast<size_t>(n) * sizeof(__half)), "cudaMalloc(scales)");
         to_half_kernel<<<(n + 255) / 256, 256>>>(src, scale_dtype, n, *dst);
@@ -267,80 +282,89 @@ int b200exl3_linear_create(const uint16_t* d_trellis, const void* d_suh, const v
     }
     if (!rc) rc = check(cudaDeviceSynchronize(), "linear_create");
     if (rc) {
-        b200exl3_linear_free(h);
+        b200exl3_linear_free(handle);
         return -1;
     }
-    *out_handle = h;
+    *out_handle = handle;
     return 0;
 }
 
 void b200exl3_linear_free(b200exl3_linear* h) {
     if (!h) return;
-    cudaFree(h->suh);
-    cudaFree(h->svh);
-    cudaFree(h->bias);
-    cudaFree(h->wq);
+    core_free(h->c);
     delete h;
 }
 
-int b200exl3_linear_input_dims(const b200exl3_linear* h) { return h ? h->in : fail("NULL handle"); }
-int b200exl3_linear_output_dims(const b200exl3_linear* h) { return h ? h->out : fail("NULL handle"); }
+int b200exl3_linear_input_dims(const b200exl3_linear* h) { return h ? h->c.in : fail("NULL handle"); }
+int b200exl3_linear_output_dims(const b200exl3_linear* h) { return h ? h->c.out : fail("NULL handle"); }
 
 static size_t round256(size_t v) { return (v + 255) / 256 * 256; }
 
 // workspace = [counters + status | partial tiles | rotated activations (only when the kernel does not rotate)]
-static size_t xhat_bytes(const b200exl3_linear* h, int64_t rows) {
-    return rows > kQmvFusedRows ? round256(static_cast<size_t>(rows) * h->in * sizeof(__half)) : 0;
+static size_t xhat_bytes(const LayerCore& c, int64_t rows) {
+    return rows > kQmvFusedRows ? round256(static_cast<size_t>(c.groups) * rows * c.in * sizeof(__half)) : 0;
 }
 
-int b200exl3_linear_workspace_bytes(const b200exl3_linear* h, int64_t rows, size_t* out_bytes) {
-    if (!h || !out_bytes) return fail("NULL argument");
+static int core_workspace_bytes(const LayerCore& c, int64_t rows, size_t* out_bytes) {
+    if (!out_bytes) return fail("NULL argument");
     if (rows <= 0) return fail("EXL3 linear input cannot be empty");
-    QmvPlan plan = plan_qmv(h->in, h->out, h->k, rows);
-    *out_bytes = kCounterBytes + qmv_partial_bytes(plan, h->out, rows) + xhat_bytes(h, rows);
+    QmvPlan plan = plan_qmv(c.in, c.out, c.k, rows);
+    *out_bytes = kCounterBytes + qmv_partial_bytes(plan, c.out, rows) + xhat_bytes(c, rows);
     return 0;
 }
 
+int b200exl3_linear_workspace_bytes(const b200exl3_linear* h, int64_t rows, size_t* out_bytes) {
+    if (!h) return fail("NULL argument");
+    return core_workspace_bytes(h->c, rows, out_bytes);
+}
+
 // One fused launch per batch of up to kMaxBatchRows rows.  Exactly one of d_x / d_xhat is given;
-// d_y != nullptr selects the rotated output, otherwise the summed fp32 product goes to d_yhat.
-static int forward_common(const b200exl3_linear* h, const void* d_x, int x_dtype, const uint16_t* d_xhat, int64_t rows,
-                          void* d_y, float* d_yhat, void* ws, size_t ws_bytes, cudaStream_t stream) {
-    if (!h) return fail("NULL handle");
+// ys (one pointer per group) selects the rotated output, otherwise the summed fp32 product goes to d_yhat.
+static int forward_common(const LayerCore& c, const void* d_x, int x_dtype, const uint16_t* d_xhat, int64_t rows,
+                          void* const* ys, float* d_yhat, void* ws, size_t ws_bytes, cudaStream_t stream) {
     if (rows <= 0) return fail("EXL3 linear input cannot be empty");
     size_t need = 0;
-    if (b200exl3_linear_workspace_bytes(h, rows, &need)) return -1;
+    if (core_workspace_bytes(c, rows, &need)) return -1;
     if (!ws || ws_bytes < need) return fail("workspace too small: %zu bytes given, %zu needed", ws_bytes, need);
     if (!aligned16(ws)) return fail("device pointers must be 16-byte aligned");
     char* base = static_cast<char*>(ws);
-    const bool exact = (h->flags & B200EXL3_EXACT_WEIGHTS) != 0;
+    const bool exact = (c.flags & B200EXL3_EXACT_WEIGHTS) != 0;
     const size_t x_size = dtype_size(x_dtype);
     const __half* xhat = reinterpret_cast<const __half*>(d_xhat);
     if (!xhat && rows > kQmvFusedRows) {
-        // more than two rows: rotate all of them once, the product kernel reads the rotated rows
-        const QmvPlan first = plan_qmv(h->in, h->out, h->k, rows);
-        __half* buf = reinterpret_cast<__half*>(base + kCounterBytes + qmv_partial_bytes(first, h->out, rows));
-        B200_TRY(launch_prepare(d_x, x_dtype, h->suh, 1, rows, h->in, buf, stream), "prepare");
+        // more than two rows: rotate all of them once per group, the product kernel reads the rotated rows
+        const QmvPlan first = plan_qmv(c.in, c.out, c.k, rows);
+        __half* buf = reinterpret_cast<__half*>(base + kCounterBytes + qmv_partial_bytes(first, c.out, rows));
+        for (int g = 0; g < c.groups; ++g)
+            B200_TRY(launch_prepare(d_x, x_dtype, c.suh + static_cast<size_t>(g) * c.in, 1, rows, c.in,
+                                    buf + static_cast<size_t>(g) * rows * c.in, stream), "prepare");
         xhat = buf;
     }
     for (int64_t r0 = 0; r0 < rows; r0 += kMaxBatchRows) {
         const int64_t n = rows - r0 < kMaxBatchRows ? rows - r0 : kMaxBatchRows;
-        const QmvPlan plan = plan_qmv(h->in, h->out, h->k, n);
+        const QmvPlan plan = plan_qmv(c.in, c.out, c.k, n);
         QmvArgs a{};
-        a.wq = h->wq;
-        a.x = !xhat ? static_cast<const char*>(d_x) + static_cast<size_t>(r0) * h->in * x_size : nullptr;
-        a.suh = h->suh;
-        a.xhat = xhat ? xhat + r0 * h->in : nullptr;
+        a.wq = c.wq;
+        a.x = !xhat ? static_cast<const char*>(d_x) + static_cast<size_t>(r0) * c.in * x_size : nullptr;
+        a.suh = c.suh;
+        a.xhat = xhat ? xhat + r0 * c.in : nullptr;
+        a.xhat_group_stride = rows * c.in;
         a.counters = reinterpret_cast<unsigned int*>(base);
         a.error = reinterpret_cast<unsigned int*>(base + kCounterBytes - sizeof(unsigned int));
         a.partials = reinterpret_cast<float*>(base + kCounterBytes);
-        a.svh = h->svh;
-        a.bias = h->bias;
-        a.y = d_y ? static_cast<char*>(d_y) + static_cast<size_t>(r0) * h->out * x_size : nullptr;
-        a.yhat = d_yhat ? d_yhat + r0 * h->out : nullptr;
+        a.svh = c.svh;
+        a.bias = c.bias;
+        a.yhat = d_yhat ? d_yhat + r0 * c.out : nullptr;
+        a.groups = c.groups;
+        for (int g = 0; g < c.groups; ++g) {
+            a.gcol0[g] = c.gcol0[g];
+            a.gout[g] = c.gout[g];
+            a.gy[g] = ys ? static_cast<char*>(ys[g]) + static_cast<size_t>(r0) * c.gout[g] * x_size : nullptr;
+        }
         a.x_dtype = x_dtype;
         a.y_dtype = x_dtype;
-        a.in = h->in; a.out = h->out; a.rows = static_cast<int>(n);
-        B200_TRY(launch_qmv(a, h->k, h->cb, exact, plan, stream), "fused linear kernel");
+        a.in = c.in; a.out = c.out; a.rows = static_cast<int>(n);
+        B200_TRY(launch_qmv(a, c.k, c.cb, exact, plan, stream), "fused linear kernel");
     }
     return 0;
 }
@@ -356,23 +380,27 @@ int b200exl3_workspace_status(const void* ws, int* out_status) {
 
 int b200exl3_linear_forward(const b200exl3_linear* h, const void* d_x, int x_dtype, int64_t rows, void* d_y, void* ws,
                             size_t ws_bytes, b200exl3_stream s) {
+    if (!h) return fail("NULL handle");
     if (!dtype_is_float(x_dtype)) return fail("unsupported input dtype %d", x_dtype);
     if (!d_x || !d_y) return fail("NULL buffer");
-    return forward_common(h, d_x, x_dtype, nullptr, rows, d_y, nullptr, ws, ws_bytes, as_stream(s));
+    void* ys[1] = {d_y};
+    return forward_common(h->c, d_x, x_dtype, nullptr, rows, ys, nullptr, ws, ws_bytes, as_stream(s));
 }
 
 int b200exl3_linear_forward_raw(const b200exl3_linear* h, const uint16_t* d_xhat, int64_t rows, float* d_yhat, void* ws,
                                 size_t ws_bytes, b200exl3_stream s) {
+    if (!h) return fail("NULL handle");
     if (!d_xhat || !d_yhat) return fail("NULL buffer");
     if (!aligned16(d_xhat)) return fail("device pointers must be 16-byte aligned");
-    return forward_common(h, nullptr, kF16, d_xhat, rows, nullptr, d_yhat, ws, ws_bytes, as_stream(s));
+    return forward_common(h->c, nullptr, kF16, d_xhat, rows, nullptr, d_yhat, ws, ws_bytes, as_stream(s));
 }
 
 int b200exl3_linear_forward_partial(const b200exl3_linear* h, const void* d_x, int x_dtype, int64_t rows, float* d_yhat,
                                     void* ws, size_t ws_bytes, b200exl3_stream s) {
+    if (!h) return fail("NULL handle");
     if (!dtype_is_float(x_dtype)) return fail("unsupported input dtype %d", x_dtype);
     if (!d_x || !d_yhat) return fail("NULL buffer");
-    return forward_common(h, d_x, x_dtype, nullptr, rows, nullptr, d_yhat, ws, ws_bytes, as_stream(s));
+    return forward_common(h->c, d_x, x_dtype, nullptr, rows, nullptr, d_yhat, ws, ws_bytes, as_stream(s));
 }
 
 int b200exl3_linear_finish(const b200exl3_linear* h, const float* d_yhat, int64_t rows, int y_dtype, void* d_y,
@@ -382,15 +410,97 @@ int b200exl3_linear_finish(const b200exl3_linear* h, const float* d_yhat, int64_
     if (!dtype_is_float(y_dtype)) return fail("unsupported output dtype %d", y_dtype);
     if (!d_yhat || !d_y) return fail("NULL buffer");
     if (!aligned16(d_yhat)) return fail("device pointers must be 16-byte aligned");
-    return check(launch_finish(d_yhat, 1, rows * h->out, h->svh, 1, h->bias, rows, h->out, y_dtype, d_y, as_stream(s)),
+    return check(launch_finish(d_yhat, 1, rows * h->c.out, h->c.svh, 1, h->c.bias, rows, h->c.out, y_dtype, d_y, as_stream(s)),
                  "finish");
 }
 
 int b200exl3_linear_decode(const b200exl3_linear* h, uint16_t* d_w, b200exl3_stream s) {
     if (!h) return fail("NULL handle");
     if (!d_w || !aligned16(d_w)) return fail("device pointers must be 16-byte aligned");
-    return check(launch_reconstruct_quads(h->wq, h->in / 16, h->out / 16, h->k, h->cb, reinterpret_cast<__half*>(d_w),
+    return check(launch_reconstruct_quads(h->c.wq, h->c.in / 16, h->c.out / 16, h->c.k, h->c.cb, reinterpret_cast<__half*>(d_w),
                                           as_stream(s)), "reconstruct");
+}
+
+/* ---- Exl3Group --------------------------------------------------------------------------------- */
+
+int b200exl3_group_create(const b200exl3_linear* const* members, int count, b200exl3_group** out_handle) {
+    if (!out_handle) return fail("out pointer is NULL");
+    *out_handle = nullptr;
+    if (!members || count < 2 || count > kQmvMaxGroups) return fail("incompatible grouped projections");
+    for (int g = 0; g < count; ++g) {
+        if (!members[g]) return fail("incompatible grouped projections");
+        const LayerCore& m = members[g]->c;
+        const LayerCore& f = members[0]->c;
+        if (m.groups != 1 || m.in != f.in || m.k != f.k || m.cb != f.cb || (m.flags != f.flags))
+            return fail("incompatible grouped projections");
+    }
+    b200exl3_group* handle = new (std::nothrow) b200exl3_group{};
+    if (!handle) return fail("out of host memory");
+    LayerCore* c = &handle->c;
+    const LayerCore& f = members[0]->c;
+    c->in = f.in; c->k = f.k; c->cb = f.cb; c->flags = f.flags; c->groups = count;
+    int64_t total = 0;
+    bool any_bias = false;
+    for (int g = 0; g < count; ++g) {
+        c->gcol0[g] = static_cast<int>(total);
+        c->gout[g] = members[g]->c.out;
+        total += members[g]->c.out;
+        any_bias = any_bias || members[g]->c.bias != nullptr;
+    }
+    int rc = 0;
+    if (total / 128 >= static_cast<int64_t>(kCounterBytes / sizeof(unsigned int))) rc = fail("group width overflow");
+    c->out = static_cast<int>(total);
+    const size_t row_bytes = static_cast<size_t>(c->out / 16) * 32 * c->k;       // one input-tile row of the quad layout
+    if (!rc) rc = check(cudaMalloc(&c->wq, row_bytes * (c->in / 16)), "cudaMalloc(weights)");
+    if (!rc) rc = check(cudaMalloc(&c->suh, static_cast<size_t>(count) * c->in * sizeof(__half)), "cudaMalloc(scales)");
+    if (!rc) rc = check(cudaMalloc(&c->svh, static_cast<size_t>(c->out) * sizeof(__half)), "cudaMalloc(scales)");
+    if (!rc && any_bias) {
+        rc = check(cudaMalloc(&c->bias, static_cast<size_t>(c->out) * sizeof(__half)), "cudaMalloc(bias)");
+        if (!rc) rc = check(cudaMemset(c->bias, 0, static_cast<size_t>(c->out) * sizeof(__half)), "clear bias");
+    }
+    for (int g = 0; g < count && !rc; ++g) {
+        const LayerCore& m = members[g]->c;
+        const size_t member_row = static_cast<size_t>(m.out / 16) * 32 * m.k;
+        // concatenate along the output axis: every input-tile row of the member goes behind the previous members' rows
+        rc = check(cudaMemcpy2D(reinterpret_cast<char*>(c->wq) + static_cast<size_t>(c->gcol0[g] / 16) * 32 * c->k, row_bytes,
+                                m.wq, member_row, member_row, c->in / 16, cudaMemcpyDeviceToDevice), "concatenate weights");
+        if (!rc) rc = check(cudaMemcpy(c->suh + static_cast<size_t>(g) * c->in, m.suh, static_cast<size_t>(c->in) * sizeof(__half),
+                                       cudaMemcpyDeviceToDevice), "copy scales");
+        if (!rc) rc = check(cudaMemcpy(c->svh + c->gcol0[g], m.svh, static_cast<size_t>(m.out) * sizeof(__half),
+                                       cudaMemcpyDeviceToDevice), "copy scales");
+        if (!rc && m.bias) rc = check(cudaMemcpy(c->bias + c->gcol0[g], m.bias, static_cast<size_t>(m.out) * sizeof(__half),
+                                                 cudaMemcpyDeviceToDevice), "copy bias");
+    }
+    if (!rc) rc = check(cudaDeviceSynchronize(), "group_create");
+    if (rc) {
+        b200exl3_group_free(handle);
+        return -1;
+    }
+    *out_handle = handle;
+    return 0;
+}
+
+void b200exl3_group_free(b200exl3_group* h) {
+    if (!h) return;
+    core_free(h->c);
+    delete h;
+}
+
+int b200exl3_group_count(const b200exl3_group* h) { return h ? h->c.groups : fail("NULL handle"); }
+
+int b200exl3_group_workspace_bytes(const b200exl3_group* h, int64_t rows, size_t* out_bytes) {
+    if (!h) return fail("NULL argument");
+    return core_workspace_bytes(h->c, rows, out_bytes);
+}
+
+int b200exl3_group_forward(const b200exl3_group* h, const void* d_x, int x_dtype, int64_t rows, void* const* d_ys, void* ws,
+                           size_t ws_bytes, b200exl3_stream s) {
+    if (!h) return fail("NULL handle");
+    if (!dtype_is_float(x_dtype)) return fail("unsupported input dtype %d", x_dtype);
+    if (!d_x || !d_ys) return fail("NULL buffer");
+    for (int g = 0; g < h->c.groups; ++g)
+        if (!d_ys[g]) return fail("NULL buffer");
+    return forward_common(h->c, d_x, x_dtype, nullptr, rows, d_ys, nullptr, ws, ws_bytes, as_stream(s));
 }
 
 }  // extern "C"

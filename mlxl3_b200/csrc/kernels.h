@@ -26,6 +26,7 @@ cudaError_t launch_finish(const float* partials, int splits, int64_t split_strid
 // ---- fused linear layer (kernels_qmv*.cu) ----------------------------------------------------------
 constexpr int kQmvWarps = 8;         // warps per CTA
 constexpr int kQmvRedStride = 132;   // floats per reduced row: 128 + 4 keeps the fragment stores conflict-free
+constexpr int kQmvMaxGroups = 8;     // projections fused in one launch (q/k/v, gate/up)
 constexpr int kQmvMaxRows = 16;      // activation rows one launch can take
 constexpr int kQmvMaxSmemBytes = 200 * 1024;
 constexpr int kQmvXBlocks = 6;       // 128-blocks of rotated activations a warp keeps per row
@@ -37,16 +38,20 @@ __host__ __device__ constexpr int qmv_depth(int k) { return k <= 2 ? 8 : 4; }
 struct QmvArgs {
     const uint32_t* wq;        // quad layout [tiles_k, tiles_n/4, 8K, 4] words
     const void* x;             // [rows, in] activations in x_dtype (used when xhat == nullptr)
-    const __half* suh;         // [in]
-    const __half* xhat;        // [rows, in] already rotated activations, or nullptr
+    const __half* suh;         // [groups, in]
+    const __half* xhat;        // [groups, rows, in] already rotated activations, or nullptr
     float* partials;           // [out/128, max_pieces, rows, 128] scratch for column blocks shared by several CTAs
     unsigned int* counters;    // [out/128] arrival counters, zero on entry and on exit
     unsigned int* error;       // set to 1 if a weight copy never arrived (bounded wait gave up)
     unsigned long long* trace; // optional [grid, 8] nanosecond stamps of the phases of each CTA, or nullptr
     const __half* svh;         // [out]   (output rotation; used when y != nullptr)
     const __half* bias;        // [out] or nullptr
-    void* y;                   // [rows, out] in y_dtype, or nullptr for raw output
-    float* yhat;               // [rows, out] summed fp32 product, written when y == nullptr
+    float* yhat;               // [rows, out] summed fp32 product (raw output) when not nullptr; else:
+    void* gy[kQmvMaxGroups];   // per group: [rows, gout[g]] rotated output in y_dtype
+    int gcol0[kQmvMaxGroups];  // per group: first column in the concatenated output space
+    int gout[kQmvMaxGroups];   // per group: output width
+    int groups;                // 1 for a plain layer
+    int64_t xhat_group_stride; // halves between the rotated activations of consecutive groups
     int x_dtype, y_dtype;
     int in, out, rows, tiles_k, tiles_n, max_pieces;
     int warp_smem;             // bytes of shared memory per warp

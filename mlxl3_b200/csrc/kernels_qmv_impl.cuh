@@ -171,6 +171,14 @@ __device__ __forceinline__ void qmv_row(const uint32_t* __restrict__ row_words, 
     }
 }
 
+// group (fused projection) that owns 128-column block `cblock`
+__device__ __forceinline__ int qmv_group_of(const QmvArgs& p, int cblock) {
+    int grp = 0;
+#pragma unroll 1
+    while (grp + 1 < p.groups && cblock * 128 >= p.gcol0[grp + 1]) ++grp;
+    return grp;
+}
+
 // ---- the rarely executed parts of the kernel: written small (no unrolling) so that they cost the
 //      decode loop neither registers nor instruction-cache space -----------------------------------------
 
@@ -266,18 +274,20 @@ __device__ __forceinline__ void qmv_finish_block(const QmvArgs& p, int cblock, u
                 __stcg(reinterpret_cast<float4*>(piece_dst + row * 128 + lane * 4), a);
                 continue;
             }
-            const int col = cblock * 128 + lane * 4;
-            if (p.y == nullptr) {
+            const int col = cblock * 128 + lane * 4;              // column in the concatenated output space
+            if (p.yhat != nullptr) {
                 *reinterpret_cast<float4*>(p.yhat + static_cast<int64_t>(row) * p.out + col) = a;
             } else {
                 __half h[4] = {__float2half_rn(a.x), __float2half_rn(a.y), __float2half_rn(a.z), __float2half_rn(a.w)};
                 warp_hadamard128_f16(h, lane);
                 __align__(8) __half sv[4];
                 *reinterpret_cast<uint2*>(sv) = *reinterpret_cast<const uint2*>(p.svh + col);
+                const int grp = qmv_group_of(p, cblock);
+                const int gcol = col - p.gcol0[grp];
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
-                    store_from_half(p.y, p.y_dtype, static_cast<int64_t>(row) * p.out + col + j, __hmul_rn(h[j], sv[j]), p.bias,
-                                    col + j);
+                    store_from_half(p.gy[grp], p.y_dtype, static_cast<int64_t>(row) * p.gout[grp] + gcol + j,
+                                    __hmul_rn(h[j], sv[j]), p.bias ? p.bias + (col - gcol) : nullptr, gcol + j);
             }
         }
     }
@@ -350,6 +360,7 @@ qmv_kernel(const QmvArgs p) {
         const int u0 = max(w0, cblock * UB) - cblock * UB;
         const int u1 = min(w1, (cblock + 1) * UB) - cblock * UB;
         float* stage = reinterpret_cast<float*>(mine + p.stage_offset) + (cblock - w0 / UB) * stage_floats;
+        const int grp = qmv_group_of(p, cblock);
         {
             const int tk_first = u0 >> 3, tk_last = (u1 - 1) >> 3;
             const int lo_first = u0 & 7, hi_last = ((u1 - 1) & 7) + 1;
@@ -394,7 +405,8 @@ qmv_kernel(const QmvArgs p) {
 
                 // ---- phase 1: rotate this chunk's activations into the warp's shared memory ------------
                 if (p.xhat == nullptr)
-                    qmv_rotate_chunk(p.x, p.x_dtype, p.suh, p.in, rows, kb0, ((tk_end - 1) >> 3) - kb0 + 1, xs, lane);
+                    qmv_rotate_chunk(p.x, p.x_dtype, p.suh + static_cast<int64_t>(grp) * p.in, p.in, rows, kb0,
+                                     ((tk_end - 1) >> 3) - kb0 + 1, xs, lane);
                 if (tracing && tk0 == tk_first) p.trace[blockIdx.x * 8 + 2] = global_ns();
 
                 // ---- phase 2: decode x activations ----------------------------------------------------------
@@ -406,7 +418,7 @@ qmv_kernel(const QmvArgs p) {
                     if (p.xhat == nullptr)
                         xfrag[nb] = reinterpret_cast<const uint32_t*>(xs + row * kXsHalves + (tk0 * 16 - kb0 * 128)) + q;
                     else
-                        xfrag[nb] = reinterpret_cast<const uint32_t*>(p.xhat + static_cast<int64_t>(row) * p.in + tk0 * 16) + q;
+                        xfrag[nb] = reinterpret_cast<const uint32_t*>(p.xhat + grp * p.xhat_group_stride + static_cast<int64_t>(row) * p.in + tk0 * 16) + q;
                 }
                 for (int r = 0; r < nrows; ++r) {
                     const int tk = tk0 + r;

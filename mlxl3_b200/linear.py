@@ -174,3 +174,64 @@ class Exl3Linear:
             self.close()
         except Exception:
             pass
+
+
+class Exl3Group:
+    """Projections that read the same input, fused into one launch -- the mirror of the reference's
+    ``Exl3Group`` (native/src/linear.rs:2285-2814): ``Exl3Group(linears)`` needs at least two members
+    with the same input width, K and codebook; ``forward(x)`` returns one array per member."""
+
+    @staticmethod
+    def compatible(linears) -> bool:
+        first = linears[0] if linears else None
+        return (first is not None and len(linears) >= 2
+                and all(l.rows == first.rows and l.k == first.k and l.cb == first.cb for l in linears))
+
+    def __init__(self, linears):
+        linears = list(linears)
+        if not self.compatible(linears):
+            raise B200Exl3Error("incompatible grouped projections")
+        self.rows, self.k, self.cb = linears[0].rows, linears[0].k, linears[0].cb
+        self.widths = [l.cols for l in linears]
+        handles = (c_void_p * len(linears))(*[l.handle for l in linears])
+        out = c_void_p()
+        _lib.call("b200exl3_group_create", handles, len(linears), byref(out))
+        self.handle = out.value
+        self._workspace: DeviceBuffer | None = None
+
+    def workspace_bytes(self, rows: int) -> int:
+        out = c_size_t()
+        _lib.call("b200exl3_group_workspace_bytes", c_void_p(self.handle), rows, byref(out))
+        return out.value
+
+    def forward_device(self, d_x: int, dtype: int, rows: int, d_ys, workspace: DeviceBuffer,
+                       stream: Stream = DEFAULT_STREAM) -> None:
+        ptrs = (c_void_p * len(self.widths))(*d_ys)
+        _lib.call("b200exl3_group_forward", c_void_p(self.handle), c_void_p(d_x), dtype, rows, ptrs, c_void_p(workspace.ptr),
+                  workspace.nbytes, c_void_p(stream.handle))
+
+    def forward(self, x: np.ndarray, dtype: int | None = None, stream: Stream = DEFAULT_STREAM):
+        x = np.asarray(x)
+        if x.ndim == 0 or x.shape[-1] != self.rows or x.size == 0:
+            raise B200Exl3Error("invalid grouped EXL3 input")
+        matrix_rows = x.size // self.rows
+        code = dtype_code(x, dtype)
+        x2 = np.ascontiguousarray(x).reshape(matrix_rows, self.rows)
+        d_x = DeviceBuffer.from_numpy(x2, stream)
+        d_ys = [DeviceBuffer(matrix_rows * w * x2.dtype.itemsize) for w in self.widths]
+        need = self.workspace_bytes(matrix_rows)
+        if self._workspace is None or self._workspace.nbytes < need:
+            self._workspace = new_workspace(need)
+        self.forward_device(d_x.ptr, code, matrix_rows, [d.ptr for d in d_ys], self._workspace, stream)
+        return [d.download((matrix_rows, w), x2.dtype, stream).reshape(*x.shape[:-1], w) for d, w in zip(d_ys, self.widths)]
+
+    def close(self) -> None:
+        if getattr(self, "handle", None):
+            _lib.load().b200exl3_group_free(c_void_p(self.handle))
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
