@@ -140,6 +140,21 @@ int b200exl3_workspace_status(const void* d_workspace, int* out_status);
  * the same dtype.  rows >= 1.  The workspace must hold b200exl3_linear_workspace_bytes(rows). */
 int b200exl3_linear_forward(const b200exl3_linear* handle, const void* d_x, int x_dtype, int64_t rows, void* d_y,
                             void* d_workspace, size_t workspace_bytes, b200exl3_stream stream);
+/* Allocation-free variant of b200exl3_linear_forward.  It has no counterpart in the reference.
+ * Meant for hosts that cannot give the library a workspace -- code running inside another runtime's
+ * memory pool, latency-critical loops that must stay away from the allocator, bindings that only
+ * ever see input and output pointers: the scratch memory is a fixed 4 MiB array inside the library's
+ * device image (held by every GPU that loads the library, until the process exits), and the call
+ * itself allocates and frees nothing.  x and y are as in b200exl3_linear_forward.
+ *   - A call whose scratch need (b200exl3_linear_workspace_bytes) exceeds 4 MiB is rejected with an
+ *     error; decode-sized calls (a few rows) of any layer of the supported models fit.
+ *   - The first call on each device looks up the array's device address; make that first call
+ *     outside any stream capture.
+ *   - All calls share the one array: every call clears the counters at its head on `stream` first,
+ *     so calls must not overlap on the GPU (same stream, or otherwise ordered) -- two calls running
+ *     at the same time would race on the scratch. */
+int b200exl3_linear_forward_static(const b200exl3_linear* handle, const void* d_x, int x_dtype, int64_t rows, void* d_y,
+                                   b200exl3_stream stream);
 /* The middle of forward alone: fp32 yhat [rows, out] = xhat [rows, in] (fp16, already rotated) times
  * the inner matrix -- what the reference's QMV/QMM kernels return before the output rotation. */
 int b200exl3_linear_forward_raw(const b200exl3_linear* handle, const uint16_t* d_xhat_f16, int64_t rows, float* d_yhat,

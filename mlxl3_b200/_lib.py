@@ -56,6 +56,7 @@ SIGNATURES = {
     "b200exl3_linear_workspace_bytes": (c_int, [c_void_p, c_int64, POINTER(c_size_t)]),
     "b200exl3_workspace_status": (c_int, [c_void_p, POINTER(c_int)]),
     "b200exl3_linear_forward": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "b200exl3_linear_forward_static": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p]),
     "b200exl3_linear_forward_raw": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_size_t, c_void_p]),
     "b200exl3_linear_forward_partial": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_size_t,
                                                 c_void_p]),

@@ -6,6 +6,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 #include <new>
 #include <string>
 
@@ -419,6 +420,58 @@ int b200exl3_linear_decode(const b200exl3_linear* h, uint16_t* d_w, b200exl3_str
     if (!d_w || !aligned16(d_w)) return fail("device pointers must be 16-byte aligned");
     return check(launch_reconstruct_quads(h->c.wq, h->c.in / 16, h->c.out / 16, h->c.k, h->c.cb, reinterpret_cast<__half*>(d_w),
                                           as_stream(s)), "reconstruct");
+}
+
+/* ---- allocation-free forward ------------------------------------------------------------------- */
+
+// Scratch for b200exl3_linear_forward_static.  Some hosts cannot hand the library a workspace: a
+// plugin that runs inside somebody else's memory pool, a real-time loop that must not touch the
+// allocator, a caller that only ever receives input and output pointers.  For them the scratch lives
+// in the library's own device image: every GPU that loads the library holds these bytes until the
+// process exits.  The name below is the host-side handle of the array, not a device address; the
+// address a kernel can use comes from cudaGetSymbolAddress, asked once per device.
+constexpr size_t kStaticScratchBytes = size_t(4) << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mutex;
+void* g_static_ptr[kMaxDevices] = {};
+
+// Device address of the scratch array on the current device (looked up on first use).
+int static_scratch(void** out) {
+    int device = 0;
+    B200_TRY(cudaGetDevice(&device), "cudaGetDevice");
+    if (device < 0 || device >= kMaxDevices) return fail("device %d is beyond the %d devices supported", device, kMaxDevices);
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (!g_static_ptr[device]) {
+        void* ptr = nullptr;
+        B200_TRY(cudaGetSymbolAddress(&ptr, g_static_scratch), "cudaGetSymbolAddress(static scratch)");
+        if (!ptr) return fail("the static scratch array has no device address");
+        g_static_ptr[device] = ptr;
+    }
+    *out = g_static_ptr[device];
+    return 0;
+}
+}  // namespace
+
+int b200exl3_linear_forward_static(const b200exl3_linear* h, const void* d_x, int x_dtype, int64_t rows, void* d_y,
+                                   b200exl3_stream s) {
+    if (!h) return fail("NULL handle");
+    if (!dtype_is_float(x_dtype)) return fail("unsupported input dtype %d", x_dtype);
+    if (!d_x || !d_y) return fail("NULL buffer");
+    size_t need = 0;
+    if (core_workspace_bytes(h->c, rows, &need)) return -1;
+    if (need > kStaticScratchBytes)
+        return fail("this call needs %zu bytes of scratch but the allocation-free entry point owns %zu; "
+                    "use b200exl3_linear_forward with a caller workspace", need, kStaticScratchBytes);
+    void* scratch = nullptr;
+    if (static_scratch(&scratch)) return -1;
+    // The array keeps whatever the previous call left; the arrival counters (and the status word) at
+    // its head must start at zero, the partial sums behind them are overwritten before they are read.
+    B200_TRY(cudaMemsetAsync(scratch, 0, kCounterBytes, as_stream(s)), "clear static scratch");
+    void* ys[1] = {d_y};
+    return forward_common(h->c, d_x, x_dtype, nullptr, rows, ys, nullptr, scratch, kStaticScratchBytes, as_stream(s));
 }
 
 /* ---- Exl3Group --------------------------------------------------------------------------------- */

@@ -117,6 +117,13 @@ class Exl3Linear:
         _lib.call("b200exl3_linear_forward", c_void_p(self.handle), c_void_p(d_x), dtype, rows, c_void_p(d_y),
                   c_void_p(workspace.ptr), workspace.nbytes, c_void_p(stream.handle))
 
+    def forward_static_device(self, d_x: int, dtype: int, rows: int, d_y: int, stream: Stream = DEFAULT_STREAM) -> None:
+        """``forward_device`` without a workspace: the scratch is a fixed 4 MiB array inside the library,
+        for callers that cannot allocate device memory.  Calls must not overlap on the GPU, larger
+        scratch needs are refused, and the first call per device must happen outside a graph recording."""
+        _lib.call("b200exl3_linear_forward_static", c_void_p(self.handle), c_void_p(d_x), dtype, rows, c_void_p(d_y),
+                  c_void_p(stream.handle))
+
     def forward_partial_device(self, d_x: int, dtype: int, rows: int, d_yhat: int, workspace: DeviceBuffer,
                                stream: Stream = DEFAULT_STREAM) -> None:
         """Input rotation and product only: fp32 ``yhat[rows, out]`` of this (row-parallel) shard."""
