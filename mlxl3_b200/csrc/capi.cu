@@ -5,6 +5,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <algorithm>
 #include <cstring>
 #include <mutex>
 #include <new>
@@ -54,6 +55,7 @@ int valid_format(int k, int cb) {
     return 0;
 }
 
+bool g_qmm_enabled = true;                               // "qmm" option: 0 sends every batch through the fused kernel
 constexpr int kMaxBatchRows = kQmvMaxRows;              // rows handled by one launch of the fused kernel
 constexpr size_t kCounterBytes = B200EXL3_WORKSPACE_HEADER_BYTES;   // arrival counters at the head of a workspace
 
@@ -105,6 +107,8 @@ int b200exl3_set_option(const char* name, int64_t value) {
     if (!strcmp(name, "qmv_ctas_per_sm")) ctas = static_cast<int>(value);
     else if (!strcmp(name, "qmv_force_grid")) grid = static_cast<int>(value);
     else if (!strcmp(name, "pdl")) pdl = static_cast<int>(value);
+    else if (!strcmp(name, "qmm")) { g_qmm_enabled = value != 0; return 0; }
+    else if (!strcmp(name, "qmm_waves")) { qmm_set_tuning(static_cast<int>(value)); return 0; }
     else if (!strcmp(name, "qmv_trace_buffer")) {
         qmv_set_trace(reinterpret_cast<unsigned long long*>(static_cast<uintptr_t>(value)));
         return 0;
@@ -306,11 +310,21 @@ static size_t xhat_bytes(const LayerCore& c, int64_t rows) {
     return rows > kQmvFusedRows ? round256(static_cast<size_t>(c.groups) * rows * c.in * sizeof(__half)) : 0;
 }
 
+// From this many rows on, a plain layer's forward runs the tensor-core product (rotate all rows,
+// tcgen05 product into fp32 partials, output rotation) instead of batches through the fused kernel.
+constexpr int64_t kQmmMinRows = kQmvMaxRows + 1;
+
 static int core_workspace_bytes(const LayerCore& c, int64_t rows, size_t* out_bytes) {
     if (!out_bytes) return fail("NULL argument");
     if (rows <= 0) return fail("EXL3 linear input cannot be empty");
     QmvPlan plan = plan_qmv(c.in, c.out, c.k, rows);
-    *out_bytes = kCounterBytes + qmv_partial_bytes(plan, c.out, rows) + xhat_bytes(c, rows);
+    size_t bytes = kCounterBytes + qmv_partial_bytes(plan, c.out, rows) + xhat_bytes(c, rows);
+    if (rows >= kQmmMinRows && c.groups == 1) {
+        const QmmPlan qp = plan_qmm(c.in, c.out, rows);
+        bytes = std::max(bytes, kCounterBytes + round256(static_cast<size_t>(rows) * c.in * sizeof(__half)) +
+                                    qmm_partial_bytes(qp, c.out, rows));
+    }
+    *out_bytes = bytes;
     return 0;
 }
 
@@ -332,6 +346,18 @@ static int forward_common(const LayerCore& c, const void* d_x, int x_dtype, cons
     const bool exact = (c.flags & B200EXL3_EXACT_WEIGHTS) != 0;
     const size_t x_size = dtype_size(x_dtype);
     const __half* xhat = reinterpret_cast<const __half*>(d_xhat);
+    if (rows >= kQmmMinRows && c.groups == 1 && ys && !d_xhat && g_qmm_enabled) {
+        // many rows: input rotation -> tensor-core product (fp32 partials per input split) -> output rotation
+        __half* buf = reinterpret_cast<__half*>(base + kCounterBytes);
+        float* partials = reinterpret_cast<float*>(base + kCounterBytes + round256(static_cast<size_t>(rows) * c.in * sizeof(__half)));
+        const QmmPlan qp = plan_qmm(c.in, c.out, rows);
+        B200_TRY(launch_prepare(d_x, x_dtype, c.suh, 1, rows, c.in, buf, stream), "prepare");
+        B200_TRY(launch_qmm(c.wq, c.in, c.out, c.k, c.cb, buf, rows, qp, partials,
+                            reinterpret_cast<unsigned int*>(base + kCounterBytes - sizeof(unsigned int)), stream),
+                 "tensor-core product kernel");
+        B200_TRY(launch_finish(partials, qp.splits, rows * c.out, c.svh, 1, c.bias, rows, c.out, x_dtype, ys[0], stream), "finish");
+        return 0;
+    }
     if (!xhat && rows > kQmvFusedRows) {
         // more than two rows: rotate all of them once per group, the product kernel reads the rotated rows
         const QmvPlan first = plan_qmv(c.in, c.out, c.k, rows);
