@@ -56,7 +56,12 @@ int b200exl3_version(void);
  * weight prefetch of a layer overlaps the tail of the previous kernel in the stream; 1 releases the
  * next kernel after the main loop, 2 as soon as the first copies are in flight), "qmv_trace_buffer"
  * (device address of a uint64 [grid, 8] array that receives nanosecond stamps of each CTA's phases:
- * start, activations visible, rotated, main loop done, warps joined, reduced, finished; 0 = off). */
+ * start, activations visible, rotated, main loop done, warps joined, reduced, finished; 0 = off), "qmm" (0 = batches
+ * of more than 16 rows also go through the small-batch kernel instead of the tensor-core product; default 1),
+ * "qmm_splits" (input splits of the tensor-core product, 0 = chosen by a cost model; set it before asking for
+ * workspace sizes), "qmm_trace_buffer" (device address of a uint64 [CTAs, 8] array that receives nanosecond
+ * stamps of the tensor-core kernel's phases: start, set up, decoders done, MMAs issued, accumulator ready,
+ * epilogue done, end, activation copies issued; 0 = off). */
 int b200exl3_set_option(const char* name, int64_t value);
 
 /* Plain device-memory plumbing for hosts that have no CUDA binding of their own (replaces

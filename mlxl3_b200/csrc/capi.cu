@@ -13,6 +13,7 @@
 
 #include "common.cuh"
 #include "kernels.h"
+namespace b200exl3 { extern unsigned long long* g_qmm_trace; }
 
 using namespace b200exl3;
 
@@ -108,7 +109,8 @@ int b200exl3_set_option(const char* name, int64_t value) {
     else if (!strcmp(name, "qmv_force_grid")) grid = static_cast<int>(value);
     else if (!strcmp(name, "pdl")) pdl = static_cast<int>(value);
     else if (!strcmp(name, "qmm")) { g_qmm_enabled = value != 0; return 0; }
-    else if (!strcmp(name, "qmm_waves")) { qmm_set_tuning(static_cast<int>(value)); return 0; }
+    else if (!strcmp(name, "qmm_trace_buffer")) { b200exl3::g_qmm_trace = reinterpret_cast<unsigned long long*>(value); return 0; }
+    else if (!strcmp(name, "qmm_splits")) { qmm_set_tuning(static_cast<int>(value)); return 0; }
     else if (!strcmp(name, "qmv_trace_buffer")) {
         qmv_set_trace(reinterpret_cast<unsigned long long*>(static_cast<uintptr_t>(value)));
         return 0;

@@ -85,14 +85,14 @@ void qmv_set_trace(unsigned long long* device_buffer);
 // ---- tensor-core product for many rows (kernels_qmm.cu) ---------------------------------------------------
 struct QmmPlan {
     int splits;        // CTAs that share one (128 columns x 256 tokens) output tile along the input axis
-    int token_tiles;   // ceil(rows / 256)
+    int token_tiles;   // ceil(rows / 512)
 };
 QmmPlan plan_qmm(int in, int out, int64_t rows);
 size_t qmm_partial_bytes(const QmmPlan& plan, int out, int64_t rows);
 // partials[s, r, n] (fp32) = sum over the inputs of split s of xhat[r, :] (fp16, rotated) x W[:, n]
 cudaError_t launch_qmm(const uint32_t* wq, int in, int out, int k, int cb, const __half* xhat, int64_t rows,
                        const QmmPlan& plan, float* partials, unsigned int* error, cudaStream_t stream);
-void qmm_set_tuning(int waves);
+void qmm_set_tuning(int splits);   // force the number of input splits (0 = automatic)
 
 // ---- weight layout (kernels_codec.cu) -----------------------------------------------------------------
 // checkpoint layout [tiles_k, tiles_n, 8K] words -> quad layout [tiles_k, tiles_n/4, 8K, 4]

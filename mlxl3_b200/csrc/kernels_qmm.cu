@@ -8,20 +8,22 @@
 // in native/src/linear.rs:1940-1963).
 //
 // Mapping.  The product is computed transposed, D[out, token] = W^T[out, in] . Xhat^T[in, token]:
-//  * one CTA owns 128 output columns (the 128 lanes of tensor memory), up to 256 tokens (256 fp32
-//    columns of tensor memory) and a contiguous range of 64-input stages (split-K across CTAs);
-//  * A operand = decoded weights, [128 out, 64 in] fp16, K-major with the 128-byte swizzle.  Four
-//    decoder warps each own one 16-input tile row of the stage: a warp streams its packed row with
-//    TMA bulk copies into its own ring, decodes the eight tiles bit-exactly in registers (the lane's
-//    eight weights are two 4-byte pairs for rows g and g+8 of the A tile) and stores them with the
-//    swizzle applied (conflict-free);
-//  * B operand = rotated activations, [256 token, 64 in] fp16, K-major, loaded by one TMA tensor copy
-//    per stage with the 128-byte swizzle (rows past the batch are zero-filled by the copy);
-//  * one thread issues four tcgen05.mma (M=128, N=256, K=16) per stage and commits the stage back to
-//    the producers; after the last stage the decoder warps read the accumulator with tcgen05.ld and
-//    store the partial products.
-// Every wait on an mbarrier is bounded; a wait that gives up sets the status word and the kernel still
-// releases its tensor memory.
+//  * one CTA owns 128 output columns (the 128 lanes of tensor memory), up to 512 tokens (all 512 fp32
+//    columns of tensor memory, as two halves of 256) and a contiguous range of 64-input stages
+//    (split-K across CTAs), so a batch of up to 512 rows decodes every weight exactly once;
+//  * A operand = decoded weights, [128 out, 64 in] fp16, K-major with the 128-byte swizzle.  Eight
+//    decoder warps each own four tiles (one interleaved quad) of one 16-input tile row of the stage:
+//    a warp streams its packed quads with TMA bulk copies into its own ring, decodes the tiles
+//    bit-exactly in registers (the lane's eight weights are two 4-byte pairs for rows g and g+8 of the
+//    A tile) and stores them with the swizzle applied;
+//  * B operand = rotated activations, [256 token, 64 in] fp16 per half, K-major, loaded by one TMA
+//    tensor copy per half and stage with the 128-byte swizzle (rows past the batch are zero-filled);
+//    the B ring is decoupled from the A ring;
+//  * one thread issues four tcgen05.mma (M=128, N=256, K=16) per half and stage, commits each B slot
+//    and each A stage back to its producers; after the last stage the decoder warps read the
+//    accumulator with tcgen05.ld and store the partial products.
+// Every wait on an mbarrier is bounded in time; a wait that gives up sets the status word and the
+// kernel still releases its tensor memory.
 #include <cuda.h>
 
 #include <algorithm>
@@ -33,19 +35,30 @@ namespace b200exl3 {
 
 namespace {
 
-constexpr int kStages = 4;            // A/B stages in flight
-constexpr int kRawDepth = 3;          // packed rows in flight per decoder warp
-constexpr int kTokTile = 256;         // tokens per CTA = MMA N
-constexpr int kDecoders = 4;          // decoder warps (= 16-input tile rows per stage)
-constexpr int kThreads = 32 * (kDecoders + 2);
+constexpr int kStages = 3;            // decoded A stages in flight
+constexpr int kBSlots = 5;            // activation half-stages in flight
+// packed stages (4 tile rows x 8 tiles = 1024*K bytes) in flight: a 16 KiB ring, at most 8 slots
+constexpr int raw_depth(int k) { return 16 / k > 8 ? 8 : 16 / k; }
+constexpr int kRawDepthMax = 8;
+constexpr uint32_t kRawBytes = 16 * 1024;
+constexpr int kTokHalf = 256;         // tokens per accumulator half = MMA N
+constexpr int kTokTile = 2 * kTokHalf;   // tokens per CTA
+constexpr int kDecoderGroups = 2;     // groups of eight decoder warps that take alternate stages
+constexpr int kGroupWarps = 8;        // (tile row of the stage, quad of the 8-tile row)
+constexpr int kDecoders = kDecoderGroups * kGroupWarps;
+// Warp roles.  The single-thread roles take the lowest warp numbers: the scheduler favours older warps, and a
+// producer starved by spinning decoder warps stalls the whole pipeline.
+constexpr int kMmaWarp = 0, kActWarp = 1, kWeightWarp = 2, kFirstDecoder = 4;
+constexpr int kThreads = 32 * (kFirstDecoder + kDecoders);
 constexpr uint32_t kAStageBytes = 128 * 128;           // 128 rows x 64 fp16
-constexpr uint32_t kBStageBytes = kTokTile * 128;      // 256 rows x 64 fp16
+constexpr uint32_t kBSlotBytes = kTokHalf * 128;       // 256 rows x 64 fp16
 
 struct QmmArgs {
     const uint32_t* wq;        // quad layout
     float* partials;           // [splits, rows, out]
     unsigned int* error;
     int in, out, rows, tiles_n, splits, stages_total;   // stages_total = in / 64
+    unsigned long long* trace;   // optional [CTA, 8] nanosecond stamps of the phases
 };
 
 __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_byte_addr) {
@@ -62,7 +75,7 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_byte_addr) {
 constexpr uint32_t kInstrDesc = (1u << 4)                      // D = fp32
                                 | (0u << 7) | (0u << 10)       // A, B = fp16
                                 | (0u << 15) | (0u << 16)      // both K-major
-                                | ((kTokTile >> 3) << 17)      // N
+                                | ((kTokHalf >> 3) << 17)      // N
                                 | ((128u >> 4) << 24);         // M
 
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t cols) {
@@ -102,158 +115,226 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 
 // Wait that gives up after about a quarter of a second, or at once when another role of the CTA has
 // already given up, so that a lost copy or a miscounted barrier ends the kernel instead of hanging it.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok) : "r"(smem_addr(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ bool qmm_wait(uint64_t* bar, uint32_t parity, volatile int* cta_failed) {
-    if (mbar_try_wait(bar, parity)) return true;
+    // non-blocking tests: a suspended try_wait was seen to resume long after the phase completed.
+    // Reading the global timer costs about 0.2 us, so the clock only starts after many plain polls.
+    for (int i = 0; i < 4096; ++i)
+        if (mbar_test_wait(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
     for (int i = 1;; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 63) == 0 && (*cta_failed || global_ns() - t0 > 250000000ull)) { *cta_failed = 1; return false; }
+        if (mbar_test_wait(bar, parity)) return true;
+        if ((i & 255) == 0 && (*cta_failed || global_ns() - t0 > 250000000ull)) { *cta_failed = 1; return false; }
     }
+}
+// The same wait for a whole warp: one lane polls (32 lanes polling one barrier flood the shared-memory
+// pipe that the copies, the stores and the MMA issue also need), then every lane observes the completed
+// phase itself, which makes the data the barrier guards visible to it.
+__device__ __forceinline__ bool qmm_wait_warp(uint64_t* bar, uint32_t parity, volatile int* cta_failed, int lane) {
+    int ok = 1;
+    if (lane == 0) ok = qmm_wait(bar, parity, cta_failed);
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    if (!ok) return false;
+    return mbar_test_wait(bar, parity) || qmm_wait(bar, parity, cta_failed);
 }
 
 template <int K, int CB>
 __global__ void __launch_bounds__(kThreads, 1)
-qmm_kernel(const __grid_constant__ CUtensorMap xmap, const QmmArgs p) {
+qmm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, const QmmArgs p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    constexpr int kRowWords = 64 * K;                        // one 8-tile row of packed words
-    constexpr uint32_t kRowBytes = kRowWords * 4;
-    __shared__ __align__(8) uint64_t full_a[kStages], full_b[kStages], empty[kStages], accum_bar;
-    __shared__ __align__(8) uint64_t raw_bar[kDecoders][kRawDepth];
+    constexpr int kQuadWords = 32 * K;                       // four interleaved tiles
+    constexpr int kRawStageWords = 8 * kQuadWords;           // 4 tile rows x 2 quads
+    constexpr uint32_t kRawStageBytes = kRawStageWords * 4;
+    constexpr int kRawDepth = raw_depth(K);
+    __shared__ __align__(8) uint64_t full_a[kStages], done[kStages], full_b[kBSlots], accum_bar;
+    __shared__ __align__(8) uint64_t raw_full[kRawDepthMax], raw_empty[kRawDepthMax];
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile int s_failed;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, q = lane & 3;
+    unsigned long long* tr = p.trace ? p.trace + (blockIdx.y * gridDim.x + blockIdx.x) * 8 : nullptr;
+    if (tr && threadIdx.x == 0) tr[0] = global_ns();
     const int col_blocks = p.out >> 7;
     const int cblock = blockIdx.x % col_blocks;
     const int split = blockIdx.x / col_blocks;
     const int tok0 = blockIdx.y * kTokTile;
+    const int halves = p.rows - tok0 > kTokHalf ? 2 : 1;      // accumulator halves this CTA fills
+    const uint32_t tmem_cols = halves * kTokHalf;
     const int st0 = static_cast<int>(static_cast<int64_t>(p.stages_total) * split / p.splits);
     const int st1 = static_cast<int>(static_cast<int64_t>(p.stages_total) * (split + 1) / p.splits);
     const int nst = st1 - st0;
 
-    // shared memory: A stages | B stages | raw rings; the swizzled stages need 1024-byte alignment
+    // shared memory: A stages | B slots | raw rings; the swizzled operands need 1024-byte alignment
     unsigned char* a_base = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
     unsigned char* b_base = a_base + kStages * kAStageBytes;
-    uint32_t* raw_base = reinterpret_cast<uint32_t*>(b_base + kStages * kBStageBytes);
+    uint32_t* raw_base = reinterpret_cast<uint32_t*>(b_base + kBSlots * kBSlotBytes);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) { mbar_init(&full_a[s], kDecoders); mbar_init(&full_b[s], 1); mbar_init(&empty[s], 1); }
+        for (int s = 0; s < kStages; ++s) { mbar_init(&full_a[s], kGroupWarps); mbar_init(&done[s], 1); }
+        for (int s = 0; s < kBSlots; ++s) mbar_init(&full_b[s], 1);
         mbar_init(&accum_bar, 1);
-        for (int w = 0; w < kDecoders; ++w)
-            for (int d = 0; d < kRawDepth; ++d) mbar_init(&raw_bar[w][d], 1);
+        for (int d = 0; d < kRawDepth; ++d) { mbar_init(&raw_full[d], 1); mbar_init(&raw_empty[d], kGroupWarps); }
         s_failed = 0;
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    if (warp == kDecoders + 1) tmem_alloc(&tmem_base_slot, kTokTile);
+    if (warp == kMmaWarp) tmem_alloc(&tmem_base_slot, tmem_cols);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = tmem_base_slot;
+    if (tr && threadIdx.x == 0) tr[1] = global_ns();
 
-    if (warp < kDecoders) {
-        // ================= decoder warps: packed row -> 16 x 128 slice of the A stage =================
+    const int dec = warp - kFirstDecoder;                        // decoder index, negative for the other roles
+    if (dec >= 0) {
+        // ================= decoder warps: packed quad -> 16 inputs x 64 outputs of the A stage =================
+        // Two groups of eight warps take alternate stages, so that one group's barrier round trips and
+        // proxy fence overlap the other group's arithmetic.  Within a group: (tile row of the stage, quad).
+        const int group = dec >> 3, trow = dec & 3, quad = (dec >> 2) & 1;
         const LaneGeom<K> geom(lane);
-        uint32_t* ring = raw_base + static_cast<size_t>(warp) * kRawDepth * kRowWords;
-        const size_t row_stride = static_cast<size_t>(p.tiles_n) * (32 * K);
-        // this warp's rows: input tile 4*stage + warp, for stage = st0 .. st1-1
-        const char* next_src = reinterpret_cast<const char*>(
-            p.wq + (static_cast<int64_t>(4 * st0 + warp) * p.tiles_n + cblock * 8) * (8 * K));
-        if (lane == 0)
-            for (int d = 0; d < kRawDepth; ++d)
-                if (d < nst) {
-                    mbar_expect_tx(&raw_bar[warp][d], kRowBytes);
-                    bulk_copy_g2s(ring + d * kRowWords, next_src + static_cast<size_t>(d) * 4 * row_stride, kRowBytes, &raw_bar[warp][d]);
-                }
-        next_src += static_cast<size_t>(kRawDepth) * 4 * row_stride;
-        int rslot = 0;
-        uint32_t rparity = 0;
-        for (int it = 0; it < nst; ++it) {
-            const int s = it % kStages;
-            const uint32_t par = (it / kStages) & 1u;
-            // the MMAs that read this stage are done, and this warp's packed row has landed
-            const bool ready = qmm_wait(&empty[s], par ^ 1u, &s_failed) && qmm_wait(&raw_bar[warp][rslot], rparity, &s_failed);
-            if (!__all_sync(0xffffffffu, ready)) break;
+        // this warp's quad of a packed stage: input tile 4*stage + trow, output tiles 8*cblock + 4*quad .. +3
+        const uint32_t* my_quad = raw_base + (trow * 2 + quad) * kQuadWords;
+        // A barrier test takes a few hundred cycles to answer, so the tests for the warp's next stage are
+        // issued before the current stage is decoded and their answer is only looked at afterwards.
+        auto stage_ready = [&](int it) -> bool {
+            return mbar_test_wait(&raw_full[it % kRawDepth], (it / kRawDepth) & 1u) &
+                   mbar_test_wait(&done[it % kStages], ((it / kStages) & 1u) ^ 1u);
+        };
+        bool ready = group < nst && stage_ready(group);
+        for (int it = group; it < nst; it += kDecoderGroups) {
+            const int s = it % kStages, rslot = it % kRawDepth;
+            if (!__all_sync(0xffffffffu, ready)) {
+                // the packed stage has landed, and the MMAs that read this A stage last time are done
+                ready = qmm_wait(&raw_full[rslot], (it / kRawDepth) & 1u, &s_failed) &&
+                        qmm_wait(&done[s], ((it / kStages) & 1u) ^ 1u, &s_failed);
+                if (!__all_sync(0xffffffffu, ready)) break;
+            }
             unsigned char* a_stage = a_base + s * kAStageBytes;
-            const uint32_t* row_words = ring + rslot * kRowWords;
+            const uint4* qw = reinterpret_cast<const uint4*>(my_quad + rslot * kRawStageWords);
+            const uint4 W2 = qw[geom.i2];
+            const uint4 W1 = qw[geom.i1];
+            uint4 W0 = make_uint4(0, 0, 0, 0);
+            if constexpr (K >= 5) W0 = qw[geom.i0];
+            const uint32_t w2[4] = {W2.x, W2.y, W2.z, W2.w}, w1[4] = {W1.x, W1.y, W1.z, W1.w},
+                           w0[4] = {W0.x, W0.y, W0.z, W0.w};
+            ready = it + kDecoderGroups < nst && stage_ready(it + kDecoderGroups);
 #pragma unroll
-            for (int quad = 0; quad < 2; ++quad) {
-                const uint4* qw = reinterpret_cast<const uint4*>(row_words + quad * (32 * K));
-                const uint4 W2 = qw[geom.i2];
-                const uint4 W1 = qw[geom.i1];
-                uint4 W0 = make_uint4(0, 0, 0, 0);
-                if constexpr (K >= 5) W0 = qw[geom.i0];
-                const uint32_t w2[4] = {W2.x, W2.y, W2.z, W2.w}, w1[4] = {W1.x, W1.y, W1.z, W1.w},
-                               w0[4] = {W0.x, W0.y, W0.z, W0.w};
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    uint32_t a0, a1, a2, a3;
-                    lane_weights_exact<K, CB>(w2[j], w1[j], w0[j], geom.slack, a0, a1, a2, a3);
-                    // rows (= output columns) 16t+g and 16t+g+8 of the A tile; 16-byte chunks 2w and 2w+1 of
-                    // the row, XORed with the row index modulo 8 (the 128-byte swizzle); 4q bytes into the chunk
-                    const int t = quad * 4 + j;
-                    unsigned char* r0 = a_stage + (16 * t + g) * 128 + 4 * q;
-                    const int c0 = ((2 * warp) ^ g) << 4, c1 = ((2 * warp + 1) ^ g) << 4;
-                    *reinterpret_cast<uint32_t*>(r0 + c0) = a0;
-                    *reinterpret_cast<uint32_t*>(r0 + 8 * 128 + c0) = a1;
-                    *reinterpret_cast<uint32_t*>(r0 + c1) = a2;
-                    *reinterpret_cast<uint32_t*>(r0 + 8 * 128 + c1) = a3;
-                }
+            for (int j = 0; j < 4; ++j) {
+                uint32_t a0, a1, a2, a3;
+                lane_weights_exact<K, CB>(w2[j], w1[j], w0[j], geom.slack, a0, a1, a2, a3);
+                // rows (= output columns) 16t+g and 16t+g+8 of the A tile; 16-byte chunks 2*trow and 2*trow+1 of
+                // the row, XORed with the row index modulo 8 (the 128-byte swizzle); 4q bytes into the chunk
+                const int t = quad * 4 + j;
+                unsigned char* r0 = a_stage + (16 * t + g) * 128 + 4 * q;
+                const int c0 = ((2 * trow) ^ g) << 4, c1 = ((2 * trow + 1) ^ g) << 4;
+                *reinterpret_cast<uint32_t*>(r0 + c0) = a0;
+                *reinterpret_cast<uint32_t*>(r0 + 8 * 128 + c0) = a1;
+                *reinterpret_cast<uint32_t*>(r0 + c1) = a2;
+                *reinterpret_cast<uint32_t*>(r0 + 8 * 128 + c1) = a3;
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the MMA unit
             __syncwarp();
             if (lane == 0) {
+                mbar_arrive(&raw_empty[rslot]);                         // the packed words were consumed: slot free for this warp
                 mbar_arrive(&full_a[s]);
-                if (it + kRawDepth < nst) {
-                    mbar_expect_tx(&raw_bar[warp][rslot], kRowBytes);
-                    bulk_copy_g2s(ring + rslot * kRowWords, next_src, kRowBytes, &raw_bar[warp][rslot]);
+            }
+        }
+        if (tr && threadIdx.x == 32 * kFirstDecoder) tr[2] = global_ns();
+    } else if (warp == kActWarp) {
+        // ================= activation producer: one tensor copy per half and stage =================
+        if (lane == 0) {
+            // a slot is free once the MMAs of the stage that used it last are done
+            int slot = 0;
+            for (int it = 0; it < nst && !s_failed; ++it) {
+                for (int h = 0; h < halves; ++h) {
+                    const int before = it * halves + h - kBSlots;     // the use of this slot one lap earlier
+                    if (before >= 0) {
+                        const int st = before / halves;
+                        if (!qmm_wait(&done[st % kStages], (st / kStages) & 1u, &s_failed)) break;
+                    }
+                    mbar_expect_tx(&full_b[slot], kBSlotBytes);
+                    tma_load_2d(b_base + slot * kBSlotBytes, &xmap, (st0 + it) * 64, tok0 + h * kTokHalf, &full_b[slot]);
+                    if (++slot == kBSlots) slot = 0;
                 }
             }
-            next_src += 4 * row_stride;
-            if (++rslot == kRawDepth) { rslot = 0; rparity ^= 1u; }
+            if (tr) tr[7] = global_ns();
         }
-    } else if (warp == kDecoders) {
-        // ================= activation producer: one tensor copy per stage =================
+    } else if (warp == kWeightWarp) {
+        // ================= weight producer: one tensor copy (4 tile rows x 8 tiles) per stage =================
         if (lane == 0) {
-            for (int it = 0; it < nst; ++it) {
-                const int s = it % kStages;
-                const uint32_t par = (it / kStages) & 1u;
-                if (!qmm_wait(&empty[s], par ^ 1u, &s_failed)) break;
-                mbar_expect_tx(&full_b[s], kBStageBytes);
-                tma_load_2d(b_base + s * kBStageBytes, &xmap, (st0 + it) * 64, tok0, &full_b[s]);
+            int slot = 0;
+            uint32_t par = 0;
+            for (int it = 0; it < nst && !s_failed; ++it) {
+                if (!qmm_wait(&raw_empty[slot], par ^ 1u, &s_failed)) break;
+                mbar_expect_tx(&raw_full[slot], kRawStageBytes);
+                tma_load_2d(raw_base + slot * kRawStageWords, &wmap, cblock * (32 * K), 4 * (st0 + it), &raw_full[slot]);
+                if (++slot == kRawDepth) { slot = 0; par ^= 1u; }
             }
         }
-    } else {
+    } else if (warp == kMmaWarp) {
         // ================= MMA issuer =================
         if (lane == 0) {
-            for (int it = 0; it < nst; ++it) {
+            // all barrier tests of a stage are issued together (each takes a few hundred cycles to answer)
+            auto stage_ready = [&](int it) -> bool {
+                bool ok = mbar_test_wait(&full_a[it % kStages], (it / kStages) & 1u);
+                for (int h = 0; h < halves; ++h) {
+                    const int u = it * halves + h;
+                    ok &= mbar_test_wait(&full_b[u % kBSlots], (u / kBSlots) & 1u);
+                }
+                return ok;
+            };
+            bool ready = nst > 0 && stage_ready(0);
+            for (int it = 0; it < nst && !s_failed; ++it) {
                 const int s = it % kStages;
-                const uint32_t par = (it / kStages) & 1u;
-                if (!qmm_wait(&full_a[s], par, &s_failed)) break;
-                if (!qmm_wait(&full_b[s], par, &s_failed)) break;
+                if (!ready) {
+                    if (!qmm_wait(&full_a[s], (it / kStages) & 1u, &s_failed)) break;
+                    bool ok = true;
+                    for (int h = 0; h < halves && ok; ++h) {
+                        const int u = it * halves + h;
+                        ok = qmm_wait(&full_b[u % kBSlots], (u / kBSlots) & 1u, &s_failed);
+                    }
+                    if (!ok) break;
+                }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a_addr = smem_addr(a_base + s * kAStageBytes), b_addr = smem_addr(b_base + s * kBStageBytes);
+                const uint32_t a_addr = smem_addr(a_base + s * kAStageBytes);
+                for (int h = 0; h < halves; ++h) {
+                    const uint32_t b_addr = smem_addr(b_base + ((it * halves + h) % kBSlots) * kBSlotBytes);
 #pragma unroll
-                for (int kk = 0; kk < 4; ++kk)                          // 4 x 16 inputs = one 64-input stage
-                    umma_f16(tmem, umma_desc(a_addr + kk * 32), umma_desc(b_addr + kk * 32), kInstrDesc, (it > 0 || kk > 0) ? 1u : 0u);
-                umma_commit(&empty[s]);                                 // stage free once these MMAs have read it
+                    for (int kk = 0; kk < 4; ++kk)                      // 4 x 16 inputs = one 64-input stage
+                        umma_f16(tmem + h * kTokHalf, umma_desc(a_addr + kk * 32), umma_desc(b_addr + kk * 32), kInstrDesc,
+                                 (it > 0 || kk > 0) ? 1u : 0u);
+                }
+                umma_commit(&done[s]);                                  // A stage and B slots free once these MMAs have read them
+                ready = it + 1 < nst && stage_ready(it + 1);
             }
             umma_commit(&accum_bar);                                    // accumulator complete
+            if (tr) tr[3] = global_ns();
         }
     }
 
     // ================= epilogue: accumulator -> fp32 partial products =================
-    if (warp < kDecoders) {
+    if (dec >= 0) {
         if (nst > 0) {
-            qmm_wait(&accum_bar, 0, &s_failed);
+            qmm_wait_warp(&accum_bar, 0, &s_failed, lane);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         }
-        const int col = cblock * 128 + warp * 32 + lane;                // this thread's output column = its TMEM lane
+        if (tr && threadIdx.x == 32 * kFirstDecoder) tr[4] = global_ns();
+        // a warp may read the 32 lanes 32*(warp%4)..; the warps of a lane quarter share the token columns
+        const int lq = warp & 3, cpart = dec >> 2;
+        const int col = cblock * 128 + lq * 32 + lane;                  // this thread's output column = its TMEM lane
         float* dst = p.partials + (static_cast<int64_t>(split) * p.rows) * p.out + col;
-        for (int c = 0; c < kTokTile; c += 32) {
+        const int c_span = static_cast<int>(tmem_cols) / (kDecoders / 4);
+        const int c_begin = cpart * c_span, c_end = c_begin + c_span;
+        for (int c = c_begin; c < c_end; c += 32) {
             if (tok0 + c >= p.rows) break;
             uint32_t r[32];
-            if (nst > 0) tmem_ld32(tmem + (static_cast<uint32_t>(warp * 32) << 16) + c, r);
+            if (nst > 0) tmem_ld32(tmem + (static_cast<uint32_t>(lq * 32) << 16) + c, r);
             else
 #pragma unroll
                 for (int i = 0; i < 32; ++i) r[i] = 0;
@@ -264,14 +345,16 @@ qmm_kernel(const __grid_constant__ CUtensorMap xmap, const QmmArgs p) {
             }
         }
     }
+    if (tr && threadIdx.x == 32 * kFirstDecoder) tr[5] = global_ns();
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if (tr && threadIdx.x == 0) tr[6] = global_ns();
     if (s_failed) {
         // copies that were still in flight when a wait gave up must land before the CTA's shared memory is released
         const unsigned long long t0 = global_ns();
         while (global_ns() - t0 < 2000000ull) __nanosleep(1000);
     }
-    if (warp == kDecoders + 1) tmem_dealloc(tmem, kTokTile);
+    if (warp == kMmaWarp) tmem_dealloc(tmem, tmem_cols);
     if (threadIdx.x == 0 && s_failed) atomicExch(p.error, 3u);
 }
 
@@ -293,7 +376,7 @@ EncodeFn encode_fn() {
 }
 
 template <int K, int CB>
-cudaError_t qmm_launch_one(const CUtensorMap& map, const QmmArgs& p, dim3 grid, size_t smem, cudaStream_t stream) {
+cudaError_t qmm_launch_one(const CUtensorMap& map, const CUtensorMap& wmap, const QmmArgs& p, dim3 grid, size_t smem, cudaStream_t stream) {
     auto kernel = qmm_kernel<K, CB>;
     static bool attribute_set = false;
     if (!attribute_set) {
@@ -301,21 +384,22 @@ cudaError_t qmm_launch_one(const CUtensorMap& map, const QmmArgs& p, dim3 grid, 
         if (e != cudaSuccess) return e;
         attribute_set = true;
     }
-    kernel<<<grid, kThreads, smem, stream>>>(map, p);
+    kernel<<<grid, kThreads, smem, stream>>>(map, wmap, p);
     return cudaGetLastError();
 }
 
 template <int K>
-cudaError_t qmm_launch_k(int cb, const CUtensorMap& map, const QmmArgs& p, dim3 grid, size_t smem, cudaStream_t stream) {
-    if (cb == 0) return qmm_launch_one<K, 0>(map, p, grid, smem, stream);
-    if (cb == 1) return qmm_launch_one<K, 1>(map, p, grid, smem, stream);
-    return qmm_launch_one<K, 2>(map, p, grid, smem, stream);
+cudaError_t qmm_launch_k(int cb, const CUtensorMap& map, const CUtensorMap& wmap, const QmmArgs& p, dim3 grid, size_t smem, cudaStream_t stream) {
+    if (cb == 0) return qmm_launch_one<K, 0>(map, wmap, p, grid, smem, stream);
+    if (cb == 1) return qmm_launch_one<K, 1>(map, wmap, p, grid, smem, stream);
+    return qmm_launch_one<K, 2>(map, wmap, p, grid, smem, stream);
 }
 
 }  // namespace
 
-static int g_qmm_waves = 1;
-void qmm_set_tuning(int waves) { if (waves > 0) g_qmm_waves = waves; }
+unsigned long long* g_qmm_trace = nullptr;
+static int g_qmm_splits = 0;                              // 0 = chosen by the cost model below
+void qmm_set_tuning(int splits) { g_qmm_splits = splits > 0 ? splits : 0; }
 
 QmmPlan plan_qmm(int in, int out, int64_t rows) {
     QmmPlan plan{};
@@ -323,11 +407,19 @@ QmmPlan plan_qmm(int in, int out, int64_t rows) {
     plan.token_tiles = static_cast<int>((rows + kTokTile - 1) / kTokTile);
     const int stages_total = in / 64;
     const int64_t base = static_cast<int64_t>(col_blocks) * plan.token_tiles;
-    // split the input range so that the CTAs fill the 148 SMs g_qmm_waves times (one CTA per SM: the
-    // stages take most of the shared memory); every split keeps at least 8 stages
-    int splits = static_cast<int>((static_cast<int64_t>(kSmCount) * g_qmm_waves + base / 2) / base);
-    splits = std::max(1, std::min(splits, std::max(1, stages_total / 8)));
-    plan.splits = splits;
+    const int max_splits = std::max(1, stages_total / 8);     // every split keeps at least 8 stages
+    if (g_qmm_splits) { plan.splits = std::min(g_qmm_splits, max_splits); return plan; }
+    // One CTA per SM (the operand rings take most of the shared memory).  Estimated time of a choice:
+    // waves x (stages per CTA + fixed prologue/epilogue) + the fp32 partials every extra split writes and
+    // the output rotation reads back.
+    const double stage_us = rows > kTokHalf ? 0.6 : 0.35, fixed_us = 4.0;
+    const double partial_us = static_cast<double>(rows) * out * 8.0 / 8.0e6;
+    double best = 0;
+    for (int s = 1; s <= max_splits; ++s) {
+        const int64_t waves = (base * s + kSmCount - 1) / kSmCount;
+        const double t = waves * (((stages_total + s - 1) / s) * stage_us + fixed_us) + (s - 1) * partial_us;
+        if (s == 1 || t < best) { best = t; plan.splits = s; }
+    }
     return plan;
 }
 
@@ -344,27 +436,37 @@ cudaError_t launch_qmm(const uint32_t* wq, int in, int out, int k, int cb, const
     CUtensorMap map;
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(in), static_cast<cuuint64_t>(rows)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(in) * sizeof(__half)};
-    const cuuint32_t box[2] = {64, kTokTile};
+    const cuuint32_t box[2] = {64, kTokHalf};
     const cuuint32_t elem[2] = {1, 1};
     if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(xhat), dims, strides, box, elem,
                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return cudaErrorInvalidValue;
+    // packed weights as a 2-D array of 8-byte words [in/16 tile rows, out/16 * 4K]: a box of one stage is
+    // 4 tile rows x 8 tiles (32*K words of a row), landing contiguously in shared memory
+    CUtensorMap wmap;
+    const cuuint64_t wdims[2] = {static_cast<cuuint64_t>(out / 16) * 4 * k, static_cast<cuuint64_t>(in / 16)};
+    const cuuint64_t wstrides[1] = {static_cast<cuuint64_t>(out / 16) * 32 * k};
+    const cuuint32_t wbox[2] = {static_cast<cuuint32_t>(32 * k), 4};
+    if (encode(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint32_t*>(wq), wdims, wstrides, wbox, elem,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return cudaErrorInvalidValue;
     QmmArgs p{};
     p.wq = wq; p.partials = partials; p.error = error;
     p.in = in; p.out = out; p.rows = static_cast<int>(rows); p.tiles_n = out / 16;
-    p.splits = plan.splits; p.stages_total = in / 64;
+    p.splits = plan.splits; p.stages_total = in / 64; p.trace = g_qmm_trace;
     const dim3 grid(static_cast<unsigned>((out / 128) * plan.splits), static_cast<unsigned>(plan.token_tiles));
-    const size_t smem = kStages * (kAStageBytes + kBStageBytes) + static_cast<size_t>(kDecoders) * kRawDepth * 64 * 8 * 4 + 1024;
+    const size_t smem = kStages * kAStageBytes + kBSlots * kBSlotBytes + kRawBytes + 1024;
     switch (k) {
-        case 1: return qmm_launch_k<1>(cb, map, p, grid, smem, stream);
-        case 2: return qmm_launch_k<2>(cb, map, p, grid, smem, stream);
-        case 3: return qmm_launch_k<3>(cb, map, p, grid, smem, stream);
-        case 4: return qmm_launch_k<4>(cb, map, p, grid, smem, stream);
-        case 5: return qmm_launch_k<5>(cb, map, p, grid, smem, stream);
-        case 6: return qmm_launch_k<6>(cb, map, p, grid, smem, stream);
-        case 7: return qmm_launch_k<7>(cb, map, p, grid, smem, stream);
-        case 8: return qmm_launch_k<8>(cb, map, p, grid, smem, stream);
+        case 1: return qmm_launch_k<1>(cb, map, wmap, p, grid, smem, stream);
+        case 2: return qmm_launch_k<2>(cb, map, wmap, p, grid, smem, stream);
+        case 3: return qmm_launch_k<3>(cb, map, wmap, p, grid, smem, stream);
+        case 4: return qmm_launch_k<4>(cb, map, wmap, p, grid, smem, stream);
+        case 5: return qmm_launch_k<5>(cb, map, wmap, p, grid, smem, stream);
+        case 6: return qmm_launch_k<6>(cb, map, wmap, p, grid, smem, stream);
+        case 7: return qmm_launch_k<7>(cb, map, wmap, p, grid, smem, stream);
+        case 8: return qmm_launch_k<8>(cb, map, wmap, p, grid, smem, stream);
         default: return cudaErrorInvalidValue;
     }
 }
