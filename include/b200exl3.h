@@ -193,6 +193,33 @@ int b200exl3_group_workspace_bytes(const b200exl3_group* handle, int64_t rows, s
 int b200exl3_group_forward(const b200exl3_group* handle, const void* d_x, int x_dtype, int64_t rows, void* const* d_ys,
                            void* d_workspace, size_t workspace_bytes, b200exl3_stream stream);
 
+/* ---- Exl3SwitchGlu: grouped SwiGLU experts ---------------------------------------------------------------
+ * Replaces Exl3SwitchGlu::{new, forward} (native/src/moe.rs:808-971; SiLU activation) and, under it,
+ * routed_inputs (moe.rs:184-236), expert_mapped / prepared_expert_raw (native/src/linear.rs:2817-2885),
+ * glu_down_input (moe.rs:438-533) and finish_and_reduce (moe.rs:586-609).
+ *
+ * Banks, in the checkpoint tile layout: gu_trellis [in/16, experts*2*hidden/16, 16K] holds the gate columns of
+ * all experts followed by the up columns of all experts (expert e, projection p starts at tile column
+ * p*experts*hidden/16 + e*hidden/16); down_trellis [hidden/16, experts*in/16, 16K].  Scales: gu_suh
+ * [experts, 2, in], gu_svh [experts, 2, hidden], down_suh [experts, hidden], down_svh [experts, in], all in
+ * scale_dtype.  Requirements as in the reference: in and hidden multiples of 128, 1 <= top_k <= experts, K != 7.
+ * The banks are re-laid into library-owned memory. */
+typedef struct b200exl3_moe b200exl3_moe;
+int b200exl3_moe_create(const uint16_t* d_gu_trellis, const void* d_gu_suh, const void* d_gu_svh,
+                        const uint16_t* d_down_trellis, const void* d_down_suh, const void* d_down_svh, int scale_dtype,
+                        int experts, int in, int hidden, int top_k, int k, int codebook, uint32_t flags,
+                        b200exl3_moe** out);
+void b200exl3_moe_free(b200exl3_moe* handle);
+int b200exl3_moe_workspace_bytes(const b200exl3_moe* handle, int64_t rows, size_t* out_bytes);
+/* x [rows, in] in x_dtype; selected [rows, top_k] expert ids (u32; ids past the bank are clamped to the last
+ * expert instead of reading out of bounds); scores [rows, top_k] routing weights in score_dtype (fp16 = 9 or
+ * fp32 = 10); y [rows, in] in score_dtype (the reference's result dtype: fp16 products promoted by the scores).
+ * Every (token, choice) slot runs as one activation row against its expert's columns; rows are processed in
+ * passes of at most 256 slots.  The workspace follows the rules of the linear layer's workspace. */
+int b200exl3_moe_forward(const b200exl3_moe* handle, const void* d_x, int x_dtype, int64_t rows,
+                         const uint32_t* d_selected, const void* d_scores, int score_dtype, void* d_y,
+                         void* d_workspace, size_t workspace_bytes, b200exl3_stream stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -78,6 +78,19 @@ struct LayerCore {
 struct b200exl3_linear { LayerCore c; };
 struct b200exl3_group { LayerCore c; };
 
+// Grouped experts of a SwiGLU block: two banks in the quad layout (gate columns of all experts, then up
+// columns of all experts; down columns of all experts) and the per-expert scales.
+struct b200exl3_moe {
+    int experts, in, hidden, top_k, k, cb;
+    uint32_t flags;
+    uint32_t* gu_wq;     // [in/16, experts*2*hidden/16] tiles
+    uint32_t* down_wq;   // [hidden/16, experts*in/16] tiles
+    __half* gu_suh;      // [experts, 2, in]
+    __half* gu_svh;      // [experts, 2, hidden]
+    __half* down_suh;    // [experts, hidden]
+    __half* down_svh;    // [experts, in]
+};
+
 static void core_free(LayerCore& c) {
     cudaFree(c.suh);
     cudaFree(c.svh);
@@ -583,5 +596,153 @@ int b200exl3_group_forward(const b200exl3_group* h, const void* d_x, int x_dtype
         if (!d_ys[g]) return fail("NULL buffer");
     return forward_common(h->c, d_x, x_dtype, nullptr, rows, d_ys, nullptr, ws, ws_bytes, as_stream(s));
 }
+
+/* ---- Exl3SwitchGlu ----------------------------------------------------------------------------- */
+
+// Slots (token, choice) handled per pass: bounds the scratch and keeps the virtual column blocks of one
+// launch below the arrival-counter capacity.
+constexpr int64_t kMoeChunkSlots = 256;
+
+static int64_t moe_blocks_per_slot(int in, int hidden) { return std::max(2 * hidden / 128, in / 128); }
+static int64_t moe_chunk_rows(const b200exl3_moe* h) {
+    const int64_t counters = static_cast<int64_t>(kCounterBytes / sizeof(unsigned int)) - 2;
+    const int64_t slots = std::min(kMoeChunkSlots, counters / moe_blocks_per_slot(h->in, h->hidden));
+    return std::max<int64_t>(1, slots / h->top_k);
+}
+
+struct MoeLayout {
+    size_t xgu, ygu, xdown, ydown, partials, total;
+    QmvPlan gu_plan, down_plan;
+};
+
+static MoeLayout moe_layout(const b200exl3_moe* h, int64_t rows) {
+    MoeLayout l{};
+    const int64_t slots = std::min(rows, moe_chunk_rows(h)) * h->top_k;
+    l.gu_plan = plan_qmv(h->in, static_cast<int>(slots * 2 * h->hidden), h->k, 1);
+    l.down_plan = plan_qmv(h->hidden, static_cast<int>(slots * h->in), h->k, 1);
+    size_t at = kCounterBytes;
+    l.xgu = at; at += round256(static_cast<size_t>(slots) * 2 * h->in * sizeof(__half));
+    l.ygu = at; at += round256(static_cast<size_t>(slots) * 2 * h->hidden * sizeof(float));
+    l.xdown = at; at += round256(static_cast<size_t>(slots) * h->hidden * sizeof(__half));
+    l.ydown = at; at += round256(static_cast<size_t>(slots) * h->in * sizeof(float));
+    l.partials = at;
+    at += std::max(qmv_partial_bytes(l.gu_plan, static_cast<int>(slots * 2 * h->hidden), 1),
+                   qmv_partial_bytes(l.down_plan, static_cast<int>(slots * h->in), 1));
+    l.total = at;
+    return l;
+}
+
+int b200exl3_moe_create(const uint16_t* d_gu_trellis, const void* d_gu_suh, const void* d_gu_svh,
+                        const uint16_t* d_down_trellis, const void* d_down_suh, const void* d_down_svh, int scale_dtype,
+                        int experts, int in, int hidden, int top_k, int k, int cb, uint32_t flags, b200exl3_moe** out_handle) {
+    if (!out_handle) return fail("out pointer is NULL");
+    *out_handle = nullptr;
+    if (valid_format(k, cb)) return -1;
+    if (experts <= 0 || top_k <= 0 || top_k > experts || in <= 0 || hidden <= 0 || in % 128 || hidden % 128 || k == 7 ||
+        static_cast<int64_t>(experts) * 2 * hidden > INT32_MAX || static_cast<int64_t>(experts) * in > INT32_MAX)
+        return fail("invalid or overflowing SwitchGLU dimensions");
+    if (top_k * moe_blocks_per_slot(in, hidden) > static_cast<int64_t>(kCounterBytes / sizeof(unsigned int)) - 2)
+        return fail("invalid or overflowing SwitchGLU dimensions");
+    if (!d_gu_trellis || !d_down_trellis || !d_gu_suh || !d_gu_svh || !d_down_suh || !d_down_svh)
+        return fail("SwitchGLU trellis/scales disagree");
+    if (!dtype_is_float(scale_dtype)) return fail("unsupported scale dtype %d", scale_dtype);
+    if (!aligned16(d_gu_trellis) || !aligned16(d_down_trellis)) return fail("device pointers must be 16-byte aligned");
+    b200exl3_moe* h = new (std::nothrow) b200exl3_moe{};
+    if (!h) return fail("out of host memory");
+    h->experts = experts; h->in = in; h->hidden = hidden; h->top_k = top_k; h->k = k; h->cb = cb; h->flags = flags;
+    auto convert = [&](const void* src, int64_t n, __half** dst) -> int {
+        B200_TRY(cudaMalloc(dst, static_cast<size_t>(n) * sizeof(__half)), "cudaMalloc(scales)");
+        to_half_kernel<<<static_cast<unsigned>((n + 255) / 256), 256>>>(src, scale_dtype, n, *dst);
+        return check(cudaGetLastError(), "convert scales");
+    };
+    auto repack = [&](const uint16_t* src, int tiles_k, int64_t tiles_n, uint32_t** dst) -> int {
+        const size_t bytes = static_cast<size_t>(tiles_k) * tiles_n * 16 * k * sizeof(uint16_t);
+        B200_TRY(cudaMalloc(dst, bytes), "cudaMalloc(weights)");
+        return check(launch_repack_quads(reinterpret_cast<const uint32_t*>(src), tiles_k, static_cast<int>(tiles_n), k, *dst, 0),
+                     "repack weights");
+    };
+    int rc = convert(d_gu_suh, static_cast<int64_t>(experts) * 2 * in, &h->gu_suh);
+    if (!rc) rc = convert(d_gu_svh, static_cast<int64_t>(experts) * 2 * hidden, &h->gu_svh);
+    if (!rc) rc = convert(d_down_suh, static_cast<int64_t>(experts) * hidden, &h->down_suh);
+    if (!rc) rc = convert(d_down_svh, static_cast<int64_t>(experts) * in, &h->down_svh);
+    if (!rc) rc = repack(d_gu_trellis, in / 16, static_cast<int64_t>(experts) * 2 * hidden / 16, &h->gu_wq);
+    if (!rc) rc = repack(d_down_trellis, hidden / 16, static_cast<int64_t>(experts) * in / 16, &h->down_wq);
+    if (!rc) rc = check(cudaDeviceSynchronize(), "moe_create");
+    if (rc) {
+        b200exl3_moe_free(h);
+        return -1;
+    }
+    *out_handle = h;
+    return 0;
+}
+
+void b200exl3_moe_free(b200exl3_moe* h) {
+    if (!h) return;
+    cudaFree(h->gu_wq); cudaFree(h->down_wq);
+    cudaFree(h->gu_suh); cudaFree(h->gu_svh); cudaFree(h->down_suh); cudaFree(h->down_svh);
+    delete h;
+}
+
+int b200exl3_moe_workspace_bytes(const b200exl3_moe* h, int64_t rows, size_t* out_bytes) {
+    if (!h || !out_bytes) return fail("NULL argument");
+    if (rows <= 0) return fail("invalid SwitchGLU input/routes");
+    *out_bytes = moe_layout(h, rows).total;
+    return 0;
+}
+
+int b200exl3_moe_forward(const b200exl3_moe* h, const void* d_x, int x_dtype, int64_t rows, const uint32_t* d_selected,
+                         const void* d_scores, int score_dtype, void* d_y, void* ws, size_t ws_bytes, b200exl3_stream s) {
+    if (!h) return fail("NULL handle");
+    if (rows <= 0) return fail("invalid SwitchGLU input/routes");
+    if (!dtype_is_float(x_dtype)) return fail("unsupported input dtype %d", x_dtype);
+    if (score_dtype != kF16 && score_dtype != kF32) return fail("unsupported score dtype %d", score_dtype);
+    if (!d_x || !d_selected || !d_scores || !d_y) return fail("NULL buffer");
+    const MoeLayout l = moe_layout(h, rows);
+    if (!ws || ws_bytes < l.total) return fail("workspace too small: %zu bytes given, %zu needed", ws_bytes, l.total);
+    if (!aligned16(ws) || !aligned16(d_y)) return fail("device pointers must be 16-byte aligned");
+    cudaStream_t stream = as_stream(s);
+    char* base = static_cast<char*>(ws);
+    const bool exact = (h->flags & B200EXL3_EXACT_WEIGHTS) != 0;
+    const size_t x_size = dtype_size(x_dtype), score_size = dtype_size(score_dtype);
+    __half* xgu = reinterpret_cast<__half*>(base + l.xgu);
+    float* ygu = reinterpret_cast<float*>(base + l.ygu);
+    __half* xdown = reinterpret_cast<__half*>(base + l.xdown);
+    float* ydown = reinterpret_cast<float*>(base + l.ydown);
+    const int64_t chunk = moe_chunk_rows(h);
+    for (int64_t r0 = 0; r0 < rows; r0 += chunk) {
+        const int64_t n = std::min(chunk, rows - r0), slots = n * h->top_k;
+        const uint32_t* sel = d_selected + r0 * h->top_k;
+        // every slot is one activation row against the columns of its own expert
+        auto mapped = [&](const uint32_t* wq, const __half* xhat, int in, int width, int proj, int stride_blocks, float* yhat) {
+            const int out = static_cast<int>(slots * proj * width);
+            QmvArgs a{};
+            a.wq = wq; a.xhat = xhat; a.xhat_group_stride = in;
+            a.counters = reinterpret_cast<unsigned int*>(base);
+            a.error = reinterpret_cast<unsigned int*>(base + kCounterBytes - sizeof(unsigned int));
+            a.partials = reinterpret_cast<float*>(base + l.partials);
+            a.yhat = yhat;
+            a.groups = 1; a.gcol0[0] = 0; a.gout[0] = out;
+            a.x_dtype = kF16; a.y_dtype = kF16;
+            a.in = in; a.out = out; a.rows = 1;
+            a.tiles_n = h->experts * proj * width / 16;
+            a.map_selected = sel; a.map_blocks = width / 128; a.map_proj = proj; a.map_stride_blocks = stride_blocks;
+            a.map_experts = h->experts;
+            return launch_qmv(a, h->k, h->cb, exact, plan_qmv(in, out, h->k, 1), stream);
+        };
+        B200_TRY(launch_routed_prepare(static_cast<const char*>(d_x) + static_cast<size_t>(r0) * h->in * x_size, x_dtype, h->gu_suh,
+                                       sel, h->experts, h->top_k, 2, slots, h->in, xgu, stream), "routed prepare");
+        B200_TRY(mapped(h->gu_wq, xgu, h->in, h->hidden, 2, h->experts * (h->hidden / 128), ygu), "expert gate/up kernel");
+        B200_TRY(launch_glu_down_input(ygu, h->gu_svh, h->down_suh, sel, h->experts, slots, h->hidden, h->hidden, xdown, stream),
+                 "SwiGLU glue");
+        B200_TRY(mapped(h->down_wq, xdown, h->hidden, h->in, 1, 0, ydown), "expert down kernel");
+        B200_TRY(launch_finish_and_reduce(ydown, h->down_svh, sel, h->experts,
+                                          static_cast<const char*>(d_scores) + static_cast<size_t>(r0) * h->top_k * score_size,
+                                          score_dtype, n, h->top_k, h->in,
+                                          static_cast<char*>(d_y) + static_cast<size_t>(r0) * h->in * score_size, stream),
+                 "expert reduction");
+    }
+    return 0;
+}
+
 
 }  // extern "C"

@@ -58,6 +58,12 @@ struct QmvArgs {
     int xs_offset;             // offset of the rotated activations inside a warp's shared memory
     int stage_offset;          // offset of the staged result tiles inside a warp's shared memory
     int pdl_early;             // 1: let the next kernel start as soon as this one has started its copies
+    // Expert-mapped mode (map_selected != nullptr; rows == 1, raw output): the `out` axis is virtual,
+    // [slots, map_proj, map_blocks * 128]; slot s reads the columns of expert map_selected[s] in the bank
+    // (column block map_proj_index * map_stride_blocks + expert * map_blocks + j; tiles_n is the bank's width)
+    // and multiplies them with its own rotated activations xhat[s * map_proj + projection, :].
+    const uint32_t* map_selected;
+    int map_blocks, map_proj, map_stride_blocks, map_experts;
 };
 
 struct QmvPlan {
@@ -81,6 +87,21 @@ size_t qmv_partial_bytes(const QmvPlan& plan, int out, int64_t rows);
 cudaError_t launch_qmv(QmvArgs args, int k, int cb, bool exact, const QmvPlan& plan, cudaStream_t stream);
 void qmv_set_tuning(int ctas_per_sm, int force_grid, int pdl);
 void qmv_set_trace(unsigned long long* device_buffer);
+
+// ---- grouped experts (kernels_moe.cu) ------------------------------------------------------------------
+// xhat[(slot * proj + p), :] = rotation of x[slot / top_k, :] * suh[selected[slot], p, :]   (native/src/moe.rs:184-236)
+cudaError_t launch_routed_prepare(const void* x, int x_dtype, const __half* suh, const uint32_t* selected, int experts,
+                                  int top_k, int proj, int64_t slots, int in, __half* xhat, cudaStream_t stream);
+// SwiGLU glue between the expert projections (native/src/moe.rs:438-533, SiLU): raw gate/up sums
+// ygu[slot * 2 + {0,1}, :] -> rotated input of the down projection xhat[slot, :]
+cudaError_t launch_glu_down_input(const float* ygu, const __half* gu_svh, const __half* down_suh, const uint32_t* selected,
+                                  int experts, int64_t slots, int hidden, int logical_hidden, __half* xhat,
+                                  cudaStream_t stream);
+// y[row, :] = sum over the row's top_k slots of rotate(half(raw[slot, :])) * svh[selected[slot], :] * score
+// (native/src/moe.rs:586-609); scores and y are fp16 or fp32 (score_dtype)
+cudaError_t launch_finish_and_reduce(const float* raw, const __half* down_svh, const uint32_t* selected, int experts,
+                                     const void* scores, int score_dtype, int64_t rows, int top_k, int out, void* y,
+                                     cudaStream_t stream);
 
 // ---- tensor-core product for many rows (kernels_qmm.cu) ---------------------------------------------------
 struct QmmPlan {

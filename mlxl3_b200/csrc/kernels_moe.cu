@@ -1,0 +1,166 @@
+// Glue kernels of the grouped-expert SwiGLU block (reference: native/src/moe.rs).  One warp per
+// 128-block; lane l holds elements 4l..4l+3, as in the stand-alone rotation kernels.
+//
+//   routed prepare    native/src/moe.rs:184-236   x row of the slot's token * gate/up input scales of the
+//                                                  slot's expert, rotated (same rounding points as the
+//                                                  plain input rotation)
+//   glu_down_input    native/src/moe.rs:438-533   SiLU path: both rotations without intermediate rounding
+//   finish_and_reduce native/src/moe.rs:586-609   output rotation, expert output scales, routing weights,
+//                                                  sum over the top_k slots of a token
+#include "hadamard.cuh"
+#include "kernels.h"
+
+namespace b200exl3 {
+
+namespace {
+
+constexpr int kWarpsPerBlock = 8;
+
+__device__ __forceinline__ int expert_of(const uint32_t* selected, int64_t slot, int experts) {
+    return min(static_cast<int>(selected[slot]), experts - 1);      // an out-of-range id must not read out of bounds
+}
+
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+routed_prepare_kernel(const void* __restrict__ x, int x_dtype, const __half* __restrict__ suh,
+                      const uint32_t* __restrict__ selected, int experts, int top_k, int proj, int64_t slots, int in,
+                      __half* __restrict__ xhat) {
+    const int lane = threadIdx.x & 31;
+    const int blocks_per_row = in >> 7;
+    const int64_t total = slots * proj * blocks_per_row;
+    for (int64_t unit = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5); unit < total;
+         unit += static_cast<int64_t>(gridDim.x) * kWarpsPerBlock) {
+        const int64_t out_row = unit / blocks_per_row;                   // slot * proj + projection
+        const int col = static_cast<int>(unit % blocks_per_row) * 128 + lane * 4;
+        const int64_t slot = out_row / proj;
+        const int p = static_cast<int>(out_row - slot * proj);
+        const int64_t token = slot / top_k;
+        const __half* s = suh + (static_cast<int64_t>(expert_of(selected, slot, experts)) * proj + p) * in + col;
+        __align__(8) __half h[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) h[j] = __hmul_rn(load_as_half(x, x_dtype, token * in + col + j), s[j]);
+        warp_hadamard128_f16(h, lane);
+        *reinterpret_cast<uint2*>(xhat + out_row * in + col) = *reinterpret_cast<uint2*>(h);
+    }
+}
+
+// The exponential is evaluated in fp32 (expf); the reference's Metal `exp` is a fast-math intrinsic whose
+// last bits are not specified, so this glue is compared with a tolerance.
+__device__ __forceinline__ float silu(float v) { return __fdiv_rn(v, __fadd_rn(1.0f, expf(-v))); }
+
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+glu_down_input_kernel(const float* __restrict__ ygu, const __half* __restrict__ gu_svh, const __half* __restrict__ down_suh,
+                      const uint32_t* __restrict__ selected, int experts, int64_t slots, int hidden, int logical_hidden,
+                      __half* __restrict__ xhat) {
+    const int lane = threadIdx.x & 31;
+    const int blocks_per_row = hidden >> 7;
+    const int64_t total = slots * blocks_per_row;
+    const float scale = had_scale();
+    for (int64_t unit = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5); unit < total;
+         unit += static_cast<int64_t>(gridDim.x) * kWarpsPerBlock) {
+        const int64_t slot = unit / blocks_per_row;
+        const int col = static_cast<int>(unit % blocks_per_row) * 128 + lane * 4;
+        const int64_t expert = expert_of(selected, slot, experts);
+        const float4 graw = *reinterpret_cast<const float4*>(ygu + (slot * 2) * hidden + col);
+        const float4 uraw = *reinterpret_cast<const float4*>(ygu + (slot * 2 + 1) * hidden + col);
+        float gv[4] = {round_half(graw.x), round_half(graw.y), round_half(graw.z), round_half(graw.w)};
+        float uv[4] = {round_half(uraw.x), round_half(uraw.y), round_half(uraw.z), round_half(uraw.w)};
+        warp_hadamard128<false, false>(gv, lane);
+        warp_hadamard128<false, false>(uv, lane);
+        const __half* sg = gu_svh + (expert * 2) * hidden + col;
+        const __half* su = gu_svh + (expert * 2 + 1) * hidden + col;
+        const __half* sd = down_suh + expert * hidden + col;
+        float d[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float gate = round_half(__fmul_rn(__fmul_rn(gv[j], scale), __half2float(sg[j])));
+            const float up = round_half(__fmul_rn(__fmul_rn(uv[j], scale), __half2float(su[j])));
+            float act = round_half(__fmul_rn(silu(gate), up));
+            if (col + j >= logical_hidden) act = 0.0f;
+            d[j] = round_half(__fmul_rn(act, __half2float(sd[j])));
+        }
+        warp_hadamard128<false, false>(d, lane);
+        __align__(8) __half h[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) h[j] = __float2half_rn(__fmul_rn(d[j], scale));
+        *reinterpret_cast<uint2*>(xhat + slot * hidden + col) = *reinterpret_cast<uint2*>(h);
+    }
+}
+
+template <bool F32>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+finish_and_reduce_kernel(const float* __restrict__ raw, const __half* __restrict__ down_svh,
+                         const uint32_t* __restrict__ selected, int experts, const void* __restrict__ scores,
+                         int64_t rows, int top_k, int out, void* __restrict__ y) {
+    const int lane = threadIdx.x & 31;
+    const int blocks_per_row = out >> 7;
+    const int64_t total = rows * blocks_per_row;
+    for (int64_t unit = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5); unit < total;
+         unit += static_cast<int64_t>(gridDim.x) * kWarpsPerBlock) {
+        const int64_t row = unit / blocks_per_row;
+        const int col = static_cast<int>(unit % blocks_per_row) * 128 + lane * 4;
+        float acc32[4] = {0.f, 0.f, 0.f, 0.f};
+        __half acc16[4];
+        for (int t = 0; t < top_k; ++t) {
+            const int64_t slot = row * top_k + t;
+            const float4 r = *reinterpret_cast<const float4*>(raw + slot * out + col);
+            __half h[4] = {__float2half_rn(r.x), __float2half_rn(r.y), __float2half_rn(r.z), __float2half_rn(r.w)};
+            warp_hadamard128_f16(h, lane);
+            const __half* sv = down_svh + static_cast<int64_t>(expert_of(selected, slot, experts)) * out + col;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const __half scaled = __hmul_rn(h[j], sv[j]);
+                if (F32) {
+                    // fp16 product promoted to the fp32 routing weight; the sum over slots stays in fp32
+                    const float v = __fmul_rn(__half2float(scaled), reinterpret_cast<const float*>(scores)[slot]);
+                    acc32[j] = t == 0 ? v : __fadd_rn(acc32[j], v);
+                } else {
+                    const __half v = __hmul_rn(scaled, reinterpret_cast<const __half*>(scores)[slot]);
+                    acc16[j] = t == 0 ? v : __hadd_rn(acc16[j], v);
+                }
+            }
+        }
+        if (F32) *reinterpret_cast<float4*>(reinterpret_cast<float*>(y) + row * out + col) = make_float4(acc32[0], acc32[1], acc32[2], acc32[3]);
+        else *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(y) + row * out + col) = *reinterpret_cast<uint2*>(acc16);
+    }
+}
+
+unsigned grid_for(int64_t units) {
+    const int64_t blocks = (units + kWarpsPerBlock - 1) / kWarpsPerBlock;
+    const int64_t cap = static_cast<int64_t>(kSmCount) * 8;
+    return static_cast<unsigned>(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
+}
+
+}  // namespace
+
+cudaError_t launch_routed_prepare(const void* x, int x_dtype, const __half* suh, const uint32_t* selected, int experts,
+                                  int top_k, int proj, int64_t slots, int in, __half* xhat, cudaStream_t stream) {
+    if (slots == 0) return cudaSuccess;
+    routed_prepare_kernel<<<grid_for(slots * proj * (in / 128)), kWarpsPerBlock * 32, 0, stream>>>(
+        x, x_dtype, suh, selected, experts, top_k, proj, slots, in, xhat);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_glu_down_input(const float* ygu, const __half* gu_svh, const __half* down_suh, const uint32_t* selected,
+                                  int experts, int64_t slots, int hidden, int logical_hidden, __half* xhat,
+                                  cudaStream_t stream) {
+    if (slots == 0) return cudaSuccess;
+    glu_down_input_kernel<<<grid_for(slots * (hidden / 128)), kWarpsPerBlock * 32, 0, stream>>>(
+        ygu, gu_svh, down_suh, selected, experts, slots, hidden, logical_hidden, xhat);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_finish_and_reduce(const float* raw, const __half* down_svh, const uint32_t* selected, int experts,
+                                     const void* scores, int score_dtype, int64_t rows, int top_k, int out, void* y,
+                                     cudaStream_t stream) {
+    if (rows == 0) return cudaSuccess;
+    const unsigned grid = grid_for(rows * (out / 128));
+    if (score_dtype == kF32)
+        finish_and_reduce_kernel<true><<<grid, kWarpsPerBlock * 32, 0, stream>>>(raw, down_svh, selected, experts, scores,
+                                                                                 rows, top_k, out, y);
+    else
+        finish_and_reduce_kernel<false><<<grid, kWarpsPerBlock * 32, 0, stream>>>(raw, down_svh, selected, experts, scores,
+                                                                                  rows, top_k, out, y);
+    return cudaGetLastError();
+}
+
+}  // namespace b200exl3

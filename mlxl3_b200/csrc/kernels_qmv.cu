@@ -73,7 +73,7 @@ size_t qmv_partial_bytes(const QmvPlan& plan, int out, int64_t rows) {
 cudaError_t launch_qmv(QmvArgs args, int k, int cb, bool exact, const QmvPlan& plan, cudaStream_t stream) {
     if (args.rows <= 0 || args.rows > kQmvMaxRows) return cudaErrorInvalidValue;
     args.tiles_k = args.in / 16;
-    args.tiles_n = args.out / 16;
+    if (args.map_selected == nullptr) args.tiles_n = args.out / 16;   // the expert-mapped caller gives the bank's width
     args.max_pieces = plan.max_pieces;
     args.trace = g_trace;
     args.warp_smem = plan.warp_smem;

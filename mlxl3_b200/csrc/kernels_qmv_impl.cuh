@@ -272,11 +272,19 @@ qmv_kernel(const QmvArgs p) {
         const int u0 = max(w0, cblock * UB) - cblock * UB;
         const int u1 = min(w1, (cblock + 1) * UB) - cblock * UB;
         float* stage = reinterpret_cast<float*>(mine + p.stage_offset) + (cblock - w0 / UB) * stage_floats;
-        const int grp = qmv_group_of(p, cblock);
+        int grp = qmv_group_of(p, cblock);
+        int tn0 = cblock * 8;                               // first tile column of the block in the weight array
+        if (p.map_selected != nullptr) {
+            // expert-mapped: virtual block -> (slot, projection, block of the expert's columns)
+            const int sp = cblock / p.map_blocks, j = cblock - sp * p.map_blocks;
+            const int slot = sp / p.map_proj, proj = sp - slot * p.map_proj;
+            const int expert = min(static_cast<int>(p.map_selected[slot]), p.map_experts - 1);
+            tn0 = (proj * p.map_stride_blocks + expert * p.map_blocks + j) * 8;
+            grp = sp;                                       // row of the rotated activations (stride: one row)
+        }
         {
             const int tk_first = u0 >> 3, tk_last = (u1 - 1) >> 3;
             const int lo_first = u0 & 7, hi_last = ((u1 - 1) & 7) + 1;
-            const int tn0 = cblock * 8;
 
             float acc[8][NB][4];
 #pragma unroll

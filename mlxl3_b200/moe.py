@@ -1,0 +1,102 @@
+"""Host-side mirror of the reference's grouped-expert SwiGLU block ``Exl3SwitchGlu``
+(native/src/moe.rs:808-971) over the C ABI (``b200exl3_moe_*``)."""
+from __future__ import annotations
+
+from ctypes import byref, c_size_t, c_void_p
+
+import numpy as np
+
+from . import _lib
+from ._lib import B200Exl3Error, F16, F32
+from .linear import DEFAULT, MCG, MUL1, dtype_code, _np_dtype, new_workspace
+from .runtime import DEFAULT_STREAM, DeviceBuffer, Stream
+
+
+class Exl3SwitchGlu:
+    """``Exl3SwitchGlu(gu_trellis, gu_suh, gu_svh, down_trellis, down_suh, down_svh, top_k, k, cb)`` with the
+    shapes ``Exl3SwitchGlu::new`` checks (native/src/moe.rs:808-905): ``gu_suh [experts, 2, in]``,
+    ``gu_svh [experts, 2, hidden]``, ``down_suh [experts, hidden]``, ``down_svh [experts, in]``,
+    ``gu_trellis [in/16, experts*hidden/8, 16k]`` (gate columns of all experts, then up columns),
+    ``down_trellis [hidden/16, experts*in/16, 16k]``.  ``forward(x, selected, scores)`` takes ``x [rows, in]``,
+    ``selected [rows, top_k]`` uint32 and ``scores [rows, top_k]`` (f16 or f32) and returns ``[rows, in]`` in the
+    dtype of ``scores``."""
+
+    def __init__(self, gu_trellis, gu_suh, gu_svh, down_trellis, down_suh, down_svh, top_k: int, k: int,
+                 cb: int = DEFAULT, *, scale_dtype: int | None = None, exact_weights: bool = False):
+        gu_suh, gu_svh = np.asarray(gu_suh), np.asarray(gu_svh)
+        down_suh, down_svh = np.asarray(down_suh), np.asarray(down_svh)
+        gu_trellis, down_trellis = np.asarray(gu_trellis), np.asarray(down_trellis)
+        if gu_suh.ndim != 3:
+            raise B200Exl3Error("gate/up input scales must have rank 3")
+        if gu_svh.ndim != 3:
+            raise B200Exl3Error("gate/up output scales must have rank 3")
+        experts, projections, n_in = gu_suh.shape
+        hidden = gu_svh.shape[2]
+        if (not 1 <= k <= 8 or k == 7 or cb not in (DEFAULT, MCG, MUL1) or experts <= 0 or top_k <= 0 or top_k > experts
+                or n_in <= 0 or hidden <= 0 or n_in % 128 or hidden % 128):
+            raise B200Exl3Error("invalid or overflowing SwitchGLU dimensions")
+        if projections != 2 or gu_svh.shape[:2] != (experts, 2):
+            raise B200Exl3Error("invalid SwitchGLU dimensions")
+        if (down_suh.shape != (experts, hidden) or down_svh.shape != (experts, n_in)
+                or gu_trellis.shape != (n_in // 16, experts * hidden // 8, 16 * k)
+                or down_trellis.shape != (hidden // 16, experts * n_in // 16, 16 * k)):
+            raise B200Exl3Error("SwitchGLU trellis/scales disagree")
+        if any(t.dtype not in (np.uint16, np.int16) for t in (gu_trellis, down_trellis)):
+            raise B200Exl3Error("expert trellis must contain 16-bit integers")
+        code = dtype_code(gu_suh, scale_dtype)
+        cast = _np_dtype(code)
+        self.experts, self.input, self.hidden, self.top_k, self.k, self.cb = experts, n_in, hidden, top_k, k, cb
+        bufs = [DeviceBuffer.from_numpy(a) for a in (
+            gu_trellis.view(np.uint16), gu_suh.astype(cast, copy=False), gu_svh.astype(cast, copy=False),
+            down_trellis.view(np.uint16), down_suh.astype(cast, copy=False), down_svh.astype(cast, copy=False))]
+        handle = c_void_p()
+        _lib.call("b200exl3_moe_create", *(c_void_p(b.ptr) for b in bufs), code, experts, n_in, hidden, top_k, k, cb,
+                  _lib.EXACT_WEIGHTS if exact_weights else 0, byref(handle))
+        self.handle = handle.value
+        self._workspace: DeviceBuffer | None = None
+
+    def workspace_bytes(self, rows: int) -> int:
+        out = c_size_t()
+        _lib.call("b200exl3_moe_workspace_bytes", c_void_p(self.handle), rows, byref(out))
+        return out.value
+
+    def forward_device(self, d_x: int, x_dtype: int, rows: int, d_selected: int, d_scores: int, score_dtype: int, d_y: int,
+                       workspace: DeviceBuffer, stream: Stream = DEFAULT_STREAM) -> None:
+        _lib.call("b200exl3_moe_forward", c_void_p(self.handle), c_void_p(d_x), x_dtype, rows, c_void_p(d_selected),
+                  c_void_p(d_scores), score_dtype, c_void_p(d_y), c_void_p(workspace.ptr), workspace.nbytes,
+                  c_void_p(stream.handle))
+
+    def forward(self, x: np.ndarray, selected: np.ndarray, scores: np.ndarray, dtype: int | None = None,
+                stream: Stream = DEFAULT_STREAM) -> np.ndarray:
+        """``Exl3SwitchGlu::forward`` (native/src/moe.rs:905-971) with host arrays in and out."""
+        x, selected, scores = np.asarray(x), np.asarray(selected), np.asarray(scores)
+        if x.ndim != 2:
+            raise B200Exl3Error("SwitchGLU input must have rank 2")
+        rows = x.shape[0]
+        if (rows <= 0 or x.shape[1] != self.input or selected.shape != (rows, self.top_k)
+                or scores.shape != (rows, self.top_k)):
+            raise B200Exl3Error("invalid SwitchGLU input/routes")
+        if scores.dtype not in (np.float16, np.float32):
+            raise B200Exl3Error("routing weights must be float16 or float32")
+        score_code = F16 if scores.dtype == np.float16 else F32
+        d_x = DeviceBuffer.from_numpy(x, stream)
+        d_sel = DeviceBuffer.from_numpy(selected.astype(np.uint32, copy=False), stream)
+        d_scores = DeviceBuffer.from_numpy(scores, stream)
+        d_y = DeviceBuffer(rows * self.input * scores.dtype.itemsize)
+        need = self.workspace_bytes(rows)
+        if self._workspace is None or self._workspace.nbytes < need:
+            self._workspace = new_workspace(need)
+        self.forward_device(d_x.ptr, dtype_code(x, dtype), rows, d_sel.ptr, d_scores.ptr, score_code, d_y.ptr,
+                            self._workspace, stream)
+        return d_y.download((rows, self.input), scores.dtype, stream)
+
+    def close(self) -> None:
+        if getattr(self, "handle", None):
+            _lib.load().b200exl3_moe_free(c_void_p(self.handle))
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -223,3 +223,31 @@ def finish_and_reduce(down_raw, down_svh, scores, top_k: int) -> np.ndarray:
     if lib().exl3o_finish_and_reduce(_ptr(d), _ptr(s), _ptr(w), rows, top_k, n, _ptr(out)):
         raise ValueError("finish_and_reduce: bad arguments")
     return out.view(np.float16)
+
+
+def switch_glu_forward(gu_trellis, gu_suh, gu_svh, down_trellis, down_suh, down_svh, top_k: int, k: int, cb: int,
+                       x: np.ndarray, selected, scores, x_dtype: int | None = None) -> np.ndarray:
+    """``Exl3SwitchGlu::forward`` for SiLU models (native/src/moe.rs:905-971), one slot at a time: routed input
+    rotation (moe.rs:184-236), gate and up products on the expert's columns of the bank (gate columns of all
+    experts, then up columns: native/src/linear.rs:2817-2885), ``glu_down_input``, down product,
+    ``finish_and_reduce``.  ``scores`` fp16; result fp16 ``[rows, in]``."""
+    gu_t, down_t = _u16(gu_trellis), _u16(down_trellis)
+    gu_suh, gu_svh = np.asarray(gu_suh, np.float16), np.asarray(gu_svh, np.float16)
+    down_suh, down_svh = np.asarray(down_suh, np.float16), np.asarray(down_svh, np.float16)
+    experts, _, n_in = gu_suh.shape
+    hidden = gu_svh.shape[2]
+    sel = np.asarray(selected).reshape(-1)
+    rows = x.shape[0]
+    ht, it = hidden // 16, n_in // 16
+    down_raw = np.empty((rows * top_k, n_in), np.float32)
+    for slot, e in enumerate(sel):
+        e = int(e)
+        xr = x[slot // top_k: slot // top_k + 1]
+        raw = []
+        for p in range(2):
+            xhat = prepare(xr, gu_suh[e, p], x_dtype)
+            c0 = p * experts * ht + e * ht
+            raw.append(matmul_raw(np.ascontiguousarray(gu_t[:, c0:c0 + ht]), k, cb, xhat))
+        xd = glu_down_input(raw[0], raw[1], gu_svh[e, 0][None], gu_svh[e, 1][None], down_suh[e][None])
+        down_raw[slot] = matmul_raw(np.ascontiguousarray(down_t[:, e * it:(e + 1) * it]), k, cb, xd)[0]
+    return finish_and_reduce(down_raw, down_svh[sel], np.asarray(scores, np.float16), top_k)

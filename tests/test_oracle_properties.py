@@ -88,3 +88,32 @@ def test_linear_forward_dtypes_and_bias():
     parts = oracle.matmul_raw(trellis, k, cb, xh, (0, 3)) + oracle.matmul_raw(trellis, k, cb, xh, (3, 8))
     exact = oracle.matmul_raw(trellis, k, cb, xh, f64acc=True)
     assert np.abs(full - exact).max() < 1e-4 and np.abs(parts - exact).max() < 1e-4
+
+
+def test_switch_glu_oracle_reduces_to_one_expert_chain():
+    """With top_k = 1 and weight 1 the grouped block equals the chain written out for that expert
+    (native/src/moe.rs:905-971), and a slot's result does not depend on the other rows."""
+    rng = np.random.default_rng(31)
+    experts, n_in, hidden, k, cb = 3, 128, 256, 3, 1
+    gu_t = rng.integers(0, 65536, (n_in // 16, experts * hidden // 8, 16 * k), dtype=np.uint16)
+    down_t = rng.integers(0, 65536, (hidden // 16, experts * n_in // 16, 16 * k), dtype=np.uint16)
+    sign = lambda *s: np.where(rng.random(s) > 0.5, -1, 1).astype(np.float16)  # noqa: E731
+    gu_suh, down_suh = sign(experts, 2, n_in), sign(experts, hidden)
+    gu_svh = (sign(experts, 2, hidden).astype(np.float32) / np.sqrt(n_in)).astype(np.float16)
+    down_svh = (sign(experts, n_in).astype(np.float32) / np.sqrt(hidden)).astype(np.float16)
+    x = rng.standard_normal((2, n_in)).astype(np.float16)
+    selected = np.array([[2], [0]], np.uint32)
+    ones = np.ones((2, 1), np.float16)
+    got = oracle.switch_glu_forward(gu_t, gu_suh, gu_svh, down_t, down_suh, down_svh, 1, k, cb, x, selected, ones)
+    ht, it = hidden // 16, n_in // 16
+    for row, e in enumerate((2, 0)):
+        xr = x[row:row + 1]
+        gate = oracle.matmul_raw(np.ascontiguousarray(gu_t[:, e * ht:(e + 1) * ht]), k, cb, oracle.prepare(xr, gu_suh[e, 0]))
+        up = oracle.matmul_raw(np.ascontiguousarray(gu_t[:, (experts + e) * ht:(experts + e + 1) * ht]), k, cb,
+                               oracle.prepare(xr, gu_suh[e, 1]))
+        xd = oracle.glu_down_input(gate, up, gu_svh[e, 0][None], gu_svh[e, 1][None], down_suh[e][None])
+        down = oracle.matmul_raw(np.ascontiguousarray(down_t[:, e * it:(e + 1) * it]), k, cb, xd)
+        want = oracle.finish(down, down_svh[e])          # weight 1: the plain output rotation
+        assert np.array_equal(got[row].view(np.uint16), want[0].view(np.uint16))
+    alone = oracle.switch_glu_forward(gu_t, gu_suh, gu_svh, down_t, down_suh, down_svh, 1, k, cb, x[1:], selected[1:], ones[1:])
+    assert np.array_equal(alone.view(np.uint16), got[1:].view(np.uint16))
