@@ -106,13 +106,8 @@ class ClockSampler:
 # ------------------------------------------------------------------------------------------------ ours
 
 def shard(kind: str, n_in: int, n_out: int, world: int) -> tuple[int, int]:
-    if world == 1:
-        return n_in, n_out
-    if kind == "col":
-        assert n_out % (128 * world) == 0
-        return n_in, n_out // world
-    assert n_in % (128 * world) == 0
-    return n_in // world, n_out
+    from mlxl3_b200 import tp
+    return tp.shard_dims(kind, n_in, n_out, world)
 
 
 def run_ours(args) -> dict:
