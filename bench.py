@@ -16,8 +16,9 @@ Metric: effective HBM GB/s = algorithmic bytes / device time, where the algorith
 projection are in*out*K/8 (trellis) + 2*(in+out) (sign vectors) + 2*M*(in+out) (x read, y write).
 
 With N > 1 (launched under torch.distributed.run) every projection is tensor-parallel: q/k/v/gate/up
-are split by output columns, o/down by input rows with an all-reduce of the fp32 partial sums, and
-the total work is fixed (strong scaling).
+are split by output columns, o/down by input rows with a sum of the fp32 partial products across ranks, and
+the total work is fixed (strong scaling).  The sum over ranks and the output rotation of a row-parallel
+projection are one kernel over peer memory (NVLink), so a step stays a single graph replay on every rank.
 
 ``--impl reference`` times the CPU oracle (the C restatement of the reference's arithmetic) on the
 host cores, on a bounded sample of the same workload.
@@ -156,12 +157,20 @@ def run_ours(args) -> dict:
     y_host = PinnedBuffer((rows, layers[-1][2][0]), np.float16)
     ws = ex.new_workspace(max(l[3].workspace_bytes(rows) for l in layers))
 
+    stream = Stream()
+    tp_ctx = None
     if world > 1:
-        import torch
-        stream = Stream(handle=torch.cuda.current_stream().cuda_stream)
-        yhat = {n: torch.empty((rows, n), dtype=torch.float32, device="cuda") for n in {o for l in layers for o in l[2]}}
-    else:
-        stream = Stream()
+        # row-parallel layers exchange their fp32 partial sums through peer memory inside one kernel
+        # (b200exl3_linear_finish_tp); torch.distributed only carries the IPC handles, the barriers and the timing
+        from mlxl3_b200.tp import TpContext
+
+        def exchange(raw: bytes) -> list:
+            gathered = [None] * world
+            dist.all_gather_object(gathered, raw)
+            return gathered
+        widths = {o for l in layers if l[0] == "row" for o in l[2]}
+        tp_ctx = TpContext(rank, world, rows * max(widths) // 128, exchange)
+        yhat = {n: DeviceBuffer(rows * n * 4) for n in widths}
 
     from ctypes import c_void_p
     from mlxl3_b200 import _lib
@@ -173,11 +182,10 @@ def run_ours(args) -> dict:
     def launch_all() -> None:
         for kind, s_in, s_outs, op in layers:
             if world > 1 and kind == "row":
-                # row-parallel: fp32 partial sums -> all-reduce over NVLink -> output rotation
+                # row-parallel: fp32 partial sums -> sum over peer memory + output rotation in one kernel
                 buf = yhat[s_outs[0]]
-                op.forward_partial_device(d_x[s_in].ptr, ex.F16, rows, buf.data_ptr(), ws, stream)
-                dist.all_reduce(buf)
-                op.finish_device(buf.data_ptr(), rows, ex.F16, d_y[s_outs[0]][0].ptr, stream)
+                op.forward_partial_device(d_x[s_in].ptr, ex.F16, rows, buf.ptr, ws, stream)
+                tp_ctx.finish(op, buf.ptr, rows, ex.F16, d_y[s_outs[0]][0].ptr, stream)
             elif len(s_outs) > 1:
                 op.forward_device(d_x[s_in].ptr, ex.F16, rows, [d_y[o][i].ptr for i, o in enumerate(s_outs)], ws, stream)
             else:
@@ -222,20 +230,23 @@ def run_ours(args) -> dict:
             ms = float(t.item())
         return ms
 
-    if world == 1 and not args.no_graph:
+    barrier()                                        # all ranks start the first exchange together
+    if not args.no_graph:
         # one decode step = one graph replay: the 128 launches are recorded once (the reference's
         # engine does the same with its graph replay, native/ffi/mlx_bridge.cpp:150-175)
         launch_all()
-        stream.sync()
+        barrier()
         with Graph.record(stream) as graph:
             launch_all()
+        barrier()
 
     sampler = ClockSampler(local_rank) if rank == 0 else None
     ms_device = timed(host_io=False)
     clocks = sampler.stop() if sampler else None
     ms_e2e = timed(host_io=True)
 
-    launches_per_step = len(layers)                  # one fused kernel per projection
+    # one fused kernel per projection, plus the exchange kernel of every row-parallel projection when sharded
+    launches_per_step = len(layers) + (sum(1 for l in layers if l[0] == "row") if world > 1 else 0)
     ms_per_step = ms_device / args.steps
     value = total_bytes / (ms_per_step * 1e-3) / 1e9
     e2e_value = total_bytes / (ms_e2e / args.steps * 1e-3) / 1e9
@@ -261,6 +272,12 @@ def run_ours(args) -> dict:
     }
     if rank == 0 and world == 1:
         result["cpu_baseline"] = cpu_baseline(budget_s=12.0)
+    if tp_ctx is not None:
+        status = tp_ctx.status()
+        barrier()
+        tp_ctx.close()
+        if status:
+            raise SystemExit(f"rank {rank}: tensor-parallel exchange reported status {status}")
     if dist is not None:
         dist.destroy_process_group()
     return result if rank == 0 else {}

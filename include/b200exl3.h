@@ -220,6 +220,30 @@ int b200exl3_moe_forward(const b200exl3_moe* handle, const void* d_x, int x_dtyp
                          const uint32_t* d_selected, const void* d_scores, int score_dtype, void* d_y,
                          void* d_workspace, size_t workspace_bytes, b200exl3_stream stream);
 
+/* ---- tensor parallelism over peer memory (one process per GPU of one node) -----------------------------------
+ * No counterpart in the reference (single GPU).  Column-parallel shards need nothing from here.  A row-parallel
+ * shard computes its fp32 partial product with b200exl3_linear_forward_partial; b200exl3_linear_finish_tp then
+ * replaces "all-reduce + b200exl3_linear_finish" by one kernel: every rank stores its partial sums into all
+ * ranks' exchange buffers over NVLink, waits (bounded, about four seconds) for the other ranks' sums, adds them
+ * in rank order in fp32 (the reference's split-K sum, native/src/linear.rs:978-982; every rank gets the same
+ * bits) and applies the output rotation.  It is a plain kernel launch: it can be recorded into a graph.
+ *
+ * Set-up: every rank calls b200exl3_tp_alloc (buffer + 64-byte IPC handle), the host exchanges the handles by
+ * its own means, opens the other ranks' buffers with b200exl3_tp_open, and passes all `world` buffers (its own
+ * at index `rank`) to b200exl3_tp_create.  max_units bounds rows * out / 128 of any layer finished through the
+ * context.  All ranks must issue the same sequence of b200exl3_linear_finish_tp calls.  A wait that gives up
+ * sets the context's status to 4 (b200exl3_tp_status) instead of hanging. */
+typedef struct b200exl3_tp b200exl3_tp;
+int b200exl3_tp_buffer_bytes(int world, int max_units, size_t* out_bytes);
+int b200exl3_tp_alloc(int world, int max_units, void** out_buffer, unsigned char* out_handle64);
+int b200exl3_tp_open(const unsigned char* handle64, void** out_peer_buffer);
+int b200exl3_tp_close(void* peer_buffer);
+int b200exl3_tp_create(int rank, int world, int max_units, void* const* buffers, b200exl3_tp** out);
+void b200exl3_tp_free(b200exl3_tp* handle);
+int b200exl3_tp_status(const b200exl3_tp* handle, int* out_status);
+int b200exl3_linear_finish_tp(const b200exl3_linear* handle, b200exl3_tp* tp, const float* d_yhat, int64_t rows,
+                              int y_dtype, void* d_y, b200exl3_stream stream);
+
 #ifdef __cplusplus
 }
 #endif

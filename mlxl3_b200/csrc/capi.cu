@@ -78,6 +78,14 @@ struct LayerCore {
 struct b200exl3_linear { LayerCore c; };
 struct b200exl3_group { LayerCore c; };
 
+// Peer-memory context of one tensor-parallel rank: every rank's exchange buffer ([flags | inbox]) mapped into
+// this process, and this rank's per-unit use counts.
+struct b200exl3_tp {
+    int rank, world, max_units;
+    void* buffers[kTpMaxWorld];
+    unsigned int* done;      // [max_units] + one status word
+};
+
 // Grouped experts of a SwiGLU block: two banks in the quad layout (gate columns of all experts, then up
 // columns of all experts; down columns of all experts) and the per-expert scales.
 struct b200exl3_moe {
@@ -742,6 +750,106 @@ int b200exl3_moe_forward(const b200exl3_moe* h, const void* d_x, int x_dtype, in
                  "expert reduction");
     }
     return 0;
+}
+
+
+/* ---- tensor parallelism over peer memory ------------------------------------------------------------ */
+
+static size_t tp_flag_bytes(int world, int max_units) { return round256(static_cast<size_t>(world) * max_units * sizeof(unsigned int)); }
+
+int b200exl3_tp_buffer_bytes(int world, int max_units, size_t* out_bytes) {
+    if (!out_bytes) return fail("NULL argument");
+    if (world < 1 || world > kTpMaxWorld || max_units < 1) return fail("invalid tensor-parallel geometry");
+    *out_bytes = tp_flag_bytes(world, max_units) + static_cast<size_t>(2) * world * max_units * 128 * sizeof(float);
+    return 0;
+}
+
+int b200exl3_tp_alloc(int world, int max_units, void** out_buffer, unsigned char* out_handle64) {
+    if (!out_buffer || !out_handle64) return fail("NULL argument");
+    *out_buffer = nullptr;
+    size_t bytes = 0;
+    if (b200exl3_tp_buffer_bytes(world, max_units, &bytes)) return -1;
+    void* p = nullptr;
+    B200_TRY(cudaMalloc(&p, bytes), "cudaMalloc(exchange buffer)");
+    cudaIpcMemHandle_t handle;
+    if (check(cudaMemset(p, 0, bytes), "clear exchange buffer") || check(cudaDeviceSynchronize(), "clear exchange buffer") ||
+        check(cudaIpcGetMemHandle(&handle, p), "cudaIpcGetMemHandle")) {
+        cudaFree(p);
+        return -1;
+    }
+    static_assert(sizeof(handle) == 64, "IPC handle size");
+    memcpy(out_handle64, &handle, sizeof handle);
+    *out_buffer = p;
+    return 0;
+}
+
+int b200exl3_tp_open(const unsigned char* handle64, void** out_peer) {
+    if (!handle64 || !out_peer) return fail("NULL argument");
+    cudaIpcMemHandle_t handle;
+    memcpy(&handle, handle64, sizeof handle);
+    return check(cudaIpcOpenMemHandle(out_peer, handle, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle");
+}
+
+int b200exl3_tp_close(void* peer) { return peer ? check(cudaIpcCloseMemHandle(peer), "cudaIpcCloseMemHandle") : 0; }
+
+int b200exl3_tp_create(int rank, int world, int max_units, void* const* buffers, b200exl3_tp** out_handle) {
+    if (!out_handle) return fail("out pointer is NULL");
+    *out_handle = nullptr;
+    if (world < 1 || world > kTpMaxWorld || rank < 0 || rank >= world || max_units < 1)
+        return fail("invalid tensor-parallel geometry");
+    if (!buffers) return fail("NULL argument");
+    for (int r = 0; r < world; ++r)
+        if (!buffers[r] || !aligned16(buffers[r])) return fail("exchange buffer of rank %d is NULL or misaligned", r);
+    b200exl3_tp* h = new (std::nothrow) b200exl3_tp{};
+    if (!h) return fail("out of host memory");
+    h->rank = rank; h->world = world; h->max_units = max_units;
+    for (int r = 0; r < world; ++r) h->buffers[r] = buffers[r];
+    const size_t bytes = (static_cast<size_t>(max_units) + 1) * sizeof(unsigned int);
+    if (check(cudaMalloc(&h->done, bytes), "cudaMalloc(use counts)") || check(cudaMemset(h->done, 0, bytes), "clear use counts") ||
+        check(cudaDeviceSynchronize(), "tp_create")) {
+        cudaFree(h->done);
+        delete h;
+        return -1;
+    }
+    *out_handle = h;
+    return 0;
+}
+
+void b200exl3_tp_free(b200exl3_tp* h) {
+    if (!h) return;
+    cudaFree(h->done);
+    delete h;
+}
+
+int b200exl3_tp_status(const b200exl3_tp* h, int* out_status) {
+    if (!h || !out_status) return fail("NULL argument");
+    unsigned int flag = 0;
+    B200_TRY(cudaMemcpy(&flag, h->done + h->max_units, sizeof flag, cudaMemcpyDeviceToHost), "read status");
+    *out_status = static_cast<int>(flag);
+    return 0;
+}
+
+int b200exl3_linear_finish_tp(const b200exl3_linear* h, b200exl3_tp* tp, const float* d_yhat, int64_t rows, int y_dtype,
+                              void* d_y, b200exl3_stream s) {
+    if (!h || !tp) return fail("NULL handle");
+    if (rows <= 0) return fail("EXL3 linear input cannot be empty");
+    if (!dtype_is_float(y_dtype)) return fail("unsupported output dtype %d", y_dtype);
+    if (!d_yhat || !d_y) return fail("NULL buffer");
+    if (!aligned16(d_yhat)) return fail("device pointers must be 16-byte aligned");
+    const int64_t units = rows * (h->c.out / 128);
+    if (units > tp->max_units) return fail("%lld units exceed the exchange buffers' %d", static_cast<long long>(units), tp->max_units);
+    TpArgs a{};
+    a.yhat = d_yhat;
+    for (int r = 0; r < tp->world; ++r) {
+        a.flags[r] = static_cast<unsigned int*>(tp->buffers[r]);
+        a.inbox[r] = reinterpret_cast<float*>(static_cast<char*>(tp->buffers[r]) + tp_flag_bytes(tp->world, tp->max_units));
+    }
+    a.done = tp->done;
+    a.error = tp->done + tp->max_units;
+    a.svh = h->c.svh; a.bias = h->c.bias; a.y = d_y;
+    a.rank = tp->rank; a.world = tp->world; a.max_units = tp->max_units;
+    a.rows = static_cast<int>(rows); a.out = h->c.out; a.y_dtype = y_dtype;
+    return check(launch_tp_finish(a, as_stream(s)), "tensor-parallel finish kernel");
 }
 
 

@@ -103,6 +103,21 @@ cudaError_t launch_finish_and_reduce(const float* raw, const __half* down_svh, c
                                      const void* scores, int score_dtype, int64_t rows, int top_k, int out, void* y,
                                      cudaStream_t stream);
 
+// ---- row-parallel sum over peer memory + output rotation (kernels_tp.cu) -----------------------------------
+constexpr int kTpMaxWorld = 8;
+struct TpArgs {
+    const float* yhat;               // [rows, out] this rank's fp32 partial product
+    float* inbox[kTpMaxWorld];       // every rank's inbox [2, world, max_units, 128] (own one at [rank])
+    unsigned int* flags[kTpMaxWorld];// every rank's arrival flags [world, max_units]
+    unsigned int* done;              // [max_units] uses completed by this rank
+    unsigned int* error;             // status word: 4 = a peer's data never arrived
+    const __half* svh;               // [out]
+    const __half* bias;              // [out] or nullptr
+    void* y;                         // [rows, out] in y_dtype
+    int rank, world, max_units, rows, out, y_dtype;
+};
+cudaError_t launch_tp_finish(const TpArgs& args, cudaStream_t stream);
+
 // ---- tensor-core product for many rows (kernels_qmm.cu) ---------------------------------------------------
 struct QmmPlan {
     int splits;        // CTAs that share one (128 columns x 256 tokens) output tile along the input axis

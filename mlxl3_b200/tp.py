@@ -48,3 +48,69 @@ def row_shard(trellis: np.ndarray, suh: np.ndarray, svh: np.ndarray, bias: np.nd
     s_in, _ = shard_dims("row", n_in, n_out, world)
     lo, hi = rank * s_in, (rank + 1) * s_in
     return (np.ascontiguousarray(trellis[lo // 16:hi // 16]), np.ascontiguousarray(suh[lo:hi]), svh, bias), slice(lo, hi)
+
+
+class TpContext:
+    """Peer-memory exchange buffers of one rank (``b200exl3_tp_*``).
+
+    ``exchange`` is a callable that takes this rank's 64-byte handle and returns the list of all ranks'
+    handles in rank order (for example ``torch.distributed.all_gather_object``); the library itself has no
+    communication layer.  ``finish(layer, d_yhat, rows, dtype, d_y, stream)`` then replaces the all-reduce and
+    the output rotation of a row-parallel layer by one kernel launch.
+    """
+
+    def __init__(self, rank: int, world: int, max_units: int, exchange):
+        import ctypes
+        from ctypes import byref, c_void_p
+
+        from . import _lib
+        self.rank, self.world, self.max_units = rank, world, max_units
+        own = c_void_p()
+        handle = ctypes.create_string_buffer(64)
+        _lib.call("b200exl3_tp_alloc", world, max_units, byref(own), handle)
+        self._own = own.value
+        handles = exchange(handle.raw)
+        if len(handles) != world or handles[rank] != handle.raw:
+            raise ValueError("exchange must return every rank's handle in rank order")
+        self._peers = []
+        pointers = (c_void_p * world)()
+        for r, raw in enumerate(handles):
+            if r == rank:
+                pointers[r] = self._own
+                continue
+            peer = c_void_p()
+            _lib.call("b200exl3_tp_open", raw, byref(peer))
+            self._peers.append(peer.value)
+            pointers[r] = peer.value
+        ctx = c_void_p()
+        _lib.call("b200exl3_tp_create", rank, world, max_units, pointers, byref(ctx))
+        self.handle = ctx.value
+
+    def finish(self, layer, d_yhat: int, rows: int, dtype: int, d_y: int, stream) -> None:
+        from ctypes import c_void_p
+
+        from . import _lib
+        _lib.call("b200exl3_linear_finish_tp", c_void_p(layer.handle), c_void_p(self.handle), c_void_p(d_yhat), rows, dtype,
+                  c_void_p(d_y), c_void_p(stream.handle))
+
+    def status(self) -> int:
+        from ctypes import byref, c_int, c_void_p
+
+        from . import _lib
+        out = c_int()
+        _lib.call("b200exl3_tp_status", c_void_p(self.handle), byref(out))
+        return out.value
+
+    def close(self) -> None:
+        """Call on every rank after all ranks have finished using the buffers."""
+        from ctypes import c_void_p
+
+        from . import _lib
+        if getattr(self, "handle", None):
+            _lib.load().b200exl3_tp_free(c_void_p(self.handle))
+            self.handle = None
+            for peer in self._peers:
+                _lib.load().b200exl3_tp_close(c_void_p(peer))
+            self._peers = []
+            _lib.load().b200exl3_free(c_void_p(self._own))
+            self._own = None
