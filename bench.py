@@ -18,7 +18,8 @@ projection are in*out*K/8 (trellis) + 2*(in+out) (sign vectors) + 2*M*(in+out) (
 With N > 1 (launched under torch.distributed.run) every projection is tensor-parallel: q/k/v/gate/up
 are split by output columns, o/down by input rows with a sum of the fp32 partial products across ranks, and
 the total work is fixed (strong scaling).  The sum over ranks and the output rotation of a row-parallel
-projection are one kernel over peer memory (NVLink), so a step stays a single graph replay on every rank.
+projection happen inside the projection's own kernel, over peer memory (NVLink), so a step stays a single
+graph replay of 128 launches on every rank.
 
 ``--impl reference`` times the CPU oracle (the C restatement of the reference's arithmetic) on the
 host cores, on a bounded sample of the same workload.
@@ -182,10 +183,13 @@ def run_ours(args) -> dict:
     def launch_all() -> None:
         for kind, s_in, s_outs, op in layers:
             if world > 1 and kind == "row":
-                # row-parallel: fp32 partial sums -> sum over peer memory + output rotation in one kernel
-                buf = yhat[s_outs[0]]
-                op.forward_partial_device(d_x[s_in].ptr, ex.F16, rows, buf.ptr, ws, stream)
-                tp_ctx.finish(op, buf.ptr, rows, ex.F16, d_y[s_outs[0]][0].ptr, stream)
+                # row-parallel: the kernel's final reduction also adds the other ranks' partial sums (peer memory)
+                if args.unfused_exchange:
+                    buf = yhat[s_outs[0]]
+                    op.forward_partial_device(d_x[s_in].ptr, ex.F16, rows, buf.ptr, ws, stream)
+                    tp_ctx.finish(op, buf.ptr, rows, ex.F16, d_y[s_outs[0]][0].ptr, stream)
+                else:
+                    tp_ctx.forward(op, d_x[s_in].ptr, ex.F16, rows, d_y[s_outs[0]][0].ptr, ws, stream)
             elif len(s_outs) > 1:
                 op.forward_device(d_x[s_in].ptr, ex.F16, rows, [d_y[o][i].ptr for i, o in enumerate(s_outs)], ws, stream)
             else:
@@ -246,7 +250,7 @@ def run_ours(args) -> dict:
     ms_e2e = timed(host_io=True)
 
     # one fused kernel per projection, plus the exchange kernel of every row-parallel projection when sharded
-    launches_per_step = len(layers) + (sum(1 for l in layers if l[0] == "row") if world > 1 else 0)
+    launches_per_step = len(layers) + (sum(1 for l in layers if l[0] == "row") if world > 1 and args.unfused_exchange else 0)
     ms_per_step = ms_device / args.steps
     value = total_bytes / (ms_per_step * 1e-3) / 1e9
     e2e_value = total_bytes / (ms_e2e / args.steps * 1e-3) / 1e9
@@ -330,6 +334,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying a graph")
+    ap.add_argument("--unfused-exchange", action="store_true",
+                    help="N > 1: run the sum over ranks as its own kernel after the product instead of inside it")
     ap.add_argument("--pdl", type=int, default=1, help="programmatic dependent launch between layers (0/1)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

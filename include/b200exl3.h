@@ -241,6 +241,13 @@ int b200exl3_tp_close(void* peer_buffer);
 int b200exl3_tp_create(int rank, int world, int max_units, void* const* buffers, b200exl3_tp** out);
 void b200exl3_tp_free(b200exl3_tp* handle);
 int b200exl3_tp_status(const b200exl3_tp* handle, int* out_status);
+/* The whole row-parallel layer in one launch: input rotation of this rank's input slice, product, exchange of
+ * the partial sums with the other ranks inside the kernel's final reduction, output rotation.  Same result as
+ * b200exl3_linear_forward_partial followed by b200exl3_linear_finish_tp.  Batches of more than 16 rows run as
+ * several launches. */
+int b200exl3_linear_forward_tp(const b200exl3_linear* handle, b200exl3_tp* tp, const void* d_x, int x_dtype,
+                               int64_t rows, void* d_y, void* d_workspace, size_t workspace_bytes,
+                               b200exl3_stream stream);
 int b200exl3_linear_finish_tp(const b200exl3_linear* handle, b200exl3_tp* tp, const float* d_yhat, int64_t rows,
                               int y_dtype, void* d_y, b200exl3_stream stream);
 

@@ -74,6 +74,7 @@ SIGNATURES = {
     "b200exl3_tp_create": (c_int, [c_int, c_int, c_int, POINTER(c_void_p), POINTER(c_void_p)]),
     "b200exl3_tp_free": (None, [c_void_p]),
     "b200exl3_tp_status": (c_int, [c_void_p, POINTER(c_int)]),
+    "b200exl3_linear_forward_tp": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_size_t, c_void_p]),
     "b200exl3_linear_finish_tp": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p]),
     "b200exl3_moe_create": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                     c_int, c_int, c_int, c_uint32, POINTER(c_void_p)]),

@@ -358,8 +358,11 @@ int b200exl3_linear_workspace_bytes(const b200exl3_linear* h, int64_t rows, size
 
 // One fused launch per batch of up to kMaxBatchRows rows.  Exactly one of d_x / d_xhat is given;
 // ys (one pointer per group) selects the rotated output, otherwise the summed fp32 product goes to d_yhat.
+static TpPeers tp_peers(const b200exl3_tp* tp);
+
 static int forward_common(const LayerCore& c, const void* d_x, int x_dtype, const uint16_t* d_xhat, int64_t rows,
-                          void* const* ys, float* d_yhat, void* ws, size_t ws_bytes, cudaStream_t stream) {
+                          void* const* ys, float* d_yhat, void* ws, size_t ws_bytes, cudaStream_t stream,
+                          const b200exl3_tp* tp = nullptr) {
     if (rows <= 0) return fail("EXL3 linear input cannot be empty");
     size_t need = 0;
     if (core_workspace_bytes(c, rows, &need)) return -1;
@@ -369,7 +372,7 @@ static int forward_common(const LayerCore& c, const void* d_x, int x_dtype, cons
     const bool exact = (c.flags & B200EXL3_EXACT_WEIGHTS) != 0;
     const size_t x_size = dtype_size(x_dtype);
     const __half* xhat = reinterpret_cast<const __half*>(d_xhat);
-    if (rows >= kQmmMinRows && c.groups == 1 && ys && !d_xhat && g_qmm_enabled) {
+    if (rows >= kQmmMinRows && c.groups == 1 && ys && !d_xhat && g_qmm_enabled && !tp) {
         // many rows: input rotation -> tensor-core product (fp32 partials per input split) -> output rotation
         __half* buf = reinterpret_cast<__half*>(base + kCounterBytes);
         float* partials = reinterpret_cast<float*>(base + kCounterBytes + round256(static_cast<size_t>(rows) * c.in * sizeof(__half)));
@@ -414,6 +417,7 @@ static int forward_common(const LayerCore& c, const void* d_x, int x_dtype, cons
         a.x_dtype = x_dtype;
         a.y_dtype = x_dtype;
         a.in = c.in; a.out = c.out; a.rows = static_cast<int>(n);
+        if (tp) { a.tp = tp_peers(tp); a.tp_row0 = static_cast<int>(r0); }
         B200_TRY(launch_qmv(a, c.k, c.cb, exact, plan, stream), "fused linear kernel");
     }
     return 0;
@@ -829,6 +833,17 @@ int b200exl3_tp_status(const b200exl3_tp* h, int* out_status) {
     return 0;
 }
 
+int b200exl3_linear_forward_tp(const b200exl3_linear* h, b200exl3_tp* tp, const void* d_x, int x_dtype, int64_t rows, void* d_y,
+                              void* ws, size_t ws_bytes, b200exl3_stream s) {
+    if (!h || !tp) return fail("NULL handle");
+    if (!dtype_is_float(x_dtype)) return fail("unsupported input dtype %d", x_dtype);
+    if (!d_x || !d_y) return fail("NULL buffer");
+    if (rows > 0 && rows * (h->c.out / 128) > tp->max_units)
+        return fail("%lld units exceed the exchange buffers' %d", static_cast<long long>(rows * (h->c.out / 128)), tp->max_units);
+    void* ys[1] = {d_y};
+    return forward_common(h->c, d_x, x_dtype, nullptr, rows, ys, nullptr, ws, ws_bytes, as_stream(s), tp);
+}
+
 int b200exl3_linear_finish_tp(const b200exl3_linear* h, b200exl3_tp* tp, const float* d_yhat, int64_t rows, int y_dtype,
                               void* d_y, b200exl3_stream s) {
     if (!h || !tp) return fail("NULL handle");
@@ -840,17 +855,24 @@ int b200exl3_linear_finish_tp(const b200exl3_linear* h, b200exl3_tp* tp, const f
     if (units > tp->max_units) return fail("%lld units exceed the exchange buffers' %d", static_cast<long long>(units), tp->max_units);
     TpArgs a{};
     a.yhat = d_yhat;
-    for (int r = 0; r < tp->world; ++r) {
-        a.flags[r] = static_cast<unsigned int*>(tp->buffers[r]);
-        a.inbox[r] = reinterpret_cast<float*>(static_cast<char*>(tp->buffers[r]) + tp_flag_bytes(tp->world, tp->max_units));
-    }
-    a.done = tp->done;
-    a.error = tp->done + tp->max_units;
+    a.peers = tp_peers(tp);
     a.svh = h->c.svh; a.bias = h->c.bias; a.y = d_y;
-    a.rank = tp->rank; a.world = tp->world; a.max_units = tp->max_units;
     a.rows = static_cast<int>(rows); a.out = h->c.out; a.y_dtype = y_dtype;
     return check(launch_tp_finish(a, as_stream(s)), "tensor-parallel finish kernel");
 }
 
 
 }  // extern "C"
+
+static TpPeers tp_peers(const b200exl3_tp* tp) {
+    TpPeers t{};
+    for (int r = 0; r < tp->world; ++r) {
+        t.flags[r] = static_cast<unsigned int*>(tp->buffers[r]);
+        t.inbox[r] = reinterpret_cast<float*>(static_cast<char*>(tp->buffers[r]) + tp_flag_bytes(tp->world, tp->max_units));
+    }
+    t.done = tp->done;
+    t.error = tp->done + tp->max_units;
+    t.rank = tp->rank; t.world = tp->world; t.max_units = tp->max_units;
+    return t;
+}
+

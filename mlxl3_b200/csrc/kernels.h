@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "tp_exchange.cuh"
+
 namespace b200exl3 {
 
 // ---- codec (kernels_codec.cu) ---------------------------------------------------------------------
@@ -64,6 +66,10 @@ struct QmvArgs {
     // and multiplies them with its own rotated activations xhat[s * map_proj + projection, :].
     const uint32_t* map_selected;
     int map_blocks, map_proj, map_stride_blocks, map_experts;
+    // Tensor-parallel row shard (tp.world > 0; rotated output): the complete sum of a column block is
+    // exchanged with the other ranks (unit = (tp_row0 + row) * out/128 + block) before the output rotation.
+    TpPeers tp;
+    int tp_row0;
 };
 
 struct QmvPlan {
@@ -104,17 +110,13 @@ cudaError_t launch_finish_and_reduce(const float* raw, const __half* down_svh, c
                                      cudaStream_t stream);
 
 // ---- row-parallel sum over peer memory + output rotation (kernels_tp.cu) -----------------------------------
-constexpr int kTpMaxWorld = 8;
 struct TpArgs {
     const float* yhat;               // [rows, out] this rank's fp32 partial product
-    float* inbox[kTpMaxWorld];       // every rank's inbox [2, world, max_units, 128] (own one at [rank])
-    unsigned int* flags[kTpMaxWorld];// every rank's arrival flags [world, max_units]
-    unsigned int* done;              // [max_units] uses completed by this rank
-    unsigned int* error;             // status word: 4 = a peer's data never arrived
+    TpPeers peers;
     const __half* svh;               // [out]
     const __half* bias;              // [out] or nullptr
     void* y;                         // [rows, out] in y_dtype
-    int rank, world, max_units, rows, out, y_dtype;
+    int rows, out, y_dtype;
 };
 cudaError_t launch_tp_finish(const TpArgs& args, cudaStream_t stream);
 

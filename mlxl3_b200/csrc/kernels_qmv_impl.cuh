@@ -190,6 +190,8 @@ __device__ __forceinline__ void qmv_finish_block(const QmvArgs& p, int cblock, u
             if (p.yhat != nullptr) {
                 *reinterpret_cast<float4*>(p.yhat + static_cast<int64_t>(row) * p.out + col) = a;
             } else {
+                // a row shard of a tensor-parallel layer first adds the other ranks' sums for this block
+                if (p.tp.world > 0) a = tp_exchange_unit(p.tp, (p.tp_row0 + row) * (p.out >> 7) + cblock, a, lane);
                 __half h[4] = {__float2half_rn(a.x), __float2half_rn(a.y), __float2half_rn(a.z), __float2half_rn(a.w)};
                 warp_hadamard128_f16(h, lane);
                 __align__(8) __half sv[4];

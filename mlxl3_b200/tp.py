@@ -93,6 +93,15 @@ class TpContext:
         _lib.call("b200exl3_linear_finish_tp", c_void_p(layer.handle), c_void_p(self.handle), c_void_p(d_yhat), rows, dtype,
                   c_void_p(d_y), c_void_p(stream.handle))
 
+    def forward(self, layer, d_x: int, dtype: int, rows: int, d_y: int, workspace, stream) -> None:
+        """The whole row-parallel layer in one launch (``b200exl3_linear_forward_tp``): ``d_x`` is this rank's
+        slice of the input columns, ``d_y`` receives the full-width output, identical on every rank."""
+        from ctypes import c_void_p
+
+        from . import _lib
+        _lib.call("b200exl3_linear_forward_tp", c_void_p(layer.handle), c_void_p(self.handle), c_void_p(d_x), dtype, rows,
+                  c_void_p(d_y), c_void_p(workspace.ptr), workspace.nbytes, c_void_p(stream.handle))
+
     def status(self) -> int:
         from ctypes import byref, c_int, c_void_p
 

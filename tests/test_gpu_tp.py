@@ -49,6 +49,15 @@ def test_world_of_one_equals_plain_finish(gpu):
         ctx.finish(layer, d_yhat.ptr, rows, gpu.F16, d_y.ptr, stream)
         got = d_y.download((rows, N_OUT), np.float16, stream)
         assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+    # the fused form (exchange inside the layer kernel) gives the same bits as the plain forward
+    layer.forward_device(d_x.ptr, gpu.F16, rows, d_ref.ptr, ws, stream)
+    want = d_ref.download((rows, N_OUT), np.float16, stream)
+    for _ in range(3):
+        d_y.fill(0, stream)
+        ctx.forward(layer, d_x.ptr, gpu.F16, rows, d_y.ptr, ws, stream)
+        got = d_y.download((rows, N_OUT), np.float16, stream)
+        assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+    assert gpu.workspace_status(ws) == 0
     assert ctx.status() == 0
     with pytest.raises(gpu.B200Exl3Error, match="exceed the exchange buffers"):
         small = TpContext(0, 1, 2, lambda raw: [raw])
@@ -87,6 +96,10 @@ def _rank(rank, world, port, out):
             ctx.finish(layer, d_yhat.ptr, rows, ex.F16, d_y.ptr, stream)
             results.append(d_y.download((rows, N_OUT), np.float16, stream))
         partial = d_yhat.download((rows, N_OUT), np.float32, stream)
+        for _ in range(3):                               # the same layer with the exchange inside its kernel
+            d_y.fill(0, stream)
+            ctx.forward(layer, d_x.ptr, ex.F16, rows, d_y.ptr, ws, stream)
+            results.append(d_y.download((rows, N_OUT), np.float16, stream))
         # column-parallel shard of the same layer: no exchange
         tc, c_in, c_out, cb_ = tp.column_shard(trellis, suh, svh, bias, rank, world)
         col_layer = ex.Exl3Linear(tc, c_in, c_out, cb_, K, CB, exact_weights=True)
