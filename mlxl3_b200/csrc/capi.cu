@@ -378,10 +378,16 @@ static int forward_common(const LayerCore& c, const void* d_x, int x_dtype, cons
         float* partials = reinterpret_cast<float*>(base + kCounterBytes + round256(static_cast<size_t>(rows) * c.in * sizeof(__half)));
         const QmmPlan qp = plan_qmm(c.in, c.out, rows);
         B200_TRY(launch_prepare(d_x, x_dtype, c.suh, 1, rows, c.in, buf, stream), "prepare");
-        B200_TRY(launch_qmm(c.wq, c.in, c.out, c.k, c.cb, buf, rows, qp, partials,
-                            reinterpret_cast<unsigned int*>(base + kCounterBytes - sizeof(unsigned int)), stream),
-                 "tensor-core product kernel");
-        B200_TRY(launch_finish(partials, qp.splits, rows * c.out, c.svh, 1, c.bias, rows, c.out, x_dtype, ys[0], stream), "finish");
+        unsigned int* status = reinterpret_cast<unsigned int*>(base + kCounterBytes - sizeof(unsigned int));
+        if (qp.splits == 1) {
+            // one CTA holds the whole input range of its columns: the output rotation runs in its epilogue
+            B200_TRY(launch_qmm(c.wq, c.in, c.out, c.k, c.cb, buf, rows, qp, partials, status, c.svh, c.bias, ys[0], x_dtype, stream),
+                     "tensor-core product kernel");
+        } else {
+            B200_TRY(launch_qmm(c.wq, c.in, c.out, c.k, c.cb, buf, rows, qp, partials, status, nullptr, nullptr, nullptr, 0, stream),
+                     "tensor-core product kernel");
+            B200_TRY(launch_finish(partials, qp.splits, rows * c.out, c.svh, 1, c.bias, rows, c.out, x_dtype, ys[0], stream), "finish");
+        }
         return 0;
     }
     if (!xhat && rows > kQmvFusedRows) {

@@ -127,9 +127,12 @@ struct QmmPlan {
 };
 QmmPlan plan_qmm(int in, int out, int64_t rows);
 size_t qmm_partial_bytes(const QmmPlan& plan, int out, int64_t rows);
-// partials[s, r, n] (fp32) = sum over the inputs of split s of xhat[r, :] (fp16, rotated) x W[:, n]
+// partials[s, r, n] (fp32) = sum over the inputs of split s of xhat[r, :] (fp16, rotated) x W[:, n]; with one
+// split and y != nullptr the output rotation (half -> H128 -> * svh, + bias) is applied in the kernel's epilogue
+// and y[r, n] is stored in y_dtype instead.
 cudaError_t launch_qmm(const uint32_t* wq, int in, int out, int k, int cb, const __half* xhat, int64_t rows,
-                       const QmmPlan& plan, float* partials, unsigned int* error, cudaStream_t stream);
+                       const QmmPlan& plan, float* partials, unsigned int* error, const __half* svh, const __half* bias,
+                       void* y, int y_dtype, cudaStream_t stream);
 void qmm_set_tuning(int splits);   // force the number of input splits (0 = automatic)
 
 // ---- weight layout (kernels_codec.cu) -----------------------------------------------------------------

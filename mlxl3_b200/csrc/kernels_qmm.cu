@@ -29,6 +29,7 @@
 #include <algorithm>
 
 #include "kernels.h"
+#include "hadamard.cuh"
 #include "tile_decode.cuh"
 
 namespace b200exl3 {
@@ -59,6 +60,10 @@ struct QmmArgs {
     unsigned int* error;
     int in, out, rows, tiles_n, splits, stages_total;   // stages_total = in / 64
     unsigned long long* trace;   // optional [CTA, 8] nanosecond stamps of the phases
+    const __half* svh;           // fused output rotation (y != nullptr; one input split): [out]
+    const __half* bias;          // [out] or nullptr
+    void* y;                     // [rows, out] in y_dtype, or nullptr: store fp32 partial products
+    int y_dtype;
 };
 
 __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_byte_addr) {
@@ -331,17 +336,50 @@ qmm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUt
         float* dst = p.partials + (static_cast<int64_t>(split) * p.rows) * p.out + col;
         const int c_span = static_cast<int>(tmem_cols) / (kDecoders / 4);
         const int c_begin = cpart * c_span, c_end = c_begin + c_span;
-        for (int c = c_begin; c < c_end; c += 32) {
-            if (tok0 + c >= p.rows) break;
-            uint32_t r[32];
-            if (nst > 0) tmem_ld32(tmem + (static_cast<uint32_t>(lq * 32) << 16) + c, r);
-            else
+        if (p.y == nullptr) {
+            for (int c = c_begin; c < c_end; c += 32) {
+                if (tok0 + c >= p.rows) break;
+                uint32_t r[32];
+                if (nst > 0) tmem_ld32(tmem + (static_cast<uint32_t>(lq * 32) << 16) + c, r);
+                else
 #pragma unroll
-                for (int i = 0; i < 32; ++i) r[i] = 0;
+                    for (int i = 0; i < 32; ++i) r[i] = 0;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                const int tok = tok0 + c + i;
-                if (tok < p.rows) dst[static_cast<int64_t>(tok) * p.out] = __uint_as_float(r[i]);
+                for (int i = 0; i < 32; ++i) {
+                    const int tok = tok0 + c + i;
+                    if (tok < p.rows) dst[static_cast<int64_t>(tok) * p.out] = __uint_as_float(r[i]);
+                }
+            }
+        } else {
+            // Output rotation fused (one input split only): the four warps that share a range of token
+            // columns transpose 32 tokens x 128 outputs through shared memory (the operand rings are free
+            // once the accumulator is complete), then every warp rotates eight token rows:
+            // half(sum) -> H128 -> * svh (+ bias), stored in the caller's dtype.
+            __half* stage_base = reinterpret_cast<__half*>(b_base) + cpart * (2 * 32 * 128);
+            const __half* sv = p.svh + cblock * 128 + lane * 4;
+            const __half* bias = p.bias ? p.bias + cblock * 128 : nullptr;
+            int buf = 0;
+            for (int c = c_begin; c < c_end; c += 32) {
+                if (tok0 + c >= p.rows) break;
+                uint32_t r[32];
+                tmem_ld32(tmem + (static_cast<uint32_t>(lq * 32) << 16) + c, r);
+                __half* stage = stage_base + buf * (32 * 128);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) stage[i * 128 + lq * 32 + lane] = __float2half_rn(__uint_as_float(r[i]));
+                asm volatile("bar.sync %0, %1;" ::"r"(1 + cpart), "r"(128) : "memory");
+#pragma unroll 1
+                for (int j = 0; j < 8; ++j) {
+                    const int t = lq * 8 + j, tok = tok0 + c + t;
+                    if (tok >= p.rows) break;
+                    __align__(8) __half h[4];
+                    *reinterpret_cast<uint2*>(h) = *reinterpret_cast<const uint2*>(stage + t * 128 + lane * 4);
+                    warp_hadamard128_f16(h, lane);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        store_from_half(p.y, p.y_dtype, static_cast<int64_t>(tok) * p.out + cblock * 128 + lane * 4 + e,
+                                        __hmul_rn(h[e], sv[e]), bias, lane * 4 + e);
+                }
+                buf ^= 1;
             }
         }
     }
@@ -410,14 +448,15 @@ QmmPlan plan_qmm(int in, int out, int64_t rows) {
     const int max_splits = std::max(1, stages_total / 8);     // every split keeps at least 8 stages
     if (g_qmm_splits) { plan.splits = std::min(g_qmm_splits, max_splits); return plan; }
     // One CTA per SM (the operand rings take most of the shared memory).  Estimated time of a choice:
-    // waves x (stages per CTA + fixed prologue/epilogue) + the fp32 partials every extra split writes and
-    // the output rotation reads back.
+    // waves x (stages per CTA + fixed prologue/epilogue) + the fp32 partials that several splits write and
+    // the separate output rotation reads back.
     const double stage_us = rows > kTokHalf ? 0.6 : 0.35, fixed_us = 4.0;
     const double partial_us = static_cast<double>(rows) * out * 8.0 / 8.0e6;
     double best = 0;
     for (int s = 1; s <= max_splits; ++s) {
         const int64_t waves = (base * s + kSmCount - 1) / kSmCount;
-        const double t = waves * (((stages_total + s - 1) / s) * stage_us + fixed_us) + (s - 1) * partial_us;
+        // with one split the output rotation runs in the epilogue; more splits write fp32 partials and add a launch
+        const double t = waves * (((stages_total + s - 1) / s) * stage_us + fixed_us) + (s > 1 ? s * partial_us + 5.0 : 0.0);
         if (s == 1 || t < best) { best = t; plan.splits = s; }
     }
     return plan;
@@ -428,8 +467,10 @@ size_t qmm_partial_bytes(const QmmPlan& plan, int out, int64_t rows) {
 }
 
 cudaError_t launch_qmm(const uint32_t* wq, int in, int out, int k, int cb, const __half* xhat, int64_t rows,
-                       const QmmPlan& plan, float* partials, unsigned int* error, cudaStream_t stream) {
+                       const QmmPlan& plan, float* partials, unsigned int* error, const __half* svh, const __half* bias,
+                       void* y, int y_dtype, cudaStream_t stream) {
     if (in % 128 || out % 128 || rows <= 0) return cudaErrorInvalidValue;
+    if (y != nullptr && plan.splits != 1) return cudaErrorInvalidValue;     // the fused rotation needs the complete sum
     EncodeFn encode = encode_fn();
     if (!encode) return cudaErrorNotSupported;
     // rotated activations [rows, in] fp16 as a 2-D tensor: boxes of 64 inputs x 256 tokens, 128-byte swizzle
@@ -454,6 +495,7 @@ cudaError_t launch_qmm(const uint32_t* wq, int in, int out, int k, int cb, const
         return cudaErrorInvalidValue;
     QmmArgs p{};
     p.wq = wq; p.partials = partials; p.error = error;
+    p.svh = svh; p.bias = bias; p.y = y; p.y_dtype = y_dtype;
     p.in = in; p.out = out; p.rows = static_cast<int>(rows); p.tiles_n = out / 16;
     p.splits = plan.splits; p.stages_total = in / 64; p.trace = g_qmm_trace;
     const dim3 grid(static_cast<unsigned>((out / 128) * plan.splits), static_cast<unsigned>(plan.token_tiles));

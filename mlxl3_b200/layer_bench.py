@@ -29,7 +29,12 @@ def main(argv=None) -> None:
     ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE", help="b200exl3_set_option before the run")
     ap.add_argument("--no-graph", action="store_true", help="launch every call from the host instead of replaying a graph")
     ap.add_argument("--device", type=int, default=0)
+    ap.add_argument("--experts", type=int, default=0,
+                    help="> 0: time the grouped-expert SwiGLU block instead (--in = model width, --out = expert width)")
+    ap.add_argument("--top-k", type=int, default=8)
     args = ap.parse_args(argv)
+    if args.experts > 0:
+        return moe_main(args)
 
     init(args.device)
     for item in args.option:
@@ -74,6 +79,66 @@ def main(argv=None) -> None:
         "us_per_forward": round(ms * 1e3, 2),
         "weight_GBps": round(weight_bytes / ms / 1e6, 1),
         "TFLOPs": round(2.0 * args.rows * args.n_in * args.n_out / ms / 1e9, 1),
+    }))
+
+
+def moe_main(args) -> None:
+    """``Exl3SwitchGlu.forward`` on random banks: every token picks ``top_k`` distinct experts at random."""
+    from . import Exl3SwitchGlu
+
+    init(args.device)
+    for item in args.option:
+        name, value = item.split("=")
+        set_option(name, int(value))
+    rng = np.random.default_rng(0)
+    e, n_in, hidden, k = args.experts, args.n_in, args.n_out, args.k
+    gu = rng.integers(0, 65536, (n_in // 16, e * hidden // 8, 16 * k), dtype=np.uint16)
+    down = rng.integers(0, 65536, (hidden // 16, e * n_in // 16, 16 * k), dtype=np.uint16)
+    ones = lambda *shape: np.ones(shape, np.float16)  # noqa: E731
+    block = Exl3SwitchGlu(gu, ones(e, 2, n_in), ones(e, 2, hidden) / np.float16(64), down, ones(e, hidden),
+                          ones(e, n_in) / np.float16(32), args.top_k, k, args.cb, exact_weights=args.exact)
+    rows = args.rows
+    x = rng.standard_normal((rows, n_in)).astype(np.float16)
+    selected = np.stack([rng.permutation(e)[:args.top_k] for _ in range(rows)]).astype(np.uint32)
+    scores = np.full((rows, args.top_k), 1.0 / args.top_k, np.float16)
+    stream = Stream()
+    d_x, d_sel, d_sc = (DeviceBuffer.from_numpy(a, stream) for a in (x, selected, scores))
+    d_y = DeviceBuffer(rows * n_in * 2)
+    ws = new_workspace(block.workspace_bytes(rows))
+
+    def call() -> None:
+        block.forward_device(d_x.ptr, F16, rows, d_sel.ptr, d_sc.ptr, F16, d_y.ptr, ws, stream)
+    for _ in range(args.warmup):
+        call()
+    stream.sync()
+    start, stop = Event(), Event()
+    if args.no_graph:
+        start.record(stream)
+        for _ in range(args.iters):
+            call()
+        stop.record(stream)
+    else:
+        with Graph.record(stream) as graph:
+            for _ in range(args.iters):
+                call()
+        graph.launch(stream)
+        stream.sync()
+        start.record(stream)
+        graph.launch(stream)
+        stop.record(stream)
+    stream.sync()
+    ms = start.elapsed_ms(stop) / max(args.iters, 1)
+    status = workspace_status(ws)
+    if status:
+        raise SystemExit(f"kernel reported status {status}")
+    # bytes of the expert columns a call touches at least once (distinct experts), and the reads it issues
+    distinct = len(np.unique(selected))
+    per_expert = 3 * n_in * hidden * k / 8
+    print(json.dumps({
+        "experts": e, "top_k": args.top_k, "in": n_in, "hidden": hidden, "k": k, "cb": args.cb, "rows": rows,
+        "us_per_forward": round(ms * 1e3, 2),
+        "routed_weight_GBps": round(rows * args.top_k * per_expert / ms / 1e6, 1),
+        "distinct_expert_GBps": round(distinct * per_expert / ms / 1e6, 1),
     }))
 
 
