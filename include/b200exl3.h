@@ -59,7 +59,8 @@ int b200exl3_version(void);
  * start, activations visible, rotated, main loop done, warps joined, reduced, finished; 0 = off), "qmm" (0 = batches
  * of more than 16 rows also go through the small-batch kernel instead of the tensor-core product; default 1),
  * "qmm_splits" (input splits of the tensor-core product, 0 = chosen by a cost model; set it before asking for
- * workspace sizes), "qmm_trace_buffer" (device address of a uint64 [CTAs, 8] array that receives nanosecond
+ * workspace sizes), "moe_sorted" (0 = the expert block runs one row per slot for any batch instead of grouping
+ * slots by expert for larger batches; set it before asking for workspace sizes), "qmm_trace_buffer" (device address of a uint64 [CTAs, 8] array that receives nanosecond
  * stamps of the tensor-core kernel's phases: start, set up, decoders done, MMAs issued, accumulator ready,
  * epilogue done, end, activation copies issued; 0 = off). */
 int b200exl3_set_option(const char* name, int64_t value);
@@ -214,8 +215,11 @@ int b200exl3_moe_workspace_bytes(const b200exl3_moe* handle, int64_t rows, size_
 /* x [rows, in] in x_dtype; selected [rows, top_k] expert ids (u32; ids past the bank are clamped to the last
  * expert instead of reading out of bounds); scores [rows, top_k] routing weights in score_dtype (fp16 = 9 or
  * fp32 = 10); y [rows, in] in score_dtype (the reference's result dtype: fp16 products promoted by the scores).
- * Every (token, choice) slot runs as one activation row against its expert's columns; rows are processed in
- * passes of at most 256 slots.  The workspace follows the rules of the linear layer's workspace. */
+ * Small batches run one activation row per (token, choice) slot against the slot's expert's columns.  From 33
+ * slots and three slots per expert on, the slots are grouped by expert on the device (the reference's route_plan, native/src/moe.rs:66-182) into
+ * segments of 16 rows, so that an expert's columns are decoded once per 16 rows that use them; rows are
+ * processed in passes of at most 16384 slots.  No host synchronisation either way.
+ * The workspace follows the rules of the linear layer's workspace. */
 int b200exl3_moe_forward(const b200exl3_moe* handle, const void* d_x, int x_dtype, int64_t rows,
                          const uint32_t* d_selected, const void* d_scores, int score_dtype, void* d_y,
                          void* d_workspace, size_t workspace_bytes, b200exl3_stream stream);

@@ -56,6 +56,7 @@ int valid_format(int k, int cb) {
     return 0;
 }
 
+bool g_moe_sorted = true;                                // "moe_sorted" option: 0 keeps one row per slot for any batch
 bool g_qmm_enabled = true;                               // "qmm" option: 0 sends every batch through the fused kernel
 constexpr int kMaxBatchRows = kQmvMaxRows;              // rows handled by one launch of the fused kernel
 constexpr size_t kCounterBytes = B200EXL3_WORKSPACE_HEADER_BYTES;   // arrival counters at the head of a workspace
@@ -131,6 +132,7 @@ int b200exl3_set_option(const char* name, int64_t value) {
     else if (!strcmp(name, "pdl")) pdl = static_cast<int>(value);
     else if (!strcmp(name, "qmm")) { g_qmm_enabled = value != 0; return 0; }
     else if (!strcmp(name, "qmm_trace_buffer")) { b200exl3::g_qmm_trace = reinterpret_cast<unsigned long long*>(value); return 0; }
+    else if (!strcmp(name, "moe_sorted")) { g_moe_sorted = value != 0; return 0; }
     else if (!strcmp(name, "qmm_splits")) { qmm_set_tuning(static_cast<int>(value)); return 0; }
     else if (!strcmp(name, "qmv_trace_buffer")) {
         qmv_set_trace(reinterpret_cast<unsigned long long*>(static_cast<uintptr_t>(value)));
@@ -650,6 +652,61 @@ static MoeLayout moe_layout(const b200exl3_moe* h, int64_t rows) {
     return l;
 }
 
+// Expert-sorted form, used from this many slots on: slots are grouped by expert into segments of 16 rows, so an
+// expert's columns are decoded once per 16 rows that use them instead of once per slot.
+constexpr int64_t kMoeSortedMinSlots = 33;
+constexpr int kMoeSegRows = 16;
+
+static int64_t moe_max_segments(const b200exl3_moe* h, int64_t slots) {
+    return std::min<int64_t>(h->experts, slots) + slots / kMoeSegRows;   // one partly filled segment per expert at most
+}
+// rows per pass (bounds the scratch); the passes of a call get equal shares
+constexpr int64_t kMoeSortedPassSlots = 16384;
+static int64_t moe_sorted_chunk_rows(const b200exl3_moe* h, int64_t rows) {
+    const int64_t cap = std::max<int64_t>(1, kMoeSortedPassSlots / h->top_k);
+    const int64_t passes = (rows + cap - 1) / cap;
+    return (rows + passes - 1) / passes;
+}
+
+struct MoeSortedLayout {
+    size_t counters, counter_bytes, seg_count, seg_expert, row_slot, slot_row, xgu, ygu, xdown, ydown, partials, total;
+    int max_segments;
+    QmvPlan gu_plan, down_plan;
+};
+
+static MoeSortedLayout moe_sorted_layout(const b200exl3_moe* h, int64_t rows) {
+    MoeSortedLayout l{};
+    const int64_t slots = moe_sorted_chunk_rows(h, rows) * h->top_k;
+    const int64_t segs = moe_max_segments(h, slots);
+    l.max_segments = static_cast<int>(segs);
+    l.gu_plan = plan_qmv(h->in, static_cast<int>(segs * 2 * h->hidden), h->k, kMoeSegRows);
+    l.down_plan = plan_qmv(h->hidden, static_cast<int>(segs * h->in), h->k, kMoeSegRows);
+    size_t at = kCounterBytes;
+    // arrival counters of its own (one per virtual column block; the header's 16 KiB would cap a pass at 4093 blocks),
+    // cleared at the start of every call
+    l.counter_bytes = round256((static_cast<size_t>(segs) * moe_blocks_per_slot(h->in, h->hidden) + 2) * sizeof(unsigned int));
+    l.counters = at; at += l.counter_bytes;
+    l.seg_count = at; at += 256;
+    l.seg_expert = at; at += round256(static_cast<size_t>(segs) * sizeof(uint32_t));
+    l.row_slot = at; at += round256(static_cast<size_t>(segs) * kMoeSegRows * sizeof(uint32_t));
+    l.slot_row = at; at += round256(static_cast<size_t>(slots) * sizeof(uint32_t));
+    l.xgu = at; at += round256(static_cast<size_t>(segs) * 2 * kMoeSegRows * h->in * sizeof(__half));
+    l.ygu = at; at += round256(static_cast<size_t>(segs) * 2 * kMoeSegRows * h->hidden * sizeof(float));
+    l.xdown = at; at += round256(static_cast<size_t>(segs) * kMoeSegRows * h->hidden * sizeof(__half));
+    l.ydown = at; at += round256(static_cast<size_t>(segs) * kMoeSegRows * h->in * sizeof(float));
+    l.partials = at;
+    at += std::max(qmv_partial_bytes(l.gu_plan, static_cast<int>(segs * 2 * h->hidden), kMoeSegRows),
+                   qmv_partial_bytes(l.down_plan, static_cast<int>(segs * h->in), kMoeSegRows));
+    l.total = at;
+    return l;
+}
+
+static bool moe_sorted(const b200exl3_moe* h, int64_t rows) {
+    // worth it once experts see several rows each: below three slots per expert one row per slot is faster
+    return g_moe_sorted && rows * h->top_k >= std::max<int64_t>(kMoeSortedMinSlots, 3 * static_cast<int64_t>(h->experts)) &&
+           2 * static_cast<size_t>(h->experts) + 1 <= 12 * 1024;
+}
+
 int b200exl3_moe_create(const uint16_t* d_gu_trellis, const void* d_gu_suh, const void* d_gu_svh,
                         const uint16_t* d_down_trellis, const void* d_down_suh, const void* d_down_svh, int scale_dtype,
                         int experts, int in, int hidden, int top_k, int k, int cb, uint32_t flags, b200exl3_moe** out_handle) {
@@ -704,7 +761,7 @@ void b200exl3_moe_free(b200exl3_moe* h) {
 int b200exl3_moe_workspace_bytes(const b200exl3_moe* h, int64_t rows, size_t* out_bytes) {
     if (!h || !out_bytes) return fail("NULL argument");
     if (rows <= 0) return fail("invalid SwitchGLU input/routes");
-    *out_bytes = moe_layout(h, rows).total;
+    *out_bytes = moe_sorted(h, rows) ? moe_sorted_layout(h, rows).total : moe_layout(h, rows).total;
     return 0;
 }
 
@@ -715,13 +772,64 @@ int b200exl3_moe_forward(const b200exl3_moe* h, const void* d_x, int x_dtype, in
     if (!dtype_is_float(x_dtype)) return fail("unsupported input dtype %d", x_dtype);
     if (score_dtype != kF16 && score_dtype != kF32) return fail("unsupported score dtype %d", score_dtype);
     if (!d_x || !d_selected || !d_scores || !d_y) return fail("NULL buffer");
-    const MoeLayout l = moe_layout(h, rows);
-    if (!ws || ws_bytes < l.total) return fail("workspace too small: %zu bytes given, %zu needed", ws_bytes, l.total);
     if (!aligned16(ws) || !aligned16(d_y)) return fail("device pointers must be 16-byte aligned");
     cudaStream_t stream = as_stream(s);
     char* base = static_cast<char*>(ws);
     const bool exact = (h->flags & B200EXL3_EXACT_WEIGHTS) != 0;
     const size_t x_size = dtype_size(x_dtype), score_size = dtype_size(score_dtype);
+    if (moe_sorted(h, rows)) {
+        const MoeSortedLayout l = moe_sorted_layout(h, rows);
+        if (!ws || ws_bytes < l.total) return fail("workspace too small: %zu bytes given, %zu needed", ws_bytes, l.total);
+        int* seg_count = reinterpret_cast<int*>(base + l.seg_count);
+        uint32_t* seg_expert = reinterpret_cast<uint32_t*>(base + l.seg_expert);
+        uint32_t* row_slot = reinterpret_cast<uint32_t*>(base + l.row_slot);
+        uint32_t* slot_row = reinterpret_cast<uint32_t*>(base + l.slot_row);
+        __half* xgu = reinterpret_cast<__half*>(base + l.xgu);
+        float* ygu = reinterpret_cast<float*>(base + l.ygu);
+        __half* xdown = reinterpret_cast<__half*>(base + l.xdown);
+        float* ydown = reinterpret_cast<float*>(base + l.ydown);
+        const int segs = l.max_segments;
+        const int64_t chunk = moe_sorted_chunk_rows(h, rows);
+        B200_TRY(cudaMemsetAsync(base + l.counters, 0, l.counter_bytes, stream), "clear arrival counters");
+        for (int64_t r0 = 0; r0 < rows; r0 += chunk) {
+            const int64_t n = std::min(chunk, rows - r0), slots = n * h->top_k;
+            const uint32_t* sel = d_selected + r0 * h->top_k;
+            // 16 rows per segment against the columns of the segment's expert; segments past the count are skipped
+            auto mapped = [&](const uint32_t* wq, const __half* xhat, int in, int width, int proj, int stride_blocks, float* yhat,
+                              const QmvPlan& plan) {
+                const int out = segs * proj * width;
+                QmvArgs a{};
+                a.wq = wq; a.xhat = xhat; a.xhat_group_stride = static_cast<int64_t>(kMoeSegRows) * in;
+                a.counters = reinterpret_cast<unsigned int*>(base + l.counters);
+                a.error = reinterpret_cast<unsigned int*>(base + kCounterBytes - sizeof(unsigned int));
+                a.partials = reinterpret_cast<float*>(base + l.partials);
+                a.yhat = yhat;
+                a.groups = 1; a.gcol0[0] = 0; a.gout[0] = out;
+                a.x_dtype = kF16; a.y_dtype = kF16;
+                a.in = in; a.out = out; a.rows = kMoeSegRows;
+                a.tiles_n = h->experts * proj * width / 16;
+                a.map_selected = seg_expert; a.map_count = seg_count;
+                a.map_blocks = width / 128; a.map_proj = proj; a.map_stride_blocks = stride_blocks; a.map_experts = h->experts;
+                return launch_qmv(a, h->k, h->cb, exact, plan, stream);
+            };
+            B200_TRY(launch_route_plan(sel, slots, h->experts, segs, seg_count, seg_expert, row_slot, slot_row, stream), "route plan");
+            B200_TRY(launch_routed_prepare_padded(static_cast<const char*>(d_x) + static_cast<size_t>(r0) * h->in * x_size, x_dtype,
+                                                  h->gu_suh, seg_expert, row_slot, seg_count, h->experts, h->top_k, 2, segs, h->in,
+                                                  xgu, stream), "routed prepare");
+            B200_TRY(mapped(h->gu_wq, xgu, h->in, h->hidden, 2, h->experts * (h->hidden / 128), ygu, l.gu_plan), "expert gate/up kernel");
+            B200_TRY(launch_glu_down_input_padded(ygu, h->gu_svh, h->down_suh, seg_expert, row_slot, seg_count, h->experts, segs,
+                                                  h->hidden, h->hidden, xdown, stream), "SwiGLU glue");
+            B200_TRY(mapped(h->down_wq, xdown, h->hidden, h->in, 1, 0, ydown, l.down_plan), "expert down kernel");
+            B200_TRY(launch_finish_and_reduce_padded(ydown, h->down_svh, sel, slot_row, h->experts,
+                                                     static_cast<const char*>(d_scores) + static_cast<size_t>(r0) * h->top_k * score_size,
+                                                     score_dtype, n, h->top_k, h->in, segs,
+                                                     static_cast<char*>(d_y) + static_cast<size_t>(r0) * h->in * score_size, stream),
+                     "expert reduction");
+        }
+        return 0;
+    }
+    const MoeLayout l = moe_layout(h, rows);
+    if (!ws || ws_bytes < l.total) return fail("workspace too small: %zu bytes given, %zu needed", ws_bytes, l.total);
     __half* xgu = reinterpret_cast<__half*>(base + l.xgu);
     float* ygu = reinterpret_cast<float*>(base + l.ygu);
     __half* xdown = reinterpret_cast<__half*>(base + l.xdown);

@@ -65,6 +65,7 @@ struct QmvArgs {
     // (column block map_proj_index * map_stride_blocks + expert * map_blocks + j; tiles_n is the bank's width)
     // and multiplies them with its own rotated activations xhat[s * map_proj + projection, :].
     const uint32_t* map_selected;
+    const int* map_count;      // optional: number of slots in use; the blocks of later slots are skipped
     int map_blocks, map_proj, map_stride_blocks, map_experts;
     // Tensor-parallel row shard (tp.world > 0; rotated output): the complete sum of a column block is
     // exchanged with the other ranks (unit = (tp_row0 + row) * out/128 + block) before the output rotation.
@@ -119,6 +120,28 @@ struct TpArgs {
     int rows, out, y_dtype;
 };
 cudaError_t launch_tp_finish(const TpArgs& args, cudaStream_t stream);
+
+// Expert-sorted form for many slots (native/src/moe.rs:66-182 route_plan, 1001-1085): slots are grouped by expert
+// into segments of up to 16 rows, so that an expert's columns are decoded once per 16 rows that use them.
+//   seg_count[0]         number of segments
+//   seg_expert[s]        expert of segment s
+//   row_slot[16 s + r]   slot in row r of segment s, or 0xffffffff for a padding row
+//   slot_row[slot]       padded row 16 s + r that holds the slot
+// max_segments bounds the arrays (min(experts, slots) + slots / 16 always suffices).
+cudaError_t launch_route_plan(const uint32_t* selected, int64_t slots, int experts, int max_segments, int* seg_count,
+                              uint32_t* seg_expert, uint32_t* row_slot, uint32_t* slot_row, cudaStream_t stream);
+// padded-row forms of the three glue kernels; activations and products are laid out per segment:
+// xhat[(s * proj + p) * 16 + r, :], products y[r, (s * proj + p) * width + col] with row stride max_segments * proj * width
+cudaError_t launch_routed_prepare_padded(const void* x, int x_dtype, const __half* suh, const uint32_t* seg_expert,
+                                         const uint32_t* row_slot, const int* seg_count, int experts, int top_k, int proj,
+                                         int max_segments, int in, __half* xhat, cudaStream_t stream);
+cudaError_t launch_glu_down_input_padded(const float* ygu, const __half* gu_svh, const __half* down_suh,
+                                         const uint32_t* seg_expert, const uint32_t* row_slot, const int* seg_count,
+                                         int experts, int max_segments, int hidden, int logical_hidden, __half* xhat,
+                                         cudaStream_t stream);
+cudaError_t launch_finish_and_reduce_padded(const float* raw, const __half* down_svh, const uint32_t* selected,
+                                            const uint32_t* slot_row, int experts, const void* scores, int score_dtype,
+                                            int64_t rows, int top_k, int out, int max_segments, void* y, cudaStream_t stream);
 
 // ---- tensor-core product for many rows (kernels_qmm.cu) ---------------------------------------------------
 struct QmmPlan {

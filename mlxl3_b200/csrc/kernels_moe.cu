@@ -164,3 +164,210 @@ cudaError_t launch_finish_and_reduce(const float* raw, const __half* down_svh, c
 }
 
 }  // namespace b200exl3
+
+// ---- expert-sorted form (many slots) ------------------------------------------------------------------------
+namespace b200exl3 {
+
+namespace {
+
+constexpr int kSegRows = 16;
+constexpr uint32_t kNoSlot = 0xffffffffu;
+
+// One CTA plans the whole batch: counts per expert, segments of 16 rows per expert in expert order, and the
+// two maps between slots and padded rows.
+__global__ void __launch_bounds__(1024)
+route_plan_kernel(const uint32_t* __restrict__ selected, int64_t slots, int experts, int max_segments,
+                  int* __restrict__ seg_count, uint32_t* __restrict__ seg_expert, uint32_t* __restrict__ row_slot,
+                  uint32_t* __restrict__ slot_row) {
+    extern __shared__ int s_mem[];
+    int* count = s_mem;                 // [experts] rows per expert, then running position
+    int* base = s_mem + experts;        // [experts + 1] first segment of each expert
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
+    for (int64_t r = threadIdx.x; r < static_cast<int64_t>(max_segments) * kSegRows; r += blockDim.x) row_slot[r] = kNoSlot;
+    __syncthreads();
+    // One thread per expert walks the slots in order: a slot's position among its expert's rows is the number
+    // of earlier slots with the same expert, so the plan (and with it the summation order of every row's
+    // products, which depends on the segment a row lands in) is the same on every call.
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+        int pos = 0;
+        for (int64_t s = 0; s < slots; ++s)
+            if (min(static_cast<int>(selected[s]), experts - 1) == e) slot_row[s] = static_cast<uint32_t>(pos++);
+        count[e] = pos;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int e = 0; e < experts; ++e) { base[e] = at; at += (count[e] + kSegRows - 1) / kSegRows; }
+        base[experts] = at;
+        seg_count[0] = min(at, max_segments);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < experts; e += blockDim.x)
+        for (int s = base[e]; s < base[e + 1] && s < max_segments; ++s) seg_expert[s] = static_cast<uint32_t>(e);
+    for (int64_t s = threadIdx.x; s < slots; s += blockDim.x) {
+        const int e = min(static_cast<int>(selected[s]), experts - 1);
+        const int pos = static_cast<int>(slot_row[s]);
+        const int64_t row = static_cast<int64_t>(base[e] + pos / kSegRows) * kSegRows + pos % kSegRows;
+        slot_row[s] = static_cast<uint32_t>(row);
+        if (row < static_cast<int64_t>(max_segments) * kSegRows) row_slot[row] = static_cast<uint32_t>(s);
+    }
+}
+
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+routed_prepare_padded_kernel(const void* __restrict__ x, int x_dtype, const __half* __restrict__ suh,
+                             const uint32_t* __restrict__ seg_expert, const uint32_t* __restrict__ row_slot,
+                             const int* __restrict__ seg_count, int top_k, int proj, int in, __half* __restrict__ xhat) {
+    const int lane = threadIdx.x & 31;
+    const int blocks_per_row = in >> 7;
+    const int64_t total = static_cast<int64_t>(seg_count[0]) * proj * kSegRows * blocks_per_row;
+    for (int64_t unit = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5); unit < total;
+         unit += static_cast<int64_t>(gridDim.x) * kWarpsPerBlock) {
+        const int64_t out_row = unit / blocks_per_row;                   // (segment * proj + p) * 16 + r
+        const int col = static_cast<int>(unit % blocks_per_row) * 128 + lane * 4;
+        const int r = static_cast<int>(out_row % kSegRows);
+        const int64_t sp = out_row / kSegRows;
+        const int64_t seg = sp / proj;
+        const int p = static_cast<int>(sp - seg * proj);
+        const uint32_t slot = row_slot[seg * kSegRows + r];
+        __align__(8) __half h[4] = {__half(), __half(), __half(), __half()};
+        if (slot != kNoSlot) {                                           // warp-uniform: one row per warp
+            const __half* s = suh + (static_cast<int64_t>(seg_expert[seg]) * proj + p) * in + col;
+            const int64_t token = slot / top_k;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) h[j] = __hmul_rn(load_as_half(x, x_dtype, token * in + col + j), s[j]);
+            warp_hadamard128_f16(h, lane);
+        }
+        *reinterpret_cast<uint2*>(xhat + out_row * in + col) = *reinterpret_cast<uint2*>(h);
+    }
+}
+
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+glu_down_input_padded_kernel(const float* __restrict__ ygu, const __half* __restrict__ gu_svh, const __half* __restrict__ down_suh,
+                             const uint32_t* __restrict__ seg_expert, const uint32_t* __restrict__ row_slot,
+                             const int* __restrict__ seg_count, int max_segments, int hidden, int logical_hidden,
+                             __half* __restrict__ xhat) {
+    const int lane = threadIdx.x & 31;
+    const int blocks_per_row = hidden >> 7;
+    const int64_t total = static_cast<int64_t>(seg_count[0]) * kSegRows * blocks_per_row;
+    const int64_t row_stride = static_cast<int64_t>(max_segments) * 2 * hidden;       // products are [16, segments * 2 * hidden]
+    const float scale = had_scale();
+    for (int64_t unit = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5); unit < total;
+         unit += static_cast<int64_t>(gridDim.x) * kWarpsPerBlock) {
+        const int64_t prow = unit / blocks_per_row;                      // segment * 16 + r
+        const int col = static_cast<int>(unit % blocks_per_row) * 128 + lane * 4;
+        const int64_t seg = prow / kSegRows;
+        const int r = static_cast<int>(prow - seg * kSegRows);
+        __align__(8) __half h[4] = {__half(), __half(), __half(), __half()};
+        if (row_slot[prow] != kNoSlot) {
+            const int64_t expert = seg_expert[seg];
+            const float4 graw = *reinterpret_cast<const float4*>(ygu + r * row_stride + (seg * 2) * hidden + col);
+            const float4 uraw = *reinterpret_cast<const float4*>(ygu + r * row_stride + (seg * 2 + 1) * hidden + col);
+            float gv[4] = {round_half(graw.x), round_half(graw.y), round_half(graw.z), round_half(graw.w)};
+            float uv[4] = {round_half(uraw.x), round_half(uraw.y), round_half(uraw.z), round_half(uraw.w)};
+            warp_hadamard128<false, false>(gv, lane);
+            warp_hadamard128<false, false>(uv, lane);
+            const __half* sg = gu_svh + (expert * 2) * hidden + col;
+            const __half* su = gu_svh + (expert * 2 + 1) * hidden + col;
+            const __half* sd = down_suh + expert * hidden + col;
+            float d[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float gate = round_half(__fmul_rn(__fmul_rn(gv[j], scale), __half2float(sg[j])));
+                const float up = round_half(__fmul_rn(__fmul_rn(uv[j], scale), __half2float(su[j])));
+                float act = round_half(__fmul_rn(silu(gate), up));
+                if (col + j >= logical_hidden) act = 0.0f;
+                d[j] = round_half(__fmul_rn(act, __half2float(sd[j])));
+            }
+            warp_hadamard128<false, false>(d, lane);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) h[j] = __float2half_rn(__fmul_rn(d[j], scale));
+        }
+        *reinterpret_cast<uint2*>(xhat + prow * hidden + col) = *reinterpret_cast<uint2*>(h);
+    }
+}
+
+template <bool F32>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+finish_and_reduce_padded_kernel(const float* __restrict__ raw, const __half* __restrict__ down_svh,
+                                const uint32_t* __restrict__ selected, const uint32_t* __restrict__ slot_row, int experts,
+                                const void* __restrict__ scores, int64_t rows, int top_k, int out, int max_segments,
+                                void* __restrict__ y) {
+    const int lane = threadIdx.x & 31;
+    const int blocks_per_row = out >> 7;
+    const int64_t total = rows * blocks_per_row;
+    const int64_t row_stride = static_cast<int64_t>(max_segments) * out;              // products are [16, segments * out]
+    for (int64_t unit = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5); unit < total;
+         unit += static_cast<int64_t>(gridDim.x) * kWarpsPerBlock) {
+        const int64_t row = unit / blocks_per_row;
+        const int col = static_cast<int>(unit % blocks_per_row) * 128 + lane * 4;
+        float acc32[4] = {0.f, 0.f, 0.f, 0.f};
+        __half acc16[4];
+        for (int t = 0; t < top_k; ++t) {
+            const int64_t slot = row * top_k + t;
+            const int64_t prow = slot_row[slot];
+            const float4 r = *reinterpret_cast<const float4*>(raw + (prow % kSegRows) * row_stride + (prow / kSegRows) * out + col);
+            __half h[4] = {__float2half_rn(r.x), __float2half_rn(r.y), __float2half_rn(r.z), __float2half_rn(r.w)};
+            warp_hadamard128_f16(h, lane);
+            const __half* sv = down_svh + static_cast<int64_t>(expert_of(selected, slot, experts)) * out + col;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const __half scaled = __hmul_rn(h[j], sv[j]);
+                if (F32) {
+                    const float v = __fmul_rn(__half2float(scaled), reinterpret_cast<const float*>(scores)[slot]);
+                    acc32[j] = t == 0 ? v : __fadd_rn(acc32[j], v);
+                } else {
+                    const __half v = __hmul_rn(scaled, reinterpret_cast<const __half*>(scores)[slot]);
+                    acc16[j] = t == 0 ? v : __hadd_rn(acc16[j], v);
+                }
+            }
+        }
+        if (F32) *reinterpret_cast<float4*>(reinterpret_cast<float*>(y) + row * out + col) = make_float4(acc32[0], acc32[1], acc32[2], acc32[3]);
+        else *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(y) + row * out + col) = *reinterpret_cast<uint2*>(acc16);
+    }
+}
+
+}  // namespace
+
+cudaError_t launch_route_plan(const uint32_t* selected, int64_t slots, int experts, int max_segments, int* seg_count,
+                              uint32_t* seg_expert, uint32_t* row_slot, uint32_t* slot_row, cudaStream_t stream) {
+    const size_t smem = (2 * static_cast<size_t>(experts) + 1) * sizeof(int);
+    if (smem > 48 * 1024) return cudaErrorInvalidValue;
+    route_plan_kernel<<<1, 1024, smem, stream>>>(selected, slots, experts, max_segments, seg_count, seg_expert, row_slot, slot_row);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_routed_prepare_padded(const void* x, int x_dtype, const __half* suh, const uint32_t* seg_expert,
+                                         const uint32_t* row_slot, const int* seg_count, int experts, int top_k, int proj,
+                                         int max_segments, int in, __half* xhat, cudaStream_t stream) {
+    (void)experts;
+    routed_prepare_padded_kernel<<<grid_for(static_cast<int64_t>(max_segments) * proj * kSegRows * (in / 128)), kWarpsPerBlock * 32, 0,
+                                   stream>>>(x, x_dtype, suh, seg_expert, row_slot, seg_count, top_k, proj, in, xhat);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_glu_down_input_padded(const float* ygu, const __half* gu_svh, const __half* down_suh,
+                                         const uint32_t* seg_expert, const uint32_t* row_slot, const int* seg_count,
+                                         int experts, int max_segments, int hidden, int logical_hidden, __half* xhat,
+                                         cudaStream_t stream) {
+    (void)experts;
+    glu_down_input_padded_kernel<<<grid_for(static_cast<int64_t>(max_segments) * kSegRows * (hidden / 128)), kWarpsPerBlock * 32, 0,
+                                   stream>>>(ygu, gu_svh, down_suh, seg_expert, row_slot, seg_count, max_segments, hidden,
+                                             logical_hidden, xhat);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_finish_and_reduce_padded(const float* raw, const __half* down_svh, const uint32_t* selected,
+                                            const uint32_t* slot_row, int experts, const void* scores, int score_dtype,
+                                            int64_t rows, int top_k, int out, int max_segments, void* y, cudaStream_t stream) {
+    if (rows == 0) return cudaSuccess;
+    const unsigned grid = grid_for(rows * (out / 128));
+    if (score_dtype == kF32)
+        finish_and_reduce_padded_kernel<true><<<grid, kWarpsPerBlock * 32, 0, stream>>>(raw, down_svh, selected, slot_row, experts,
+                                                                                        scores, rows, top_k, out, max_segments, y);
+    else
+        finish_and_reduce_padded_kernel<false><<<grid, kWarpsPerBlock * 32, 0, stream>>>(raw, down_svh, selected, slot_row, experts,
+                                                                                         scores, rows, top_k, out, max_segments, y);
+    return cudaGetLastError();
+}
+
+}  // namespace b200exl3

@@ -276,13 +276,16 @@ qmv_kernel(const QmvArgs p) {
         float* stage = reinterpret_cast<float*>(mine + p.stage_offset) + (cblock - w0 / UB) * stage_floats;
         int grp = qmv_group_of(p, cblock);
         int tn0 = cblock * 8;                               // first tile column of the block in the weight array
+        bool active = true;
         if (p.map_selected != nullptr) {
             // expert-mapped: virtual block -> (slot, projection, block of the expert's columns)
             const int sp = cblock / p.map_blocks, j = cblock - sp * p.map_blocks;
             const int slot = sp / p.map_proj, proj = sp - slot * p.map_proj;
             const int expert = min(static_cast<int>(p.map_selected[slot]), p.map_experts - 1);
             tn0 = (proj * p.map_stride_blocks + expert * p.map_blocks + j) * 8;
-            grp = sp;                                       // row of the rotated activations (stride: one row)
+            grp = sp;                                       // rows of the rotated activations (stride: one slot)
+            // slots past the device-side count hold nothing: no weights are read for them, zeros are reduced
+            active = p.map_count == nullptr || slot < *p.map_count;
         }
         {
             const int tk_first = u0 >> 3, tk_last = (u1 - 1) >> 3;
@@ -298,7 +301,7 @@ qmv_kernel(const QmvArgs p) {
 
             // The segment is walked in chunks whose inputs span at most kQmvXBlocks 128-blocks, so that
             // the rotated activations of a chunk fit the warp's shared memory.
-            for (int tk0 = tk_first; tk0 <= tk_last;) {
+            for (int tk0 = tk_first; active && tk0 <= tk_last;) {
                 const int kb0 = tk0 >> 3;
                 const int tk_end = min(tk_last + 1, (kb0 + kQmvXBlocks) * 8);
                 const int nrows = tk_end - tk0;
@@ -372,6 +375,10 @@ qmv_kernel(const QmvArgs p) {
                 tk0 = tk_end;
             }
 
+            if (first_chunk) {                                  // a warp whose block was skipped has not waited yet
+                pdl_wait();
+                first_chunk = false;
+            }
             // ---- phase 3: stage the fragment as a [rows][128] tile in this warp's shared memory -----------
 #pragma unroll
             for (int nb = 0; nb < NB; ++nb)

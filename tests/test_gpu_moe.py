@@ -66,20 +66,48 @@ def test_switch_glu_matches_oracle(gpu, k, cb, experts, top_k, n_in, hidden, row
 
 
 def test_switch_glu_many_rows_and_repeated_experts(gpu):
-    """More slots than one pass takes (passes of 256 slots), every expert chosen many times."""
+    """More than 32 slots: the expert-sorted form (segments of 16 rows per expert), several passes, every
+    expert chosen many times, and experts that nobody chose."""
     rng = np.random.default_rng(77)
-    experts, top_k, n_in, hidden, k, cb, rows = 8, 4, 256, 256, 3, 1, 150
+    experts, top_k, n_in, hidden, k, cb, rows = 12, 4, 256, 256, 3, 1, 150
+    bank = make_bank(rng, experts, n_in, hidden, k)
+    moe = gpu.Exl3SwitchGlu(*bank, top_k, k, cb, exact_weights=True)
+    x = rng.standard_normal((rows, n_in)).astype(np.float16)
+    selected, scores = routes(rng, rows, experts - 2, top_k)          # the last two experts stay idle
+    got = moe.forward(x, selected, scores)
+    assert gpu.workspace_status(moe._workspace) == 0
+    pick = np.array([0, 1, 63, 64, 65, 127, 128, 149])
+    want = oracle.switch_glu_forward(*bank, top_k, k, cb, x[pick], selected[pick], scores[pick])
+    check(got[pick], want)
+    # same call again: bit-identical (a slot's place inside its segment may change, its arithmetic does not)
+    assert np.array_equal(got.view(np.uint16), moe.forward(x, selected, scores).view(np.uint16))
+    # one row per slot (sorting switched off) agrees to accumulation order
+    gpu.set_option("moe_sorted", 0)
+    try:
+        plain = moe.forward(x, selected, scores)
+    finally:
+        gpu.set_option("moe_sorted", 1)
+    check(got, plain, rms=2e-3)
+    # a row computed alone (few slots: one row per slot) matches its result inside the batch
+    alone = moe.forward(x[64:65], selected[64:65], scores[64:65])
+    check(alone, got[64:65], rms=2e-3)
+    moe.close()
+
+
+@pytest.mark.parametrize("rows,top_k,experts", [(9, 4, 4), (40, 1, 3), (80, 2, 32)])
+def test_switch_glu_sorted_edge_shapes(gpu, rows, top_k, experts):
+    """Segments that are exactly full, a single expert taking every slot, many experts with few rows each."""
+    rng = np.random.default_rng(1000 + rows)
+    n_in, hidden, k, cb = 128, 128, 4, 0
     bank = make_bank(rng, experts, n_in, hidden, k)
     moe = gpu.Exl3SwitchGlu(*bank, top_k, k, cb, exact_weights=True)
     x = rng.standard_normal((rows, n_in)).astype(np.float16)
     selected, scores = routes(rng, rows, experts, top_k)
+    if experts == 3:
+        selected[:] = 1                                               # everybody picks the same expert
     got = moe.forward(x, selected, scores)
-    pick = np.array([0, 1, 63, 64, 65, 127, 128, 149])
-    want = oracle.switch_glu_forward(*bank, top_k, k, cb, x[pick], selected[pick], scores[pick])
-    check(got[pick], want)
-    # a row computed alone equals the same row inside the batch bit for bit (slots are independent)
-    alone = moe.forward(x[64:65], selected[64:65], scores[64:65])
-    assert np.array_equal(alone.view(np.uint16), got[64:65].view(np.uint16))
+    check(got, oracle.switch_glu_forward(*bank, top_k, k, cb, x, selected, scores))
+    assert gpu.workspace_status(moe._workspace) == 0
     moe.close()
 
 
