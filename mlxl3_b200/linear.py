@@ -35,6 +35,17 @@ def _np_dtype(code: int):
     return {F16: np.float16, F32: np.float32, BF16: np.uint16}[code]
 
 
+def _to_f32(array: np.ndarray, code: int) -> np.ndarray:
+    if code == BF16:
+        return (np.asarray(array, np.uint16).astype(np.uint32) << 16).view(np.float32)
+    return np.asarray(array).astype(np.float32)
+
+
+def _f32_to_bf16_bits(array: np.ndarray) -> np.ndarray:
+    u = np.ascontiguousarray(array, np.float32).view(np.uint32)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
 def new_workspace(nbytes: int) -> DeviceBuffer:
     """Scratch memory for forward calls: its header of arrival counters is zeroed here, once."""
     buf = DeviceBuffer(max(nbytes, _lib.WORKSPACE_HEADER_BYTES))
@@ -92,6 +103,39 @@ class Exl3Linear:
                   c_void_p(d_bias.ptr) if d_bias else None, code, rows, cols, k, cb, flags, byref(handle))
         self.handle = handle.value
         self._workspace: DeviceBuffer | None = None
+
+    @classmethod
+    def from_checkpoint(cls, checkpoint, prefix: str, **options) -> "Exl3Linear":
+        """``Exl3Linear::from_checkpoint`` (native/src/linear.rs:454-575): ``{prefix}.trellis``, scales
+        ``suh``/``svh`` or their legacy names ``su``/``sv``, the codebook from the presence of ``{prefix}.mul1``
+        or ``{prefix}.mcg``, an optional ``{prefix}.bias`` (converted to fp16), K from the trellis' last axis.
+        ``checkpoint`` comes from :func:`mlxl3_b200.checkpoint.inspect`."""
+        trellis = checkpoint.array(f"{prefix}.trellis")
+        if trellis.ndim == 0 or trellis.shape[-1] % 16:
+            raise B200Exl3Error("trellis must have dimensions")
+        codes = {"F16": F16, "BF16": BF16, "F32": F32}
+
+        def load(name):
+            info = checkpoint.tensors.get(name)
+            if info is None:
+                raise B200Exl3Error(f"missing tensor {name}")
+            if info.dtype not in codes:
+                raise B200Exl3Error(f"invalid scale dtype {name}")
+            return checkpoint.array(name), codes[info.dtype]
+        scales = [load(checkpoint.scale_name(prefix, primary, legacy)) for primary, legacy in (("suh", "su"), ("svh", "sv"))]
+        bias = None
+        if f"{prefix}.bias" in checkpoint.tensors:
+            bias = _to_f32(*load(f"{prefix}.bias")).astype(np.float16)          # the reference stores the bias as fp16
+        code = scales[0][1]
+        if scales[1][1] != code or (bias is not None and code == BF16):
+            # the device side takes one dtype for a layer's vectors: widen all of them to fp32 (exact)
+            scales = [(_to_f32(a, c), F32) for a, c in scales]
+            code = F32
+        if bias is not None and code == F32:
+            bias = bias.astype(np.float32)
+        scales = [a for a, _ in scales]
+        return cls(trellis, scales[0], scales[1], bias, trellis.shape[-1] // 16, checkpoint.codebook(prefix),
+                   scale_dtype=code, **options)
 
     # ---- reference accessors (native/src/linear.rs:655-660) ---------------------------------------
     def input_dims(self) -> int:

@@ -55,6 +55,58 @@ class Exl3SwitchGlu:
         self.handle = handle.value
         self._workspace: DeviceBuffer | None = None
 
+    @classmethod
+    def from_checkpoint(cls, checkpoint, prefix: str, experts: int, top_k: int,
+                        names=("gate_proj", "up_proj", "down_proj"), **options) -> "Exl3SwitchGlu":
+        """``Exl3SwitchGlu::from_checkpoint`` (native/src/moe.rs:629-807): experts ``{prefix}.{e}.{projection}``
+        for e in 0..experts; the gate trellises of all experts followed by the up trellises of all experts are
+        joined on the output axis, the down trellises likewise; scales are stacked per expert.  All experts must
+        share one bit width and one codebook.  ``names=("w1", "w3", "w2")`` reads the LFM naming."""
+        if not (experts > 0 and 0 < top_k <= experts and experts <= len(checkpoint.tensors) // 3):
+            raise B200Exl3Error("invalid expert count or incomplete expert bank")
+        gate, up, down = ([f"{prefix}.{e}.{projection}" for e in range(experts)] for projection in names)
+        k = cb = None
+        for name in gate + up + down:
+            info = checkpoint.tensors.get(f"{name}.trellis")
+            if info is None:
+                raise B200Exl3Error(f"missing expert trellis {name}")
+            if info.dtype not in ("I16", "U16"):
+                raise B200Exl3Error(f"{name}: expert trellis must contain 16-bit integers")
+            if not info.shape:
+                raise B200Exl3Error("empty expert trellis")
+            bits = info.shape[-1] // 16
+            if k is not None and k != bits:
+                raise B200Exl3Error("mixed expert bit widths")
+            mode = checkpoint.codebook(name)
+            if cb is not None and cb != mode:
+                raise B200Exl3Error("mixed expert codebooks")
+            k, cb = bits, mode
+
+        def trellises(group):
+            # signed and unsigned trellis words carry bits, never numeric values
+            return [checkpoint.array(f"{name}.trellis").view(np.uint16) for name in group]
+
+        def scales(group, primary, legacy):
+            out = []
+            for name in group:
+                key = checkpoint.scale_name(name, primary, legacy)
+                info = checkpoint.tensors.get(key)
+                if info is None:
+                    raise B200Exl3Error(f"missing tensor {key}")
+                code = {"F16": F16, "BF16": 12, "F32": F32}.get(info.dtype)
+                if code is None:
+                    raise B200Exl3Error(f"invalid scale dtype {key}")
+                a = checkpoint.array(key)
+                out.append((a.astype(np.uint32) << 16).view(np.float32) if code == 12 else a.astype(np.float32))
+            return np.stack(out)
+
+        gu_trellis = np.concatenate(trellises(gate) + trellises(up), axis=1)
+        down_trellis = np.concatenate(trellises(down), axis=1)
+        gu_suh = np.stack([scales(gate, "suh", "su"), scales(up, "suh", "su")], axis=1)
+        gu_svh = np.stack([scales(gate, "svh", "sv"), scales(up, "svh", "sv")], axis=1)
+        return cls(gu_trellis, gu_suh, gu_svh, down_trellis, scales(down, "suh", "su"), scales(down, "svh", "sv"),
+                   top_k, k, cb, **options)
+
     def workspace_bytes(self, rows: int) -> int:
         out = c_size_t()
         _lib.call("b200exl3_moe_workspace_bytes", c_void_p(self.handle), rows, byref(out))
