@@ -112,3 +112,39 @@ def finish(partials: np.ndarray, svh: np.ndarray, bias: np.ndarray | None = None
     _lib.call("b200exl3_finish", c_void_p(d_p.ptr), splits, c_void_p(d_s.ptr), scale_rows, c_void_p(d_b.ptr) if d_b else None,
               rows, n, y_dtype, c_void_p(d_y.ptr), c_void_p(stream.handle))
     return d_y.download((rows, n), out_dtype, stream)
+
+
+def permutation() -> np.ndarray:
+    """Kernel-order index -> position ``row * 16 + col`` in the 16x16 tile (``codec::permutation``,
+    native/src/codec.rs:126-138): lane ``L`` of a warp owns indices ``8L..8L+7`` = rows ``2q + {0, 1, 8, 9}``
+    (q = L % 4) of columns ``g`` and ``g + 8`` (g = L // 4), the ``mma.m16n8k16`` fragment order."""
+    lane = np.arange(32)[:, None, None]
+    rows = (lane % 4) * 2 + np.array([0, 1, 8, 9])[None, None, :]
+    cols = lane // 4 + np.array([0, 8])[None, :, None]
+    return (rows * 16 + cols).reshape(256)
+
+
+def permutation_inverse() -> np.ndarray:
+    """Tile position -> kernel-order index (``codec::permutation_inverse``, native/src/codec.rs:150-156)."""
+    out = np.empty(256, np.int64)
+    out[permutation()] = np.arange(256)
+    return out
+
+
+def pack(states: np.ndarray, k: int) -> np.ndarray:
+    """States -> packed tiles on the host (``codec::pack``, native/src/codec.rs:72-100): the low ``k`` bits of
+    state ``t`` are bits ``[t*k, (t+1)*k)`` of the tile's 256*k-bit stream, most significant bit first; the
+    stream is stored as little-endian 32-bit words, i.e. 16-bit group ``l`` of the stream lands at index
+    ``l ^ 1``.  Only the quantizer side needs this; it lives here so that the codec tool is complete."""
+    _check_k(k)
+    s = np.ascontiguousarray(states, np.uint16).reshape(-1)
+    if s.size % 256:
+        raise B200Exl3Error("encoded length must be a multiple of 256")
+    tiles = s.reshape(-1, 256)
+    shifts = np.arange(k - 1, -1, -1, dtype=np.uint16)
+    bits = ((tiles[:, :, None] >> shifts) & 1).astype(np.uint8).reshape(tiles.shape[0], 256 * k)
+    weights = (1 << np.arange(15, -1, -1)).astype(np.uint32)
+    groups = (bits.reshape(tiles.shape[0], 16 * k, 16) * weights).sum(axis=2).astype(np.uint16)
+    out = np.empty_like(groups)
+    out[:, np.arange(16 * k) ^ 1] = groups
+    return out.reshape(-1)

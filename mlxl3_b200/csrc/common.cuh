@@ -106,6 +106,19 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// cudaFuncSetAttribute is per device: remembers, per kernel instantiation, the devices it was done on.
+struct PerDeviceOnce {
+    bool done[64] = {};
+    bool needed() const {
+        int device = 0;
+        return cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64 || !done[device];
+    }
+    void mark() {
+        int device = 0;
+        if (cudaGetDevice(&device) == cudaSuccess && device >= 0 && device < 64) done[device] = true;
+    }
+};
+
 __device__ __forceinline__ unsigned long long global_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));

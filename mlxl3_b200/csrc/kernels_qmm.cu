@@ -416,11 +416,11 @@ EncodeFn encode_fn() {
 template <int K, int CB>
 cudaError_t qmm_launch_one(const CUtensorMap& map, const CUtensorMap& wmap, const QmmArgs& p, dim3 grid, size_t smem, cudaStream_t stream) {
     auto kernel = qmm_kernel<K, CB>;
-    static bool attribute_set = false;
-    if (!attribute_set) {
+    static PerDeviceOnce attribute;                         // once per kernel and device
+    if (attribute.needed()) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (e != cudaSuccess) return e;
-        attribute_set = true;
+        attribute.mark();
     }
     kernel<<<grid, kThreads, smem, stream>>>(map, wmap, p);
     return cudaGetLastError();

@@ -426,11 +426,11 @@ qmv_kernel(const QmvArgs p) {
 template <int K, int CB, int NB, int MODE>
 cudaError_t qmv_launch_one(const QmvArgs& p, const QmvPlan& plan, cudaStream_t stream) {
     auto kernel = qmv_kernel<K, CB, NB, MODE>;
-    static bool attribute_set = false;                      // once per kernel: allow the largest carve-out
-    if (!attribute_set) {
+    static PerDeviceOnce attribute;                         // once per kernel and device: allow the largest carve-out
+    if (attribute.needed()) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kQmvMaxSmemBytes);
         if (e != cudaSuccess) return e;
-        attribute_set = true;
+        attribute.mark();
     }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(static_cast<unsigned>(plan.grid));
