@@ -228,9 +228,10 @@ int b200exl3_moe_forward(const b200exl3_moe* handle, const void* d_x, int x_dtyp
  * No counterpart in the reference (single GPU).  Column-parallel shards need nothing from here.  A row-parallel
  * shard computes its fp32 partial product with b200exl3_linear_forward_partial; b200exl3_linear_finish_tp then
  * replaces "all-reduce + b200exl3_linear_finish" by one kernel: every rank stores its partial sums into all
- * ranks' exchange buffers over NVLink, waits (bounded, about four seconds) for the other ranks' sums, adds them
- * in rank order in fp32 (the reference's split-K sum, native/src/linear.rs:978-982; every rank gets the same
- * bits) and applies the output rotation.  It is a plain kernel launch: it can be recorded into a graph.
+ * ranks' exchange buffers over NVLink as 8-byte {value, sequence number} words (no fence, no flag), polls its
+ * own buffer (bounded, about four seconds) until the other ranks' words of this call have arrived, adds them in
+ * rank order in fp32 (the reference's split-K sum, native/src/linear.rs:978-982; every rank gets the same bits)
+ * and applies the output rotation.  It is a plain kernel launch: it can be recorded into a graph.
  *
  * Set-up: every rank calls b200exl3_tp_alloc (buffer + 64-byte IPC handle), the host exchanges the handles by
  * its own means, opens the other ranks' buffers with b200exl3_tp_open, and passes all `world` buffers (its own

@@ -873,12 +873,11 @@ int b200exl3_moe_forward(const b200exl3_moe* h, const void* d_x, int x_dtype, in
 
 /* ---- tensor parallelism over peer memory ------------------------------------------------------------ */
 
-static size_t tp_flag_bytes(int world, int max_units) { return round256(static_cast<size_t>(world) * max_units * sizeof(unsigned int)); }
-
 int b200exl3_tp_buffer_bytes(int world, int max_units, size_t* out_bytes) {
     if (!out_bytes) return fail("NULL argument");
     if (world < 1 || world > kTpMaxWorld || max_units < 1) return fail("invalid tensor-parallel geometry");
-    *out_bytes = tp_flag_bytes(world, max_units) + static_cast<size_t>(2) * world * max_units * 128 * sizeof(float);
+    // inbox [2 slots, world sources, max_units, 128 words of {value, sequence number}]
+    *out_bytes = static_cast<size_t>(2) * world * max_units * kTpUnitWords * sizeof(uint2);
     return 0;
 }
 
@@ -980,13 +979,9 @@ int b200exl3_linear_finish_tp(const b200exl3_linear* h, b200exl3_tp* tp, const f
 
 static TpPeers tp_peers(const b200exl3_tp* tp) {
     TpPeers t{};
-    for (int r = 0; r < tp->world; ++r) {
-        t.flags[r] = static_cast<unsigned int*>(tp->buffers[r]);
-        t.inbox[r] = reinterpret_cast<float*>(static_cast<char*>(tp->buffers[r]) + tp_flag_bytes(tp->world, tp->max_units));
-    }
+    for (int r = 0; r < tp->world; ++r) t.inbox[r] = static_cast<uint2*>(tp->buffers[r]);
     t.done = tp->done;
     t.error = tp->done + tp->max_units;
     t.rank = tp->rank; t.world = tp->world; t.max_units = tp->max_units;
     return t;
 }
-

@@ -5,7 +5,7 @@
 // (native/src/linear.rs:978-982); they are added in fp32, in rank order on every rank (so all ranks
 // hold bit-identical outputs), then rounded to fp16, rotated and scaled as in linear.rs:983-996.
 //
-// The exchange itself (peer stores, flags, bounded wait, rank-ordered sum) is tp_exchange_unit.
+// The exchange itself (peer stores of {value, sequence} words, bounded wait, rank-ordered sum) is tp_exchange_unit.
 #include "hadamard.cuh"
 #include "kernels.h"
 #include "tp_exchange.cuh"
