@@ -57,7 +57,7 @@ int b200exl3_version(void);
  * next kernel after the main loop, 2 as soon as the first copies are in flight), "qmv_trace_buffer"
  * (device address of a uint64 [grid, 8] array that receives nanosecond stamps of each CTA's phases:
  * start, activations visible, rotated, main loop done, warps joined, reduced, finished; 0 = off), "qmm" (0 = batches
- * of more than 16 rows also go through the small-batch kernel instead of the tensor-core product; default 1),
+ * of more than 8 rows also go through the small-batch kernel (16 rows per launch) instead of the tensor-core product; default 1),
  * "qmm_splits" (input splits of the tensor-core product, 0 = chosen by a cost model; set it before asking for
  * workspace sizes), "moe_sorted" (0 = the expert block runs one row per slot for any batch instead of grouping
  * slots by expert for larger batches; set it before asking for workspace sizes), "qmm_trace_buffer" (device address of a uint64 [CTAs, 8] array that receives nanosecond

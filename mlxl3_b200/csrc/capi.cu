@@ -335,9 +335,10 @@ static size_t xhat_bytes(const LayerCore& c, int64_t rows) {
     return rows > kQmvFusedRows ? round256(static_cast<size_t>(c.groups) * rows * c.in * sizeof(__half)) : 0;
 }
 
-// From this many rows on, a plain layer's forward runs the tensor-core product (rotate all rows,
-// tcgen05 product into fp32 partials, output rotation) instead of batches through the fused kernel.
-constexpr int64_t kQmmMinRows = kQmvMaxRows + 1;
+// From this many rows on, a plain layer's forward runs the tensor-core product (rotate all rows, tcgen05 product,
+// output rotation) instead of the fused kernel: its small shape (two CTAs per SM) takes 43 us for 9..64 rows of a
+// 4096 -> 14336 layer where the fused kernel's two-block form takes 61 us for 9..16 rows.
+constexpr int64_t kQmmMinRows = 9;
 
 static int core_workspace_bytes(const LayerCore& c, int64_t rows, size_t* out_bytes) {
     if (!out_bytes) return fail("NULL argument");

@@ -145,8 +145,9 @@ cudaError_t launch_finish_and_reduce_padded(const float* raw, const __half* down
 
 // ---- tensor-core product for many rows (kernels_qmm.cu) ---------------------------------------------------
 struct QmmPlan {
-    int splits;        // CTAs that share one (128 columns x 256 tokens) output tile along the input axis
-    int token_tiles;   // ceil(rows / 512)
+    int splits;        // CTAs that share one (128 columns x token tile) output tile along the input axis
+    int token_tiles;   // ceil(rows / 512), or ceil(rows / 64) for the small shape
+    bool small;        // up to 64 rows: 64 tokens per CTA, two CTAs per SM
 };
 QmmPlan plan_qmm(int in, int out, int64_t rows);
 size_t qmm_partial_bytes(const QmmPlan& plan, int out, int64_t rows);

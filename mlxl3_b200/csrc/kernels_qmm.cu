@@ -37,22 +37,38 @@ namespace b200exl3 {
 namespace {
 
 constexpr int kStages = 3;            // decoded A stages in flight
-constexpr int kBSlots = 5;            // activation half-stages in flight
 // packed stages (4 tile rows x 8 tiles = 1024*K bytes) in flight: a 16 KiB ring, at most 8 slots
 constexpr int raw_depth(int k) { return 16 / k > 8 ? 8 : 16 / k; }
 constexpr int kRawDepthMax = 8;
 constexpr uint32_t kRawBytes = 16 * 1024;
-constexpr int kTokHalf = 256;         // tokens per accumulator half = MMA N
-constexpr int kTokTile = 2 * kTokHalf;   // tokens per CTA
-constexpr int kDecoderGroups = 2;     // groups of eight decoder warps that take alternate stages
-constexpr int kGroupWarps = 8;        // (tile row of the stage, quad of the 8-tile row)
-constexpr int kDecoders = kDecoderGroups * kGroupWarps;
+constexpr int kGroupWarps = 8;        // decoder warps of a group: (tile row of the stage, quad of the 8-tile row)
 // Warp roles.  The single-thread roles take the lowest warp numbers: the scheduler favours older warps, and a
 // producer starved by spinning decoder warps stalls the whole pipeline.
 constexpr int kMmaWarp = 0, kActWarp = 1, kWeightWarp = 2, kFirstDecoder = 4;
-constexpr int kThreads = 32 * (kFirstDecoder + kDecoders);
 constexpr uint32_t kAStageBytes = 128 * 128;           // 128 rows x 64 fp16
-constexpr uint32_t kBSlotBytes = kTokHalf * 128;       // 256 rows x 64 fp16
+
+// Two shapes of the same kernel.  Large (more than 64 rows): a CTA holds up to 512 tokens (two accumulator
+// halves of 256), sixteen decoder warps in two groups on alternate stages, one CTA per SM.  Small (up to 64
+// rows): 64 tokens per CTA, eight decoder warps, under half of the shared memory and registers, so two CTAs
+// share an SM and twice as many warps decode -- these batches are bound by the decode, not by the MMAs.
+template <bool SMALL>
+struct QmmShape {
+    static constexpr int kTokHalf = SMALL ? 64 : 256;          // tokens per accumulator half = MMA N
+    static constexpr int kMaxHalves = SMALL ? 1 : 2;
+    static constexpr int kTokTile = kTokHalf * kMaxHalves;     // tokens per CTA
+    static constexpr int kDecoderGroups = SMALL ? 1 : 2;       // groups of eight decoder warps that take alternate stages
+    static constexpr int kDecoders = kDecoderGroups * kGroupWarps;
+    static constexpr int kThreads = 32 * (kFirstDecoder + kDecoders);
+    static constexpr int kMinBlocks = SMALL ? 2 : 1;
+    static constexpr int kBSlots = SMALL ? 4 : 5;              // activation half-stages in flight
+    static constexpr uint32_t kBSlotBytes = kTokHalf * 128;    // kTokHalf rows x 64 fp16
+    static constexpr uint32_t kInstrDesc = (1u << 4)                      // D = fp32
+                                           | (0u << 7) | (0u << 10)       // A, B = fp16
+                                           | (0u << 15) | (0u << 16)      // both K-major
+                                           | ((kTokHalf >> 3) << 17)      // N
+                                           | ((128u >> 4) << 24);         // M
+    static constexpr size_t kSmemBytes = kStages * kAStageBytes + kBSlots * kBSlotBytes + kRawBytes + 1024;
+};
 
 struct QmmArgs {
     const uint32_t* wq;        // quad layout
@@ -76,12 +92,6 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_byte_addr) {
     d |= static_cast<uint64_t>(2) << 61;                 // SWIZZLE_128B
     return d;
 }
-
-constexpr uint32_t kInstrDesc = (1u << 4)                      // D = fp32
-                                | (0u << 7) | (0u << 10)       // A, B = fp16
-                                | (0u << 15) | (0u << 16)      // both K-major
-                                | ((kTokHalf >> 3) << 17)      // N
-                                | ((128u >> 4) << 24);         // M
 
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t cols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(smem_dst)), "r"(cols) : "memory");
@@ -149,15 +159,16 @@ __device__ __forceinline__ bool qmm_wait_warp(uint64_t* bar, uint32_t parity, vo
     return mbar_test_wait(bar, parity) || qmm_wait(bar, parity, cta_failed);
 }
 
-template <int K, int CB>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int K, int CB, bool SMALL>
+__global__ void __launch_bounds__(QmmShape<SMALL>::kThreads, QmmShape<SMALL>::kMinBlocks)
 qmm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, const QmmArgs p) {
+    using S = QmmShape<SMALL>;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int kQuadWords = 32 * K;                       // four interleaved tiles
     constexpr int kRawStageWords = 8 * kQuadWords;           // 4 tile rows x 2 quads
     constexpr uint32_t kRawStageBytes = kRawStageWords * 4;
     constexpr int kRawDepth = raw_depth(K);
-    __shared__ __align__(8) uint64_t full_a[kStages], done[kStages], full_b[kBSlots], accum_bar;
+    __shared__ __align__(8) uint64_t full_a[kStages], done[kStages], full_b[S::kBSlots], accum_bar;
     __shared__ __align__(8) uint64_t raw_full[kRawDepthMax], raw_empty[kRawDepthMax];
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile int s_failed;
@@ -169,9 +180,9 @@ qmm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUt
     const int col_blocks = p.out >> 7;
     const int cblock = blockIdx.x % col_blocks;
     const int split = blockIdx.x / col_blocks;
-    const int tok0 = blockIdx.y * kTokTile;
-    const int halves = p.rows - tok0 > kTokHalf ? 2 : 1;      // accumulator halves this CTA fills
-    const uint32_t tmem_cols = halves * kTokHalf;
+    const int tok0 = blockIdx.y * S::kTokTile;
+    const int halves = (S::kMaxHalves == 2 && p.rows - tok0 > S::kTokHalf) ? 2 : 1;      // accumulator halves this CTA fills
+    const uint32_t tmem_cols = halves * S::kTokHalf;
     const int st0 = static_cast<int>(static_cast<int64_t>(p.stages_total) * split / p.splits);
     const int st1 = static_cast<int>(static_cast<int64_t>(p.stages_total) * (split + 1) / p.splits);
     const int nst = st1 - st0;
@@ -179,11 +190,11 @@ qmm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUt
     // shared memory: A stages | B slots | raw rings; the swizzled operands need 1024-byte alignment
     unsigned char* a_base = smem_raw + ((1024u - (smem_addr(smem_raw) & 1023u)) & 1023u);
     unsigned char* b_base = a_base + kStages * kAStageBytes;
-    uint32_t* raw_base = reinterpret_cast<uint32_t*>(b_base + kBSlots * kBSlotBytes);
+    uint32_t* raw_base = reinterpret_cast<uint32_t*>(b_base + S::kBSlots * S::kBSlotBytes);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) { mbar_init(&full_a[s], kGroupWarps); mbar_init(&done[s], 1); }
-        for (int s = 0; s < kBSlots; ++s) mbar_init(&full_b[s], 1);
+        for (int s = 0; s < S::kBSlots; ++s) mbar_init(&full_b[s], 1);
         mbar_init(&accum_bar, 1);
         for (int d = 0; d < kRawDepth; ++d) { mbar_init(&raw_full[d], 1); mbar_init(&raw_empty[d], kGroupWarps); }
         s_failed = 0;
@@ -212,7 +223,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUt
                    mbar_test_wait(&done[it % kStages], ((it / kStages) & 1u) ^ 1u);
         };
         bool ready = group < nst && stage_ready(group);
-        for (int it = group; it < nst; it += kDecoderGroups) {
+        for (int it = group; it < nst; it += S::kDecoderGroups) {
             const int s = it % kStages, rslot = it % kRawDepth;
             if (!__all_sync(0xffffffffu, ready)) {
                 // the packed stage has landed, and the MMAs that read this A stage last time are done
@@ -228,7 +239,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUt
             if constexpr (K >= 5) W0 = qw[geom.i0];
             const uint32_t w2[4] = {W2.x, W2.y, W2.z, W2.w}, w1[4] = {W1.x, W1.y, W1.z, W1.w},
                            w0[4] = {W0.x, W0.y, W0.z, W0.w};
-            ready = it + kDecoderGroups < nst && stage_ready(it + kDecoderGroups);
+            ready = it + S::kDecoderGroups < nst && stage_ready(it + S::kDecoderGroups);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 uint32_t a0, a1, a2, a3;
@@ -258,14 +269,14 @@ qmm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUt
             int slot = 0;
             for (int it = 0; it < nst && !s_failed; ++it) {
                 for (int h = 0; h < halves; ++h) {
-                    const int before = it * halves + h - kBSlots;     // the use of this slot one lap earlier
+                    const int before = it * halves + h - S::kBSlots;     // the use of this slot one lap earlier
                     if (before >= 0) {
                         const int st = before / halves;
                         if (!qmm_wait(&done[st % kStages], (st / kStages) & 1u, &s_failed)) break;
                     }
-                    mbar_expect_tx(&full_b[slot], kBSlotBytes);
-                    tma_load_2d(b_base + slot * kBSlotBytes, &xmap, (st0 + it) * 64, tok0 + h * kTokHalf, &full_b[slot]);
-                    if (++slot == kBSlots) slot = 0;
+                    mbar_expect_tx(&full_b[slot], S::kBSlotBytes);
+                    tma_load_2d(b_base + slot * S::kBSlotBytes, &xmap, (st0 + it) * 64, tok0 + h * S::kTokHalf, &full_b[slot]);
+                    if (++slot == S::kBSlots) slot = 0;
                 }
             }
             if (tr) tr[7] = global_ns();
@@ -290,7 +301,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUt
                 bool ok = mbar_test_wait(&full_a[it % kStages], (it / kStages) & 1u);
                 for (int h = 0; h < halves; ++h) {
                     const int u = it * halves + h;
-                    ok &= mbar_test_wait(&full_b[u % kBSlots], (u / kBSlots) & 1u);
+                    ok &= mbar_test_wait(&full_b[u % S::kBSlots], (u / S::kBSlots) & 1u);
                 }
                 return ok;
             };
@@ -302,17 +313,17 @@ qmm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUt
                     bool ok = true;
                     for (int h = 0; h < halves && ok; ++h) {
                         const int u = it * halves + h;
-                        ok = qmm_wait(&full_b[u % kBSlots], (u / kBSlots) & 1u, &s_failed);
+                        ok = qmm_wait(&full_b[u % S::kBSlots], (u / S::kBSlots) & 1u, &s_failed);
                     }
                     if (!ok) break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t a_addr = smem_addr(a_base + s * kAStageBytes);
                 for (int h = 0; h < halves; ++h) {
-                    const uint32_t b_addr = smem_addr(b_base + ((it * halves + h) % kBSlots) * kBSlotBytes);
+                    const uint32_t b_addr = smem_addr(b_base + ((it * halves + h) % S::kBSlots) * S::kBSlotBytes);
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk)                      // 4 x 16 inputs = one 64-input stage
-                        umma_f16(tmem + h * kTokHalf, umma_desc(a_addr + kk * 32), umma_desc(b_addr + kk * 32), kInstrDesc,
+                        umma_f16(tmem + h * S::kTokHalf, umma_desc(a_addr + kk * 32), umma_desc(b_addr + kk * 32), S::kInstrDesc,
                                  (it > 0 || kk > 0) ? 1u : 0u);
                 }
                 umma_commit(&done[s]);                                  // A stage and B slots free once these MMAs have read them
@@ -334,7 +345,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUt
         const int lq = warp & 3, cpart = dec >> 2;
         const int col = cblock * 128 + lq * 32 + lane;                  // this thread's output column = its TMEM lane
         float* dst = p.partials + (static_cast<int64_t>(split) * p.rows) * p.out + col;
-        const int c_span = static_cast<int>(tmem_cols) / (kDecoders / 4);
+        const int c_span = static_cast<int>(tmem_cols) / (S::kDecoders / 4);
         const int c_begin = cpart * c_span, c_end = c_begin + c_span;
         if (p.y == nullptr) {
             for (int c = c_begin; c < c_end; c += 32) {
@@ -413,24 +424,31 @@ EncodeFn encode_fn() {
     return fn;
 }
 
-template <int K, int CB>
-cudaError_t qmm_launch_one(const CUtensorMap& map, const CUtensorMap& wmap, const QmmArgs& p, dim3 grid, size_t smem, cudaStream_t stream) {
-    auto kernel = qmm_kernel<K, CB>;
+template <int K, int CB, bool SMALL>
+cudaError_t qmm_launch_shape(const CUtensorMap& map, const CUtensorMap& wmap, const QmmArgs& p, dim3 grid, cudaStream_t stream) {
+    using S = QmmShape<SMALL>;
+    constexpr size_t smem = S::kSmemBytes;
+    auto kernel = qmm_kernel<K, CB, SMALL>;
     static PerDeviceOnce attribute;                         // once per kernel and device
     if (attribute.needed()) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (e != cudaSuccess) return e;
         attribute.mark();
     }
-    kernel<<<grid, kThreads, smem, stream>>>(map, wmap, p);
+    kernel<<<grid, S::kThreads, smem, stream>>>(map, wmap, p);
     return cudaGetLastError();
 }
 
+template <int K, int CB>
+cudaError_t qmm_launch_one(const CUtensorMap& map, const CUtensorMap& wmap, const QmmArgs& p, dim3 grid, bool small, cudaStream_t stream) {
+    return small ? qmm_launch_shape<K, CB, true>(map, wmap, p, grid, stream) : qmm_launch_shape<K, CB, false>(map, wmap, p, grid, stream);
+}
+
 template <int K>
-cudaError_t qmm_launch_k(int cb, const CUtensorMap& map, const CUtensorMap& wmap, const QmmArgs& p, dim3 grid, size_t smem, cudaStream_t stream) {
-    if (cb == 0) return qmm_launch_one<K, 0>(map, wmap, p, grid, smem, stream);
-    if (cb == 1) return qmm_launch_one<K, 1>(map, wmap, p, grid, smem, stream);
-    return qmm_launch_one<K, 2>(map, wmap, p, grid, smem, stream);
+cudaError_t qmm_launch_k(int cb, const CUtensorMap& map, const CUtensorMap& wmap, const QmmArgs& p, dim3 grid, bool small, cudaStream_t stream) {
+    if (cb == 0) return qmm_launch_one<K, 0>(map, wmap, p, grid, small, stream);
+    if (cb == 1) return qmm_launch_one<K, 1>(map, wmap, p, grid, small, stream);
+    return qmm_launch_one<K, 2>(map, wmap, p, grid, small, stream);
 }
 
 }  // namespace
@@ -439,22 +457,27 @@ unsigned long long* g_qmm_trace = nullptr;
 static int g_qmm_splits = 0;                              // 0 = chosen by the cost model below
 void qmm_set_tuning(int splits) { g_qmm_splits = splits > 0 ? splits : 0; }
 
+constexpr int64_t kQmmSmallMaxRows = 64;     // one token tile: a second one would decode every weight twice
+
 QmmPlan plan_qmm(int in, int out, int64_t rows) {
     QmmPlan plan{};
+    plan.small = rows <= kQmmSmallMaxRows;
     const int col_blocks = out / 128;
-    plan.token_tiles = static_cast<int>((rows + kTokTile - 1) / kTokTile);
+    const int tile = plan.small ? QmmShape<true>::kTokTile : QmmShape<false>::kTokTile;
+    plan.token_tiles = static_cast<int>((rows + tile - 1) / tile);
     const int stages_total = in / 64;
     const int64_t base = static_cast<int64_t>(col_blocks) * plan.token_tiles;
     const int max_splits = std::max(1, stages_total / 8);     // every split keeps at least 8 stages
     if (g_qmm_splits) { plan.splits = std::min(g_qmm_splits, max_splits); return plan; }
-    // One CTA per SM (the operand rings take most of the shared memory).  Estimated time of a choice:
-    // waves x (stages per CTA + fixed prologue/epilogue) + the fp32 partials that several splits write and
-    // the separate output rotation reads back.
-    const double stage_us = rows > kTokHalf ? 0.6 : 0.35, fixed_us = 4.0;
+    // CTAs that run at once: one per SM for the large shape (the operand rings take most of the shared memory),
+    // two for the small one.  Estimated time of a choice: waves x (stages per CTA + fixed prologue/epilogue) + the
+    // fp32 partials that several splits write and the separate output rotation reads back.
+    const int64_t slots = static_cast<int64_t>(kSmCount) * (plan.small ? 2 : 1);
+    const double stage_us = plan.small ? 0.55 : (rows > 256 ? 0.6 : 0.35), fixed_us = 4.0;
     const double partial_us = static_cast<double>(rows) * out * 8.0 / 8.0e6;
     double best = 0;
     for (int s = 1; s <= max_splits; ++s) {
-        const int64_t waves = (base * s + kSmCount - 1) / kSmCount;
+        const int64_t waves = (base * s + slots - 1) / slots;
         // with one split the output rotation runs in the epilogue; more splits write fp32 partials and add a launch
         const double t = waves * (((stages_total + s - 1) / s) * stage_us + fixed_us) + (s > 1 ? s * partial_us + 5.0 : 0.0);
         if (s == 1 || t < best) { best = t; plan.splits = s; }
@@ -477,7 +500,7 @@ cudaError_t launch_qmm(const uint32_t* wq, int in, int out, int k, int cb, const
     CUtensorMap map;
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(in), static_cast<cuuint64_t>(rows)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(in) * sizeof(__half)};
-    const cuuint32_t box[2] = {64, kTokHalf};
+    const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(plan.small ? QmmShape<true>::kTokHalf : QmmShape<false>::kTokHalf)};
     const cuuint32_t elem[2] = {1, 1};
     if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(xhat), dims, strides, box, elem,
                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -499,16 +522,15 @@ cudaError_t launch_qmm(const uint32_t* wq, int in, int out, int k, int cb, const
     p.in = in; p.out = out; p.rows = static_cast<int>(rows); p.tiles_n = out / 16;
     p.splits = plan.splits; p.stages_total = in / 64; p.trace = g_qmm_trace;
     const dim3 grid(static_cast<unsigned>((out / 128) * plan.splits), static_cast<unsigned>(plan.token_tiles));
-    const size_t smem = kStages * kAStageBytes + kBSlots * kBSlotBytes + kRawBytes + 1024;
     switch (k) {
-        case 1: return qmm_launch_k<1>(cb, map, wmap, p, grid, smem, stream);
-        case 2: return qmm_launch_k<2>(cb, map, wmap, p, grid, smem, stream);
-        case 3: return qmm_launch_k<3>(cb, map, wmap, p, grid, smem, stream);
-        case 4: return qmm_launch_k<4>(cb, map, wmap, p, grid, smem, stream);
-        case 5: return qmm_launch_k<5>(cb, map, wmap, p, grid, smem, stream);
-        case 6: return qmm_launch_k<6>(cb, map, wmap, p, grid, smem, stream);
-        case 7: return qmm_launch_k<7>(cb, map, wmap, p, grid, smem, stream);
-        case 8: return qmm_launch_k<8>(cb, map, wmap, p, grid, smem, stream);
+        case 1: return qmm_launch_k<1>(cb, map, wmap, p, grid, plan.small, stream);
+        case 2: return qmm_launch_k<2>(cb, map, wmap, p, grid, plan.small, stream);
+        case 3: return qmm_launch_k<3>(cb, map, wmap, p, grid, plan.small, stream);
+        case 4: return qmm_launch_k<4>(cb, map, wmap, p, grid, plan.small, stream);
+        case 5: return qmm_launch_k<5>(cb, map, wmap, p, grid, plan.small, stream);
+        case 6: return qmm_launch_k<6>(cb, map, wmap, p, grid, plan.small, stream);
+        case 7: return qmm_launch_k<7>(cb, map, wmap, p, grid, plan.small, stream);
+        case 8: return qmm_launch_k<8>(cb, map, wmap, p, grid, plan.small, stream);
         default: return cudaErrorInvalidValue;
     }
 }

@@ -90,11 +90,15 @@ def test_fused_rotations_are_bit_exact(gpu, k, cb, rows):
     bias = (rng.standard_normal(384) * 0.3).astype(np.float16)
     layer = gpu.Exl3Linear(trellis, suh, svh, bias, k, cb)
     x = rng.standard_normal((rows, 1024)).astype(np.float16)
-    yhat = layer.forward_raw(oracle.prepare(x, suh))
-    assert np.array_equal(bits(layer.forward(x)), bits(oracle.finish(yhat, svh, bias)))
-    x32 = x.astype(np.float32) * 1.0009765625
-    yhat32 = layer.forward_raw(oracle.prepare(x32, suh))
-    assert np.array_equal(layer.forward(x32), oracle.finish(yhat32, svh, bias, y_dtype=oracle.F32))
+    gpu.set_option("qmm", 0)          # from 9 rows on a plain forward would take the tensor-core path: keep it on the fused kernel
+    try:
+        yhat = layer.forward_raw(oracle.prepare(x, suh))
+        assert np.array_equal(bits(layer.forward(x)), bits(oracle.finish(yhat, svh, bias)))
+        x32 = x.astype(np.float32) * 1.0009765625
+        yhat32 = layer.forward_raw(oracle.prepare(x32, suh))
+        assert np.array_equal(layer.forward(x32), oracle.finish(yhat32, svh, bias, y_dtype=oracle.F32))
+    finally:
+        gpu.set_option("qmm", 1)
 
 
 def test_rows_are_independent_and_deterministic(gpu):
