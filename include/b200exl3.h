@@ -216,8 +216,8 @@ int b200exl3_moe_workspace_bytes(const b200exl3_moe* handle, int64_t rows, size_
  * expert instead of reading out of bounds); scores [rows, top_k] routing weights in score_dtype (fp16 = 9 or
  * fp32 = 10); y [rows, in] in score_dtype (the reference's result dtype: fp16 products promoted by the scores).
  * Small batches run one activation row per (token, choice) slot against the slot's expert's columns.  From 33
- * slots and three slots per expert on, the slots are grouped by expert on the device (the reference's route_plan, native/src/moe.rs:66-182) into
- * segments of 16 rows, so that an expert's columns are decoded once per 16 rows that use them; rows are
+ * slots and two slots per expert on, the slots are grouped by expert on the device (the reference's route_plan, native/src/moe.rs:66-182) into
+ * segments of 8 rows, so that an expert's columns are decoded once per 8 rows that use them; rows are
  * processed in passes of at most 16384 slots.  No host synchronisation either way.
  * The workspace follows the rules of the linear layer's workspace. */
 int b200exl3_moe_forward(const b200exl3_moe* handle, const void* d_x, int x_dtype, int64_t rows,

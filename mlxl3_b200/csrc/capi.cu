@@ -653,10 +653,9 @@ static MoeLayout moe_layout(const b200exl3_moe* h, int64_t rows) {
     return l;
 }
 
-// Expert-sorted form, used from this many slots on: slots are grouped by expert into segments of 16 rows, so an
-// expert's columns are decoded once per 16 rows that use them instead of once per slot.
+// Expert-sorted form, used from this many slots on: slots are grouped by expert into segments of kMoeSegRows rows,
+// so an expert's columns are decoded once per segment instead of once per slot.
 constexpr int64_t kMoeSortedMinSlots = 33;
-constexpr int kMoeSegRows = 16;
 
 static int64_t moe_max_segments(const b200exl3_moe* h, int64_t slots) {
     return std::min<int64_t>(h->experts, slots) + slots / kMoeSegRows;   // one partly filled segment per expert at most
@@ -703,8 +702,8 @@ static MoeSortedLayout moe_sorted_layout(const b200exl3_moe* h, int64_t rows) {
 }
 
 static bool moe_sorted(const b200exl3_moe* h, int64_t rows) {
-    // worth it once experts see several rows each: below three slots per expert one row per slot is faster
-    return g_moe_sorted && rows * h->top_k >= std::max<int64_t>(kMoeSortedMinSlots, 3 * static_cast<int64_t>(h->experts)) &&
+    // worth it once experts see several rows each: below two slots per expert one row per slot is faster
+    return g_moe_sorted && rows * h->top_k >= std::max<int64_t>(kMoeSortedMinSlots, 2 * static_cast<int64_t>(h->experts)) &&
            2 * static_cast<size_t>(h->experts) + 1 <= 12 * 1024;
 }
 
@@ -795,7 +794,7 @@ int b200exl3_moe_forward(const b200exl3_moe* h, const void* d_x, int x_dtype, in
         for (int64_t r0 = 0; r0 < rows; r0 += chunk) {
             const int64_t n = std::min(chunk, rows - r0), slots = n * h->top_k;
             const uint32_t* sel = d_selected + r0 * h->top_k;
-            // 16 rows per segment against the columns of the segment's expert; segments past the count are skipped
+            // kMoeSegRows rows per segment against the columns of the segment's expert; segments past the count are skipped
             auto mapped = [&](const uint32_t* wq, const __half* xhat, int in, int width, int proj, int stride_blocks, float* yhat,
                               const QmvPlan& plan) {
                 const int out = segs * proj * width;

@@ -122,16 +122,19 @@ struct TpArgs {
 cudaError_t launch_tp_finish(const TpArgs& args, cudaStream_t stream);
 
 // Expert-sorted form for many slots (native/src/moe.rs:66-182 route_plan, 1001-1085): slots are grouped by expert
-// into segments of up to 16 rows, so that an expert's columns are decoded once per 16 rows that use them.
-//   seg_count[0]         number of segments
-//   seg_expert[s]        expert of segment s
-//   row_slot[16 s + r]   slot in row r of segment s, or 0xffffffff for a padding row
-//   slot_row[slot]       padded row 16 s + r that holds the slot
-// max_segments bounds the arrays (min(experts, slots) + slots / 16 always suffices).
+// into segments of up to kMoeSegRows rows (R below), so that an expert's columns are decoded once per R rows that
+// use them.  R = 8 is one block of rows of the fused kernel, whose one-block form runs two CTAs per SM and decodes
+// almost twice as fast per tile as the two-block form that 16 rows would need.
+//   seg_count[0]        number of segments
+//   seg_expert[s]       expert of segment s
+//   row_slot[R s + r]   slot in row r of segment s, or 0xffffffff for a padding row
+//   slot_row[slot]      padded row R s + r that holds the slot
+// max_segments bounds the arrays (min(experts, slots) + slots / R always suffices).
+constexpr int kMoeSegRows = 8;
 cudaError_t launch_route_plan(const uint32_t* selected, int64_t slots, int experts, int max_segments, int* seg_count,
                               uint32_t* seg_expert, uint32_t* row_slot, uint32_t* slot_row, cudaStream_t stream);
 // padded-row forms of the three glue kernels; activations and products are laid out per segment:
-// xhat[(s * proj + p) * 16 + r, :], products y[r, (s * proj + p) * width + col] with row stride max_segments * proj * width
+// xhat[(s * proj + p) * R + r, :], products y[r, (s * proj + p) * width + col] with row stride max_segments * proj * width
 cudaError_t launch_routed_prepare_padded(const void* x, int x_dtype, const __half* suh, const uint32_t* seg_expert,
                                          const uint32_t* row_slot, const int* seg_count, int experts, int top_k, int proj,
                                          int max_segments, int in, __half* xhat, cudaStream_t stream);

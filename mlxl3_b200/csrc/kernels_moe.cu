@@ -170,10 +170,10 @@ namespace b200exl3 {
 
 namespace {
 
-constexpr int kSegRows = 16;
+constexpr int kSegRows = kMoeSegRows;
 constexpr uint32_t kNoSlot = 0xffffffffu;
 
-// One CTA plans the whole batch: counts per expert, segments of 16 rows per expert in expert order, and the
+// One CTA plans the whole batch: counts per expert, segments of kSegRows rows per expert in expert order, and the
 // two maps between slots and padded rows.
 __global__ void __launch_bounds__(1024)
 route_plan_kernel(const uint32_t* __restrict__ selected, int64_t slots, int experts, int max_segments,
@@ -222,7 +222,7 @@ routed_prepare_padded_kernel(const void* __restrict__ x, int x_dtype, const __ha
     const int64_t total = static_cast<int64_t>(seg_count[0]) * proj * kSegRows * blocks_per_row;
     for (int64_t unit = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5); unit < total;
          unit += static_cast<int64_t>(gridDim.x) * kWarpsPerBlock) {
-        const int64_t out_row = unit / blocks_per_row;                   // (segment * proj + p) * 16 + r
+        const int64_t out_row = unit / blocks_per_row;                   // (segment * proj + p) * kSegRows + r
         const int col = static_cast<int>(unit % blocks_per_row) * 128 + lane * 4;
         const int r = static_cast<int>(out_row % kSegRows);
         const int64_t sp = out_row / kSegRows;
@@ -249,11 +249,11 @@ glu_down_input_padded_kernel(const float* __restrict__ ygu, const __half* __rest
     const int lane = threadIdx.x & 31;
     const int blocks_per_row = hidden >> 7;
     const int64_t total = static_cast<int64_t>(seg_count[0]) * kSegRows * blocks_per_row;
-    const int64_t row_stride = static_cast<int64_t>(max_segments) * 2 * hidden;       // products are [16, segments * 2 * hidden]
+    const int64_t row_stride = static_cast<int64_t>(max_segments) * 2 * hidden;       // products are [kSegRows, segments * 2 * hidden]
     const float scale = had_scale();
     for (int64_t unit = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5); unit < total;
          unit += static_cast<int64_t>(gridDim.x) * kWarpsPerBlock) {
-        const int64_t prow = unit / blocks_per_row;                      // segment * 16 + r
+        const int64_t prow = unit / blocks_per_row;                      // segment * kSegRows + r
         const int col = static_cast<int>(unit % blocks_per_row) * 128 + lane * 4;
         const int64_t seg = prow / kSegRows;
         const int r = static_cast<int>(prow - seg * kSegRows);
@@ -295,7 +295,7 @@ finish_and_reduce_padded_kernel(const float* __restrict__ raw, const __half* __r
     const int lane = threadIdx.x & 31;
     const int blocks_per_row = out >> 7;
     const int64_t total = rows * blocks_per_row;
-    const int64_t row_stride = static_cast<int64_t>(max_segments) * out;              // products are [16, segments * out]
+    const int64_t row_stride = static_cast<int64_t>(max_segments) * out;              // products are [kSegRows, segments * out]
     for (int64_t unit = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5); unit < total;
          unit += static_cast<int64_t>(gridDim.x) * kWarpsPerBlock) {
         const int64_t row = unit / blocks_per_row;

@@ -66,7 +66,7 @@ def test_switch_glu_matches_oracle(gpu, k, cb, experts, top_k, n_in, hidden, row
 
 
 def test_switch_glu_many_rows_and_repeated_experts(gpu):
-    """More than 32 slots: the expert-sorted form (segments of 16 rows per expert), several passes, every
+    """More than 32 slots: the expert-sorted form (segments of 8 rows per expert), several passes, every
     expert chosen many times, and experts that nobody chose."""
     rng = np.random.default_rng(77)
     experts, top_k, n_in, hidden, k, cb, rows = 12, 4, 256, 256, 3, 1, 150
