@@ -178,7 +178,7 @@ def run_ours(args) -> dict:
     from mlxl3_b200 import _lib
 
     if args.pdl:
-        ex.set_option("pdl", 1)
+        ex.set_option("pdl", int(args.pdl))
     graph = None
 
     def launch_all() -> None:

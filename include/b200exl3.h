@@ -224,6 +224,16 @@ int b200exl3_moe_forward(const b200exl3_moe* handle, const void* d_x, int x_dtyp
                          const uint32_t* d_selected, const void* d_scores, int score_dtype, void* d_y,
                          void* d_workspace, size_t workspace_bytes, b200exl3_stream stream);
 
+/* ---- router: stable top-k ----------------------------------------------------------------------------------
+ * Replaces router::topk / routes (native/src/router.rs:28-120, native/shaders/router_topk.h:1-34): values
+ * [rows, experts] (fp16 = 9 or fp32 = 10, experts <= 1024) -> indices [rows, top_k] (u32) and scores
+ * [rows, top_k] in the values' dtype.  Per row the top_k largest values in ascending order (the best last); equal
+ * values go to the higher expert index, +0 and -0 compare equal, NaN ranks above every number.  With `normalize`
+ * the scores are divided by their sum, added in slot order in the values' own type.  The outputs feed
+ * b200exl3_moe_forward directly, on the device. */
+int b200exl3_router_topk(const void* d_values, int dtype, int64_t rows, int experts, int top_k, int normalize,
+                         uint32_t* d_indices, void* d_scores, b200exl3_stream stream);
+
 /* ---- tensor parallelism over peer memory (one process per GPU of one node) -----------------------------------
  * No counterpart in the reference (single GPU).  Column-parallel shards need nothing from here.  A row-parallel
  * shard computes its fp32 partial product with b200exl3_linear_forward_partial; b200exl3_linear_finish_tp then

@@ -7,9 +7,9 @@ from ._lib import BF16, F16, F32, B200Exl3Error, LIB_PATH
 from .linear import DEFAULT, MCG, MUL1, Exl3Group, Exl3Linear, new_workspace, workspace_status
 from .moe import Exl3SwitchGlu
 from .runtime import DEFAULT_STREAM, DeviceBuffer, Event, Graph, PinnedBuffer, Stream, init, set_option
-from . import checkpoint, codec
+from . import checkpoint, codec, router
 
 __all__ = [
     "BF16", "F16", "F32", "B200Exl3Error", "LIB_PATH", "DEFAULT", "MCG", "MUL1", "Exl3Group", "Exl3Linear", "new_workspace", "workspace_status", "DEFAULT_STREAM",
-    "Exl3SwitchGlu", "DeviceBuffer", "Event", "Graph", "PinnedBuffer", "Stream", "init", "set_option", "checkpoint", "codec",
+    "Exl3SwitchGlu", "DeviceBuffer", "Event", "Graph", "PinnedBuffer", "Stream", "init", "set_option", "checkpoint", "codec", "router",
 ]

@@ -67,6 +67,7 @@ SIGNATURES = {
     "b200exl3_group_count": (c_int, [c_void_p]),
     "b200exl3_group_workspace_bytes": (c_int, [c_void_p, c_int64, POINTER(c_size_t)]),
     "b200exl3_group_forward": (c_int, [c_void_p, c_void_p, c_int, c_int64, POINTER(c_void_p), c_void_p, c_size_t, c_void_p]),
+    "b200exl3_router_topk": (c_int, [c_void_p, c_int, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "b200exl3_tp_buffer_bytes": (c_int, [c_int, c_int, POINTER(c_size_t)]),
     "b200exl3_tp_alloc": (c_int, [c_int, c_int, POINTER(c_void_p), c_char_p]),
     "b200exl3_tp_open": (c_int, [c_char_p, POINTER(c_void_p)]),

@@ -871,6 +871,19 @@ int b200exl3_moe_forward(const b200exl3_moe* h, const void* d_x, int x_dtype, in
 }
 
 
+/* ---- router ------------------------------------------------------------------------------------------------ */
+
+int b200exl3_router_topk(const void* d_values, int dtype, int64_t rows, int experts, int top_k, int normalize,
+                         uint32_t* d_indices, void* d_scores, b200exl3_stream s) {
+    if (rows <= 0 || experts <= 0 || experts > 1024) return fail("native router accepts positive rows and at most 1024 experts");
+    if (top_k <= 0 || top_k > experts) return fail("invalid router top-k");
+    if (dtype != kF16 && dtype != kF32) return fail("native router expects FP16 or FP32 values");
+    if (rows * static_cast<int64_t>(top_k) > INT32_MAX || rows * static_cast<int64_t>(experts) > INT32_MAX) return fail("router index overflow");
+    if (!d_values || !d_indices || !d_scores) return fail("NULL buffer");
+    return check(launch_router_topk(d_values, dtype, rows, experts, top_k, normalize != 0, d_indices, d_scores, as_stream(s)),
+                 "router kernel");
+}
+
 /* ---- tensor parallelism over peer memory ------------------------------------------------------------ */
 
 int b200exl3_tp_buffer_bytes(int world, int max_units, size_t* out_bytes) {

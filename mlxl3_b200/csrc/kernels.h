@@ -146,6 +146,11 @@ cudaError_t launch_finish_and_reduce_padded(const float* raw, const __half* down
                                             const uint32_t* slot_row, int experts, const void* scores, int score_dtype,
                                             int64_t rows, int top_k, int out, int max_segments, void* y, cudaStream_t stream);
 
+// ---- router (kernels_router.cu) --------------------------------------------------------------------------
+// stable top-k per row with index tie-break; values and scores fp16 or fp32; experts <= 1024
+cudaError_t launch_router_topk(const void* values, int dtype, int64_t rows, int experts, int k, bool normalize,
+                               uint32_t* indices, void* scores, cudaStream_t stream);
+
 // ---- tensor-core product for many rows (kernels_qmm.cu) ---------------------------------------------------
 struct QmmPlan {
     int splits;        // CTAs that share one (128 columns x token tile) output tile along the input axis
