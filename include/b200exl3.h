@@ -217,7 +217,8 @@ int b200exl3_moe_workspace_bytes(const b200exl3_moe* handle, int64_t rows, size_
  * fp32 = 10); y [rows, in] in score_dtype (the reference's result dtype: fp16 products promoted by the scores).
  * Small batches run one activation row per (token, choice) slot against the slot's expert's columns.  From 33
  * slots and two slots per expert on, the slots are grouped by expert on the device (the reference's route_plan, native/src/moe.rs:66-182) into
- * segments of 8 rows, so that an expert's columns are decoded once per 8 rows that use them; rows are
+ * segments of 8 rows (fused kernel) or, from 12 slots per expert on, of 64 rows (tensor cores), so that an expert's
+ * columns are decoded once per segment; rows are
  * processed in passes of at most 16384 slots.  No host synchronisation either way.
  * The workspace follows the rules of the linear layer's workspace. */
 int b200exl3_moe_forward(const b200exl3_moe* handle, const void* d_x, int x_dtype, int64_t rows,

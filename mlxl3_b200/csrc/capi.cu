@@ -657,8 +657,13 @@ static MoeLayout moe_layout(const b200exl3_moe* h, int64_t rows) {
 // so an expert's columns are decoded once per segment instead of once per slot.
 constexpr int64_t kMoeSortedMinSlots = 33;
 
-static int64_t moe_max_segments(const b200exl3_moe* h, int64_t slots) {
-    return std::min<int64_t>(h->experts, slots) + slots / kMoeSegRows;   // one partly filled segment per expert at most
+static int64_t moe_max_segments(const b200exl3_moe* h, int64_t slots, int seg_rows) {
+    return std::min<int64_t>(h->experts, slots) + slots / seg_rows;   // one partly filled segment per expert at most
+}
+// Segments of 8 rows run in the fused kernel; once most experts see many rows, segments of 64 rows run on the tensor cores.
+constexpr int64_t kMoeTensorSlotsPerExpert = 12;
+static int moe_seg_rows(const b200exl3_moe* h, int64_t rows) {
+    return g_qmm_enabled && rows * h->top_k >= kMoeTensorSlotsPerExpert * h->experts ? kQmmSegRows : kMoeSegRows;
 }
 // rows per pass (bounds the scratch); the passes of a call get equal shares
 constexpr int64_t kMoeSortedPassSlots = 16384;
@@ -670,15 +675,17 @@ static int64_t moe_sorted_chunk_rows(const b200exl3_moe* h, int64_t rows) {
 
 struct MoeSortedLayout {
     size_t counters, counter_bytes, seg_count, seg_expert, row_slot, slot_row, xgu, ygu, xdown, ydown, partials, total;
-    int max_segments;
+    int max_segments, seg_rows;
     QmvPlan gu_plan, down_plan;
 };
 
 static MoeSortedLayout moe_sorted_layout(const b200exl3_moe* h, int64_t rows) {
     MoeSortedLayout l{};
     const int64_t slots = moe_sorted_chunk_rows(h, rows) * h->top_k;
-    const int64_t segs = moe_max_segments(h, slots);
+    const int seg_rows = moe_seg_rows(h, rows);
+    const int64_t segs = moe_max_segments(h, slots, seg_rows);
     l.max_segments = static_cast<int>(segs);
+    l.seg_rows = seg_rows;
     l.gu_plan = plan_qmv(h->in, static_cast<int>(segs * 2 * h->hidden), h->k, kMoeSegRows);
     l.down_plan = plan_qmv(h->hidden, static_cast<int>(segs * h->in), h->k, kMoeSegRows);
     size_t at = kCounterBytes;
@@ -688,15 +695,16 @@ static MoeSortedLayout moe_sorted_layout(const b200exl3_moe* h, int64_t rows) {
     l.counters = at; at += l.counter_bytes;
     l.seg_count = at; at += 256;
     l.seg_expert = at; at += round256(static_cast<size_t>(segs) * sizeof(uint32_t));
-    l.row_slot = at; at += round256(static_cast<size_t>(segs) * kMoeSegRows * sizeof(uint32_t));
+    l.row_slot = at; at += round256(static_cast<size_t>(segs) * seg_rows * sizeof(uint32_t));
     l.slot_row = at; at += round256(static_cast<size_t>(slots) * sizeof(uint32_t));
-    l.xgu = at; at += round256(static_cast<size_t>(segs) * 2 * kMoeSegRows * h->in * sizeof(__half));
-    l.ygu = at; at += round256(static_cast<size_t>(segs) * 2 * kMoeSegRows * h->hidden * sizeof(float));
-    l.xdown = at; at += round256(static_cast<size_t>(segs) * kMoeSegRows * h->hidden * sizeof(__half));
-    l.ydown = at; at += round256(static_cast<size_t>(segs) * kMoeSegRows * h->in * sizeof(float));
+    l.xgu = at; at += round256(static_cast<size_t>(segs) * 2 * seg_rows * h->in * sizeof(__half));
+    l.ygu = at; at += round256(static_cast<size_t>(segs) * 2 * seg_rows * h->hidden * sizeof(float));
+    l.xdown = at; at += round256(static_cast<size_t>(segs) * seg_rows * h->hidden * sizeof(__half));
+    l.ydown = at; at += round256(static_cast<size_t>(segs) * seg_rows * h->in * sizeof(float));
     l.partials = at;
-    at += std::max(qmv_partial_bytes(l.gu_plan, static_cast<int>(segs * 2 * h->hidden), kMoeSegRows),
-                   qmv_partial_bytes(l.down_plan, static_cast<int>(segs * h->in), kMoeSegRows));
+    if (seg_rows == kMoeSegRows)
+        at += std::max(qmv_partial_bytes(l.gu_plan, static_cast<int>(segs * 2 * h->hidden), kMoeSegRows),
+                       qmv_partial_bytes(l.down_plan, static_cast<int>(segs * h->in), kMoeSegRows));
     l.total = at;
     return l;
 }
@@ -788,7 +796,7 @@ int b200exl3_moe_forward(const b200exl3_moe* h, const void* d_x, int x_dtype, in
         float* ygu = reinterpret_cast<float*>(base + l.ygu);
         __half* xdown = reinterpret_cast<__half*>(base + l.xdown);
         float* ydown = reinterpret_cast<float*>(base + l.ydown);
-        const int segs = l.max_segments;
+        const int segs = l.max_segments, seg_rows = l.seg_rows;
         const int64_t chunk = moe_sorted_chunk_rows(h, rows);
         B200_TRY(cudaMemsetAsync(base + l.counters, 0, l.counter_bytes, stream), "clear arrival counters");
         for (int64_t r0 = 0; r0 < rows; r0 += chunk) {
@@ -812,17 +820,28 @@ int b200exl3_moe_forward(const b200exl3_moe* h, const void* d_x, int x_dtype, in
                 a.map_blocks = width / 128; a.map_proj = proj; a.map_stride_blocks = stride_blocks; a.map_experts = h->experts;
                 return launch_qmv(a, h->k, h->cb, exact, plan, stream);
             };
-            B200_TRY(launch_route_plan(sel, slots, h->experts, segs, seg_count, seg_expert, row_slot, slot_row, stream), "route plan");
+            // the same on the tensor cores: 64 rows per segment, one CTA per (segment, projection, 128 columns)
+            auto mapped_tensor = [&](const uint32_t* wq, const __half* xhat, int in, int width, int proj, int stride_blocks, float* yhat) {
+                return launch_qmm_mapped(wq, in, width, h->experts * proj * width / 16, h->k, h->cb, xhat, segs, proj, stride_blocks,
+                                         h->experts, seg_expert, seg_count, yhat,
+                                         reinterpret_cast<unsigned int*>(base + kCounterBytes - sizeof(unsigned int)), stream);
+            };
+            const bool tensor = seg_rows == kQmmSegRows;
+            B200_TRY(launch_route_plan(sel, slots, h->experts, segs, seg_rows, seg_count, seg_expert, row_slot, slot_row, stream), "route plan");
             B200_TRY(launch_routed_prepare_padded(static_cast<const char*>(d_x) + static_cast<size_t>(r0) * h->in * x_size, x_dtype,
-                                                  h->gu_suh, seg_expert, row_slot, seg_count, h->experts, h->top_k, 2, segs, h->in,
-                                                  xgu, stream), "routed prepare");
-            B200_TRY(mapped(h->gu_wq, xgu, h->in, h->hidden, 2, h->experts * (h->hidden / 128), ygu, l.gu_plan), "expert gate/up kernel");
+                                                  h->gu_suh, seg_expert, row_slot, seg_count, h->experts, h->top_k, 2, segs, seg_rows,
+                                                  h->in, xgu, stream), "routed prepare");
+            B200_TRY(tensor ? mapped_tensor(h->gu_wq, xgu, h->in, h->hidden, 2, h->experts * (h->hidden / 128), ygu)
+                            : mapped(h->gu_wq, xgu, h->in, h->hidden, 2, h->experts * (h->hidden / 128), ygu, l.gu_plan),
+                     "expert gate/up kernel");
             B200_TRY(launch_glu_down_input_padded(ygu, h->gu_svh, h->down_suh, seg_expert, row_slot, seg_count, h->experts, segs,
-                                                  h->hidden, h->hidden, xdown, stream), "SwiGLU glue");
-            B200_TRY(mapped(h->down_wq, xdown, h->hidden, h->in, 1, 0, ydown, l.down_plan), "expert down kernel");
+                                                  seg_rows, h->hidden, h->hidden, xdown, stream), "SwiGLU glue");
+            B200_TRY(tensor ? mapped_tensor(h->down_wq, xdown, h->hidden, h->in, 1, 0, ydown)
+                            : mapped(h->down_wq, xdown, h->hidden, h->in, 1, 0, ydown, l.down_plan),
+                     "expert down kernel");
             B200_TRY(launch_finish_and_reduce_padded(ydown, h->down_svh, sel, slot_row, h->experts,
                                                      static_cast<const char*>(d_scores) + static_cast<size_t>(r0) * h->top_k * score_size,
-                                                     score_dtype, n, h->top_k, h->in, segs,
+                                                     score_dtype, n, h->top_k, h->in, segs, seg_rows,
                                                      static_cast<char*>(d_y) + static_cast<size_t>(r0) * h->in * score_size, stream),
                      "expert reduction");
         }

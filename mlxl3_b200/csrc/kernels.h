@@ -122,29 +122,30 @@ struct TpArgs {
 cudaError_t launch_tp_finish(const TpArgs& args, cudaStream_t stream);
 
 // Expert-sorted form for many slots (native/src/moe.rs:66-182 route_plan, 1001-1085): slots are grouped by expert
-// into segments of up to kMoeSegRows rows (R below), so that an expert's columns are decoded once per R rows that
-// use them.  R = 8 is one block of rows of the fused kernel, whose one-block form runs two CTAs per SM and decodes
-// almost twice as fast per tile as the two-block form that 16 rows would need.
+// into segments of up to R rows (seg_rows), so that an expert's columns are decoded once per R rows that use them.
+// R = kMoeSegRows = 8 is one block of rows of the fused kernel, whose one-block form runs two CTAs per SM and decodes
+// almost twice as fast per tile as the two-block form that 16 rows would need; R = kQmmSegRows = 64 is the token tile
+// of the small tensor-core shape, for batches that give most experts many rows.
 //   seg_count[0]        number of segments
 //   seg_expert[s]       expert of segment s
 //   row_slot[R s + r]   slot in row r of segment s, or 0xffffffff for a padding row
 //   slot_row[slot]      padded row R s + r that holds the slot
 // max_segments bounds the arrays (min(experts, slots) + slots / R always suffices).
 constexpr int kMoeSegRows = 8;
-cudaError_t launch_route_plan(const uint32_t* selected, int64_t slots, int experts, int max_segments, int* seg_count,
+cudaError_t launch_route_plan(const uint32_t* selected, int64_t slots, int experts, int max_segments, int seg_rows, int* seg_count,
                               uint32_t* seg_expert, uint32_t* row_slot, uint32_t* slot_row, cudaStream_t stream);
 // padded-row forms of the three glue kernels; activations and products are laid out per segment:
 // xhat[(s * proj + p) * R + r, :], products y[r, (s * proj + p) * width + col] with row stride max_segments * proj * width
 cudaError_t launch_routed_prepare_padded(const void* x, int x_dtype, const __half* suh, const uint32_t* seg_expert,
                                          const uint32_t* row_slot, const int* seg_count, int experts, int top_k, int proj,
-                                         int max_segments, int in, __half* xhat, cudaStream_t stream);
+                                         int max_segments, int seg_rows, int in, __half* xhat, cudaStream_t stream);
 cudaError_t launch_glu_down_input_padded(const float* ygu, const __half* gu_svh, const __half* down_suh,
                                          const uint32_t* seg_expert, const uint32_t* row_slot, const int* seg_count,
-                                         int experts, int max_segments, int hidden, int logical_hidden, __half* xhat,
+                                         int experts, int max_segments, int seg_rows, int hidden, int logical_hidden, __half* xhat,
                                          cudaStream_t stream);
 cudaError_t launch_finish_and_reduce_padded(const float* raw, const __half* down_svh, const uint32_t* selected,
                                             const uint32_t* slot_row, int experts, const void* scores, int score_dtype,
-                                            int64_t rows, int top_k, int out, int max_segments, void* y, cudaStream_t stream);
+                                            int64_t rows, int top_k, int out, int max_segments, int seg_rows, void* y, cudaStream_t stream);
 
 // ---- router (kernels_router.cu) --------------------------------------------------------------------------
 // stable top-k per row with index tie-break; values and scores fp16 or fp32; experts <= 1024
@@ -165,6 +166,12 @@ size_t qmm_partial_bytes(const QmmPlan& plan, int out, int64_t rows);
 cudaError_t launch_qmm(const uint32_t* wq, int in, int out, int k, int cb, const __half* xhat, int64_t rows,
                        const QmmPlan& plan, float* partials, unsigned int* error, const __half* svh, const __half* bias,
                        void* y, int y_dtype, cudaStream_t stream);
+// Expert-mapped form of the small shape: segment s = 64 padded rows xhat[(s * proj + p) * 64 + r, :] that all use expert
+// seg_expert[s]; products[r, (s * proj + p) * width + col] (fp32, row stride max_segments * proj * width).
+constexpr int kQmmSegRows = 64;
+cudaError_t launch_qmm_mapped(const uint32_t* wq, int in, int width, int bank_tiles_n, int k, int cb, const __half* xhat,
+                              int max_segments, int proj, int stride_blocks, int experts, const uint32_t* seg_expert,
+                              const int* seg_count, float* products, unsigned int* error, cudaStream_t stream);
 void qmm_set_tuning(int splits);   // force the number of input splits (0 = automatic)
 
 // ---- weight layout (kernels_codec.cu) -----------------------------------------------------------------

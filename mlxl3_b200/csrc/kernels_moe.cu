@@ -170,20 +170,19 @@ namespace b200exl3 {
 
 namespace {
 
-constexpr int kSegRows = kMoeSegRows;
 constexpr uint32_t kNoSlot = 0xffffffffu;
 
-// One CTA plans the whole batch: counts per expert, segments of kSegRows rows per expert in expert order, and the
+// One CTA plans the whole batch: counts per expert, segments of seg_rows rows per expert in expert order, and the
 // two maps between slots and padded rows.
 __global__ void __launch_bounds__(1024)
-route_plan_kernel(const uint32_t* __restrict__ selected, int64_t slots, int experts, int max_segments,
+route_plan_kernel(const uint32_t* __restrict__ selected, int64_t slots, int experts, int max_segments, int seg_rows,
                   int* __restrict__ seg_count, uint32_t* __restrict__ seg_expert, uint32_t* __restrict__ row_slot,
                   uint32_t* __restrict__ slot_row) {
     extern __shared__ int s_mem[];
     int* count = s_mem;                 // [experts] rows per expert, then running position
     int* base = s_mem + experts;        // [experts + 1] first segment of each expert
     for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
-    for (int64_t r = threadIdx.x; r < static_cast<int64_t>(max_segments) * kSegRows; r += blockDim.x) row_slot[r] = kNoSlot;
+    for (int64_t r = threadIdx.x; r < static_cast<int64_t>(max_segments) * seg_rows; r += blockDim.x) row_slot[r] = kNoSlot;
     __syncthreads();
     // One thread per expert walks the slots in order: a slot's position among its expert's rows is the number
     // of earlier slots with the same expert, so the plan (and with it the summation order of every row's
@@ -197,7 +196,7 @@ route_plan_kernel(const uint32_t* __restrict__ selected, int64_t slots, int expe
     __syncthreads();
     if (threadIdx.x == 0) {
         int at = 0;
-        for (int e = 0; e < experts; ++e) { base[e] = at; at += (count[e] + kSegRows - 1) / kSegRows; }
+        for (int e = 0; e < experts; ++e) { base[e] = at; at += (count[e] + seg_rows - 1) / seg_rows; }
         base[experts] = at;
         seg_count[0] = min(at, max_segments);
     }
@@ -207,28 +206,28 @@ route_plan_kernel(const uint32_t* __restrict__ selected, int64_t slots, int expe
     for (int64_t s = threadIdx.x; s < slots; s += blockDim.x) {
         const int e = min(static_cast<int>(selected[s]), experts - 1);
         const int pos = static_cast<int>(slot_row[s]);
-        const int64_t row = static_cast<int64_t>(base[e] + pos / kSegRows) * kSegRows + pos % kSegRows;
+        const int64_t row = static_cast<int64_t>(base[e] + pos / seg_rows) * seg_rows + pos % seg_rows;
         slot_row[s] = static_cast<uint32_t>(row);
-        if (row < static_cast<int64_t>(max_segments) * kSegRows) row_slot[row] = static_cast<uint32_t>(s);
+        if (row < static_cast<int64_t>(max_segments) * seg_rows) row_slot[row] = static_cast<uint32_t>(s);
     }
 }
 
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 routed_prepare_padded_kernel(const void* __restrict__ x, int x_dtype, const __half* __restrict__ suh,
                              const uint32_t* __restrict__ seg_expert, const uint32_t* __restrict__ row_slot,
-                             const int* __restrict__ seg_count, int top_k, int proj, int in, __half* __restrict__ xhat) {
+                             const int* __restrict__ seg_count, int top_k, int proj, int in, int seg_rows, __half* __restrict__ xhat) {
     const int lane = threadIdx.x & 31;
     const int blocks_per_row = in >> 7;
-    const int64_t total = static_cast<int64_t>(seg_count[0]) * proj * kSegRows * blocks_per_row;
+    const int64_t total = static_cast<int64_t>(seg_count[0]) * proj * seg_rows * blocks_per_row;
     for (int64_t unit = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5); unit < total;
          unit += static_cast<int64_t>(gridDim.x) * kWarpsPerBlock) {
-        const int64_t out_row = unit / blocks_per_row;                   // (segment * proj + p) * kSegRows + r
+        const int64_t out_row = unit / blocks_per_row;                   // (segment * proj + p) * seg_rows + r
         const int col = static_cast<int>(unit % blocks_per_row) * 128 + lane * 4;
-        const int r = static_cast<int>(out_row % kSegRows);
-        const int64_t sp = out_row / kSegRows;
+        const int r = static_cast<int>(out_row % seg_rows);
+        const int64_t sp = out_row / seg_rows;
         const int64_t seg = sp / proj;
         const int p = static_cast<int>(sp - seg * proj);
-        const uint32_t slot = row_slot[seg * kSegRows + r];
+        const uint32_t slot = row_slot[seg * seg_rows + r];
         __align__(8) __half h[4] = {__half(), __half(), __half(), __half()};
         if (slot != kNoSlot) {                                           // warp-uniform: one row per warp
             const __half* s = suh + (static_cast<int64_t>(seg_expert[seg]) * proj + p) * in + col;
@@ -244,19 +243,19 @@ routed_prepare_padded_kernel(const void* __restrict__ x, int x_dtype, const __ha
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 glu_down_input_padded_kernel(const float* __restrict__ ygu, const __half* __restrict__ gu_svh, const __half* __restrict__ down_suh,
                              const uint32_t* __restrict__ seg_expert, const uint32_t* __restrict__ row_slot,
-                             const int* __restrict__ seg_count, int max_segments, int hidden, int logical_hidden,
+                             const int* __restrict__ seg_count, int max_segments, int hidden, int logical_hidden, int seg_rows,
                              __half* __restrict__ xhat) {
     const int lane = threadIdx.x & 31;
     const int blocks_per_row = hidden >> 7;
-    const int64_t total = static_cast<int64_t>(seg_count[0]) * kSegRows * blocks_per_row;
-    const int64_t row_stride = static_cast<int64_t>(max_segments) * 2 * hidden;       // products are [kSegRows, segments * 2 * hidden]
+    const int64_t total = static_cast<int64_t>(seg_count[0]) * seg_rows * blocks_per_row;
+    const int64_t row_stride = static_cast<int64_t>(max_segments) * 2 * hidden;       // products are [seg_rows, segments * 2 * hidden]
     const float scale = had_scale();
     for (int64_t unit = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5); unit < total;
          unit += static_cast<int64_t>(gridDim.x) * kWarpsPerBlock) {
-        const int64_t prow = unit / blocks_per_row;                      // segment * kSegRows + r
+        const int64_t prow = unit / blocks_per_row;                      // segment * seg_rows + r
         const int col = static_cast<int>(unit % blocks_per_row) * 128 + lane * 4;
-        const int64_t seg = prow / kSegRows;
-        const int r = static_cast<int>(prow - seg * kSegRows);
+        const int64_t seg = prow / seg_rows;
+        const int r = static_cast<int>(prow - seg * seg_rows);
         __align__(8) __half h[4] = {__half(), __half(), __half(), __half()};
         if (row_slot[prow] != kNoSlot) {
             const int64_t expert = seg_expert[seg];
@@ -290,12 +289,12 @@ template <bool F32>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 finish_and_reduce_padded_kernel(const float* __restrict__ raw, const __half* __restrict__ down_svh,
                                 const uint32_t* __restrict__ selected, const uint32_t* __restrict__ slot_row, int experts,
-                                const void* __restrict__ scores, int64_t rows, int top_k, int out, int max_segments,
+                                const void* __restrict__ scores, int64_t rows, int top_k, int out, int max_segments, int seg_rows,
                                 void* __restrict__ y) {
     const int lane = threadIdx.x & 31;
     const int blocks_per_row = out >> 7;
     const int64_t total = rows * blocks_per_row;
-    const int64_t row_stride = static_cast<int64_t>(max_segments) * out;              // products are [kSegRows, segments * out]
+    const int64_t row_stride = static_cast<int64_t>(max_segments) * out;              // products are [seg_rows, segments * out]
     for (int64_t unit = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5); unit < total;
          unit += static_cast<int64_t>(gridDim.x) * kWarpsPerBlock) {
         const int64_t row = unit / blocks_per_row;
@@ -305,7 +304,7 @@ finish_and_reduce_padded_kernel(const float* __restrict__ raw, const __half* __r
         for (int t = 0; t < top_k; ++t) {
             const int64_t slot = row * top_k + t;
             const int64_t prow = slot_row[slot];
-            const float4 r = *reinterpret_cast<const float4*>(raw + (prow % kSegRows) * row_stride + (prow / kSegRows) * out + col);
+            const float4 r = *reinterpret_cast<const float4*>(raw + (prow % seg_rows) * row_stride + (prow / seg_rows) * out + col);
             __half h[4] = {__float2half_rn(r.x), __float2half_rn(r.y), __float2half_rn(r.z), __float2half_rn(r.w)};
             warp_hadamard128_f16(h, lane);
             const __half* sv = down_svh + static_cast<int64_t>(expert_of(selected, slot, experts)) * out + col;
@@ -328,45 +327,45 @@ finish_and_reduce_padded_kernel(const float* __restrict__ raw, const __half* __r
 
 }  // namespace
 
-cudaError_t launch_route_plan(const uint32_t* selected, int64_t slots, int experts, int max_segments, int* seg_count,
+cudaError_t launch_route_plan(const uint32_t* selected, int64_t slots, int experts, int max_segments, int seg_rows, int* seg_count,
                               uint32_t* seg_expert, uint32_t* row_slot, uint32_t* slot_row, cudaStream_t stream) {
     const size_t smem = (2 * static_cast<size_t>(experts) + 1) * sizeof(int);
     if (smem > 48 * 1024) return cudaErrorInvalidValue;
-    route_plan_kernel<<<1, 1024, smem, stream>>>(selected, slots, experts, max_segments, seg_count, seg_expert, row_slot, slot_row);
+    route_plan_kernel<<<1, 1024, smem, stream>>>(selected, slots, experts, max_segments, seg_rows, seg_count, seg_expert, row_slot, slot_row);
     return cudaGetLastError();
 }
 
 cudaError_t launch_routed_prepare_padded(const void* x, int x_dtype, const __half* suh, const uint32_t* seg_expert,
                                          const uint32_t* row_slot, const int* seg_count, int experts, int top_k, int proj,
-                                         int max_segments, int in, __half* xhat, cudaStream_t stream) {
+                                         int max_segments, int seg_rows, int in, __half* xhat, cudaStream_t stream) {
     (void)experts;
-    routed_prepare_padded_kernel<<<grid_for(static_cast<int64_t>(max_segments) * proj * kSegRows * (in / 128)), kWarpsPerBlock * 32, 0,
-                                   stream>>>(x, x_dtype, suh, seg_expert, row_slot, seg_count, top_k, proj, in, xhat);
+    routed_prepare_padded_kernel<<<grid_for(static_cast<int64_t>(max_segments) * proj * seg_rows * (in / 128)), kWarpsPerBlock * 32, 0,
+                                   stream>>>(x, x_dtype, suh, seg_expert, row_slot, seg_count, top_k, proj, in, seg_rows, xhat);
     return cudaGetLastError();
 }
 
 cudaError_t launch_glu_down_input_padded(const float* ygu, const __half* gu_svh, const __half* down_suh,
                                          const uint32_t* seg_expert, const uint32_t* row_slot, const int* seg_count,
-                                         int experts, int max_segments, int hidden, int logical_hidden, __half* xhat,
+                                         int experts, int max_segments, int seg_rows, int hidden, int logical_hidden, __half* xhat,
                                          cudaStream_t stream) {
     (void)experts;
-    glu_down_input_padded_kernel<<<grid_for(static_cast<int64_t>(max_segments) * kSegRows * (hidden / 128)), kWarpsPerBlock * 32, 0,
+    glu_down_input_padded_kernel<<<grid_for(static_cast<int64_t>(max_segments) * seg_rows * (hidden / 128)), kWarpsPerBlock * 32, 0,
                                    stream>>>(ygu, gu_svh, down_suh, seg_expert, row_slot, seg_count, max_segments, hidden,
-                                             logical_hidden, xhat);
+                                             logical_hidden, seg_rows, xhat);
     return cudaGetLastError();
 }
 
 cudaError_t launch_finish_and_reduce_padded(const float* raw, const __half* down_svh, const uint32_t* selected,
                                             const uint32_t* slot_row, int experts, const void* scores, int score_dtype,
-                                            int64_t rows, int top_k, int out, int max_segments, void* y, cudaStream_t stream) {
+                                            int64_t rows, int top_k, int out, int max_segments, int seg_rows, void* y, cudaStream_t stream) {
     if (rows == 0) return cudaSuccess;
     const unsigned grid = grid_for(rows * (out / 128));
     if (score_dtype == kF32)
         finish_and_reduce_padded_kernel<true><<<grid, kWarpsPerBlock * 32, 0, stream>>>(raw, down_svh, selected, slot_row, experts,
-                                                                                        scores, rows, top_k, out, max_segments, y);
+                                                                                        scores, rows, top_k, out, max_segments, seg_rows, y);
     else
         finish_and_reduce_padded_kernel<false><<<grid, kWarpsPerBlock * 32, 0, stream>>>(raw, down_svh, selected, slot_row, experts,
-                                                                                         scores, rows, top_k, out, max_segments, y);
+                                                                                         scores, rows, top_k, out, max_segments, seg_rows, y);
     return cudaGetLastError();
 }
 

@@ -80,6 +80,12 @@ struct QmmArgs {
     const __half* bias;          // [out] or nullptr
     void* y;                     // [rows, out] in y_dtype, or nullptr: store fp32 partial products
     int y_dtype;
+    // Expert-mapped mode (map_expert != nullptr; small shape, one split, fp32 products): the `out` axis is virtual,
+    // [segments, map_proj, map_blocks * 128]; segment s holds 64 padded rows that all use expert map_expert[s], whose
+    // columns start at column block map_proj_index * map_stride_blocks + expert * map_blocks of the bank.
+    const uint32_t* map_expert;
+    const int* map_count;      // segments in use; the CTAs of later segments return at once
+    int map_blocks, map_proj, map_stride_blocks, map_experts;
 };
 
 __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_byte_addr) {
@@ -181,6 +187,16 @@ qmm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUt
     const int cblock = blockIdx.x % col_blocks;
     const int split = blockIdx.x / col_blocks;
     const int tok0 = blockIdx.y * S::kTokTile;
+    int wblock = cblock;            // column block of the weight array
+    int brow0 = tok0;               // first row of the activation tile
+    if (p.map_expert != nullptr) {
+        const int sp = cblock / p.map_blocks, j = cblock - sp * p.map_blocks;
+        const int seg = sp / p.map_proj, proj = sp - seg * p.map_proj;
+        if (seg >= *p.map_count) return;                          // uniform for the CTA; nothing is allocated yet
+        const int expert = min(static_cast<int>(p.map_expert[seg]), p.map_experts - 1);
+        wblock = proj * p.map_stride_blocks + expert * p.map_blocks + j;
+        brow0 = sp * S::kTokTile;
+    }
     const int halves = (S::kMaxHalves == 2 && p.rows - tok0 > S::kTokHalf) ? 2 : 1;      // accumulator halves this CTA fills
     const uint32_t tmem_cols = halves * S::kTokHalf;
     const int st0 = static_cast<int>(static_cast<int64_t>(p.stages_total) * split / p.splits);
@@ -275,7 +291,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUt
                         if (!qmm_wait(&done[st % kStages], (st / kStages) & 1u, &s_failed)) break;
                     }
                     mbar_expect_tx(&full_b[slot], S::kBSlotBytes);
-                    tma_load_2d(b_base + slot * S::kBSlotBytes, &xmap, (st0 + it) * 64, tok0 + h * S::kTokHalf, &full_b[slot]);
+                    tma_load_2d(b_base + slot * S::kBSlotBytes, &xmap, (st0 + it) * 64, brow0 + h * S::kTokHalf, &full_b[slot]);
                     if (++slot == S::kBSlots) slot = 0;
                 }
             }
@@ -289,7 +305,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUt
             for (int it = 0; it < nst && !s_failed; ++it) {
                 if (!qmm_wait(&raw_empty[slot], par ^ 1u, &s_failed)) break;
                 mbar_expect_tx(&raw_full[slot], kRawStageBytes);
-                tma_load_2d(raw_base + slot * kRawStageWords, &wmap, cblock * (32 * K), 4 * (st0 + it), &raw_full[slot]);
+                tma_load_2d(raw_base + slot * kRawStageWords, &wmap, wblock * (32 * K), 4 * (st0 + it), &raw_full[slot]);
                 if (++slot == kRawDepth) { slot = 0; par ^= 1u; }
             }
         }
@@ -531,6 +547,52 @@ cudaError_t launch_qmm(const uint32_t* wq, int in, int out, int k, int cb, const
         case 6: return qmm_launch_k<6>(cb, map, wmap, p, grid, plan.small, stream);
         case 7: return qmm_launch_k<7>(cb, map, wmap, p, grid, plan.small, stream);
         case 8: return qmm_launch_k<8>(cb, map, wmap, p, grid, plan.small, stream);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+
+cudaError_t launch_qmm_mapped(const uint32_t* wq, int in, int width, int bank_tiles_n, int k, int cb, const __half* xhat,
+                              int max_segments, int proj, int stride_blocks, int experts, const uint32_t* seg_expert,
+                              const int* seg_count, float* products, unsigned int* error, cudaStream_t stream) {
+    using S = QmmShape<true>;
+    if (in % 128 || width % 128 || max_segments <= 0 || proj <= 0) return cudaErrorInvalidValue;
+    EncodeFn encode = encode_fn();
+    if (!encode) return cudaErrorNotSupported;
+    const int64_t rows = static_cast<int64_t>(max_segments) * proj * S::kTokTile;   // padded activation rows
+    const int out = max_segments * proj * width;                                   // virtual output width
+    CUtensorMap map, wmap;
+    const cuuint32_t elem[2] = {1, 1};
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(in), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(in) * sizeof(__half)};
+    const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(S::kTokHalf)};
+    if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(xhat), dims, strides, box, elem,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return cudaErrorInvalidValue;
+    const cuuint64_t wdims[2] = {static_cast<cuuint64_t>(bank_tiles_n) * 4 * k, static_cast<cuuint64_t>(in / 16)};
+    const cuuint64_t wstrides[1] = {static_cast<cuuint64_t>(bank_tiles_n) * 32 * k};
+    const cuuint32_t wbox[2] = {static_cast<cuuint32_t>(32 * k), 4};
+    if (encode(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint32_t*>(wq), wdims, wstrides, wbox, elem,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return cudaErrorInvalidValue;
+    QmmArgs p{};
+    p.wq = wq; p.partials = products; p.error = error;
+    p.in = in; p.out = out; p.rows = S::kTokTile; p.tiles_n = bank_tiles_n;
+    p.splits = 1; p.stages_total = in / 64; p.trace = nullptr;
+    p.map_expert = seg_expert; p.map_count = seg_count;
+    p.map_blocks = width / 128; p.map_proj = proj; p.map_stride_blocks = stride_blocks; p.map_experts = experts;
+    const dim3 grid(static_cast<unsigned>(out / 128), 1);
+    switch (k) {
+        case 1: return qmm_launch_k<1>(cb, map, wmap, p, grid, true, stream);
+        case 2: return qmm_launch_k<2>(cb, map, wmap, p, grid, true, stream);
+        case 3: return qmm_launch_k<3>(cb, map, wmap, p, grid, true, stream);
+        case 4: return qmm_launch_k<4>(cb, map, wmap, p, grid, true, stream);
+        case 5: return qmm_launch_k<5>(cb, map, wmap, p, grid, true, stream);
+        case 6: return qmm_launch_k<6>(cb, map, wmap, p, grid, true, stream);
+        case 7: return qmm_launch_k<7>(cb, map, wmap, p, grid, true, stream);
+        case 8: return qmm_launch_k<8>(cb, map, wmap, p, grid, true, stream);
         default: return cudaErrorInvalidValue;
     }
 }
