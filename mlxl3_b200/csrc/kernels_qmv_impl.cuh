@@ -232,8 +232,13 @@ qmv_kernel(const QmvArgs p) {
     const int wid = static_cast<int>(blockIdx.x) * WARPS + warp;
     const int UB = p.tiles_k * 8;
     const int T = UB * (p.out >> 7);
-    const int w0 = static_cast<int>(static_cast<int64_t>(T) * wid / W);
-    const int w1 = static_cast<int>(static_cast<int64_t>(T) * (wid + 1) / W);
+    // a * b / d with a * b below (T + 1) * W: 32-bit when that fits (64-bit division is emulated and slow)
+    const bool narrow = static_cast<unsigned long long>(T + 1) * static_cast<unsigned long long>(W) < 0xffffffffull;
+    auto muldiv = [narrow](unsigned int a, unsigned int b, unsigned int d) -> int {
+        return narrow ? static_cast<int>(a * b / d) : static_cast<int>(static_cast<unsigned long long>(a) * b / d);
+    };
+    const int w0 = muldiv(T, wid, W);
+    const int w1 = muldiv(T, wid + 1, W);
 
     unsigned char* mine = smem_raw + static_cast<size_t>(warp) * p.warp_smem;
     uint32_t* ring = reinterpret_cast<uint32_t*>(mine);                  // DEPTH rows of packed words
@@ -249,7 +254,7 @@ qmv_kernel(const QmvArgs p) {
     __shared__ int s_begin[WARPS + 1];
     __shared__ unsigned int s_arrived[WARPS + 2];            // per visited block: warps that staged their tile
     if (threadIdx.x <= WARPS)
-        s_begin[threadIdx.x] = static_cast<int>(static_cast<int64_t>(T) * (static_cast<int64_t>(blockIdx.x) * WARPS + threadIdx.x) / W);
+        s_begin[threadIdx.x] = muldiv(T, blockIdx.x * WARPS + threadIdx.x, W);
     if (threadIdx.x < WARPS + 2) s_arrived[threadIdx.x] = 0;
     if (lane == 0) {
 #pragma unroll
@@ -413,8 +418,10 @@ qmv_kernel(const QmvArgs p) {
         if (prev + 1 == static_cast<unsigned int>(__popc(mask))) {
             __threadfence_block();
             // CTA holding unit x: (ceil((x+1)*W/T) - 1) / WARPS
-            const int i_first = static_cast<int>((((static_cast<int64_t>(cblock) * UB + 1) * W - 1) / T) / WARPS);
-            const int i_last = static_cast<int>(((static_cast<int64_t>(cblock + 1) * UB * W - 1) / T) / WARPS);
+            const int i_first = narrow ? static_cast<int>(((static_cast<unsigned int>(cblock * UB + 1) * W - 1u) / T) / WARPS)
+                                       : static_cast<int>((((static_cast<int64_t>(cblock) * UB + 1) * W - 1) / T) / WARPS);
+            const int i_last = narrow ? static_cast<int>(((static_cast<unsigned int>((cblock + 1) * UB) * W - 1u) / T) / WARPS)
+                                      : static_cast<int>(((static_cast<int64_t>(cblock + 1) * UB * W - 1) / T) / WARPS);
             qmv_finish_block(p, cblock, mask, second, i_last - i_first + 1, static_cast<int>(blockIdx.x) - i_first, smem_raw,
                              lane);
             if (tracing) p.trace[blockIdx.x * 8 + 5] = global_ns();
