@@ -862,21 +862,25 @@ int b200exl3_moe_forward(const b200exl3_moe* h, const void* d_x, int x_dtype, in
             const int out = static_cast<int>(slots * proj * width);
             QmvArgs a{};
             a.wq = wq; a.xhat = xhat; a.xhat_group_stride = in;
+            if (!xhat) {                                      // fused routed rotation
+                a.x = static_cast<const char*>(d_x) + static_cast<size_t>(r0) * h->in * x_size;
+                a.suh = h->gu_suh;
+                a.map_top_k = h->top_k;
+            }
             a.counters = reinterpret_cast<unsigned int*>(base);
             a.error = reinterpret_cast<unsigned int*>(base + kCounterBytes - sizeof(unsigned int));
             a.partials = reinterpret_cast<float*>(base + l.partials);
             a.yhat = yhat;
             a.groups = 1; a.gcol0[0] = 0; a.gout[0] = out;
-            a.x_dtype = kF16; a.y_dtype = kF16;
+            a.x_dtype = xhat ? kF16 : x_dtype; a.y_dtype = kF16;
             a.in = in; a.out = out; a.rows = 1;
             a.tiles_n = h->experts * proj * width / 16;
             a.map_selected = sel; a.map_blocks = width / 128; a.map_proj = proj; a.map_stride_blocks = stride_blocks;
             a.map_experts = h->experts;
             return launch_qmv(a, h->k, h->cb, exact, plan_qmv(in, out, h->k, 1), stream);
         };
-        B200_TRY(launch_routed_prepare(static_cast<const char*>(d_x) + static_cast<size_t>(r0) * h->in * x_size, x_dtype, h->gu_suh,
-                                       sel, h->experts, h->top_k, 2, slots, h->in, xgu, stream), "routed prepare");
-        B200_TRY(mapped(h->gu_wq, xgu, h->in, h->hidden, 2, h->experts * (h->hidden / 128), ygu), "expert gate/up kernel");
+        // gate/up: the kernel rotates each slot's token row itself, with the input scales of the slot's expert
+        B200_TRY(mapped(h->gu_wq, nullptr, h->in, h->hidden, 2, h->experts * (h->hidden / 128), ygu), "expert gate/up kernel");
         B200_TRY(launch_glu_down_input(ygu, h->gu_svh, h->down_suh, sel, h->experts, slots, h->hidden, h->hidden, xdown, stream),
                  "SwiGLU glue");
         B200_TRY(mapped(h->down_wq, xdown, h->hidden, h->in, 1, 0, ydown), "expert down kernel");

@@ -67,6 +67,7 @@ struct QmvArgs {
     const uint32_t* map_selected;
     const int* map_count;      // optional: number of slots in use; the blocks of later slots are skipped
     int map_blocks, map_proj, map_stride_blocks, map_experts;
+    int map_top_k;             // with xhat == nullptr: slot s reads row s / map_top_k of x and rotates it with suh[expert, projection]
     // Tensor-parallel row shard (tp.world > 0; rotated output): the complete sum of a column block is
     // exchanged with the other ranks (unit = (tp_row0 + row) * out/128 + block) before the output rotation.
     TpPeers tp;
@@ -96,9 +97,6 @@ void qmv_set_tuning(int ctas_per_sm, int force_grid, int pdl);
 void qmv_set_trace(unsigned long long* device_buffer);
 
 // ---- grouped experts (kernels_moe.cu) ------------------------------------------------------------------
-// xhat[(slot * proj + p), :] = rotation of x[slot / top_k, :] * suh[selected[slot], p, :]   (native/src/moe.rs:184-236)
-cudaError_t launch_routed_prepare(const void* x, int x_dtype, const __half* suh, const uint32_t* selected, int experts,
-                                  int top_k, int proj, int64_t slots, int in, __half* xhat, cudaStream_t stream);
 // SwiGLU glue between the expert projections (native/src/moe.rs:438-533, SiLU): raw gate/up sums
 // ygu[slot * 2 + {0,1}, :] -> rotated input of the down projection xhat[slot, :]
 cudaError_t launch_glu_down_input(const float* ygu, const __half* gu_svh, const __half* down_suh, const uint32_t* selected,

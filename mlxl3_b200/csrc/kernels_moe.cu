@@ -3,7 +3,8 @@
 //
 //   routed prepare    native/src/moe.rs:184-236   x row of the slot's token * gate/up input scales of the
 //                                                  slot's expert, rotated (same rounding points as the
-//                                                  plain input rotation)
+//                                                  plain input rotation); for small batches the expert kernel
+//                                                  does this itself, the padded form below serves the sorted path
 //   glu_down_input    native/src/moe.rs:438-533   SiLU path: both rotations without intermediate rounding
 //   finish_and_reduce native/src/moe.rs:586-609   output rotation, expert output scales, routing weights,
 //                                                  sum over the top_k slots of a token
@@ -18,29 +19,6 @@ constexpr int kWarpsPerBlock = 8;
 
 __device__ __forceinline__ int expert_of(const uint32_t* selected, int64_t slot, int experts) {
     return min(static_cast<int>(selected[slot]), experts - 1);      // an out-of-range id must not read out of bounds
-}
-
-__global__ void __launch_bounds__(kWarpsPerBlock * 32)
-routed_prepare_kernel(const void* __restrict__ x, int x_dtype, const __half* __restrict__ suh,
-                      const uint32_t* __restrict__ selected, int experts, int top_k, int proj, int64_t slots, int in,
-                      __half* __restrict__ xhat) {
-    const int lane = threadIdx.x & 31;
-    const int blocks_per_row = in >> 7;
-    const int64_t total = slots * proj * blocks_per_row;
-    for (int64_t unit = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5); unit < total;
-         unit += static_cast<int64_t>(gridDim.x) * kWarpsPerBlock) {
-        const int64_t out_row = unit / blocks_per_row;                   // slot * proj + projection
-        const int col = static_cast<int>(unit % blocks_per_row) * 128 + lane * 4;
-        const int64_t slot = out_row / proj;
-        const int p = static_cast<int>(out_row - slot * proj);
-        const int64_t token = slot / top_k;
-        const __half* s = suh + (static_cast<int64_t>(expert_of(selected, slot, experts)) * proj + p) * in + col;
-        __align__(8) __half h[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) h[j] = __hmul_rn(load_as_half(x, x_dtype, token * in + col + j), s[j]);
-        warp_hadamard128_f16(h, lane);
-        *reinterpret_cast<uint2*>(xhat + out_row * in + col) = *reinterpret_cast<uint2*>(h);
-    }
 }
 
 // The exponential is evaluated in fp32 (expf); the reference's Metal `exp` is a fast-math intrinsic whose
@@ -131,14 +109,6 @@ unsigned grid_for(int64_t units) {
 }
 
 }  // namespace
-
-cudaError_t launch_routed_prepare(const void* x, int x_dtype, const __half* suh, const uint32_t* selected, int experts,
-                                  int top_k, int proj, int64_t slots, int in, __half* xhat, cudaStream_t stream) {
-    if (slots == 0) return cudaSuccess;
-    routed_prepare_kernel<<<grid_for(slots * proj * (in / 128)), kWarpsPerBlock * 32, 0, stream>>>(
-        x, x_dtype, suh, selected, experts, top_k, proj, slots, in, xhat);
-    return cudaGetLastError();
-}
 
 cudaError_t launch_glu_down_input(const float* ygu, const __half* gu_svh, const __half* down_suh, const uint32_t* selected,
                                   int experts, int64_t slots, int hidden, int logical_hidden, __half* xhat,

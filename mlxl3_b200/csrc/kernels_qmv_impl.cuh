@@ -282,6 +282,8 @@ qmv_kernel(const QmvArgs p) {
         int grp = qmv_group_of(p, cblock);
         int tn0 = cblock * 8;                               // first tile column of the block in the weight array
         bool active = true;
+        const void* x_rows = p.x;                           // activations and input scales this block's rotation reads
+        int64_t suh_row = grp;
         if (p.map_selected != nullptr) {
             // expert-mapped: virtual block -> (slot, projection, block of the expert's columns)
             const int sp = cblock / p.map_blocks, j = cblock - sp * p.map_blocks;
@@ -289,6 +291,9 @@ qmv_kernel(const QmvArgs p) {
             const int expert = min(static_cast<int>(p.map_selected[slot]), p.map_experts - 1);
             tn0 = (proj * p.map_stride_blocks + expert * p.map_blocks + j) * 8;
             grp = sp;                                       // rows of the rotated activations (stride: one slot)
+            suh_row = static_cast<int64_t>(expert) * p.map_proj + proj;
+            if (p.xhat == nullptr)
+                x_rows = static_cast<const char*>(p.x) + static_cast<int64_t>(slot / p.map_top_k) * p.in * dtype_size(p.x_dtype);
             // slots past the device-side count hold nothing: no weights are read for them, zeros are reduced
             active = p.map_count == nullptr || slot < *p.map_count;
         }
@@ -335,7 +340,7 @@ qmv_kernel(const QmvArgs p) {
 
                 // ---- phase 1: rotate this chunk's activations into the warp's shared memory ------------
                 if (p.xhat == nullptr)
-                    qmv_rotate_chunk(p.x, p.x_dtype, p.suh + static_cast<int64_t>(grp) * p.in, p.in, rows, kb0,
+                    qmv_rotate_chunk(x_rows, p.x_dtype, p.suh + suh_row * p.in, p.in, rows, kb0,
                                      ((tk_end - 1) >> 3) - kb0 + 1, xs, lane);
                 if (tracing && tk0 == tk_first) p.trace[blockIdx.x * 8 + 2] = global_ns();
 
