@@ -154,14 +154,22 @@ route_plan_kernel(const uint32_t* __restrict__ selected, int64_t slots, int expe
     for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
     for (int64_t r = threadIdx.x; r < static_cast<int64_t>(max_segments) * seg_rows; r += blockDim.x) row_slot[r] = kNoSlot;
     __syncthreads();
-    // One thread per expert walks the slots in order: a slot's position among its expert's rows is the number
-    // of earlier slots with the same expert, so the plan (and with it the summation order of every row's
-    // products, which depends on the segment a row lands in) is the same on every call.
-    for (int e = threadIdx.x; e < experts; e += blockDim.x) {
-        int pos = 0;
-        for (int64_t s = 0; s < slots; ++s)
-            if (min(static_cast<int>(selected[s]), experts - 1) == e) slot_row[s] = static_cast<uint32_t>(pos++);
-        count[e] = pos;
+    // One warp per expert walks the slots in order, 32 at a time: a slot's position among its expert's rows is the
+    // number of earlier slots with the same expert (ballot + population count), so the plan (and with it the
+    // summation order of every row's products, which depends on the segment a row lands in) is the same on every call.
+    {
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+        for (int e = warp; e < experts; e += warps) {
+            int pos = 0;
+            for (int64_t s0 = 0; s0 < slots; s0 += 32) {
+                const int64_t s = s0 + lane;
+                const bool mine = s < slots && min(static_cast<int>(selected[s]), experts - 1) == e;
+                const unsigned int votes = __ballot_sync(0xffffffffu, mine);
+                if (mine) slot_row[s] = static_cast<uint32_t>(pos + __popc(votes & ((1u << lane) - 1u)));
+                pos += __popc(votes);
+            }
+            if (lane == 0) count[e] = pos;
+        }
     }
     __syncthreads();
     if (threadIdx.x == 0) {
