@@ -151,6 +151,10 @@ route_plan_kernel(const uint32_t* __restrict__ selected, int64_t slots, int expe
     extern __shared__ int s_mem[];
     int* count = s_mem;                 // [experts] rows per expert, then running position
     int* base = s_mem + experts;        // [experts + 1] first segment of each expert
+    // expert of every slot, staged once (the walk below reads each of them once per expert)
+    unsigned short* ids = reinterpret_cast<unsigned short*>(s_mem + 2 * experts + 1);
+    for (int64_t s = threadIdx.x; s < slots; s += blockDim.x)
+        ids[s] = static_cast<unsigned short>(min(static_cast<int>(selected[s]), experts - 1));
     for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
     for (int64_t r = threadIdx.x; r < static_cast<int64_t>(max_segments) * seg_rows; r += blockDim.x) row_slot[r] = kNoSlot;
     __syncthreads();
@@ -163,7 +167,7 @@ route_plan_kernel(const uint32_t* __restrict__ selected, int64_t slots, int expe
             int pos = 0;
             for (int64_t s0 = 0; s0 < slots; s0 += 32) {
                 const int64_t s = s0 + lane;
-                const bool mine = s < slots && min(static_cast<int>(selected[s]), experts - 1) == e;
+                const bool mine = s < slots && ids[s] == e;
                 const unsigned int votes = __ballot_sync(0xffffffffu, mine);
                 if (mine) slot_row[s] = static_cast<uint32_t>(pos + __popc(votes & ((1u << lane) - 1u)));
                 pos += __popc(votes);
@@ -182,7 +186,7 @@ route_plan_kernel(const uint32_t* __restrict__ selected, int64_t slots, int expe
     for (int e = threadIdx.x; e < experts; e += blockDim.x)
         for (int s = base[e]; s < base[e + 1] && s < max_segments; ++s) seg_expert[s] = static_cast<uint32_t>(e);
     for (int64_t s = threadIdx.x; s < slots; s += blockDim.x) {
-        const int e = min(static_cast<int>(selected[s]), experts - 1);
+        const int e = ids[s];
         const int pos = static_cast<int>(slot_row[s]);
         const int64_t row = static_cast<int64_t>(base[e] + pos / seg_rows) * seg_rows + pos % seg_rows;
         slot_row[s] = static_cast<uint32_t>(row);
@@ -206,14 +210,15 @@ routed_prepare_padded_kernel(const void* __restrict__ x, int x_dtype, const __ha
         const int64_t seg = sp / proj;
         const int p = static_cast<int>(sp - seg * proj);
         const uint32_t slot = row_slot[seg * seg_rows + r];
-        __align__(8) __half h[4] = {__half(), __half(), __half(), __half()};
-        if (slot != kNoSlot) {                                           // warp-uniform: one row per warp
-            const __half* s = suh + (static_cast<int64_t>(seg_expert[seg]) * proj + p) * in + col;
-            const int64_t token = slot / top_k;
+        // Padding rows are left as they are: every activation row is multiplied on its own, and nothing downstream
+        // reads the products of a padding row.
+        if (slot == kNoSlot) continue;                                   // warp-uniform: one row per warp
+        const __half* s = suh + (static_cast<int64_t>(seg_expert[seg]) * proj + p) * in + col;
+        const int64_t token = slot / top_k;
+        __align__(8) __half h[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) h[j] = __hmul_rn(load_as_half(x, x_dtype, token * in + col + j), s[j]);
-            warp_hadamard128_f16(h, lane);
-        }
+        for (int j = 0; j < 4; ++j) h[j] = __hmul_rn(load_as_half(x, x_dtype, token * in + col + j), s[j]);
+        warp_hadamard128_f16(h, lane);
         *reinterpret_cast<uint2*>(xhat + out_row * in + col) = *reinterpret_cast<uint2*>(h);
     }
 }
@@ -307,8 +312,8 @@ finish_and_reduce_padded_kernel(const float* __restrict__ raw, const __half* __r
 
 cudaError_t launch_route_plan(const uint32_t* selected, int64_t slots, int experts, int max_segments, int seg_rows, int* seg_count,
                               uint32_t* seg_expert, uint32_t* row_slot, uint32_t* slot_row, cudaStream_t stream) {
-    const size_t smem = (2 * static_cast<size_t>(experts) + 1) * sizeof(int);
-    if (smem > 48 * 1024) return cudaErrorInvalidValue;
+    const size_t smem = (2 * static_cast<size_t>(experts) + 1) * sizeof(int) + static_cast<size_t>(slots) * sizeof(unsigned short);
+    if (smem > 48 * 1024 || experts > 65535) return cudaErrorInvalidValue;
     route_plan_kernel<<<1, 1024, smem, stream>>>(selected, slots, experts, max_segments, seg_rows, seg_count, seg_expert, row_slot, slot_row);
     return cudaGetLastError();
 }
