@@ -78,22 +78,39 @@ finish_and_reduce_kernel(const float* __restrict__ raw, const __half* __restrict
         const int col = static_cast<int>(unit % blocks_per_row) * 128 + lane * 4;
         float acc32[4] = {0.f, 0.f, 0.f, 0.f};
         __half acc16[4];
-        for (int t = 0; t < top_k; ++t) {
-            const int64_t slot = row * top_k + t;
-            const float4 r = *reinterpret_cast<const float4*>(raw + slot * out + col);
-            __half h[4] = {__float2half_rn(r.x), __float2half_rn(r.y), __float2half_rn(r.z), __float2half_rn(r.w)};
-            warp_hadamard128_f16(h, lane);
-            const __half* sv = down_svh + static_cast<int64_t>(expert_of(selected, slot, experts)) * out + col;
+        // the slots are added in order, but their loads go out four at a time (a token has few slots and few
+        // 128-blocks: the latency of one slot after the other would be the whole kernel)
+        for (int t0 = 0; t0 < top_k; t0 += 4) {
+            float4 r[4];
+            uint2 svw[4];
+            float score32[4];
+            __half score16[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const __half scaled = __hmul_rn(h[j], sv[j]);
-                if (F32) {
-                    // fp16 product promoted to the fp32 routing weight; the sum over slots stays in fp32
-                    const float v = __fmul_rn(__half2float(scaled), reinterpret_cast<const float*>(scores)[slot]);
-                    acc32[j] = t == 0 ? v : __fadd_rn(acc32[j], v);
-                } else {
-                    const __half v = __hmul_rn(scaled, reinterpret_cast<const __half*>(scores)[slot]);
-                    acc16[j] = t == 0 ? v : __hadd_rn(acc16[j], v);
+            for (int i = 0; i < 4; ++i) {
+                if (t0 + i >= top_k) continue;
+                const int64_t slot = row * top_k + t0 + i;
+                r[i] = *reinterpret_cast<const float4*>(raw + slot * out + col);
+                svw[i] = *reinterpret_cast<const uint2*>(down_svh + static_cast<int64_t>(expert_of(selected, slot, experts)) * out + col);
+                if (F32) score32[i] = reinterpret_cast<const float*>(scores)[slot];
+                else score16[i] = reinterpret_cast<const __half*>(scores)[slot];
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                if (t0 + i >= top_k) continue;
+                __half h[4] = {__float2half_rn(r[i].x), __float2half_rn(r[i].y), __float2half_rn(r[i].z), __float2half_rn(r[i].w)};
+                warp_hadamard128_f16(h, lane);
+                const __half* sv = reinterpret_cast<const __half*>(&svw[i]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const __half scaled = __hmul_rn(h[j], sv[j]);
+                    if (F32) {
+                        // fp16 product promoted to the fp32 routing weight; the sum over slots stays in fp32
+                        const float v = __fmul_rn(__half2float(scaled), score32[i]);
+                        acc32[j] = t0 + i == 0 ? v : __fadd_rn(acc32[j], v);
+                    } else {
+                        const __half v = __hmul_rn(scaled, score16[i]);
+                        acc16[j] = t0 + i == 0 ? v : __hadd_rn(acc16[j], v);
+                    }
                 }
             }
         }
