@@ -829,8 +829,8 @@ int b200exl3_moe_forward(const b200exl3_moe* h, const void* d_x, int x_dtype, in
             const bool tensor = seg_rows == kQmmSegRows;
             B200_TRY(launch_route_plan(sel, slots, h->experts, segs, seg_rows, seg_count, seg_expert, row_slot, slot_row, stream), "route plan");
             B200_TRY(launch_routed_prepare_padded(static_cast<const char*>(d_x) + static_cast<size_t>(r0) * h->in * x_size, x_dtype,
-                                                  h->gu_suh, seg_expert, row_slot, seg_count, h->experts, h->top_k, 2, segs, seg_rows,
-                                                  h->in, xgu, stream), "routed prepare");
+                                                  h->gu_suh, seg_expert, slot_row, slots, h->top_k, 2, segs, seg_rows, h->in, xgu,
+                                                  stream), "routed prepare");
             B200_TRY(tensor ? mapped_tensor(h->gu_wq, xgu, h->in, h->hidden, 2, h->experts * (h->hidden / 128), ygu)
                             : mapped(h->gu_wq, xgu, h->in, h->hidden, 2, h->experts * (h->hidden / 128), ygu, l.gu_plan),
                      "expert gate/up kernel");

@@ -135,8 +135,8 @@ cudaError_t launch_route_plan(const uint32_t* selected, int64_t slots, int exper
 // padded-row forms of the three glue kernels; activations and products are laid out per segment:
 // xhat[(s * proj + p) * R + r, :], products y[r, (s * proj + p) * width + col] with row stride max_segments * proj * width
 cudaError_t launch_routed_prepare_padded(const void* x, int x_dtype, const __half* suh, const uint32_t* seg_expert,
-                                         const uint32_t* row_slot, const int* seg_count, int experts, int top_k, int proj,
-                                         int max_segments, int seg_rows, int in, __half* xhat, cudaStream_t stream);
+                                         const uint32_t* slot_row, int64_t slots, int top_k, int proj, int max_segments,
+                                         int seg_rows, int in, __half* xhat, cudaStream_t stream);
 cudaError_t launch_glu_down_input_padded(const float* ygu, const __half* gu_svh, const __half* down_suh,
                                          const uint32_t* seg_expert, const uint32_t* row_slot, const int* seg_count,
                                          int experts, int max_segments, int seg_rows, int hidden, int logical_hidden, __half* xhat,

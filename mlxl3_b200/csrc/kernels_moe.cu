@@ -211,25 +211,25 @@ route_plan_kernel(const uint32_t* __restrict__ selected, int64_t slots, int expe
     }
 }
 
+// One warp per (slot, projection, 128-block): only rows that hold a slot are written.  Padding rows are left as they
+// are: every activation row is multiplied on its own, and nothing downstream reads the products of a padding row.
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 routed_prepare_padded_kernel(const void* __restrict__ x, int x_dtype, const __half* __restrict__ suh,
-                             const uint32_t* __restrict__ seg_expert, const uint32_t* __restrict__ row_slot,
-                             const int* __restrict__ seg_count, int top_k, int proj, int in, int seg_rows, __half* __restrict__ xhat) {
+                             const uint32_t* __restrict__ seg_expert, const uint32_t* __restrict__ slot_row, int64_t slots,
+                             int max_segments, int top_k, int proj, int in, int seg_rows, __half* __restrict__ xhat) {
     const int lane = threadIdx.x & 31;
     const int blocks_per_row = in >> 7;
-    const int64_t total = static_cast<int64_t>(seg_count[0]) * proj * seg_rows * blocks_per_row;
+    const int64_t total = slots * proj * blocks_per_row;
     for (int64_t unit = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5); unit < total;
          unit += static_cast<int64_t>(gridDim.x) * kWarpsPerBlock) {
-        const int64_t out_row = unit / blocks_per_row;                   // (segment * proj + p) * seg_rows + r
         const int col = static_cast<int>(unit % blocks_per_row) * 128 + lane * 4;
-        const int r = static_cast<int>(out_row % seg_rows);
-        const int64_t sp = out_row / seg_rows;
-        const int64_t seg = sp / proj;
-        const int p = static_cast<int>(sp - seg * proj);
-        const uint32_t slot = row_slot[seg * seg_rows + r];
-        // Padding rows are left as they are: every activation row is multiplied on its own, and nothing downstream
-        // reads the products of a padding row.
-        if (slot == kNoSlot) continue;                                   // warp-uniform: one row per warp
+        const int64_t sp = unit / blocks_per_row;                        // slot * proj + p
+        const int64_t slot = sp / proj;
+        const int p = static_cast<int>(sp - slot * proj);
+        const int64_t prow = slot_row[slot];                             // segment * seg_rows + r
+        const int64_t seg = prow / seg_rows;
+        if (seg >= max_segments) continue;
+        const int64_t out_row = (seg * proj + p) * seg_rows + (prow - seg * seg_rows);
         const __half* s = suh + (static_cast<int64_t>(seg_expert[seg]) * proj + p) * in + col;
         const int64_t token = slot / top_k;
         __align__(8) __half h[4];
@@ -336,11 +336,10 @@ cudaError_t launch_route_plan(const uint32_t* selected, int64_t slots, int exper
 }
 
 cudaError_t launch_routed_prepare_padded(const void* x, int x_dtype, const __half* suh, const uint32_t* seg_expert,
-                                         const uint32_t* row_slot, const int* seg_count, int experts, int top_k, int proj,
-                                         int max_segments, int seg_rows, int in, __half* xhat, cudaStream_t stream) {
-    (void)experts;
-    routed_prepare_padded_kernel<<<grid_for(static_cast<int64_t>(max_segments) * proj * seg_rows * (in / 128)), kWarpsPerBlock * 32, 0,
-                                   stream>>>(x, x_dtype, suh, seg_expert, row_slot, seg_count, top_k, proj, in, seg_rows, xhat);
+                                         const uint32_t* slot_row, int64_t slots, int top_k, int proj, int max_segments,
+                                         int seg_rows, int in, __half* xhat, cudaStream_t stream) {
+    routed_prepare_padded_kernel<<<grid_for(slots * proj * (in / 128)), kWarpsPerBlock * 32, 0, stream>>>(
+        x, x_dtype, suh, seg_expert, slot_row, slots, max_segments, top_k, proj, in, seg_rows, xhat);
     return cudaGetLastError();
 }
 
