@@ -161,6 +161,11 @@ int b200exl3_linear_forward(const b200exl3_linear* handle, const void* d_x, int 
  *     at the same time would race on the scratch. */
 int b200exl3_linear_forward_static(const b200exl3_linear* handle, const void* d_x, int x_dtype, int64_t rows, void* d_y,
                                    b200exl3_stream stream);
+/* Status word of the static scratch on the current device (the counterpart of b200exl3_workspace_status for
+ * b200exl3_linear_forward_static; no counterpart in the reference): 0, or the code of the bounded wait that gave up
+ * during some earlier static call.  The word is sticky; a non-zero `clear` resets it after reading.  Synchronises
+ * with the device, so call it after the stream of the static calls has drained. */
+int b200exl3_static_status(int* out_status, int clear);
 /* The middle of forward alone: fp32 yhat [rows, out] = xhat [rows, in] (fp16, already rotated) times
  * the inner matrix -- what the reference's QMV/QMM kernels return before the output rotation. */
 int b200exl3_linear_forward_raw(const b200exl3_linear* handle, const uint16_t* d_xhat_f16, int64_t rows, float* d_yhat,
@@ -234,6 +239,15 @@ int b200exl3_moe_forward(const b200exl3_moe* handle, const void* d_x, int x_dtyp
  * b200exl3_moe_forward directly, on the device. */
 int b200exl3_router_topk(const void* d_values, int dtype, int64_t rows, int experts, int top_k, int normalize,
                          uint32_t* d_indices, void* d_scores, b200exl3_stream stream);
+/* The same on logits: routes are taken on the row softmax of d_logits, computed in fp32 and rounded to `dtype` as
+ * the reference's softmax_precise() does (native/src/qwen35.rs:214, 240: topk(&logits.softmax_precise(), k, true));
+ * d_probabilities [rows, experts] receives the softmax when it is not NULL.  One pass: a warp per token row. */
+int b200exl3_router_softmax_topk(const void* d_logits, int dtype, int64_t rows, int experts, int top_k, int normalize,
+                                 uint32_t* d_indices, void* d_scores, void* d_probabilities, b200exl3_stream stream);
+/* Router gate product (the plain fp16 linear in front of the router, `self.gate.forward(x)`, native/src/qwen35.rs:207-213,
+ * 240): logits [rows, experts] fp16 = x [rows, in] times weight [experts, in] fp16, fp32 accumulation. */
+int b200exl3_router_gate(const void* d_x, int x_dtype, const uint16_t* d_weight_f16, int64_t rows, int in, int experts,
+                         uint16_t* d_logits_f16, b200exl3_stream stream);
 
 /* ---- tensor parallelism over peer memory (one process per GPU of one node) -----------------------------------
  * No counterpart in the reference (single GPU).  Column-parallel shards need nothing from here.  A row-parallel
@@ -247,8 +261,12 @@ int b200exl3_router_topk(const void* d_values, int dtype, int64_t rows, int expe
  * Set-up: every rank calls b200exl3_tp_alloc (buffer + 64-byte IPC handle), the host exchanges the handles by
  * its own means, opens the other ranks' buffers with b200exl3_tp_open, and passes all `world` buffers (its own
  * at index `rank`) to b200exl3_tp_create.  max_units bounds rows * out / 128 of any layer finished through the
- * context.  All ranks must issue the same sequence of b200exl3_linear_finish_tp calls.  A wait that gives up
- * sets the context's status to 4 (b200exl3_tp_status) instead of hanging. */
+ * context.  All ranks must issue the same sequence of b200exl3_linear_finish_tp calls.  A rank polls for its
+ * peers' sums for at most four seconds (option "tp_wait_ms": 1..60000); a wait that gives up sets the
+ * context's status to 4 (b200exl3_tp_status) instead of hanging, the kernel returns with what it has, and
+ * later waits of that context give up after a few hundred polls.  The ranks' use counts may then disagree:
+ * once every rank has stopped launching, each calls b200exl3_tp_reset (own inbox, use counts and status back
+ * to zero; synchronises the device) before the context is used again, or the contexts are rebuilt. */
 typedef struct b200exl3_tp b200exl3_tp;
 int b200exl3_tp_buffer_bytes(int world, int max_units, size_t* out_bytes);
 int b200exl3_tp_alloc(int world, int max_units, void** out_buffer, unsigned char* out_handle64);
@@ -257,6 +275,7 @@ int b200exl3_tp_close(void* peer_buffer);
 int b200exl3_tp_create(int rank, int world, int max_units, void* const* buffers, b200exl3_tp** out);
 void b200exl3_tp_free(b200exl3_tp* handle);
 int b200exl3_tp_status(const b200exl3_tp* handle, int* out_status);
+int b200exl3_tp_reset(b200exl3_tp* handle);
 /* The whole row-parallel layer in one launch: input rotation of this rank's input slice, product, exchange of
  * the partial sums with the other ranks inside the kernel's final reduction, output rotation.  Same result as
  * b200exl3_linear_forward_partial followed by b200exl3_linear_finish_tp.  Batches of more than 16 rows run as

@@ -57,6 +57,7 @@ SIGNATURES = {
     "b200exl3_workspace_status": (c_int, [c_void_p, POINTER(c_int)]),
     "b200exl3_linear_forward": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_size_t, c_void_p]),
     "b200exl3_linear_forward_static": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p]),
+    "b200exl3_static_status": (c_int, [POINTER(c_int), c_int]),
     "b200exl3_linear_forward_raw": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_size_t, c_void_p]),
     "b200exl3_linear_forward_partial": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_size_t,
                                                 c_void_p]),
@@ -68,6 +69,8 @@ SIGNATURES = {
     "b200exl3_group_workspace_bytes": (c_int, [c_void_p, c_int64, POINTER(c_size_t)]),
     "b200exl3_group_forward": (c_int, [c_void_p, c_void_p, c_int, c_int64, POINTER(c_void_p), c_void_p, c_size_t, c_void_p]),
     "b200exl3_router_topk": (c_int, [c_void_p, c_int, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "b200exl3_router_softmax_topk": (c_int, [c_void_p, c_int, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "b200exl3_router_gate": (c_int, [c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p]),
     "b200exl3_tp_buffer_bytes": (c_int, [c_int, c_int, POINTER(c_size_t)]),
     "b200exl3_tp_alloc": (c_int, [c_int, c_int, POINTER(c_void_p), c_char_p]),
     "b200exl3_tp_open": (c_int, [c_char_p, POINTER(c_void_p)]),
@@ -75,6 +78,7 @@ SIGNATURES = {
     "b200exl3_tp_create": (c_int, [c_int, c_int, c_int, POINTER(c_void_p), POINTER(c_void_p)]),
     "b200exl3_tp_free": (None, [c_void_p]),
     "b200exl3_tp_status": (c_int, [c_void_p, POINTER(c_int)]),
+    "b200exl3_tp_reset": (c_int, [c_void_p]),
     "b200exl3_linear_forward_tp": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_size_t, c_void_p]),
     "b200exl3_linear_finish_tp": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p]),
     "b200exl3_moe_create": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,

@@ -13,7 +13,8 @@
 
 #include "common.cuh"
 #include "kernels.h"
-namespace b200exl3 { extern unsigned long long* g_qmm_trace; }
+#include <atomic>
+namespace b200exl3 { extern std::atomic<unsigned long long*> g_qmm_trace; }
 
 using namespace b200exl3;
 
@@ -56,8 +57,9 @@ int valid_format(int k, int cb) {
     return 0;
 }
 
-bool g_moe_sorted = true;                                // "moe_sorted" option: 0 keeps one row per slot for any batch
-bool g_qmm_enabled = true;                               // "qmm" option: 0 sends every batch through the fused kernel
+std::atomic<bool> g_moe_sorted{true};                    // "moe_sorted" option: 0 keeps one row per slot for any batch
+std::atomic<bool> g_qmm_enabled{true};                   // "qmm" option: 0 sends every batch through the fused kernel
+std::atomic<long long> g_tp_wait_ms{4000};               // "tp_wait_ms" option: how long a rank polls for its peers' sums
 constexpr int kMaxBatchRows = kQmvMaxRows;              // rows handled by one launch of the fused kernel
 constexpr size_t kCounterBytes = B200EXL3_WORKSPACE_HEADER_BYTES;   // arrival counters at the head of a workspace
 
@@ -125,12 +127,17 @@ int b200exl3_init(int device) {
 }
 
 int b200exl3_set_option(const char* name, int64_t value) {
-    static int ctas = 0, grid = 0, pdl = 0;
+    static std::atomic<int> ctas{0}, grid{0}, pdl{0};
     if (!name) return fail("option name is NULL");
     if (!strcmp(name, "qmv_ctas_per_sm")) ctas = static_cast<int>(value);
     else if (!strcmp(name, "qmv_force_grid")) grid = static_cast<int>(value);
     else if (!strcmp(name, "pdl")) pdl = static_cast<int>(value);
     else if (!strcmp(name, "qmm")) { g_qmm_enabled = value != 0; return 0; }
+    else if (!strcmp(name, "tp_wait_ms")) {
+        if (value < 1 || value > 60000) return fail("tp_wait_ms must be between 1 and 60000");
+        g_tp_wait_ms = value;
+        return 0;
+    }
     else if (!strcmp(name, "qmm_trace_buffer")) { b200exl3::g_qmm_trace = reinterpret_cast<unsigned long long*>(value); return 0; }
     else if (!strcmp(name, "moe_sorted")) { g_moe_sorted = value != 0; return 0; }
     else if (!strcmp(name, "qmm_splits")) { qmm_set_tuning(static_cast<int>(value)); return 0; }
@@ -529,11 +536,25 @@ int b200exl3_linear_forward_static(const b200exl3_linear* h, const void* d_x, in
                     "use b200exl3_linear_forward with a caller workspace", need, kStaticScratchBytes);
     void* scratch = nullptr;
     if (static_scratch(&scratch)) return -1;
-    // The array keeps whatever the previous call left; the arrival counters (and the status word) at
-    // its head must start at zero, the partial sums behind them are overwritten before they are read.
-    B200_TRY(cudaMemsetAsync(scratch, 0, kCounterBytes, as_stream(s)), "clear static scratch");
+    // The array keeps whatever the previous call left; the arrival counters at its head must start at
+    // zero, the partial sums behind them are overwritten before they are read.  The status word (the
+    // last word of the header) is left alone, so a failure stays visible to b200exl3_static_status
+    // until that call clears it, as it does in a caller's workspace.
+    B200_TRY(cudaMemsetAsync(scratch, 0, kCounterBytes - sizeof(unsigned int), as_stream(s)), "clear static scratch");
     void* ys[1] = {d_y};
     return forward_common(h->c, d_x, x_dtype, nullptr, rows, ys, nullptr, scratch, kStaticScratchBytes, as_stream(s));
+}
+
+int b200exl3_static_status(int* out_status, int clear) {
+    if (!out_status) return fail("NULL argument");
+    void* scratch = nullptr;
+    if (static_scratch(&scratch)) return -1;
+    unsigned int* word = reinterpret_cast<unsigned int*>(static_cast<char*>(scratch) + kCounterBytes - sizeof(unsigned int));
+    unsigned int flag = 0;
+    B200_TRY(cudaMemcpy(&flag, word, sizeof flag, cudaMemcpyDeviceToHost), "read static scratch status");
+    if (clear && flag) B200_TRY(cudaMemset(word, 0, sizeof flag), "clear static scratch status");
+    *out_status = static_cast<int>(flag);
+    return 0;
 }
 
 /* ---- Exl3Group --------------------------------------------------------------------------------- */
@@ -711,8 +732,12 @@ static MoeSortedLayout moe_sorted_layout(const b200exl3_moe* h, int64_t rows) {
 
 static bool moe_sorted(const b200exl3_moe* h, int64_t rows) {
     // worth it once experts see several rows each: below two slots per expert one row per slot is faster
-    return g_moe_sorted && rows * h->top_k >= std::max<int64_t>(kMoeSortedMinSlots, 2 * static_cast<int64_t>(h->experts)) &&
-           2 * static_cast<size_t>(h->experts) + 1 <= 12 * 1024;
+    if (!g_moe_sorted || rows * h->top_k < std::max<int64_t>(kMoeSortedMinSlots, 2 * static_cast<int64_t>(h->experts))) return false;
+    // the route plan keeps 2 * experts + 1 counters and one 16-bit expert id per slot of a pass in 48 KiB of shared
+    // memory; shapes beyond that keep one row per slot
+    const size_t plan_smem = (2 * static_cast<size_t>(h->experts) + 1) * sizeof(int) +
+                             static_cast<size_t>(moe_sorted_chunk_rows(h, rows)) * h->top_k * sizeof(unsigned short);
+    return plan_smem <= 48 * 1024 && h->experts <= 65535;
 }
 
 int b200exl3_moe_create(const uint16_t* d_gu_trellis, const void* d_gu_suh, const void* d_gu_svh,
@@ -896,15 +921,37 @@ int b200exl3_moe_forward(const b200exl3_moe* h, const void* d_x, int x_dtype, in
 
 /* ---- router ------------------------------------------------------------------------------------------------ */
 
-int b200exl3_router_topk(const void* d_values, int dtype, int64_t rows, int experts, int top_k, int normalize,
-                         uint32_t* d_indices, void* d_scores, b200exl3_stream s) {
+static int router_check(int64_t rows, int experts, int top_k, int dtype) {
     if (rows <= 0 || experts <= 0 || experts > 1024) return fail("native router accepts positive rows and at most 1024 experts");
     if (top_k <= 0 || top_k > experts) return fail("invalid router top-k");
     if (dtype != kF16 && dtype != kF32) return fail("native router expects FP16 or FP32 values");
     if (rows * static_cast<int64_t>(top_k) > INT32_MAX || rows * static_cast<int64_t>(experts) > INT32_MAX) return fail("router index overflow");
+    return 0;
+}
+
+int b200exl3_router_topk(const void* d_values, int dtype, int64_t rows, int experts, int top_k, int normalize,
+                         uint32_t* d_indices, void* d_scores, b200exl3_stream s) {
+    if (router_check(rows, experts, top_k, dtype)) return -1;
     if (!d_values || !d_indices || !d_scores) return fail("NULL buffer");
-    return check(launch_router_topk(d_values, dtype, rows, experts, top_k, normalize != 0, d_indices, d_scores, as_stream(s)),
-                 "router kernel");
+    return check(launch_router_topk(d_values, dtype, rows, experts, top_k, normalize != 0, false, d_indices, d_scores, nullptr,
+                                    as_stream(s)), "router kernel");
+}
+
+int b200exl3_router_softmax_topk(const void* d_logits, int dtype, int64_t rows, int experts, int top_k, int normalize,
+                                 uint32_t* d_indices, void* d_scores, void* d_probabilities, b200exl3_stream s) {
+    if (router_check(rows, experts, top_k, dtype)) return -1;
+    if (!d_logits || !d_indices || !d_scores) return fail("NULL buffer");
+    return check(launch_router_topk(d_logits, dtype, rows, experts, top_k, normalize != 0, true, d_indices, d_scores,
+                                    d_probabilities, as_stream(s)), "router kernel");
+}
+
+int b200exl3_router_gate(const void* d_x, int x_dtype, const uint16_t* d_weight_f16, int64_t rows, int in, int experts,
+                         uint16_t* d_logits_f16, b200exl3_stream s) {
+    if (rows <= 0 || rows > 8 * 65535ll || in <= 0 || in % 2 || experts <= 0) return fail("invalid router gate dimensions");
+    if (!dtype_is_float(x_dtype)) return fail("unsupported input dtype %d", x_dtype);
+    if (!d_x || !d_weight_f16 || !d_logits_f16) return fail("NULL buffer");
+    return check(launch_router_gate(d_x, x_dtype, reinterpret_cast<const __half*>(d_weight_f16), rows, in, experts,
+                                    reinterpret_cast<__half*>(d_logits_f16), as_stream(s)), "router gate kernel");
 }
 
 /* ---- tensor parallelism over peer memory ------------------------------------------------------------ */
@@ -982,6 +1029,16 @@ int b200exl3_tp_status(const b200exl3_tp* h, int* out_status) {
     return 0;
 }
 
+int b200exl3_tp_reset(b200exl3_tp* h) {
+    if (!h) return fail("NULL handle");
+    B200_TRY(cudaDeviceSynchronize(), "tp_reset");
+    size_t bytes = 0;
+    if (b200exl3_tp_buffer_bytes(h->world, h->max_units, &bytes)) return -1;
+    B200_TRY(cudaMemset(h->buffers[h->rank], 0, bytes), "clear exchange buffer");
+    B200_TRY(cudaMemset(h->done, 0, (static_cast<size_t>(h->max_units) + 1) * sizeof(unsigned int)), "clear use counts");
+    return check(cudaDeviceSynchronize(), "tp_reset");
+}
+
 int b200exl3_linear_forward_tp(const b200exl3_linear* h, b200exl3_tp* tp, const void* d_x, int x_dtype, int64_t rows, void* d_y,
                               void* ws, size_t ws_bytes, b200exl3_stream s) {
     if (!h || !tp) return fail("NULL handle");
@@ -1019,5 +1076,6 @@ static TpPeers tp_peers(const b200exl3_tp* tp) {
     t.done = tp->done;
     t.error = tp->done + tp->max_units;
     t.rank = tp->rank; t.world = tp->world; t.max_units = tp->max_units;
+    t.wait_ns = static_cast<unsigned long long>(g_tp_wait_ms.load()) * 1000000ull;
     return t;
 }

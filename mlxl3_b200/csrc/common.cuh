@@ -15,7 +15,7 @@ constexpr int kF16 = 9;
 constexpr int kF32 = 10;
 constexpr int kBF16 = 12;
 
-constexpr int kSmCount = 148;
+constexpr int kDefaultSmCount = 148;   // B200; sm_count() asks the device
 
 __host__ __device__ inline bool dtype_is_float(int code) { return code == kF16 || code == kF32 || code == kBF16; }
 __host__ __device__ inline size_t dtype_size(int code) { return code == kF32 ? 4 : 2; }
@@ -57,22 +57,9 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
-// 16-byte asynchronous global->shared copy that bypasses L1 (weights are read once).
-__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr(smem)), "l"(gmem) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
 // ---- mbarrier + bulk (TMA) copies ---------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count) : "memory");
-}
-// makes freshly initialised barriers visible to the asynchronous proxy that completes the copies
-__device__ __forceinline__ void mbar_init_fence() {
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");

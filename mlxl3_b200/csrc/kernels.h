@@ -9,6 +9,10 @@
 
 namespace b200exl3 {
 
+// Multiprocessors of the current device, asked once per device (148 when no device answers, so that the launch
+// planners can be exercised on a machine without a GPU).
+int sm_count();
+
 // ---- codec (kernels_codec.cu) ---------------------------------------------------------------------
 cudaError_t launch_unpack_states(const uint16_t* packed, int64_t tiles, int k, int cb, uint16_t* states, __half* values,
                                  cudaStream_t stream);
@@ -88,7 +92,6 @@ struct QmvPlan {
 };
 QmvPlan plan_qmv(int in, int out, int k, int64_t rows);
 // Scratch a launch needs: counters first (zero-initialised once by the owner), then the partial sums.
-size_t qmv_counter_bytes(int out);
 size_t qmv_partial_bytes(const QmvPlan& plan, int out, int64_t rows);
 // exact: decode the reference's fp16 weight bit for bit before multiplying (codebooks 0/1 default to
 // feeding the two fp16 halves of a weight as two products, which differs by fp16 rounding of the weight).
@@ -146,9 +149,14 @@ cudaError_t launch_finish_and_reduce_padded(const float* raw, const __half* down
                                             int64_t rows, int top_k, int out, int max_segments, int seg_rows, void* y, cudaStream_t stream);
 
 // ---- router (kernels_router.cu) --------------------------------------------------------------------------
-// stable top-k per row with index tie-break; values and scores fp16 or fp32; experts <= 1024
-cudaError_t launch_router_topk(const void* values, int dtype, int64_t rows, int experts, int k, bool normalize,
-                               uint32_t* indices, void* scores, cudaStream_t stream);
+// stable top-k per row with index tie-break; values and scores fp16 or fp32; experts <= 1024.  With `softmax` the
+// values are logits and the routes are taken on their row softmax (fp32 arithmetic, rounded to the values' type),
+// which is also stored to `probabilities` when that is not nullptr.
+cudaError_t launch_router_topk(const void* values, int dtype, int64_t rows, int experts, int k, bool normalize, bool softmax,
+                               uint32_t* indices, void* scores, void* probabilities, cudaStream_t stream);
+// logits [rows, experts] fp16 = x [rows, in] times the fp16 router weights w [experts, in], fp32 accumulation
+cudaError_t launch_router_gate(const void* x, int x_dtype, const __half* w, int64_t rows, int in, int experts, __half* logits,
+                               cudaStream_t stream);
 
 // ---- tensor-core product for many rows (kernels_qmm.cu) ---------------------------------------------------
 struct QmmPlan {

@@ -18,7 +18,8 @@ namespace {
 constexpr int kWarpsPerBlock = 8;
 
 __device__ __forceinline__ int expert_of(const uint32_t* selected, int64_t slot, int experts) {
-    return min(static_cast<int>(selected[slot]), experts - 1);      // an out-of-range id must not read out of bounds
+    // an out-of-range id must not read out of bounds (unsigned compare: ids of 2^31 and more stay large)
+    return static_cast<int>(min(selected[slot], static_cast<uint32_t>(experts - 1)));
 }
 
 // The exponential is evaluated in fp32 (expf); the reference's Metal `exp` is a fast-math intrinsic whose
@@ -121,7 +122,7 @@ finish_and_reduce_kernel(const float* __restrict__ raw, const __half* __restrict
 
 unsigned grid_for(int64_t units) {
     const int64_t blocks = (units + kWarpsPerBlock - 1) / kWarpsPerBlock;
-    const int64_t cap = static_cast<int64_t>(kSmCount) * 8;
+    const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
     return static_cast<unsigned>(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
 }
 
@@ -171,7 +172,7 @@ route_plan_kernel(const uint32_t* __restrict__ selected, int64_t slots, int expe
     // expert of every slot, staged once (the walk below reads each of them once per expert)
     unsigned short* ids = reinterpret_cast<unsigned short*>(s_mem + 2 * experts + 1);
     for (int64_t s = threadIdx.x; s < slots; s += blockDim.x)
-        ids[s] = static_cast<unsigned short>(min(static_cast<int>(selected[s]), experts - 1));
+        ids[s] = static_cast<unsigned short>(min(selected[s], static_cast<uint32_t>(experts - 1)));
     for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
     for (int64_t r = threadIdx.x; r < static_cast<int64_t>(max_segments) * seg_rows; r += blockDim.x) row_slot[r] = kNoSlot;
     __syncthreads();

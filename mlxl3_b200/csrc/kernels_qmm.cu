@@ -27,6 +27,7 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <atomic>
 
 #include "kernels.h"
 #include "hadamard.cuh"
@@ -193,7 +194,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUt
         const int sp = cblock / p.map_blocks, j = cblock - sp * p.map_blocks;
         const int seg = sp / p.map_proj, proj = sp - seg * p.map_proj;
         if (seg >= *p.map_count) return;                          // uniform for the CTA; nothing is allocated yet
-        const int expert = min(static_cast<int>(p.map_expert[seg]), p.map_experts - 1);
+        const int expert = static_cast<int>(min(p.map_expert[seg], static_cast<uint32_t>(p.map_experts - 1)));
         wblock = proj * p.map_stride_blocks + expert * p.map_blocks + j;
         brow0 = sp * S::kTokTile;
     }
@@ -469,8 +470,8 @@ cudaError_t qmm_launch_k(int cb, const CUtensorMap& map, const CUtensorMap& wmap
 
 }  // namespace
 
-unsigned long long* g_qmm_trace = nullptr;
-static int g_qmm_splits = 0;                              // 0 = chosen by the cost model below
+std::atomic<unsigned long long*> g_qmm_trace{nullptr};
+static std::atomic<int> g_qmm_splits{0};                              // 0 = chosen by the cost model below
 void qmm_set_tuning(int splits) { g_qmm_splits = splits > 0 ? splits : 0; }
 
 constexpr int64_t kQmmSmallMaxRows = 64;     // one token tile: a second one would decode every weight twice
@@ -484,11 +485,11 @@ QmmPlan plan_qmm(int in, int out, int64_t rows) {
     const int stages_total = in / 64;
     const int64_t base = static_cast<int64_t>(col_blocks) * plan.token_tiles;
     const int max_splits = std::max(1, stages_total / 8);     // every split keeps at least 8 stages
-    if (g_qmm_splits) { plan.splits = std::min(g_qmm_splits, max_splits); return plan; }
+    if (const int forced = g_qmm_splits.load()) { plan.splits = std::min(forced, max_splits); return plan; }
     // CTAs that run at once: one per SM for the large shape (the operand rings take most of the shared memory),
     // two for the small one.  Estimated time of a choice: waves x (stages per CTA + fixed prologue/epilogue) + the
     // fp32 partials that several splits write and the separate output rotation reads back.
-    const int64_t slots = static_cast<int64_t>(kSmCount) * (plan.small ? 2 : 1);
+    const int64_t slots = static_cast<int64_t>(sm_count()) * (plan.small ? 2 : 1);
     const double stage_us = plan.small ? 0.55 : (rows > 256 ? 0.6 : 0.35), fixed_us = 4.0;
     const double partial_us = static_cast<double>(rows) * out * 8.0 / 8.0e6;
     double best = 0;
@@ -536,7 +537,7 @@ cudaError_t launch_qmm(const uint32_t* wq, int in, int out, int k, int cb, const
     p.wq = wq; p.partials = partials; p.error = error;
     p.svh = svh; p.bias = bias; p.y = y; p.y_dtype = y_dtype;
     p.in = in; p.out = out; p.rows = static_cast<int>(rows); p.tiles_n = out / 16;
-    p.splits = plan.splits; p.stages_total = in / 64; p.trace = g_qmm_trace;
+    p.splits = plan.splits; p.stages_total = in / 64; p.trace = g_qmm_trace.load();
     const dim3 grid(static_cast<unsigned>((out / 128) * plan.splits), static_cast<unsigned>(plan.token_tiles));
     switch (k) {
         case 1: return qmm_launch_k<1>(cb, map, wmap, p, grid, plan.small, stream);

@@ -7,6 +7,7 @@
 #include "kernels.h"
 
 #include <algorithm>
+#include <atomic>
 
 namespace b200exl3 {
 
@@ -19,9 +20,27 @@ cudaError_t qmv_dispatch_k6(const QmvArgs&, int, bool, const QmvPlan&, cudaStrea
 cudaError_t qmv_dispatch_k7(const QmvArgs&, int, bool, const QmvPlan&, cudaStream_t);
 cudaError_t qmv_dispatch_k8(const QmvArgs&, int, bool, const QmvPlan&, cudaStream_t);
 
-static int g_ctas_per_sm = 2;       // CTAs per SM the grid is sized for (one wave)
-static int g_force_grid = 0;        // > 0 overrides the grid size (tuning and tests)
-static int g_pdl = 0;               // programmatic dependent launch between consecutive layers: 0 off, 1 late trigger, 2 early
+// Process-wide knobs; atomics because handles may be used from several threads while another thread sets an option.
+static std::atomic<int> g_ctas_per_sm{2};   // CTAs per SM the grid is sized for (one wave)
+static std::atomic<int> g_force_grid{0};    // > 0 overrides the grid size (tuning and tests)
+static std::atomic<int> g_pdl{0};           // programmatic dependent launch between consecutive layers: 0 off, 1 late trigger, 2 early
+
+int sm_count() {
+    static std::atomic<int> cached[64];
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) {
+        (void)cudaGetLastError();
+        return kDefaultSmCount;
+    }
+    int n = cached[device].load(std::memory_order_relaxed);
+    if (n > 0) return n;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0) {
+        (void)cudaGetLastError();
+        return kDefaultSmCount;
+    }
+    cached[device].store(n, std::memory_order_relaxed);
+    return n;
+}
 
 void qmv_set_tuning(int ctas_per_sm, int force_grid, int pdl) {
     if (ctas_per_sm > 0) g_ctas_per_sm = ctas_per_sm;
@@ -29,7 +48,7 @@ void qmv_set_tuning(int ctas_per_sm, int force_grid, int pdl) {
     g_pdl = pdl > 0 ? pdl : 0;
 }
 
-static unsigned long long* g_trace = nullptr;
+static std::atomic<unsigned long long*> g_trace{nullptr};
 void qmv_set_trace(unsigned long long* device_buffer) { g_trace = device_buffer; }
 
 QmvPlan plan_qmv(int in, int out, int k, int64_t rows) {
@@ -39,8 +58,9 @@ QmvPlan plan_qmv(int in, int out, int k, int64_t rows) {
     const int64_t total = static_cast<int64_t>(tiles_k) * 8 * plan.col_blocks;
     const int r = static_cast<int>(std::min<int64_t>(rows, kQmvMaxRows));
     // two 8-row blocks need about twice the registers and shared memory: one CTA per SM
-    const int resident = r <= 8 ? g_ctas_per_sm : 1;
-    int64_t grid = g_force_grid > 0 ? g_force_grid : static_cast<int64_t>(kSmCount) * resident;
+    const int resident = r <= 8 ? g_ctas_per_sm.load() : 1;
+    const int forced = g_force_grid.load();
+    int64_t grid = forced > 0 ? forced : static_cast<int64_t>(sm_count()) * resident;
     // keep at least four tiles per warp so a warp is not all prologue and epilogue
     grid = std::max<int64_t>(1, std::min(grid, total / (kQmvWarps * 4)));
     // a warp's range must not exceed one column block (it then touches at most two blocks)
@@ -58,12 +78,11 @@ QmvPlan plan_qmv(int in, int out, int k, int64_t rows) {
     plan.stage_offset = static_cast<int>(ring + xs);
     plan.warp_smem = static_cast<int>((ring + xs + stage + 15) / 16 * 16);
     plan.smem_bytes = static_cast<size_t>(plan.warp_smem) * kQmvWarps;
-    plan.pdl = g_pdl != 0;
-    plan.pdl_early = g_pdl == 2;
+    const int pdl = g_pdl.load();
+    plan.pdl = pdl != 0;
+    plan.pdl_early = pdl == 2;
     return plan;
 }
-
-size_t qmv_counter_bytes(int out) { return (static_cast<size_t>(out / 128) * sizeof(unsigned int) + 255) / 256 * 256; }
 
 size_t qmv_partial_bytes(const QmvPlan& plan, int out, int64_t rows) {
     const int64_t r = std::min<int64_t>(rows, kQmvMaxRows);
@@ -75,7 +94,7 @@ cudaError_t launch_qmv(QmvArgs args, int k, int cb, bool exact, const QmvPlan& p
     args.tiles_k = args.in / 16;
     if (args.map_selected == nullptr) args.tiles_n = args.out / 16;   // the expert-mapped caller gives the bank's width
     args.max_pieces = plan.max_pieces;
-    args.trace = g_trace;
+    args.trace = g_trace.load();
     args.warp_smem = plan.warp_smem;
     args.xs_offset = plan.xs_offset;
     args.stage_offset = plan.stage_offset;

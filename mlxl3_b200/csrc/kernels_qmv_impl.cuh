@@ -10,8 +10,8 @@
 // kept off the issue slots:
 //  * weights live in a "quad" layout made once at load (4 neighbouring tiles interleaved word by
 //    word), so one 16-byte shared-memory load gives a lane its stream word for four tiles;
-//  * packed words are staged with 16-byte cp.async copies into a per-warp ring in shared memory,
-//    issued before anything that depends on the activations;
+//  * packed words are staged by the TMA unit (one cp.async.bulk per row of 8 tiles) into a per-warp ring in
+//    shared memory, issued before anything that depends on the activations;
 //  * lane L owns states 8L..8L+7 of a tile, which are exactly the A-fragment of mma.m16n8k16 for
 //    W^T; the product runs on the tensor cores with the activation rows in the n dimension, so
 //    1..8 rows cost the same and the fp32 accumulators are the MMA fragment;
@@ -285,10 +285,19 @@ qmv_kernel(const QmvArgs p) {
         const void* x_rows = p.x;                           // activations and input scales this block's rotation reads
         int64_t suh_row = grp;
         if (p.map_selected != nullptr) {
+            // The routes (and the slot count) are written by the previous kernel in the stream: under a programmatic
+            // dependent launch they may be read only once that kernel's memory is visible, so this mode gives up
+            // the early weight prefetch.
+            if (first_chunk) {
+                if (p.pdl_early) pdl_launch_dependents();
+                pdl_wait();
+                first_chunk = false;
+            }
             // expert-mapped: virtual block -> (slot, projection, block of the expert's columns)
             const int sp = cblock / p.map_blocks, j = cblock - sp * p.map_blocks;
             const int slot = sp / p.map_proj, proj = sp - slot * p.map_proj;
-            const int expert = min(static_cast<int>(p.map_selected[slot]), p.map_experts - 1);
+            // unsigned clamp: an id of 2^31 or more must not turn into a negative index
+            const int expert = static_cast<int>(min(p.map_selected[slot], static_cast<uint32_t>(p.map_experts - 1)));
             tn0 = (proj * p.map_stride_blocks + expert * p.map_blocks + j) * 8;
             grp = sp;                                       // rows of the rotated activations (stride: one slot)
             suh_row = static_cast<int64_t>(expert) * p.map_proj + proj;

@@ -60,7 +60,7 @@ finish_kernel(const float* __restrict__ partials, int splits, int64_t split_stri
 
 static unsigned grid_for(int64_t units) {
     int64_t blocks = (units + 7) / 8;
-    int64_t cap = static_cast<int64_t>(kSmCount) * 8;
+    int64_t cap = static_cast<int64_t>(sm_count()) * 8;
     return static_cast<unsigned>(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
 }
 

@@ -40,7 +40,7 @@ cudaError_t launch_tp_finish(const TpArgs& args, cudaStream_t stream) {
     if (units <= 0 || units > args.peers.max_units || args.peers.world < 1 || args.peers.world > kTpMaxWorld) return cudaErrorInvalidValue;
     // every rank must use the same grid: it only depends on the unit count
     const int grid = (units + kTpWarps - 1) / kTpWarps;
-    tp_finish_kernel<<<grid < 4 * kSmCount ? grid : 4 * kSmCount, kTpWarps * 32, 0, stream>>>(args);
+    tp_finish_kernel<<<grid < 4 * sm_count() ? grid : 4 * sm_count(), kTpWarps * 32, 0, stream>>>(args);
     return cudaGetLastError();
 }
 

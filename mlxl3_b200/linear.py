@@ -62,6 +62,15 @@ def workspace_status(workspace: DeviceBuffer) -> int:
     return out.value
 
 
+def static_status(clear: bool = False) -> int:
+    """Status word of the library's fixed scratch array (used by ``forward_static_device``) on the current
+    device: 0, or the code of a bounded device-side wait that gave up.  Sticky until read with ``clear``."""
+    from ctypes import c_int
+    out = c_int()
+    _lib.call("b200exl3_static_status", byref(out), 1 if clear else 0)
+    return out.value
+
+
 class Exl3Linear:
     """One EXL3-quantized linear layer resident on the GPU.
 

@@ -32,3 +32,36 @@ def topk(values: np.ndarray, top_k: int, normalize: bool, stream: Stream = DEFAU
     topk_device(d_values.ptr, F16 if values.dtype == np.float16 else F32, rows, experts, top_k, normalize, d_indices.ptr,
                 d_scores.ptr, stream)
     return (d_indices.download((rows, top_k), np.uint32, stream), d_scores.download((rows, top_k), values.dtype, stream))
+
+
+def softmax_topk(logits: np.ndarray, top_k: int, normalize: bool = True, stream: Stream = DEFAULT_STREAM):
+    """``router::topk(&logits.softmax_precise(), top_k, normalize)`` (native/src/qwen35.rs:214): returns
+    ``(indices, scores, probabilities)``; the softmax runs in fp32 and is rounded to the logits' dtype."""
+    logits = np.asarray(logits)
+    if logits.ndim != 2:
+        raise B200Exl3Error("router values must have rank 2")
+    if logits.dtype not in (np.float16, np.float32):
+        raise B200Exl3Error("native router expects FP16 or FP32 values")
+    rows, experts = logits.shape
+    d_logits = DeviceBuffer.from_numpy(logits, stream)
+    d_indices = DeviceBuffer(max(rows * top_k, 1) * 4)
+    d_scores = DeviceBuffer(max(rows * top_k, 1) * logits.dtype.itemsize)
+    d_probs = DeviceBuffer(max(logits.nbytes, 1))
+    _lib.call("b200exl3_router_softmax_topk", c_void_p(d_logits.ptr), F16 if logits.dtype == np.float16 else F32, rows, experts,
+              top_k, int(normalize), c_void_p(d_indices.ptr), c_void_p(d_scores.ptr), c_void_p(d_probs.ptr), c_void_p(stream.handle))
+    return (d_indices.download((rows, top_k), np.uint32, stream), d_scores.download((rows, top_k), logits.dtype, stream),
+            d_probs.download((rows, experts), logits.dtype, stream))
+
+
+def gate(x: np.ndarray, weight: np.ndarray, stream: Stream = DEFAULT_STREAM) -> np.ndarray:
+    """fp16 router logits ``x [rows, in] @ weight [experts, in].T`` with fp32 accumulation."""
+    x, weight = np.ascontiguousarray(x, np.float16), np.ascontiguousarray(weight, np.float16)
+    if x.ndim != 2 or weight.ndim != 2 or x.shape[1] != weight.shape[1]:
+        raise B200Exl3Error("invalid router gate dimensions")
+    rows, n_in = x.shape
+    experts = weight.shape[0]
+    d_x, d_w = DeviceBuffer.from_numpy(x, stream), DeviceBuffer.from_numpy(weight, stream)
+    d_logits = DeviceBuffer(rows * experts * 2)
+    _lib.call("b200exl3_router_gate", c_void_p(d_x.ptr), F16, c_void_p(d_w.ptr), rows, n_in, experts, c_void_p(d_logits.ptr),
+              c_void_p(stream.handle))
+    return d_logits.download((rows, experts), np.float16, stream)

@@ -110,6 +110,14 @@ class TpContext:
         _lib.call("b200exl3_tp_status", c_void_p(self.handle), byref(out))
         return out.value
 
+    def reset(self) -> None:
+        """After a wait gave up (status 4): clears this rank's inbox, use counts and status.  Every rank calls it,
+        between steps, once all ranks have stopped launching."""
+        from ctypes import c_void_p
+
+        from . import _lib
+        _lib.call("b200exl3_tp_reset", c_void_p(self.handle))
+
     def close(self) -> None:
         """Call on every rank after all ranks have finished using the buffers."""
         from ctypes import c_void_p

@@ -34,3 +34,20 @@ def topk(values: np.ndarray, k: int, normalize: bool):
         else:
             scores[r] = selected
     return indices, scores
+
+
+def softmax_precise(logits: np.ndarray) -> np.ndarray:
+    """Row softmax in fp32, rounded to the logits' dtype: ``exp(x - max) * (1 / sum)`` -- the arithmetic of MLX's
+    ``softmax(..., precise=True)`` (third-party, MLX 0.32.2, reached through native/src/array.rs:1589).  The order
+    of its fp32 sum and the last bits of its ``exp`` are not pinned by any stored reference output (parity unpinned
+    for those bits); comparisons against this function allow one unit in the last place of the result."""
+    logits = np.asarray(logits)
+    x = logits.astype(np.float32)
+    e = np.exp(x - x.max(axis=1, keepdims=True), dtype=np.float32)
+    inv = np.float32(1.0) / e.sum(axis=1, keepdims=True, dtype=np.float32)
+    return (e * inv).astype(logits.dtype)
+
+
+def gate(x: np.ndarray, weight: np.ndarray) -> np.ndarray:
+    """fp16 logits of the router gate: fp32 product of fp16 operands, rounded once."""
+    return (np.asarray(x, np.float16).astype(np.float32) @ np.asarray(weight, np.float16).astype(np.float32).T).astype(np.float16)

@@ -124,3 +124,40 @@ def test_switch_glu_validation(gpu):
     with pytest.raises(gpu.B200Exl3Error, match="SwitchGLU input must have rank 2"):
         moe.forward(np.zeros(128, np.float16), np.zeros((1, 2), np.uint32), np.zeros((1, 2), np.float16))
     moe.close()
+
+
+@pytest.mark.parametrize("pdl", [1, 2])
+def test_routes_written_by_the_previous_kernel_under_dependent_launch(gpu, pdl):
+    """Router and expert block alternate on one stream with programmatic dependent launch switched on and routes
+    that change every iteration: the expert kernels must read the routes the router has just written, never the
+    previous iteration's (they wait for the previous kernel's memory before touching them)."""
+    from mlxl3_b200 import router
+    from mlxl3_b200.runtime import DeviceBuffer, Stream
+    from oracle import router as oracle_router
+    rng = np.random.default_rng(60 + pdl)
+    experts, top_k, n_in, hidden, k, cb = 16, 4, 256, 256, 4, 0
+    bank = make_bank(rng, experts, n_in, hidden, k)
+    moe = gpu.Exl3SwitchGlu(*bank, top_k, k, cb, exact_weights=True)
+    stream = Stream()
+    ws = gpu.new_workspace(moe.workspace_bytes(1))
+    d_sel, d_scores, d_y = DeviceBuffer(top_k * 4), DeviceBuffer(top_k * 2), DeviceBuffer(n_in * 2)
+    iters = 6
+    xs = rng.standard_normal((iters, 1, n_in)).astype(np.float16)
+    logits = (rng.standard_normal((iters, 1, experts)) * 2).astype(np.float16)
+    d_xs = [DeviceBuffer.from_numpy(x) for x in xs]
+    d_logits = [DeviceBuffer.from_numpy(v) for v in logits]
+    d_ys = [DeviceBuffer(n_in * 2) for _ in range(iters)]
+    gpu.set_option("pdl", pdl)
+    try:
+        for i in range(iters):                         # back to back, no host synchronisation in between
+            router.topk_device(d_logits[i].ptr, gpu.F16, 1, experts, top_k, True, d_sel.ptr, d_scores.ptr, stream)
+            moe.forward_device(d_xs[i].ptr, gpu.F16, 1, d_sel.ptr, d_scores.ptr, gpu.F16, d_ys[i].ptr, ws, stream)
+        stream.sync()
+    finally:
+        gpu.set_option("pdl", 0)
+    assert gpu.workspace_status(ws) == 0
+    for i in range(iters):
+        sel, scores = oracle_router.topk(logits[i], top_k, True)
+        want = oracle.switch_glu_forward(*bank, top_k, k, cb, xs[i], sel, scores)
+        check(d_ys[i].download((1, n_in), np.float16, stream), want)
+    moe.close()

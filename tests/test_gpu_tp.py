@@ -152,3 +152,57 @@ def test_two_gpus_row_and_column_shards(gpu):
     assert np.abs(res0[0].astype(np.float32) - full).max() <= 1e-2 * np.abs(full).max()
     y_col = np.concatenate([col0, col1], axis=1).astype(np.float32)
     assert np.abs(y_col - full).max() <= 1e-2 * np.abs(full).max()
+
+
+def test_wait_that_runs_out_sets_status_and_returns(gpu):
+    """Failure made on the host: a world of two on one GPU whose second rank does not exist, so its words never
+    arrive.  With the wait limit shortened to 30 ms the kernel must return (nothing hangs or faults), the context's
+    status must read 4, a second call must return at once, a reset must make the context clean again, and other
+    work on the device must be unaffected."""
+    import ctypes
+    import time
+    from ctypes import byref, c_int, c_void_p
+
+    from mlxl3_b200 import _lib
+    from mlxl3_b200.runtime import DeviceBuffer, Stream
+    rows = 2
+    trellis, suh, svh, bias, x = _layer(rows)
+    layer = gpu.Exl3Linear(trellis, suh, svh, bias, K, CB, exact_weights=True)
+    units = rows * N_OUT // 128
+    bufs, handle = [], ctypes.create_string_buffer(64)
+    for _ in range(2):
+        p = c_void_p()
+        _lib.call("b200exl3_tp_alloc", 2, units, byref(p), handle)
+        bufs.append(p.value)
+    ctx = c_void_p()
+    _lib.call("b200exl3_tp_create", 0, 2, units, (c_void_p * 2)(*bufs), byref(ctx))
+    stream = Stream()
+    d_x, d_y, d_ref = DeviceBuffer.from_numpy(x), DeviceBuffer(rows * N_OUT * 2), DeviceBuffer(rows * N_OUT * 2)
+    ws = gpu.new_workspace(layer.workspace_bytes(rows))
+    gpu.set_option("tp_wait_ms", 30)
+    try:
+        status = c_int(-1)
+        for call in range(2):
+            t0 = time.perf_counter()
+            _lib.call("b200exl3_linear_forward_tp", c_void_p(layer.handle), ctx, c_void_p(d_x.ptr), gpu.F16, rows,
+                      c_void_p(d_y.ptr), c_void_p(ws.ptr), ws.nbytes, c_void_p(stream.handle))
+            stream.sync()
+            elapsed = time.perf_counter() - t0
+            assert elapsed < 2.0, elapsed                    # the first call waits about 30 ms per unit at most
+            _lib.call("b200exl3_tp_status", ctx, byref(status))
+            assert status.value == 4
+        assert gpu.workspace_status(ws) == 0                 # the layer's own copies were fine
+        _lib.call("b200exl3_tp_reset", ctx)
+        _lib.call("b200exl3_tp_status", ctx, byref(status))
+        assert status.value == 0
+        # the device and the layer are still usable: a plain forward gives the oracle's result
+        layer.forward_device(d_x.ptr, gpu.F16, rows, d_ref.ptr, ws, stream)
+        got = d_ref.download((rows, N_OUT), np.float16, stream).astype(np.float32)
+        want = oracle.linear_forward(trellis, K, CB, suh, svh, bias, x).astype(np.float32)
+        assert np.abs(got - want).max() <= 1e-2 * np.abs(want).max()
+    finally:
+        gpu.set_option("tp_wait_ms", 4000)
+        _lib.load().b200exl3_tp_free(ctx)
+        for p in bufs:
+            _lib.call("b200exl3_free", c_void_p(p))
+        layer.close()

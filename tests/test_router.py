@@ -95,3 +95,40 @@ def test_router_specials_and_validation(gpu):
         router.topk(np.zeros((1, 1025), np.float16), 2, False)
     with pytest.raises(gpu.B200Exl3Error, match="rank 2"):
         router.topk(np.zeros(4, np.float16), 2, False)
+
+
+def test_oracle_softmax_rows_sum_to_one_and_keep_order():
+    rng = np.random.default_rng(3)
+    logits = (rng.standard_normal((4, 128)) * 2).astype(np.float16)
+    p = oracle_router.softmax_precise(logits)
+    assert p.dtype == np.float16 and np.abs(p.astype(np.float32).sum(axis=1) - 1).max() < 2e-3
+    assert np.array_equal(np.argmax(p, axis=1), np.argmax(logits, axis=1))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [np.float16, np.float32])
+@pytest.mark.parametrize("rows,experts,k", [(1, 128, 8), (256, 128, 8), (7, 60, 4), (3, 1024, 10)])
+def test_softmax_router_matches_oracle(gpu, dtype, rows, experts, k):
+    """The softmax may differ from the oracle's by one unit in the last place (exp and the fp32 sum order are not
+    pinned); the routes must be exactly the oracle's routes on the probabilities the GPU produced."""
+    from mlxl3_b200 import router
+    rng = np.random.default_rng(experts + rows)
+    logits = (rng.standard_normal((rows, experts)) * 1.5).astype(dtype)
+    ids, scores, probs = router.softmax_topk(logits, k, True)
+    want = oracle_router.softmax_precise(logits)
+    as_int = np.int32 if dtype == np.float32 else np.int16
+    assert probs.dtype == dtype and np.abs(probs.view(as_int).astype(np.int64) - want.view(as_int).astype(np.int64)).max() <= (1 if dtype == np.float16 else 8)
+    want_i, want_s = oracle_router.topk(probs, k, True)
+    bits_t = np.uint16 if dtype == np.float16 else np.uint32
+    assert np.array_equal(ids, want_i) and np.array_equal(scores.view(bits_t), want_s.view(bits_t))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows", [1, 8, 13, 256])
+def test_router_gate_product(gpu, rows):
+    from mlxl3_b200 import router
+    rng = np.random.default_rng(rows)
+    x = rng.standard_normal((rows, 2048)).astype(np.float16)
+    w = (rng.standard_normal((128, 2048)) * 0.02).astype(np.float16)
+    got, want = router.gate(x, w).astype(np.float32), oracle_router.gate(x, w).astype(np.float32)
+    assert np.abs(got - want).max() <= 2e-3 * np.abs(want).max()

@@ -10,7 +10,7 @@ from tests.test_gpu_linear import _check_out
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("rows", [1, 5])
+@pytest.mark.parametrize("rows", [1, 5, 24])   # 24 rows: the tensor-core product also runs on the static scratch
 def test_static_scratch_forward_matches_workspace_forward(gpu, rows):
     from mlxl3_b200.runtime import DeviceBuffer, Stream
     rng = np.random.default_rng(4100 + rows)
@@ -32,6 +32,7 @@ def test_static_scratch_forward_matches_workspace_forward(gpu, rows):
         _check_out(got, want)                               # the tolerance of the layer tests ...
         assert np.array_equal(bits(got), bits(want))        # ... and in fact the same bits: same kernel, same plan
         _check_out(got, oracle.linear_forward(trellis, 4, 0, suh, svh, bias, x))
+        assert gpu.static_status() == 0                     # no bounded wait gave up on the shared array
 
 
 def test_static_scratch_rejects_oversized_calls(gpu):
