@@ -236,7 +236,22 @@ def run_ours(args) -> dict:
         return ms
 
     barrier()                                        # all ranks start the first exchange together
-    if not args.no_graph:
+    stack = None
+    if args.mode == "stack":
+        # one decode step = ONE persistent kernel launch that walks all 128 layers (b200exl3_stack_*)
+        ops = []
+        for kind, s_in, s_outs, op in layers:
+            ys = [d_y[o][i].ptr for i, o in enumerate(s_outs)] if len(s_outs) > 1 else d_y[s_outs[0]][0].ptr
+            ops.append((op, d_x[s_in].ptr, ys, tp_ctx) if (world > 1 and kind == "row") else (op, d_x[s_in].ptr, ys))
+        stack = ex.Exl3Stack(ops, ex.F16, rows)
+
+        class _Replay:
+            def launch(self, stream):
+                stack.forward(stream)
+        graph = _Replay()
+        graph.launch(stream)
+        barrier()
+    elif not args.no_graph:
         # one decode step = one graph replay: the 128 launches are recorded once (the reference's
         # engine does the same with its graph replay, native/ffi/mlx_bridge.cpp:150-175)
         launch_all()
@@ -252,6 +267,8 @@ def run_ours(args) -> dict:
 
     # one fused kernel per projection, plus the exchange kernel of every row-parallel projection when sharded
     launches_per_step = len(layers) + (sum(1 for l in layers if l[0] == "row") if world > 1 and args.unfused_exchange else 0)
+    if stack is not None:
+        launches_per_step = 1
     ms_per_step = ms_device / args.steps
     value = total_bytes / (ms_per_step * 1e-3) / 1e9
     e2e_value = total_bytes / (ms_e2e / args.steps * 1e-3) / 1e9
@@ -263,7 +280,7 @@ def run_ours(args) -> dict:
         "scaling": "strong", "vs_baseline": None, "dtype": "f16 x 4-bit trellis, f32 accumulate", "data": "synthetic",
         "config": {"workload": WORKLOAD, "k_bits": K_BITS, "codebook": CB, "rows": rows,
                    "bytes_per_step": total_bytes, "l2_policy": "inputs larger than L2 (3.49 GB of weights per step)",
-                   "parallelism": f"tp{world}", "graph_replay": graph is not None, "pdl": bool(args.pdl)},
+                   "parallelism": f"tp{world}", "mode": args.mode, "graph_replay": graph is not None and stack is None, "pdl": bool(args.pdl)},
         "linear_stack_tok_s": round(1e3 / ms_per_step, 1),
         "roofline": {"bound": "hbm", "achieved": round(per_gpu, 2), "peak": peak, "unit": "GB/s",
                      "frac": round(per_gpu / peak, 4),
@@ -282,6 +299,8 @@ def run_ours(args) -> dict:
     }
     if rank == 0 and world == 1:
         result["cpu_baseline"] = cpu_baseline(budget_s=12.0)
+    if stack is not None and stack.status() != 0:
+        raise SystemExit(f"rank {rank}: the decode-step kernel reported status {stack.status()}")
     if tp_ctx is not None:
         status = tp_ctx.status()
         barrier()
@@ -342,6 +361,8 @@ def main() -> None:
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying a graph")
     ap.add_argument("--unfused-exchange", action="store_true",
                     help="N > 1: run the sum over ranks as its own kernel after the product instead of inside it")
+    ap.add_argument("--mode", default="stack", choices=["stack", "graph"],
+                    help="stack: the whole step is one persistent kernel; graph: one fused kernel per layer, replayed as a CUDA graph")
     ap.add_argument("--pdl", type=int, default=1, help="programmatic dependent launch between layers (0/1)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

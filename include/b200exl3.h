@@ -230,6 +230,39 @@ int b200exl3_moe_forward(const b200exl3_moe* handle, const void* d_x, int x_dtyp
                          const uint32_t* d_selected, const void* d_scores, int score_dtype, void* d_y,
                          void* d_workspace, size_t workspace_bytes, b200exl3_stream stream);
 
+/* ---- a decode step as ONE launch -------------------------------------------------------------------------------
+ * Replaces the reference's recorded decode step (mlxl3_replay_capture / mlxl3_replay_apply,
+ * native/ffi/mlx_bridge.cpp:150-175): `count` layers (Exl3Linear or Exl3Group), each with its input and output
+ * pointers, become one object, and b200exl3_stack_forward runs them all, in order, in a single persistent kernel:
+ * the result is what the per-layer forward calls issued in that order on one stream would give (same kernels'
+ * arithmetic, same summation order), but the weight stream does not stop at layer boundaries and a boundary costs
+ * a counter instead of a launch.  Layer i+1 may read anything layer i wrote.
+ *   - all layers share bit width, codebook and weight mode; 1..4 activation rows in `x_dtype`; outputs in x_dtype;
+ *   - pointers are fixed at creation (as a recorded graph fixes them); the object owns its scratch memory, so
+ *     forward allocates nothing and can itself be recorded into a graph;
+ *   - a layer with `tp` set is a row shard: its column-block sums are exchanged with the other ranks inside the
+ *     kernel (all such layers of a step use the same context, all ranks run the same step);
+ *   - every wait inside the kernel is bounded (option "stack_wait_ms", default 2000): b200exl3_stack_status reads
+ *     0, or 1 (a weight copy never arrived), 2 (partition violated), 5 (a layer boundary was never reached);
+ *     after a non-zero status call b200exl3_stack_reset before the next forward;
+ *   - one forward at a time per object (calls on one stream, or otherwise ordered). */
+typedef struct b200exl3_stack b200exl3_stack;
+typedef struct b200exl3_tp b200exl3_tp;
+typedef struct {
+    const b200exl3_linear* linear;   /* exactly one of linear and group */
+    const b200exl3_group* group;
+    const void* d_x;                 /* [rows, in] */
+    void* d_y[8];                    /* one [rows, out] pointer per member (a plain layer uses d_y[0]) */
+    b200exl3_tp* tp;                 /* NULL, or the exchange context of a row-parallel layer */
+} b200exl3_stack_op;
+int b200exl3_stack_create(const b200exl3_stack_op* ops, int count, int x_dtype, int64_t rows, b200exl3_stack** out);
+void b200exl3_stack_free(b200exl3_stack* handle);
+int b200exl3_stack_forward(b200exl3_stack* handle, b200exl3_stream stream);
+int b200exl3_stack_status(const b200exl3_stack* handle, int* out_status);
+int b200exl3_stack_reset(b200exl3_stack* handle);
+/* CTAs of the persistent grid and dynamic shared memory per CTA (for reports). */
+int b200exl3_stack_geometry(const b200exl3_stack* handle, int* out_grid, size_t* out_smem_bytes);
+
 /* ---- router: stable top-k ----------------------------------------------------------------------------------
  * Replaces router::topk / routes (native/src/router.rs:28-120, native/shaders/router_topk.h:1-34): values
  * [rows, experts] (fp16 = 9 or fp32 = 10, experts <= 1024) -> indices [rows, top_k] (u32) and scores
@@ -267,7 +300,6 @@ int b200exl3_router_gate(const void* d_x, int x_dtype, const uint16_t* d_weight_
  * later waits of that context give up after a few hundred polls.  The ranks' use counts may then disagree:
  * once every rank has stopped launching, each calls b200exl3_tp_reset (own inbox, use counts and status back
  * to zero; synchronises the device) before the context is used again, or the contexts are rebuilt. */
-typedef struct b200exl3_tp b200exl3_tp;
 int b200exl3_tp_buffer_bytes(int world, int max_units, size_t* out_bytes);
 int b200exl3_tp_alloc(int world, int max_units, void** out_buffer, unsigned char* out_handle64);
 int b200exl3_tp_open(const unsigned char* handle64, void** out_peer_buffer);

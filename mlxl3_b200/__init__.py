@@ -6,10 +6,11 @@ and it raises if the library is not built -- there is no CPU fallback.
 from ._lib import BF16, F16, F32, B200Exl3Error, LIB_PATH
 from .linear import DEFAULT, MCG, MUL1, Exl3Group, Exl3Linear, new_workspace, static_status, workspace_status
 from .moe import Exl3SwitchGlu
+from .stack import Exl3Stack
 from .runtime import DEFAULT_STREAM, DeviceBuffer, Event, Graph, PinnedBuffer, Stream, init, set_option
 from . import checkpoint, codec, router
 
 __all__ = [
     "BF16", "F16", "F32", "B200Exl3Error", "LIB_PATH", "DEFAULT", "MCG", "MUL1", "Exl3Group", "Exl3Linear", "new_workspace", "static_status", "workspace_status", "DEFAULT_STREAM",
-    "Exl3SwitchGlu", "DeviceBuffer", "Event", "Graph", "PinnedBuffer", "Stream", "init", "set_option", "checkpoint", "codec", "router",
+    "Exl3SwitchGlu", "Exl3Stack", "DeviceBuffer", "Event", "Graph", "PinnedBuffer", "Stream", "init", "set_option", "checkpoint", "codec", "router",
 ]

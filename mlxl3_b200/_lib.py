@@ -68,6 +68,12 @@ SIGNATURES = {
     "b200exl3_group_count": (c_int, [c_void_p]),
     "b200exl3_group_workspace_bytes": (c_int, [c_void_p, c_int64, POINTER(c_size_t)]),
     "b200exl3_group_forward": (c_int, [c_void_p, c_void_p, c_int, c_int64, POINTER(c_void_p), c_void_p, c_size_t, c_void_p]),
+    "b200exl3_stack_create": (c_int, [c_void_p, c_int, c_int, c_int64, POINTER(c_void_p)]),
+    "b200exl3_stack_free": (None, [c_void_p]),
+    "b200exl3_stack_forward": (c_int, [c_void_p, c_void_p]),
+    "b200exl3_stack_status": (c_int, [c_void_p, POINTER(c_int)]),
+    "b200exl3_stack_reset": (c_int, [c_void_p]),
+    "b200exl3_stack_geometry": (c_int, [c_void_p, POINTER(c_int), POINTER(c_size_t)]),
     "b200exl3_router_topk": (c_int, [c_void_p, c_int, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "b200exl3_router_softmax_topk": (c_int, [c_void_p, c_int, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "b200exl3_router_gate": (c_int, [c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p]),

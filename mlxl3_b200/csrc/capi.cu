@@ -10,6 +10,7 @@
 #include <mutex>
 #include <new>
 #include <string>
+#include <vector>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -59,7 +60,9 @@ int valid_format(int k, int cb) {
 
 std::atomic<bool> g_moe_sorted{true};                    // "moe_sorted" option: 0 keeps one row per slot for any batch
 std::atomic<bool> g_qmm_enabled{true};                   // "qmm" option: 0 sends every batch through the fused kernel
-std::atomic<long long> g_tp_wait_ms{4000};               // "tp_wait_ms" option: how long a rank polls for its peers' sums
+std::atomic<long long> g_tp_wait_ms{4000};
+std::atomic<long long> g_stack_wait_ms{2000};            // "stack_wait_ms" option: bound of a layer-boundary wait inside a step
+std::atomic<unsigned long long*> g_stack_trace{nullptr}; // "stack_trace_buffer" option               // "tp_wait_ms" option: how long a rank polls for its peers' sums
 constexpr int kMaxBatchRows = kQmvMaxRows;              // rows handled by one launch of the fused kernel
 constexpr size_t kCounterBytes = B200EXL3_WORKSPACE_HEADER_BYTES;   // arrival counters at the head of a workspace
 
@@ -133,6 +136,12 @@ int b200exl3_set_option(const char* name, int64_t value) {
     else if (!strcmp(name, "qmv_force_grid")) grid = static_cast<int>(value);
     else if (!strcmp(name, "pdl")) pdl = static_cast<int>(value);
     else if (!strcmp(name, "qmm")) { g_qmm_enabled = value != 0; return 0; }
+    else if (!strcmp(name, "stack_wait_ms")) {
+        if (value < 1 || value > 60000) return fail("stack_wait_ms must be between 1 and 60000");
+        g_stack_wait_ms = value;
+        return 0;
+    }
+    else if (!strcmp(name, "stack_trace_buffer")) { g_stack_trace = reinterpret_cast<unsigned long long*>(static_cast<uintptr_t>(value)); return 0; }
     else if (!strcmp(name, "tp_wait_ms")) {
         if (value < 1 || value > 60000) return fail("tp_wait_ms must be between 1 and 60000");
         g_tp_wait_ms = value;
@@ -637,6 +646,130 @@ int b200exl3_group_forward(const b200exl3_group* h, const void* d_x, int x_dtype
     for (int g = 0; g < h->c.groups; ++g)
         if (!d_ys[g]) return fail("NULL buffer");
     return forward_common(h->c, d_x, x_dtype, nullptr, rows, d_ys, nullptr, ws, ws_bytes, as_stream(s));
+}
+
+/* ---- a decode step as one persistent launch ----------------------------------------------------------------- */
+
+struct b200exl3_stack {
+    int n_ops, k, cb;
+    bool exact;
+    StackPlan plan;
+    StackOp* d_ops;
+    char* scratch;
+    size_t sync_bytes, scratch_bytes;
+    StackArgs args;
+};
+
+int b200exl3_stack_create(const b200exl3_stack_op* ops, int count, int x_dtype, int64_t rows, b200exl3_stack** out_handle) {
+    if (!out_handle) return fail("out pointer is NULL");
+    *out_handle = nullptr;
+    if (!ops || count <= 0 || count > 4096) return fail("a step needs between 1 and 4096 layers");
+    if (rows <= 0 || rows > kStackMaxRows) return fail("a step takes 1 to %d activation rows, got %lld", kStackMaxRows, static_cast<long long>(rows));
+    if (!dtype_is_float(x_dtype)) return fail("unsupported input dtype %d", x_dtype);
+    const LayerCore* first = nullptr;
+    const b200exl3_tp* tp = nullptr;
+    std::vector<StackOp> table(static_cast<size_t>(count));
+    for (int i = 0; i < count; ++i) {
+        const b200exl3_stack_op& src = ops[i];
+        if ((src.linear != nullptr) == (src.group != nullptr)) return fail("layer %d: give exactly one of linear and group", i);
+        const LayerCore& c = src.linear ? src.linear->c : src.group->c;
+        if (!first) first = &c;
+        if (c.k != first->k || c.cb != first->cb || ((c.flags ^ first->flags) & B200EXL3_EXACT_WEIGHTS))
+            return fail("layer %d: every layer of a step must share bit width, codebook and weight mode", i);
+        if (!src.d_x || !aligned16(src.d_x)) return fail("layer %d: input pointer is NULL or not 16-byte aligned", i);
+        for (int g = 0; g < c.groups; ++g)
+            if (!src.d_y[g] || !aligned16(src.d_y[g])) return fail("layer %d: output pointer %d is NULL or not 16-byte aligned", i, g);
+        if (src.tp) {
+            if (c.groups != 1) return fail("layer %d: a grouped layer cannot be a row shard", i);
+            if (tp && tp != src.tp) return fail("layer %d: a step uses one exchange context", i);
+            tp = src.tp;
+            if (rows * (c.out / 128) > src.tp->max_units)
+                return fail("layer %d: %lld units exceed the exchange buffers' %d", i, static_cast<long long>(rows * (c.out / 128)), src.tp->max_units);
+        }
+        StackOp& o = table[static_cast<size_t>(i)];
+        o = StackOp{};
+        o.wq = c.wq; o.x = src.d_x; o.suh = c.suh; o.svh = c.svh; o.bias = c.bias;
+        o.groups = c.groups; o.in = c.in; o.out = c.out;
+        for (int g = 0; g < c.groups; ++g) { o.gy[g] = src.d_y[g]; o.gcol0[g] = c.gcol0[g]; o.gout[g] = c.gout[g]; }
+        o.tp_unit0 = src.tp ? 0 : -1;
+    }
+    b200exl3_stack* h = new (std::nothrow) b200exl3_stack{};
+    if (!h) return fail("out of host memory");
+    h->n_ops = count; h->k = first->k; h->cb = first->cb; h->exact = (first->flags & B200EXL3_EXACT_WEIGHTS) != 0;
+    h->plan = plan_stack(h->k, static_cast<int>(rows));
+    size_t max_blocks = 0, max_partials = 0;
+    for (int i = 0; i < count; ++i) {
+        StackOp& o = table[static_cast<size_t>(i)];
+        if (!plan_stack_op(h->plan, o)) {
+            delete h;
+            return fail("layer %d (%d -> %d) cannot be part of a step", i, o.in, o.out);
+        }
+        max_blocks = std::max(max_blocks, static_cast<size_t>(o.col_blocks));
+        max_partials = std::max(max_partials, static_cast<size_t>(o.col_blocks) * o.max_pieces * rows * 128 * sizeof(float));
+    }
+    h->sync_bytes = round256((static_cast<size_t>(count) + 2) * sizeof(unsigned int));
+    const size_t counter_bytes = round256(max_blocks * sizeof(unsigned int));
+    max_partials = round256(max_partials);
+    h->scratch_bytes = h->sync_bytes + 2 * counter_bytes + 2 * max_partials;
+    int rc = check(cudaMalloc(&h->d_ops, table.size() * sizeof(StackOp)), "cudaMalloc(step table)");
+    if (!rc) rc = check(cudaMalloc(&h->scratch, h->scratch_bytes), "cudaMalloc(step scratch)");
+    if (!rc) rc = check(cudaMemcpy(h->d_ops, table.data(), table.size() * sizeof(StackOp), cudaMemcpyHostToDevice), "copy step table");
+    if (!rc) rc = check(cudaMemset(h->scratch, 0, h->sync_bytes + 2 * counter_bytes), "clear step scratch");
+    if (!rc) rc = check(cudaDeviceSynchronize(), "stack_create");
+    if (rc) {
+        b200exl3_stack_free(h);
+        return -1;
+    }
+    StackArgs& a = h->args;
+    a = StackArgs{};
+    a.ops = h->d_ops; a.n_ops = count; a.rows = static_cast<int>(rows); a.x_dtype = x_dtype; a.y_dtype = x_dtype;
+    a.op_done = reinterpret_cast<unsigned int*>(h->scratch);
+    a.exit_count = a.op_done + count;
+    a.error = a.op_done + count + 1;
+    a.counters[0] = reinterpret_cast<unsigned int*>(h->scratch + h->sync_bytes);
+    a.counters[1] = reinterpret_cast<unsigned int*>(h->scratch + h->sync_bytes + counter_bytes);
+    a.partials[0] = reinterpret_cast<float*>(h->scratch + h->sync_bytes + 2 * counter_bytes);
+    a.partials[1] = reinterpret_cast<float*>(h->scratch + h->sync_bytes + 2 * counter_bytes + max_partials);
+    a.warp_smem = h->plan.warp_smem; a.xs_offset = h->plan.xs_offset; a.stage_offset = h->plan.stage_offset;
+    a.wait_ns = static_cast<unsigned long long>(g_stack_wait_ms.load()) * 1000000ull;
+    if (tp) a.tp = tp_peers(tp);
+    *out_handle = h;
+    return 0;
+}
+
+void b200exl3_stack_free(b200exl3_stack* h) {
+    if (!h) return;
+    cudaFree(h->d_ops);
+    cudaFree(h->scratch);
+    delete h;
+}
+
+int b200exl3_stack_forward(b200exl3_stack* h, b200exl3_stream s) {
+    if (!h) return fail("NULL handle");
+    h->args.trace = g_stack_trace.load();
+    return check(launch_stack(h->args, h->k, h->cb, h->exact, h->plan, as_stream(s)), "decode-step kernel");
+}
+
+int b200exl3_stack_status(const b200exl3_stack* h, int* out_status) {
+    if (!h || !out_status) return fail("NULL argument");
+    unsigned int flag = 0;
+    B200_TRY(cudaMemcpy(&flag, h->args.error, sizeof flag, cudaMemcpyDeviceToHost), "read step status");
+    *out_status = static_cast<int>(flag);
+    return 0;
+}
+
+int b200exl3_stack_reset(b200exl3_stack* h) {
+    if (!h) return fail("NULL handle");
+    B200_TRY(cudaDeviceSynchronize(), "stack_reset");
+    B200_TRY(cudaMemset(h->scratch, 0, h->scratch_bytes), "clear step scratch");
+    return check(cudaDeviceSynchronize(), "stack_reset");
+}
+
+int b200exl3_stack_geometry(const b200exl3_stack* h, int* out_grid, size_t* out_smem_bytes) {
+    if (!h) return fail("NULL handle");
+    if (out_grid) *out_grid = h->plan.grid;
+    if (out_smem_bytes) *out_smem_bytes = h->plan.smem_bytes;
+    return 0;
 }
 
 /* ---- Exl3SwitchGlu ----------------------------------------------------------------------------- */

@@ -99,6 +99,55 @@ cudaError_t launch_qmv(QmvArgs args, int k, int cb, bool exact, const QmvPlan& p
 void qmv_set_tuning(int ctas_per_sm, int force_grid, int pdl);
 void qmv_set_trace(unsigned long long* device_buffer);
 
+// ---- a whole decode step in one persistent launch (kernels_stack*.cu) ------------------------------------------
+// rows of 8 tiles a warp keeps in flight: about 8 KB per warp, so that the stream does not run dry while a layer
+// boundary is crossed
+__host__ __device__ constexpr int stack_depth(int k) { return k <= 4 ? 8 : 32 / k; }
+constexpr int kStackMaxRows = 4;     // activation rows of a step (batch-1 decode and small speculative batches)
+
+struct StackOp {               // one layer of the step; lives in device memory
+    const uint32_t* wq;        // quad layout
+    const void* x;             // [rows, in] activations (x_dtype of the stack)
+    const __half* suh;         // [groups, in]
+    const __half* svh;         // [out]
+    const __half* bias;        // [out] or nullptr
+    void* gy[kQmvMaxGroups];   // per group: [rows, gout[g]] output
+    int gcol0[kQmvMaxGroups];
+    int gout[kQmvMaxGroups];
+    int groups;
+    int in, out, tiles_k, tiles_n, col_blocks;
+    int warps;                 // warps of the grid that share this layer's tiles (a multiple of the CTA's 8)
+    int narrow;                // 1: (tiles + 1) * warps fits 32 bits
+    int max_pieces;            // bound on the CTAs that share one column block
+    int tp_unit0;              // >= 0: row shard of a tensor-parallel layer, first exchange unit; -1: none
+};
+
+struct StackArgs {
+    const StackOp* ops;
+    int n_ops, rows, x_dtype, y_dtype;
+    unsigned int* op_done;     // [n_ops] finished column blocks per layer: zero at launch, zero again at exit
+    unsigned int* exit_count;  // CTAs that have left
+    unsigned int* error;       // status word: 1 lost copy, 2 plan violated, 5 a layer-boundary wait gave up
+    float* partials[2];        // by layer parity: [col_blocks, max_pieces, rows, 128]
+    unsigned int* counters[2]; // by layer parity: [col_blocks] arrival counters, zero between layers
+    int warp_smem, xs_offset, stage_offset;
+    unsigned long long wait_ns;
+    unsigned long long* trace; // optional [grid, 4] stamps
+    TpPeers tp;
+};
+
+struct StackPlan {
+    int grid;
+    size_t smem_bytes;
+    int warp_smem, xs_offset, stage_offset;
+    bool cooperative;
+};
+// grid and shared memory of a step with `rows` activation rows at K bits
+StackPlan plan_stack(int k, int rows);
+// fills the partition fields of one layer (warps, narrow, max_pieces); false if the layer cannot be part of a step
+bool plan_stack_op(const StackPlan& plan, StackOp& op);
+cudaError_t launch_stack(const StackArgs& args, int k, int cb, bool exact, const StackPlan& plan, cudaStream_t stream);
+
 // ---- grouped experts (kernels_moe.cu) ------------------------------------------------------------------
 // SwiGLU glue between the expert projections (native/src/moe.rs:438-533, SiLU): raw gate/up sums
 // ygu[slot * 2 + {0,1}, :] -> rotated input of the down projection xhat[slot, :]
