@@ -113,6 +113,42 @@ def shard(kind: str, n_in: int, n_out: int, world: int) -> tuple[int, int]:
     return tp.shard_dims(kind, n_in, n_out, world)
 
 
+def layer_arrays(layer: int, j: int, m: int, rank: int, world: int, kind: str, n_in: int, n_out: int):
+    """Seeded synthetic tensors of rank `rank`'s shard of one projection: uniform random trellis words (any bit string
+    is a valid tile; the full layer is the ranks' shards side by side), +-1 input signs, and output scales +-c with
+    c = 1 / (1.2437 * sqrt(in)) (1.2437 = standard deviation of the default codebook's values), so that activations
+    chained through 128 projections keep a magnitude of about one.  The sign vectors are slices of full-width
+    vectors that do not depend on the rank."""
+    s_in, s_out = shard(kind, n_in, n_out, world)
+    trellis = np.random.default_rng([1001, layer, j, m, rank]).integers(0, 65536, (s_in // 16, s_out // 16, 16 * K_BITS), dtype=np.uint16)
+    rng = np.random.default_rng([1002, layer, j, m])
+    suh = np.where(rng.random(n_in) > 0.5, -1, 1).astype(np.float16)
+    scale = np.float16(1.0 / (1.2437 * np.sqrt(n_in)))
+    svh = (np.where(rng.random(n_out) > 0.5, -1, 1).astype(np.float16) * scale).astype(np.float16)
+    if world > 1 and kind == "row":
+        suh = np.ascontiguousarray(suh[rank * s_in:(rank + 1) * s_in])
+    if world > 1 and kind == "col":
+        svh = np.ascontiguousarray(svh[rank * s_out:(rank + 1) * s_out])
+    return trellis, suh, svh
+
+
+def full_layer_arrays(layer: int, j: int, m: int, world: int, kind: str, n_in: int, n_out: int):
+    """The unsharded projection the ranks' shards make up (for the CPU check)."""
+    parts = [layer_arrays(layer, j, m, r, world, kind, n_in, n_out) for r in range(world)]
+    if world == 1:
+        return parts[0]
+    axis = 0 if kind == "row" else 1
+    trellis = np.concatenate([p[0] for p in parts], axis=axis)
+    suh = np.concatenate([p[1] for p in parts]) if kind == "row" else parts[0][1]
+    svh = np.concatenate([p[2] for p in parts]) if kind == "col" else parts[0][2]
+    return trellis, suh, svh
+
+
+def close_enough(got: np.ndarray, want: np.ndarray, rel: float = 1e-2) -> bool:
+    g, w = got.astype(np.float32), want.astype(np.float32)
+    return bool(np.isfinite(g).all() and np.abs(g - w).max() <= rel * np.abs(w).max())
+
+
 def run_ours(args) -> dict:
     import mlxl3_b200 as ex
     from mlxl3_b200.runtime import DeviceBuffer, Event, Graph, PinnedBuffer, Stream
@@ -130,19 +166,16 @@ def run_ours(args) -> dict:
     rows = 1
 
     # ---- build the sharded projections, each with its own seeded weights -------------------------
+    # The activations are chained as in a decoder: [q|k|v] reads the hidden row, o reads q's output (standing in for
+    # the attention output), [gate|up] reads o's output, down reads gate's output, the next layer reads down's output.
+    # Every projection therefore depends on the one before it.
     layers = []            # (kind, in, [outs], operator)
     total_bytes = 0
-    rng_x = np.random.default_rng(4242)
     for layer in range(LAYERS):
         for j, (names, n_in, n_outs, kind) in enumerate(LAUNCHES):
             members = []
             for m, n_out in enumerate(n_outs):
-                s_in, s_out = shard(kind, n_in, n_out, world)
-                rng = np.random.default_rng([1001, layer, j, m, rank])
-                trellis = rng.integers(0, 65536, (s_in // 16, s_out // 16, 16 * K_BITS), dtype=np.uint16)
-                suh = np.where(rng.random(s_in) > 0.5, -1, 1).astype(np.float16)
-                svh = np.where(rng.random(s_out) > 0.5, -1, 1).astype(np.float16)
-                members.append(ex.Exl3Linear(trellis, suh, svh, None, K_BITS, CB))
+                members.append(ex.Exl3Linear(*layer_arrays(layer, j, m, rank, world, kind, n_in, n_out), None, K_BITS, CB))
                 total_bytes += algorithmic_bytes(n_in, n_out, K_BITS, rows)   # whole-job bytes, counted once
             if len(members) > 1:
                 op = ex.Exl3Group(members)
@@ -151,19 +184,32 @@ def run_ours(args) -> dict:
             else:
                 op = members[0]
             layers.append((kind, shard(kind, n_in, n_outs[0], world)[0], [shard(kind, n_in, o, world)[1] for o in n_outs], op))
-    x_host = {n: PinnedBuffer((rows, n), np.float16) for n in {l[1] for l in layers}}
-    for n, buf in x_host.items():
-        buf.array[...] = rng_x.standard_normal((rows, n)).astype(np.float16)
-    d_x = {n: DeviceBuffer.from_numpy(buf.array) for n, buf in x_host.items()}
-    d_y = {n: [DeviceBuffer(rows * n * 2) for _ in range(3)] for n in {o for l in layers for o in l[2]}}
+    x_host = PinnedBuffer((rows, HIDDEN), np.float16)
+    x_host.array[...] = np.random.default_rng(4242).standard_normal((rows, HIDDEN)).astype(np.float16)
+    d_in = DeviceBuffer.from_numpy(x_host.array)
+    # one output buffer per member of every launch of layer 0 (kept for the parity check) and a shared set for the
+    # other layers (their values only feed the next launch)
+    outs = []              # per launch: list of DeviceBuffer, one per member
+    shared = {}
+    for index, (kind, s_in, s_outs, op) in enumerate(layers):
+        if index < len(LAUNCHES):
+            outs.append([DeviceBuffer(rows * o * 2) for o in s_outs])
+        else:
+            key = index % len(LAUNCHES)
+            if key not in shared:
+                shared[key] = [DeviceBuffer(rows * o * 2) for o in s_outs]
+            outs.append(shared[key])
+    inputs = []            # per launch: DeviceBuffer it reads
+    for index in range(len(layers)):
+        inputs.append(d_in if index == 0 else outs[index - 1][0])
     y_host = PinnedBuffer((rows, layers[-1][2][0]), np.float16)
     ws = ex.new_workspace(max(l[3].workspace_bytes(rows) for l in layers))
 
     stream = Stream()
     tp_ctx = None
     if world > 1:
-        # row-parallel layers exchange their fp32 partial sums through peer memory inside one kernel
-        # (b200exl3_linear_finish_tp); torch.distributed only carries the IPC handles, the barriers and the timing
+        # row-parallel layers exchange their fp32 partial sums through peer memory inside the kernel;
+        # torch.distributed only carries the IPC handles, the barriers and the timing
         from mlxl3_b200.tp import TpContext
 
         def exchange(raw: bytes) -> list:
@@ -182,31 +228,29 @@ def run_ours(args) -> dict:
     graph = None
 
     def launch_all() -> None:
-        for kind, s_in, s_outs, op in layers:
+        for index, (kind, s_in, s_outs, op) in enumerate(layers):
+            src, dst = inputs[index], outs[index]
             if world > 1 and kind == "row":
-                # row-parallel: the kernel's final reduction also adds the other ranks' partial sums (peer memory)
                 if args.unfused_exchange:
                     buf = yhat[s_outs[0]]
-                    op.forward_partial_device(d_x[s_in].ptr, ex.F16, rows, buf.ptr, ws, stream)
-                    tp_ctx.finish(op, buf.ptr, rows, ex.F16, d_y[s_outs[0]][0].ptr, stream)
+                    op.forward_partial_device(src.ptr, ex.F16, rows, buf.ptr, ws, stream)
+                    tp_ctx.finish(op, buf.ptr, rows, ex.F16, dst[0].ptr, stream)
                 else:
-                    tp_ctx.forward(op, d_x[s_in].ptr, ex.F16, rows, d_y[s_outs[0]][0].ptr, ws, stream)
+                    tp_ctx.forward(op, src.ptr, ex.F16, rows, dst[0].ptr, ws, stream)
             elif len(s_outs) > 1:
-                op.forward_device(d_x[s_in].ptr, ex.F16, rows, [d_y[o][i].ptr for i, o in enumerate(s_outs)], ws, stream)
+                op.forward_device(src.ptr, ex.F16, rows, [d.ptr for d in dst], ws, stream)
             else:
-                op.forward_device(d_x[s_in].ptr, ex.F16, rows, d_y[s_outs[0]][0].ptr, ws, stream)
+                op.forward_device(src.ptr, ex.F16, rows, dst[0].ptr, ws, stream)
 
     def step(host_io: bool) -> None:
         if host_io:
-            first = layers[0][1]
-            d_x[first].upload(x_host[first].array, stream)
+            d_in.upload(x_host.array, stream)
         if graph is not None:
             graph.launch(stream)
         else:
             launch_all()
         if host_io:
-            last = layers[-1][2][0]
-            _lib.call("b200exl3_memcpy_d2h", c_void_p(y_host.ptr), c_void_p(d_y[last][0].ptr), y_host.nbytes,
+            _lib.call("b200exl3_memcpy_d2h", c_void_p(y_host.ptr), c_void_p(outs[-1][0].ptr), y_host.nbytes,
                       c_void_p(stream.handle))
             stream.sync()
 
@@ -240,9 +284,9 @@ def run_ours(args) -> dict:
     if args.mode == "stack":
         # one decode step = ONE persistent kernel launch that walks all 128 layers (b200exl3_stack_*)
         ops = []
-        for kind, s_in, s_outs, op in layers:
-            ys = [d_y[o][i].ptr for i, o in enumerate(s_outs)] if len(s_outs) > 1 else d_y[s_outs[0]][0].ptr
-            ops.append((op, d_x[s_in].ptr, ys, tp_ctx) if (world > 1 and kind == "row") else (op, d_x[s_in].ptr, ys))
+        for index, (kind, s_in, s_outs, op) in enumerate(layers):
+            ys = [d.ptr for d in outs[index]] if len(s_outs) > 1 else outs[index][0].ptr
+            ops.append((op, inputs[index].ptr, ys, tp_ctx) if (world > 1 and kind == "row") else (op, inputs[index].ptr, ys))
         stack = ex.Exl3Stack(ops, ex.F16, rows)
 
         class _Replay:
@@ -260,12 +304,79 @@ def run_ours(args) -> dict:
             launch_all()
         barrier()
 
+    # ---- correctness before timing, on the very buffers that are timed (outside the timed region) ------------
+    # Layer 0's launches are compared with the CPU oracle on the inputs they actually read.  With several ranks the
+    # ranks' outputs of the row-parallel o projection must also be the same bytes, and the per-layer fused kernel's
+    # output must equal the oracle's rotation of the rank-ordered fp32 sum of the ranks' partial products bit for bit.
+    import oracle
+    step(False)
+    barrier()
+    mine = {"in": x_host.array.copy()}
+    for index in range(len(LAUNCHES)):
+        for m, buf in enumerate(outs[index]):
+            mine[(index, m)] = buf.download((rows, layers[index][2][m]), np.float16, stream)
+    last = outs[-1][0].download((rows, layers[-1][2][0]), np.float16, stream)
+    if world > 1:
+        o_kind, o_in, o_outs, o_op = layers[1]
+        d_part, d_fused = DeviceBuffer(rows * o_outs[0] * 4), DeviceBuffer(rows * o_outs[0] * 2)
+        o_op.forward_partial_device(inputs[1].ptr, ex.F16, rows, d_part.ptr, ws, stream)
+        barrier()
+        tp_ctx.forward(o_op, inputs[1].ptr, ex.F16, rows, d_fused.ptr, ws, stream)
+        barrier()
+        mine["o_partial"] = d_part.download((rows, o_outs[0]), np.float32, stream)
+        mine["o_fused"] = d_fused.download((rows, o_outs[0]), np.float16, stream)
+        everyone = [None] * world
+        dist.all_gather_object(everyone, mine)
+    else:
+        everyone = [mine]
+    checked = {"ok": True, "cases": 0}
+    if rank == 0:
+        def whole(index, m):            # a launch member's full-width output
+            kind = layers[index][0]
+            return everyone[0][(index, m)] if kind == "row" else np.concatenate([e[(index, m)] for e in everyone], axis=1)
+        failures = []
+        source = everyone[0]["in"]
+        for index, (names, n_in, n_outs, kind) in enumerate(LAUNCHES):
+            for m, n_out in enumerate(n_outs):
+                trellis, suh, svh = full_layer_arrays(0, index, m, world, kind, n_in, n_out)
+                want = oracle.linear_forward(trellis, K_BITS, CB, suh, svh, None, source)
+                checked["cases"] += 1
+                if not close_enough(whole(index, m), want):
+                    failures.append(f"layer 0 {names[m]} differs from the CPU oracle")
+            if kind == "row":
+                for r in range(1, world):
+                    if not np.array_equal(everyone[r][(index, 0)].view(np.uint16), everyone[0][(index, 0)].view(np.uint16)):
+                        failures.append(f"layer 0 {names[0]}: rank {r} and rank 0 hold different bytes")
+            source = whole(index, 0)
+        if world > 1:
+            total = everyone[0]["o_partial"].copy()
+            for r in range(1, world):
+                total = total + everyone[r]["o_partial"]                       # fp32, rank order
+            _, _, svh_o = full_layer_arrays(0, 1, 0, world, "row", HIDDEN, HIDDEN)
+            want_bits = oracle.finish(total, svh_o, None).view(np.uint16)
+            for r in range(world):
+                if not np.array_equal(everyone[r]["o_fused"].view(np.uint16), want_bits):
+                    failures.append(f"rank {r}: fused row-parallel kernel != oracle.finish(sum of partials), bit for bit")
+            checked["tp_bit_exact_ranks"] = world
+        if not np.isfinite(last.astype(np.float32)).all() or not np.abs(last.astype(np.float32)).max() > 0:
+            failures.append("the step's last output is not finite or is all zero")
+        checked["ok"] = not failures
+        checked["failures"] = failures
+    if dist is not None:
+        flag = [checked["ok"]]
+        dist.broadcast_object_list(flag, src=0)
+        checked["ok"] = flag[0]
+    if not checked["ok"]:
+        if rank == 0:
+            print(json.dumps({"checked": checked}), flush=True)
+        raise SystemExit(f"rank {rank}: parity check failed before timing")
+
     sampler = ClockSampler(local_rank) if rank == 0 else None
     ms_device = timed(host_io=False)
     clocks = sampler.stop() if sampler else None
     ms_e2e = timed(host_io=True)
 
-    # one fused kernel per projection, plus the exchange kernel of every row-parallel projection when sharded
+    # launches per step: one persistent kernel, or one fused kernel per projection (plus the exchange kernels when unfused)
     launches_per_step = len(layers) + (sum(1 for l in layers if l[0] == "row") if world > 1 and args.unfused_exchange else 0)
     if stack is not None:
         launches_per_step = 1
@@ -280,19 +391,20 @@ def run_ours(args) -> dict:
         "scaling": "strong", "vs_baseline": None, "dtype": "f16 x 4-bit trellis, f32 accumulate", "data": "synthetic",
         "config": {"workload": WORKLOAD, "k_bits": K_BITS, "codebook": CB, "rows": rows,
                    "bytes_per_step": total_bytes, "l2_policy": "inputs larger than L2 (3.49 GB of weights per step)",
-                   "parallelism": f"tp{world}", "mode": args.mode, "graph_replay": graph is not None and stack is None, "pdl": bool(args.pdl)},
+                   "parallelism": f"tp{world}", "mode": args.mode, "graph_replay": graph is not None and stack is None,
+                   "pdl": bool(args.pdl), "dataflow": "chained: every projection reads the output of the one before it"},
         "linear_stack_tok_s": round(1e3 / ms_per_step, 1),
+        "checked": checked,
         "roofline": {"bound": "hbm", "achieved": round(per_gpu, 2), "peak": peak, "unit": "GB/s",
                      "frac": round(per_gpu / peak, 4),
                      "traffic": int(total_bytes / world / len(layers) * NCU_TRAFFIC_RATIO),
-                     "traffic_note": "DRAM bytes per launch = algorithmic bytes of the average launch x 1.0007, the ratio "
+                     "traffic_note": "DRAM bytes per layer = algorithmic bytes of the average layer x 1.0007, the ratio "
                                      "ncu measured on one 4096->14336 launch (29 455 360 B read, 0 written, against "
                                      "29 433 856 B algorithmic); every weight byte is copied once, so traffic scales with the layer",
                      "peak_kind": f"of {peak_kind}",
-                     "note": "achieved = algorithmic bytes of a step / device time of the step, per GPU; the step "
-                             "is 128 launches of the one fused kernel (rotations included), so this is also the "
-                             "per-launch average"},
-        "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": rows * layers[0][1] * 2,
+                     "note": "achieved = algorithmic bytes of a step / device time of the step, per GPU; the step is "
+                             "128 layers run by one kernel family (rotations included), so this is also the per-layer average"},
+        "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": rows * HIDDEN * 2,
                 "d2h_bytes_per_step": rows * layers[-1][2][0] * 2},
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks,
@@ -330,9 +442,14 @@ def cpu_baseline(budget_s: float) -> dict:
         oracle.linear_forward(trellis, K_BITS, CB, suh, svh, None, x, threads=threads)
         reps += 1
     dt = (time.perf_counter() - t0) / reps
+    step_bytes = LAYERS * sum(algorithmic_bytes(n_in, o, K_BITS, 1) for _, n_in, outs, _ in LAUNCHES for o in outs)
+    share = algorithmic_bytes(n, n, K_BITS, 1) / step_bytes
     return {"value": round(algorithmic_bytes(n, n, K_BITS, 1) / dt / 1e9, 3), "unit": "GB/s", "cores": threads,
-            "kind": "port", "ms_per_layer": round(dt * 1e3, 3),
-            "sample": f"{reps} calls of the 4096x4096 K=4 o projection, one row (1/224 of a step each)"}
+            "kind": "port", "ms_per_layer": round(dt * 1e3, 3), "ms_per_step_extrapolated": round(dt * 1e3 / share, 1),
+            "sample": f"{reps} calls of the 4096x4096 K=4 o projection, one row ({share:.5f} of a step's bytes each)",
+            "python_ref": {"ms": 288.4, "layer": "128x128, K=4, one row", "what": "the reference's own numpy path "
+                           "(ponyexl3.ref.linear_forward_reconstruct), timed once where the reference tree is mounted; "
+                           "it does not travel with this repository"}}
 
 
 def run_reference(args) -> dict:
@@ -343,7 +460,7 @@ def run_reference(args) -> dict:
     base = cpu_baseline(budget_s=max(2.0, min(60.0, 2.0 * (args.steps + args.warmup))))
     return {
         "impl": "reference", "metric": "exl3_qmv_effective_hbm_gbs", "value": base["value"], "unit": "GB/s",
-        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_layer"] * 224,
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_step_extrapolated"],
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16 x 4-bit trellis, f32 accumulate",
         "data": "synthetic", "config": {"workload": WORKLOAD, "k_bits": K_BITS, "codebook": CB, "rows": 1},
         "cpu_baseline": base,

@@ -232,12 +232,12 @@ int b200exl3_moe_forward(const b200exl3_moe* handle, const void* d_x, int x_dtyp
 
 /* ---- a decode step as ONE launch -------------------------------------------------------------------------------
  * Replaces the reference's recorded decode step (mlxl3_replay_capture / mlxl3_replay_apply,
- * native/ffi/mlx_bridge.cpp:150-175): `count` layers (Exl3Linear or Exl3Group), each with its input and output
+ * native/ffi/mlx_bridge.cpp:150-175): `count` (1..256) layers (Exl3Linear or Exl3Group), each with its input and output
  * pointers, become one object, and b200exl3_stack_forward runs them all, in order, in a single persistent kernel:
  * the result is what the per-layer forward calls issued in that order on one stream would give (same kernels'
  * arithmetic, same summation order), but the weight stream does not stop at layer boundaries and a boundary costs
  * a counter instead of a launch.  Layer i+1 may read anything layer i wrote.
- *   - all layers share bit width, codebook and weight mode; 1..4 activation rows in `x_dtype`; outputs in x_dtype;
+ *   - all layers share bit width, codebook and weight mode; 1..2 activation rows in `x_dtype`; outputs in x_dtype;
  *   - pointers are fixed at creation (as a recorded graph fixes them); the object owns its scratch memory, so
  *     forward allocates nothing and can itself be recorded into a graph;
  *   - a layer with `tp` set is a row shard: its column-block sums are exchanged with the other ranks inside the

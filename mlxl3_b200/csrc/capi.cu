@@ -663,7 +663,7 @@ struct b200exl3_stack {
 int b200exl3_stack_create(const b200exl3_stack_op* ops, int count, int x_dtype, int64_t rows, b200exl3_stack** out_handle) {
     if (!out_handle) return fail("out pointer is NULL");
     *out_handle = nullptr;
-    if (!ops || count <= 0 || count > 4096) return fail("a step needs between 1 and 4096 layers");
+    if (!ops || count <= 0 || count > kStackMaxOps) return fail("a step needs between 1 and %d layers", kStackMaxOps);
     if (rows <= 0 || rows > kStackMaxRows) return fail("a step takes 1 to %d activation rows, got %lld", kStackMaxRows, static_cast<long long>(rows));
     if (!dtype_is_float(x_dtype)) return fail("unsupported input dtype %d", x_dtype);
     const LayerCore* first = nullptr;
@@ -696,25 +696,24 @@ int b200exl3_stack_create(const b200exl3_stack_op* ops, int count, int x_dtype, 
     b200exl3_stack* h = new (std::nothrow) b200exl3_stack{};
     if (!h) return fail("out of host memory");
     h->n_ops = count; h->k = first->k; h->cb = first->cb; h->exact = (first->flags & B200EXL3_EXACT_WEIGHTS) != 0;
-    h->plan = plan_stack(h->k, static_cast<int>(rows));
-    size_t max_blocks = 0, max_partials = 0;
+    h->plan = plan_stack(h->k, static_cast<int>(rows), count);
+    size_t max_words = 0;
     for (int i = 0; i < count; ++i) {
         StackOp& o = table[static_cast<size_t>(i)];
         if (!plan_stack_op(h->plan, o)) {
             delete h;
             return fail("layer %d (%d -> %d) cannot be part of a step", i, o.in, o.out);
         }
-        max_blocks = std::max(max_blocks, static_cast<size_t>(o.col_blocks));
-        max_partials = std::max(max_partials, static_cast<size_t>(o.col_blocks) * o.max_pieces * rows * 128 * sizeof(float));
+        max_words = std::max(max_words, static_cast<size_t>(o.col_blocks) * o.max_pieces * rows * 128 * sizeof(unsigned long long));
     }
-    h->sync_bytes = round256((static_cast<size_t>(count) + 2) * sizeof(unsigned int));
-    const size_t counter_bytes = round256(max_blocks * sizeof(unsigned int));
-    max_partials = round256(max_partials);
-    h->scratch_bytes = h->sync_bytes + 2 * counter_bytes + 2 * max_partials;
+    // [finished blocks per layer | CTAs that left | status | launch number] then the tagged partial sums, by layer parity
+    h->sync_bytes = round256((static_cast<size_t>(count) + 3) * sizeof(unsigned int));
+    max_words = round256(max_words);
+    h->scratch_bytes = h->sync_bytes + 2 * max_words;
     int rc = check(cudaMalloc(&h->d_ops, table.size() * sizeof(StackOp)), "cudaMalloc(step table)");
     if (!rc) rc = check(cudaMalloc(&h->scratch, h->scratch_bytes), "cudaMalloc(step scratch)");
     if (!rc) rc = check(cudaMemcpy(h->d_ops, table.data(), table.size() * sizeof(StackOp), cudaMemcpyHostToDevice), "copy step table");
-    if (!rc) rc = check(cudaMemset(h->scratch, 0, h->sync_bytes + 2 * counter_bytes), "clear step scratch");
+    if (!rc) rc = check(cudaMemset(h->scratch, 0, h->scratch_bytes), "clear step scratch");
     if (!rc) rc = check(cudaDeviceSynchronize(), "stack_create");
     if (rc) {
         b200exl3_stack_free(h);
@@ -726,11 +725,11 @@ int b200exl3_stack_create(const b200exl3_stack_op* ops, int count, int x_dtype, 
     a.op_done = reinterpret_cast<unsigned int*>(h->scratch);
     a.exit_count = a.op_done + count;
     a.error = a.op_done + count + 1;
-    a.counters[0] = reinterpret_cast<unsigned int*>(h->scratch + h->sync_bytes);
-    a.counters[1] = reinterpret_cast<unsigned int*>(h->scratch + h->sync_bytes + counter_bytes);
-    a.partials[0] = reinterpret_cast<float*>(h->scratch + h->sync_bytes + 2 * counter_bytes);
-    a.partials[1] = reinterpret_cast<float*>(h->scratch + h->sync_bytes + 2 * counter_bytes + max_partials);
+    a.launch = a.op_done + count + 2;
+    a.piece_words[0] = reinterpret_cast<unsigned long long*>(h->scratch + h->sync_bytes);
+    a.piece_words[1] = reinterpret_cast<unsigned long long*>(h->scratch + h->sync_bytes + max_words);
     a.warp_smem = h->plan.warp_smem; a.xs_offset = h->plan.xs_offset; a.stage_offset = h->plan.stage_offset;
+    a.table_offset = h->plan.table_offset; a.x_blocks = h->plan.x_blocks;
     a.wait_ns = static_cast<unsigned long long>(g_stack_wait_ms.load()) * 1000000ull;
     if (tp) a.tp = tp_peers(tp);
     *out_handle = h;

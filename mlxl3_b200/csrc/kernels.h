@@ -103,7 +103,14 @@ void qmv_set_trace(unsigned long long* device_buffer);
 // rows of 8 tiles a warp keeps in flight: about 8 KB per warp, so that the stream does not run dry while a layer
 // boundary is crossed
 __host__ __device__ constexpr int stack_depth(int k) { return k <= 4 ? 8 : 32 / k; }
-constexpr int kStackMaxRows = 4;     // activation rows of a step (batch-1 decode and small speculative batches)
+#ifndef B200_STACK_WARPS
+#define B200_STACK_WARPS 12
+#endif
+constexpr int kStackWarps = B200_STACK_WARPS;   // warps per CTA, one CTA per SM.  Measured on one decoder layer: 12 warps (3 per scheduler, up to 170 registers each) 88 us, 16 warps (128 registers) 100 us, 8 warps 98 us, 10 and 14 (uneven over the four schedulers) 103-106 us
+constexpr int kStackCtasPerSm = 1;
+constexpr int kStackMaxRows = 2;
+constexpr int kStackTraceSlots = 8 + kStackWarps;   // stamps per (layer, CTA) in the optional trace buffer
+constexpr int kStackMaxSmemBytes = 224 * 1024;   // dynamic shared memory the kernel may ask for (227 KB per CTA less the static part)     // activation rows of a step (batch-1 decode and small speculative batches)
 
 struct StackOp {               // one layer of the step; lives in device memory
     const uint32_t* wq;        // quad layout
@@ -116,34 +123,50 @@ struct StackOp {               // one layer of the step; lives in device memory
     int gout[kQmvMaxGroups];
     int groups;
     int in, out, tiles_k, tiles_n, col_blocks;
-    int warps;                 // warps of the grid that share this layer's tiles (a multiple of the CTA's 8)
+    int warps;                 // warps of the grid that share this layer's tiles (a multiple of the CTA's warps)
     int narrow;                // 1: (tiles + 1) * warps fits 32 bits
     int max_pieces;            // bound on the CTAs that share one column block
     int tp_unit0;              // >= 0: row shard of a tensor-parallel layer, first exchange unit; -1: none
 };
+
+// What every warp needs at a layer boundary, staged in shared memory at kernel start so that the weight cursor
+// and the main loop never wait for a table read from global memory.
+struct StackOpLite {
+    const uint32_t* wq;
+    const void* x;
+    const __half* suh;
+    const __half* svh;
+    const __half* bias;
+    void* y0;                  // output of a plain layer (grouped layers read their outputs from the full table)
+    int tiles_k, tiles_n, col_blocks, warps, narrow, in, groups, max_pieces, tp_unit0, gout0;
+};
+constexpr int kStackMaxOps = 256;    // layers per launch: the staged table takes 88 bytes per layer
 
 struct StackArgs {
     const StackOp* ops;
     int n_ops, rows, x_dtype, y_dtype;
     unsigned int* op_done;     // [n_ops] finished column blocks per layer: zero at launch, zero again at exit
     unsigned int* exit_count;  // CTAs that have left
-    unsigned int* error;       // status word: 1 lost copy, 2 plan violated, 5 a layer-boundary wait gave up
-    float* partials[2];        // by layer parity: [col_blocks, max_pieces, rows, 128]
-    unsigned int* counters[2]; // by layer parity: [col_blocks] arrival counters, zero between layers
+    unsigned int* error;       // status word: 1 lost copy, 2 plan violated, 5 a layer-boundary wait gave up, 6 a partial sum never arrived
+    unsigned long long* piece_words[2];   // by layer parity: [col_blocks, max_pieces, rows, 128] {partial sum, tag} words
+    unsigned int* launch;      // number of completed launches (the tags of a launch are made of it)
     int warp_smem, xs_offset, stage_offset;
+    int x_blocks;              // 128-blocks of rotated activations a warp keeps per row (the chunk length of its walk)
     unsigned long long wait_ns;
-    unsigned long long* trace; // optional [grid, 4] stamps
+    unsigned long long* trace; // optional [n_ops, grid, kStackTraceSlots] stamps; warp 0: boundary passed, rotated, main loop done, block carried on; the warp that
+                               // carries a block on: start, after the atomic, pieces added, stored and counted; then every warp: its tiles done
+    int table_offset;          // offset of the staged layer table in dynamic shared memory
     TpPeers tp;
 };
 
 struct StackPlan {
     int grid;
     size_t smem_bytes;
-    int warp_smem, xs_offset, stage_offset;
+    int warp_smem, xs_offset, stage_offset, table_offset, x_blocks;
     bool cooperative;
 };
 // grid and shared memory of a step with `rows` activation rows at K bits
-StackPlan plan_stack(int k, int rows);
+StackPlan plan_stack(int k, int rows, int n_ops);
 // fills the partition fields of one layer (warps, narrow, max_pieces); false if the layer cannot be part of a step
 bool plan_stack_op(const StackPlan& plan, StackOp& op);
 cudaError_t launch_stack(const StackArgs& args, int k, int cb, bool exact, const StackPlan& plan, cudaStream_t stream);

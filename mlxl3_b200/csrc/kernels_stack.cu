@@ -16,20 +16,20 @@ cudaError_t stack_dispatch_k6(const StackArgs&, int, bool, const StackPlan&, cud
 cudaError_t stack_dispatch_k7(const StackArgs&, int, bool, const StackPlan&, cudaStream_t);
 cudaError_t stack_dispatch_k8(const StackArgs&, int, bool, const StackPlan&, cudaStream_t);
 
-StackPlan plan_stack(int k, int rows) {
+StackPlan plan_stack(int k, int rows, int n_ops) {
     StackPlan plan{};
     const int r = std::max(1, std::min(rows, kStackMaxRows));
     // per warp: [ring of packed rows | rotated activations | two staged result tiles]
     const size_t ring = static_cast<size_t>(stack_depth(k)) * 64 * k * sizeof(uint32_t);
-    const size_t xs = static_cast<size_t>(r) * kQmvXBlocks * 128 * sizeof(__half);
+    plan.x_blocks = r == 1 ? kQmvXBlocks : 4;
+    const size_t xs = static_cast<size_t>(r) * plan.x_blocks * 128 * sizeof(__half);
     const size_t stage = 2 * static_cast<size_t>(r) * kQmvRedStride * sizeof(float);
     plan.xs_offset = static_cast<int>(ring);
     plan.stage_offset = static_cast<int>(ring + xs);
     plan.warp_smem = static_cast<int>((ring + xs + stage + 15) / 16 * 16);
-    plan.smem_bytes = static_cast<size_t>(plan.warp_smem) * kQmvWarps;
-    // two CTAs per SM when their shared memory fits (about 227 KB per SM, 1 KB reserved per CTA)
-    const int per_sm = 2 * (plan.smem_bytes + 1024 + 512) <= 227 * 1024 ? 2 : 1;
-    plan.grid = sm_count() * per_sm;
+    plan.table_offset = plan.warp_smem * kStackWarps;
+    plan.smem_bytes = static_cast<size_t>(plan.table_offset) + static_cast<size_t>(n_ops) * sizeof(StackOpLite);
+    plan.grid = sm_count() * kStackCtasPerSm;                 // 16 warps per SM
     plan.cooperative = true;
     return plan;
 }
@@ -43,19 +43,19 @@ bool plan_stack_op(const StackPlan& plan, StackOp& op) {
     const int64_t total = ub * op.col_blocks;
     if (total >= (int64_t(1) << 31)) return false;
     // every warp of the grid takes part unless that would leave a warp fewer than four tiles
-    int64_t ctas = std::max<int64_t>(1, std::min<int64_t>(plan.grid, total / (kQmvWarps * 4)));
+    int64_t ctas = std::max<int64_t>(1, std::min<int64_t>(plan.grid, total / (kStackWarps * 4)));
     // a warp's range must stay within one column block's worth of units (it then touches at most two blocks)
     const int64_t min_warps = (total + ub - 2) / (ub - 1) + 1;
-    ctas = std::max(ctas, (min_warps + kQmvWarps - 1) / kQmvWarps);
+    ctas = std::max(ctas, (min_warps + kStackWarps - 1) / kStackWarps);
     if (ctas > plan.grid) return false;                       // wider than the grid can cover in one pass
-    op.warps = static_cast<int>(ctas) * kQmvWarps;
+    op.warps = static_cast<int>(ctas) * kStackWarps;
     op.narrow = static_cast<unsigned long long>(total + 1) * static_cast<unsigned long long>(op.warps) < 0xffffffffull ? 1 : 0;
     op.max_pieces = static_cast<int>((ctas + op.col_blocks - 1) / op.col_blocks + 1);
     return true;
 }
 
 cudaError_t launch_stack(const StackArgs& args, int k, int cb, bool exact, const StackPlan& plan, cudaStream_t stream) {
-    if (args.rows <= 0 || args.rows > kStackMaxRows || args.n_ops <= 0) return cudaErrorInvalidValue;
+    if (args.rows <= 0 || args.rows > kStackMaxRows || args.n_ops <= 0 || args.n_ops > kStackMaxOps) return cudaErrorInvalidValue;
     switch (k) {
         case 1: return stack_dispatch_k1(args, cb, exact, plan, stream);
         case 2: return stack_dispatch_k2(args, cb, exact, plan, stream);

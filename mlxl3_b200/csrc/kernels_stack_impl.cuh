@@ -19,8 +19,12 @@
 //    the layer before it is complete (one warp per CTA polls global memory with acquire loads, the others watch a
 //    shared-memory word), bounded in time -- when a wait gives up the status word is set and everybody carries on,
 //    so a lost signal ends the kernel instead of hanging the GPU;
-//  * CTAs that share a column block meet through one acq_rel atomic instead of two fences and an atomic.
-// The counters are zero when the kernel starts and the last CTA to leave sets them back to zero.
+//  * CTAs that share a column block meet without any fence: partial sums travel as 8-byte {value, tag} words (the
+//    tag names the launch and the layer), which the block's first CTA polls and adds in piece order;
+//  * one CTA of 12 warps per SM (three per scheduler, up to 170 registers each): warps of one age advance evenly,
+//    a column block is shared by fewer CTAs, and the decode loop gets the registers it wants.
+// The layer counts are zero when the kernel starts and the last CTA to leave sets them back to zero and advances the
+// launch number the tags are made of.
 #pragma once
 
 #include "kernels_qmv_impl.cuh"
@@ -49,6 +53,17 @@ __device__ __forceinline__ void st_release_cta_shared(int* p, int v) {
     asm volatile("st.release.cta.shared::cta.s32 [%0], %1;" ::"r"(smem_addr(p)), "r"(v) : "memory");
 }
 
+// an 8-byte word {value, tag}: written and read as one 64-bit scalar access, so value and tag are seen together
+__device__ __forceinline__ void st_flagged(unsigned long long* p, uint32_t value, uint32_t tag) {
+    const unsigned long long w = (static_cast<unsigned long long>(tag) << 32) | value;
+    asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_flagged(const unsigned long long* p) {
+    unsigned long long w;
+    asm volatile("ld.relaxed.gpu.global.b64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+    return w;
+}
+
 // this warp's units [w0, w1) of a layer with T units shared by `warps` warps (warps beyond that have none)
 struct StackRange {
     int w0, w1;
@@ -69,7 +84,7 @@ struct StackCursor {
     size_t stride;
     bool valid;
 
-    __device__ __forceinline__ void segment(const StackOp& o, int w0) {
+    __device__ __forceinline__ void segment(const StackOpLite& o, int w0) {
         const int u0 = max(w0, cblock * UB) - cblock * UB;
         const int u1 = min(w1, (cblock + 1) * UB) - cblock * UB;
         tk = u0 >> 3;
@@ -78,10 +93,11 @@ struct StackCursor {
         src = reinterpret_cast<const char*>(o.wq + (static_cast<int64_t>(tk) * o.tiles_n + cblock * 8) * (8 * K));
     }
     // first layer at or after `first` in which the warp has work
-    __device__ __forceinline__ void seek(const StackOp* ops, int n_ops, int first, int wid) {
+    __device__ __forceinline__ void seek(const StackOpLite* ops, int n_ops, int first, int wid) {
         valid = false;
+#pragma unroll 1
         for (op = first; op < n_ops; ++op) {
-            const StackOp& o = ops[op];
+            const StackOpLite& o = ops[op];
             UB = o.tiles_k * 8;
             const int T = UB * o.col_blocks;
             const int w0 = stack_unit_begin(T, o.warps, wid, o.narrow != 0);
@@ -94,7 +110,7 @@ struct StackCursor {
             }
         }
     }
-    __device__ __forceinline__ void next(const StackOp* ops, int n_ops, int wid) {
+    __device__ __forceinline__ void next(const StackOpLite* ops, int n_ops, int wid) {
         if (tk < tk_last) {
             ++tk;
             src += stride;
@@ -109,9 +125,9 @@ struct StackCursor {
 
 // Makes sure every layer before `op` is complete before this warp reads activations.  One warp of the CTA polls
 // the previous layer's count in global memory; the others wait for the shared word it sets.
-__device__ __forceinline__ void stack_wait(const StackArgs& a, int op, int* s_ready, unsigned int* s_poller, int lane) {
+__device__ __forceinline__ void stack_wait(const StackArgs& a, int op, int prev_blocks, int* s_ready, unsigned int* s_poller, int lane) {
     if (op > 0 && lane == 0 && ld_acquire_cta_shared(s_ready) < op) {
-        const unsigned int target = static_cast<unsigned int>(a.ops[op - 1].col_blocks);
+        const unsigned int target = static_cast<unsigned int>(prev_blocks);
         const unsigned int* count = a.op_done + (op - 1);
         unsigned long long t0 = 0;
 #pragma unroll 1
@@ -145,44 +161,57 @@ __device__ __forceinline__ void stack_wait(const StackArgs& a, int op, int* s_re
     __syncwarp();
 }
 
-// Activations of input 128-blocks [kb0, kb0 + nblk) of every row, rotated into the warp's shared memory.  As
-// qmv_rotate_chunk, but the activations are read from L2 (another SM wrote them a moment ago).
-__device__ __forceinline__ void stack_rotate_chunk(const void* x, int x_dtype, const __half* suh, int in, int rows, int kb0,
-                                                   int nblk, __half* xs, int lane) {
-    constexpr int kXsHalves = kQmvXBlocks * 128;
-    const int total = rows * nblk;
-    auto fetch = [&](int unit, uint2& sv, __half (&xv)[4]) {
-        const int row = unit / nblk, blk = unit - row * nblk;
-        const int col = (kb0 + blk) * 128 + lane * 4;
-        sv = *reinterpret_cast<const uint2*>(suh + col);
-        const int64_t at = static_cast<int64_t>(row) * in + col;
-        if (x_dtype == kF16) {
-            const uint2 v = __ldcg(reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(x) + at));
-            *reinterpret_cast<uint2*>(xv) = v;
-        } else if (x_dtype == kF32) {
-            const float4 v = __ldcg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(x) + at));
-            xv[0] = __float2half_rn(v.x); xv[1] = __float2half_rn(v.y); xv[2] = __float2half_rn(v.z); xv[3] = __float2half_rn(v.w);
-        } else {
-            const uint2 v = __ldcg(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(x) + at));
-            const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(&v);
+// Input scales of 128-blocks [kb0, kb0 + nblk) for this lane's four columns of each block.  They do not depend on
+// the previous layer, so they are fetched before the layer-boundary wait.
+__device__ __forceinline__ void stack_fetch_scales(const __half* suh, int kb0, int nblk, int lane, uint2 (&sv)[kQmvXBlocks]) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) xv[j] = __float2half_rn(__bfloat162float(b[j]));
-        }
-    };
-    uint2 sv_next;
-    __align__(8) __half xv_next[4];
-    fetch(0, sv_next, xv_next);
+    for (int b = 0; b < kQmvXBlocks; ++b)
+        if (b < nblk) sv[b] = __ldg(reinterpret_cast<const uint2*>(suh + (kb0 + b) * 128 + lane * 4));
+}
+
+// Activations of input 128-blocks [kb0, kb0 + nblk) of every row, rotated into the warp's shared memory:
+// xs[row][blk][128] = H128(half(half(x) * suh)).  The activations are read from L2 (another SM wrote them a moment
+// ago), and all loads of a row are issued before the first butterfly, so a row costs one memory round trip.
+__device__ __forceinline__ void stack_rotate_chunk(const void* x, int x_dtype, const uint2 (&sv)[kQmvXBlocks], int in, int rows,
+                                                   int kb0, int nblk, int kXsHalves, __half* xs, int lane) {
 #pragma unroll 1
-    for (int unit = 0; unit < total; ++unit) {
-        const uint2 sv = sv_next;
-        __align__(8) __half h[4];
-        const __half* sc = reinterpret_cast<const __half*>(&sv);
+    for (int row = 0; row < rows; ++row) {
+        const int64_t at = static_cast<int64_t>(row) * in + kb0 * 128 + lane * 4;
+        uint2 raw[kQmvXBlocks];
+        if (x_dtype == kF32) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) h[j] = __hmul_rn(xv_next[j], sc[j]);
-        if (unit + 1 < total) fetch(unit + 1, sv_next, xv_next);
-        warp_hadamard128_f16(h, lane);
-        const int row = unit / nblk, blk = unit - row * nblk;
-        *reinterpret_cast<uint2*>(xs + row * kXsHalves + blk * 128 + lane * 4) = *reinterpret_cast<uint2*>(h);
+            for (int b = 0; b < kQmvXBlocks; ++b)
+                if (b < nblk) {
+                    const float4 wide = __ldcg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(x) + at + b * 128));
+                    const __half2 lo = __floats2half2_rn(wide.x, wide.y), hi = __floats2half2_rn(wide.z, wide.w);
+                    raw[b] = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+                }
+        } else {
+#pragma unroll
+            for (int b = 0; b < kQmvXBlocks; ++b)
+                if (b < nblk) raw[b] = __ldcg(reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(x) + at + b * 128));
+            if (x_dtype == kBF16) {
+#pragma unroll
+                for (int b = 0; b < kQmvXBlocks; ++b)
+                    if (b < nblk) {
+                        const __nv_bfloat16* v = reinterpret_cast<const __nv_bfloat16*>(&raw[b]);
+                        const __half2 lo = __floats2half2_rn(__bfloat162float(v[0]), __bfloat162float(v[1]));
+                        const __half2 hi = __floats2half2_rn(__bfloat162float(v[2]), __bfloat162float(v[3]));
+                        raw[b] = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+                    }
+            }
+        }
+#pragma unroll
+        for (int b = 0; b < kQmvXBlocks; ++b)
+            if (b < nblk) {
+                __align__(8) __half h[4];
+                const __half* xv = reinterpret_cast<const __half*>(&raw[b]);
+                const __half* sc = reinterpret_cast<const __half*>(&sv[b]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) h[j] = __hmul_rn(xv[j], sc[j]);
+                warp_hadamard128_f16(h, lane);
+                *reinterpret_cast<uint2*>(xs + row * kXsHalves + b * 128 + lane * 4) = *reinterpret_cast<uint2*>(h);
+            }
     }
     __syncwarp();
 }
@@ -194,93 +223,156 @@ __device__ __forceinline__ int stack_group_of(const StackOp& o, int cblock) {
     return grp;
 }
 
-// The last warp of a CTA to stage its tile of column block `cblock`: adds the CTA's staged tiles in warp order,
-// meets the other CTAs of the block in global memory (the last one adds the pieces in piece order), and whoever
-// holds the complete sum exchanges it with the other ranks (row shard), rotates, stores, and counts the block as done.
-__device__ __forceinline__ void stack_finish_block(const StackArgs& a, const StackOp& o, int op, int cblock, unsigned int warp_mask,
-                                                   unsigned int second_mask, int pieces, int piece, const unsigned char* smem_base,
-                                                   int lane) {
+// The last warp of a CTA to stage its tile of column block `cblock`: adds the CTA's staged tiles in warp order and
+// meets the other CTAs of the block in global memory: every CTA but the block's first publishes its sum as tagged
+// words, the first CTA collects them and adds them in piece order.  The warp that holds the complete sum exchanges
+// it with the other ranks (row shard), rotates, stores, and counts the block as done.  Everything the last steps need
+// from memory (output scales, bias, the output pointer of a grouped layer) is requested at the start, so that the
+// chain of memory round trips is: pieces out, pieces in, result out.
+__device__ __forceinline__ void stack_finish_block(const StackArgs& a, const StackOpLite& o, int op, int cblock,
+                                                   unsigned int warp_mask, unsigned int second_mask, int pieces, int piece,
+                                                   uint32_t tag, const unsigned char* smem_base, int lane) {
     const int rows = a.rows;
     const int tile_floats = rows * 128;
-    float* partials = a.partials[op & 1];
-    unsigned int* counters = a.counters[op & 1];
-    const float* piece_base = partials + static_cast<int64_t>(cblock) * o.max_pieces * tile_floats;
-    float* piece_dst = partials + (static_cast<int64_t>(cblock) * o.max_pieces + piece) * tile_floats;
     const int stage_floats = rows * kQmvRedStride;
-#pragma unroll 1
-    for (int pass = 0; pass < (pieces > 1 ? 2 : 1); ++pass) {
-        if (pass == 1) {
-            __syncwarp();                                       // every lane's piece stores, before lane 0's release
-            unsigned int prev = 0;
-            if (lane == 0) prev = atom_acq_rel_gpu_add(counters + cblock, 1u);
-            prev = __shfl_sync(0xffffffffu, prev, 0);
-            if (prev != static_cast<unsigned int>(pieces - 1)) return;       // not the last CTA of this block
-            if (lane == 0) counters[cblock] = 0;                // ready for the next layer that uses this slot
-        }
-        const bool complete = pass == 1 || pieces == 1;
-#pragma unroll 1
-        for (int row = 0; row < rows; ++row) {
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (pass == 0) {
-                bool any = false;
-#pragma unroll 1
-                for (int w = 0; w < kQmvWarps; ++w) {
-                    if (!((warp_mask >> w) & 1u)) continue;
-                    const float4 t4 = *reinterpret_cast<const float4*>(
-                        reinterpret_cast<const float*>(smem_base + static_cast<size_t>(w) * a.warp_smem + a.stage_offset) +
-                        ((second_mask >> w) & 1u) * stage_floats + row * kQmvRedStride + lane * 4);
-                    if (!any) { v = t4; any = true; }
-                    else { v.x = __fadd_rn(v.x, t4.x); v.y = __fadd_rn(v.y, t4.y); v.z = __fadd_rn(v.z, t4.z); v.w = __fadd_rn(v.w, t4.w); }
-                }
-            } else {
-                const float* src = piece_base + row * 128 + lane * 4;
-                v = __ldcg(reinterpret_cast<const float4*>(src));
-#pragma unroll 1
-                for (int s0 = 1; s0 < pieces; s0 += 4) {
-                    float4 part[4];
+    const int col = cblock * 128 + lane * 4;
+    unsigned long long* stamp = a.trace != nullptr && lane == 0 ? a.trace + (static_cast<size_t>(op) * gridDim.x + blockIdx.x) * kStackTraceSlots : nullptr;
+    if (stamp) stamp[4] = global_ns();
+    // requested now, used at the very end
+    const uint2 sv2 = __ldg(reinterpret_cast<const uint2*>(o.svh + col));
+    uint2 bias2 = make_uint2(0u, 0u);
+    if (o.bias != nullptr) bias2 = __ldg(reinterpret_cast<const uint2*>(o.bias + col));
+    void* y = o.y0;
+    int gout = o.gout0, gcol = col;
+    if (o.groups > 1) {
+        const StackOp& full = a.ops[op];
+        const int grp = stack_group_of(full, cblock);
+        y = full.gy[grp];
+        gout = full.gout[grp];
+        gcol = col - full.gcol0[grp];
+    }
+    float4 v[kStackMaxRows];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        if (s0 + j < pieces) part[j] = __ldcg(reinterpret_cast<const float4*>(src + (s0 + j) * tile_floats));
-#pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        if (s0 + j < pieces) {
-                            v.x = __fadd_rn(v.x, part[j].x); v.y = __fadd_rn(v.y, part[j].y);
-                            v.z = __fadd_rn(v.z, part[j].z); v.w = __fadd_rn(v.w, part[j].w);
-                        }
+    for (int row = 0; row < kStackMaxRows; ++row) {
+        v[row] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (row < rows) {
+            bool any = false;
+#pragma unroll 1
+            for (int w = 0; w < kStackWarps; ++w) {
+                if (!((warp_mask >> w) & 1u)) continue;
+                const float4 t4 = *reinterpret_cast<const float4*>(
+                    reinterpret_cast<const float*>(smem_base + static_cast<size_t>(w) * a.warp_smem + a.stage_offset) +
+                    ((second_mask >> w) & 1u) * stage_floats + row * kQmvRedStride + lane * 4);
+                if (!any) { v[row] = t4; any = true; }
+                else {
+                    v[row].x = __fadd_rn(v[row].x, t4.x); v[row].y = __fadd_rn(v[row].y, t4.y);
+                    v[row].z = __fadd_rn(v[row].z, t4.z); v[row].w = __fadd_rn(v[row].w, t4.w);
                 }
             }
-            if (!complete) {
-                __stcg(reinterpret_cast<float4*>(piece_dst + row * 128 + lane * 4), v);
-                continue;
-            }
-            const int col = cblock * 128 + lane * 4;
-            if (o.tp_unit0 >= 0) v = tp_exchange_unit(a.tp, o.tp_unit0 + row * o.col_blocks + cblock, v, lane);
-            __half h[4] = {__float2half_rn(v.x), __float2half_rn(v.y), __float2half_rn(v.z), __float2half_rn(v.w)};
-            warp_hadamard128_f16(h, lane);
-            __align__(8) __half sv[4];
-            *reinterpret_cast<uint2*>(sv) = *reinterpret_cast<const uint2*>(o.svh + col);
-            const int grp = stack_group_of(o, cblock);
-            const int gcol = col - o.gcol0[grp];
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-                store_from_half(o.gy[grp], a.y_dtype, static_cast<int64_t>(row) * o.gout[grp] + gcol + j, __hmul_rn(h[j], sv[j]),
-                                o.bias ? o.bias + (col - gcol) : nullptr, gcol + j);
         }
     }
+    if (pieces > 1) {
+        // CTAs that share the block meet without a fence or an atomic: every partial sum travels in an 8-byte word
+        // together with this layer's tag (one store publishes it), and the block's first CTA polls the others' words.
+        unsigned long long* words = a.piece_words[op & 1] + (static_cast<int64_t>(cblock) * o.max_pieces + piece) * tile_floats + lane;
+        if (piece != 0) {
+#pragma unroll
+            for (int row = 0; row < kStackMaxRows; ++row)
+                if (row < rows) {
+                    const float f[4] = {v[row].x, v[row].y, v[row].z, v[row].w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) st_flagged(words + row * 128 + j * 32, __float_as_uint(f[j]), tag);   // word j of all lanes: one coalesced store
+                }
+            if (stamp) stamp[5] = global_ns();
+            return;
+        }
+        if (stamp) stamp[5] = global_ns();
+        unsigned long long t0 = 0;
+        bool lost = false;
+        constexpr int kBatch = 4;                                // pieces polled together: one memory round trip per batch
+#pragma unroll 1
+        for (int row = 0; row < rows; ++row) {
+#pragma unroll 1
+            for (int p0 = 1; p0 < pieces; p0 += kBatch) {
+                const unsigned long long* src = words + static_cast<int64_t>(p0) * tile_floats + row * 128;
+                unsigned long long w[kBatch][4];
+#pragma unroll 1
+                for (int i = 0;; ++i) {
+                    bool ok = true;
+#pragma unroll
+                    for (int b = 0; b < kBatch; ++b)
+                        if (p0 + b < pieces) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) w[b][j] = ld_flagged(src + static_cast<int64_t>(b) * tile_floats + j * 32);
+                        }
+#pragma unroll
+                    for (int b = 0; b < kBatch; ++b)
+                        if (p0 + b < pieces) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) ok = ok && static_cast<uint32_t>(w[b][j] >> 32) == tag;
+                        }
+                    if (__all_sync(0xffffffffu, ok)) break;
+                    if ((i & 63) == 63) {
+                        if (t0 == 0) t0 = global_ns();
+                        if (*reinterpret_cast<volatile unsigned int*>(a.error) != 0 || global_ns() - t0 > a.wait_ns) { lost = true; break; }
+                    }
+                }
+#pragma unroll
+                for (int b = 0; b < kBatch; ++b)
+                    if (p0 + b < pieces) {
+                        const float4 part = make_float4(__uint_as_float(static_cast<uint32_t>(w[b][0])), __uint_as_float(static_cast<uint32_t>(w[b][1])),
+                                                        __uint_as_float(static_cast<uint32_t>(w[b][2])), __uint_as_float(static_cast<uint32_t>(w[b][3])));
+#pragma unroll
+                        for (int r = 0; r < kStackMaxRows; ++r)
+                            if (r == row) {
+                                v[r].x = __fadd_rn(v[r].x, part.x); v[r].y = __fadd_rn(v[r].y, part.y);
+                                v[r].z = __fadd_rn(v[r].z, part.z); v[r].w = __fadd_rn(v[r].w, part.w);
+                            }
+                    }
+            }
+        }
+        if (lost && lane == 0) atomicCAS(a.error, 0u, 6u);
+    }
+    if (stamp) stamp[6] = global_ns();
+    const __half* sv = reinterpret_cast<const __half*>(&sv2);
+    const __half* bias = o.bias != nullptr ? reinterpret_cast<const __half*>(&bias2) : nullptr;
+#pragma unroll
+    for (int row = 0; row < kStackMaxRows; ++row)
+        if (row < rows) {
+            float4 s = v[row];
+            if (o.tp_unit0 >= 0) s = tp_exchange_unit(a.tp, o.tp_unit0 + row * o.col_blocks + cblock, s, lane);
+            __half h[4] = {__float2half_rn(s.x), __float2half_rn(s.y), __float2half_rn(s.z), __float2half_rn(s.w)};
+            warp_hadamard128_f16(h, lane);
+            if (a.y_dtype == kF16) {                            // one 8-byte store per lane
+                __align__(8) __half out[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    out[j] = __hmul_rn(h[j], sv[j]);
+                    if (bias) out[j] = __hadd_rn(out[j], bias[j]);
+                }
+                *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(y) + static_cast<int64_t>(row) * gout + gcol) =
+                    *reinterpret_cast<const uint2*>(out);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    store_from_half(y, a.y_dtype, static_cast<int64_t>(row) * gout + gcol + j, __hmul_rn(h[j], sv[j]), bias, j);
+            }
+        }
     // the block's outputs are stored: count it (release: the stores of every lane come before the count)
     __syncwarp();
     if (lane == 0) red_release_gpu_add(a.op_done + op, 1u);
+    if (stamp) stamp[7] = global_ns();
 }
 
 template <int K, int CB, int MODE>
-__global__ void __launch_bounds__(kQmvWarps * 32, 2)
+__global__ void __launch_bounds__(kStackWarps * 32, kStackCtasPerSm)
 stack_kernel(const StackArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    constexpr int WARPS = kQmvWarps;
+    constexpr int WARPS = kStackWarps;
     constexpr int DEPTH = stack_depth(K);
     constexpr int kRowWords = 64 * K;
     constexpr uint32_t kRowBytes = kRowWords * 4;
-    constexpr int kXsHalves = kQmvXBlocks * 128;
+    const int kXsHalves = a.x_blocks * 128;
     constexpr int NB = 1;
     __shared__ __align__(8) uint64_t s_bar[WARPS][DEPTH];
     __shared__ unsigned int s_arrived[WARPS + 2];
@@ -298,9 +390,17 @@ stack_kernel(const StackArgs a) {
     const int stage_floats = rows * kQmvRedStride;
     uint64_t* bars = s_bar[warp];
     const LaneGeom<K> geom(lane);
-    const bool tracing = a.trace != nullptr && threadIdx.x == 0;
-    if (tracing) a.trace[blockIdx.x * 4 + 0] = global_ns();
-
+    // the fields of every layer that the stream cursor and the main loop need, staged once
+    StackOpLite* lite = reinterpret_cast<StackOpLite*>(smem_raw + a.table_offset);
+    for (int i = threadIdx.x; i < a.n_ops; i += blockDim.x) {
+        const StackOp& o = a.ops[i];
+        StackOpLite l;
+        l.wq = o.wq; l.x = o.x; l.suh = o.suh;
+        l.tiles_k = o.tiles_k; l.tiles_n = o.tiles_n; l.col_blocks = o.col_blocks; l.warps = o.warps; l.narrow = o.narrow;
+        l.in = o.in; l.groups = o.groups; l.max_pieces = o.max_pieces; l.tp_unit0 = o.tp_unit0; l.gout0 = o.gout[0];
+        l.svh = o.svh; l.bias = o.bias; l.y0 = o.gy[0];
+        lite[i] = l;
+    }
     if (threadIdx.x < WARPS + 2) s_arrived[threadIdx.x] = 0;
     if (threadIdx.x == 0) { s_ready = 0; s_poller = 0; }
     if (lane == 0) {
@@ -312,16 +412,18 @@ stack_kernel(const StackArgs a) {
 
     // ---- start the weight stream: the first DEPTH rows of this warp, whatever layers they belong to ----------
     StackCursor<K> cur;
-    cur.seek(a.ops, a.n_ops, 0, wid);
+    cur.seek(lite, a.n_ops, 0, wid);
 #pragma unroll 1
     for (int i = 0; i < DEPTH && cur.valid; ++i) {
         if (lane == 0) {
             mbar_expect_tx(bars + i, kRowBytes);
             bulk_copy_g2s(ring + i * kRowWords, cur.src, kRowBytes, bars + i);
         }
-        cur.next(a.ops, a.n_ops, wid);
+        cur.next(lite, a.n_ops, wid);
     }
     pdl_wait();                                   // the step's inputs come from whatever ran before in the stream
+    // tags of this launch: the launch number (advanced by the last CTA to leave) and the layer
+    const uint32_t tag_base = *reinterpret_cast<volatile unsigned int*>(a.launch) * 4096u;
 
     int slot = 0;
     uint32_t parity = 0;
@@ -329,10 +431,12 @@ stack_kernel(const StackArgs a) {
 
 #pragma unroll 1
     for (int op = 0; op < a.n_ops; ++op) {
-        const StackOp& o = a.ops[op];
+        const StackOpLite& o = lite[op];
         const int UB = o.tiles_k * 8;
         const int T = UB * o.col_blocks;
         const bool narrow = o.narrow != 0;
+        const bool tracing = a.trace != nullptr && threadIdx.x == 0;
+        unsigned long long* stamp = a.trace == nullptr ? nullptr : a.trace + (static_cast<size_t>(op) * gridDim.x + blockIdx.x) * kStackTraceSlots;
         const int w0 = stack_unit_begin(T, o.warps, wid, narrow);
         const int w1 = stack_unit_begin(T, o.warps, wid + 1, narrow);
         if (w1 <= w0) continue;
@@ -341,12 +445,40 @@ stack_kernel(const StackArgs a) {
             break;
         }
         bool waited = false;
+        // unit ranges of the CTA's warps: lane w holds the begin of warp w (lane WARPS: the end of the last warp)
+        const int my_b = lane <= WARPS ? stack_unit_begin(T, o.warps, static_cast<int>(blockIdx.x) * WARPS + lane, narrow) : 0;
+        const int next_b = __shfl_down_sync(0xffffffffu, my_b, 1);
+        const int cta0 = __shfl_sync(0xffffffffu, my_b, 0);
+        const uint32_t tag = tag_base + static_cast<uint32_t>(op) + 1u;
+        auto arrive = [&](int cblock) {
+            const bool has = lane < WARPS && min(next_b, (cblock + 1) * UB) > max(my_b, cblock * UB);
+            const unsigned int mask = __ballot_sync(0xffffffffu, has);
+            const unsigned int second = __ballot_sync(0xffffffffu, has && my_b / UB != cblock);
+            unsigned int prev = 0;
+            if (lane == 0) {
+                __threadfence_block();                          // the staged tile before the arrival
+                prev = atomicAdd(&s_arrived[cblock - cta0 / UB], 1u);
+            }
+            prev = __shfl_sync(0xffffffffu, prev, 0);
+            if (prev + 1 == static_cast<unsigned int>(__popc(mask))) {
+                __threadfence_block();
+                if (lane == 0) s_arrived[cblock - cta0 / UB] = 0;         // the next layer's arrivals start from zero
+                const int Wop = o.warps;
+                const int i_first = narrow ? static_cast<int>(((static_cast<unsigned int>(cblock * UB + 1) * Wop - 1u) / T) / WARPS)
+                                           : static_cast<int>((((static_cast<int64_t>(cblock) * UB + 1) * Wop - 1) / T) / WARPS);
+                const int i_last = narrow ? static_cast<int>(((static_cast<unsigned int>((cblock + 1) * UB) * Wop - 1u) / T) / WARPS)
+                                          : static_cast<int>(((static_cast<int64_t>(cblock + 1) * UB * Wop - 1) / T) / WARPS);
+                stack_finish_block(a, o, op, cblock, mask, second, i_last - i_first + 1, static_cast<int>(blockIdx.x) - i_first, tag,
+                                   smem_raw, lane);
+            }
+            if (tracing) stamp[3] = global_ns();
+        };
 #pragma unroll 1
         for (int cblock = w0 / UB; cblock * UB < w1; ++cblock) {
             const int u0 = max(w0, cblock * UB) - cblock * UB;
             const int u1 = min(w1, (cblock + 1) * UB) - cblock * UB;
             float* stage = reinterpret_cast<float*>(mine + a.stage_offset) + (cblock - w0 / UB) * stage_floats;
-            const int grp = stack_group_of(o, cblock);
+            const int grp = o.groups > 1 ? stack_group_of(a.ops[op], cblock) : 0;
             {
                 const int tk_first = u0 >> 3, tk_last = (u1 - 1) >> 3;
                 const int lo_first = u0 & 7, hi_last = ((u1 - 1) & 7) + 1;
@@ -359,17 +491,22 @@ stack_kernel(const StackArgs a) {
 #pragma unroll 1
                 for (int tk0 = tk_first; tk0 <= tk_last;) {
                     const int kb0 = tk0 >> 3;
-                    const int tk_end = min(tk_last + 1, (kb0 + kQmvXBlocks) * 8);
+                    const int tk_end = min(tk_last + 1, (kb0 + a.x_blocks) * 8);
                     const int nrows = tk_end - tk0;
+                    const bool first_chunk = !waited;
+                    const int nblk = ((tk_end - 1) >> 3) - kb0 + 1;
+                    uint2 sv[kQmvXBlocks];
+                    stack_fetch_scales(o.suh + static_cast<int64_t>(grp) * o.in, kb0, nblk, lane, sv);
                     if (!waited) {
-                        stack_wait(a, op, &s_ready, &s_poller, lane);
+                        stack_wait(a, op, lite[op > 0 ? op - 1 : 0].col_blocks, &s_ready, &s_poller, lane);
                         waited = true;
+                        if (tracing) stamp[0] = global_ns();
                     }
-                    stack_rotate_chunk(o.x, a.x_dtype, o.suh + static_cast<int64_t>(grp) * o.in, o.in, rows, kb0,
-                                       ((tk_end - 1) >> 3) - kb0 + 1, xs, lane);
+                    stack_rotate_chunk(o.x, a.x_dtype, sv, o.in, rows, kb0, nblk, kXsHalves, xs, lane);
+                    if (tracing && first_chunk) stamp[1] = global_ns();
                     const uint32_t* xfrag =
                         reinterpret_cast<const uint32_t*>(xs + min(g, rows - 1) * kXsHalves + (tk0 * 16 - kb0 * 128)) + q;
-#pragma unroll 1
+#pragma unroll 1      // measured: unrolling this loop by 2 or 4 rows makes the step 8 % and 13 % slower
                     for (int r = 0; r < nrows; ++r) {
                         const int tk = tk0 + r;
                         uint32_t bx[NB][4];
@@ -392,12 +529,14 @@ stack_kernel(const StackArgs a) {
                                 mbar_expect_tx(bars + slot, kRowBytes);
                                 bulk_copy_g2s(ring + slot * kRowWords, cur.src, kRowBytes, bars + slot);
                             }
-                            cur.next(a.ops, a.n_ops, wid);
+                            cur.next(lite, a.n_ops, wid);
                         }
                         if (++slot == DEPTH) { slot = 0; parity ^= 1u; }
                     }
                     tk0 = tk_end;
                 }
+                if (tracing) stamp[2] = global_ns();
+                if (a.trace != nullptr && lane == 0) stamp[8 + warp] = global_ns();          // every warp: its tiles are done
 #pragma unroll
                 for (int t = 0; t < 8; ++t)
 #pragma unroll
@@ -406,37 +545,12 @@ stack_kernel(const StackArgs a) {
                         if (row < rows) stage[row * kQmvRedStride + col] = acc[t][0][i];
                     }
             }
-
-            // ---- the last warp of the CTA to arrive at this block adds the CTA's tiles and carries the block on ----
-            // unit ranges of the CTA's warps: lane w holds the begin of warp w (lane 8: the end of warp 7)
-            const int my_b = lane <= WARPS ? stack_unit_begin(T, o.warps, static_cast<int>(blockIdx.x) * WARPS + lane, narrow) : 0;
-            const int next_b = __shfl_down_sync(0xffffffffu, my_b, 1);
-            const bool has = lane < WARPS && min(next_b, (cblock + 1) * UB) > max(my_b, cblock * UB);
-            const unsigned int mask = __ballot_sync(0xffffffffu, has);
-            const unsigned int second = __ballot_sync(0xffffffffu, has && my_b / UB != cblock);
-            const int cta0 = __shfl_sync(0xffffffffu, my_b, 0);
-            unsigned int prev = 0;
-            if (lane == 0) {
-                __threadfence_block();                          // the staged tile before the arrival
-                prev = atomicAdd(&s_arrived[cblock - cta0 / UB], 1u);
-            }
-            prev = __shfl_sync(0xffffffffu, prev, 0);
-            if (prev + 1 == static_cast<unsigned int>(__popc(mask))) {
-                __threadfence_block();
-                if (lane == 0) s_arrived[cblock - cta0 / UB] = 0;         // the next layer's arrivals start from zero
-                const int Wop = o.warps;
-                const int i_first = narrow ? static_cast<int>(((static_cast<unsigned int>(cblock * UB + 1) * Wop - 1u) / T) / WARPS)
-                                           : static_cast<int>((((static_cast<int64_t>(cblock) * UB + 1) * Wop - 1) / T) / WARPS);
-                const int i_last = narrow ? static_cast<int>(((static_cast<unsigned int>((cblock + 1) * UB) * Wop - 1u) / T) / WARPS)
-                                          : static_cast<int>(((static_cast<int64_t>(cblock + 1) * UB * Wop - 1) / T) / WARPS);
-                stack_finish_block(a, o, op, cblock, mask, second, i_last - i_first + 1, static_cast<int>(blockIdx.x) - i_first,
-                                   smem_raw, lane);
-            }
+            // the last warp of the CTA to arrive at this block adds the CTA's tiles and carries the block on (measured:
+            // doing this only after all of the warp's tiles of the layer makes the step 4 % slower, not faster)
+            arrive(cblock);
         }
     }
     if (copy_lost && lane == 0) atomicCAS(a.error, 0u, 1u);
-    if (tracing) a.trace[blockIdx.x * 4 + 1] = global_ns();
-
     // ---- the last CTA to leave puts the step's counters back to zero ----------------------------------------
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -445,6 +559,7 @@ stack_kernel(const StackArgs a) {
         if (left == gridDim.x - 1) {
             for (int i = 0; i < a.n_ops; ++i) a.op_done[i] = 0;
             *a.exit_count = 0;
+            *a.launch = *a.launch + 1u;
             __threadfence();
         }
     }
@@ -455,13 +570,13 @@ cudaError_t stack_launch_one(const StackArgs& a, const StackPlan& plan, cudaStre
     auto kernel = stack_kernel<K, CB, MODE>;
     static PerDeviceOnce attribute;
     if (attribute.needed()) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kQmvMaxSmemBytes);
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kStackMaxSmemBytes);
         if (e != cudaSuccess) return e;
         attribute.mark();
     }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(static_cast<unsigned>(plan.grid));
-    cfg.blockDim = dim3(kQmvWarps * 32);
+    cfg.blockDim = dim3(kStackWarps * 32);
     cfg.dynamicSmemBytes = plan.smem_bytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];

@@ -26,7 +26,7 @@ class Exl3Stack:
     def __init__(self, ops, dtype: int, rows: int = 1):
         ops = list(ops)
         if not ops:
-            raise B200Exl3Error("a step needs between 1 and 4096 layers")
+            raise B200Exl3Error("a step needs between 1 and 256 layers")
         table = (_StackOp * len(ops))()
         self._keep = []
         for entry, op in zip(table, ops):
