@@ -263,6 +263,41 @@ int b200exl3_stack_reset(b200exl3_stack* handle);
 /* CTAs of the persistent grid and dynamic shared memory per CTA (for reports). */
 int b200exl3_stack_geometry(const b200exl3_stack* handle, int* out_grid, size_t* out_smem_bytes);
 
+/* ---- decoder-block glue: fp16, one token per call (batch-1 decode) ----------------------------------------------
+ * The operators a decoder block runs between its quantized projections (call order: native/src/lfm2.rs:704-793), as
+ * the reference reaches them through MLX (native/src/array.rs:1517-1519 rope, 1662-1664 rms_norm, 1741-1743 swiglu,
+ * 1766-1777 sdpa; native/ffi/mlx_bridge.cpp:678, 743, 745-750, 846-849).  All tensors are fp16 device arrays;
+ * positions and token ids live in device memory so that a recorded step can be replayed while they advance. */
+
+/* out[r, :] = table[tokens[r], :]  (ids are clamped to the table) */
+int b200exl3_embed(const uint16_t* d_table_f16, const int32_t* d_tokens, int64_t rows, int64_t vocab, int hidden,
+                   uint16_t* d_out_f16, b200exl3_stream stream);
+/* s = half(x + residual) (d_residual may be NULL; s is stored to d_sum when that is not NULL; d_sum may alias either
+ * input); y = weight * half(s * rsqrt(mean(s^2) + eps)), fp32 inside, as fast::rms_norm.  n <= 49152. */
+int b200exl3_rms_norm(const uint16_t* d_x_f16, const uint16_t* d_residual_f16, const uint16_t* d_weight_f16, int64_t rows,
+                      int n, float eps, uint16_t* d_sum_f16, uint16_t* d_y_f16, b200exl3_stream stream);
+/* out = half(half(gate * half(sigmoid(gate))) * up) */
+int b200exl3_swiglu(const uint16_t* d_gate_f16, const uint16_t* d_up_f16, int64_t n, uint16_t* d_out_f16, b200exl3_stream stream);
+/* Rotary embedding of the new token's heads at position *d_pos (pairs (i, i + head_dim/2), base theta): q [heads,
+ * head_dim] is rotated in place; the rotated k and v [kv_heads, head_dim] are written to row *d_pos of the caches
+ * [kv_heads, max_ctx, head_dim]. */
+int b200exl3_rope_append(uint16_t* d_q_f16, const uint16_t* d_k_f16, const uint16_t* d_v_f16, int heads, int kv_heads,
+                         int head_dim, const int32_t* d_pos, float theta, int max_ctx, uint16_t* d_k_cache_f16,
+                         uint16_t* d_v_cache_f16, b200exl3_stream stream);
+/* softmax(q k^T * scale) v for one query row per head against keys 0..*d_pos of the caches (grouped-query: heads /
+ * kv_heads query heads share a key head), fp32 inside, split over the context; head_dim must be 128. */
+int b200exl3_attention_workspace_bytes(int heads, int kv_heads, size_t* out_bytes);
+int b200exl3_attention_decode(const uint16_t* d_q_f16, const uint16_t* d_k_cache_f16, const uint16_t* d_v_cache_f16, int heads,
+                              int kv_heads, int head_dim, const int32_t* d_pos, int max_ctx, float scale, uint16_t* d_out_f16,
+                              void* d_workspace, size_t workspace_bytes, b200exl3_stream stream);
+/* fp16 vocabulary head: logits [vocab] = half(x [hidden] . weight [vocab, hidden]) (stored when d_logits is not NULL)
+ * and their arg-max (first index on ties) as (*d_best_value, *d_best_index + index_offset); a vocabulary shard passes
+ * its first row as index_offset. */
+int b200exl3_head_workspace_bytes(size_t* out_bytes);
+int b200exl3_head_argmax(const uint16_t* d_x_f16, const uint16_t* d_weight_f16, int64_t vocab, int hidden, int64_t index_offset,
+                         uint16_t* d_logits_f16, float* d_best_value, int64_t* d_best_index, void* d_workspace,
+                         size_t workspace_bytes, b200exl3_stream stream);
+
 /* ---- router: stable top-k ----------------------------------------------------------------------------------
  * Replaces router::topk / routes (native/src/router.rs:28-120, native/shaders/router_topk.h:1-34): values
  * [rows, experts] (fp16 = 9 or fp32 = 10, experts <= 1024) -> indices [rows, top_k] (u32) and scores

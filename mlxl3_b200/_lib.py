@@ -74,6 +74,14 @@ SIGNATURES = {
     "b200exl3_stack_status": (c_int, [c_void_p, POINTER(c_int)]),
     "b200exl3_stack_reset": (c_int, [c_void_p]),
     "b200exl3_stack_geometry": (c_int, [c_void_p, POINTER(c_int), POINTER(c_size_t)]),
+    "b200exl3_embed": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p]),
+    "b200exl3_rms_norm": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_float, c_void_p, c_void_p, c_void_p]),
+    "b200exl3_swiglu": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
+    "b200exl3_rope_append": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_float, c_int, c_void_p, c_void_p, c_void_p]),
+    "b200exl3_attention_workspace_bytes": (c_int, [c_int, c_int, POINTER(c_size_t)]),
+    "b200exl3_attention_decode": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_float, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "b200exl3_head_workspace_bytes": (c_int, [POINTER(c_size_t)]),
+    "b200exl3_head_argmax": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     "b200exl3_router_topk": (c_int, [c_void_p, c_int, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "b200exl3_router_softmax_topk": (c_int, [c_void_p, c_int, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "b200exl3_router_gate": (c_int, [c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p]),

@@ -1086,6 +1086,92 @@ int b200exl3_router_gate(const void* d_x, int x_dtype, const uint16_t* d_weight_
                                     reinterpret_cast<__half*>(d_logits_f16), as_stream(s)), "router gate kernel");
 }
 
+/* ---- decoder-block glue (fp16, batch-1 decode) ----------------------------------------------------------------- */
+
+int b200exl3_embed(const uint16_t* d_table, const int32_t* d_tokens, int64_t rows, int64_t vocab, int hidden, uint16_t* d_out,
+                   b200exl3_stream s) {
+    if (rows <= 0 || rows > INT32_MAX || vocab <= 0 || hidden <= 0 || hidden % 8) return fail("invalid embedding dimensions");
+    if (!d_table || !d_tokens || !d_out) return fail("NULL buffer");
+    if (!aligned16(d_table) || !aligned16(d_out)) return fail("device pointers must be 16-byte aligned");
+    return check(launch_embed(reinterpret_cast<const __half*>(d_table), d_tokens, rows, vocab, hidden, reinterpret_cast<__half*>(d_out),
+                              as_stream(s)), "embedding kernel");
+}
+
+int b200exl3_rms_norm(const uint16_t* d_x, const uint16_t* d_residual, const uint16_t* d_weight, int64_t rows, int n, float eps,
+                      uint16_t* d_sum, uint16_t* d_y, b200exl3_stream s) {
+    if (rows <= 0 || rows > INT32_MAX || n <= 0 || n % 2 || n > 48 * 1024) return fail("invalid RMSNorm dimensions");
+    if (!(eps >= 0.0f)) return fail("invalid RMSNorm epsilon");
+    if (!d_x || !d_weight || !d_y) return fail("NULL buffer");
+    return check(launch_rms_norm(reinterpret_cast<const __half*>(d_x), reinterpret_cast<const __half*>(d_residual),
+                                 reinterpret_cast<const __half*>(d_weight), rows, n, eps, reinterpret_cast<__half*>(d_sum),
+                                 reinterpret_cast<__half*>(d_y), as_stream(s)), "RMSNorm kernel");
+}
+
+int b200exl3_swiglu(const uint16_t* d_gate, const uint16_t* d_up, int64_t n, uint16_t* d_out, b200exl3_stream s) {
+    if (n <= 0 || n % 2) return fail("invalid SwiGLU length");
+    if (!d_gate || !d_up || !d_out) return fail("NULL buffer");
+    return check(launch_swiglu(reinterpret_cast<const __half*>(d_gate), reinterpret_cast<const __half*>(d_up), n,
+                               reinterpret_cast<__half*>(d_out), as_stream(s)), "SwiGLU kernel");
+}
+
+static int attention_shape(int heads, int kv_heads, int head_dim, int max_ctx) {
+    if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || max_ctx <= 0) return fail("invalid attention head counts");
+    if (head_dim != 128) return fail("decode attention is built for a head dimension of 128, got %d", head_dim);
+    return 0;
+}
+
+int b200exl3_rope_append(uint16_t* d_q, const uint16_t* d_k, const uint16_t* d_v, int heads, int kv_heads, int head_dim,
+                         const int32_t* d_pos, float theta, int max_ctx, uint16_t* d_k_cache, uint16_t* d_v_cache, b200exl3_stream s) {
+    if (attention_shape(heads, kv_heads, head_dim, max_ctx)) return -1;
+    if (!(theta > 1.0f)) return fail("invalid RoPE base");
+    if (!d_q || !d_k || !d_v || !d_pos || !d_k_cache || !d_v_cache) return fail("NULL buffer");
+    return check(launch_rope_append(reinterpret_cast<__half*>(d_q), reinterpret_cast<const __half*>(d_k), reinterpret_cast<const __half*>(d_v),
+                                    heads, kv_heads, head_dim, d_pos, theta, max_ctx, reinterpret_cast<__half*>(d_k_cache),
+                                    reinterpret_cast<__half*>(d_v_cache), as_stream(s)), "RoPE kernel");
+}
+
+int b200exl3_attention_workspace_bytes(int heads, int kv_heads, size_t* out_bytes) {
+    if (!out_bytes) return fail("NULL argument");
+    if (attention_shape(heads, kv_heads, 128, 1)) return -1;
+    *out_bytes = round256(attention_workspace_bytes(heads, kv_heads));
+    return 0;
+}
+
+int b200exl3_attention_decode(const uint16_t* d_q, const uint16_t* d_k_cache, const uint16_t* d_v_cache, int heads, int kv_heads,
+                              int head_dim, const int32_t* d_pos, int max_ctx, float scale, uint16_t* d_out, void* ws, size_t ws_bytes,
+                              b200exl3_stream s) {
+    if (attention_shape(heads, kv_heads, head_dim, max_ctx)) return -1;
+    if (!d_q || !d_k_cache || !d_v_cache || !d_pos || !d_out) return fail("NULL buffer");
+    if (!aligned16(d_q) || !aligned16(d_k_cache) || !aligned16(d_v_cache) || !aligned16(ws)) return fail("device pointers must be 16-byte aligned");
+    const size_t need = round256(attention_workspace_bytes(heads, kv_heads));
+    if (!ws || ws_bytes < need) return fail("workspace too small: %zu bytes given, %zu needed", ws_bytes, need);
+    return check(launch_attention_decode(reinterpret_cast<const __half*>(d_q), reinterpret_cast<const __half*>(d_k_cache),
+                                         reinterpret_cast<const __half*>(d_v_cache), heads, kv_heads, head_dim, d_pos, max_ctx, scale,
+                                         reinterpret_cast<__half*>(d_out), ws, as_stream(s)), "attention kernel");
+}
+
+int b200exl3_head_workspace_bytes(size_t* out_bytes) {
+    if (!out_bytes) return fail("NULL argument");
+    *out_bytes = round256(static_cast<size_t>(head_candidates()) * (sizeof(float) + sizeof(long long)));
+    return 0;
+}
+
+int b200exl3_head_argmax(const uint16_t* d_x, const uint16_t* d_weight, int64_t vocab, int hidden, int64_t index_offset,
+                         uint16_t* d_logits, float* d_best_value, int64_t* d_best_index, void* ws, size_t ws_bytes, b200exl3_stream s) {
+    if (vocab <= 0 || hidden <= 0 || hidden % 8 || hidden > 48 * 1024) return fail("invalid head dimensions");
+    if (!d_x || !d_weight || !d_best_value || !d_best_index) return fail("NULL buffer");
+    if (!aligned16(d_x) || !aligned16(d_weight) || !aligned16(ws)) return fail("device pointers must be 16-byte aligned");
+    size_t need = 0;
+    b200exl3_head_workspace_bytes(&need);
+    if (!ws || ws_bytes < need) return fail("workspace too small: %zu bytes given, %zu needed", ws_bytes, need);
+    const int n = head_candidates();
+    long long* cand_index = static_cast<long long*>(ws);
+    float* cand_value = reinterpret_cast<float*>(cand_index + n);
+    return check(launch_head_argmax(reinterpret_cast<const __half*>(d_x), reinterpret_cast<const __half*>(d_weight), vocab, hidden,
+                                    index_offset, reinterpret_cast<__half*>(d_logits), cand_value, cand_index, d_best_value,
+                                    reinterpret_cast<long long*>(d_best_index), as_stream(s)), "head kernel");
+}
+
 /* ---- tensor parallelism over peer memory ------------------------------------------------------------ */
 
 int b200exl3_tp_buffer_bytes(int world, int max_units, size_t* out_bytes) {

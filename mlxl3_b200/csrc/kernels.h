@@ -230,6 +230,25 @@ cudaError_t launch_router_topk(const void* values, int dtype, int64_t rows, int 
 cudaError_t launch_router_gate(const void* x, int x_dtype, const __half* w, int64_t rows, int in, int experts, __half* logits,
                                cudaStream_t stream);
 
+// ---- decoder-block glue, fp16, batch-1 decode (kernels_decoder.cu) -------------------------------------------------
+cudaError_t launch_embed(const __half* table, const int* token, int64_t rows, int64_t vocab, int hidden, __half* out, cudaStream_t stream);
+// s = half(x + residual) (residual and the stored sum are optional); y = weight * half(s * rsqrt(mean(s^2) + eps))
+cudaError_t launch_rms_norm(const __half* x, const __half* residual, const __half* weight, int64_t rows, int n, float eps, __half* sum,
+                            __half* y, cudaStream_t stream);
+cudaError_t launch_swiglu(const __half* gate, const __half* up, int64_t n, __half* out, cudaStream_t stream);
+// rotates q in place, writes the rotated k and v into row *pos of their heads' caches [kv_heads, max_ctx, dim]
+cudaError_t launch_rope_append(__half* q, const __half* k, const __half* v, int heads, int kv_heads, int dim, const int* pos, float theta,
+                               int max_ctx, __half* k_cache, __half* v_cache, cudaStream_t stream);
+int attention_splits(int kv_heads, int heads);
+size_t attention_workspace_bytes(int heads, int kv_heads);
+// one query row against keys 0..*pos of the cache; dim must be 128
+cudaError_t launch_attention_decode(const __half* q, const __half* k_cache, const __half* v_cache, int heads, int kv_heads, int dim,
+                                    const int* pos, int max_ctx, float scale, __half* out, void* workspace, cudaStream_t stream);
+int head_candidates();
+// logits (optional) and the arg-max (value, index + index_offset) of x [hidden] times w [vocab, hidden]^T
+cudaError_t launch_head_argmax(const __half* x, const __half* w, int64_t vocab, int hidden, int64_t index_offset, __half* logits,
+                               float* cand_value, long long* cand_index, float* out_value, long long* out_index, cudaStream_t stream);
+
 // ---- tensor-core product for many rows (kernels_qmm.cu) ---------------------------------------------------
 struct QmmPlan {
     int splits;        // CTAs that share one (128 columns x token tile) output tile along the input axis

@@ -1,0 +1,173 @@
+"""GPU parity of the decoder-block glue (RMSNorm, RoPE + cache append, grouped-query decode attention, SwiGLU, fp16 head
+with arg-max) and of a small dense decoder built from it, against the CPU restatement in oracle/decoder.py.
+
+These operators are floating point with fp32 inside and fp16 at their outputs; the reference computes them through MLX,
+whose last-bit behaviour no stored output pins.  Stated bars: element-wise operators within 2 units in the last place of
+fp16 (exp, sin and cos differ in their last fp32 bits between libraries); attention and the head within 2e-3 of the
+row's largest magnitude; a whole decode step (two layers) within 3e-2 of the largest magnitude of the hidden state and
+of the logits, with an arg-max whose oracle logit is within that bar of the oracle's maximum.
+"""
+import numpy as np
+import pytest
+
+import oracle
+from oracle import decoder as od
+from tests.gpu_util import bits, gpu  # noqa: F401
+
+pytestmark = pytest.mark.gpu
+
+
+def ulps(a, b):
+    """Distance in fp16 units in the last place (on the ordered integer line)."""
+    def key(x):
+        u = np.ascontiguousarray(x, np.float16).view(np.uint16).astype(np.int32)
+        return np.where(u & 0x8000, -(u & 0x7FFF), u)
+    return np.abs(key(a) - key(b))
+
+
+def test_rms_norm_swiglu_rope(gpu):
+    from mlxl3_b200 import decoder as dec
+    from mlxl3_b200.runtime import DeviceBuffer
+    rng = np.random.default_rng(1)
+    n = 4096
+    x = rng.standard_normal((3, n)).astype(np.float16)
+    r = (rng.standard_normal((3, n)) * 0.5).astype(np.float16)
+    w = (1 + 0.1 * rng.standard_normal(n)).astype(np.float16)
+    d_x, d_r, d_w = DeviceBuffer.from_numpy(x), DeviceBuffer.from_numpy(r), DeviceBuffer.from_numpy(w)
+    d_s, d_y = DeviceBuffer(x.nbytes), DeviceBuffer(x.nbytes)
+    for residual in (None, r):
+        dec.rms_norm(d_x.ptr, d_r.ptr if residual is not None else 0, d_w.ptr, 3, n, 1e-5, d_s.ptr, d_y.ptr)
+        want_y, want_s = od.rms_norm(x, w, 1e-5, residual)
+        assert np.array_equal(bits(d_s.download((3, n), np.float16)), bits(want_s))
+        assert ulps(d_y.download((3, n), np.float16), want_y).max() <= 1
+    # in place on the residual stream: sum written over x
+    d_h = DeviceBuffer.from_numpy(x)
+    dec.rms_norm(d_h.ptr, d_r.ptr, d_w.ptr, 3, n, 1e-5, d_h.ptr, d_y.ptr)
+    assert np.array_equal(bits(d_h.download((3, n), np.float16)), bits(od.rms_norm(x, w, 1e-5, r)[1]))
+    # SwiGLU
+    g, u = (rng.standard_normal(14336) * 2).astype(np.float16), rng.standard_normal(14336).astype(np.float16)
+    d_g, d_u, d_o = DeviceBuffer.from_numpy(g), DeviceBuffer.from_numpy(u), DeviceBuffer(g.nbytes)
+    dec.swiglu(d_g.ptr, d_u.ptr, g.size, d_o.ptr)
+    assert ulps(d_o.download(g.shape, np.float16), od.swiglu(g, u)).max() <= 2
+    # RoPE + append
+    heads, kv_heads, dim, ctx, pos, theta = 8, 2, 128, 64, 37, 500000.0
+    q = rng.standard_normal((heads, dim)).astype(np.float16)
+    k, v = rng.standard_normal((kv_heads, dim)).astype(np.float16), rng.standard_normal((kv_heads, dim)).astype(np.float16)
+    d_q, d_k, d_v = DeviceBuffer.from_numpy(q), DeviceBuffer.from_numpy(k), DeviceBuffer.from_numpy(v)
+    d_kc, d_vc = DeviceBuffer(kv_heads * ctx * dim * 2), DeviceBuffer(kv_heads * ctx * dim * 2)
+    d_kc.fill(0), d_vc.fill(0)
+    d_pos = DeviceBuffer.from_numpy(np.array([pos], np.int32))
+    dec.rope_append(d_q.ptr, d_k.ptr, d_v.ptr, heads, kv_heads, dim, d_pos.ptr, theta, ctx, d_kc.ptr, d_vc.ptr)
+    got_q = d_q.download((heads, dim), np.float16).astype(np.float32)
+    assert np.abs(got_q - od.rope(q, pos, theta).astype(np.float32)).max() <= 4e-3
+    kc, vc = d_kc.download((kv_heads, ctx, dim), np.float16), d_vc.download((kv_heads, ctx, dim), np.float16)
+    assert np.abs(kc[:, pos].astype(np.float32) - od.rope(k, pos, theta).astype(np.float32)).max() <= 4e-3
+    assert np.array_equal(bits(vc[:, pos]), bits(v))
+    assert not kc[:, :pos].any() and not kc[:, pos + 1:].any()           # only row `pos` is written
+    with pytest.raises(gpu.B200Exl3Error, match="head dimension of 128"):
+        dec.rope_append(d_q.ptr, d_k.ptr, d_v.ptr, heads, kv_heads, 64, d_pos.ptr, theta, ctx, d_kc.ptr, d_vc.ptr)
+
+
+@pytest.mark.parametrize("heads,kv_heads,keys,ctx", [(32, 8, 2048, 2048), (4, 4, 1, 16), (16, 2, 77, 128), (64, 8, 300, 512), (4, 1, 4096, 4096)])
+def test_attention_decode(gpu, heads, kv_heads, keys, ctx):
+    from mlxl3_b200 import decoder as dec
+    from mlxl3_b200.runtime import DeviceBuffer
+    rng = np.random.default_rng(heads + keys)
+    dim = 128
+    q = rng.standard_normal((heads, dim)).astype(np.float16)
+    kc = np.zeros((kv_heads, ctx, dim), np.float16)
+    vc = np.zeros((kv_heads, ctx, dim), np.float16)
+    kc[:, :keys] = rng.standard_normal((kv_heads, keys, dim)).astype(np.float16)
+    vc[:, :keys] = rng.standard_normal((kv_heads, keys, dim)).astype(np.float16)
+    kc[:, keys:], vc[:, keys:] = 100.0, 100.0                         # rows past the position must not be read
+    d_q, d_k, d_v = DeviceBuffer.from_numpy(q), DeviceBuffer.from_numpy(kc), DeviceBuffer.from_numpy(vc)
+    d_o = DeviceBuffer(q.nbytes)
+    d_pos = DeviceBuffer.from_numpy(np.array([keys - 1], np.int32))
+    ws = DeviceBuffer(dec.attention_workspace_bytes(heads, kv_heads))
+    dec.attention_decode(d_q.ptr, d_k.ptr, d_v.ptr, heads, kv_heads, dim, d_pos.ptr, ctx, dim ** -0.5, d_o.ptr, ws)
+    got = d_o.download((heads, dim), np.float16)
+    want = od.attention_decode(q, kc[:, :keys], vc[:, :keys], dim ** -0.5)
+    assert np.isfinite(got.astype(np.float32)).all()
+    assert np.abs(got.astype(np.float32) - want.astype(np.float32)).max() <= 2e-3 * max(1.0, np.abs(want.astype(np.float32)).max())
+    dec.attention_decode(d_q.ptr, d_k.ptr, d_v.ptr, heads, kv_heads, dim, d_pos.ptr, ctx, dim ** -0.5, d_o.ptr, ws)
+    assert np.array_equal(bits(got), bits(d_o.download((heads, dim), np.float16)))         # fixed merge order
+
+
+def test_head_argmax(gpu):
+    from mlxl3_b200 import decoder as dec
+    from mlxl3_b200.runtime import DeviceBuffer
+    rng = np.random.default_rng(9)
+    vocab, hidden = 16032, 4096
+    x = rng.standard_normal(hidden).astype(np.float16)
+    w = (rng.standard_normal((vocab, hidden)) / 64).astype(np.float16)
+    w[5000] = w[123]                                                  # an exact tie: the first index wins
+    d_x, d_w, d_l = DeviceBuffer.from_numpy(x), DeviceBuffer.from_numpy(w), DeviceBuffer(vocab * 2)
+    d_bv, d_bi = DeviceBuffer(16), DeviceBuffer(16)
+    ws = DeviceBuffer(dec.head_workspace_bytes())
+    dec.head_argmax(d_x.ptr, d_w.ptr, vocab, hidden, 1000, d_l.ptr, d_bv.ptr, d_bi.ptr, ws)
+    logits = d_l.download((vocab,), np.float16)
+    want, _ = od.head_argmax(x, w)
+    assert np.abs(logits.astype(np.float32) - want.astype(np.float32)).max() <= 2e-3 * np.abs(want.astype(np.float32)).max()
+    assert np.array_equal(bits(logits[5000:5001]), bits(logits[123:124]))
+    best = int(d_bi.download((1,), np.int64)[0]) - 1000
+    assert best == int(np.argmax(logits)) and float(d_bv.download((1,), np.float32)[0]) == float(logits[best])
+    # without storing the logits
+    dec.head_argmax(d_x.ptr, d_w.ptr, vocab, hidden, 0, 0, d_bv.ptr, d_bi.ptr, ws)
+    assert int(d_bi.download((1,), np.int64)[0]) == best
+
+
+def _small():
+    from mlxl3_b200.decoder import DecoderConfig, SyntheticWeights
+    config = DecoderConfig(layers=2, hidden=512, heads=4, kv_heads=2, head_dim=128, ffn=1024, vocab=1024, k_bits=4, codebook=0, max_ctx=32)
+    return config, SyntheticWeights(config, seed=11)
+
+
+def _oracle_model(config, weights):
+    def linear(p, x):
+        return oracle.linear_forward(p[0], config.k_bits, config.codebook, p[1], p[2], None, np.ascontiguousarray(x, np.float16).reshape(1, -1))
+    layers = []
+    for l in range(config.layers):
+        layer = {n: weights.projection(l, n) for n in weights.NAMES}
+        layer["attn_norm"], layer["mlp_norm"] = weights.norm(l, 0), weights.norm(l, 1)
+        layers.append(layer)
+    model = {"embed": weights.embed(), "head": weights.head(), "final_norm": weights.norm(config.layers, 0), "theta": config.theta,
+             "eps": config.eps, "heads": config.heads, "kv_heads": config.kv_heads, "head_dim": config.head_dim, "layers": layers}
+    return model, linear
+
+
+def test_small_decoder_steps_match_oracle(gpu):
+    from mlxl3_b200.decoder import DenseDecoder
+    config, weights = _small()
+    model, linear = _oracle_model(config, weights)
+    dec = DenseDecoder(config, weights)
+    dec.store_logits = True
+    kc = [np.zeros((config.kv_heads, config.max_ctx, config.head_dim), np.float16) for _ in range(config.layers)]
+    vc = [np.zeros((config.kv_heads, config.max_ctx, config.head_dim), np.float16) for _ in range(config.layers)]
+    for e in dec.layers:
+        e["k_cache"].fill(0, dec.stream), e["v_cache"].fill(0, dec.stream)
+    tokens = [3, 700, 41, 1023, 5]
+    eager = []
+    for pos, token in enumerate(tokens):
+        dec.set_input(token, pos)
+        dec.step()
+        value, index = dec.result()
+        logits, hidden = dec.download("logits"), dec.download("h")
+        want_logits, want_best, want_h = od.dense_decoder_step(model, token, pos, kc, vc, linear)
+        bar_h = 3e-2 * np.abs(want_h.astype(np.float32)).max()
+        bar_l = 3e-2 * np.abs(want_logits.astype(np.float32)).max()
+        assert np.abs(hidden.astype(np.float32) - want_h.astype(np.float32).ravel()).max() <= bar_h
+        assert np.abs(logits.astype(np.float32) - want_logits.astype(np.float32)).max() <= bar_l
+        assert index == int(np.argmax(logits)) and value == float(logits[index])
+        assert float(want_logits[want_best]) - float(want_logits[index]) <= bar_l
+        eager.append((bits(logits).copy(), index))
+    # the same five steps replayed from a recorded graph give the same bits
+    for e in dec.layers:
+        e["k_cache"].fill(0, dec.stream), e["v_cache"].fill(0, dec.stream)
+    dec.set_input(tokens[0], 0)
+    dec.record()
+    for pos, token in enumerate(tokens):
+        dec.set_input(token, pos)
+        dec.step()
+        _, index = dec.result()
+        assert index == eager[pos][1] and np.array_equal(bits(dec.download("logits")), eager[pos][0])
+    assert gpu.workspace_status(dec.ws) == 0
