@@ -21,6 +21,11 @@ the total work is fixed (strong scaling).  The sum over ranks and the output rot
 projection happen inside the projection's own kernel, over peer memory (NVLink), so a step stays a single
 graph replay of 128 launches on every rank.
 
+The same run also measures the whole model the projections belong to (key ``decode`` of the JSON line): one decode
+step of the Llama-3-8B-shaped decoder at a 2048-token fp16 KV context -- embedding, 32 blocks of RMSNorm, [q|k|v],
+RoPE, grouped-query attention, o, RMSNorm, [gate|up], SwiGLU, down, then the final norm, the fp16 head and its
+arg-max: 4.82 GB read per token.
+
 ``--impl reference`` times the CPU oracle (the C restatement of the reference's arithmetic) on the
 host cores, on a bounded sample of the same workload.
 """
@@ -40,6 +45,7 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 HIDDEN, FFN, KV, LAYERS, K_BITS, CB = 4096, 14336, 1024, 32, 4, 0
+VOCAB, CONTEXT = 128256, 2048
 # launch unit: (member names, in, member outs, tensor-parallel kind).  q/k/v and gate/up read the same
 # input and run as one Exl3Group launch each, as the reference's ProjectionBundle fuses them
 # (native/src/qwen35.rs:63-96 of the reference).
@@ -113,37 +119,6 @@ def shard(kind: str, n_in: int, n_out: int, world: int) -> tuple[int, int]:
     return tp.shard_dims(kind, n_in, n_out, world)
 
 
-def layer_arrays(layer: int, j: int, m: int, rank: int, world: int, kind: str, n_in: int, n_out: int):
-    """Seeded synthetic tensors of rank `rank`'s shard of one projection: uniform random trellis words (any bit string
-    is a valid tile; the full layer is the ranks' shards side by side), +-1 input signs, and output scales +-c with
-    c = 1 / (1.2437 * sqrt(in)) (1.2437 = standard deviation of the default codebook's values), so that activations
-    chained through 128 projections keep a magnitude of about one.  The sign vectors are slices of full-width
-    vectors that do not depend on the rank."""
-    s_in, s_out = shard(kind, n_in, n_out, world)
-    trellis = np.random.default_rng([1001, layer, j, m, rank]).integers(0, 65536, (s_in // 16, s_out // 16, 16 * K_BITS), dtype=np.uint16)
-    rng = np.random.default_rng([1002, layer, j, m])
-    suh = np.where(rng.random(n_in) > 0.5, -1, 1).astype(np.float16)
-    scale = np.float16(1.0 / (1.2437 * np.sqrt(n_in)))
-    svh = (np.where(rng.random(n_out) > 0.5, -1, 1).astype(np.float16) * scale).astype(np.float16)
-    if world > 1 and kind == "row":
-        suh = np.ascontiguousarray(suh[rank * s_in:(rank + 1) * s_in])
-    if world > 1 and kind == "col":
-        svh = np.ascontiguousarray(svh[rank * s_out:(rank + 1) * s_out])
-    return trellis, suh, svh
-
-
-def full_layer_arrays(layer: int, j: int, m: int, world: int, kind: str, n_in: int, n_out: int):
-    """The unsharded projection the ranks' shards make up (for the CPU check)."""
-    parts = [layer_arrays(layer, j, m, r, world, kind, n_in, n_out) for r in range(world)]
-    if world == 1:
-        return parts[0]
-    axis = 0 if kind == "row" else 1
-    trellis = np.concatenate([p[0] for p in parts], axis=axis)
-    suh = np.concatenate([p[1] for p in parts]) if kind == "row" else parts[0][1]
-    svh = np.concatenate([p[2] for p in parts]) if kind == "col" else parts[0][2]
-    return trellis, suh, svh
-
-
 def close_enough(got: np.ndarray, want: np.ndarray, rel: float = 1e-2) -> bool:
     g, w = got.astype(np.float32), want.astype(np.float32)
     return bool(np.isfinite(g).all() and np.abs(g - w).max() <= rel * np.abs(w).max())
@@ -165,25 +140,35 @@ def run_ours(args) -> dict:
     ex.init(local_rank)
     rows = 1
 
-    # ---- build the sharded projections, each with its own seeded weights -------------------------
+    # ---- the model: a Llama-3-8B-shaped dense decoder with seeded synthetic weights, this rank's shard of it ----------
+    from mlxl3_b200.decoder import DecoderConfig, DenseDecoder, SyntheticWeights
+    config = DecoderConfig(layers=LAYERS, hidden=HIDDEN, heads=32, kv_heads=8, head_dim=128, ffn=FFN, vocab=VOCAB, k_bits=K_BITS,
+                           codebook=CB, theta=500000.0, eps=1e-5, max_ctx=CONTEXT)
+    weights = SyntheticWeights(config, seed=1001)
+    stream = Stream()
+    tp_ctx = None
+    if world > 1:
+        # row-parallel layers exchange their fp32 partial sums through peer memory inside the kernel;
+        # torch.distributed only carries the IPC handles, the barriers and the timing
+        from mlxl3_b200.tp import TpContext
+
+        def exchange(raw: bytes) -> list:
+            gathered = [None] * world
+            dist.all_gather_object(gathered, raw)
+            return gathered
+        tp_ctx = TpContext(rank, world, rows * HIDDEN // 128, exchange)
+    model = DenseDecoder(config, weights, rank, world, tp_ctx, stream)
+
+    # ---- workload of the headline metric: the model's 224 quantized projections as 128 launches ----------------------
     # The activations are chained as in a decoder: [q|k|v] reads the hidden row, o reads q's output (standing in for
     # the attention output), [gate|up] reads o's output, down reads gate's output, the next layer reads down's output.
     # Every projection therefore depends on the one before it.
     layers = []            # (kind, in, [outs], operator)
     total_bytes = 0
-    for layer in range(LAYERS):
-        for j, (names, n_in, n_outs, kind) in enumerate(LAUNCHES):
-            members = []
-            for m, n_out in enumerate(n_outs):
-                members.append(ex.Exl3Linear(*layer_arrays(layer, j, m, rank, world, kind, n_in, n_out), None, K_BITS, CB))
-                total_bytes += algorithmic_bytes(n_in, n_out, K_BITS, rows)   # whole-job bytes, counted once
-            if len(members) > 1:
-                op = ex.Exl3Group(members)
-                for m in members:
-                    m.close()
-            else:
-                op = members[0]
-            layers.append((kind, shard(kind, n_in, n_outs[0], world)[0], [shard(kind, n_in, o, world)[1] for o in n_outs], op))
+    for entry in model.layers:
+        for (names, n_in, n_outs, kind), key in zip(LAUNCHES, ("qkv", "o", "gu", "down")):
+            total_bytes += sum(algorithmic_bytes(n_in, o, K_BITS, rows) for o in n_outs)      # whole-job bytes, counted once
+            layers.append((kind, shard(kind, n_in, n_outs[0], world)[0], [shard(kind, n_in, o, world)[1] for o in n_outs], entry[key]))
     x_host = PinnedBuffer((rows, HIDDEN), np.float16)
     x_host.array[...] = np.random.default_rng(4242).standard_normal((rows, HIDDEN)).astype(np.float16)
     d_in = DeviceBuffer.from_numpy(x_host.array)
@@ -205,21 +190,8 @@ def run_ours(args) -> dict:
     y_host = PinnedBuffer((rows, layers[-1][2][0]), np.float16)
     ws = ex.new_workspace(max(l[3].workspace_bytes(rows) for l in layers))
 
-    stream = Stream()
-    tp_ctx = None
     if world > 1:
-        # row-parallel layers exchange their fp32 partial sums through peer memory inside the kernel;
-        # torch.distributed only carries the IPC handles, the barriers and the timing
-        from mlxl3_b200.tp import TpContext
-
-        def exchange(raw: bytes) -> list:
-            gathered = [None] * world
-            dist.all_gather_object(gathered, raw)
-            return gathered
-        widths = {o for l in layers if l[0] == "row" for o in l[2]}
-        tp_ctx = TpContext(rank, world, rows * max(widths) // 128, exchange)
-        yhat = {n: DeviceBuffer(rows * n * 4) for n in widths}
-
+        yhat = {HIDDEN: DeviceBuffer(rows * HIDDEN * 4)}
     from ctypes import c_void_p
     from mlxl3_b200 import _lib
 
@@ -338,7 +310,7 @@ def run_ours(args) -> dict:
         source = everyone[0]["in"]
         for index, (names, n_in, n_outs, kind) in enumerate(LAUNCHES):
             for m, n_out in enumerate(n_outs):
-                trellis, suh, svh = full_layer_arrays(0, index, m, world, kind, n_in, n_out)
+                trellis, suh, svh = weights.projection(0, names[m])
                 want = oracle.linear_forward(trellis, K_BITS, CB, suh, svh, None, source)
                 checked["cases"] += 1
                 if not close_enough(whole(index, m), want):
@@ -352,7 +324,7 @@ def run_ours(args) -> dict:
             total = everyone[0]["o_partial"].copy()
             for r in range(1, world):
                 total = total + everyone[r]["o_partial"]                       # fp32, rank order
-            _, _, svh_o = full_layer_arrays(0, 1, 0, world, "row", HIDDEN, HIDDEN)
+            _, _, svh_o = weights.projection(0, "o")
             want_bits = oracle.finish(total, svh_o, None).view(np.uint16)
             for r in range(world):
                 if not np.array_equal(everyone[r]["o_fused"].view(np.uint16), want_bits):
@@ -376,6 +348,74 @@ def run_ours(args) -> dict:
     clocks = sampler.stop() if sampler else None
     ms_e2e = timed(host_io=True)
 
+    # ---- the whole model: one decode step at a 2048-token context (embedding, 32 decoder blocks, final norm, fp16 head,
+    #      arg-max), recorded once and replayed; the token id and the position are uploaded and the arg-max read back in
+    #      the end-to-end loop ----------------------------------------------------------------------------------------
+    decode = None
+    if not args.no_decode:
+        model.fill_cache(CONTEXT - 1, seed=7)
+        token_rng = np.random.default_rng(99)
+        model.set_input(int(token_rng.integers(0, VOCAB)), CONTEXT - 1)
+        model.record()
+        barrier()
+        model.step()
+        barrier()
+        # check on the last block's attention (its query, caches and output are still in place) against the CPU oracle
+        from oracle import decoder as oracle_decoder
+        last_block = model.layers[-1]
+        q_rot = model.download("q").reshape(model.heads, 128)
+        k_cache = last_block["k_cache"].download((model.kv_heads, CONTEXT, 128), np.float16, stream)
+        v_cache = last_block["v_cache"].download((model.kv_heads, CONTEXT, 128), np.float16, stream)
+        want_att = oracle_decoder.attention_decode(q_rot, k_cache, v_cache, 128 ** -0.5)
+        got_att = model.download("att").reshape(model.heads, 128)
+        att_ok = close_enough(got_att, want_att, rel=2e-3)
+        best_value, best_index = model.result()
+        decode_ok = att_ok and np.isfinite(best_value) and 0 <= best_index < VOCAB
+        if dist is not None:
+            flags = [None] * world
+            dist.all_gather_object(flags, bool(decode_ok))
+            decode_ok = all(flags)
+        if not decode_ok:
+            raise SystemExit(f"rank {rank}: the decode step failed its check (attention parity {att_ok}, arg-max {best_index})")
+
+        def decode_step(host_io: bool) -> None:
+            if host_io:
+                model.set_input(int(token_rng.integers(0, VOCAB)), CONTEXT - 1)
+            model.step()
+            if host_io:
+                mine_best = model.result()                           # 12 bytes device -> host, synchronises
+                if dist is not None:                                 # vocabulary shards: the largest logit wins
+                    everyone_best = [None] * world
+                    dist.all_gather_object(everyone_best, mine_best)
+
+        def decode_timed(host_io: bool) -> float:
+            for _ in range(args.warmup):
+                decode_step(host_io)
+            barrier()
+            start, stop = Event(), Event()
+            start.record(stream)
+            for _ in range(args.steps):
+                decode_step(host_io)
+            stop.record(stream)
+            ms = start.elapsed_ms(stop)
+            barrier()
+            if dist is not None:
+                import torch
+                t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms = float(t.item())
+            return ms / args.steps
+        ms_token = decode_timed(False)
+        ms_token_e2e = decode_timed(True)
+        token_bytes = config.bytes_per_token(CONTEXT)
+        decode = {"tok_s": round(1e3 / ms_token, 1), "ms_per_token": round(ms_token, 4), "e2e_tok_s": round(1e3 / ms_token_e2e, 1),
+                  "context": CONTEXT, "bytes_per_token": token_bytes, "hbm_gbs_per_gpu": round(token_bytes / world / ms_token / 1e6, 1),
+                  "frac_of_hbm_peak": round(token_bytes / world / ms_token / 1e6 / measured_peak_gbs()[0], 4),
+                  "launches_per_token": model.launches_per_step, "h2d_bytes_per_token": 8, "d2h_bytes_per_token": 12,
+                  "checked": {"last_block_attention_vs_oracle": bool(att_ok)},
+                  "what": "embedding, 32 x (RMSNorm, [q|k|v], RoPE + cache append, grouped-query attention over 2048 fp16 keys, o, "
+                          "RMSNorm, [gate|up], SwiGLU, down), final norm, fp16 head 128256 x 4096, arg-max; one graph replay per token"}
+
     # launches per step: one persistent kernel, or one fused kernel per projection (plus the exchange kernels when unfused)
     launches_per_step = len(layers) + (sum(1 for l in layers if l[0] == "row") if world > 1 and args.unfused_exchange else 0)
     if stack is not None:
@@ -394,6 +434,7 @@ def run_ours(args) -> dict:
                    "parallelism": f"tp{world}", "mode": args.mode, "graph_replay": graph is not None and stack is None,
                    "pdl": bool(args.pdl), "dataflow": "chained: every projection reads the output of the one before it"},
         "linear_stack_tok_s": round(1e3 / ms_per_step, 1),
+        "decode": decode,
         "checked": checked,
         "roofline": {"bound": "hbm", "achieved": round(per_gpu, 2), "peak": peak, "unit": "GB/s",
                      "frac": round(per_gpu / peak, 4),
@@ -480,6 +521,7 @@ def main() -> None:
                     help="N > 1: run the sum over ranks as its own kernel after the product instead of inside it")
     ap.add_argument("--mode", default="stack", choices=["stack", "graph"],
                     help="stack: the whole step is one persistent kernel; graph: one fused kernel per layer, replayed as a CUDA graph")
+    ap.add_argument("--no-decode", action="store_true", help="skip the whole-model decode measurement")
     ap.add_argument("--pdl", type=int, default=1, help="programmatic dependent launch between layers (0/1)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
