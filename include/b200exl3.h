@@ -263,6 +263,31 @@ int b200exl3_stack_reset(b200exl3_stack* handle);
 /* CTAs of the persistent grid and dynamic shared memory per CTA (for reports). */
 int b200exl3_stack_geometry(const b200exl3_stack* handle, int* out_grid, size_t* out_smem_bytes);
 
+/* ---- expert parallelism for Exl3SwitchGlu -----------------------------------------------------------------------
+ * No counterpart in the reference (it runs every expert on one device, native/src/moe.rs:905-971); the arithmetic of
+ * a slot and of the final sum is the reference's (moe.rs:184-236 routed rotation, 586-609 finish_and_reduce), only
+ * where a slot is computed changes.  Rank r owns experts [first_expert, first_expert + E_local): its b200exl3_moe
+ * handle is created from that range's banks.  Every rank passes the same token rows, routes (GLOBAL expert ids) and
+ * scores and receives the same output.  One call = plan (local slots, in slot order) -> dispatch (routed rotation of
+ * those slots) -> local expert products and SwiGLU glue -> combine: owners publish their slots' rotated, scaled fp16
+ * results into every rank's inbox over peer memory as {two values, sequence number} words, and every rank adds its
+ * rows' top-k slot results in slot order.  No library collective, no separate exchange launch beyond these kernels.
+ * Set-up mirrors the tensor-parallel context: every rank allocates an inbox of b200exl3_ep_buffer_bytes with
+ * b200exl3_ipc_alloc, the host exchanges the 64-byte handles, opens the peers' inboxes with b200exl3_tp_open and passes
+ * all `world` pointers (its own at index rank) to b200exl3_ep_create.  max_slots bounds rows * top_k of one pass (a
+ * call with more rows runs in passes of b200exl3_moe's chunk).  Waits are bounded by the "tp_wait_ms" option; a wait
+ * that gives up sets status 7 (b200exl3_ep_status). */
+typedef struct b200exl3_ep b200exl3_ep;
+int b200exl3_ipc_alloc(size_t bytes, void** out_buffer, unsigned char* out_handle64);
+int b200exl3_ep_buffer_bytes(int max_slots, int out, size_t* out_bytes);
+int b200exl3_ep_create(int rank, int world, int max_slots, int out, void* const* buffers, b200exl3_ep** out_handle);
+void b200exl3_ep_free(b200exl3_ep* handle);
+int b200exl3_ep_status(const b200exl3_ep* handle, int* out_status);
+int b200exl3_moe_ep_workspace_bytes(const b200exl3_moe* local_experts, int64_t rows, size_t* out_bytes);
+int b200exl3_moe_forward_ep(const b200exl3_moe* local_experts, b200exl3_ep* ep, int first_expert, const void* d_x, int x_dtype,
+                            int64_t rows, const uint32_t* d_selected, const void* d_scores, int score_dtype, void* d_y,
+                            void* d_workspace, size_t workspace_bytes, b200exl3_stream stream);
+
 /* ---- decoder-block glue: fp16, one token per call (batch-1 decode) ----------------------------------------------
  * The operators a decoder block runs between its quantized projections (call order: native/src/lfm2.rs:704-793), as
  * the reference reaches them through MLX (native/src/array.rs:1517-1519 rope, 1662-1664 rms_norm, 1741-1743 swiglu,

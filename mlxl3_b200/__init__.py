@@ -8,9 +8,9 @@ from .linear import DEFAULT, MCG, MUL1, Exl3Group, Exl3Linear, new_workspace, st
 from .moe import Exl3SwitchGlu
 from .stack import Exl3Stack
 from .runtime import DEFAULT_STREAM, DeviceBuffer, Event, Graph, PinnedBuffer, Stream, init, set_option
-from . import checkpoint, codec, decoder, router
+from . import checkpoint, codec, decoder, ep, router
 
 __all__ = [
     "BF16", "F16", "F32", "B200Exl3Error", "LIB_PATH", "DEFAULT", "MCG", "MUL1", "Exl3Group", "Exl3Linear", "new_workspace", "static_status", "workspace_status", "DEFAULT_STREAM",
-    "Exl3SwitchGlu", "Exl3Stack", "DeviceBuffer", "Event", "Graph", "PinnedBuffer", "Stream", "init", "set_option", "checkpoint", "codec", "decoder", "router",
+    "Exl3SwitchGlu", "Exl3Stack", "DeviceBuffer", "Event", "Graph", "PinnedBuffer", "Stream", "init", "set_option", "checkpoint", "codec", "decoder", "ep", "router",
 ]

@@ -74,6 +74,14 @@ SIGNATURES = {
     "b200exl3_stack_status": (c_int, [c_void_p, POINTER(c_int)]),
     "b200exl3_stack_reset": (c_int, [c_void_p]),
     "b200exl3_stack_geometry": (c_int, [c_void_p, POINTER(c_int), POINTER(c_size_t)]),
+    "b200exl3_ipc_alloc": (c_int, [c_size_t, POINTER(c_void_p), c_char_p]),
+    "b200exl3_ep_buffer_bytes": (c_int, [c_int, c_int, POINTER(c_size_t)]),
+    "b200exl3_ep_create": (c_int, [c_int, c_int, c_int, c_int, POINTER(c_void_p), POINTER(c_void_p)]),
+    "b200exl3_ep_free": (None, [c_void_p]),
+    "b200exl3_ep_status": (c_int, [c_void_p, POINTER(c_int)]),
+    "b200exl3_moe_ep_workspace_bytes": (c_int, [c_void_p, c_int64, POINTER(c_size_t)]),
+    "b200exl3_moe_forward_ep": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                        c_size_t, c_void_p]),
     "b200exl3_embed": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p, c_void_p]),
     "b200exl3_rms_norm": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_float, c_void_p, c_void_p, c_void_p]),
     "b200exl3_swiglu": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),

@@ -1086,6 +1086,172 @@ int b200exl3_router_gate(const void* d_x, int x_dtype, const uint16_t* d_weight_
                                     reinterpret_cast<__half*>(d_logits_f16), as_stream(s)), "router gate kernel");
 }
 
+/* ---- expert parallelism ---------------------------------------------------------------------------------------------- */
+
+struct b200exl3_ep {
+    int rank, world, max_slots, out;
+    void* buffers[kTpMaxWorld];
+    unsigned int* done;          // [max_slots] use counts + one status word
+};
+
+int b200exl3_ep_buffer_bytes(int max_slots, int out, size_t* out_bytes) {
+    if (!out_bytes) return fail("NULL argument");
+    if (max_slots < 1 || out <= 0 || out % 128) return fail("invalid expert-parallel geometry");
+    *out_bytes = static_cast<size_t>(2) * max_slots * (out / 2) * sizeof(unsigned long long);
+    return 0;
+}
+
+int b200exl3_ipc_alloc(size_t bytes, void** out_buffer, unsigned char* out_handle64) {
+    if (!out_buffer || !out_handle64 || bytes == 0) return fail("NULL argument");
+    *out_buffer = nullptr;
+    void* p = nullptr;
+    B200_TRY(cudaMalloc(&p, bytes), "cudaMalloc(exchange buffer)");
+    cudaIpcMemHandle_t handle;
+    if (check(cudaMemset(p, 0, bytes), "clear exchange buffer") || check(cudaDeviceSynchronize(), "clear exchange buffer") ||
+        check(cudaIpcGetMemHandle(&handle, p), "cudaIpcGetMemHandle")) {
+        cudaFree(p);
+        return -1;
+    }
+    memcpy(out_handle64, &handle, sizeof handle);
+    *out_buffer = p;
+    return 0;
+}
+
+int b200exl3_ep_create(int rank, int world, int max_slots, int out, void* const* buffers, b200exl3_ep** out_handle) {
+    if (!out_handle) return fail("out pointer is NULL");
+    *out_handle = nullptr;
+    if (world < 1 || world > kTpMaxWorld || rank < 0 || rank >= world || max_slots < 1 || out <= 0 || out % 128)
+        return fail("invalid expert-parallel geometry");
+    if (!buffers) return fail("NULL argument");
+    for (int r = 0; r < world; ++r)
+        if (!buffers[r] || !aligned16(buffers[r])) return fail("exchange buffer of rank %d is NULL or misaligned", r);
+    b200exl3_ep* h = new (std::nothrow) b200exl3_ep{};
+    if (!h) return fail("out of host memory");
+    h->rank = rank; h->world = world; h->max_slots = max_slots; h->out = out;
+    for (int r = 0; r < world; ++r) h->buffers[r] = buffers[r];
+    const size_t bytes = (static_cast<size_t>(max_slots) + 1) * sizeof(unsigned int);
+    if (check(cudaMalloc(&h->done, bytes), "cudaMalloc(use counts)") || check(cudaMemset(h->done, 0, bytes), "clear use counts") ||
+        check(cudaDeviceSynchronize(), "ep_create")) {
+        cudaFree(h->done);
+        delete h;
+        return -1;
+    }
+    *out_handle = h;
+    return 0;
+}
+
+void b200exl3_ep_free(b200exl3_ep* h) {
+    if (!h) return;
+    cudaFree(h->done);
+    delete h;
+}
+
+int b200exl3_ep_status(const b200exl3_ep* h, int* out_status) {
+    if (!h || !out_status) return fail("NULL argument");
+    unsigned int flag = 0;
+    B200_TRY(cudaMemcpy(&flag, h->done + h->max_slots, sizeof flag, cudaMemcpyDeviceToHost), "read status");
+    *out_status = static_cast<int>(flag);
+    return 0;
+}
+
+struct MoeEpLayout {
+    size_t local_count, local_slot, local_expert, xgu, ygu, xdown, ydown, partials, total;
+    QmvPlan gu_plan, down_plan;
+};
+
+static MoeEpLayout moe_ep_layout(const b200exl3_moe* h, int64_t slots) {
+    MoeEpLayout l{};
+    l.gu_plan = plan_qmv(h->in, static_cast<int>(slots * 2 * h->hidden), h->k, 1);
+    l.down_plan = plan_qmv(h->hidden, static_cast<int>(slots * h->in), h->k, 1);
+    size_t at = kCounterBytes;
+    l.local_count = at; at += 256;
+    l.local_slot = at; at += round256(static_cast<size_t>(slots) * sizeof(uint32_t));
+    l.local_expert = at; at += round256(static_cast<size_t>(slots) * sizeof(uint32_t));
+    l.xgu = at; at += round256(static_cast<size_t>(slots) * 2 * h->in * sizeof(__half));
+    l.ygu = at; at += round256(static_cast<size_t>(slots) * 2 * h->hidden * sizeof(float));
+    l.xdown = at; at += round256(static_cast<size_t>(slots) * h->hidden * sizeof(__half));
+    l.ydown = at; at += round256(static_cast<size_t>(slots) * h->in * sizeof(float));
+    l.partials = at;
+    at += std::max(qmv_partial_bytes(l.gu_plan, static_cast<int>(slots * 2 * h->hidden), 1),
+                   qmv_partial_bytes(l.down_plan, static_cast<int>(slots * h->in), 1));
+    l.total = at;
+    return l;
+}
+
+int b200exl3_moe_ep_workspace_bytes(const b200exl3_moe* h, int64_t rows, size_t* out_bytes) {
+    if (!h || !out_bytes) return fail("NULL argument");
+    if (rows <= 0) return fail("invalid SwitchGLU input/routes");
+    *out_bytes = moe_ep_layout(h, std::min(rows, moe_chunk_rows(h)) * h->top_k).total;
+    return 0;
+}
+
+int b200exl3_moe_forward_ep(const b200exl3_moe* h, b200exl3_ep* ep, int first_expert, const void* d_x, int x_dtype, int64_t rows,
+                            const uint32_t* d_selected, const void* d_scores, int score_dtype, void* d_y, void* ws, size_t ws_bytes,
+                            b200exl3_stream s) {
+    if (!h || !ep) return fail("NULL handle");
+    if (rows <= 0) return fail("invalid SwitchGLU input/routes");
+    if (!dtype_is_float(x_dtype)) return fail("unsupported input dtype %d", x_dtype);
+    if (score_dtype != kF16 && score_dtype != kF32) return fail("unsupported score dtype %d", score_dtype);
+    if (!d_x || !d_selected || !d_scores || !d_y) return fail("NULL buffer");
+    if (!aligned16(ws) || !aligned16(d_y)) return fail("device pointers must be 16-byte aligned");
+    if (first_expert < 0) return fail("invalid first expert");
+    if (ep->out != h->in) return fail("the exchange buffers were made for rows of %d values, the block produces %d", ep->out, h->in);
+    const int64_t chunk = moe_chunk_rows(h);
+    if (std::min(rows, chunk) * h->top_k > ep->max_slots)
+        return fail("%lld slots exceed the exchange buffers' %d", static_cast<long long>(std::min(rows, chunk) * h->top_k), ep->max_slots);
+    const MoeEpLayout l = moe_ep_layout(h, std::min(rows, chunk) * h->top_k);
+    if (!ws || ws_bytes < l.total) return fail("workspace too small: %zu bytes given, %zu needed", ws_bytes, l.total);
+    cudaStream_t stream = as_stream(s);
+    char* base = static_cast<char*>(ws);
+    const bool exact = (h->flags & B200EXL3_EXACT_WEIGHTS) != 0;
+    const size_t x_size = dtype_size(x_dtype), score_size = dtype_size(score_dtype);
+    int* local_count = reinterpret_cast<int*>(base + l.local_count);
+    uint32_t* local_slot = reinterpret_cast<uint32_t*>(base + l.local_slot);
+    uint32_t* local_expert = reinterpret_cast<uint32_t*>(base + l.local_expert);
+    __half* xgu = reinterpret_cast<__half*>(base + l.xgu);
+    float* ygu = reinterpret_cast<float*>(base + l.ygu);
+    __half* xdown = reinterpret_cast<__half*>(base + l.xdown);
+    float* ydown = reinterpret_cast<float*>(base + l.ydown);
+    EpPeers peers{};
+    for (int r = 0; r < ep->world; ++r) peers.inbox[r] = static_cast<unsigned long long*>(ep->buffers[r]);
+    peers.done = ep->done; peers.error = ep->done + ep->max_slots;
+    peers.rank = ep->rank; peers.world = ep->world; peers.max_slots = ep->max_slots;
+    peers.wait_ns = static_cast<unsigned long long>(g_tp_wait_ms.load()) * 1000000ull;
+    for (int64_t r0 = 0; r0 < rows; r0 += chunk) {
+        const int64_t n = std::min(chunk, rows - r0), slots = n * h->top_k;
+        const uint32_t* sel = d_selected + r0 * h->top_k;
+        // one activation row per local slot against the columns of its (local) expert; slots past the count are skipped
+        auto mapped = [&](const uint32_t* wq, const __half* xhat, int in, int width, int proj, int stride_blocks, float* yhat) {
+            const int out = static_cast<int>(slots * proj * width);
+            QmvArgs a{};
+            a.wq = wq; a.xhat = xhat; a.xhat_group_stride = in;
+            a.counters = reinterpret_cast<unsigned int*>(base);
+            a.error = reinterpret_cast<unsigned int*>(base + kCounterBytes - sizeof(unsigned int));
+            a.partials = reinterpret_cast<float*>(base + l.partials);
+            a.yhat = yhat;
+            a.groups = 1; a.gcol0[0] = 0; a.gout[0] = out;
+            a.x_dtype = kF16; a.y_dtype = kF16;
+            a.in = in; a.out = out; a.rows = 1;
+            a.tiles_n = h->experts * proj * width / 16;
+            a.map_selected = local_expert; a.map_count = local_count;
+            a.map_blocks = width / 128; a.map_proj = proj; a.map_stride_blocks = stride_blocks; a.map_experts = h->experts;
+            return launch_qmv(a, h->k, h->cb, exact, plan_qmv(in, out, h->k, 1), stream);
+        };
+        B200_TRY(launch_ep_plan(sel, slots, first_expert, h->experts, local_count, local_slot, local_expert, stream), "expert plan");
+        B200_TRY(launch_ep_dispatch(static_cast<const char*>(d_x) + static_cast<size_t>(r0) * h->in * x_size, x_dtype, h->gu_suh, local_count,
+                                    local_slot, local_expert, h->top_k, h->in, slots, xgu, stream), "expert dispatch");
+        B200_TRY(mapped(h->gu_wq, xgu, h->in, h->hidden, 2, h->experts * (h->hidden / 128), ygu), "expert gate/up kernel");
+        B200_TRY(launch_glu_down_input(ygu, h->gu_svh, h->down_suh, local_expert, h->experts, slots, h->hidden, h->hidden, xdown, stream,
+                                       local_count), "SwiGLU glue");
+        B200_TRY(mapped(h->down_wq, xdown, h->hidden, h->in, 1, 0, ydown), "expert down kernel");
+        B200_TRY(launch_ep_publish(ydown, h->down_svh, local_count, local_slot, local_expert, h->in, slots, peers, stream), "expert publish");
+        B200_TRY(launch_ep_combine(static_cast<const char*>(d_scores) + static_cast<size_t>(r0) * h->top_k * score_size, score_dtype, n,
+                                   h->top_k, h->in, static_cast<char*>(d_y) + static_cast<size_t>(r0) * h->in * score_size, peers, stream),
+                 "expert combine");
+    }
+    return 0;
+}
+
 /* ---- decoder-block glue (fp16, batch-1 decode) ----------------------------------------------------------------- */
 
 int b200exl3_embed(const uint16_t* d_table, const int32_t* d_tokens, int64_t rows, int64_t vocab, int hidden, uint16_t* d_out,

@@ -174,14 +174,32 @@ cudaError_t launch_stack(const StackArgs& args, int k, int cb, bool exact, const
 // ---- grouped experts (kernels_moe.cu) ------------------------------------------------------------------
 // SwiGLU glue between the expert projections (native/src/moe.rs:438-533, SiLU): raw gate/up sums
 // ygu[slot * 2 + {0,1}, :] -> rotated input of the down projection xhat[slot, :]
+// `count` (optional, device): only slots below *count are computed
 cudaError_t launch_glu_down_input(const float* ygu, const __half* gu_svh, const __half* down_suh, const uint32_t* selected,
                                   int experts, int64_t slots, int hidden, int logical_hidden, __half* xhat,
-                                  cudaStream_t stream);
+                                  cudaStream_t stream, const int* count = nullptr);
 // y[row, :] = sum over the row's top_k slots of rotate(half(raw[slot, :])) * svh[selected[slot], :] * score
 // (native/src/moe.rs:586-609); scores and y are fp16 or fp32 (score_dtype)
 cudaError_t launch_finish_and_reduce(const float* raw, const __half* down_svh, const uint32_t* selected, int experts,
                                      const void* scores, int score_dtype, int64_t rows, int top_k, int out, void* y,
                                      cudaStream_t stream);
+
+// ---- expert parallelism (kernels_ep.cu) -------------------------------------------------------------------------------
+struct EpPeers {
+    unsigned long long* inbox[kTpMaxWorld];   // every rank's inbox [2, max_slots, out / 2] of {two fp16 values, sequence} words
+    unsigned int* done;                       // [max_slots] calls that used each slot index (identical on all ranks)
+    unsigned int* error;                      // status word: 7 = a slot result never arrived
+    int rank, world, max_slots;
+    unsigned long long wait_ns;
+};
+cudaError_t launch_ep_plan(const uint32_t* selected, int64_t slots, int first, int count, int* local_count, uint32_t* local_slot,
+                           uint32_t* local_expert, cudaStream_t stream);
+cudaError_t launch_ep_dispatch(const void* x, int x_dtype, const __half* gu_suh, const int* local_count, const uint32_t* local_slot,
+                               const uint32_t* local_expert, int top_k, int in, int64_t max_slots, __half* xhat, cudaStream_t stream);
+cudaError_t launch_ep_publish(const float* raw, const __half* down_svh, const int* local_count, const uint32_t* local_slot,
+                              const uint32_t* local_expert, int out, int64_t max_slots, const EpPeers& ep, cudaStream_t stream);
+cudaError_t launch_ep_combine(const void* scores, int score_dtype, int64_t rows, int top_k, int out, void* y, const EpPeers& ep,
+                              cudaStream_t stream);
 
 // ---- row-parallel sum over peer memory + output rotation (kernels_tp.cu) -----------------------------------
 struct TpArgs {

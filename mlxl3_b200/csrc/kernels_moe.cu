@@ -29,9 +29,10 @@ __device__ __forceinline__ float silu(float v) { return __fdiv_rn(v, __fadd_rn(1
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 glu_down_input_kernel(const float* __restrict__ ygu, const __half* __restrict__ gu_svh, const __half* __restrict__ down_suh,
                       const uint32_t* __restrict__ selected, int experts, int64_t slots, int hidden, int logical_hidden,
-                      __half* __restrict__ xhat) {
+                      __half* __restrict__ xhat, const int* __restrict__ count) {
     const int lane = threadIdx.x & 31;
     const int blocks_per_row = hidden >> 7;
+    if (count != nullptr) slots = min(slots, static_cast<int64_t>(*count));
     const int64_t total = slots * blocks_per_row;
     const float scale = had_scale();
     for (int64_t unit = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5); unit < total;
@@ -130,10 +131,10 @@ unsigned grid_for(int64_t units) {
 
 cudaError_t launch_glu_down_input(const float* ygu, const __half* gu_svh, const __half* down_suh, const uint32_t* selected,
                                   int experts, int64_t slots, int hidden, int logical_hidden, __half* xhat,
-                                  cudaStream_t stream) {
+                                  cudaStream_t stream, const int* count) {
     if (slots == 0) return cudaSuccess;
     glu_down_input_kernel<<<grid_for(slots * (hidden / 128)), kWarpsPerBlock * 32, 0, stream>>>(
-        ygu, gu_svh, down_suh, selected, experts, slots, hidden, logical_hidden, xhat);
+        ygu, gu_svh, down_suh, selected, experts, slots, hidden, logical_hidden, xhat, count);
     return cudaGetLastError();
 }
 
