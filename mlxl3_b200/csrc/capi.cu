@@ -361,10 +361,13 @@ static int core_workspace_bytes(const LayerCore& c, int64_t rows, size_t* out_by
     if (rows <= 0) return fail("EXL3 linear input cannot be empty");
     QmvPlan plan = plan_qmv(c.in, c.out, c.k, rows);
     size_t bytes = kCounterBytes + qmv_partial_bytes(plan, c.out, rows) + xhat_bytes(c, rows);
-    if (rows >= kQmmMinRows && c.groups == 1) {
-        const QmmPlan qp = plan_qmm(c.in, c.out, rows);
-        bytes = std::max(bytes, kCounterBytes + round256(static_cast<size_t>(rows) * c.in * sizeof(__half)) +
-                                    qmm_partial_bytes(qp, c.out, rows));
+    if (rows >= kQmmMinRows) {
+        // tensor-core path: one rotated copy of the rows at a time (per member of a group) and the member's partials
+        for (int g = 0; g < c.groups; ++g) {
+            const QmmPlan qp = plan_qmm(c.in, c.gout[g], rows);
+            bytes = std::max(bytes, kCounterBytes + round256(static_cast<size_t>(rows) * c.in * sizeof(__half)) +
+                                        qmm_partial_bytes(qp, c.gout[g], rows));
+        }
     }
     *out_bytes = bytes;
     return 0;
@@ -391,21 +394,36 @@ static int forward_common(const LayerCore& c, const void* d_x, int x_dtype, cons
     const bool exact = (c.flags & B200EXL3_EXACT_WEIGHTS) != 0;
     const size_t x_size = dtype_size(x_dtype);
     const __half* xhat = reinterpret_cast<const __half*>(d_xhat);
-    if (rows >= kQmmMinRows && c.groups == 1 && ys && !d_xhat && g_qmm_enabled && !tp) {
-        // many rows: input rotation -> tensor-core product (fp32 partials per input split) -> output rotation
+    if (rows >= kQmmMinRows && ys && !d_xhat && g_qmm_enabled) {
+        // many rows: input rotation -> tensor-core product (fp32 partials per input split) -> output rotation.
+        // A group runs member by member (each member has its own input scales, so its own rotated rows); a row shard
+        // of a tensor-parallel layer keeps one split, and the sum over ranks and the rotation follow as one kernel.
         __half* buf = reinterpret_cast<__half*>(base + kCounterBytes);
         float* partials = reinterpret_cast<float*>(base + kCounterBytes + round256(static_cast<size_t>(rows) * c.in * sizeof(__half)));
-        const QmmPlan qp = plan_qmm(c.in, c.out, rows);
-        B200_TRY(launch_prepare(d_x, x_dtype, c.suh, 1, rows, c.in, buf, stream), "prepare");
         unsigned int* status = reinterpret_cast<unsigned int*>(base + kCounterBytes - sizeof(unsigned int));
-        if (qp.splits == 1) {
-            // one CTA holds the whole input range of its columns: the output rotation runs in its epilogue
-            B200_TRY(launch_qmm(c.wq, c.in, c.out, c.k, c.cb, buf, rows, qp, partials, status, c.svh, c.bias, ys[0], x_dtype, stream),
-                     "tensor-core product kernel");
-        } else {
-            B200_TRY(launch_qmm(c.wq, c.in, c.out, c.k, c.cb, buf, rows, qp, partials, status, nullptr, nullptr, nullptr, 0, stream),
-                     "tensor-core product kernel");
-            B200_TRY(launch_finish(partials, qp.splits, rows * c.out, c.svh, 1, c.bias, rows, c.out, x_dtype, ys[0], stream), "finish");
+        for (int g = 0; g < c.groups; ++g) {
+            QmmPlan qp = plan_qmm(c.in, c.gout[g], rows);
+            const __half* svh = c.svh + c.gcol0[g];
+            const __half* bias = c.bias ? c.bias + c.gcol0[g] : nullptr;
+            const int ld = c.out / 16, col0 = c.gcol0[g] / 16;
+            B200_TRY(launch_prepare(d_x, x_dtype, c.suh + static_cast<size_t>(g) * c.in, 1, rows, c.in, buf, stream), "prepare");
+            if (tp) {
+                qp.splits = 1;
+                B200_TRY(launch_qmm(c.wq, c.in, c.gout[g], c.k, c.cb, buf, rows, qp, partials, status, nullptr, nullptr, nullptr, 0, stream, ld, col0),
+                         "tensor-core product kernel");
+                TpArgs a{};
+                a.yhat = partials; a.peers = tp_peers(tp); a.svh = svh; a.bias = bias; a.y = ys[g];
+                a.rows = static_cast<int>(rows); a.out = c.gout[g]; a.y_dtype = x_dtype;
+                B200_TRY(launch_tp_finish(a, stream), "tensor-parallel finish kernel");
+            } else if (qp.splits == 1) {
+                // one CTA holds the whole input range of its columns: the output rotation runs in its epilogue
+                B200_TRY(launch_qmm(c.wq, c.in, c.gout[g], c.k, c.cb, buf, rows, qp, partials, status, svh, bias, ys[g], x_dtype, stream, ld, col0),
+                         "tensor-core product kernel");
+            } else {
+                B200_TRY(launch_qmm(c.wq, c.in, c.gout[g], c.k, c.cb, buf, rows, qp, partials, status, nullptr, nullptr, nullptr, 0, stream, ld, col0),
+                         "tensor-core product kernel");
+                B200_TRY(launch_finish(partials, qp.splits, rows * c.gout[g], svh, 1, bias, rows, c.gout[g], x_dtype, ys[g], stream), "finish");
+            }
         }
         return 0;
     }

@@ -278,9 +278,11 @@ size_t qmm_partial_bytes(const QmmPlan& plan, int out, int64_t rows);
 // partials[s, r, n] (fp32) = sum over the inputs of split s of xhat[r, :] (fp16, rotated) x W[:, n]; with one
 // split and y != nullptr the output rotation (half -> H128 -> * svh, + bias) is applied in the kernel's epilogue
 // and y[r, n] is stored in y_dtype instead.
+// A member of a group (projections concatenated on the output axis) is addressed by ld_tiles (tiles per row of the
+// whole weight array; 0 = out / 16) and col_tile0 (the member's first tile column, a multiple of 8).
 cudaError_t launch_qmm(const uint32_t* wq, int in, int out, int k, int cb, const __half* xhat, int64_t rows,
                        const QmmPlan& plan, float* partials, unsigned int* error, const __half* svh, const __half* bias,
-                       void* y, int y_dtype, cudaStream_t stream);
+                       void* y, int y_dtype, cudaStream_t stream, int ld_tiles = 0, int col_tile0 = 0);
 // Expert-mapped form of the small shape: segment s = 64 padded rows xhat[(s * proj + p) * 64 + r, :] that all use expert
 // seg_expert[s]; products[r, (s * proj + p) * width + col] (fp32, row stride max_segments * proj * width).
 constexpr int kQmmSegRows = 64;

@@ -508,8 +508,11 @@ size_t qmm_partial_bytes(const QmmPlan& plan, int out, int64_t rows) {
 
 cudaError_t launch_qmm(const uint32_t* wq, int in, int out, int k, int cb, const __half* xhat, int64_t rows,
                        const QmmPlan& plan, float* partials, unsigned int* error, const __half* svh, const __half* bias,
-                       void* y, int y_dtype, cudaStream_t stream) {
-    if (in % 128 || out % 128 || rows <= 0) return cudaErrorInvalidValue;
+                       void* y, int y_dtype, cudaStream_t stream, int ld_tiles, int col_tile0) {
+    if (in % 128 || out % 128 || rows <= 0 || col_tile0 % 8) return cudaErrorInvalidValue;
+    if (ld_tiles <= 0) ld_tiles = out / 16;
+    // a member of a group: its columns start col_tile0 tiles into rows that are ld_tiles tiles long
+    wq += static_cast<size_t>(col_tile0) * 8 * k;
     if (y != nullptr && plan.splits != 1) return cudaErrorInvalidValue;     // the fused rotation needs the complete sum
     EncodeFn encode = encode_fn();
     if (!encode) return cudaErrorNotSupported;
@@ -527,7 +530,7 @@ cudaError_t launch_qmm(const uint32_t* wq, int in, int out, int k, int cb, const
     // 4 tile rows x 8 tiles (32*K words of a row), landing contiguously in shared memory
     CUtensorMap wmap;
     const cuuint64_t wdims[2] = {static_cast<cuuint64_t>(out / 16) * 4 * k, static_cast<cuuint64_t>(in / 16)};
-    const cuuint64_t wstrides[1] = {static_cast<cuuint64_t>(out / 16) * 32 * k};
+    const cuuint64_t wstrides[1] = {static_cast<cuuint64_t>(ld_tiles) * 32 * k};
     const cuuint32_t wbox[2] = {static_cast<cuuint32_t>(32 * k), 4};
     if (encode(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint32_t*>(wq), wdims, wstrides, wbox, elem,
                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,

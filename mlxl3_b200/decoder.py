@@ -250,3 +250,39 @@ class DenseDecoder:
 
     def download(self, name: str) -> np.ndarray:
         return self.buf[name].download((self.buf[name].nbytes // 2,), np.float16, self.stream)
+
+
+class DenseMlp:
+    """The dense SwiGLU MLP block for any number of rows: [gate|up] as one ``Exl3Group``, SwiGLU, down.  With 9 rows
+    and more every projection runs on the tensor cores (tcgen05); below that on the fused small-batch kernel."""
+
+    def __init__(self, gate: Exl3Linear, up: Exl3Linear, down: Exl3Linear):
+        if gate.cols != up.cols or down.rows != gate.cols or down.cols != gate.rows:
+            raise _lib.B200Exl3Error("MLP projections disagree")
+        self.group, self.down = Exl3Group([gate, up]), down
+        self.hidden, self.ffn = gate.rows, gate.cols
+        self._rows, self._bufs, self._ws = 0, None, None
+
+    def _ensure(self, rows: int) -> None:
+        if rows > self._rows:
+            self._bufs = [DeviceBuffer(rows * self.ffn * 2) for _ in range(3)]
+            self._ws = new_workspace(max(self.group.workspace_bytes(rows), self.down.workspace_bytes(rows)))
+            self._rows = rows
+
+    def forward_device(self, d_x: int, rows: int, d_y: int, stream: Stream = DEFAULT_STREAM) -> None:
+        """fp16 rows in, fp16 rows out, no host copies."""
+        self._ensure(rows)
+        gate, up, act = self._bufs
+        self.group.forward_device(d_x, F16, rows, [gate.ptr, up.ptr], self._ws, stream)
+        swiglu(gate.ptr, up.ptr, rows * self.ffn, act.ptr, stream)
+        self.down.forward_device(act.ptr, F16, rows, d_y, self._ws, stream)
+
+    def forward(self, x: np.ndarray, stream: Stream = DEFAULT_STREAM) -> np.ndarray:
+        x = np.ascontiguousarray(x, np.float16)
+        rows = x.shape[0]
+        d_x, d_y = DeviceBuffer.from_numpy(x, stream), DeviceBuffer(rows * self.hidden * 2)
+        self.forward_device(d_x.ptr, rows, d_y.ptr, stream)
+        return d_y.download((rows, self.hidden), np.float16, stream)
+
+    def flops(self, rows: int) -> int:
+        return 3 * 2 * rows * self.hidden * self.ffn

@@ -171,3 +171,24 @@ def test_small_decoder_steps_match_oracle(gpu):
         _, index = dec.result()
         assert index == eager[pos][1] and np.array_equal(bits(dec.download("logits")), eager[pos][0])
     assert gpu.workspace_status(dec.ws) == 0
+
+
+@pytest.mark.parametrize("rows", [3, 40])
+def test_dense_mlp_block(gpu, rows):
+    """[gate|up] -> SwiGLU -> down against the oracle's projections and SwiGLU, on the fused kernel (3 rows) and on
+    the tensor cores (40 rows: the grouped pair runs member by member through the tcgen05 product)."""
+    from mlxl3_b200.decoder import DenseMlp
+    from tests.gpu_util import random_layer
+    rng = np.random.default_rng(50 + rows)
+    hidden, ffn, k = 512, 1024, 3
+    layers = []
+    for n_in, n_out in ((hidden, ffn), (hidden, ffn), (ffn, hidden)):
+        t, s, v = random_layer(rng, n_in, n_out, k)
+        layers.append((t, s, (v.astype(np.float32) / (1.2437 * np.sqrt(n_in))).astype(np.float16)))
+    mlp = DenseMlp(*(gpu.Exl3Linear(t, s, v, None, k, 0) for t, s, v in layers))
+    x = rng.standard_normal((rows, hidden)).astype(np.float16)
+    got = mlp.forward(x).astype(np.float32)
+    g, u = (oracle.linear_forward(t, k, 0, s, v, None, x) for t, s, v in layers[:2])
+    want = oracle.linear_forward(*layers[2][:1], k, 0, layers[2][1], layers[2][2], None, od.swiglu(g, u)).astype(np.float32)
+    assert np.isfinite(got).all() and np.abs(got - want).max() <= 2e-2 * np.abs(want).max()
+    assert mlp.flops(512) == 3 * 2 * 512 * hidden * ffn
