@@ -124,6 +124,63 @@ def close_enough(got: np.ndarray, want: np.ndarray, rel: float = 1e-2) -> bool:
     return bool(np.isfinite(g).all() and np.abs(g - w).max() <= rel * np.abs(w).max())
 
 
+def measure_extras(ex, stream, Event, DeviceBuffer) -> dict:
+    """Device times (CUDA events on the launching stream, 3 warm-up and 10 timed calls each) of the prefill MLP block
+    and of the expert block, with seeded synthetic weights."""
+    from mlxl3_b200.decoder import DenseMlp
+    peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+    tensor_peak = float(peaks.get("bf16_tflops", 1590.0))
+
+    def timed(call, reps=10):
+        for _ in range(3):
+            call()
+        stream.sync()
+        start, stop = Event(), Event()
+        start.record(stream)
+        for _ in range(reps):
+            call()
+        stop.record(stream)
+        return start.elapsed_ms(stop) / reps
+    rng = np.random.default_rng(2001)
+
+    def layer(n_in, n_out, k):
+        trellis = rng.integers(0, 65536, (n_in // 16, n_out // 16, 16 * k), dtype=np.uint16)
+        suh = np.where(rng.random(n_in) > 0.5, -1, 1).astype(np.float16)
+        svh = (np.where(rng.random(n_out) > 0.5, -1, 1) / (1.2437 * np.sqrt(n_in))).astype(np.float16)
+        return ex.Exl3Linear(trellis, suh, svh, None, k, CB)
+    rows = 512
+    mlp = DenseMlp(layer(HIDDEN, FFN, 3), layer(HIDDEN, FFN, 3), layer(FFN, HIDDEN, 3))
+    d_x = DeviceBuffer.from_numpy(rng.standard_normal((rows, HIDDEN)).astype(np.float16))
+    d_y = DeviceBuffer(rows * HIDDEN * 2)
+    ms = timed(lambda: mlp.forward_device(d_x.ptr, rows, d_y.ptr, stream))
+    y = d_y.download((rows, HIDDEN), np.float16, stream).astype(np.float32)
+    tflops = mlp.flops(rows) / ms / 1e9
+    qmm = {"workload": "dense MLP block, 512 rows: [gate|up] 4096->14336 x2, SwiGLU, down 14336->4096, 3 bits", "ms": round(ms, 4),
+           "tflops": round(tflops, 1), "peak_tflops": tensor_peak, "frac": round(tflops / tensor_peak, 4), "bound": "tensor",
+           "finite": bool(np.isfinite(y).all() and np.abs(y).max() > 0)}
+    # expert block
+    experts, top_k, n_in, hidden, k = 128, 8, 2048, 768, 3
+    gu_t = rng.integers(0, 65536, (n_in // 16, experts * hidden // 8, 16 * k), dtype=np.uint16)
+    down_t = rng.integers(0, 65536, (hidden // 16, experts * n_in // 16, 16 * k), dtype=np.uint16)
+    sign = lambda *shape: np.where(rng.random(shape) > 0.5, -1, 1).astype(np.float16)  # noqa: E731
+    block = ex.Exl3SwitchGlu(gu_t, sign(experts, 2, n_in), (sign(experts, 2, hidden) / np.sqrt(n_in)).astype(np.float16), down_t,
+                             sign(experts, hidden), (sign(experts, n_in) / np.sqrt(hidden)).astype(np.float16), top_k, k, CB)
+    moe = {"workload": "expert SwiGLU block: 128 experts, top-8, 2048 <-> 768, 3 bits", "cases": []}
+    slab = 3 * n_in * hidden * k // 8
+    for tokens in (1, 256):
+        x = rng.standard_normal((tokens, n_in)).astype(np.float16)
+        selected = np.stack([rng.permutation(experts)[:top_k] for _ in range(tokens)]).astype(np.uint32)
+        scores = np.full((tokens, top_k), 1.0 / top_k, np.float16)
+        d_in, d_sel, d_sc = DeviceBuffer.from_numpy(x), DeviceBuffer.from_numpy(selected), DeviceBuffer.from_numpy(scores)
+        d_out = DeviceBuffer(tokens * n_in * 2)
+        ws = ex.new_workspace(block.workspace_bytes(tokens))
+        ms = timed(lambda: block.forward_device(d_in.ptr, ex.F16, tokens, d_sel.ptr, d_sc.ptr, ex.F16, d_out.ptr, ws, stream))
+        touched = len(np.unique(selected)) * slab                    # packed bytes of the experts the routes name, read once
+        moe["cases"].append({"tokens": tokens, "ms": round(ms, 4), "expert_bytes": int(touched),
+                             "hbm_gbs": round(touched / ms / 1e6, 1), "frac_of_hbm_peak": round(touched / ms / 1e6 / measured_peak_gbs()[0], 4)})
+    return {"qmm": qmm, "moe": moe}
+
+
 def run_ours(args) -> dict:
     import mlxl3_b200 as ex
     from mlxl3_b200.runtime import DeviceBuffer, Event, Graph, PinnedBuffer, Stream
@@ -416,6 +473,12 @@ def run_ours(args) -> dict:
                   "what": "embedding, 32 x (RMSNorm, [q|k|v], RoPE + cache append, grouped-query attention over 2048 fp16 keys, o, "
                           "RMSNorm, [gate|up], SwiGLU, down), final norm, fp16 head 128256 x 4096, arg-max; one graph replay per token"}
 
+    # ---- the other configurations' headline shapes, one GPU only: the dense MLP block at 512 rows (tensor cores) and
+    #      the grouped-expert block (128 experts, top-8, 2048 <-> 768, 3 bits) at 1 and 256 tokens -----------------------
+    extras = None
+    if world == 1 and not args.no_extras:
+        extras = measure_extras(ex, stream, Event, DeviceBuffer)
+
     # launches per step: one persistent kernel, or one fused kernel per projection (plus the exchange kernels when unfused)
     launches_per_step = len(layers) + (sum(1 for l in layers if l[0] == "row") if world > 1 and args.unfused_exchange else 0)
     if stack is not None:
@@ -435,6 +498,8 @@ def run_ours(args) -> dict:
                    "pdl": bool(args.pdl), "dataflow": "chained: every projection reads the output of the one before it"},
         "linear_stack_tok_s": round(1e3 / ms_per_step, 1),
         "decode": decode,
+        "qmm": extras["qmm"] if extras else None,
+        "moe": extras["moe"] if extras else None,
         "checked": checked,
         "roofline": {"bound": "hbm", "achieved": round(per_gpu, 2), "peak": peak, "unit": "GB/s",
                      "frac": round(per_gpu / peak, 4),
@@ -521,6 +586,7 @@ def main() -> None:
                     help="N > 1: run the sum over ranks as its own kernel after the product instead of inside it")
     ap.add_argument("--mode", default="stack", choices=["stack", "graph"],
                     help="stack: the whole step is one persistent kernel; graph: one fused kernel per layer, replayed as a CUDA graph")
+    ap.add_argument("--no-extras", action="store_true", help="skip the 512-row MLP block and the expert block measurements")
     ap.add_argument("--no-decode", action="store_true", help="skip the whole-model decode measurement")
     ap.add_argument("--pdl", type=int, default=1, help="programmatic dependent launch between layers (0/1)")
     args = ap.parse_args()
