@@ -263,6 +263,27 @@ int b200exl3_stack_reset(b200exl3_stack* handle);
 /* CTAs of the persistent grid and dynamic shared memory per CTA (for reports). */
 int b200exl3_stack_geometry(const b200exl3_stack* handle, int* out_grid, size_t* out_smem_bytes);
 
+/* expert_mapped (native/src/linear.rs:2817-2851) as a stand-alone operator: row r = slot * projections + p of x [rows,
+ * in] against the columns of expert selected[slot] of projection p in a bank trellis [in/16, source_tiles, 16k]
+ * (checkpoint layout; projection p starts projection_stride_tiles tiles in, expert e another e * out/16).  The input is
+ * rotated with its own row of d_suh [rows, in] unless input_pretransformed; the result is the raw fp32 product [rows,
+ * out] (return_raw) or its output rotation scaled by the row's d_svh [rows, out], in x_dtype.  A tool-level call: it
+ * re-lays the bank, allocates its temporaries and waits for the stream.  K = 7 is refused as in the reference. */
+int b200exl3_expert_mapped(const void* d_x, int x_dtype, const uint16_t* d_trellis, int64_t source_tiles, const uint16_t* d_suh_f16,
+                           const uint16_t* d_svh_f16, const uint32_t* d_selected, int64_t slots, int in, int out, int projections,
+                           int64_t projection_stride_tiles, int k, int codebook, int input_pretransformed, int return_raw,
+                           void* d_out, b200exl3_stream stream);
+/* moe::swiglu_down_input (native/src/moe.rs:438-533): raw gate/up products [slots * 2, hidden] fp32 -> the rotated
+ * input of the down projection [slots, hidden] fp16; gu_svh [experts, 2, hidden], down_suh [experts, hidden]. */
+int b200exl3_swiglu_down_input(const float* d_gate_up_raw, const uint16_t* d_gu_svh_f16, const uint16_t* d_down_suh_f16,
+                               const uint32_t* d_selected, int experts, int64_t slots, int hidden, uint16_t* d_xhat_f16,
+                               b200exl3_stream stream);
+/* moe::finish_and_reduce (native/src/moe.rs:586-609): y[row] = sum over the row's top_k slots, in order, of
+ * half(H128(half(raw[slot]))) * svh[selected[slot]] * score[slot]; scores and y fp16 or fp32. */
+int b200exl3_finish_and_reduce(const float* d_raw, const uint16_t* d_svh_f16, const uint32_t* d_selected, int experts,
+                               const void* d_scores, int score_dtype, int64_t rows, int top_k, int out, void* d_y,
+                               b200exl3_stream stream);
+
 /* ---- expert parallelism for Exl3SwitchGlu -----------------------------------------------------------------------
  * No counterpart in the reference (it runs every expert on one device, native/src/moe.rs:905-971); the arithmetic of
  * a slot and of the final sum is the reference's (moe.rs:184-236 routed rotation, 586-609 finish_and_reduce), only

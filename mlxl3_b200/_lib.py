@@ -74,6 +74,10 @@ SIGNATURES = {
     "b200exl3_stack_status": (c_int, [c_void_p, POINTER(c_int)]),
     "b200exl3_stack_reset": (c_int, [c_void_p]),
     "b200exl3_stack_geometry": (c_int, [c_void_p, POINTER(c_int), POINTER(c_size_t)]),
+    "b200exl3_expert_mapped": (c_int, [c_void_p, c_int, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int64,
+                                       c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "b200exl3_swiglu_down_input": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_void_p, c_void_p]),
+    "b200exl3_finish_and_reduce": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int64, c_int, c_int, c_void_p, c_void_p]),
     "b200exl3_ipc_alloc": (c_int, [c_size_t, POINTER(c_void_p), c_char_p]),
     "b200exl3_ep_buffer_bytes": (c_int, [c_int, c_int, POINTER(c_size_t)]),
     "b200exl3_ep_create": (c_int, [c_int, c_int, c_int, c_int, POINTER(c_void_p), POINTER(c_void_p)]),

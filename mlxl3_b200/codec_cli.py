@@ -113,6 +113,59 @@ def _switch(request: dict, k: int, cb: int):
         block.close()
 
 
+def _expert(request: dict, k: int, cb: int):
+    """``mlx-expert`` (native/src/main.rs:540-597): field for field."""
+    from .moe import expert_mapped
+    projections = int(request.get("projections_per_route", 0))
+    selected = np.asarray(request.get("selected", []), dtype=np.uint32)
+    if projections <= 0:
+        raise B200Exl3Error("invalid projection count")
+    rows = selected.size * projections
+    if rows <= 0:
+        raise B200Exl3Error("missing expert routes")
+    x = _u16(request, "x")
+    if x.size % rows:
+        raise B200Exl3Error("invalid expert input dimensions")
+    n_in, cols = x.size // rows, int(request.get("cols", 0))
+    data = _u16(request, "data")
+    per_column = (n_in // 16) * 16 * k
+    if n_in <= 0 or n_in % 16 or data.size % per_column:
+        raise B200Exl3Error("invalid expert trellis dimensions")
+    raw = bool(request.get("return_raw", False))
+    out = expert_mapped(x.view(np.float16).reshape(rows, n_in), data.reshape(n_in // 16, data.size // per_column, 16 * k),
+                        _f16(request, "suh", (rows, n_in)), None if raw else _f16(request, "svh", (rows, cols)), selected, cols, projections,
+                        int(request.get("projection_stride_tiles", 0)), k, cb, False, raw)
+    return {"f32": out.reshape(-1).tolist()} if raw else {"f16": out.view(np.uint16).reshape(-1).tolist()}
+
+
+def _swiglu_prepare(request: dict):
+    """``mlx-swiglu-prepare`` (native/src/main.rs:599-614): ``suh`` carries the gate/up output scales [experts, 2, hidden],
+    ``svh`` the down input scales [experts, hidden]."""
+    from .moe import swiglu_down_input
+    hidden = int(request.get("cols", 0))
+    selected = np.asarray(request.get("selected", []), dtype=np.uint32)
+    scales = _u16(request, "suh")
+    if hidden <= 0 or scales.size % (2 * hidden):
+        raise B200Exl3Error("invalid gate/up scales")
+    experts = scales.size // (2 * hidden)
+    state = np.asarray(request.get("state", []), dtype=np.float32).reshape(selected.size * 2, hidden)
+    out = swiglu_down_input(state, scales.view(np.float16).reshape(experts, 2, hidden), _f16(request, "svh", (experts, hidden)), selected)
+    return out.view(np.uint16).reshape(-1).tolist()
+
+
+def _expert_reduce(request: dict):
+    """``mlx-expert-reduce`` (native/src/main.rs:615-626): one output row from ``len(beta)`` slots."""
+    from .moe import finish_and_reduce
+    width = int(request.get("cols", 0))
+    beta = _u16(request, "beta")
+    slots = beta.size
+    if width <= 0 or slots <= 0:
+        raise B200Exl3Error("invalid expert reduction input")
+    state = np.asarray(request.get("state", []), dtype=np.float32).reshape(slots, width)
+    out = finish_and_reduce(state, _f16(request, "svh", (slots, width)), beta.view(np.float16).reshape(1, slots))
+    return out.view(np.uint16).reshape(-1).tolist()
+
+
 def handle(request: dict):
     """One request -> the value of its ``data`` answer (raises on a bad request)."""
     if not isinstance(request, dict) or not isinstance(request.get("op"), str):
@@ -134,10 +187,16 @@ def handle(request: dict):
         return _group(request, k, cb)
     if op == "mlx-switch":
         return _switch(request, k, cb)
+    if op == "mlx-expert":
+        return _expert(request, k, cb)
+    if op == "mlx-swiglu-prepare":
+        return _swiglu_prepare(request)
+    if op == "mlx-expert-reduce":
+        return _expert_reduce(request)
     raise B200Exl3Error(f"unknown or unavailable codec operation {op}")
 
 
-_DEVICE_OPS = ("unpack", "codebook", "mlx-linear", "mlx-group", "mlx-switch")
+_DEVICE_OPS = ("unpack", "codebook", "mlx-linear", "mlx-group", "mlx-switch", "mlx-expert", "mlx-swiglu-prepare", "mlx-expert-reduce")
 
 
 def main(stdin=None, stdout=None, device: int = 0) -> None:

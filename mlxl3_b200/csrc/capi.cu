@@ -1069,6 +1069,91 @@ int b200exl3_moe_forward(const b200exl3_moe* h, const void* d_x, int x_dtype, in
 }
 
 
+/* ---- expert_mapped and the two glue operators of the expert block, as stand-alone entry points ------------------------ */
+
+int b200exl3_expert_mapped(const void* d_x, int x_dtype, const uint16_t* d_trellis, int64_t source_tiles, const uint16_t* d_suh,
+                           const uint16_t* d_svh, const uint32_t* d_selected, int64_t slots, int in, int out, int projections,
+                           int64_t projection_stride_tiles, int k, int cb, int input_pretransformed, int return_raw, void* d_out,
+                           b200exl3_stream s) {
+    if (valid_format(k, cb)) return -1;
+    if (k == 7) return fail("K = 7 is not supported by the expert-mapped product");
+    if (slots <= 0 || projections <= 0 || in <= 0 || out <= 0 || in % 128 || out % 128 || source_tiles <= 0 || source_tiles % 8 ||
+        projection_stride_tiles < 0 || projection_stride_tiles % 8)
+        return fail("invalid expert-mapped dimensions");
+    if (!dtype_is_float(x_dtype)) return fail("unsupported input dtype %d", x_dtype);
+    if (!d_x || !d_trellis || !d_selected || !d_out || (!input_pretransformed && !d_suh) || (!return_raw && !d_svh)) return fail("NULL buffer");
+    if (input_pretransformed && x_dtype != kF16) return fail("pretransformed expert input must be fp16");
+    const int width_tiles = out / 16;
+    const int64_t experts = projection_stride_tiles > 0 ? projection_stride_tiles / width_tiles : source_tiles / width_tiles;
+    if (experts <= 0 || (projections - 1) * projection_stride_tiles + experts * width_tiles > source_tiles)
+        return fail("expert bank is smaller than the routes' layout");
+    cudaStream_t stream = as_stream(s);
+    const int64_t rows = slots * projections;
+    const int blocks_per_slot = projections * (out / 128);
+    const int64_t pass_slots = std::max<int64_t>(1, (static_cast<int64_t>(kCounterBytes / sizeof(unsigned int)) - 2) / blocks_per_slot);
+    // temporaries of a tool-level call: the bank in the quad layout, rotated rows, raw products, scratch
+    uint32_t* wq = nullptr;
+    __half* xhat = nullptr;
+    float* raw = nullptr;
+    char* ws = nullptr;
+    const size_t bank_bytes = static_cast<size_t>(in / 16) * source_tiles * 16 * k * sizeof(uint16_t);
+    const QmvPlan plan = plan_qmv(in, static_cast<int>(std::min(pass_slots, slots) * projections * out), k, 1);
+    const size_t ws_bytes = kCounterBytes + qmv_partial_bytes(plan, static_cast<int>(std::min(pass_slots, slots) * projections * out), 1);
+    int rc = check(cudaMalloc(&wq, bank_bytes), "cudaMalloc(bank)");
+    if (!rc) rc = check(cudaMalloc(&xhat, static_cast<size_t>(rows) * in * sizeof(__half)), "cudaMalloc(rows)");
+    if (!rc && !return_raw) rc = check(cudaMalloc(&raw, static_cast<size_t>(rows) * out * sizeof(float)), "cudaMalloc(products)");
+    if (!rc) rc = check(cudaMalloc(&ws, ws_bytes), "cudaMalloc(scratch)");
+    if (!rc) rc = check(cudaMemsetAsync(ws, 0, kCounterBytes, stream), "clear scratch");
+    if (!rc) rc = check(launch_repack_quads(reinterpret_cast<const uint32_t*>(d_trellis), in / 16, static_cast<int>(source_tiles), k, wq, stream),
+                        "repack weights");
+    if (!rc) {
+        if (input_pretransformed) rc = check(cudaMemcpyAsync(xhat, d_x, static_cast<size_t>(rows) * in * sizeof(__half), cudaMemcpyDeviceToDevice, stream), "copy rows");
+        else rc = check(launch_prepare(d_x, x_dtype, reinterpret_cast<const __half*>(d_suh), rows, rows, in, xhat, stream), "prepare");
+    }
+    float* products = return_raw ? static_cast<float*>(d_out) : raw;
+    for (int64_t s0 = 0; s0 < slots && !rc; s0 += pass_slots) {
+        const int64_t n = std::min(pass_slots, slots - s0);
+        const int vout = static_cast<int>(n * projections * out);
+        QmvArgs a{};
+        a.wq = wq; a.xhat = xhat + s0 * projections * in; a.xhat_group_stride = in;
+        a.counters = reinterpret_cast<unsigned int*>(ws);
+        a.error = reinterpret_cast<unsigned int*>(ws + kCounterBytes - sizeof(unsigned int));
+        a.partials = reinterpret_cast<float*>(ws + kCounterBytes);
+        a.yhat = products + s0 * projections * out;
+        a.groups = 1; a.gcol0[0] = 0; a.gout[0] = vout;
+        a.x_dtype = kF16; a.y_dtype = kF16;
+        a.in = in; a.out = vout; a.rows = 1;
+        a.tiles_n = static_cast<int>(source_tiles);
+        a.map_selected = d_selected + s0; a.map_blocks = out / 128; a.map_proj = projections;
+        a.map_stride_blocks = static_cast<int>(projection_stride_tiles / 8); a.map_experts = static_cast<int>(experts);
+        rc = check(launch_qmv(a, k, cb, true, plan_qmv(in, vout, k, 1), stream), "expert-mapped kernel");
+    }
+    if (!rc && !return_raw)
+        rc = check(launch_finish(raw, 1, rows * out, reinterpret_cast<const __half*>(d_svh), rows, nullptr, rows, out, x_dtype, d_out, stream), "finish");
+    if (!rc) rc = check(cudaStreamSynchronize(stream), "expert_mapped");
+    cudaFree(wq); cudaFree(xhat); cudaFree(raw); cudaFree(ws);
+    return rc;
+}
+
+int b200exl3_swiglu_down_input(const float* d_gate_up_raw, const uint16_t* d_gu_svh, const uint16_t* d_down_suh, const uint32_t* d_selected,
+                               int experts, int64_t slots, int hidden, uint16_t* d_xhat, b200exl3_stream s) {
+    if (experts <= 0 || slots <= 0 || hidden <= 0 || hidden % 128) return fail("invalid SwiGLU glue dimensions");
+    if (!d_gate_up_raw || !d_gu_svh || !d_down_suh || !d_selected || !d_xhat) return fail("NULL buffer");
+    if (!aligned16(d_gate_up_raw) || !aligned16(d_xhat)) return fail("device pointers must be 16-byte aligned");
+    return check(launch_glu_down_input(d_gate_up_raw, reinterpret_cast<const __half*>(d_gu_svh), reinterpret_cast<const __half*>(d_down_suh),
+                                       d_selected, experts, slots, hidden, hidden, reinterpret_cast<__half*>(d_xhat), as_stream(s)), "SwiGLU glue");
+}
+
+int b200exl3_finish_and_reduce(const float* d_raw, const uint16_t* d_svh, const uint32_t* d_selected, int experts, const void* d_scores,
+                               int score_dtype, int64_t rows, int top_k, int out, void* d_y, b200exl3_stream s) {
+    if (experts <= 0 || rows <= 0 || top_k <= 0 || out <= 0 || out % 128) return fail("invalid expert reduction dimensions");
+    if (score_dtype != kF16 && score_dtype != kF32) return fail("unsupported score dtype %d", score_dtype);
+    if (!d_raw || !d_svh || !d_selected || !d_scores || !d_y) return fail("NULL buffer");
+    if (!aligned16(d_raw) || !aligned16(d_y)) return fail("device pointers must be 16-byte aligned");
+    return check(launch_finish_and_reduce(d_raw, reinterpret_cast<const __half*>(d_svh), d_selected, experts, d_scores, score_dtype, rows, top_k,
+                                          out, d_y, as_stream(s)), "expert reduction");
+}
+
 /* ---- router ------------------------------------------------------------------------------------------------ */
 
 static int router_check(int64_t rows, int experts, int top_k, int dtype) {

@@ -152,3 +152,63 @@ class Exl3SwitchGlu:
             self.close()
         except Exception:
             pass
+
+
+def expert_mapped(x: np.ndarray, trellis: np.ndarray, suh, svh, selected: np.ndarray, output_dims: int, projections_per_route: int,
+                  projection_stride_tiles: int, k: int, cb: int = DEFAULT, input_pretransformed: bool = False, return_raw: bool = False,
+                  stream: Stream = DEFAULT_STREAM) -> np.ndarray:
+    """``expert_mapped`` (native/src/linear.rs:2817-2851): ``x [slots * projections, in]`` (fp16), a bank trellis
+    ``[in/16, source_tiles, 16k]``, per-row scales ``suh [rows, in]`` / ``svh [rows, out]`` (``None`` where unused),
+    ``selected [slots]`` uint32 -> fp32 raw products or fp16 rotated outputs ``[rows, output_dims]``."""
+    x = np.ascontiguousarray(x, np.float16)
+    trellis = np.ascontiguousarray(trellis).view(np.uint16)
+    selected = np.ascontiguousarray(selected, np.uint32).reshape(-1)
+    rows, n_in = x.shape
+    if selected.size == 0 or rows != selected.size * projections_per_route:
+        raise B200Exl3Error("missing expert routes")
+    if trellis.ndim != 3 or trellis.shape[0] * 16 != n_in or trellis.shape[2] != 16 * k:
+        raise B200Exl3Error("invalid expert trellis dimensions")
+    bufs = [DeviceBuffer.from_numpy(a, stream) for a in (x, trellis, selected)]
+    d_suh = DeviceBuffer.from_numpy(np.ascontiguousarray(suh, np.float16), stream) if suh is not None else None
+    d_svh = DeviceBuffer.from_numpy(np.ascontiguousarray(svh, np.float16), stream) if svh is not None else None
+    d_out = DeviceBuffer(rows * output_dims * (4 if return_raw else 2))
+    _lib.call("b200exl3_expert_mapped", c_void_p(bufs[0].ptr), F16, c_void_p(bufs[1].ptr), trellis.shape[1],
+              c_void_p(d_suh.ptr) if d_suh else None, c_void_p(d_svh.ptr) if d_svh else None, c_void_p(bufs[2].ptr), selected.size, n_in,
+              output_dims, projections_per_route, projection_stride_tiles, k, cb, int(input_pretransformed), int(return_raw),
+              c_void_p(d_out.ptr), c_void_p(stream.handle))
+    return d_out.download((rows, output_dims), np.float32 if return_raw else np.float16, stream)
+
+
+def swiglu_down_input(state: np.ndarray, gu_svh: np.ndarray, down_suh: np.ndarray, selected: np.ndarray,
+                      stream: Stream = DEFAULT_STREAM) -> np.ndarray:
+    """``moe::swiglu_down_input`` (native/src/moe.rs:438-533): raw gate/up products ``[slots * 2, hidden]`` fp32 ->
+    rotated down-projection inputs ``[slots, hidden]`` fp16."""
+    state = np.ascontiguousarray(state, np.float32)
+    gu_svh, down_suh = np.ascontiguousarray(gu_svh, np.float16), np.ascontiguousarray(down_suh, np.float16)
+    selected = np.ascontiguousarray(selected, np.uint32).reshape(-1)
+    hidden = state.shape[1]
+    if state.shape[0] != 2 * selected.size or gu_svh.shape[1:] != (2, hidden) or down_suh.shape != (gu_svh.shape[0], hidden):
+        raise B200Exl3Error("invalid gate/up scales")
+    bufs = [DeviceBuffer.from_numpy(a, stream) for a in (state, gu_svh, down_suh, selected)]
+    d_out = DeviceBuffer(selected.size * hidden * 2)
+    _lib.call("b200exl3_swiglu_down_input", *(c_void_p(b.ptr) for b in bufs), gu_svh.shape[0], selected.size, hidden, c_void_p(d_out.ptr),
+              c_void_p(stream.handle))
+    return d_out.download((selected.size, hidden), np.float16, stream)
+
+
+def finish_and_reduce(state: np.ndarray, svh_rows: np.ndarray, scores: np.ndarray, stream: Stream = DEFAULT_STREAM) -> np.ndarray:
+    """``moe::finish_and_reduce`` (native/src/moe.rs:586-609): raw down products ``[rows * top_k, width]`` fp32, the
+    output scales of every slot ``[rows * top_k, width]`` and ``scores [rows, top_k]`` -> ``[rows, width]``."""
+    state = np.ascontiguousarray(state, np.float32)
+    svh_rows = np.ascontiguousarray(svh_rows, np.float16)
+    scores = np.ascontiguousarray(scores)
+    if scores.dtype not in (np.float16, np.float32) or scores.ndim != 2 or state.shape != svh_rows.shape or state.shape[0] != scores.size:
+        raise B200Exl3Error("invalid expert reduction input")
+    rows, top_k = scores.shape
+    slots, width = state.shape
+    every = np.arange(slots, dtype=np.uint32)                      # each slot has its own row of scales
+    bufs = [DeviceBuffer.from_numpy(a, stream) for a in (state, svh_rows, every, scores)]
+    d_y = DeviceBuffer(rows * width * scores.dtype.itemsize)
+    _lib.call("b200exl3_finish_and_reduce", c_void_p(bufs[0].ptr), c_void_p(bufs[1].ptr), c_void_p(bufs[2].ptr), slots, c_void_p(bufs[3].ptr),
+              F16 if scores.dtype == np.float16 else F32, rows, top_k, width, c_void_p(d_y.ptr), c_void_p(stream.handle))
+    return d_y.download((rows, width), scores.dtype, stream)

@@ -68,3 +68,51 @@ def test_device_operations(gpu):
         assert np.abs(got - want).max() <= 1e-2 * np.abs(want).max()
     assert answers[4] == {"error": "unsupported group"}
     assert answers[5] == {"error": "packed length is not a whole tile"}
+
+
+@pytest.mark.gpu
+def test_expert_stage_operations(gpu):
+    """mlx-expert, mlx-swiglu-prepare and mlx-expert-reduce: the stages of the expert block one by one, in the wire
+    format of native/src/main.rs:540-626, each against the oracle's function for that stage."""
+    rng = np.random.default_rng(3)
+    k, cb, n_in, hidden, experts, slots = 4, 0, 256, 128, 4, 3
+    bits = lambda a: np.ascontiguousarray(a).view(np.uint16).reshape(-1).tolist()  # noqa: E731
+    bank = rng.integers(0, 65536, (n_in // 16, 2 * experts * hidden // 16, 16 * k), dtype=np.uint16)
+    selected = np.array([2, 0, 3], np.uint32)
+    x = rng.standard_normal((slots * 2, n_in)).astype(np.float16)
+    suh = np.where(rng.random((slots * 2, n_in)) > 0.5, -1, 1).astype(np.float16)
+    svh = rng.uniform(0.5, 1.5, (slots * 2, hidden)).astype(np.float16)
+    gu_svh = (rng.uniform(0.5, 1.5, (experts, 2, hidden)) / 16).astype(np.float16)
+    down_suh = np.where(rng.random((experts, hidden)) > 0.5, -1, 1).astype(np.float16)
+    state = (rng.standard_normal((slots * 2, hidden)) * 16).astype(np.float32)
+    raw = rng.standard_normal((slots, 256)).astype(np.float32) * 8
+    red_svh = rng.uniform(0.5, 1.5, (slots, 256)).astype(np.float16)
+    beta = rng.random(slots).astype(np.float16)
+    common = {"k": k, "mode": cb, "cols": hidden, "data": bits(bank), "x": bits(x), "suh": bits(suh), "selected": selected.tolist(),
+              "projections_per_route": 2, "projection_stride_tiles": experts * hidden // 16}
+    answers = run([
+        dict(common, op="mlx-expert", return_raw=True, svh=[]),
+        dict(common, op="mlx-expert", return_raw=False, svh=bits(svh)),
+        {"op": "mlx-swiglu-prepare", "cols": hidden, "state": state.reshape(-1).tolist(), "suh": bits(gu_svh), "svh": bits(down_suh),
+         "selected": selected.tolist()},
+        {"op": "mlx-expert-reduce", "cols": 256, "state": raw.reshape(-1).tolist(), "svh": bits(red_svh), "beta": bits(beta)},
+        dict(common, op="mlx-expert", projections_per_route=0),
+    ])
+    ht = hidden // 16
+    want_raw = np.empty((slots * 2, hidden), np.float32)
+    for slot, e in enumerate(selected):
+        for p in range(2):
+            r = slot * 2 + p
+            c0 = (p * experts + int(e)) * ht
+            want_raw[r] = oracle.matmul_raw(np.ascontiguousarray(bank[:, c0:c0 + ht]), k, cb, oracle.prepare(x[r:r + 1], suh[r]))[0]
+    got_raw = np.asarray(answers[0]["data"]["f32"], np.float32).reshape(slots * 2, hidden)
+    assert np.abs(got_raw - want_raw).max() <= 2e-4 * np.abs(want_raw).max()
+    got = np.asarray(answers[1]["data"]["f16"], np.uint16).view(np.float16).reshape(slots * 2, hidden).astype(np.float32)
+    want = oracle.finish(want_raw, svh, None).astype(np.float32)
+    assert np.abs(got - want).max() <= 1e-2 * np.abs(want).max()
+    want_xd = oracle.glu_down_input(state[0::2], state[1::2], gu_svh[selected, 0], gu_svh[selected, 1], down_suh[selected])
+    got_xd = np.asarray(answers[2]["data"], np.uint16).view(np.float16).reshape(slots, hidden)
+    assert np.abs(got_xd.astype(np.float32) - want_xd.astype(np.float32)).max() <= 1e-2 * np.abs(want_xd.astype(np.float32)).max()
+    want_y = oracle.finish_and_reduce(raw, red_svh, beta.reshape(1, slots), slots)
+    assert answers[3]["data"] == want_y.view(np.uint16).reshape(-1).tolist()           # rotations and fp16 sums are bit-exact
+    assert answers[4] == {"error": "invalid projection count"}
