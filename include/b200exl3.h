@@ -65,6 +65,14 @@ int b200exl3_version(void);
  * epilogue done, end, activation copies issued; 0 = off). */
 int b200exl3_set_option(const char* name, int64_t value);
 
+/* The launch policy as data, for tests and reports (replaces the Kani proofs beside exl3_projection_splits and
+ * qmv_batch_layout, native/src/contracts.rs:1995-2012, 1051-1069, by values an exhaustive test can check; needs no GPU:
+ * without one the planners assume 148 multiprocessors).  kind "qmv": {CTAs, bound on CTAs sharing a column block,
+ * column blocks, warps per CTA, shared memory per CTA, kernel rotates the rows itself}; "qmm": {input splits, token
+ * tiles, small shape, 64-input stages}; "stack": {CTAs, bound on CTAs per block, column blocks, warps per CTA, shared
+ * memory, warps that share the layer, 32-bit partition arithmetic, layer accepted}. */
+int b200exl3_plan_query(const char* kind, int in, int out, int k, int64_t rows, int64_t* out_values, int capacity);
+
 /* Plain device-memory plumbing for hosts that have no CUDA binding of their own (replaces
  * mlxl3_array_from_bytes, mlxl3_array_copy_bytes, mlxl3_array_free and mlxl3_synchronize,
  * native/ffi/mlx_bridge.cpp:337, 610, 233, 192).  Streams are created non-blocking. */

@@ -25,6 +25,7 @@ SIGNATURES = {
     "b200exl3_last_error": (c_char_p, []),
     "b200exl3_version": (c_int, []),
     "b200exl3_set_option": (c_int, [c_char_p, c_int64]),
+    "b200exl3_plan_query": (c_int, [c_char_p, c_int, c_int, c_int, c_int64, POINTER(c_int64), c_int]),
     "b200exl3_malloc": (c_int, [c_size_t, POINTER(c_void_p)]),
     "b200exl3_free": (c_int, [c_void_p]),
     "b200exl3_host_alloc": (c_int, [c_size_t, POINTER(c_void_p)]),

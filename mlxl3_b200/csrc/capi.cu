@@ -159,6 +159,36 @@ int b200exl3_set_option(const char* name, int64_t value) {
     return 0;
 }
 
+/* ---- launch policy, as data (host arithmetic only: needs no GPU) --------------------------------------------------- */
+
+int b200exl3_plan_query(const char* kind, int in, int out, int k, int64_t rows, int64_t* out_values, int capacity) {
+    if (!kind || !out_values || capacity < 8) return fail("plan query needs room for 8 values");
+    if (in <= 0 || out <= 0 || in % 128 || out % 128 || k < 1 || k > 8 || rows <= 0) return fail("invalid plan query");
+    for (int i = 0; i < 8; ++i) out_values[i] = 0;
+    if (!strcmp(kind, "qmv")) {
+        const QmvPlan p = plan_qmv(in, out, k, rows);
+        out_values[0] = p.grid; out_values[1] = p.max_pieces; out_values[2] = p.col_blocks; out_values[3] = kQmvWarps;
+        out_values[4] = static_cast<int64_t>(p.smem_bytes); out_values[5] = p.fused_rotation ? 1 : 0;
+        return 0;
+    }
+    if (!strcmp(kind, "qmm")) {
+        const QmmPlan p = plan_qmm(in, out, rows);
+        out_values[0] = p.splits; out_values[1] = p.token_tiles; out_values[2] = p.small ? 1 : 0; out_values[3] = in / 64;
+        return 0;
+    }
+    if (!strcmp(kind, "stack")) {
+        const StackPlan p = plan_stack(k, static_cast<int>(std::min<int64_t>(rows, kStackMaxRows)), 1);
+        StackOp op{};
+        op.in = in; op.out = out;
+        const bool ok = plan_stack_op(p, op);
+        out_values[0] = p.grid; out_values[1] = ok ? op.max_pieces : 0; out_values[2] = ok ? op.col_blocks : 0; out_values[3] = kStackWarps;
+        out_values[4] = static_cast<int64_t>(p.smem_bytes); out_values[5] = ok ? op.warps : 0; out_values[6] = ok ? op.narrow : 0;
+        out_values[7] = ok ? 1 : 0;
+        return 0;
+    }
+    return fail("unknown plan kind %s", kind);
+}
+
 /* ---- memory / stream plumbing ---------------------------------------------------------------- */
 
 int b200exl3_malloc(size_t bytes, void** out) {
