@@ -71,6 +71,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "=r"(ok) : "r"(smem_addr(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
+// Non-blocking probe of a barrier phase (the answer takes a few hundred cycles: issue it well before it is needed).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok) : "r"(smem_addr(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
 // Bounded wait: gives up after `limit` polls (each poll already blocks for a while in hardware) so a
 // lost copy can never hang the GPU; the caller records the failure and carries on.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int limit = 1 << 20) {

@@ -13,6 +13,27 @@ namespace b200exl3 {
 // planners can be exercised on a machine without a GPU).
 int sm_count();
 
+// True when kernels are launched with programmatic stream serialization (option "pdl"): a kernel may then start while
+// its predecessor in the stream is still running, and must execute griddepcontrol.wait before it touches memory.
+bool pdl_enabled();
+
+// Launch of a small dependent kernel: with "pdl" on, the kernel is allowed to start early (its first statements are
+// pdl_launch_dependents(); pdl_wait();), which hides its launch latency behind the predecessor's tail.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // ---- codec (kernels_codec.cu) ---------------------------------------------------------------------
 cudaError_t launch_unpack_states(const uint16_t* packed, int64_t tiles, int k, int cb, uint16_t* states, __half* values,
                                  cudaStream_t stream);

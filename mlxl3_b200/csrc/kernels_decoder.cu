@@ -30,6 +30,8 @@ __device__ __forceinline__ float warp_sum(float v) {
 // ---- embedding row ----------------------------------------------------------------------------------------
 __global__ void embed_kernel(const __half* __restrict__ table, const int* __restrict__ token, int64_t vocab, int hidden,
                              __half* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
     int64_t id = token[blockIdx.x];
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
     const uint4* src = reinterpret_cast<const uint4*>(table + id * hidden);
@@ -43,6 +45,8 @@ constexpr int kNormThreads = 256;
 __global__ void __launch_bounds__(kNormThreads)
 rms_norm_kernel(const __half* __restrict__ x, const __half* __restrict__ residual, const __half* __restrict__ weight, int n,
                 float eps, __half* __restrict__ sum, __half* __restrict__ y) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ __half s_row[];                    // the (summed) row, kept for the second pass
     __shared__ float s_part[kNormThreads / 32];
     const int64_t base = static_cast<int64_t>(blockIdx.x) * n;
@@ -73,6 +77,8 @@ rms_norm_kernel(const __half* __restrict__ x, const __half* __restrict__ residua
 // ---- SwiGLU --------------------------------------------------------------------------------------------------
 // out = half(half(x * half(sigmoid(x))) * up): the three fp16 operators of the reference's compiled expression.
 __global__ void swiglu_kernel(const __half* __restrict__ gate, const __half* __restrict__ up, int64_t n, __half* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 2;
     if (i >= n) return;
     const __half2 g = *reinterpret_cast<const __half2*>(gate + i);
@@ -88,6 +94,8 @@ __global__ void swiglu_kernel(const __half* __restrict__ gate, const __half* __r
 __global__ void rope_append_kernel(__half* __restrict__ q, const __half* __restrict__ k, const __half* __restrict__ v, int heads,
                                    int kv_heads, int dim, const int* __restrict__ pos_ptr, float log2_theta, int max_ctx,
                                    __half* __restrict__ k_cache, __half* __restrict__ v_cache) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const int head = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (head >= heads + 2 * kv_heads) return;
@@ -133,6 +141,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32)
 attn_partial_kernel(const __half* __restrict__ q, const __half* __restrict__ k_cache, const __half* __restrict__ v_cache,
                     int heads, int kv_heads, const int* __restrict__ pos_ptr, int max_ctx, float scale_log2e,
                     float* __restrict__ part_acc, float2* __restrict__ part_ml) {
+    pdl_launch_dependents();
+    pdl_wait();
     constexpr int GQ = kAttnHeadsPerPass;
     __shared__ float s_acc[kAttnWarps][GQ][kAttnDim];
     __shared__ float s_m[kAttnWarps][GQ], s_l[kAttnWarps][GQ];
@@ -254,6 +264,8 @@ attn_partial_kernel(const __half* __restrict__ q, const __half* __restrict__ k_c
 // one CTA per query head, one thread per dimension: merges the splits in split order and normalises
 __global__ void __launch_bounds__(kAttnDim)
 attn_combine_kernel(const float* __restrict__ part_acc, const float2* __restrict__ part_ml, int splits, __half* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int head = blockIdx.x, d = threadIdx.x;
     float mm = -INFINITY;
     for (int s = 0; s < splits; ++s) mm = fmaxf(mm, part_ml[static_cast<int64_t>(head) * splits + s].x);
@@ -283,6 +295,8 @@ __device__ __forceinline__ bool better(float v, int64_t i, float bv, int64_t bi)
 __global__ void __launch_bounds__(kHeadWarps * 32)
 head_kernel(const __half* __restrict__ x, const __half* __restrict__ w, int64_t vocab, int hidden, int64_t index_offset,
             __half* __restrict__ logits, float* __restrict__ cand_value, long long* __restrict__ cand_index) {
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ __align__(16) __half s_x[];
     __shared__ float s_v[kHeadWarps];
     __shared__ long long s_i[kHeadWarps];
@@ -325,6 +339,8 @@ head_kernel(const __half* __restrict__ x, const __half* __restrict__ w, int64_t 
 __global__ void __launch_bounds__(256)
 argmax_candidates_kernel(const float* __restrict__ cand_value, const long long* __restrict__ cand_index, int n,
                          float* __restrict__ out_value, long long* __restrict__ out_index) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float s_v[256];
     __shared__ long long s_i[256];
     float best_v = -INFINITY;
@@ -346,8 +362,7 @@ argmax_candidates_kernel(const float* __restrict__ cand_value, const long long* 
 // ---- launchers -----------------------------------------------------------------------------------------------------
 
 cudaError_t launch_embed(const __half* table, const int* token, int64_t rows, int64_t vocab, int hidden, __half* out, cudaStream_t stream) {
-    embed_kernel<<<static_cast<unsigned>(rows), 128, 0, stream>>>(table, token, vocab, hidden, out);
-    return cudaGetLastError();
+    return launch_dependent(embed_kernel, dim3(static_cast<unsigned>(rows)), dim3(128), 0, stream, table, token, vocab, hidden, out);
 }
 
 cudaError_t launch_rms_norm(const __half* x, const __half* residual, const __half* weight, int64_t rows, int n, float eps, __half* sum,
@@ -360,21 +375,19 @@ cudaError_t launch_rms_norm(const __half* x, const __half* residual, const __hal
         if (e != cudaSuccess) return e;
         attribute.mark();
     }
-    rms_norm_kernel<<<static_cast<unsigned>(rows), kNormThreads, smem, stream>>>(x, residual, weight, n, eps, sum, y);
-    return cudaGetLastError();
+    return launch_dependent(rms_norm_kernel, dim3(static_cast<unsigned>(rows)), dim3(kNormThreads), smem, stream, x, residual, weight, n, eps, sum, y);
 }
 
 cudaError_t launch_swiglu(const __half* gate, const __half* up, int64_t n, __half* out, cudaStream_t stream) {
     const int64_t threads = (n + 1) / 2;
-    swiglu_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, stream>>>(gate, up, n, out);
-    return cudaGetLastError();
+    return launch_dependent(swiglu_kernel, dim3(static_cast<unsigned>((threads + 255) / 256)), dim3(256), 0, stream, gate, up, n, out);
 }
 
 cudaError_t launch_rope_append(__half* q, const __half* k, const __half* v, int heads, int kv_heads, int dim, const int* pos, float theta,
                                int max_ctx, __half* k_cache, __half* v_cache, cudaStream_t stream) {
     const int total = heads + 2 * kv_heads;
-    rope_append_kernel<<<(total + 3) / 4, 128, 0, stream>>>(q, k, v, heads, kv_heads, dim, pos, log2f(theta), max_ctx, k_cache, v_cache);
-    return cudaGetLastError();
+    return launch_dependent(rope_append_kernel, dim3((total + 3) / 4), dim3(128), 0, stream, q, k, v, heads, kv_heads, dim, pos, log2f(theta), max_ctx,
+                            k_cache, v_cache);
 }
 
 int attention_splits(int kv_heads, int heads) {
@@ -395,12 +408,10 @@ cudaError_t launch_attention_decode(const __half* q, const __half* k_cache, cons
     const int passes = (heads / kv_heads + kAttnHeadsPerPass - 1) / kAttnHeadsPerPass;
     float* part_acc = static_cast<float*>(workspace);
     float2* part_ml = reinterpret_cast<float2*>(part_acc + static_cast<size_t>(heads) * splits * kAttnDim);
-    attn_partial_kernel<<<dim3(splits, kv_heads * passes), kAttnWarps * 32, 0, stream>>>(q, k_cache, v_cache, heads, kv_heads, pos, max_ctx,
-                                                                                        scale * 1.4426950408889634f, part_acc, part_ml);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_dependent(attn_partial_kernel, dim3(splits, kv_heads * passes), dim3(kAttnWarps * 32), 0, stream, q, k_cache, v_cache,
+                                     heads, kv_heads, pos, max_ctx, scale * 1.4426950408889634f, part_acc, part_ml);
     if (e != cudaSuccess) return e;
-    attn_combine_kernel<<<heads, kAttnDim, 0, stream>>>(part_acc, part_ml, splits, out);
-    return cudaGetLastError();
+    return launch_dependent(attn_combine_kernel, dim3(heads), dim3(kAttnDim), 0, stream, part_acc, part_ml, splits, out);
 }
 
 int head_candidates() { return 4 * sm_count(); }
@@ -416,11 +427,10 @@ cudaError_t launch_head_argmax(const __half* x, const __half* w, int64_t vocab, 
         attribute.mark();
     }
     const int grid = head_candidates();
-    head_kernel<<<grid, kHeadWarps * 32, smem, stream>>>(x, w, vocab, hidden, index_offset, logits, cand_value, cand_index);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_dependent(head_kernel, dim3(grid), dim3(kHeadWarps * 32), smem, stream, x, w, vocab, hidden, index_offset, logits,
+                                     cand_value, cand_index);
     if (e != cudaSuccess) return e;
-    argmax_candidates_kernel<<<1, 256, 0, stream>>>(cand_value, cand_index, grid, out_value, out_index);
-    return cudaGetLastError();
+    return launch_dependent(argmax_candidates_kernel, dim3(1), dim3(256), 0, stream, cand_value, cand_index, grid, out_value, out_index);
 }
 
 }  // namespace b200exl3

@@ -25,6 +25,8 @@ static std::atomic<int> g_ctas_per_sm{2};   // CTAs per SM the grid is sized for
 static std::atomic<int> g_force_grid{0};    // > 0 overrides the grid size (tuning and tests)
 static std::atomic<int> g_pdl{0};           // programmatic dependent launch between consecutive layers: 0 off, 1 late trigger, 2 early
 
+bool pdl_enabled() { return g_pdl.load() != 0; }
+
 int sm_count() {
     static std::atomic<int> cached[64];
     int device = 0;

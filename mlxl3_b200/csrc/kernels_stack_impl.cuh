@@ -428,6 +428,7 @@ stack_kernel(const StackArgs a) {
     int slot = 0;
     uint32_t parity = 0;
     bool copy_lost = false;
+    bool ready = false;                           // the barrier of the row consumed next has already been seen complete
 
 #pragma unroll 1
     for (int op = 0; op < a.n_ops; ++op) {
@@ -506,11 +507,14 @@ stack_kernel(const StackArgs a) {
                     if (tracing && first_chunk) stamp[1] = global_ns();
                     const uint32_t* xfrag =
                         reinterpret_cast<const uint32_t*>(xs + min(g, rows - 1) * kXsHalves + (tk0 * 16 - kb0 * 128)) + q;
+                    // The row loop is software-pipelined by hand: while row r is decoded, the activation fragment of row
+                    // r + 1 is already loaded and the barrier of row r + 1 already probed (a probe answers after a few
+                    // hundred cycles), so neither latency sits between two rows.
+                    uint32_t p0 = xfrag[0], p1 = xfrag[4];
 #pragma unroll 1      // measured: unrolling this loop by 2 or 4 rows makes the step 8 % and 13 % slower
                     for (int r = 0; r < nrows; ++r) {
                         const int tk = tk0 + r;
                         uint32_t bx[NB][4];
-                        uint32_t p0 = xfrag[r * 8], p1 = xfrag[r * 8 + 4];
                         if (g >= rows) { p0 = 0; p1 = 0; }
                         if constexpr (MODE == 0) {
                             bx[0][0] = prmt(p0, p0, 0x1010); bx[0][1] = prmt(p0, p0, 0x3232);
@@ -518,7 +522,11 @@ stack_kernel(const StackArgs a) {
                         } else {
                             bx[0][0] = p0; bx[0][1] = p1; bx[0][2] = 0; bx[0][3] = 0;
                         }
-                        if (!mbar_wait(bars + slot, parity)) copy_lost = true;
+                        if (!ready && !mbar_wait(bars + slot, parity)) copy_lost = true;
+                        const int nslot = slot + 1 == DEPTH ? 0 : slot + 1;
+                        const uint32_t nparity = slot + 1 == DEPTH ? parity ^ 1u : parity;
+                        ready = mbar_test_wait(bars + nslot, nparity);
+                        if (r + 1 < nrows) { p0 = xfrag[(r + 1) * 8]; p1 = xfrag[(r + 1) * 8 + 4]; }
                         const uint32_t* row_words = ring + slot * kRowWords;
                         const int lo = tk == tk_first ? lo_first : 0, hi = tk == tk_last ? hi_last : 8;
                         if (lo == 0 && hi == 8) qmv_row<K, CB, NB, MODE, true>(row_words, geom, 0, 8, bx, acc);
@@ -531,7 +539,8 @@ stack_kernel(const StackArgs a) {
                             }
                             cur.next(lite, a.n_ops, wid);
                         }
-                        if (++slot == DEPTH) { slot = 0; parity ^= 1u; }
+                        slot = nslot;
+                        parity = nparity;
                     }
                     tk0 = tk_end;
                 }

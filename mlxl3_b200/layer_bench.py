@@ -32,9 +32,15 @@ def main(argv=None) -> None:
     ap.add_argument("--experts", type=int, default=0,
                     help="> 0: time the grouped-expert SwiGLU block instead (--in = model width, --out = expert width)")
     ap.add_argument("--top-k", type=int, default=8)
+    ap.add_argument("--step-layers", type=int, default=0,
+                    help="> 0: time the persistent decode-step kernel on this many Llama-3-8B-shaped decoder layers "
+                         "([q|k|v], o, [gate|up], down at --k bits, chained), one launch per step")
+    ap.add_argument("--trace", action="store_true", help="with --step-layers: print the per-layer phase stamps of one step")
     args = ap.parse_args(argv)
     if args.experts > 0:
         return moe_main(args)
+    if args.step_layers > 0:
+        return step_main(args)
 
     init(args.device)
     for item in args.option:
@@ -80,6 +86,72 @@ def main(argv=None) -> None:
         "weight_GBps": round(weight_bytes / ms / 1e6, 1),
         "TFLOPs": round(2.0 * args.rows * args.n_in * args.n_out / ms / 1e9, 1),
     }))
+
+
+def step_main(args) -> None:
+    """The decode-step kernel (``Exl3Stack``) on ``--step-layers`` decoder layers of the Llama-3-8B shape, every
+    projection reading the output of the one before it."""
+    from . import Exl3Group, Exl3Stack
+
+    init(args.device)
+    for item in args.option:
+        name, value = item.split("=")
+        set_option(name, int(value))
+    rng = np.random.default_rng(0)
+    hidden, ffn, kv, k = 4096, 14336, 1024, args.k
+
+    def lin(n_in, n_out):
+        trellis = rng.integers(0, 65536, (n_in // 16, n_out // 16, 16 * k), dtype=np.uint16)
+        svh = np.full(n_out, 1.0 / (1.2437 * np.sqrt(n_in)), np.float16)
+        return Exl3Linear(trellis, np.ones(n_in, np.float16), svh, None, k, args.cb, exact_weights=args.exact)
+    stream = Stream()
+    source = DeviceBuffer.from_numpy(rng.standard_normal((1, hidden)).astype(np.float16), stream)
+    ops, names, keep, nbytes = [], [], [], 0
+    for _ in range(args.step_layers):
+        q, kk, v, o, gate, up, down = (DeviceBuffer(n * 2) for n in (hidden, kv, kv, hidden, ffn, ffn, hidden))
+        ops += [(Exl3Group([lin(hidden, hidden), lin(hidden, kv), lin(hidden, kv)]), source.ptr, [q.ptr, kk.ptr, v.ptr]),
+                (lin(hidden, hidden), q.ptr, o.ptr),
+                (Exl3Group([lin(hidden, ffn), lin(hidden, ffn)]), o.ptr, [gate.ptr, up.ptr]),
+                (lin(ffn, hidden), gate.ptr, down.ptr)]
+        names += ["qkv", "o", "gate|up", "down"]
+        nbytes += (hidden * (hidden + 2 * kv) + hidden * hidden + 2 * hidden * ffn + ffn * hidden) * k // 8
+        keep += [q, kk, v, o, gate, up, down]
+        source = down
+    stack = Exl3Stack(ops, F16, 1)
+    grid, smem = stack.geometry()
+    for _ in range(args.warmup):
+        stack.forward(stream)
+    stream.sync()
+    start, stop = Event(), Event()
+    start.record(stream)
+    for _ in range(args.iters):
+        stack.forward(stream)
+    stop.record(stream)
+    ms = start.elapsed_ms(stop) / max(args.iters, 1)
+    if stack.status():
+        raise SystemExit(f"kernel reported status {stack.status()}")
+    print(json.dumps({"step_layers": args.step_layers, "k": k, "grid": grid, "smem_per_cta": smem, "us_per_step": round(ms * 1e3, 2),
+                      "us_per_layer": round(ms * 1e3 / args.step_layers, 2), "weight_GBps": round(nbytes / ms / 1e6, 1)}))
+    if args.trace:
+        slots = 8 + 12                                    # stamps per (layer, CTA): see kStackTraceSlots
+        trace = DeviceBuffer(len(ops) * grid * slots * 8)
+        trace.fill(0, stream)
+        set_option("stack_trace_buffer", trace.ptr)
+        stack.forward(stream)
+        stream.sync()
+        set_option("stack_trace_buffer", 0)
+        t = trace.download((len(ops), grid, slots), np.uint64, stream).astype(np.float64)
+        t0 = t[t > 0].min()
+        end_prev = 0.0
+        for i, name in enumerate(names):
+            s = np.where(t[i] > 0, (t[i] - t0) / 1e3, np.nan)
+            done = s[:, 8:]
+            fin = s[~np.isnan(s[:, 7])]
+            end = float(np.nanmax(fin[:, 7])) if len(fin) else float("nan")
+            print(f"{i:3d} {name:8s} start {end_prev:8.2f} | boundary passed {np.nanmin(s[:, 0]):8.2f} | rotated {np.nanmax(s[:, 1]):8.2f} | "
+                  f"tiles done p50 {np.nanpercentile(done, 50):8.2f} max {np.nanmax(done):8.2f} | last block stored {end:8.2f} | "
+                  f"layer {end - end_prev:6.2f} us")
+            end_prev = end
 
 
 def moe_main(args) -> None:
