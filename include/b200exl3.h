@@ -399,8 +399,8 @@ int b200exl3_tp_status(const b200exl3_tp* handle, int* out_status);
 int b200exl3_tp_reset(b200exl3_tp* handle);
 /* The whole row-parallel layer in one launch: input rotation of this rank's input slice, product, exchange of
  * the partial sums with the other ranks inside the kernel's final reduction, output rotation.  Same result as
- * b200exl3_linear_forward_partial followed by b200exl3_linear_finish_tp.  Batches of more than 16 rows run as
- * several launches. */
+ * b200exl3_linear_forward_partial followed by b200exl3_linear_finish_tp.  Up to 8 rows this is one launch; from 9 rows
+ * on the product runs on the tensor cores with a single input split and the exchange kernel follows it. */
 int b200exl3_linear_forward_tp(const b200exl3_linear* handle, b200exl3_tp* tp, const void* d_x, int x_dtype,
                                int64_t rows, void* d_y, void* d_workspace, size_t workspace_bytes,
                                b200exl3_stream stream);

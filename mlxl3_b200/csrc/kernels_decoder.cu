@@ -341,16 +341,23 @@ argmax_candidates_kernel(const float* __restrict__ cand_value, const long long* 
                          float* __restrict__ out_value, long long* __restrict__ out_index) {
     pdl_launch_dependents();
     pdl_wait();
-    __shared__ float s_v[256];
-    __shared__ long long s_i[256];
+    __shared__ float s_v[8];
+    __shared__ long long s_i[8];
     float best_v = -INFINITY;
     int64_t best_i = INT64_MAX;
     for (int i = threadIdx.x; i < n; i += 256)
         if (better(cand_value[i], cand_index[i], best_v, best_i)) { best_v = cand_value[i]; best_i = cand_index[i]; }
-    s_v[threadIdx.x] = best_v; s_i[threadIdx.x] = best_i;
+    // "better" is a total order on (value, index) pairs, so the reduction tree gives the same winner as a serial scan
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best_v, d);
+        const long long oi = __shfl_xor_sync(0xffffffffu, static_cast<long long>(best_i), d);
+        if (better(ov, oi, best_v, best_i)) { best_v = ov; best_i = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { s_v[threadIdx.x >> 5] = best_v; s_i[threadIdx.x >> 5] = best_i; }
     __syncthreads();
     if (threadIdx.x == 0) {
-        for (int i = 1; i < 256; ++i)
+        for (int i = 1; i < 8; ++i)
             if (better(s_v[i], s_i[i], best_v, best_i)) { best_v = s_v[i]; best_i = s_i[i]; }
         *out_value = best_v;
         *out_index = best_i;

@@ -35,12 +35,17 @@ def main(argv=None) -> None:
     ap.add_argument("--step-layers", type=int, default=0,
                     help="> 0: time the persistent decode-step kernel on this many Llama-3-8B-shaped decoder layers "
                          "([q|k|v], o, [gate|up], down at --k bits, chained), one launch per step")
+    ap.add_argument("--decoder-layers", type=int, default=0,
+                    help="> 0: time one decode step of a Llama-3-8B-shaped dense decoder with this many layers at --context keys")
+    ap.add_argument("--context", type=int, default=2048)
     ap.add_argument("--trace", action="store_true", help="with --step-layers: print the per-layer phase stamps of one step")
     args = ap.parse_args(argv)
     if args.experts > 0:
         return moe_main(args)
     if args.step_layers > 0:
         return step_main(args)
+    if args.decoder_layers > 0:
+        return decoder_main(args)
 
     init(args.device)
     for item in args.option:
@@ -152,6 +157,35 @@ def step_main(args) -> None:
                   f"tiles done p50 {np.nanpercentile(done, 50):8.2f} max {np.nanmax(done):8.2f} | last block stored {end:8.2f} | "
                   f"layer {end - end_prev:6.2f} us")
             end_prev = end
+
+
+def decoder_main(args) -> None:
+    """One decode step of ``DenseDecoder`` (embedding, blocks, final norm, fp16 head, arg-max) with synthetic weights."""
+    from .decoder import DecoderConfig, DenseDecoder, SyntheticWeights
+
+    init(args.device)
+    for item in args.option:
+        name, value = item.split("=")
+        set_option(name, int(value))
+    config = DecoderConfig(layers=args.decoder_layers, k_bits=args.k, codebook=args.cb, max_ctx=args.context)
+    model = DenseDecoder(config, SyntheticWeights(config, seed=1))
+    model.fill_cache(args.context - 1)
+    model.set_input(17, args.context - 1)
+    if not args.no_graph:
+        model.record()
+    for _ in range(args.warmup):
+        model.step()
+    model.stream.sync()
+    start, stop = Event(), Event()
+    start.record(model.stream)
+    for _ in range(args.iters):
+        model.step()
+    stop.record(model.stream)
+    ms = start.elapsed_ms(stop) / max(args.iters, 1)
+    value, index = model.result()
+    print(json.dumps({"decoder_layers": args.decoder_layers, "context": args.context, "k": args.k, "ms_per_token": round(ms, 4),
+                      "launches_per_token": model.launches_per_step, "bytes_per_token": config.bytes_per_token(args.context),
+                      "GBps": round(config.bytes_per_token(args.context) / ms / 1e6, 1), "argmax": index, "finite": bool(np.isfinite(value))}))
 
 
 def moe_main(args) -> None:
