@@ -238,6 +238,41 @@ int b200exl3_moe_forward(const b200exl3_moe* handle, const void* d_x, int x_dtyp
                          const uint32_t* d_selected, const void* d_scores, int score_dtype, void* d_y,
                          void* d_workspace, size_t workspace_bytes, b200exl3_stream stream);
 
+/* ---- layers with a fused prologue (fp16, 1 or 2 rows: decode) ---------------------------------------------------
+ * The reference fuses the operators around a projection into its prologue kernels where dispatch count matters
+ * (flash_up_finish_swiglu_prepare and its neighbours, native/shaders/exl3.metal:240-291).  Here the layer kernel's own
+ * input rotation takes the operator in front of it:
+ *   kind 1  RMSNorm: s = half(x + aux) (aux = residual rows or NULL), input = weight * half(s * rsqrt(mean(s^2) + eps));
+ *           s is also stored to d_sum when that is not NULL (it must not be x: other warps still read x);
+ *   kind 2  SwiGLU: input = half(half(x * half(sigmoid(x))) * aux), x = gate rows, aux = up rows.
+ * Same arithmetic as b200exl3_rms_norm / b200exl3_swiglu followed by the plain forward; the row sum of the norm is added
+ * in another order, so the last fp32 bit of 1/rms may differ from the stand-alone kernel's.  Kind 1 makes every warp
+ * add up the whole row; the cheaper pairing is the residual EPILOGUE of the layer before (which already holds each
+ * output block in registers) with a kind-3 prologue. */
+typedef struct {
+    int kind;
+    const uint16_t* d_aux;
+    const uint16_t* d_weight;
+    uint16_t* d_sum;
+    float eps;
+    /* kind 3: RMSNorm of x whose sums of squares per 128-block, [rows, in / 128] fp32, were left in d_sumsq by the
+     * residual epilogue of the layer before (d_weight and eps as for kind 1; no residual, nothing stored) */
+    const float* d_sumsq;
+    /* epilogue (plain layers only; 0 = none): 1 = the layer's output is added to the residual rows d_residual [rows,
+     * out], the sum is stored to d_residual_out (may be d_residual itself) instead of d_y, and the sum of its squares
+     * over every 128-block to d_sumsq_out [rows, out / 128] -- what the next layer's kind-3 prologue reads */
+    int epilogue;
+    const uint16_t* d_residual;
+    uint16_t* d_residual_out;
+    float* d_sumsq_out;
+} b200exl3_prologue;
+typedef struct b200exl3_tp b200exl3_tp;
+int b200exl3_linear_forward_fused(const b200exl3_linear* handle, const b200exl3_prologue* prologue, b200exl3_tp* tp_or_null,
+                                  const void* d_x_f16, int64_t rows, void* d_y_f16, void* d_workspace, size_t workspace_bytes,
+                                  b200exl3_stream stream);
+int b200exl3_group_forward_fused(const b200exl3_group* handle, const b200exl3_prologue* prologue, const void* d_x_f16, int64_t rows,
+                                 void* const* d_ys_f16, void* d_workspace, size_t workspace_bytes, b200exl3_stream stream);
+
 /* ---- a decode step as ONE launch -------------------------------------------------------------------------------
  * Replaces the reference's recorded decode step (mlxl3_replay_capture / mlxl3_replay_apply,
  * native/ffi/mlx_bridge.cpp:150-175): `count` (1..256) layers (Exl3Linear or Exl3Group), each with its input and output
@@ -255,7 +290,6 @@ int b200exl3_moe_forward(const b200exl3_moe* handle, const void* d_x, int x_dtyp
  *     after a non-zero status call b200exl3_stack_reset before the next forward;
  *   - one forward at a time per object (calls on one stream, or otherwise ordered). */
 typedef struct b200exl3_stack b200exl3_stack;
-typedef struct b200exl3_tp b200exl3_tp;
 typedef struct {
     const b200exl3_linear* linear;   /* exactly one of linear and group */
     const b200exl3_group* group;

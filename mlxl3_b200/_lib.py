@@ -69,6 +69,8 @@ SIGNATURES = {
     "b200exl3_group_count": (c_int, [c_void_p]),
     "b200exl3_group_workspace_bytes": (c_int, [c_void_p, c_int64, POINTER(c_size_t)]),
     "b200exl3_group_forward": (c_int, [c_void_p, c_void_p, c_int, c_int64, POINTER(c_void_p), c_void_p, c_size_t, c_void_p]),
+    "b200exl3_linear_forward_fused": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "b200exl3_group_forward_fused": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, POINTER(c_void_p), c_void_p, c_size_t, c_void_p]),
     "b200exl3_stack_create": (c_int, [c_void_p, c_int, c_int, c_int64, POINTER(c_void_p)]),
     "b200exl3_stack_free": (None, [c_void_p]),
     "b200exl3_stack_forward": (c_int, [c_void_p, c_void_p]),

@@ -414,7 +414,7 @@ static TpPeers tp_peers(const b200exl3_tp* tp);
 
 static int forward_common(const LayerCore& c, const void* d_x, int x_dtype, const uint16_t* d_xhat, int64_t rows,
                           void* const* ys, float* d_yhat, void* ws, size_t ws_bytes, cudaStream_t stream,
-                          const b200exl3_tp* tp = nullptr) {
+                          const b200exl3_tp* tp = nullptr, const b200exl3_prologue* pro = nullptr) {
     if (rows <= 0) return fail("EXL3 linear input cannot be empty");
     size_t need = 0;
     if (core_workspace_bytes(c, rows, &need)) return -1;
@@ -491,6 +491,20 @@ static int forward_common(const LayerCore& c, const void* d_x, int x_dtype, cons
         a.y_dtype = x_dtype;
         a.in = c.in; a.out = c.out; a.rows = static_cast<int>(n);
         if (tp) { a.tp = tp_peers(tp); a.tp_row0 = static_cast<int>(r0); }
+        if (pro && pro->kind != 0) {
+            a.prologue = pro->kind;
+            a.pro_aux = reinterpret_cast<const __half*>(pro->d_aux);
+            a.pro_weight = reinterpret_cast<const __half*>(pro->d_weight);
+            a.pro_sum = reinterpret_cast<__half*>(pro->d_sum);
+            a.pro_eps = pro->eps;
+            a.pro_sumsq = pro->d_sumsq;
+        }
+        if (pro && pro->epilogue == 1) {
+            a.epilogue = 1;
+            a.epi_residual = reinterpret_cast<const __half*>(pro->d_residual);
+            a.epi_sum = reinterpret_cast<__half*>(pro->d_residual_out);
+            a.epi_sumsq = pro->d_sumsq_out;
+        }
         B200_TRY(launch_qmv(a, c.k, c.cb, exact, plan, stream), "fused linear kernel");
     }
     return 0;
@@ -546,6 +560,32 @@ int b200exl3_linear_decode(const b200exl3_linear* h, uint16_t* d_w, b200exl3_str
     if (!d_w || !aligned16(d_w)) return fail("device pointers must be 16-byte aligned");
     return check(launch_reconstruct_quads(h->c.wq, h->c.in / 16, h->c.out / 16, h->c.k, h->c.cb, reinterpret_cast<__half*>(d_w),
                                           as_stream(s)), "reconstruct");
+}
+
+static int check_prologue(const b200exl3_prologue* pro, const void* d_x, int64_t rows) {
+    if (!pro) return fail("NULL argument");
+    if (rows < 1 || rows > kQmvFusedRows) return fail("a fused prologue takes 1 or %d rows, got %lld", kQmvFusedRows, static_cast<long long>(rows));
+    if (pro->kind < 0 || pro->kind > 3) return fail("unknown prologue kind %d", pro->kind);
+    if ((pro->kind == 1 || pro->kind == 3) && (!pro->d_weight || !(pro->eps >= 0.0f)))
+        return fail("the RMSNorm prologue needs a weight and a non-negative epsilon");
+    if (pro->kind == 3 && !pro->d_sumsq) return fail("the RMSNorm prologue of kind 3 needs the block sums of squares");
+    if (pro->epilogue < 0 || pro->epilogue > 1) return fail("unknown epilogue kind %d", pro->epilogue);
+    if (pro->epilogue == 1 && (!pro->d_residual || !pro->d_residual_out || !pro->d_sumsq_out)) return fail("the residual epilogue needs its three buffers");
+    if (!aligned16(pro->d_residual) || !aligned16(pro->d_residual_out)) return fail("device pointers must be 16-byte aligned");
+    if (pro->kind == 1 && pro->d_sum == d_x) return fail("the RMSNorm prologue cannot store the sum over its own input");
+    if (pro->kind == 2 && !pro->d_aux) return fail("the SwiGLU prologue needs the up rows");
+    if (!aligned16(pro->d_aux) || !aligned16(pro->d_weight) || !aligned16(pro->d_sum)) return fail("device pointers must be 16-byte aligned");
+    return 0;
+}
+
+int b200exl3_linear_forward_fused(const b200exl3_linear* h, const b200exl3_prologue* pro, b200exl3_tp* tp, const void* d_x, int64_t rows,
+                                  void* d_y, void* ws, size_t ws_bytes, b200exl3_stream s) {
+    if (!h) return fail("NULL handle");
+    if (!d_x || (!d_y && !(pro && pro->epilogue == 1))) return fail("NULL buffer");
+    if (check_prologue(pro, d_x, rows)) return -1;
+    if (tp && rows * (h->c.out / 128) > tp->max_units) return fail("units exceed the exchange buffers' %d", tp->max_units);
+    void* ys[1] = {d_y};
+    return forward_common(h->c, d_x, kF16, nullptr, rows, ys, nullptr, ws, ws_bytes, as_stream(s), tp, pro);
 }
 
 /* ---- allocation-free forward ------------------------------------------------------------------- */
@@ -694,6 +734,17 @@ int b200exl3_group_forward(const b200exl3_group* h, const void* d_x, int x_dtype
     for (int g = 0; g < h->c.groups; ++g)
         if (!d_ys[g]) return fail("NULL buffer");
     return forward_common(h->c, d_x, x_dtype, nullptr, rows, d_ys, nullptr, ws, ws_bytes, as_stream(s));
+}
+
+int b200exl3_group_forward_fused(const b200exl3_group* h, const b200exl3_prologue* pro, const void* d_x, int64_t rows, void* const* d_ys,
+                                 void* ws, size_t ws_bytes, b200exl3_stream s) {
+    if (!h) return fail("NULL handle");
+    if (!d_x || !d_ys) return fail("NULL buffer");
+    for (int g = 0; g < h->c.groups; ++g)
+        if (!d_ys[g]) return fail("NULL buffer");
+    if (check_prologue(pro, d_x, rows)) return -1;
+    if (pro->epilogue != 0) return fail("the residual epilogue belongs to plain layers");
+    return forward_common(h->c, d_x, kF16, nullptr, rows, d_ys, nullptr, ws, ws_bytes, as_stream(s), nullptr, pro);
 }
 
 /* ---- a decode step as one persistent launch ----------------------------------------------------------------- */

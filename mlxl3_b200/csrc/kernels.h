@@ -93,6 +93,23 @@ struct QmvArgs {
     const int* map_count;      // optional: number of slots in use; the blocks of later slots are skipped
     int map_blocks, map_proj, map_stride_blocks, map_experts;
     int map_top_k;             // with xhat == nullptr: slot s reads row s / map_top_k of x and rotates it with suh[expert, projection]
+    // Fused prologue (fp16 rows, the kernel rotates the rows itself): 0 none; 1 RMSNorm of x (+ residual `pro_aux`) with
+    // weight `pro_weight`, the sum stored to `pro_sum` (a buffer other than x) by the warps of the first column block;
+    // 2 SwiGLU: the input is swiglu(x, pro_aux).
+    // 3 RMSNorm of x whose per-128-block sums of squares `pro_sumsq` [rows, in / 128] were left by the layer before.
+    int prologue;
+    const __half* pro_aux;
+    const __half* pro_weight;
+    __half* pro_sum;
+    const float* pro_sumsq;
+    float pro_eps;
+    // Fused epilogue (plain fp16 layer): 1 = the output is added to the residual rows `epi_residual` [rows, out]; the sum
+    // goes to `epi_sum` (may be the residual buffer itself: a column block is read and written by one warp only) and the
+    // sum of its squares over each 128-block to `epi_sumsq` [rows, out / 128] for the next layer's RMSNorm.
+    int epilogue;
+    const __half* epi_residual;
+    __half* epi_sum;
+    float* epi_sumsq;
     // Tensor-parallel row shard (tp.world > 0; rotated output): the complete sum of a column block is
     // exchanged with the other ranks (unit = (tp_row0 + row) * out/128 + block) before the output rotation.
     TpPeers tp;

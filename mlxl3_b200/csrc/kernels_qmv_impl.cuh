@@ -126,6 +126,88 @@ __device__ __forceinline__ void qmv_rotate_chunk(const void* x, int x_dtype, con
     __syncwarp();
 }
 
+// 1 / rms of every row of x (+ residual), for the fused RMSNorm prologue: every warp adds the whole row in the same
+// fixed order (lane partial sums over 8-element groups, then a shuffle tree), so all warps of the grid get the same bits.
+__device__ __forceinline__ void qmv_row_inv_rms(const __half* x, const __half* residual, int in, int rows, float eps, int lane,
+                                                float (&inv)[kQmvFusedRows]) {
+#pragma unroll
+    for (int row = 0; row < kQmvFusedRows; ++row) {
+        inv[row] = 0.0f;
+        if (row < rows) {
+            float acc = 0.0f;
+            for (int i = lane * 8; i < in; i += 256) {
+                const uint4 xv = __ldcg(reinterpret_cast<const uint4*>(x + static_cast<int64_t>(row) * in + i));
+                const __half2* xh = reinterpret_cast<const __half2*>(&xv);
+                uint4 rv = make_uint4(0, 0, 0, 0);
+                if (residual != nullptr) rv = __ldcg(reinterpret_cast<const uint4*>(residual + static_cast<int64_t>(row) * in + i));
+                const __half2* rh = reinterpret_cast<const __half2*>(&rv);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 f = __half22float2(residual != nullptr ? __hadd2_rn(xh[j], rh[j]) : xh[j]);
+                    acc = fmaf(f.x, f.x, acc);
+                    acc = fmaf(f.y, f.y, acc);
+                }
+            }
+#pragma unroll
+            for (int d = 16; d >= 1; d >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
+            inv[row] = rsqrtf(acc / static_cast<float>(in) + eps);
+        }
+    }
+}
+
+// qmv_rotate_chunk with a fused prologue in front of the input scales: RMSNorm (after an optional residual add) or SwiGLU.
+__device__ __forceinline__ void qmv_rotate_chunk_fused(const QmvArgs& p, const __half* suh, const float (&inv)[kQmvFusedRows], int rows, int kb0,
+                                                       int nblk, bool store_sum, __half* xs, int lane) {
+    constexpr int kXsHalves = kQmvXBlocks * 128;
+    const __half* x = reinterpret_cast<const __half*>(p.x);
+#pragma unroll 1
+    for (int row = 0; row < rows; ++row) {
+#pragma unroll 1
+        for (int blk = 0; blk < nblk; ++blk) {
+            const int col = (kb0 + blk) * 128 + lane * 4;
+            const int64_t at = static_cast<int64_t>(row) * p.in + col;
+            const uint2 xv = __ldcg(reinterpret_cast<const uint2*>(x + at));
+            const uint2 sv = *reinterpret_cast<const uint2*>(suh + col);
+            const __half2* xh = reinterpret_cast<const __half2*>(&xv);
+            __align__(8) __half2 v[2];
+            if (p.prologue == 1 || p.prologue == 3) {
+                const uint2 wv = *reinterpret_cast<const uint2*>(p.pro_weight + col);
+                const __half2* wh = reinterpret_cast<const __half2*>(&wv);
+                __half2 s0 = xh[0], s1 = xh[1];
+                if (p.prologue == 1 && p.pro_aux != nullptr) {
+                    const uint2 rv = __ldcg(reinterpret_cast<const uint2*>(p.pro_aux + at));
+                    const __half2* rh = reinterpret_cast<const __half2*>(&rv);
+                    s0 = __hadd2_rn(s0, rh[0]);
+                    s1 = __hadd2_rn(s1, rh[1]);
+                }
+                if (p.prologue == 1 && store_sum && p.pro_sum != nullptr) {
+                    __align__(8) __half2 keep[2] = {s0, s1};
+                    *reinterpret_cast<uint2*>(p.pro_sum + at) = *reinterpret_cast<const uint2*>(keep);
+                }
+                const float2 f0 = __half22float2(s0), f1 = __half22float2(s1);
+                v[0] = __hmul2_rn(wh[0], __floats2half2_rn(f0.x * inv[row], f0.y * inv[row]));
+                v[1] = __hmul2_rn(wh[1], __floats2half2_rn(f1.x * inv[row], f1.y * inv[row]));
+            } else {
+                const uint2 uv = __ldcg(reinterpret_cast<const uint2*>(p.pro_aux + at));
+                const __half2* uh = reinterpret_cast<const __half2*>(&uv);
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const float2 f = __half22float2(xh[j]);
+                    const __half2 sg = __floats2half2_rn(1.0f / (1.0f + expf(-f.x)), 1.0f / (1.0f + expf(-f.y)));
+                    v[j] = __hmul2_rn(__hmul2_rn(xh[j], sg), uh[j]);
+                }
+            }
+            const __half2* sh = reinterpret_cast<const __half2*>(&sv);
+            __align__(8) __half h[4];
+            *reinterpret_cast<__half2*>(h) = __hmul2_rn(v[0], sh[0]);
+            *reinterpret_cast<__half2*>(h + 2) = __hmul2_rn(v[1], sh[1]);
+            warp_hadamard128_f16(h, lane);
+            *reinterpret_cast<uint2*>(xs + row * kXsHalves + blk * 128 + lane * 4) = *reinterpret_cast<uint2*>(h);
+        }
+    }
+    __syncwarp();
+}
+
 // The last warp of a CTA to stage its tile of column block `cblock`: adds the tiles of the warps that
 // had work in the block (warp_mask) in warp order; if other CTAs share the block, publishes the
 // sum as this CTA's piece and counts arrivals; the last CTA adds the pieces in piece order.  Whoever
@@ -196,6 +278,27 @@ __device__ __forceinline__ void qmv_finish_block(const QmvArgs& p, int cblock, u
                 warp_hadamard128_f16(h, lane);
                 __align__(8) __half sv[4];
                 *reinterpret_cast<uint2*>(sv) = *reinterpret_cast<const uint2*>(p.svh + col);
+                if (p.epilogue == 1) {
+                    // residual add and the block's sum of squares for the next RMSNorm (fixed shuffle order)
+                    const int64_t at = static_cast<int64_t>(row) * p.out + col;
+                    const uint2 rv = __ldcg(reinterpret_cast<const uint2*>(p.epi_residual + at));
+                    const __half* rh = reinterpret_cast<const __half*>(&rv);
+                    __align__(8) __half sum[4];
+                    float sq = 0.0f;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        __half y = __hmul_rn(h[j], sv[j]);
+                        if (p.bias) y = __hadd_rn(y, p.bias[col + j]);
+                        sum[j] = __hadd_rn(rh[j], y);
+                        const float f = __half2float(sum[j]);
+                        sq = fmaf(f, f, sq);
+                    }
+                    *reinterpret_cast<uint2*>(p.epi_sum + at) = *reinterpret_cast<const uint2*>(sum);
+#pragma unroll
+                    for (int d = 16; d >= 1; d >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, d);
+                    if (lane == 0) p.epi_sumsq[row * (p.out >> 7) + cblock] = sq;
+                    continue;
+                }
                 const int grp = qmv_group_of(p, cblock);
                 const int gcol = col - p.gcol0[grp];
 #pragma unroll
@@ -273,6 +376,8 @@ qmv_kernel(const QmvArgs p) {
     uint32_t parity = 0;
     bool copy_lost = false;
     bool first_chunk = true;
+    bool have_inv = false;                       // fused RMSNorm prologue: the rows' 1 / rms, computed once per warp
+    float inv_rms[kQmvFusedRows] = {};
 
     for (int cblock = w0 / UB; cblock * UB < w1; ++cblock) {
         // ---- this warp's segment [u0, u1) of the block ----------------------------------------------------
@@ -348,9 +453,31 @@ qmv_kernel(const QmvArgs p) {
                 }
 
                 // ---- phase 1: rotate this chunk's activations into the warp's shared memory ------------
-                if (p.xhat == nullptr)
-                    qmv_rotate_chunk(x_rows, p.x_dtype, p.suh + suh_row * p.in, p.in, rows, kb0,
-                                     ((tk_end - 1) >> 3) - kb0 + 1, xs, lane);
+                if (p.xhat == nullptr) {
+                    if (p.prologue != 0) {
+                        if (!have_inv && p.prologue == 1) {
+                            qmv_row_inv_rms(reinterpret_cast<const __half*>(p.x), p.pro_aux, p.in, rows, p.pro_eps, lane, inv_rms);
+                            have_inv = true;
+                        }
+                        if (!have_inv && p.prologue == 3) {
+                            // the layer before left the sum of squares of every 128-block: add them in a fixed order
+#pragma unroll
+                            for (int row = 0; row < kQmvFusedRows; ++row)
+                                if (row < rows) {
+                                    float acc = 0.0f;
+                                    for (int b = lane; b < (p.in >> 7); b += 32) acc += __ldcg(p.pro_sumsq + row * (p.in >> 7) + b);
+#pragma unroll
+                                    for (int d = 16; d >= 1; d >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
+                                    inv_rms[row] = rsqrtf(acc / static_cast<float>(p.in) + p.pro_eps);
+                                }
+                            have_inv = true;
+                        }
+                        qmv_rotate_chunk_fused(p, p.suh + suh_row * p.in, inv_rms, rows, kb0, ((tk_end - 1) >> 3) - kb0 + 1, cblock == 0, xs, lane);
+                    } else {
+                        qmv_rotate_chunk(x_rows, p.x_dtype, p.suh + suh_row * p.in, p.in, rows, kb0,
+                                         ((tk_end - 1) >> 3) - kb0 + 1, xs, lane);
+                    }
+                }
                 if (tracing && tk0 == tk_first) p.trace[blockIdx.x * 8 + 2] = global_ns();
 
                 // ---- phase 2: decode x activations ----------------------------------------------------------

@@ -15,7 +15,7 @@ import numpy as np
 
 from . import _lib
 from ._lib import F16
-from .linear import Exl3Group, Exl3Linear, new_workspace
+from .linear import Exl3Group, Exl3Linear, Prologue, new_workspace
 from .runtime import DEFAULT_STREAM, DeviceBuffer, Graph, Stream
 
 
@@ -173,8 +173,9 @@ class DenseDecoder:
         qd, kvd = self.heads * c.head_dim, self.kv_heads * c.head_dim
         self.buf = {name: DeviceBuffer(n * 2) for name, n in (("h", c.hidden), ("xn", c.hidden), ("q", qd), ("k", kvd), ("v", kvd), ("att", qd),
                                                                ("o", c.hidden), ("gate", self.ffn), ("up", self.ffn), ("act", self.ffn),
-                                                               ("down", c.hidden), ("logits", self.vocab))}
+                                                               ("down", c.hidden), ("logits", self.vocab), ("h2", c.hidden))}
         self.d_token, self.d_pos = DeviceBuffer(16), DeviceBuffer(16)
+        self.sumsq = DeviceBuffer(max(c.hidden // 128, 4) * 4)      # sums of squares of the residual row per 128-block
         self.d_best_value, self.d_best_index = DeviceBuffer(16), DeviceBuffer(16)
         ops = [e[n] for e in self.layers for n in ("qkv", "o", "gu", "down")]
         self.ws = new_workspace(max(op.workspace_bytes(1) for op in ops))
@@ -182,6 +183,8 @@ class DenseDecoder:
         self.head_ws = DeviceBuffer(head_workspace_bytes())
         self.graph = None
         self.store_logits = False
+        self.fused = True            # norms, residual adds and SwiGLU run inside the projections' kernels; False: as kernels of their own
+        self.hidden_name = "h"       # buffer that holds the residual stream after a step
         self.launches_per_step = 0
 
     def set_input(self, token: int, pos: int) -> None:
@@ -206,6 +209,8 @@ class DenseDecoder:
             op.forward_device(d_x, F16, 1, d_y, self.ws, self.stream)
 
     def _launch(self) -> None:
+        if self.fused:
+            return self._launch_fused()
         c, b, s = self.config, self.buf, self.stream
         count = 0
         embed(self.embed_table.ptr, self.d_token.ptr, 1, c.vocab, c.hidden, b["h"].ptr, s)
@@ -223,11 +228,38 @@ class DenseDecoder:
             swiglu(b["gate"].ptr, b["up"].ptr, self.ffn, b["act"].ptr, s)
             self._row(e["down"], b["act"].ptr, b["down"].ptr)
             pending = b["down"].ptr
-            count += 11
+            count += 10
         rms_norm(b["h"].ptr, pending, self.final_norm.ptr, 1, c.hidden, c.eps, b["h"].ptr, b["xn"].ptr, s)
         head_argmax(b["xn"].ptr, self.head_weight.ptr, self.vocab, c.hidden, self.rank * self.vocab, b["logits"].ptr if self.store_logits else 0,
                     self.d_best_value.ptr, self.d_best_index.ptr, self.head_ws, s)
         self.launches_per_step = count + 4
+
+    def _launch_fused(self) -> None:
+        """The same step with the glue folded into the projections' kernels: the residual add runs in the epilogue of
+        o and down (which hold every output block in registers) and leaves the sum of squares of each 128-block, the
+        RMSNorm of the next projection is its input-rotation prologue (it only adds those block sums), and SwiGLU is the
+        prologue of down.  7 launches per block instead of 10."""
+        c, b, s = self.config, self.buf, self.stream
+        h, sq = b["h"].ptr, self.sumsq.ptr
+        embed(self.embed_table.ptr, self.d_token.ptr, 1, c.vocab, c.hidden, h, s)
+        first = True
+        for e in self.layers:
+            pro = Prologue.rms_norm(e["attn_norm"].ptr, c.eps) if first else Prologue.rms_norm_from_blocks(e["attn_norm"].ptr, c.eps, sq)
+            first = False
+            e["qkv"].forward_fused_device(pro, h, 1, [b["q"].ptr, b["k"].ptr, b["v"].ptr], self.ws, s)
+            rope_append(b["q"].ptr, b["k"].ptr, b["v"].ptr, self.heads, self.kv_heads, c.head_dim, self.d_pos.ptr, c.theta, c.max_ctx,
+                        e["k_cache"].ptr, e["v_cache"].ptr, s)
+            attention_decode(b["q"].ptr, e["k_cache"].ptr, e["v_cache"].ptr, self.heads, self.kv_heads, c.head_dim, self.d_pos.ptr, c.max_ctx,
+                             c.head_dim ** -0.5, b["att"].ptr, self.attn_ws, s)
+            e["o"].forward_fused_device(Prologue.plain().with_residual(h, h, sq), b["att"].ptr, 1, 0, self.ws, s, tp=self.tp)
+            e["gu"].forward_fused_device(Prologue.rms_norm_from_blocks(e["mlp_norm"].ptr, c.eps, sq), h, 1, [b["gate"].ptr, b["up"].ptr],
+                                         self.ws, s)
+            e["down"].forward_fused_device(Prologue.swiglu(b["up"].ptr).with_residual(h, h, sq), b["gate"].ptr, 1, 0, self.ws, s, tp=self.tp)
+        rms_norm(h, 0, self.final_norm.ptr, 1, c.hidden, c.eps, 0, b["xn"].ptr, s)
+        self.hidden_name = "h"
+        head_argmax(b["xn"].ptr, self.head_weight.ptr, self.vocab, c.hidden, self.rank * self.vocab, b["logits"].ptr if self.store_logits else 0,
+                    self.d_best_value.ptr, self.d_best_index.ptr, self.head_ws, s)
+        self.launches_per_step = 7 * len(self.layers) + 4
 
     def record(self) -> None:
         self._launch()                                  # every distinct call once before recording

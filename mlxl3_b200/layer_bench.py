@@ -38,6 +38,7 @@ def main(argv=None) -> None:
     ap.add_argument("--decoder-layers", type=int, default=0,
                     help="> 0: time one decode step of a Llama-3-8B-shaped dense decoder with this many layers at --context keys")
     ap.add_argument("--context", type=int, default=2048)
+    ap.add_argument("--unfused", action="store_true", help="with --decoder-layers: norms and SwiGLU as kernels of their own")
     ap.add_argument("--trace", action="store_true", help="with --step-layers: print the per-layer phase stamps of one step")
     args = ap.parse_args(argv)
     if args.experts > 0:
@@ -169,6 +170,7 @@ def decoder_main(args) -> None:
         set_option(name, int(value))
     config = DecoderConfig(layers=args.decoder_layers, k_bits=args.k, codebook=args.cb, max_ctx=args.context)
     model = DenseDecoder(config, SyntheticWeights(config, seed=1))
+    model.fused = not args.unfused
     model.fill_cache(args.context - 1)
     model.set_input(17, args.context - 1)
     if not args.no_graph:

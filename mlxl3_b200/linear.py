@@ -8,6 +8,7 @@ runs in the CUDA library; there is no CPU path.
 """
 from __future__ import annotations
 
+import ctypes
 from ctypes import byref, c_size_t, c_void_p
 
 import numpy as np
@@ -69,6 +70,37 @@ def static_status(clear: bool = False) -> int:
     out = c_int()
     _lib.call("b200exl3_static_status", byref(out), 1 if clear else 0)
     return out.value
+
+
+class Prologue(ctypes.Structure):
+    """``b200exl3_prologue``: the operators fused in front of a layer's input rotation and behind its output rotation
+    (fp16, 1 or 2 rows)."""
+    _fields_ = [("kind", ctypes.c_int), ("d_aux", c_void_p), ("d_weight", c_void_p), ("d_sum", c_void_p), ("eps", ctypes.c_float),
+                ("d_sumsq", c_void_p), ("epilogue", ctypes.c_int), ("d_residual", c_void_p), ("d_residual_out", c_void_p),
+                ("d_sumsq_out", c_void_p)]
+
+    @classmethod
+    def rms_norm(cls, d_weight: int, eps: float, d_residual: int = 0, d_sum: int = 0) -> "Prologue":
+        """Every warp adds up the whole row (+ residual) itself."""
+        return cls(1, d_residual or None, d_weight, d_sum or None, eps)
+
+    @classmethod
+    def rms_norm_from_blocks(cls, d_weight: int, eps: float, d_sumsq: int) -> "Prologue":
+        """The row's sums of squares per 128-block were left by the residual epilogue of the layer before."""
+        return cls(3, None, d_weight, None, eps, d_sumsq)
+
+    @classmethod
+    def swiglu(cls, d_up: int) -> "Prologue":
+        return cls(2, d_up, None, None, 0.0)
+
+    @classmethod
+    def plain(cls) -> "Prologue":
+        return cls(0)
+
+    def with_residual(self, d_residual: int, d_residual_out: int, d_sumsq_out: int) -> "Prologue":
+        """Adds the residual epilogue: output + residual -> d_residual_out, block sums of squares -> d_sumsq_out."""
+        self.epilogue, self.d_residual, self.d_residual_out, self.d_sumsq_out = 1, d_residual, d_residual_out, d_sumsq_out
+        return self
 
 
 class Exl3Linear:
@@ -170,6 +202,13 @@ class Exl3Linear:
         _lib.call("b200exl3_linear_forward", c_void_p(self.handle), c_void_p(d_x), dtype, rows, c_void_p(d_y),
                   c_void_p(workspace.ptr), workspace.nbytes, c_void_p(stream.handle))
 
+    def forward_fused_device(self, prologue: Prologue, d_x: int, rows: int, d_y: int, workspace: DeviceBuffer,
+                             stream: Stream = DEFAULT_STREAM, tp=None) -> None:
+        """``forward_device`` for fp16 rows with an RMSNorm or SwiGLU prologue fused into the kernel's input rotation;
+        ``tp`` (a ``TpContext``) makes it the row-parallel form."""
+        _lib.call("b200exl3_linear_forward_fused", c_void_p(self.handle), byref(prologue), c_void_p(tp.handle) if tp is not None else None,
+                  c_void_p(d_x), rows, c_void_p(d_y), c_void_p(workspace.ptr), workspace.nbytes, c_void_p(stream.handle))
+
     def forward_static_device(self, d_x: int, dtype: int, rows: int, d_y: int, stream: Stream = DEFAULT_STREAM) -> None:
         """``forward_device`` without a workspace: the scratch is a fixed 4 MiB array inside the library,
         for callers that cannot allocate device memory.  Calls must not overlap on the GPU, larger
@@ -268,6 +307,12 @@ class Exl3Group:
                        stream: Stream = DEFAULT_STREAM) -> None:
         ptrs = (c_void_p * len(self.widths))(*d_ys)
         _lib.call("b200exl3_group_forward", c_void_p(self.handle), c_void_p(d_x), dtype, rows, ptrs, c_void_p(workspace.ptr),
+                  workspace.nbytes, c_void_p(stream.handle))
+
+    def forward_fused_device(self, prologue: Prologue, d_x: int, rows: int, d_ys, workspace: DeviceBuffer,
+                             stream: Stream = DEFAULT_STREAM) -> None:
+        ptrs = (c_void_p * len(self.widths))(*d_ys)
+        _lib.call("b200exl3_group_forward_fused", c_void_p(self.handle), byref(prologue), c_void_p(d_x), rows, ptrs, c_void_p(workspace.ptr),
                   workspace.nbytes, c_void_p(stream.handle))
 
     def forward(self, x: np.ndarray, dtype: int | None = None, stream: Stream = DEFAULT_STREAM):

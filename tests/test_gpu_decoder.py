@@ -192,3 +192,88 @@ def test_dense_mlp_block(gpu, rows):
     want = oracle.linear_forward(*layers[2][:1], k, 0, layers[2][1], layers[2][2], None, od.swiglu(g, u)).astype(np.float32)
     assert np.isfinite(got).all() and np.abs(got - want).max() <= 2e-2 * np.abs(want).max()
     assert mlp.flops(512) == 3 * 2 * 512 * hidden * ffn
+
+
+def test_fused_prologues_match_the_separate_kernels(gpu):
+    """The RMSNorm (+ residual) and SwiGLU prologues fused into the layer kernel against the stand-alone kernels
+    followed by the plain layer: same arithmetic, so the outputs agree to the last bits except where the norm's row sum
+    (added in another order) moves 1/rms by one fp32 unit."""
+    from mlxl3_b200 import Prologue, decoder as dec
+    from mlxl3_b200.runtime import DeviceBuffer, Stream
+    from tests.gpu_util import random_layer
+    rng = np.random.default_rng(77)
+    n_in, n_out, k = 1024, 512, 4
+    stream = Stream()
+    members = [gpu.Exl3Linear(*random_layer(rng, n_in, w, k), None, k, 0) for w in (n_out, 256)]
+    group = gpu.Exl3Group(members)
+    layer = gpu.Exl3Linear(*random_layer(rng, n_in, n_out, k), None, k, 0)
+    for rows in (1, 2):
+        x = rng.standard_normal((rows, n_in)).astype(np.float16)
+        r = (rng.standard_normal((rows, n_in)) * 0.5).astype(np.float16)
+        w = (1 + 0.1 * rng.standard_normal(n_in)).astype(np.float16)
+        d_x, d_r, d_w = DeviceBuffer.from_numpy(x), DeviceBuffer.from_numpy(r), DeviceBuffer.from_numpy(w)
+        d_s, d_s2, d_xn = DeviceBuffer(x.nbytes), DeviceBuffer(x.nbytes), DeviceBuffer(x.nbytes)
+        ws = gpu.new_workspace(max(group.workspace_bytes(rows), layer.workspace_bytes(rows)))
+        outs = [[DeviceBuffer(rows * wd * 2) for wd in (n_out, 256)] for _ in range(2)]
+        # RMSNorm with residual in front of a group
+        dec.rms_norm(d_x.ptr, d_r.ptr, d_w.ptr, rows, n_in, 1e-5, d_s.ptr, d_xn.ptr, stream)
+        group.forward_device(d_xn.ptr, gpu.F16, rows, [o.ptr for o in outs[0]], ws, stream)
+        group.forward_fused_device(Prologue.rms_norm(d_w.ptr, 1e-5, d_r.ptr, d_s2.ptr), d_x.ptr, rows, [o.ptr for o in outs[1]], ws, stream)
+        assert np.array_equal(bits(d_s.download(x.shape, np.float16, stream)), bits(d_s2.download(x.shape, np.float16, stream)))
+        for a, b_, wd in zip(outs[0], outs[1], (n_out, 256)):
+            ya, yb = a.download((rows, wd), np.float16, stream).astype(np.float32), b_.download((rows, wd), np.float16, stream).astype(np.float32)
+            assert np.abs(ya - yb).max() <= 2e-3 * np.abs(ya).max()
+        # SwiGLU in front of a plain layer
+        g, u = (rng.standard_normal((rows, n_in)) * 2).astype(np.float16), rng.standard_normal((rows, n_in)).astype(np.float16)
+        d_g, d_u, d_a = DeviceBuffer.from_numpy(g), DeviceBuffer.from_numpy(u), DeviceBuffer(g.nbytes)
+        y0, y1 = DeviceBuffer(rows * n_out * 2), DeviceBuffer(rows * n_out * 2)
+        dec.swiglu(d_g.ptr, d_u.ptr, g.size, d_a.ptr, stream)
+        layer.forward_device(d_a.ptr, gpu.F16, rows, y0.ptr, ws, stream)
+        layer.forward_fused_device(Prologue.swiglu(d_u.ptr), d_g.ptr, rows, y1.ptr, ws, stream)
+        assert np.array_equal(bits(y0.download((rows, n_out), np.float16, stream)), bits(y1.download((rows, n_out), np.float16, stream)))
+        # residual epilogue, then the norm of the next layer from the block sums it left
+        hres = rng.standard_normal((rows, n_out)).astype(np.float16)
+        d_h, d_sq = DeviceBuffer.from_numpy(hres), DeviceBuffer(rows * (n_out // 128) * 4)
+        layer.forward_fused_device(Prologue.plain().with_residual(d_h.ptr, d_h.ptr, d_sq.ptr), d_a.ptr, rows, 0, ws, stream)
+        want_sum = (hres.astype(np.float32) + y0.download((rows, n_out), np.float16, stream).astype(np.float32)).astype(np.float16)
+        got_sum = d_h.download((rows, n_out), np.float16, stream)
+        assert np.array_equal(bits(got_sum), bits(want_sum))
+        sq = d_sq.download((rows, n_out // 128), np.float32, stream)
+        want_sq = (got_sum.astype(np.float32) ** 2).reshape(rows, -1, 128).sum(axis=2)
+        assert np.abs(sq - want_sq).max() <= 1e-4 * want_sq.max()
+        nxt = gpu.Exl3Linear(*random_layer(rng, n_out, 256, k), None, k, 0)
+        wn = (1 + 0.1 * rng.standard_normal(n_out)).astype(np.float16)
+        d_wn, d_n, z0, z1 = DeviceBuffer.from_numpy(wn), DeviceBuffer(rows * n_out * 2), DeviceBuffer(rows * 256 * 2), DeviceBuffer(rows * 256 * 2)
+        ws2 = gpu.new_workspace(nxt.workspace_bytes(rows))
+        dec.rms_norm(d_h.ptr, 0, d_wn.ptr, rows, n_out, 1e-5, 0, d_n.ptr, stream)
+        nxt.forward_device(d_n.ptr, gpu.F16, rows, z0.ptr, ws2, stream)
+        nxt.forward_fused_device(Prologue.rms_norm_from_blocks(d_wn.ptr, 1e-5, d_sq.ptr), d_h.ptr, rows, z1.ptr, ws2, stream)
+        za, zb = z0.download((rows, 256), np.float16, stream).astype(np.float32), z1.download((rows, 256), np.float16, stream).astype(np.float32)
+        assert np.abs(za - zb).max() <= 2e-3 * np.abs(za).max()
+    with pytest.raises(gpu.B200Exl3Error, match="1 or 2 rows"):
+        layer.forward_fused_device(Prologue.swiglu(d_u.ptr), d_g.ptr, 3, y1.ptr, ws, stream)
+    with pytest.raises(gpu.B200Exl3Error, match="over its own input"):
+        layer.forward_fused_device(Prologue.rms_norm(d_w.ptr, 1e-5, d_r.ptr, d_x.ptr), d_x.ptr, 1, y1.ptr, ws, stream)
+
+
+def test_small_decoder_with_glue_kernels_of_their_own(gpu):
+    from mlxl3_b200.decoder import DenseDecoder
+    config, weights = _small()
+    model, linear = _oracle_model(config, weights)
+    dec = DenseDecoder(config, weights)
+    dec.store_logits, dec.fused = True, False
+    kc = [np.zeros((config.kv_heads, config.max_ctx, config.head_dim), np.float16) for _ in range(config.layers)]
+    vc = [np.zeros((config.kv_heads, config.max_ctx, config.head_dim), np.float16) for _ in range(config.layers)]
+    for e in dec.layers:
+        e["k_cache"].fill(0, dec.stream), e["v_cache"].fill(0, dec.stream)
+    for pos, token in enumerate([3, 700, 41]):
+        dec.set_input(token, pos)
+        dec.step()
+        _, index = dec.result()
+        logits, hidden = dec.download("logits"), dec.download(dec.hidden_name)
+        want_logits, want_best, want_h = od.dense_decoder_step(model, token, pos, kc, vc, linear)
+        assert np.abs(hidden.astype(np.float32) - want_h.astype(np.float32).ravel()).max() <= 3e-2 * np.abs(want_h.astype(np.float32)).max()
+        bar_l = 3e-2 * np.abs(want_logits.astype(np.float32)).max()
+        assert np.abs(logits.astype(np.float32) - want_logits.astype(np.float32)).max() <= bar_l
+        assert float(want_logits[want_best]) - float(want_logits[index]) <= bar_l
+    assert dec.launches_per_step == 10 * config.layers + 4
