@@ -62,7 +62,14 @@ int b200exl3_version(void);
  * workspace sizes), "moe_sorted" (0 = the expert block runs one row per slot for any batch instead of grouping
  * slots by expert for larger batches; set it before asking for workspace sizes), "qmm_trace_buffer" (device address of a uint64 [CTAs, 8] array that receives nanosecond
  * stamps of the tensor-core kernel's phases: start, set up, decoders done, MMAs issued, accumulator ready,
- * epilogue done, end, activation copies issued; 0 = off). */
+ * epilogue done, end, activation copies issued; 0 = off), "tp_wait_ms" (how long a rank waits for the other ranks'
+ * words inside a tensor- or expert-parallel kernel before it gives up with status 4; default 4000), "stack_wait_ms"
+ * (the same bound for every wait inside the decode-step kernel: status 5 = a layer never completed, 6 = a piece of
+ * a column block never arrived; default 2000), "stack_trace_buffer" (device address of a uint64
+ * [layers, CTAs, 20] array that receives nanosecond stamps of the decode-step kernel: boundary passed, activations
+ * rotated, last tile, block staged, finish begun, pieces out, pieces in, block stored, then one stamp per warp when
+ * its tiles of the layer were done; 0 = off).  Options are atomics: they may be set from any thread, and a launch
+ * reads each of them once. */
 int b200exl3_set_option(const char* name, int64_t value);
 
 /* The launch policy as data, for tests and reports (replaces the Kani proofs beside exl3_projection_splits and

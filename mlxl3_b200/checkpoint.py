@@ -144,9 +144,7 @@ def inspect(path) -> Checkpoint:
         size_bytes += entry.stat().st_size
         name = entry.name
         tokenizer |= name.startswith("tokenizer") or name.endswith(".model") or name == "vocab.json"
-        sidecar = model_type == "qwen4_exp" and name in ("ngram_embedding.safetensors",
-                                                         "mtp_hyper_connection_mixer_patch.safetensors")
-        if (name.startswith("model") or sidecar) and name.endswith(".safetensors"):
+        if name.startswith("model") and name.endswith(".safetensors"):
             for tensor, info in read_header(entry.path).items():
                 if tensor in tensors:
                     raise B200Exl3Error(f"duplicate tensor {tensor}")
@@ -169,9 +167,6 @@ def inspect(path) -> Checkpoint:
                 except (KeyError, TypeError, ValueError) as error:
                     raise B200Exl3Error("invalid stored tensor shape") from error
                 info = tensors.get(name)
-                if (info is None and model_type == "lfm2_moe" and name.startswith("model.layers.")
-                        and name.endswith(".feed_forward.gate.expert_bias")):
-                    info = tensors.get(name.replace(".gate.expert_bias", ".expert_bias"))
                 if info is None:
                     raise B200Exl3Error(f"missing tensor {name}")
                 if info.shape != shape:

@@ -40,6 +40,8 @@ def main(argv=None) -> None:
     ap.add_argument("--context", type=int, default=2048)
     ap.add_argument("--unfused", action="store_true", help="with --decoder-layers: norms and SwiGLU as kernels of their own")
     ap.add_argument("--trace", action="store_true", help="with --step-layers: print the per-layer phase stamps of one step")
+    ap.add_argument("--step-plain", action="store_true",
+                    help="with --step-layers: that many plain layers of --in x --out instead of decoder blocks (chained when square)")
     args = ap.parse_args(argv)
     if args.experts > 0:
         return moe_main(args)
@@ -113,7 +115,17 @@ def step_main(args) -> None:
     stream = Stream()
     source = DeviceBuffer.from_numpy(rng.standard_normal((1, hidden)).astype(np.float16), stream)
     ops, names, keep, nbytes = [], [], [], 0
-    for _ in range(args.step_layers):
+    for _ in range(args.step_layers if args.step_plain else 0):
+        y = DeviceBuffer(args.n_out * 2)
+        if not ops:
+            source = DeviceBuffer.from_numpy(rng.standard_normal((1, args.n_in)).astype(np.float16), stream)
+        ops.append((lin(args.n_in, args.n_out), source.ptr, y.ptr))
+        names.append("plain")
+        nbytes += args.n_in * args.n_out * k // 8
+        keep += [y, source]
+        if args.n_in == args.n_out:
+            source = y
+    for _ in range(0 if args.step_plain else args.step_layers):
         q, kk, v, o, gate, up, down = (DeviceBuffer(n * 2) for n in (hidden, kv, kv, hidden, ffn, ffn, hidden))
         ops += [(Exl3Group([lin(hidden, hidden), lin(hidden, kv), lin(hidden, kv)]), source.ptr, [q.ptr, kk.ptr, v.ptr]),
                 (lin(hidden, hidden), q.ptr, o.ptr),
