@@ -73,7 +73,7 @@ constexpr size_t kCounterBytes = B200EXL3_WORKSPACE_HEADER_BYTES;   // arrival c
 struct LayerCore {
     int in, out, k, cb;
     uint32_t flags;
-    uint32_t* wq;       // weights in the quad layout [in/16, out/64, 8K, 4], owned
+    uint32_t* wq;       // weights in the quad layout [out/128, in/16, 2, 8K, 4], owned
     __half* suh;        // [groups, in]
     __half* svh;        // [out]
     __half* bias;       // [out] or nullptr
@@ -683,7 +683,7 @@ int b200exl3_group_create(const b200exl3_linear* const* members, int count, b200
     int rc = 0;
     if (total / 128 >= static_cast<int64_t>(kCounterBytes / sizeof(unsigned int))) rc = fail("group width overflow");
     c->out = static_cast<int>(total);
-    const size_t row_bytes = static_cast<size_t>(c->out / 16) * 32 * c->k;       // one input-tile row of the quad layout
+    const size_t row_bytes = static_cast<size_t>(c->out / 16) * 32 * c->k;       // one input-tile row of all column blocks
     if (!rc) rc = check(cudaMalloc(&c->wq, row_bytes * (c->in / 16)), "cudaMalloc(weights)");
     if (!rc) rc = check(cudaMalloc(&c->suh, static_cast<size_t>(count) * c->in * sizeof(__half)), "cudaMalloc(scales)");
     if (!rc) rc = check(cudaMalloc(&c->svh, static_cast<size_t>(c->out) * sizeof(__half)), "cudaMalloc(scales)");
@@ -693,10 +693,10 @@ int b200exl3_group_create(const b200exl3_linear* const* members, int count, b200
     }
     for (int g = 0; g < count && !rc; ++g) {
         const LayerCore& m = members[g]->c;
-        const size_t member_row = static_cast<size_t>(m.out / 16) * 32 * m.k;
-        // concatenate along the output axis: every input-tile row of the member goes behind the previous members' rows
-        rc = check(cudaMemcpy2D(reinterpret_cast<char*>(c->wq) + static_cast<size_t>(c->gcol0[g] / 16) * 32 * c->k, row_bytes,
-                                m.wq, member_row, member_row, c->in / 16, cudaMemcpyDeviceToDevice), "concatenate weights");
+        // concatenate along the output axis: the layout is column-block-major, so a member's blocks go behind the
+        // previous members' blocks as one contiguous copy
+        rc = check(cudaMemcpy(c->wq + quad_row_offset(0, c->gcol0[g] / 128, c->in / 16, c->k), m.wq,
+                              static_cast<size_t>(m.out / 16) * 32 * m.k * (m.in / 16), cudaMemcpyDeviceToDevice), "concatenate weights");
         if (!rc) rc = check(cudaMemcpy(c->suh + static_cast<size_t>(g) * c->in, m.suh, static_cast<size_t>(c->in) * sizeof(__half),
                                        cudaMemcpyDeviceToDevice), "copy scales");
         if (!rc) rc = check(cudaMemcpy(c->svh + c->gcol0[g], m.svh, static_cast<size_t>(m.out) * sizeof(__half),

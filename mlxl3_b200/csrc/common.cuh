@@ -17,6 +17,12 @@ constexpr int kBF16 = 12;
 
 constexpr int kDefaultSmCount = 148;   // B200; sm_count() asks the device
 
+// Word offset of row `tk` (16 inputs) of 128-column block `cblock` in the quad layout [tiles_n/8, tiles_k, 2, 8K, 4]:
+// a row is 64K words, the rows of a block follow one another.
+__host__ __device__ __forceinline__ int64_t quad_row_offset(int tk, int cblock, int tiles_k, int k) {
+    return (static_cast<int64_t>(cblock) * tiles_k + tk) * (64 * k);
+}
+
 __host__ __device__ inline bool dtype_is_float(int code) { return code == kF16 || code == kF32 || code == kBF16; }
 __host__ __device__ inline size_t dtype_size(int code) { return code == kF32 ? 4 : 2; }
 

@@ -59,11 +59,13 @@ constexpr int kQmvMaxSmemBytes = 200 * 1024;
 constexpr int kQmvXBlocks = 6;       // 128-blocks of rotated activations a warp keeps per row
 constexpr int kQmvFusedRows = 2;     // up to this many rows the kernel rotates the activations itself
 
-// rows of 8 tiles kept in flight per warp
-__host__ __device__ constexpr int qmv_depth(int k) { return k <= 2 ? 8 : 4; }
+// The weight stream of a warp: chunks of consecutive rows of a column block (a row is 8 tiles; one bulk copy per chunk),
+// a few chunks in flight: 8 rows for 1-2 bits, 6 for 3-4 bits, 4 above (4 to 8 KB per warp)
+__host__ __device__ constexpr int qmv_chunk_rows(int k) { return k <= 2 ? 4 : 2; }
+__host__ __device__ constexpr int qmv_slots(int k) { return (k == 3 || k == 4) ? 3 : 2; }
 
 struct QmvArgs {
-    const uint32_t* wq;        // quad layout [tiles_k, tiles_n/4, 8K, 4] words
+    const uint32_t* wq;        // quad layout [tiles_n/8, tiles_k, 2, 8K, 4] words
     const void* x;             // [rows, in] activations in x_dtype (used when xhat == nullptr)
     const __half* suh;         // [groups, in]
     const __half* xhat;        // [groups, rows, in] already rotated activations, or nullptr
@@ -138,9 +140,12 @@ void qmv_set_tuning(int ctas_per_sm, int force_grid, int pdl);
 void qmv_set_trace(unsigned long long* device_buffer);
 
 // ---- a whole decode step in one persistent launch (kernels_stack*.cu) ------------------------------------------
-// rows of 8 tiles a warp keeps in flight: about 8 KB per warp, so that the stream does not run dry while a layer
-// boundary is crossed
-__host__ __device__ constexpr int stack_depth(int k) { return k <= 4 ? 8 : 32 / k; }
+// The kernel streams weights in chunks of consecutive rows of a column block (one bulk copy each; a row is 8 tiles)
+// and keeps three chunks per warp in flight (9 to 12 KB), so that the stream does not run dry while a layer boundary
+// is crossed.  Measured: chunk and ring geometry hardly matter (1 row x 8 slots to 8 rows x 2 slots: within 3 %);
+// what a chunk buys is that the barrier wait, the probe and the refill leave the row loop.
+__host__ __device__ constexpr int stack_chunk_rows(int k) { return k <= 4 ? 4 : 2; }
+constexpr int kStackSlots = 3;                  // chunks in flight per warp
 #ifndef B200_STACK_WARPS
 #define B200_STACK_WARPS 12
 #endif
@@ -330,7 +335,9 @@ cudaError_t launch_qmm_mapped(const uint32_t* wq, int in, int width, int bank_ti
 void qmm_set_tuning(int splits);   // force the number of input splits (0 = automatic)
 
 // ---- weight layout (kernels_codec.cu) -----------------------------------------------------------------
-// checkpoint layout [tiles_k, tiles_n, 8K] words -> quad layout [tiles_k, tiles_n/4, 8K, 4]
+// checkpoint layout [tiles_k, tiles_n, 8K] words -> quad layout [tiles_n/8, tiles_k, 2, 8K, 4]: the stream words of four
+// neighbouring tiles interleaved word by word (a quad), two quads = one row of a 128-column block (256K bytes), and
+// the rows of a column block one after the other, so any run of a block's rows is one contiguous copy
 cudaError_t launch_repack_quads(const uint32_t* trellis, int tiles_k, int tiles_n, int k, uint32_t* wq, cudaStream_t stream);
 // inner matrix from the quad layout, bit-exact
 cudaError_t launch_reconstruct_quads(const uint32_t* wq, int tiles_k, int tiles_n, int k, int cb, __half* w,

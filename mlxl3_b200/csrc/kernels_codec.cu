@@ -25,7 +25,7 @@ __global__ void codebook_kernel(const uint16_t* __restrict__ states, int64_t n, 
 // One CTA of 256 threads reconstructs a strip of 8 tiles: 16 rows x 128 columns of W.  Each warp
 // decodes one tile into shared memory in row-major order; the CTA then writes 16-byte pieces so
 // that every row segment (256 bytes) leaves as whole sectors.  QUADS selects the weight layout:
-// false = checkpoint layout [tiles_k, tiles_n, 8K] words, true = quad layout [tiles_k, tiles_n/4, 8K, 4].
+// false = checkpoint layout [tiles_k, tiles_n, 8K] words, true = quad layout [tiles_n/8, tiles_k, 2, 8K, 4].
 template <bool QUADS>
 __global__ void __launch_bounds__(256)
 reconstruct_kernel(const uint32_t* __restrict__ trellis, int tiles_k, int tiles_n, int k, int cb,
@@ -38,7 +38,8 @@ reconstruct_kernel(const uint32_t* __restrict__ trellis, int tiles_k, int tiles_
     const int tn = tn0 + warp;
     if (tn < tiles_n) {
         const int64_t tile = static_cast<int64_t>(tk) * tiles_n + tn;
-        const uint32_t* words = QUADS ? trellis + (tile >> 2) * (32 * k) + (tile & 3) : trellis + tile * (8 * k);
+        const uint32_t* words = QUADS ? trellis + quad_row_offset(tk, tn >> 3, tiles_k, k) + ((tn >> 2) & 1) * (32 * k) + (tn & 3)
+                                      : trellis + tile * (8 * k);
         const int r = (lane & 3) * 2, c = lane >> 2;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -58,8 +59,10 @@ reconstruct_kernel(const uint32_t* __restrict__ trellis, int tiles_k, int tiles_
     }
 }
 
-// One thread per 16-byte chunk of the quad layout: word w of four neighbouring tiles.
-__global__ void repack_quads_kernel(const uint32_t* __restrict__ trellis, int64_t quads, int k, uint32_t* __restrict__ wq) {
+// One thread per 16-byte chunk of the quad layout: word w of four neighbouring tiles.  `quads` counts the source's
+// groups of four tiles in checkpoint order (tile row, then column).
+__global__ void repack_quads_kernel(const uint32_t* __restrict__ trellis, int64_t quads, int tiles_k, int tiles_n, int k,
+                                    uint32_t* __restrict__ wq) {
     const int64_t chunk = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     const int nw = 8 * k;
     if (chunk >= quads * nw) return;
@@ -67,7 +70,10 @@ __global__ void repack_quads_kernel(const uint32_t* __restrict__ trellis, int64_
     const int wi = static_cast<int>(chunk % nw);
     const uint32_t* src = trellis + quad * 4 * nw + wi;
     uint4 v = make_uint4(src[0], src[nw], src[2 * nw], src[3 * nw]);
-    reinterpret_cast<uint4*>(wq)[chunk] = v;
+    const int quads_n = tiles_n / 4;
+    const int tk = static_cast<int>(quad / quads_n), qn = static_cast<int>(quad % quads_n);
+    uint32_t* dst = wq + quad_row_offset(tk, qn >> 1, tiles_k, k) + (qn & 1) * (32 * k) + wi * 4;
+    *reinterpret_cast<uint4*>(dst) = v;
 }
 
 cudaError_t launch_unpack_states(const uint16_t* packed, int64_t tiles, int k, int cb, uint16_t* states, __half* values,
@@ -105,7 +111,7 @@ cudaError_t launch_repack_quads(const uint32_t* trellis, int tiles_k, int tiles_
     const int64_t quads = static_cast<int64_t>(tiles_k) * (tiles_n / 4);
     const int64_t chunks = quads * 8 * k;
     if (chunks == 0) return cudaSuccess;
-    repack_quads_kernel<<<static_cast<unsigned>((chunks + 255) / 256), 256, 0, stream>>>(trellis, quads, k, wq);
+    repack_quads_kernel<<<static_cast<unsigned>((chunks + 255) / 256), 256, 0, stream>>>(trellis, quads, tiles_k, tiles_n, k, wq);
     return cudaGetLastError();
 }
 

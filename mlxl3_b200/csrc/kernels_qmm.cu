@@ -168,7 +168,7 @@ __device__ __forceinline__ bool qmm_wait_warp(uint64_t* bar, uint32_t parity, vo
 
 template <int K, int CB, bool SMALL>
 __global__ void __launch_bounds__(QmmShape<SMALL>::kThreads, QmmShape<SMALL>::kMinBlocks)
-qmm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, const QmmArgs p) {
+qmm_kernel(const __grid_constant__ CUtensorMap xmap, const QmmArgs p) {
     using S = QmmShape<SMALL>;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int kQuadWords = 32 * K;                       // four interleaved tiles
@@ -299,14 +299,15 @@ qmm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUt
             if (tr) tr[7] = global_ns();
         }
     } else if (warp == kWeightWarp) {
-        // ================= weight producer: one tensor copy (4 tile rows x 8 tiles) per stage =================
+        // ================= weight producer: one bulk copy (4 tile rows x 8 tiles, contiguous) per stage =================
         if (lane == 0) {
             int slot = 0;
             uint32_t par = 0;
             for (int it = 0; it < nst && !s_failed; ++it) {
                 if (!qmm_wait(&raw_empty[slot], par ^ 1u, &s_failed)) break;
                 mbar_expect_tx(&raw_full[slot], kRawStageBytes);
-                tma_load_2d(raw_base + slot * kRawStageWords, &wmap, wblock * (32 * K), 4 * (st0 + it), &raw_full[slot]);
+                bulk_copy_g2s(raw_base + slot * kRawStageWords, p.wq + quad_row_offset(4 * (st0 + it), wblock, p.in / 16, K), kRawStageBytes,
+                              &raw_full[slot]);
                 if (++slot == kRawDepth) { slot = 0; par ^= 1u; }
             }
         }
@@ -442,7 +443,7 @@ EncodeFn encode_fn() {
 }
 
 template <int K, int CB, bool SMALL>
-cudaError_t qmm_launch_shape(const CUtensorMap& map, const CUtensorMap& wmap, const QmmArgs& p, dim3 grid, cudaStream_t stream) {
+cudaError_t qmm_launch_shape(const CUtensorMap& map, const QmmArgs& p, dim3 grid, cudaStream_t stream) {
     using S = QmmShape<SMALL>;
     constexpr size_t smem = S::kSmemBytes;
     auto kernel = qmm_kernel<K, CB, SMALL>;
@@ -452,20 +453,20 @@ cudaError_t qmm_launch_shape(const CUtensorMap& map, const CUtensorMap& wmap, co
         if (e != cudaSuccess) return e;
         attribute.mark();
     }
-    kernel<<<grid, S::kThreads, smem, stream>>>(map, wmap, p);
+    kernel<<<grid, S::kThreads, smem, stream>>>(map, p);
     return cudaGetLastError();
 }
 
 template <int K, int CB>
-cudaError_t qmm_launch_one(const CUtensorMap& map, const CUtensorMap& wmap, const QmmArgs& p, dim3 grid, bool small, cudaStream_t stream) {
-    return small ? qmm_launch_shape<K, CB, true>(map, wmap, p, grid, stream) : qmm_launch_shape<K, CB, false>(map, wmap, p, grid, stream);
+cudaError_t qmm_launch_one(const CUtensorMap& map, const QmmArgs& p, dim3 grid, bool small, cudaStream_t stream) {
+    return small ? qmm_launch_shape<K, CB, true>(map, p, grid, stream) : qmm_launch_shape<K, CB, false>(map, p, grid, stream);
 }
 
 template <int K>
-cudaError_t qmm_launch_k(int cb, const CUtensorMap& map, const CUtensorMap& wmap, const QmmArgs& p, dim3 grid, bool small, cudaStream_t stream) {
-    if (cb == 0) return qmm_launch_one<K, 0>(map, wmap, p, grid, small, stream);
-    if (cb == 1) return qmm_launch_one<K, 1>(map, wmap, p, grid, small, stream);
-    return qmm_launch_one<K, 2>(map, wmap, p, grid, small, stream);
+cudaError_t qmm_launch_k(int cb, const CUtensorMap& map, const QmmArgs& p, dim3 grid, bool small, cudaStream_t stream) {
+    if (cb == 0) return qmm_launch_one<K, 0>(map, p, grid, small, stream);
+    if (cb == 1) return qmm_launch_one<K, 1>(map, p, grid, small, stream);
+    return qmm_launch_one<K, 2>(map, p, grid, small, stream);
 }
 
 }  // namespace
@@ -511,8 +512,9 @@ cudaError_t launch_qmm(const uint32_t* wq, int in, int out, int k, int cb, const
                        void* y, int y_dtype, cudaStream_t stream, int ld_tiles, int col_tile0) {
     if (in % 128 || out % 128 || rows <= 0 || col_tile0 % 8) return cudaErrorInvalidValue;
     if (ld_tiles <= 0) ld_tiles = out / 16;
-    // a member of a group: its columns start col_tile0 tiles into rows that are ld_tiles tiles long
-    wq += static_cast<size_t>(col_tile0) * 8 * k;
+    // a member of a group: its column blocks follow those of the members before it
+    (void)ld_tiles;
+    wq += quad_row_offset(0, col_tile0 / 8, in / 16, k);
     if (y != nullptr && plan.splits != 1) return cudaErrorInvalidValue;     // the fused rotation needs the complete sum
     EncodeFn encode = encode_fn();
     if (!encode) return cudaErrorNotSupported;
@@ -526,16 +528,8 @@ cudaError_t launch_qmm(const uint32_t* wq, int in, int out, int k, int cb, const
                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return cudaErrorInvalidValue;
-    // packed weights as a 2-D array of 8-byte words [in/16 tile rows, out/16 * 4K]: a box of one stage is
-    // 4 tile rows x 8 tiles (32*K words of a row), landing contiguously in shared memory
-    CUtensorMap wmap;
-    const cuuint64_t wdims[2] = {static_cast<cuuint64_t>(out / 16) * 4 * k, static_cast<cuuint64_t>(in / 16)};
-    const cuuint64_t wstrides[1] = {static_cast<cuuint64_t>(ld_tiles) * 32 * k};
-    const cuuint32_t wbox[2] = {static_cast<cuuint32_t>(32 * k), 4};
-    if (encode(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint32_t*>(wq), wdims, wstrides, wbox, elem,
-               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-        return cudaErrorInvalidValue;
+    // packed weights: the four tile rows of a stage are contiguous in the quad layout, so the weight producer issues plain
+    // bulk copies and needs no tensor map
     QmmArgs p{};
     p.wq = wq; p.partials = partials; p.error = error;
     p.svh = svh; p.bias = bias; p.y = y; p.y_dtype = y_dtype;
@@ -543,14 +537,14 @@ cudaError_t launch_qmm(const uint32_t* wq, int in, int out, int k, int cb, const
     p.splits = plan.splits; p.stages_total = in / 64; p.trace = g_qmm_trace.load();
     const dim3 grid(static_cast<unsigned>((out / 128) * plan.splits), static_cast<unsigned>(plan.token_tiles));
     switch (k) {
-        case 1: return qmm_launch_k<1>(cb, map, wmap, p, grid, plan.small, stream);
-        case 2: return qmm_launch_k<2>(cb, map, wmap, p, grid, plan.small, stream);
-        case 3: return qmm_launch_k<3>(cb, map, wmap, p, grid, plan.small, stream);
-        case 4: return qmm_launch_k<4>(cb, map, wmap, p, grid, plan.small, stream);
-        case 5: return qmm_launch_k<5>(cb, map, wmap, p, grid, plan.small, stream);
-        case 6: return qmm_launch_k<6>(cb, map, wmap, p, grid, plan.small, stream);
-        case 7: return qmm_launch_k<7>(cb, map, wmap, p, grid, plan.small, stream);
-        case 8: return qmm_launch_k<8>(cb, map, wmap, p, grid, plan.small, stream);
+        case 1: return qmm_launch_k<1>(cb, map, p, grid, plan.small, stream);
+        case 2: return qmm_launch_k<2>(cb, map, p, grid, plan.small, stream);
+        case 3: return qmm_launch_k<3>(cb, map, p, grid, plan.small, stream);
+        case 4: return qmm_launch_k<4>(cb, map, p, grid, plan.small, stream);
+        case 5: return qmm_launch_k<5>(cb, map, p, grid, plan.small, stream);
+        case 6: return qmm_launch_k<6>(cb, map, p, grid, plan.small, stream);
+        case 7: return qmm_launch_k<7>(cb, map, p, grid, plan.small, stream);
+        case 8: return qmm_launch_k<8>(cb, map, p, grid, plan.small, stream);
         default: return cudaErrorInvalidValue;
     }
 }
@@ -565,20 +559,13 @@ cudaError_t launch_qmm_mapped(const uint32_t* wq, int in, int width, int bank_ti
     if (!encode) return cudaErrorNotSupported;
     const int64_t rows = static_cast<int64_t>(max_segments) * proj * S::kTokTile;   // padded activation rows
     const int out = max_segments * proj * width;                                   // virtual output width
-    CUtensorMap map, wmap;
+    CUtensorMap map;
     const cuuint32_t elem[2] = {1, 1};
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(in), static_cast<cuuint64_t>(rows)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(in) * sizeof(__half)};
     const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(S::kTokHalf)};
     if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(xhat), dims, strides, box, elem,
                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-        return cudaErrorInvalidValue;
-    const cuuint64_t wdims[2] = {static_cast<cuuint64_t>(bank_tiles_n) * 4 * k, static_cast<cuuint64_t>(in / 16)};
-    const cuuint64_t wstrides[1] = {static_cast<cuuint64_t>(bank_tiles_n) * 32 * k};
-    const cuuint32_t wbox[2] = {static_cast<cuuint32_t>(32 * k), 4};
-    if (encode(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint32_t*>(wq), wdims, wstrides, wbox, elem,
-               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return cudaErrorInvalidValue;
     QmmArgs p{};
@@ -589,14 +576,14 @@ cudaError_t launch_qmm_mapped(const uint32_t* wq, int in, int width, int bank_ti
     p.map_blocks = width / 128; p.map_proj = proj; p.map_stride_blocks = stride_blocks; p.map_experts = experts;
     const dim3 grid(static_cast<unsigned>(out / 128), 1);
     switch (k) {
-        case 1: return qmm_launch_k<1>(cb, map, wmap, p, grid, true, stream);
-        case 2: return qmm_launch_k<2>(cb, map, wmap, p, grid, true, stream);
-        case 3: return qmm_launch_k<3>(cb, map, wmap, p, grid, true, stream);
-        case 4: return qmm_launch_k<4>(cb, map, wmap, p, grid, true, stream);
-        case 5: return qmm_launch_k<5>(cb, map, wmap, p, grid, true, stream);
-        case 6: return qmm_launch_k<6>(cb, map, wmap, p, grid, true, stream);
-        case 7: return qmm_launch_k<7>(cb, map, wmap, p, grid, true, stream);
-        case 8: return qmm_launch_k<8>(cb, map, wmap, p, grid, true, stream);
+        case 1: return qmm_launch_k<1>(cb, map, p, grid, true, stream);
+        case 2: return qmm_launch_k<2>(cb, map, p, grid, true, stream);
+        case 3: return qmm_launch_k<3>(cb, map, p, grid, true, stream);
+        case 4: return qmm_launch_k<4>(cb, map, p, grid, true, stream);
+        case 5: return qmm_launch_k<5>(cb, map, p, grid, true, stream);
+        case 6: return qmm_launch_k<6>(cb, map, p, grid, true, stream);
+        case 7: return qmm_launch_k<7>(cb, map, p, grid, true, stream);
+        case 8: return qmm_launch_k<8>(cb, map, p, grid, true, stream);
         default: return cudaErrorInvalidValue;
     }
 }

@@ -73,7 +73,7 @@ QmvPlan plan_qmv(int in, int out, int k, int64_t rows) {
     plan.max_pieces = static_cast<int>((grid + plan.col_blocks - 1) / plan.col_blocks + 1);
     plan.fused_rotation = r <= kQmvFusedRows;
     // per warp: [ring of packed rows | rotated activations | two staged result tiles]
-    const size_t ring = static_cast<size_t>(qmv_depth(k)) * 64 * k * sizeof(uint32_t);
+    const size_t ring = static_cast<size_t>(qmv_chunk_rows(k)) * qmv_slots(k) * 64 * k * sizeof(uint32_t);
     const size_t xs = plan.fused_rotation ? static_cast<size_t>(r) * kQmvXBlocks * 128 * sizeof(__half) : 0;
     const size_t stage = 2 * static_cast<size_t>(r) * kQmvRedStride * sizeof(float);   // first and second block of a warp
     plan.xs_offset = static_cast<int>(ring);

@@ -315,11 +315,12 @@ __global__ void __launch_bounds__(kQmvWarps * 32, NB == 1 ? 2 : 1)
 qmv_kernel(const QmvArgs p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int WARPS = kQmvWarps;
-    constexpr int DEPTH = qmv_depth(K);
+    constexpr int R = qmv_chunk_rows(K);                    // rows per bulk copy (the rows of a column block are contiguous)
+    constexpr int SLOTS = qmv_slots(K);                     // chunks in flight per warp
     constexpr int kRowWords = 64 * K;                       // 2 quads x 8K words x 4 tiles
     constexpr uint32_t kRowBytes = kRowWords * 4;
     constexpr int kXsHalves = kQmvXBlocks * 128;            // rotated activations kept per row and warp
-    __shared__ __align__(8) uint64_t s_bar[WARPS][DEPTH];
+    __shared__ __align__(8) uint64_t s_bar[WARPS][SLOTS];
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, q = lane & 3;
@@ -344,11 +345,11 @@ qmv_kernel(const QmvArgs p) {
     const int w1 = muldiv(T, wid + 1, W);
 
     unsigned char* mine = smem_raw + static_cast<size_t>(warp) * p.warp_smem;
-    uint32_t* ring = reinterpret_cast<uint32_t*>(mine);                  // DEPTH rows of packed words
+    uint32_t* ring = reinterpret_cast<uint32_t*>(mine);                  // SLOTS chunks of R rows of packed words
     __half* xs = reinterpret_cast<__half*>(mine + p.xs_offset);          // [rows][kXsHalves] (fused rotation only)
     const int stage_floats = rows * kQmvRedStride;                       // one staged [rows][128] tile
     uint64_t* bars = s_bar[warp];
-    const size_t row_stride = static_cast<size_t>(p.tiles_n) * (32 * K);
+    constexpr size_t row_stride = 256 * K;                               // consecutive rows of a column block are contiguous
     const LaneGeom<K> geom(lane);
     const bool tracing = p.trace != nullptr && threadIdx.x == 0;
     if (tracing) p.trace[blockIdx.x * 8 + 0] = global_ns();
@@ -361,7 +362,7 @@ qmv_kernel(const QmvArgs p) {
     if (threadIdx.x < WARPS + 2) s_arrived[threadIdx.x] = 0;
     if (lane == 0) {
 #pragma unroll
-        for (int i = 0; i < DEPTH; ++i) mbar_init(bars + i, 1);
+        for (int i = 0; i < SLOTS; ++i) mbar_init(bars + i, 1);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // barriers visible to the copy engine
     }
     __syncthreads();
@@ -423,28 +424,33 @@ qmv_kernel(const QmvArgs p) {
 #pragma unroll
                     for (int i = 0; i < 4; ++i) acc[t][nb][i] = 0.0f;
 
-            // The segment is walked in chunks whose inputs span at most kQmvXBlocks 128-blocks, so that
-            // the rotated activations of a chunk fit the warp's shared memory.
+            // ---- phase 0: start streaming weights (they do not depend on the previous kernel) ----------------
+            // The rows tk_first..tk_last of the block are contiguous in memory and are copied in chunks of up to R rows
+            // (one bulk copy each), counted from tk_first; whole 8-tile rows are copied even when the warp owns only
+            // part of the first or last one.
+            const char* seg_src = reinterpret_cast<const char*>(p.wq + quad_row_offset(tk_first, tn0 >> 3, p.tiles_k, K));
+            int req_tk = tk_first;                              // first row that has not been requested yet
+            auto refill = [&](int s) {
+                const int n = min(R, tk_last - req_tk + 1);
+                if (lane == 0) {
+                    mbar_expect_tx(bars + s, n * kRowBytes);
+                    bulk_copy_g2s(ring + s * (R * kRowWords), seg_src + static_cast<size_t>(req_tk - tk_first) * row_stride, n * kRowBytes, bars + s);
+                }
+                req_tk += n;
+            };
+            if (active) {
+#pragma unroll
+                for (int i = 0; i < SLOTS; ++i)
+                    if (req_tk <= tk_last) refill(slot + i < SLOTS ? slot + i : slot + i - SLOTS);
+            }
+
+            // The segment is walked in stretches whose inputs span at most kQmvXBlocks 128-blocks, so that
+            // the rotated activations of a stretch fit the warp's shared memory.
             for (int tk0 = tk_first; active && tk0 <= tk_last;) {
                 const int kb0 = tk0 >> 3;
                 const int tk_end = min(tk_last + 1, (kb0 + kQmvXBlocks) * 8);
                 const int nrows = tk_end - tk0;
 
-                // ---- phase 0: start streaming weights (they do not depend on the previous kernel) ----
-                // Whole 8-tile rows are copied even when the warp owns only part of the first or last
-                // one: one TMA copy per row, consecutive rows a fixed stride apart.
-                const char* next_src =
-                    reinterpret_cast<const char*>(p.wq + (static_cast<int64_t>(tk0) * p.tiles_n + tn0) * (8 * K));
-                if (lane == 0) {
-#pragma unroll
-                    for (int i = 0; i < DEPTH; ++i)
-                        if (i < nrows) {
-                            const int sl = slot + i < DEPTH ? slot + i : slot + i - DEPTH;
-                            mbar_expect_tx(bars + sl, kRowBytes);
-                            bulk_copy_g2s(ring + sl * kRowWords, next_src + i * row_stride, kRowBytes, bars + sl);
-                        }
-                }
-                next_src += DEPTH * row_stride;
                 if (first_chunk) {
                     if (p.pdl_early) pdl_launch_dependents();
                     pdl_wait();
@@ -491,13 +497,14 @@ qmv_kernel(const QmvArgs p) {
                     else
                         xfrag[nb] = reinterpret_cast<const uint32_t*>(p.xhat + grp * p.xhat_group_stride + static_cast<int64_t>(row) * p.in + tk0 * 16) + q;
                 }
-                for (int r = 0; r < nrows; ++r) {
-                    const int tk = tk0 + r;
-                    uint32_t bx[NB][4];
+                // The rows of the stretch are walked run by run (a run = the part of one chunk inside the stretch): the
+                // barrier wait and the hand-back of the slot happen once per chunk, and a run without a partial row takes
+                // the loop that tests nothing per tile.  Lanes whose activation row does not exist multiply the last
+                // row again: column n of the product depends on column n of the activations only, and is never stored.
+                auto fragments = [&](int r, uint32_t (&bx)[NB][4]) {
 #pragma unroll
                     for (int nb = 0; nb < NB; ++nb) {
-                        uint32_t p0 = xfrag[nb][r * 8], p1 = xfrag[nb][r * 8 + 4];
-                        if (nb * 8 + g >= rows) { p0 = 0; p1 = 0; }
+                        const uint32_t p0 = xfrag[nb][r * 8], p1 = xfrag[nb][r * 8 + 4];
                         if constexpr (MODE == 0) {
                             bx[nb][0] = prmt(p0, p0, 0x1010); bx[nb][1] = prmt(p0, p0, 0x3232);
                             bx[nb][2] = prmt(p1, p1, 0x1010); bx[nb][3] = prmt(p1, p1, 0x3232);
@@ -505,18 +512,39 @@ qmv_kernel(const QmvArgs p) {
                             bx[nb][0] = p0; bx[nb][1] = p1; bx[nb][2] = 0; bx[nb][3] = 0;
                         }
                     }
-                    if (!mbar_wait(bars + slot, parity)) copy_lost = true;
-                    const uint32_t* row_words = ring + slot * kRowWords;
-                    const int lo = tk == tk_first ? lo_first : 0, hi = tk == tk_last ? hi_last : 8;
-                    if (lo == 0 && hi == 8) qmv_row<K, CB, NB, MODE, true>(row_words, geom, 0, 8, bx, acc);
-                    else qmv_row<K, CB, NB, MODE, false>(row_words, geom, lo, hi, bx, acc);
-                    __syncwarp();                               // every lane has read the slot
-                    if (lane == 0 && r + DEPTH < nrows) {
-                        mbar_expect_tx(bars + slot, kRowBytes);
-                        bulk_copy_g2s(ring + slot * kRowWords, next_src, kRowBytes, bars + slot);
+                };
+#pragma unroll 1
+                for (int r = 0; r < nrows;) {
+                    const int tk = tk0 + r;
+                    const int ri = (tk - tk_first) & (R - 1);                   // row inside its chunk
+                    const int run = min(R - ri, nrows - r);
+                    if (ri == 0 && !copy_lost && !mbar_wait(bars + slot, parity)) copy_lost = true;
+                    const uint32_t* row_words = ring + (slot * R + ri) * kRowWords;
+                    const bool partial = (tk == tk_first && lo_first != 0) || (tk + run - 1 == tk_last && hi_last != 8);
+                    if (!partial) {
+#pragma unroll 1
+                        for (int j = 0; j < run; ++j) {
+                            uint32_t bx[NB][4];
+                            fragments(r + j, bx);
+                            qmv_row<K, CB, NB, MODE, true>(row_words, geom, 0, 8, bx, acc);
+                            row_words += kRowWords;
+                        }
+                    } else {
+#pragma unroll 1
+                        for (int j = 0; j < run; ++j) {
+                            uint32_t bx[NB][4];
+                            fragments(r + j, bx);
+                            const int lo = tk + j == tk_first ? lo_first : 0, hi = tk + j == tk_last ? hi_last : 8;
+                            qmv_row<K, CB, NB, MODE, false>(row_words, geom, lo, hi, bx, acc);
+                            row_words += kRowWords;
+                        }
                     }
-                    next_src += row_stride;
-                    if (++slot == DEPTH) { slot = 0; parity ^= 1u; }
+                    r += run;
+                    if (ri + run == R || tk0 + r > tk_last) {                   // the chunk is consumed: its slot takes the next one
+                        __syncwarp();                                           // every lane has read the slot
+                        if (req_tk <= tk_last) refill(slot);
+                        if (++slot == SLOTS) { slot = 0; parity ^= 1u; }
+                    }
                 }
                 tk0 = tk_end;
             }

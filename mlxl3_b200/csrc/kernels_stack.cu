@@ -20,7 +20,7 @@ StackPlan plan_stack(int k, int rows, int n_ops) {
     StackPlan plan{};
     const int r = std::max(1, std::min(rows, kStackMaxRows));
     // per warp: [ring of packed rows | rotated activations | two staged result tiles]
-    const size_t ring = static_cast<size_t>(stack_depth(k)) * 64 * k * sizeof(uint32_t);
+    const size_t ring = static_cast<size_t>(kStackSlots) * stack_chunk_rows(k) * 64 * k * sizeof(uint32_t);
     plan.x_blocks = r == 1 ? kQmvXBlocks : 4;
     const size_t xs = static_cast<size_t>(r) * plan.x_blocks * 128 * sizeof(__half);
     const size_t stage = 2 * static_cast<size_t>(r) * kQmvRedStride * sizeof(float);

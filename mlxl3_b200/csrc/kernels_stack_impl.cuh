@@ -74,23 +74,24 @@ __device__ __forceinline__ int stack_unit_begin(int T, int warps, int wid, bool 
                   : static_cast<int>(static_cast<unsigned long long>(T) * wid / warps);
 }
 
-// Where a warp's weight stream stands: the row (8 tiles of one 128-column block and 16 inputs) that is copied next.
-// The sequence is: for every layer, for every column block the warp has units in, the block's rows in order -- the
-// order in which the warp consumes them.
-template <int K>
+// Where a warp's weight stream stands: the chunk (up to R consecutive rows of one 128-column block; a row is 8 tiles
+// and 16 inputs) that is copied next.  The sequence is: for every layer, for every column block the warp has units in,
+// the block's rows in order -- the order in which the warp consumes them.  The rows of a block are contiguous in
+// memory, so a chunk is ONE bulk copy; chunks are counted from the first row of the warp's range in the block, which
+// is how the consumer finds their boundaries again.
+template <int K, int R>
 struct StackCursor {
     int op, cblock, tk, tk_last, w1, UB;
     const char* src;
-    size_t stride;
     bool valid;
 
+    __device__ __forceinline__ int rows() const { return min(R, tk_last - tk + 1); }
     __device__ __forceinline__ void segment(const StackOpLite& o, int w0) {
         const int u0 = max(w0, cblock * UB) - cblock * UB;
         const int u1 = min(w1, (cblock + 1) * UB) - cblock * UB;
         tk = u0 >> 3;
         tk_last = (u1 - 1) >> 3;
-        stride = static_cast<size_t>(o.tiles_n) * (32 * K);
-        src = reinterpret_cast<const char*>(o.wq + (static_cast<int64_t>(tk) * o.tiles_n + cblock * 8) * (8 * K));
+        src = reinterpret_cast<const char*>(o.wq + quad_row_offset(tk, cblock, o.tiles_k, K));
     }
     // first layer at or after `first` in which the warp has work
     __device__ __forceinline__ void seek(const StackOpLite* ops, int n_ops, int first, int wid) {
@@ -111,9 +112,9 @@ struct StackCursor {
         }
     }
     __device__ __forceinline__ void next(const StackOpLite* ops, int n_ops, int wid) {
-        if (tk < tk_last) {
-            ++tk;
-            src += stride;
+        if (tk + R <= tk_last) {
+            tk += R;
+            src += R * (256 * K);
         } else if ((cblock + 1) * UB < w1) {
             ++cblock;
             segment(ops[op], cblock * UB);          // a later block of the range starts at its first unit
@@ -364,17 +365,30 @@ __device__ __forceinline__ void stack_finish_block(const StackArgs& a, const Sta
     if (stamp) stamp[7] = global_ns();
 }
 
+// B fragments of one row of 16 inputs from the lane's two activation words: split-halves mode multiplies every
+// activation by both halves of a weight, so each activation appears twice.
+template <int MODE>
+__device__ __forceinline__ void stack_fragment(uint32_t p0, uint32_t p1, uint32_t (&bx)[4]) {
+    if constexpr (MODE == 0) {
+        bx[0] = prmt(p0, p0, 0x1010); bx[1] = prmt(p0, p0, 0x3232);
+        bx[2] = prmt(p1, p1, 0x1010); bx[3] = prmt(p1, p1, 0x3232);
+    } else {
+        bx[0] = p0; bx[1] = p1; bx[2] = 0; bx[3] = 0;
+    }
+}
+
 template <int K, int CB, int MODE>
 __global__ void __launch_bounds__(kStackWarps * 32, kStackCtasPerSm)
 stack_kernel(const StackArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int WARPS = kStackWarps;
-    constexpr int DEPTH = stack_depth(K);
+    constexpr int R = stack_chunk_rows(K);                    // rows per bulk copy
+    constexpr int SLOTS = kStackSlots;                         // chunks in flight per warp
     constexpr int kRowWords = 64 * K;
     constexpr uint32_t kRowBytes = kRowWords * 4;
     const int kXsHalves = a.x_blocks * 128;
     constexpr int NB = 1;
-    __shared__ __align__(8) uint64_t s_bar[WARPS][DEPTH];
+    __shared__ __align__(8) uint64_t s_bar[WARPS][SLOTS];
     __shared__ unsigned int s_arrived[WARPS + 2];
     __shared__ int s_ready;
     __shared__ unsigned int s_poller;
@@ -405,22 +419,24 @@ stack_kernel(const StackArgs a) {
     if (threadIdx.x == 0) { s_ready = 0; s_poller = 0; }
     if (lane == 0) {
 #pragma unroll
-        for (int i = 0; i < DEPTH; ++i) mbar_init(bars + i, 1);
+        for (int i = 0; i < SLOTS; ++i) mbar_init(bars + i, 1);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncthreads();
 
-    // ---- start the weight stream: the first DEPTH rows of this warp, whatever layers they belong to ----------
-    StackCursor<K> cur;
+    // ---- start the weight stream: the first chunks of this warp, whatever layers they belong to ---------------
+    StackCursor<K, R> cur;
     cur.seek(lite, a.n_ops, 0, wid);
-#pragma unroll 1
-    for (int i = 0; i < DEPTH && cur.valid; ++i) {
+    auto refill = [&](int s) {                    // the next chunk of the stream into chunk slot s
         if (lane == 0) {
-            mbar_expect_tx(bars + i, kRowBytes);
-            bulk_copy_g2s(ring + i * kRowWords, cur.src, kRowBytes, bars + i);
+            const uint32_t bytes = static_cast<uint32_t>(cur.rows()) * kRowBytes;
+            mbar_expect_tx(bars + s, bytes);
+            bulk_copy_g2s(ring + s * (R * kRowWords), cur.src, bytes, bars + s);
         }
         cur.next(lite, a.n_ops, wid);
-    }
+    };
+#pragma unroll 1
+    for (int i = 0; i < SLOTS && cur.valid; ++i) refill(i);
     pdl_wait();                                   // the step's inputs come from whatever ran before in the stream
     // tags of this launch: the launch number (advanced by the last CTA to leave) and the layer
     const uint32_t tag_base = *reinterpret_cast<volatile unsigned int*>(a.launch) * 4096u;
@@ -428,7 +444,7 @@ stack_kernel(const StackArgs a) {
     int slot = 0;
     uint32_t parity = 0;
     bool copy_lost = false;
-    bool ready = false;                           // the barrier of the row consumed next has already been seen complete
+    bool ready = false;                           // the barrier of the chunk consumed next has already been seen complete
 
 #pragma unroll 1
     for (int op = 0; op < a.n_ops; ++op) {
@@ -507,40 +523,54 @@ stack_kernel(const StackArgs a) {
                     if (tracing && first_chunk) stamp[1] = global_ns();
                     const uint32_t* xfrag =
                         reinterpret_cast<const uint32_t*>(xs + min(g, rows - 1) * kXsHalves + (tk0 * 16 - kb0 * 128)) + q;
-                    // The row loop is software-pipelined by hand: while row r is decoded, the activation fragment of row
-                    // r + 1 is already loaded and the barrier of row r + 1 already probed (a probe answers after a few
-                    // hundred cycles), so neither latency sits between two rows.
+                    // The rows of this stretch are walked run by run: a run is the part of one stream chunk that lies inside
+                    // the stretch.  Everything that happens once per chunk (barrier, probe of the next chunk, hand-back of the
+                    // slot) is outside the row loop, and a run without a partial row takes the loop that tests nothing per
+                    // tile.  The activation fragment of the next row is loaded while a row is decoded.  Lanes whose
+                    // activation row does not exist (g >= rows) multiply whatever the last row holds: column n of the
+                    // product depends on column n of the activations only, and those columns are never stored.
                     uint32_t p0 = xfrag[0], p1 = xfrag[4];
-#pragma unroll 1      // measured: unrolling this loop by 2 or 4 rows makes the step 8 % and 13 % slower
-                    for (int r = 0; r < nrows; ++r) {
+                    xfrag += 8;
+#pragma unroll 1
+                    for (int r = 0; r < nrows;) {
                         const int tk = tk0 + r;
-                        uint32_t bx[NB][4];
-                        if (g >= rows) { p0 = 0; p1 = 0; }
-                        if constexpr (MODE == 0) {
-                            bx[0][0] = prmt(p0, p0, 0x1010); bx[0][1] = prmt(p0, p0, 0x3232);
-                            bx[0][2] = prmt(p1, p1, 0x1010); bx[0][3] = prmt(p1, p1, 0x3232);
-                        } else {
-                            bx[0][0] = p0; bx[0][1] = p1; bx[0][2] = 0; bx[0][3] = 0;
+                        const int ri = (tk - tk_first) & (R - 1);               // row inside its chunk
+                        const int run = min(R - ri, nrows - r);
+                        if (ri == 0) {
+                            if (!ready && !copy_lost && !mbar_wait(bars + slot, parity)) copy_lost = true;   // after a lost copy: no more waits
+                            const int nslot = slot + 1 == SLOTS ? 0 : slot + 1;
+                            ready = mbar_test_wait(bars + nslot, slot + 1 == SLOTS ? parity ^ 1u : parity);
                         }
-                        if (!ready && !mbar_wait(bars + slot, parity)) copy_lost = true;
-                        const int nslot = slot + 1 == DEPTH ? 0 : slot + 1;
-                        const uint32_t nparity = slot + 1 == DEPTH ? parity ^ 1u : parity;
-                        ready = mbar_test_wait(bars + nslot, nparity);
-                        if (r + 1 < nrows) { p0 = xfrag[(r + 1) * 8]; p1 = xfrag[(r + 1) * 8 + 4]; }
-                        const uint32_t* row_words = ring + slot * kRowWords;
-                        const int lo = tk == tk_first ? lo_first : 0, hi = tk == tk_last ? hi_last : 8;
-                        if (lo == 0 && hi == 8) qmv_row<K, CB, NB, MODE, true>(row_words, geom, 0, 8, bx, acc);
-                        else qmv_row<K, CB, NB, MODE, false>(row_words, geom, lo, hi, bx, acc);
-                        __syncwarp();                           // every lane has read the slot
-                        if (cur.valid) {
-                            if (lane == 0) {
-                                mbar_expect_tx(bars + slot, kRowBytes);
-                                bulk_copy_g2s(ring + slot * kRowWords, cur.src, kRowBytes, bars + slot);
+                        const uint32_t* row_words = ring + (slot * R + ri) * kRowWords;
+                        const bool partial = (tk == tk_first && lo_first != 0) || (tk + run - 1 == tk_last && hi_last != 8);
+                        if (!partial) {
+#pragma unroll 1
+                            for (int j = 0; j < run; ++j) {
+                                uint32_t bx[NB][4];
+                                stack_fragment<MODE>(p0, p1, bx[0]);
+                                p0 = xfrag[0]; p1 = xfrag[4];                   // one row past the stretch at most: inside the warp's buffer
+                                xfrag += 8;
+                                qmv_row<K, CB, NB, MODE, true>(row_words, geom, 0, 8, bx, acc);
+                                row_words += kRowWords;
                             }
-                            cur.next(lite, a.n_ops, wid);
+                        } else {
+#pragma unroll 1
+                            for (int j = 0; j < run; ++j) {
+                                uint32_t bx[NB][4];
+                                stack_fragment<MODE>(p0, p1, bx[0]);
+                                p0 = xfrag[0]; p1 = xfrag[4];
+                                xfrag += 8;
+                                const int lo = tk + j == tk_first ? lo_first : 0, hi = tk + j == tk_last ? hi_last : 8;
+                                qmv_row<K, CB, NB, MODE, false>(row_words, geom, lo, hi, bx, acc);
+                                row_words += kRowWords;
+                            }
                         }
-                        slot = nslot;
-                        parity = nparity;
+                        r += run;
+                        if (ri + run == R || tk0 + r > tk_last) {               // the chunk is consumed: its slot takes the next one
+                            __syncwarp();                                       // every lane has read the slot
+                            if (cur.valid) refill(slot);
+                            if (++slot == SLOTS) { slot = 0; parity ^= 1u; }
+                        }
                     }
                     tk0 = tk_end;
                 }
