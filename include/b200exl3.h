@@ -272,6 +272,16 @@ typedef struct {
     const uint16_t* d_residual;
     uint16_t* d_residual_out;
     float* d_sumsq_out;
+    /* epilogue 2 (a group of exactly three members [q | k | v] with 128-wide heads, one row): rotary embedding and
+     * cache append in the kernel that produces q, k and v -- q heads are rotated by the angle of position *d_pos
+     * (pairs (i, i + 64), frequency theta^(-2i/128), as b200exl3_rope_append does) and stored to the group's first
+     * output, k heads are rotated into row *d_pos of d_k_cache [k heads, max_ctx, 128], v heads are copied into
+     * d_v_cache; the group's second and third output pointers are not written */
+    const int32_t* d_pos;
+    float theta;
+    int max_ctx;
+    uint16_t* d_k_cache;
+    uint16_t* d_v_cache;
 } b200exl3_prologue;
 typedef struct b200exl3_tp b200exl3_tp;
 int b200exl3_linear_forward_fused(const b200exl3_linear* handle, const b200exl3_prologue* prologue, b200exl3_tp* tp_or_null,
@@ -380,7 +390,10 @@ int b200exl3_rope_append(uint16_t* d_q_f16, const uint16_t* d_k_f16, const uint1
                          int head_dim, const int32_t* d_pos, float theta, int max_ctx, uint16_t* d_k_cache_f16,
                          uint16_t* d_v_cache_f16, b200exl3_stream stream);
 /* softmax(q k^T * scale) v for one query row per head against keys 0..*d_pos of the caches (grouped-query: heads /
- * kv_heads query heads share a key head), fp32 inside, split over the context; head_dim must be 128. */
+ * kv_heads query heads share a key head), fp32 inside, split over the context and merged in split order by the last
+ * CTA to arrive: one launch; head_dim must be 128.  The workspace starts with arrival counters: clear it
+ * once before the first call (b200exl3_memset); every call leaves them zero.  Calls that overlap on the
+ * GPU need workspaces of their own. */
 int b200exl3_attention_workspace_bytes(int heads, int kv_heads, size_t* out_bytes);
 int b200exl3_attention_decode(const uint16_t* d_q_f16, const uint16_t* d_k_cache_f16, const uint16_t* d_v_cache_f16, int heads,
                               int kv_heads, int head_dim, const int32_t* d_pos, int max_ctx, float scale, uint16_t* d_out_f16,

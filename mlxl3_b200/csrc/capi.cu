@@ -499,6 +499,14 @@ static int forward_common(const LayerCore& c, const void* d_x, int x_dtype, cons
             a.pro_eps = pro->eps;
             a.pro_sumsq = pro->d_sumsq;
         }
+        if (pro && pro->epilogue == 2) {
+            a.epilogue = 2;
+            a.epi_pos = pro->d_pos;
+            a.epi_log2_theta = log2f(pro->theta);
+            a.epi_max_ctx = pro->max_ctx;
+            a.epi_k_cache = reinterpret_cast<__half*>(pro->d_k_cache);
+            a.epi_v_cache = reinterpret_cast<__half*>(pro->d_v_cache);
+        }
         if (pro && pro->epilogue == 1) {
             a.epilogue = 1;
             a.epi_residual = reinterpret_cast<const __half*>(pro->d_residual);
@@ -569,7 +577,13 @@ static int check_prologue(const b200exl3_prologue* pro, const void* d_x, int64_t
     if ((pro->kind == 1 || pro->kind == 3) && (!pro->d_weight || !(pro->eps >= 0.0f)))
         return fail("the RMSNorm prologue needs a weight and a non-negative epsilon");
     if (pro->kind == 3 && !pro->d_sumsq) return fail("the RMSNorm prologue of kind 3 needs the block sums of squares");
-    if (pro->epilogue < 0 || pro->epilogue > 1) return fail("unknown epilogue kind %d", pro->epilogue);
+    if (pro->epilogue < 0 || pro->epilogue > 2) return fail("unknown epilogue kind %d", pro->epilogue);
+    if (pro->epilogue == 2) {
+        if (rows != 1) return fail("the rotary epilogue takes one row");
+        if (!pro->d_pos || !pro->d_k_cache || !pro->d_v_cache || pro->max_ctx <= 0 || !(pro->theta > 1.0f))
+            return fail("the rotary epilogue needs a position, both caches, their length and a base above 1");
+        if (!aligned16(pro->d_k_cache) || !aligned16(pro->d_v_cache)) return fail("device pointers must be 16-byte aligned");
+    }
     if (pro->epilogue == 1 && (!pro->d_residual || !pro->d_residual_out || !pro->d_sumsq_out)) return fail("the residual epilogue needs its three buffers");
     if (!aligned16(pro->d_residual) || !aligned16(pro->d_residual_out)) return fail("device pointers must be 16-byte aligned");
     if (pro->kind == 1 && pro->d_sum == d_x) return fail("the RMSNorm prologue cannot store the sum over its own input");
@@ -583,6 +597,7 @@ int b200exl3_linear_forward_fused(const b200exl3_linear* h, const b200exl3_prolo
     if (!h) return fail("NULL handle");
     if (!d_x || (!d_y && !(pro && pro->epilogue == 1))) return fail("NULL buffer");
     if (check_prologue(pro, d_x, rows)) return -1;
+    if (pro->epilogue == 2) return fail("the rotary epilogue belongs to a [q | k | v] group");
     if (tp && rows * (h->c.out / 128) > tp->max_units) return fail("units exceed the exchange buffers' %d", tp->max_units);
     void* ys[1] = {d_y};
     return forward_common(h->c, d_x, kF16, nullptr, rows, ys, nullptr, ws, ws_bytes, as_stream(s), tp, pro);
@@ -740,10 +755,15 @@ int b200exl3_group_forward_fused(const b200exl3_group* h, const b200exl3_prologu
                                  void* ws, size_t ws_bytes, b200exl3_stream s) {
     if (!h) return fail("NULL handle");
     if (!d_x || !d_ys) return fail("NULL buffer");
-    for (int g = 0; g < h->c.groups; ++g)
-        if (!d_ys[g]) return fail("NULL buffer");
     if (check_prologue(pro, d_x, rows)) return -1;
-    if (pro->epilogue != 0) return fail("the residual epilogue belongs to plain layers");
+    for (int g = 0; g < h->c.groups; ++g)
+        if (!d_ys[g] && !(pro->epilogue == 2 && g > 0)) return fail("NULL buffer");       // the rotary epilogue writes k and v to the caches
+    if (pro->epilogue == 1) return fail("the residual epilogue belongs to plain layers");
+    if (pro->epilogue == 2) {
+        const LayerCore& c = h->c;
+        if (c.groups != 3 || c.gout[1] != c.gout[2] || c.gout[0] % 128 || c.gout[1] % 128)
+            return fail("the rotary epilogue needs a group of three members [q | k | v] with 128-wide heads and as many k as v heads");
+    }
     return forward_common(h->c, d_x, kF16, nullptr, rows, d_ys, nullptr, ws, ws_bytes, as_stream(s), nullptr, pro);
 }
 

@@ -108,6 +108,11 @@ struct QmvArgs {
     // Fused epilogue (plain fp16 layer): 1 = the output is added to the residual rows `epi_residual` [rows, out]; the sum
     // goes to `epi_sum` (may be the residual buffer itself: a column block is read and written by one warp only) and the
     // sum of its squares over each 128-block to `epi_sumsq` [rows, out / 128] for the next layer's RMSNorm.
+    const int* epi_pos;        // epilogue 2 (a [q | k | v] group, one row): position of the token ...
+    float epi_log2_theta;      // ... log2 of the rotary base ...
+    int epi_max_ctx;           // ... rows per head of the caches ...
+    __half* epi_k_cache;       // ... [k heads, max_ctx, 128]: rotated keys go to row *epi_pos
+    __half* epi_v_cache;       // ... values are copied there
     int epilogue;
     const __half* epi_residual;
     __half* epi_sum;

@@ -130,7 +130,9 @@ __global__ void rope_append_kernel(__half* __restrict__ q, const __half* __restr
 // (key slot kg = lane / 8, slice j = lane % 8): a warp instruction loads four whole 256-byte cache rows, fully
 // coalesced, and lane (kg, j) holds 16 of the 128 dimensions of key kg.  Scores are reduced over the 8 slices with
 // three shuffles for all four keys at once; the softmax is the online form in fp32; the partial result of a CTA is
-// (max, sum, unnormalised output) per query head, combined over splits by a second small kernel.
+// (max, sum, unnormalised output) per query head.  The CTAs of a (key head, pass) count their arrivals; the last one
+// merges the splits in split order and normalises, so the result does not depend on who was last and the whole
+// attention is one launch.  The counters live in the caller's workspace: zero before the first use, zero after every call.
 namespace {
 
 constexpr int kAttnDim = 128;
@@ -138,9 +140,10 @@ constexpr int kAttnWarps = 4;
 constexpr int kAttnHeadsPerPass = 4;
 
 __global__ void __launch_bounds__(kAttnWarps * 32)
-attn_partial_kernel(const __half* __restrict__ q, const __half* __restrict__ k_cache, const __half* __restrict__ v_cache,
+attention_decode_kernel(const __half* __restrict__ q, const __half* __restrict__ k_cache, const __half* __restrict__ v_cache,
                     int heads, int kv_heads, const int* __restrict__ pos_ptr, int max_ctx, float scale_log2e,
-                    float* __restrict__ part_acc, float2* __restrict__ part_ml) {
+                    float* __restrict__ part_acc, float2* __restrict__ part_ml, unsigned int* __restrict__ arrived,
+                    __half* __restrict__ out) {
     pdl_launch_dependents();
     pdl_wait();
     constexpr int GQ = kAttnHeadsPerPass;
@@ -248,35 +251,65 @@ attn_partial_kernel(const __half* __restrict__ q, const __half* __restrict__ k_c
         float mm = -INFINITY;
 #pragma unroll
         for (int w = 0; w < kAttnWarps; ++w) mm = fmaxf(mm, s_m[w][h]);
-        float ll = 0.0f, out = 0.0f;
+        float ll = 0.0f, o = 0.0f;
 #pragma unroll
         for (int w = 0; w < kAttnWarps; ++w) {
             const float c = s_m[w][h] == -INFINITY ? 0.0f : exp2f(s_m[w][h] - mm);
             ll = fmaf(s_l[w][h], c, ll);
-            out = fmaf(s_acc[w][h][d], c, out);
+            o = fmaf(s_acc[w][h][d], c, o);
         }
         const int64_t slot = static_cast<int64_t>(head0 + h) * splits + split;
-        part_acc[slot * kAttnDim + d] = out;
+        part_acc[slot * kAttnDim + d] = o;
         if (d == 0) part_ml[slot] = make_float2(mm, ll);
     }
-}
-
-// one CTA per query head, one thread per dimension: merges the splits in split order and normalises
-__global__ void __launch_bounds__(kAttnDim)
-attn_combine_kernel(const float* __restrict__ part_acc, const float2* __restrict__ part_ml, int splits, __half* __restrict__ out) {
-    pdl_launch_dependents();
-    pdl_wait();
-    const int head = blockIdx.x, d = threadIdx.x;
-    float mm = -INFINITY;
-    for (int s = 0; s < splits; ++s) mm = fmaxf(mm, part_ml[static_cast<int64_t>(head) * splits + s].x);
-    float ll = 0.0f, o = 0.0f;
-    for (int s = 0; s < splits; ++s) {
-        const float2 ml = part_ml[static_cast<int64_t>(head) * splits + s];
-        const float c = ml.x == -INFINITY ? 0.0f : exp2f(ml.x - mm);
-        ll = fmaf(ml.y, c, ll);
-        o = fmaf(part_acc[(static_cast<int64_t>(head) * splits + s) * kAttnDim + d], c, o);
+    // ---- the last CTA of this (key head, pass) merges the splits: thread d owns dimension d --------------------------
+    __shared__ bool s_last;
+    __threadfence();                                            // this CTA's partials before its arrival
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int before = atomicAdd(arrived + blockIdx.y, 1u);
+        s_last = before + 1 == static_cast<unsigned int>(splits);
+        if (s_last) arrived[blockIdx.y] = 0;                    // the next call starts from zero
     }
-    out[static_cast<int64_t>(head) * kAttnDim + d] = __float2half_rn(o / ll);
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    // warp h merges query head h: lane i weighs splits i and i + 32 (at most 64 splits), then every lane adds its four
+    // dimensions over the splits in split order, eight loads in flight
+    if (warp < nheads) {
+        const int64_t base = static_cast<int64_t>(head0 + warp) * splits;
+        const float2 ml0 = lane < splits ? __ldcg(&part_ml[base + lane]) : make_float2(-INFINITY, 0.0f);
+        const float2 ml1 = lane + 32 < splits ? __ldcg(&part_ml[base + lane + 32]) : make_float2(-INFINITY, 0.0f);
+        float mm = fmaxf(ml0.x, ml1.x);
+#pragma unroll
+        for (int step = 16; step >= 1; step >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, step));
+        const float c0 = ml0.x == -INFINITY ? 0.0f : exp2f(ml0.x - mm), c1 = ml1.x == -INFINITY ? 0.0f : exp2f(ml1.x - mm);
+        float ll = 0.0f;
+        float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+        const float* acc_base = part_acc + base * kAttnDim + lane * 4;
+#pragma unroll 1
+        for (int s0 = 0; s0 < splits; s0 += 8) {
+            float4 part[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                if (s0 + i < splits) part[i] = __ldcg(reinterpret_cast<const float4*>(acc_base + static_cast<int64_t>(s0 + i) * kAttnDim));
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int sp = s0 + i;                                              // uniform over the warp
+                const float c = __shfl_sync(0xffffffffu, sp < 32 ? c0 : c1, sp & 31);
+                const float l_s = __shfl_sync(0xffffffffu, sp < 32 ? ml0.y : ml1.y, sp & 31);
+                if (sp < splits) {
+                    ll = fmaf(l_s, c, ll);
+                    o.x = fmaf(part[i].x, c, o.x); o.y = fmaf(part[i].y, c, o.y);
+                    o.z = fmaf(part[i].z, c, o.z); o.w = fmaf(part[i].w, c, o.w);
+                }
+            }
+        }
+        const float inv = 1.0f / ll;
+        const __half2 lo = __floats2half2_rn(o.x * inv, o.y * inv), hi = __floats2half2_rn(o.z * inv, o.w * inv);
+        *reinterpret_cast<uint2*>(out + static_cast<int64_t>(head0 + warp) * kAttnDim + lane * 4) =
+            make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+    }
 }
 
 }  // namespace
@@ -405,7 +438,9 @@ int attention_splits(int kv_heads, int heads) {
 
 size_t attention_workspace_bytes(int heads, int kv_heads) {
     const size_t splits = static_cast<size_t>(attention_splits(kv_heads, heads));
-    return heads * splits * (kAttnDim * sizeof(float) + sizeof(float2));
+    const size_t passes = (heads / kv_heads + kAttnHeadsPerPass - 1) / kAttnHeadsPerPass;
+    // [arrival counters, one per (key head, pass): zero before the first use | partial outputs | partial (max, sum)]
+    return 256 * ((kv_heads * passes * sizeof(unsigned int) + 255) / 256) + heads * splits * (kAttnDim * sizeof(float) + sizeof(float2));
 }
 
 cudaError_t launch_attention_decode(const __half* q, const __half* k_cache, const __half* v_cache, int heads, int kv_heads, int dim,
@@ -413,12 +448,11 @@ cudaError_t launch_attention_decode(const __half* q, const __half* k_cache, cons
     if (dim != kAttnDim || kv_heads <= 0 || heads % kv_heads) return cudaErrorInvalidValue;
     const int splits = attention_splits(kv_heads, heads);
     const int passes = (heads / kv_heads + kAttnHeadsPerPass - 1) / kAttnHeadsPerPass;
-    float* part_acc = static_cast<float*>(workspace);
+    unsigned int* arrived = static_cast<unsigned int*>(workspace);
+    float* part_acc = reinterpret_cast<float*>(static_cast<char*>(workspace) + 256 * ((kv_heads * passes * sizeof(unsigned int) + 255) / 256));
     float2* part_ml = reinterpret_cast<float2*>(part_acc + static_cast<size_t>(heads) * splits * kAttnDim);
-    cudaError_t e = launch_dependent(attn_partial_kernel, dim3(splits, kv_heads * passes), dim3(kAttnWarps * 32), 0, stream, q, k_cache, v_cache,
-                                     heads, kv_heads, pos, max_ctx, scale * 1.4426950408889634f, part_acc, part_ml);
-    if (e != cudaSuccess) return e;
-    return launch_dependent(attn_combine_kernel, dim3(heads), dim3(kAttnDim), 0, stream, part_acc, part_ml, splits, out);
+    return launch_dependent(attention_decode_kernel, dim3(splits, kv_heads * passes), dim3(kAttnWarps * 32), 0, stream, q, k_cache, v_cache,
+                            heads, kv_heads, pos, max_ctx, scale * 1.4426950408889634f, part_acc, part_ml, arrived, out);
 }
 
 int head_candidates() { return 4 * sm_count(); }

@@ -301,6 +301,37 @@ __device__ __forceinline__ void qmv_finish_block(const QmvArgs& p, int cblock, u
                 }
                 const int grp = qmv_group_of(p, cblock);
                 const int gcol = col - p.gcol0[grp];
+                if (p.epilogue == 2) {
+                    // [q | k | v] with 128-wide heads: this block is one head.  Rotary embedding of q and k heads (pairs
+                    // (i, i + 64): lane L holds columns 4L..4L+3, its partner is lane L ^ 16), keys and values go
+                    // straight into row `pos` of the caches.
+                    int pos = __ldg(p.epi_pos);
+                    pos = pos < 0 ? 0 : (pos >= p.epi_max_ctx ? p.epi_max_ctx - 1 : pos);
+                    __align__(8) __half y[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        y[j] = __hmul_rn(h[j], sv[j]);
+                        if (p.bias) y[j] = __hadd_rn(y[j], p.bias[col + j]);
+                    }
+                    if (grp < 2) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const float mine = __half2float(y[j]);
+                            const float other = __shfl_xor_sync(0xffffffffu, mine, 16);
+                            const int i = (lane & 15) * 4 + j;
+                            const float inv_freq = exp2f(-p.epi_log2_theta * static_cast<float>(2 * i) / 128.0f);
+                            float sn, cs;
+                            sincosf(static_cast<float>(pos) * inv_freq, &sn, &cs);
+                            const float a0 = lane < 16 ? mine : other, b0 = lane < 16 ? other : mine;
+                            y[j] = __float2half_rn(lane < 16 ? a0 * cs - b0 * sn : a0 * sn + b0 * cs);
+                        }
+                    }
+                    __half* dst = grp == 0 ? reinterpret_cast<__half*>(p.gy[0]) + gcol
+                                           : (grp == 1 ? p.epi_k_cache : p.epi_v_cache) +
+                                                 (static_cast<int64_t>(gcol >> 7) * p.epi_max_ctx + pos) * 128 + lane * 4;
+                    *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(y);
+                    continue;
+                }
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
                     store_from_half(p.gy[grp], p.y_dtype, static_cast<int64_t>(row) * p.gout[grp] + gcol + j,

@@ -48,6 +48,13 @@ def attention_workspace_bytes(heads: int, kv_heads: int) -> int:
     return out.value
 
 
+def new_attention_workspace(heads: int, kv_heads: int) -> DeviceBuffer:
+    """Scratch of ``attention_decode``: it starts with arrival counters that must be zero before the first call."""
+    ws = DeviceBuffer(attention_workspace_bytes(heads, kv_heads))
+    ws.fill(0)
+    return ws
+
+
 def attention_decode(d_q: int, d_k_cache: int, d_v_cache: int, heads: int, kv_heads: int, head_dim: int, d_pos: int, max_ctx: int,
                      scale: float, d_out: int, workspace: DeviceBuffer, stream: Stream = DEFAULT_STREAM) -> None:
     _lib.call("b200exl3_attention_decode", _p(d_q), _p(d_k_cache), _p(d_v_cache), heads, kv_heads, head_dim, _p(d_pos), max_ctx,
@@ -179,7 +186,7 @@ class DenseDecoder:
         self.d_best_value, self.d_best_index = DeviceBuffer(16), DeviceBuffer(16)
         ops = [e[n] for e in self.layers for n in ("qkv", "o", "gu", "down")]
         self.ws = new_workspace(max(op.workspace_bytes(1) for op in ops))
-        self.attn_ws = DeviceBuffer(attention_workspace_bytes(self.heads, self.kv_heads))
+        self.attn_ws = new_attention_workspace(self.heads, self.kv_heads)
         self.head_ws = DeviceBuffer(head_workspace_bytes())
         self.graph = None
         self.store_logits = False
@@ -228,7 +235,7 @@ class DenseDecoder:
             swiglu(b["gate"].ptr, b["up"].ptr, self.ffn, b["act"].ptr, s)
             self._row(e["down"], b["act"].ptr, b["down"].ptr)
             pending = b["down"].ptr
-            count += 10
+            count += 9
         rms_norm(b["h"].ptr, pending, self.final_norm.ptr, 1, c.hidden, c.eps, b["h"].ptr, b["xn"].ptr, s)
         head_argmax(b["xn"].ptr, self.head_weight.ptr, self.vocab, c.hidden, self.rank * self.vocab, b["logits"].ptr if self.store_logits else 0,
                     self.d_best_value.ptr, self.d_best_index.ptr, self.head_ws, s)
@@ -238,7 +245,8 @@ class DenseDecoder:
         """The same step with the glue folded into the projections' kernels: the residual add runs in the epilogue of
         o and down (which hold every output block in registers) and leaves the sum of squares of each 128-block, the
         RMSNorm of the next projection is its input-rotation prologue (it only adds those block sums), and SwiGLU is the
-        prologue of down.  7 launches per block instead of 10."""
+        prologue of down, the rotary embedding and the cache append are the epilogue of [q|k|v], and the attention merges its
+        splits itself.  5 launches per block instead of 10."""
         c, b, s = self.config, self.buf, self.stream
         h, sq = b["h"].ptr, self.sumsq.ptr
         embed(self.embed_table.ptr, self.d_token.ptr, 1, c.vocab, c.hidden, h, s)
@@ -246,9 +254,14 @@ class DenseDecoder:
         for e in self.layers:
             pro = Prologue.rms_norm(e["attn_norm"].ptr, c.eps) if first else Prologue.rms_norm_from_blocks(e["attn_norm"].ptr, c.eps, sq)
             first = False
-            e["qkv"].forward_fused_device(pro, h, 1, [b["q"].ptr, b["k"].ptr, b["v"].ptr], self.ws, s)
-            rope_append(b["q"].ptr, b["k"].ptr, b["v"].ptr, self.heads, self.kv_heads, c.head_dim, self.d_pos.ptr, c.theta, c.max_ctx,
-                        e["k_cache"].ptr, e["v_cache"].ptr, s)
+            if c.head_dim == 128:
+                # rotary embedding and cache append in the kernel that produces q, k and v
+                e["qkv"].forward_fused_device(pro.with_rope(self.d_pos.ptr, c.theta, c.max_ctx, e["k_cache"].ptr, e["v_cache"].ptr), h, 1,
+                                              [b["q"].ptr, b["k"].ptr, b["v"].ptr], self.ws, s)
+            else:
+                e["qkv"].forward_fused_device(pro, h, 1, [b["q"].ptr, b["k"].ptr, b["v"].ptr], self.ws, s)
+                rope_append(b["q"].ptr, b["k"].ptr, b["v"].ptr, self.heads, self.kv_heads, c.head_dim, self.d_pos.ptr, c.theta, c.max_ctx,
+                            e["k_cache"].ptr, e["v_cache"].ptr, s)
             attention_decode(b["q"].ptr, e["k_cache"].ptr, e["v_cache"].ptr, self.heads, self.kv_heads, c.head_dim, self.d_pos.ptr, c.max_ctx,
                              c.head_dim ** -0.5, b["att"].ptr, self.attn_ws, s)
             e["o"].forward_fused_device(Prologue.plain().with_residual(h, h, sq), b["att"].ptr, 1, 0, self.ws, s, tp=self.tp)
@@ -259,7 +272,7 @@ class DenseDecoder:
         self.hidden_name = "h"
         head_argmax(b["xn"].ptr, self.head_weight.ptr, self.vocab, c.hidden, self.rank * self.vocab, b["logits"].ptr if self.store_logits else 0,
                     self.d_best_value.ptr, self.d_best_index.ptr, self.head_ws, s)
-        self.launches_per_step = 7 * len(self.layers) + 4
+        self.launches_per_step = (5 if c.head_dim == 128 else 7) * len(self.layers) + 4
 
     def record(self) -> None:
         self._launch()                                  # every distinct call once before recording

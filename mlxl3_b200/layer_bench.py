@@ -166,9 +166,14 @@ def step_main(args) -> None:
             done = s[:, 8:]
             fin = s[~np.isnan(s[:, 7])]
             end = float(np.nanmax(fin[:, 7])) if len(fin) else float("nan")
-            print(f"{i:3d} {name:8s} start {end_prev:8.2f} | boundary passed {np.nanmin(s[:, 0]):8.2f} | rotated {np.nanmax(s[:, 1]):8.2f} | "
+            owner = s[~np.isnan(s[:, 7])]                # CTAs that finished a block of this layer (their last one)
+            chain = ""
+            if len(owner):
+                chain = (f" | finish of a block: pieces waited {np.nanmedian(owner[:, 6] - owner[:, 4]):5.2f} (max {np.nanmax(owner[:, 6] - owner[:, 4]):5.2f}), "
+                         f"rotate+store {np.nanmedian(owner[:, 7] - owner[:, 6]):5.2f}")
+            print(f"{i:3d} {name:8s} start {end_prev:8.2f} | boundary passed {np.nanmin(s[:, 0]):8.2f}..{np.nanmax(s[:, 0]):8.2f} | rotated {np.nanmax(s[:, 1]):8.2f} | "
                   f"tiles done p50 {np.nanpercentile(done, 50):8.2f} max {np.nanmax(done):8.2f} | last block stored {end:8.2f} | "
-                  f"layer {end - end_prev:6.2f} us")
+                  f"layer {end - end_prev:6.2f} us{chain}")
             end_prev = end
 
 

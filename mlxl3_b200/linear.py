@@ -77,7 +77,8 @@ class Prologue(ctypes.Structure):
     (fp16, 1 or 2 rows)."""
     _fields_ = [("kind", ctypes.c_int), ("d_aux", c_void_p), ("d_weight", c_void_p), ("d_sum", c_void_p), ("eps", ctypes.c_float),
                 ("d_sumsq", c_void_p), ("epilogue", ctypes.c_int), ("d_residual", c_void_p), ("d_residual_out", c_void_p),
-                ("d_sumsq_out", c_void_p)]
+                ("d_sumsq_out", c_void_p), ("d_pos", c_void_p), ("theta", ctypes.c_float), ("max_ctx", ctypes.c_int),
+                ("d_k_cache", c_void_p), ("d_v_cache", c_void_p)]
 
     @classmethod
     def rms_norm(cls, d_weight: int, eps: float, d_residual: int = 0, d_sum: int = 0) -> "Prologue":
@@ -100,6 +101,13 @@ class Prologue(ctypes.Structure):
     def with_residual(self, d_residual: int, d_residual_out: int, d_sumsq_out: int) -> "Prologue":
         """Adds the residual epilogue: output + residual -> d_residual_out, block sums of squares -> d_sumsq_out."""
         self.epilogue, self.d_residual, self.d_residual_out, self.d_sumsq_out = 1, d_residual, d_residual_out, d_sumsq_out
+        return self
+
+    def with_rope(self, d_pos: int, theta: float, max_ctx: int, d_k_cache: int, d_v_cache: int) -> "Prologue":
+        """Adds the rotary epilogue of a [q | k | v] group (one row, 128-wide heads): q is rotated into the group's first
+        output, k is rotated and v copied into row ``*d_pos`` of the caches."""
+        self.epilogue, self.d_pos, self.theta, self.max_ctx = 2, d_pos, theta, max_ctx
+        self.d_k_cache, self.d_v_cache = d_k_cache, d_v_cache
         return self
 
 

@@ -83,7 +83,7 @@ def test_attention_decode(gpu, heads, kv_heads, keys, ctx):
     d_q, d_k, d_v = DeviceBuffer.from_numpy(q), DeviceBuffer.from_numpy(kc), DeviceBuffer.from_numpy(vc)
     d_o = DeviceBuffer(q.nbytes)
     d_pos = DeviceBuffer.from_numpy(np.array([keys - 1], np.int32))
-    ws = DeviceBuffer(dec.attention_workspace_bytes(heads, kv_heads))
+    ws = dec.new_attention_workspace(heads, kv_heads)
     dec.attention_decode(d_q.ptr, d_k.ptr, d_v.ptr, heads, kv_heads, dim, d_pos.ptr, ctx, dim ** -0.5, d_o.ptr, ws)
     got = d_o.download((heads, dim), np.float16)
     want = od.attention_decode(q, kc[:, :keys], vc[:, :keys], dim ** -0.5)
@@ -276,4 +276,42 @@ def test_small_decoder_with_glue_kernels_of_their_own(gpu):
         bar_l = 3e-2 * np.abs(want_logits.astype(np.float32)).max()
         assert np.abs(logits.astype(np.float32) - want_logits.astype(np.float32)).max() <= bar_l
         assert float(want_logits[want_best]) - float(want_logits[index]) <= bar_l
-    assert dec.launches_per_step == 10 * config.layers + 4
+    assert dec.launches_per_step == 9 * config.layers + 4
+
+
+def test_rotary_epilogue_matches_the_separate_kernel(gpu):
+    """[q | k | v] with the rotary embedding and the cache append as the group's epilogue against the group's plain forward
+    followed by rope_append: the same rounding points, so the same bits up to the last place of the fp32 rotation."""
+    from mlxl3_b200 import decoder as dec
+    from mlxl3_b200.linear import Prologue
+    from mlxl3_b200.runtime import DeviceBuffer, Stream
+    from tests.gpu_util import random_layer
+    rng = np.random.default_rng(77)
+    hidden, heads, kv_heads, dim, k, max_ctx, theta = 512, 4, 2, 128, 4, 64, 500000.0
+    members = [gpu.Exl3Linear(*random_layer(rng, hidden, n, k), None, k, 0) for n in (heads * dim, kv_heads * dim, kv_heads * dim)]
+    group = gpu.Exl3Group(members)
+    stream = Stream()
+    ws = gpu.new_workspace(group.workspace_bytes(1))
+    x = rng.standard_normal((1, hidden)).astype(np.float16)
+    d_x = DeviceBuffer.from_numpy(x)
+    for pos in (0, 5, 63):
+        d_pos = DeviceBuffer.from_numpy(np.array([pos], np.int32))
+        q0, k0, v0 = (DeviceBuffer(n * dim * 2) for n in (heads, kv_heads, kv_heads))
+        kc0, vc0, kc1, vc1 = (DeviceBuffer(kv_heads * max_ctx * dim * 2) for _ in range(4))
+        for b in (kc0, vc0, kc1, vc1):
+            b.fill(0, stream)
+        group.forward_device(d_x.ptr, gpu.F16, 1, [q0.ptr, k0.ptr, v0.ptr], ws, stream)
+        dec.rope_append(q0.ptr, k0.ptr, v0.ptr, heads, kv_heads, dim, d_pos.ptr, theta, max_ctx, kc0.ptr, vc0.ptr, stream)
+        q1 = DeviceBuffer(heads * dim * 2)
+        group.forward_fused_device(Prologue.plain().with_rope(d_pos.ptr, theta, max_ctx, kc1.ptr, vc1.ptr), d_x.ptr, 1, [q1.ptr, 0, 0], ws, stream)
+        want_q, got_q = q0.download((heads, dim), np.float16, stream), q1.download((heads, dim), np.float16, stream)
+        assert ulps(got_q, want_q).max() <= 1
+        for a, b in ((kc0, kc1), (vc0, vc1)):
+            want, got = a.download((kv_heads, max_ctx, dim), np.float16, stream), b.download((kv_heads, max_ctx, dim), np.float16, stream)
+            assert ulps(got, want).max() <= 1
+            assert np.abs(want[:, pos]).max() > 0 and not np.any(np.delete(got, pos, axis=1))
+    assert gpu.workspace_status(ws) == 0
+    with pytest.raises(gpu.B200Exl3Error, match="one row"):
+        group.forward_fused_device(Prologue.plain().with_rope(d_pos.ptr, theta, max_ctx, kc1.ptr, vc1.ptr), d_x.ptr, 2, [q1.ptr, 0, 0], ws, stream)
+    with pytest.raises(gpu.B200Exl3Error, match="belongs to a"):
+        members[0].forward_fused_device(Prologue.plain().with_rope(d_pos.ptr, theta, max_ctx, kc1.ptr, vc1.ptr), d_x.ptr, 1, q1.ptr, ws, stream)
