@@ -30,6 +30,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 glu_down_input_kernel(const float* __restrict__ ygu, const __half* __restrict__ gu_svh, const __half* __restrict__ down_suh,
                       const uint32_t* __restrict__ selected, int experts, int64_t slots, int hidden, int logical_hidden,
                       __half* __restrict__ xhat, const int* __restrict__ count) {
+    pdl_launch_dependents();                    // the kernel after this one may start; it waits for our memory itself
+    pdl_wait();                                 // what the kernel before this one wrote is visible from here on
     const int lane = threadIdx.x & 31;
     const int blocks_per_row = hidden >> 7;
     if (count != nullptr) slots = min(slots, static_cast<int64_t>(*count));
@@ -71,6 +73,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 finish_and_reduce_kernel(const float* __restrict__ raw, const __half* __restrict__ down_svh,
                          const uint32_t* __restrict__ selected, int experts, const void* __restrict__ scores,
                          int64_t rows, int top_k, int out, void* __restrict__ y) {
+    pdl_launch_dependents();                    // the kernel after this one may start; it waits for our memory itself
+    pdl_wait();                                 // what the kernel before this one wrote is visible from here on
     const int lane = threadIdx.x & 31;
     const int blocks_per_row = out >> 7;
     const int64_t total = rows * blocks_per_row;
@@ -133,9 +137,8 @@ cudaError_t launch_glu_down_input(const float* ygu, const __half* gu_svh, const 
                                   int experts, int64_t slots, int hidden, int logical_hidden, __half* xhat,
                                   cudaStream_t stream, const int* count) {
     if (slots == 0) return cudaSuccess;
-    glu_down_input_kernel<<<grid_for(slots * (hidden / 128)), kWarpsPerBlock * 32, 0, stream>>>(
-        ygu, gu_svh, down_suh, selected, experts, slots, hidden, logical_hidden, xhat, count);
-    return cudaGetLastError();
+    return launch_dependent(glu_down_input_kernel, dim3(grid_for(slots * (hidden / 128))), dim3(kWarpsPerBlock * 32), 0, stream, ygu, gu_svh,
+                            down_suh, selected, experts, slots, hidden, logical_hidden, xhat, count);
 }
 
 cudaError_t launch_finish_and_reduce(const float* raw, const __half* down_svh, const uint32_t* selected, int experts,
@@ -143,13 +146,8 @@ cudaError_t launch_finish_and_reduce(const float* raw, const __half* down_svh, c
                                      cudaStream_t stream) {
     if (rows == 0) return cudaSuccess;
     const unsigned grid = grid_for(rows * (out / 128));
-    if (score_dtype == kF32)
-        finish_and_reduce_kernel<true><<<grid, kWarpsPerBlock * 32, 0, stream>>>(raw, down_svh, selected, experts, scores,
-                                                                                 rows, top_k, out, y);
-    else
-        finish_and_reduce_kernel<false><<<grid, kWarpsPerBlock * 32, 0, stream>>>(raw, down_svh, selected, experts, scores,
-                                                                                  rows, top_k, out, y);
-    return cudaGetLastError();
+    return launch_dependent(score_dtype == kF32 ? finish_and_reduce_kernel<true> : finish_and_reduce_kernel<false>, dim3(grid),
+                            dim3(kWarpsPerBlock * 32), 0, stream, raw, down_svh, selected, experts, scores, rows, top_k, out, y);
 }
 
 }  // namespace b200exl3
@@ -167,6 +165,8 @@ __global__ void __launch_bounds__(1024)
 route_plan_kernel(const uint32_t* __restrict__ selected, int64_t slots, int experts, int max_segments, int seg_rows,
                   int* __restrict__ seg_count, uint32_t* __restrict__ seg_expert, uint32_t* __restrict__ row_slot,
                   uint32_t* __restrict__ slot_row) {
+    pdl_launch_dependents();                    // the kernel after this one may start; it waits for our memory itself
+    pdl_wait();                                 // what the kernel before this one wrote is visible from here on
     extern __shared__ int s_mem[];
     int* count = s_mem;                 // [experts] rows per expert, then running position
     int* base = s_mem + experts;        // [experts + 1] first segment of each expert
@@ -223,6 +223,8 @@ __global__ void __launch_bounds__(1024)
 route_plan_grouped_kernel(const uint32_t* __restrict__ selected, int64_t slots, int experts, int max_segments, int seg_rows,
                           int* __restrict__ seg_count, uint32_t* __restrict__ seg_expert, uint32_t* __restrict__ row_slot,
                           uint32_t* __restrict__ slot_row) {
+    pdl_launch_dependents();                    // the kernel after this one may start; it waits for our memory itself
+    pdl_wait();                                 // what the kernel before this one wrote is visible from here on
     extern __shared__ int s_mem[];
     int* count = s_mem;                 // [experts] rows per expert
     int* base = s_mem + experts;        // [experts + 1] first segment of each expert
@@ -277,6 +279,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 routed_prepare_padded_kernel(const void* __restrict__ x, int x_dtype, const __half* __restrict__ suh,
                              const uint32_t* __restrict__ seg_expert, const uint32_t* __restrict__ slot_row, int64_t slots,
                              int max_segments, int top_k, int proj, int in, int seg_rows, __half* __restrict__ xhat) {
+    pdl_launch_dependents();                    // the kernel after this one may start; it waits for our memory itself
+    pdl_wait();                                 // what the kernel before this one wrote is visible from here on
     const int lane = threadIdx.x & 31;
     const int blocks_per_row = in >> 7;
     const int64_t total = slots * proj * blocks_per_row;
@@ -305,6 +309,8 @@ glu_down_input_padded_kernel(const float* __restrict__ ygu, const __half* __rest
                              const uint32_t* __restrict__ seg_expert, const uint32_t* __restrict__ row_slot,
                              const int* __restrict__ seg_count, int max_segments, int hidden, int logical_hidden, int seg_rows,
                              __half* __restrict__ xhat) {
+    pdl_launch_dependents();                    // the kernel after this one may start; it waits for our memory itself
+    pdl_wait();                                 // what the kernel before this one wrote is visible from here on
     const int lane = threadIdx.x & 31;
     const int blocks_per_row = hidden >> 7;
     const int64_t total = static_cast<int64_t>(seg_count[0]) * seg_rows * blocks_per_row;
@@ -351,6 +357,8 @@ finish_and_reduce_padded_kernel(const float* __restrict__ raw, const __half* __r
                                 const uint32_t* __restrict__ selected, const uint32_t* __restrict__ slot_row, int experts,
                                 const void* __restrict__ scores, int64_t rows, int top_k, int out, int max_segments, int seg_rows,
                                 void* __restrict__ y) {
+    pdl_launch_dependents();                    // the kernel after this one may start; it waits for our memory itself
+    pdl_wait();                                 // what the kernel before this one wrote is visible from here on
     const int lane = threadIdx.x & 31;
     const int blocks_per_row = out >> 7;
     const int64_t total = rows * blocks_per_row;
@@ -393,22 +401,20 @@ cudaError_t launch_route_plan(const uint32_t* selected, int64_t slots, int exper
     const size_t groups = static_cast<size_t>((slots + 31) / 32);
     const size_t grouped = (2 * static_cast<size_t>(experts) + 1) * sizeof(int) + groups * experts * sizeof(unsigned short);
     if (grouped <= 48 * 1024) {
-        route_plan_grouped_kernel<<<1, 1024, grouped, stream>>>(selected, slots, experts, max_segments, seg_rows, seg_count, seg_expert,
-                                                                row_slot, slot_row);
-        return cudaGetLastError();
+        return launch_dependent(route_plan_grouped_kernel, dim3(1), dim3(1024), grouped, stream, selected, slots, experts, max_segments,
+                                seg_rows, seg_count, seg_expert, row_slot, slot_row);
     }
     const size_t smem = (2 * static_cast<size_t>(experts) + 1) * sizeof(int) + static_cast<size_t>(slots) * sizeof(unsigned short);
     if (smem > 48 * 1024) return cudaErrorInvalidValue;
-    route_plan_kernel<<<1, 1024, smem, stream>>>(selected, slots, experts, max_segments, seg_rows, seg_count, seg_expert, row_slot, slot_row);
-    return cudaGetLastError();
+    return launch_dependent(route_plan_kernel, dim3(1), dim3(1024), smem, stream, selected, slots, experts, max_segments, seg_rows,
+                            seg_count, seg_expert, row_slot, slot_row);
 }
 
 cudaError_t launch_routed_prepare_padded(const void* x, int x_dtype, const __half* suh, const uint32_t* seg_expert,
                                          const uint32_t* slot_row, int64_t slots, int top_k, int proj, int max_segments,
                                          int seg_rows, int in, __half* xhat, cudaStream_t stream) {
-    routed_prepare_padded_kernel<<<grid_for(slots * proj * (in / 128)), kWarpsPerBlock * 32, 0, stream>>>(
-        x, x_dtype, suh, seg_expert, slot_row, slots, max_segments, top_k, proj, in, seg_rows, xhat);
-    return cudaGetLastError();
+    return launch_dependent(routed_prepare_padded_kernel, dim3(grid_for(slots * proj * (in / 128))), dim3(kWarpsPerBlock * 32), 0, stream, x,
+                            x_dtype, suh, seg_expert, slot_row, slots, max_segments, top_k, proj, in, seg_rows, xhat);
 }
 
 cudaError_t launch_glu_down_input_padded(const float* ygu, const __half* gu_svh, const __half* down_suh,
@@ -416,10 +422,9 @@ cudaError_t launch_glu_down_input_padded(const float* ygu, const __half* gu_svh,
                                          int experts, int max_segments, int seg_rows, int hidden, int logical_hidden, __half* xhat,
                                          cudaStream_t stream) {
     (void)experts;
-    glu_down_input_padded_kernel<<<grid_for(static_cast<int64_t>(max_segments) * seg_rows * (hidden / 128)), kWarpsPerBlock * 32, 0,
-                                   stream>>>(ygu, gu_svh, down_suh, seg_expert, row_slot, seg_count, max_segments, hidden,
-                                             logical_hidden, seg_rows, xhat);
-    return cudaGetLastError();
+    return launch_dependent(glu_down_input_padded_kernel, dim3(grid_for(static_cast<int64_t>(max_segments) * seg_rows * (hidden / 128))),
+                            dim3(kWarpsPerBlock * 32), 0, stream, ygu, gu_svh, down_suh, seg_expert, row_slot, seg_count, max_segments, hidden,
+                            logical_hidden, seg_rows, xhat);
 }
 
 cudaError_t launch_finish_and_reduce_padded(const float* raw, const __half* down_svh, const uint32_t* selected,
@@ -427,13 +432,9 @@ cudaError_t launch_finish_and_reduce_padded(const float* raw, const __half* down
                                             int64_t rows, int top_k, int out, int max_segments, int seg_rows, void* y, cudaStream_t stream) {
     if (rows == 0) return cudaSuccess;
     const unsigned grid = grid_for(rows * (out / 128));
-    if (score_dtype == kF32)
-        finish_and_reduce_padded_kernel<true><<<grid, kWarpsPerBlock * 32, 0, stream>>>(raw, down_svh, selected, slot_row, experts,
-                                                                                        scores, rows, top_k, out, max_segments, seg_rows, y);
-    else
-        finish_and_reduce_padded_kernel<false><<<grid, kWarpsPerBlock * 32, 0, stream>>>(raw, down_svh, selected, slot_row, experts,
-                                                                                         scores, rows, top_k, out, max_segments, seg_rows, y);
-    return cudaGetLastError();
+    return launch_dependent(score_dtype == kF32 ? finish_and_reduce_padded_kernel<true> : finish_and_reduce_padded_kernel<false>, dim3(grid),
+                            dim3(kWarpsPerBlock * 32), 0, stream, raw, down_svh, selected, slot_row, experts, scores, rows, top_k, out,
+                            max_segments, seg_rows, y);
 }
 
 }  // namespace b200exl3
