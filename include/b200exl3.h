@@ -60,7 +60,9 @@ int b200exl3_version(void);
  * of more than 8 rows also go through the small-batch kernel (16 rows per launch) instead of the tensor-core product; default 1),
  * "qmm_splits" (input splits of the tensor-core product, 0 = chosen by a cost model; set it before asking for
  * workspace sizes), "moe_sorted" (0 = the expert block runs one row per slot for any batch instead of grouping
- * slots by expert for larger batches; set it before asking for workspace sizes), "qmm_trace_buffer" (device address of a uint64 [CTAs, 8] array that receives nanosecond
+ * slots by expert for larger batches; set it before asking for workspace sizes), "moe_fused" (1 = a small batch of the
+ * expert block runs its SwiGLU glue and its weighted reduction as the prologue and the epilogue of the down product, two
+ * launches instead of four; same bits either way, measured no faster; default 0), "qmm_trace_buffer" (device address of a uint64 [CTAs, 8] array that receives nanosecond
  * stamps of the tensor-core kernel's phases: start, set up, decoders done, MMAs issued, accumulator ready,
  * epilogue done, end, activation copies issued; 0 = off), "tp_wait_ms" (how long a rank waits for the other ranks'
  * words inside a tensor- or expert-parallel kernel before it gives up with status 4; default 4000), "stack_wait_ms"

@@ -13,6 +13,9 @@
 namespace b200exl3 {
 
 __device__ __forceinline__ float round_half(float v) { return __half2float(__float2half_rn(v)); }
+// SiLU of the expert glue (native/src/moe.rs:486): the exponential is evaluated in fp32 (expf); the reference's Metal
+// `exp` is a fast-math intrinsic whose last bits are not specified, so this glue is compared with a tolerance.
+__device__ __forceinline__ float glu_silu(float v) { return __fdiv_rn(v, __fadd_rn(1.0f, expf(-v))); }
 
 // round_mid / round_end: fp16 rounding after stride 8 / stride 64.  The MoE activation glue of the
 // reference (native/src/moe.rs:27-53, SiLU models) clears both.

@@ -113,6 +113,16 @@ struct QmvArgs {
     int epi_max_ctx;           // ... rows per head of the caches ...
     __half* epi_k_cache;       // ... [k heads, max_ctx, 128]: rotated keys go to row *epi_pos
     __half* epi_v_cache;       // ... values are copied there
+    // expert-mapped down product of a small batch (one row per slot) with the glue around it in the same launch:
+    // prologue 4 = the SwiGLU glue (native/src/moe.rs:438-533) from the raw gate/up products of the launch before,
+    const float* pro_ygu;      // [slots * 2, in] raw gate and up products (in = the experts' width)
+    const __half* pro_gu_svh;  // [experts, 2, in] output scales of gate and up; suh = [experts, in] input scales of down
+    int pro_logical;           // columns at and past this one are padding: their activation is zero
+    // epilogue 3 = finish_and_reduce (moe.rs:586-609): every slot's block is rotated, scaled by svh[expert] and its score
+    // and parked in yhat; the last slot of a token to arrive adds the token's top_k blocks in slot order into gy[0]
+    const void* epi_scores;    // [slots] routing weights, fp16 or fp32 (the output has their type)
+    int epi_score_f32;
+    int epi_counter0;          // first of the (token, block) arrival counters inside `counters`
     int epilogue;
     const __half* epi_residual;
     __half* epi_sum;

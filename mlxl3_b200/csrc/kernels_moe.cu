@@ -22,9 +22,7 @@ __device__ __forceinline__ int expert_of(const uint32_t* selected, int64_t slot,
     return static_cast<int>(min(selected[slot], static_cast<uint32_t>(experts - 1)));
 }
 
-// The exponential is evaluated in fp32 (expf); the reference's Metal `exp` is a fast-math intrinsic whose
-// last bits are not specified, so this glue is compared with a tolerance.
-__device__ __forceinline__ float silu(float v) { return __fdiv_rn(v, __fadd_rn(1.0f, expf(-v))); }
+__device__ __forceinline__ float silu(float v) { return glu_silu(v); }
 
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 glu_down_input_kernel(const float* __restrict__ ygu, const __half* __restrict__ gu_svh, const __half* __restrict__ down_suh,

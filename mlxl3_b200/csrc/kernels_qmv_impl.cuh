@@ -126,6 +126,42 @@ __device__ __forceinline__ void qmv_rotate_chunk(const void* x, int x_dtype, con
     __syncwarp();
 }
 
+// Prologue 4: the SwiGLU glue of the expert block (native/src/moe.rs:438-533; SiLU path, both rotations without
+// intermediate rounding) from the raw gate and up products of slot `slot`, for input blocks [kb0, kb0 + nblk) of the down
+// product, into the warp's shared memory.  The arithmetic of glu_down_input_kernel, statement by statement.
+__device__ __forceinline__ void qmv_rotate_chunk_glu(const QmvArgs& p, int64_t slot, int64_t expert, int kb0, int nblk, __half* xs, int lane) {
+    const int hidden = p.in;
+    const float scale = had_scale();
+#pragma unroll 1
+    for (int b = 0; b < nblk; ++b) {
+        const int col = (kb0 + b) * 128 + lane * 4;
+        const float4 graw = __ldcg(reinterpret_cast<const float4*>(p.pro_ygu + (slot * 2) * hidden + col));
+        const float4 uraw = __ldcg(reinterpret_cast<const float4*>(p.pro_ygu + (slot * 2 + 1) * hidden + col));
+        float gv[4] = {round_half(graw.x), round_half(graw.y), round_half(graw.z), round_half(graw.w)};
+        float uv[4] = {round_half(uraw.x), round_half(uraw.y), round_half(uraw.z), round_half(uraw.w)};
+        warp_hadamard128<false, false>(gv, lane);
+        warp_hadamard128<false, false>(uv, lane);
+        const __half* sg = p.pro_gu_svh + (expert * 2) * hidden + col;
+        const __half* su = p.pro_gu_svh + (expert * 2 + 1) * hidden + col;
+        const __half* sd = p.suh + expert * hidden + col;
+        float d[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float gate = round_half(__fmul_rn(__fmul_rn(gv[j], scale), __half2float(sg[j])));
+            const float up = round_half(__fmul_rn(__fmul_rn(uv[j], scale), __half2float(su[j])));
+            float act = round_half(__fmul_rn(glu_silu(gate), up));
+            if (col + j >= p.pro_logical) act = 0.0f;
+            d[j] = round_half(__fmul_rn(act, __half2float(sd[j])));
+        }
+        warp_hadamard128<false, false>(d, lane);
+        __align__(8) __half h[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) h[j] = __float2half_rn(__fmul_rn(d[j], scale));
+        *reinterpret_cast<uint2*>(xs + b * 128 + lane * 4) = *reinterpret_cast<uint2*>(h);
+    }
+    __syncwarp();
+}
+
 // 1 / rms of every row of x (+ residual), for the fused RMSNorm prologue: every warp adds the whole row in the same
 // fixed order (lane partial sums over 8-element groups, then a shuffle tree), so all warps of the grid get the same bits.
 __device__ __forceinline__ void qmv_row_inv_rms(const __half* x, const __half* residual, int in, int rows, float eps, int lane,
@@ -269,7 +305,67 @@ __device__ __forceinline__ void qmv_finish_block(const QmvArgs& p, int cblock, u
                 continue;
             }
             const int col = cblock * 128 + lane * 4;              // column in the concatenated output space
-            if (p.yhat != nullptr) {
+            if (p.yhat != nullptr && p.epilogue == 3) {
+                // Expert-mapped down product, one row per slot: virtual block = (slot, block j of the expert's columns).
+                // The block is rotated, scaled by the expert's output scales and the slot's routing weight and parked in
+                // yhat; the last of a token's top_k slots to arrive adds them in slot order (the arithmetic and the order
+                // of finish_and_reduce_kernel, so the same bits).
+                const int slot = cblock / p.map_blocks, j = cblock - slot * p.map_blocks;
+                const int width = p.map_blocks << 7, top_k = p.map_top_k;
+                const int64_t expert = static_cast<int64_t>(min(p.map_selected[slot], static_cast<uint32_t>(p.map_experts - 1)));
+                __half h[4] = {__float2half_rn(a.x), __float2half_rn(a.y), __float2half_rn(a.z), __float2half_rn(a.w)};
+                warp_hadamard128_f16(h, lane);
+                const uint2 svw = *reinterpret_cast<const uint2*>(p.svh + expert * width + j * 128 + lane * 4);
+                const __half* sv = reinterpret_cast<const __half*>(&svw);
+                float v[4];
+                if (p.epi_score_f32) {
+                    const float score = reinterpret_cast<const float*>(p.epi_scores)[slot];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) v[e] = __fmul_rn(__half2float(__hmul_rn(h[e], sv[e])), score);
+                } else {
+                    const __half score = reinterpret_cast<const __half*>(p.epi_scores)[slot];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) v[e] = __half2float(__hmul_rn(__hmul_rn(h[e], sv[e]), score));
+                }
+                __stcg(reinterpret_cast<float4*>(p.yhat + col), make_float4(v[0], v[1], v[2], v[3]));
+                __threadfence();                                // the parked block before the arrival
+                __syncwarp();
+                const int token = slot / top_k;
+                unsigned int* arrived = p.counters + p.epi_counter0 + token * p.map_blocks + j;
+                unsigned int before = 0;
+                if (lane == 0) before = atomicAdd(arrived, 1u);
+                before = __shfl_sync(0xffffffffu, before, 0);
+                if (before != static_cast<unsigned int>(top_k - 1)) continue;
+                __threadfence();
+                if (lane == 0) *arrived = 0;                    // leave the scratch ready for the next call
+                const float* parked = p.yhat + (static_cast<int64_t>(token) * top_k * p.map_blocks + j) * 128 + lane * 4;
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+                for (int t0 = 0; t0 < top_k; t0 += 4) {         // four loads in flight, added in slot order
+                    float4 r[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        if (t0 + i < top_k) r[i] = __ldcg(reinterpret_cast<const float4*>(parked + static_cast<int64_t>(t0 + i) * width));
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        if (t0 + i >= top_k) continue;
+                        const float f[4] = {r[i].x, r[i].y, r[i].z, r[i].w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            if (t0 + i == 0) acc[e] = f[e];
+                            else if (p.epi_score_f32) acc[e] = __fadd_rn(acc[e], f[e]);
+                            else acc[e] = __half2float(__hadd_rn(__float2half_rn(acc[e]), __float2half_rn(f[e])));
+                        }
+                    }
+                }
+                const int64_t at = static_cast<int64_t>(token) * width + j * 128 + lane * 4;
+                if (p.epi_score_f32) {
+                    *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.gy[0]) + at) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+                } else {
+                    __align__(8) __half o16[4] = {__float2half_rn(acc[0]), __float2half_rn(acc[1]), __float2half_rn(acc[2]), __float2half_rn(acc[3])};
+                    *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(p.gy[0]) + at) = *reinterpret_cast<const uint2*>(o16);
+                }
+            } else if (p.yhat != nullptr) {
                 *reinterpret_cast<float4*>(p.yhat + static_cast<int64_t>(row) * p.out + col) = a;
             } else {
                 // a row shard of a tensor-parallel layer first adds the other ranks' sums for this block
@@ -419,6 +515,7 @@ qmv_kernel(const QmvArgs p) {
         int grp = qmv_group_of(p, cblock);
         int tn0 = cblock * 8;                               // first tile column of the block in the weight array
         bool active = true;
+        int map_slot = 0, map_expert = 0;                   // expert-mapped: the slot of this block and its expert
         const void* x_rows = p.x;                           // activations and input scales this block's rotation reads
         int64_t suh_row = grp;
         if (p.map_selected != nullptr) {
@@ -436,6 +533,7 @@ qmv_kernel(const QmvArgs p) {
             // unsigned clamp: an id of 2^31 or more must not turn into a negative index
             const int expert = static_cast<int>(min(p.map_selected[slot], static_cast<uint32_t>(p.map_experts - 1)));
             tn0 = (proj * p.map_stride_blocks + expert * p.map_blocks + j) * 8;
+            map_slot = slot; map_expert = expert;
             grp = sp;                                       // rows of the rotated activations (stride: one slot)
             suh_row = static_cast<int64_t>(expert) * p.map_proj + proj;
             if (p.xhat == nullptr)
@@ -491,7 +589,9 @@ qmv_kernel(const QmvArgs p) {
 
                 // ---- phase 1: rotate this chunk's activations into the warp's shared memory ------------
                 if (p.xhat == nullptr) {
-                    if (p.prologue != 0) {
+                    if (p.prologue == 4) {
+                        qmv_rotate_chunk_glu(p, map_slot, map_expert, kb0, ((tk_end - 1) >> 3) - kb0 + 1, xs, lane);
+                    } else if (p.prologue != 0) {
                         if (!have_inv && p.prologue == 1) {
                             qmv_row_inv_rms(reinterpret_cast<const __half*>(p.x), p.pro_aux, p.in, rows, p.pro_eps, lane, inv_rms);
                             have_inv = true;

@@ -161,3 +161,27 @@ def test_routes_written_by_the_previous_kernel_under_dependent_launch(gpu, pdl):
         want = oracle.switch_glu_forward(*bank, top_k, k, cb, xs[i], sel, scores)
         check(d_ys[i].download((1, n_in), np.float16, stream), want)
     moe.close()
+
+
+@pytest.mark.parametrize("k,cb,experts,top_k,n_in,hidden,rows", [(3, 0, 16, 8, 256, 384, 1), (4, 1, 8, 2, 384, 128, 3), (5, 2, 6, 3, 128, 256, 7)])
+def test_small_batch_glue_fused_into_the_down_product(gpu, k, cb, experts, top_k, n_in, hidden, rows):
+    """Two launches (the down product takes the SwiGLU glue as its prologue and the weighted reduction as its epilogue)
+    against four: the same arithmetic in the same order, so the same bits, for fp16 and fp32 routing weights."""
+    rng = np.random.default_rng(4400 + 10 * k + rows)
+    bank = make_bank(rng, experts, n_in, hidden, k)
+    moe = gpu.Exl3SwitchGlu(*bank, top_k, k, cb)
+    x = rng.standard_normal((rows, n_in)).astype(np.float16)
+    selected, scores = routes(rng, rows, experts, top_k)
+    want = oracle.switch_glu_forward(*bank, top_k, k, cb, x, selected, scores)
+    for s in (scores, scores.astype(np.float32)):
+        four = moe.forward(x, selected, s)
+        gpu.set_option("moe_fused", 1)
+        try:
+            two = moe.forward(x, selected, s)
+            again = moe.forward(x, selected, s)                # the counters were left at zero
+        finally:
+            gpu.set_option("moe_fused", 0)
+        assert two.dtype == four.dtype and np.array_equal(two.view(np.uint8), four.view(np.uint8))
+        assert np.array_equal(two.view(np.uint8), again.view(np.uint8))
+        check(two, want, rms=4e-3)
+    assert gpu.workspace_status(moe._workspace) == 0
