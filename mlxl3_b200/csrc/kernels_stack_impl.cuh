@@ -535,14 +535,19 @@ stack_kernel(const StackArgs a) {
                     for (int r = 0; r < nrows;) {
                         const int tk = tk0 + r;
                         const int ri = (tk - tk_first) & (R - 1);               // row inside its chunk
-                        const int run = min(R - ri, nrows - r);
+                        // a run is either one partial row (the first or the last of the warp's range) or full rows only:
+                        // a partial row must not drag the other rows of its chunk through the loop that tests every tile
+                        // (measured: warps with one more partial row finished 0.7-1.9 us after the others of the layer)
+                        const bool partial = (tk == tk_first && lo_first != 0) || (tk == tk_last && hi_last != 8);
+                        int run = min(R - ri, nrows - r);
+                        if (partial) run = 1;
+                        else if (hi_last != 8) run = min(run, tk_last - tk);
                         if (ri == 0) {
                             if (!ready && !copy_lost && !mbar_wait(bars + slot, parity)) copy_lost = true;   // after a lost copy: no more waits
                             const int nslot = slot + 1 == SLOTS ? 0 : slot + 1;
                             ready = mbar_test_wait(bars + nslot, slot + 1 == SLOTS ? parity ^ 1u : parity);
                         }
                         const uint32_t* row_words = ring + (slot * R + ri) * kRowWords;
-                        const bool partial = (tk == tk_first && lo_first != 0) || (tk + run - 1 == tk_last && hi_last != 8);
                         if (!partial) {
 #pragma unroll 1
                             for (int j = 0; j < run; ++j) {
