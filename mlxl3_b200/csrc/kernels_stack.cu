@@ -42,10 +42,11 @@ bool plan_stack_op(const StackPlan& plan, StackOp& op) {
     const int64_t ub = static_cast<int64_t>(op.tiles_k) * 8;
     const int64_t total = ub * op.col_blocks;
     if (total >= (int64_t(1) << 31)) return false;
-    // every warp of the grid takes part unless that would leave a warp fewer than four tiles
-    int64_t ctas = std::max<int64_t>(1, std::min<int64_t>(plan.grid, total / (kStackWarps * 4)));
-    // a warp's range must stay within one column block's worth of units (it then touches at most two blocks)
-    const int64_t min_warps = (total + ub - 2) / (ub - 1) + 1;
+    // the layer is dealt out in whole rows of 8 tiles; every warp of the grid takes part unless there are fewer rows than warps
+    const int64_t rb = op.tiles_k, rt = rb * op.col_blocks;
+    int64_t ctas = std::max<int64_t>(1, std::min<int64_t>(plan.grid, rt / kStackWarps));
+    // a warp's range must stay within one column block's worth of rows (it then touches at most two blocks)
+    const int64_t min_warps = (rt + rb - 2) / (rb - 1) + 1;
     ctas = std::max(ctas, (min_warps + kStackWarps - 1) / kStackWarps);
     if (ctas > plan.grid) return false;                       // wider than the grid can cover in one pass
     op.warps = static_cast<int>(ctas) * kStackWarps;

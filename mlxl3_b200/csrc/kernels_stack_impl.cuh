@@ -64,14 +64,18 @@ __device__ __forceinline__ unsigned long long ld_flagged(const unsigned long lon
     return w;
 }
 
-// this warp's units [w0, w1) of a layer with T units shared by `warps` warps (warps beyond that have none)
+// This warp's units [w0, w1) of a layer with T units (tiles, column-block-major) shared by `warps` warps (warps beyond
+// that have none).  The layer is dealt out in whole rows of 8 tiles: a warp never shares a row with another warp, so
+// no row is copied twice and no row is decoded tile by tile with a test per tile (with tile-exact shares every warp
+// touched one row more than it owned tiles for, and the layer waited for the warps with two partial rows).
 struct StackRange {
     int w0, w1;
 };
 __device__ __forceinline__ int stack_unit_begin(int T, int warps, int wid, bool narrow) {
     if (wid >= warps) return T;
-    return narrow ? static_cast<int>(static_cast<unsigned int>(T) * static_cast<unsigned int>(wid) / static_cast<unsigned int>(warps))
-                  : static_cast<int>(static_cast<unsigned long long>(T) * wid / warps);
+    const unsigned int rows = static_cast<unsigned int>(T) >> 3;
+    return 8 * (narrow ? static_cast<int>(rows * static_cast<unsigned int>(wid) / static_cast<unsigned int>(warps))
+                       : static_cast<int>(static_cast<unsigned long long>(rows) * wid / warps));
 }
 
 // Where a warp's weight stream stands: the chunk (up to R consecutive rows of one 128-column block; a row is 8 tiles
@@ -481,10 +485,12 @@ stack_kernel(const StackArgs a) {
                 __threadfence_block();
                 if (lane == 0) s_arrived[cblock - cta0 / UB] = 0;         // the next layer's arrivals start from zero
                 const int Wop = o.warps;
-                const int i_first = narrow ? static_cast<int>(((static_cast<unsigned int>(cblock * UB + 1) * Wop - 1u) / T) / WARPS)
-                                           : static_cast<int>((((static_cast<int64_t>(cblock) * UB + 1) * Wop - 1) / T) / WARPS);
-                const int i_last = narrow ? static_cast<int>(((static_cast<unsigned int>((cblock + 1) * UB) * Wop - 1u) / T) / WARPS)
-                                          : static_cast<int>(((static_cast<int64_t>(cblock + 1) * UB * Wop - 1) / T) / WARPS);
+                // first and last CTA with rows of this block: the inverse of stack_unit_begin, in rows (RB per block, RT in all)
+                const int RB = UB >> 3, RT = T >> 3;
+                const int i_first = narrow ? static_cast<int>(((static_cast<unsigned int>(cblock * RB + 1) * Wop - 1u) / RT) / WARPS)
+                                           : static_cast<int>((((static_cast<int64_t>(cblock) * RB + 1) * Wop - 1) / RT) / WARPS);
+                const int i_last = narrow ? static_cast<int>(((static_cast<unsigned int>((cblock + 1) * RB) * Wop - 1u) / RT) / WARPS)
+                                          : static_cast<int>(((static_cast<int64_t>(cblock + 1) * RB * Wop - 1) / RT) / WARPS);
                 stack_finish_block(a, o, op, cblock, mask, second, i_last - i_first + 1, static_cast<int>(blockIdx.x) - i_first, tag,
                                    smem_raw, lane);
             }

@@ -23,10 +23,13 @@ def query(kind, n_in, n_out, k, rows):
     return list(out)
 
 
-def partition_ok(tiles_k, col_blocks, warps, warps_per_cta, max_pieces):
+def partition_ok(tiles_k, col_blocks, warps, warps_per_cta, max_pieces, whole_rows=False):
     ub = tiles_k * 8
     total = ub * col_blocks
-    begin = np.minimum((np.arange(warps + 1, dtype=np.int64) * total) // warps, total)
+    if whole_rows:      # the decode-step kernel deals a layer out in rows of 8 tiles
+        begin = 8 * ((np.arange(warps + 1, dtype=np.int64) * (total // 8)) // warps)
+    else:
+        begin = np.minimum((np.arange(warps + 1, dtype=np.int64) * total) // warps, total)
     assert begin[0] == 0 and begin[-1] == total and (np.diff(begin) >= 0).all()          # every tile once
     assert np.diff(begin).max() <= ub                                                     # at most two blocks per warp
     ctas = warps // warps_per_cta
@@ -64,7 +67,7 @@ def test_decode_step_partition(k):
             assert ok == 1 and grid == 148 and smem <= 224 * 1024
             assert warps % warps_per_cta == 0 and 0 < warps <= grid * warps_per_cta
             assert narrow == (1 if (n_in // 16 * 8 * col_blocks + 1) * warps < 0xFFFFFFFF else 0)
-            assert partition_ok(n_in // 16, col_blocks, warps, warps_per_cta, max_pieces)
+            assert partition_ok(n_in // 16, col_blocks, warps, warps_per_cta, max_pieces, whole_rows=True)
     # a layer with more column blocks than the grid has warps cannot be one pass of the step
     assert query("stack", 128, 128 * 4000, k, 1)[7] == 0
 
