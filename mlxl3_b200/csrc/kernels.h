@@ -182,7 +182,7 @@ struct StackOp {               // one layer of the step; lives in device memory
     int groups;
     int in, out, tiles_k, tiles_n, col_blocks;
     int warps;                 // warps of the grid that share this layer's tiles (a multiple of the CTA's warps)
-    int narrow;                // 1: (tiles + 1) * warps fits 32 bits
+    int narrow;                // bit 0: (tiles + 1) * warps fits 32 bits; bit 1: whole warps per column block (see stack_unit_begin)
     int max_pieces;            // bound on the CTAs that share one column block
     int tp_unit0;              // >= 0: row shard of a tensor-parallel layer, first exchange unit; -1: none
 };

@@ -51,6 +51,11 @@ bool plan_stack_op(const StackPlan& plan, StackOp& op) {
     if (ctas > plan.grid) return false;                       // wider than the grid can cover in one pass
     op.warps = static_cast<int>(ctas) * kStackWarps;
     op.narrow = static_cast<unsigned long long>(total + 1) * static_cast<unsigned long long>(op.warps) < 0xffffffffull ? 1 : 0;
+    // whole warps per column block when that does not raise the largest share of rows (no warp then works on two blocks)
+    const int64_t per_block = op.warps / op.col_blocks;
+    if (per_block >= 1 && (rb + per_block - 1) / per_block <= (rt + op.warps - 1) / op.warps &&
+        static_cast<unsigned long long>(op.warps + 1) * static_cast<unsigned long long>(op.col_blocks + 1) < 0xffffffffull)
+        op.narrow |= 2;
     op.max_pieces = static_cast<int>((ctas + op.col_blocks - 1) / op.col_blocks + 1);
     return true;
 }

@@ -68,14 +68,22 @@ __device__ __forceinline__ unsigned long long ld_flagged(const unsigned long lon
 // that have none).  The layer is dealt out in whole rows of 8 tiles: a warp never shares a row with another warp, so
 // no row is copied twice and no row is decoded tile by tile with a test per tile (with tile-exact shares every warp
 // touched one row more than it owned tiles for, and the layer waited for the warps with two partial rows).
-struct StackRange {
-    int w0, w1;
-};
-__device__ __forceinline__ int stack_unit_begin(int T, int warps, int wid, bool narrow) {
+// `mode` bit 0: the products fit 32 bits; bit 1: every column block is dealt to a whole number of warps (block c gets
+// warps [c W / C, (c + 1) W / C), which share its rows evenly), so no warp's range runs from one block into the next.
+// The planner picks that whenever it does not raise the largest share: a warp that crosses a block boundary stages and
+// arrives twice and rotates activations twice, and was measured to finish 1-2.4 us after the others of its layer.
+__device__ __forceinline__ int stack_unit_begin(int T, int warps, int wid, int mode, int col_blocks) {
     if (wid >= warps) return T;
     const unsigned int rows = static_cast<unsigned int>(T) >> 3;
-    return 8 * (narrow ? static_cast<int>(rows * static_cast<unsigned int>(wid) / static_cast<unsigned int>(warps))
-                       : static_cast<int>(static_cast<unsigned long long>(rows) * wid / warps));
+    if (mode & 2) {
+        const unsigned int C = static_cast<unsigned int>(col_blocks), W = static_cast<unsigned int>(warps), w = static_cast<unsigned int>(wid);
+        const unsigned int c = ((w + 1u) * C - 1u) / W;                        // the block of this warp
+        const unsigned int first = c * W / C, count = (c + 1u) * W / C - first;
+        const unsigned int rb = rows / C;
+        return 8 * static_cast<int>(c * rb + rb * (w - first) / count);
+    }
+    return 8 * ((mode & 1) ? static_cast<int>(rows * static_cast<unsigned int>(wid) / static_cast<unsigned int>(warps))
+                           : static_cast<int>(static_cast<unsigned long long>(rows) * wid / warps));
 }
 
 // Where a warp's weight stream stands: the chunk (up to R consecutive rows of one 128-column block; a row is 8 tiles
@@ -105,8 +113,8 @@ struct StackCursor {
             const StackOpLite& o = ops[op];
             UB = o.tiles_k * 8;
             const int T = UB * o.col_blocks;
-            const int w0 = stack_unit_begin(T, o.warps, wid, o.narrow != 0);
-            w1 = stack_unit_begin(T, o.warps, wid + 1, o.narrow != 0);
+            const int w0 = stack_unit_begin(T, o.warps, wid, o.narrow, o.col_blocks);
+            w1 = stack_unit_begin(T, o.warps, wid + 1, o.narrow, o.col_blocks);
             if (w1 > w0) {
                 cblock = w0 / UB;
                 segment(o, w0);
@@ -455,11 +463,11 @@ stack_kernel(const StackArgs a) {
         const StackOpLite& o = lite[op];
         const int UB = o.tiles_k * 8;
         const int T = UB * o.col_blocks;
-        const bool narrow = o.narrow != 0;
+        const bool narrow = (o.narrow & 1) != 0;
         const bool tracing = a.trace != nullptr && threadIdx.x == 0;
         unsigned long long* stamp = a.trace == nullptr ? nullptr : a.trace + (static_cast<size_t>(op) * gridDim.x + blockIdx.x) * kStackTraceSlots;
-        const int w0 = stack_unit_begin(T, o.warps, wid, narrow);
-        const int w1 = stack_unit_begin(T, o.warps, wid + 1, narrow);
+        const int w0 = stack_unit_begin(T, o.warps, wid, o.narrow, o.col_blocks);
+        const int w1 = stack_unit_begin(T, o.warps, wid + 1, o.narrow, o.col_blocks);
         if (w1 <= w0) continue;
         if (w1 - w0 > UB) {                                     // the planner guarantees this; never run past two blocks
             if (lane == 0) atomicCAS(a.error, 0u, 2u);
@@ -467,7 +475,7 @@ stack_kernel(const StackArgs a) {
         }
         bool waited = false;
         // unit ranges of the CTA's warps: lane w holds the begin of warp w (lane WARPS: the end of the last warp)
-        const int my_b = lane <= WARPS ? stack_unit_begin(T, o.warps, static_cast<int>(blockIdx.x) * WARPS + lane, narrow) : 0;
+        const int my_b = lane <= WARPS ? stack_unit_begin(T, o.warps, static_cast<int>(blockIdx.x) * WARPS + lane, o.narrow, o.col_blocks) : 0;
         const int next_b = __shfl_down_sync(0xffffffffu, my_b, 1);
         const int cta0 = __shfl_sync(0xffffffffu, my_b, 0);
         const uint32_t tag = tag_base + static_cast<uint32_t>(op) + 1u;
@@ -487,10 +495,17 @@ stack_kernel(const StackArgs a) {
                 const int Wop = o.warps;
                 // first and last CTA with rows of this block: the inverse of stack_unit_begin, in rows (RB per block, RT in all)
                 const int RB = UB >> 3, RT = T >> 3;
-                const int i_first = narrow ? static_cast<int>(((static_cast<unsigned int>(cblock * RB + 1) * Wop - 1u) / RT) / WARPS)
-                                           : static_cast<int>((((static_cast<int64_t>(cblock) * RB + 1) * Wop - 1) / RT) / WARPS);
-                const int i_last = narrow ? static_cast<int>(((static_cast<unsigned int>((cblock + 1) * RB) * Wop - 1u) / RT) / WARPS)
-                                          : static_cast<int>(((static_cast<int64_t>(cblock + 1) * RB * Wop - 1) / RT) / WARPS);
+                int i_first, i_last;
+                if (o.narrow & 2) {
+                    i_first = static_cast<int>(static_cast<unsigned int>(cblock) * Wop / o.col_blocks) / WARPS;
+                    i_last = (static_cast<int>(static_cast<unsigned int>(cblock + 1) * Wop / o.col_blocks) - 1) / WARPS;
+                } else if (narrow) {
+                    i_first = static_cast<int>(((static_cast<unsigned int>(cblock * RB + 1) * Wop - 1u) / RT) / WARPS);
+                    i_last = static_cast<int>(((static_cast<unsigned int>((cblock + 1) * RB) * Wop - 1u) / RT) / WARPS);
+                } else {
+                    i_first = static_cast<int>((((static_cast<int64_t>(cblock) * RB + 1) * Wop - 1) / RT) / WARPS);
+                    i_last = static_cast<int>(((static_cast<int64_t>(cblock + 1) * RB * Wop - 1) / RT) / WARPS);
+                }
                 stack_finish_block(a, o, op, cblock, mask, second, i_last - i_first + 1, static_cast<int>(blockIdx.x) - i_first, tag,
                                    smem_raw, lane);
             }
@@ -503,8 +518,7 @@ stack_kernel(const StackArgs a) {
             float* stage = reinterpret_cast<float*>(mine + a.stage_offset) + (cblock - w0 / UB) * stage_floats;
             const int grp = o.groups > 1 ? stack_group_of(a.ops[op], cblock) : 0;
             {
-                const int tk_first = u0 >> 3, tk_last = (u1 - 1) >> 3;
-                const int lo_first = u0 & 7, hi_last = ((u1 - 1) & 7) + 1;
+                const int tk_first = u0 >> 3, tk_last = (u1 - 1) >> 3;      // u0 and u1 are multiples of 8: whole rows
                 float acc[8][NB][4];
 #pragma unroll
                 for (int t = 0; t < 8; ++t)
@@ -531,8 +545,8 @@ stack_kernel(const StackArgs a) {
                         reinterpret_cast<const uint32_t*>(xs + min(g, rows - 1) * kXsHalves + (tk0 * 16 - kb0 * 128)) + q;
                     // The rows of this stretch are walked run by run: a run is the part of one stream chunk that lies inside
                     // the stretch.  Everything that happens once per chunk (barrier, probe of the next chunk, hand-back of the
-                    // slot) is outside the row loop, and a run without a partial row takes the loop that tests nothing per
-                    // tile.  The activation fragment of the next row is loaded while a row is decoded.  Lanes whose
+                    // slot) is outside the row loop, whose body tests nothing per tile.  The activation fragment of the
+                    // next row is loaded while a row is decoded.  Lanes whose
                     // activation row does not exist (g >= rows) multiply whatever the last row holds: column n of the
                     // product depends on column n of the activations only, and those columns are never stored.
                     uint32_t p0 = xfrag[0], p1 = xfrag[4];
@@ -541,40 +555,21 @@ stack_kernel(const StackArgs a) {
                     for (int r = 0; r < nrows;) {
                         const int tk = tk0 + r;
                         const int ri = (tk - tk_first) & (R - 1);               // row inside its chunk
-                        // a run is either one partial row (the first or the last of the warp's range) or full rows only:
-                        // a partial row must not drag the other rows of its chunk through the loop that tests every tile
-                        // (measured: warps with one more partial row finished 0.7-1.9 us after the others of the layer)
-                        const bool partial = (tk == tk_first && lo_first != 0) || (tk == tk_last && hi_last != 8);
-                        int run = min(R - ri, nrows - r);
-                        if (partial) run = 1;
-                        else if (hi_last != 8) run = min(run, tk_last - tk);
+                        const int run = min(R - ri, nrows - r);                 // whole rows only: a warp's range starts and ends on a row
                         if (ri == 0) {
                             if (!ready && !copy_lost && !mbar_wait(bars + slot, parity)) copy_lost = true;   // after a lost copy: no more waits
                             const int nslot = slot + 1 == SLOTS ? 0 : slot + 1;
                             ready = mbar_test_wait(bars + nslot, slot + 1 == SLOTS ? parity ^ 1u : parity);
                         }
                         const uint32_t* row_words = ring + (slot * R + ri) * kRowWords;
-                        if (!partial) {
 #pragma unroll 1
-                            for (int j = 0; j < run; ++j) {
-                                uint32_t bx[NB][4];
-                                stack_fragment<MODE>(p0, p1, bx[0]);
-                                p0 = xfrag[0]; p1 = xfrag[4];                   // one row past the stretch at most: inside the warp's buffer
-                                xfrag += 8;
-                                qmv_row<K, CB, NB, MODE, true>(row_words, geom, 0, 8, bx, acc);
-                                row_words += kRowWords;
-                            }
-                        } else {
-#pragma unroll 1
-                            for (int j = 0; j < run; ++j) {
-                                uint32_t bx[NB][4];
-                                stack_fragment<MODE>(p0, p1, bx[0]);
-                                p0 = xfrag[0]; p1 = xfrag[4];
-                                xfrag += 8;
-                                const int lo = tk + j == tk_first ? lo_first : 0, hi = tk + j == tk_last ? hi_last : 8;
-                                qmv_row<K, CB, NB, MODE, false>(row_words, geom, lo, hi, bx, acc);
-                                row_words += kRowWords;
-                            }
+                        for (int j = 0; j < run; ++j) {
+                            uint32_t bx[NB][4];
+                            stack_fragment<MODE>(p0, p1, bx[0]);
+                            p0 = xfrag[0]; p1 = xfrag[4];                       // one row past the stretch at most: inside the warp's buffer
+                            xfrag += 8;
+                            qmv_row<K, CB, NB, MODE, true>(row_words, geom, 0, 8, bx, acc);
+                            row_words += kRowWords;
                         }
                         r += run;
                         if (ri + run == R || tk0 + r > tk_last) {               // the chunk is consumed: its slot takes the next one

@@ -23,10 +23,19 @@ def query(kind, n_in, n_out, k, rows):
     return list(out)
 
 
-def partition_ok(tiles_k, col_blocks, warps, warps_per_cta, max_pieces, whole_rows=False):
+def partition_ok(tiles_k, col_blocks, warps, warps_per_cta, max_pieces, whole_rows=False, whole_warps_per_block=False):
     ub = tiles_k * 8
     total = ub * col_blocks
-    if whole_rows:      # the decode-step kernel deals a layer out in rows of 8 tiles
+    if whole_warps_per_block:      # block c gets warps [c W / C, (c + 1) W / C), which share its rows evenly
+        w = np.arange(warps, dtype=np.int64)
+        c = ((w + 1) * col_blocks - 1) // warps
+        first, count = c * warps // col_blocks, (c + 1) * warps // col_blocks - c * warps // col_blocks
+        assert (count >= 1).all()
+        begin = np.append(8 * (c * tiles_k + tiles_k * (w - first) // count), total)
+        some = begin[1:] > begin[:-1]
+        assert (begin[:-1][some] // ub == (begin[1:][some] - 1) // ub).all()                 # no warp works on two blocks
+        assert np.diff(begin).max() <= 8 * -(-(tiles_k * col_blocks) // warps)              # and the largest share did not grow
+    elif whole_rows:      # the decode-step kernel deals a layer out in rows of 8 tiles
         begin = 8 * ((np.arange(warps + 1, dtype=np.int64) * (total // 8)) // warps)
     else:
         begin = np.minimum((np.arange(warps + 1, dtype=np.int64) * total) // warps, total)
@@ -61,13 +70,16 @@ def test_fused_kernel_partition(k):
 
 @pytest.mark.parametrize("k", [2, 4, 6])
 def test_decode_step_partition(k):
+    seen_modes = set()
     for n_in in DIMS_IN:
         for n_out in DIMS_OUT:
             grid, max_pieces, col_blocks, warps_per_cta, smem, warps, narrow, ok = query("stack", n_in, n_out, k, 1)
             assert ok == 1 and grid == 148 and smem <= 224 * 1024
             assert warps % warps_per_cta == 0 and 0 < warps <= grid * warps_per_cta
-            assert narrow == (1 if (n_in // 16 * 8 * col_blocks + 1) * warps < 0xFFFFFFFF else 0)
-            assert partition_ok(n_in // 16, col_blocks, warps, warps_per_cta, max_pieces, whole_rows=True)
+            assert narrow & 1 == (1 if (n_in // 16 * 8 * col_blocks + 1) * warps < 0xFFFFFFFF else 0)
+            assert partition_ok(n_in // 16, col_blocks, warps, warps_per_cta, max_pieces, whole_rows=True, whole_warps_per_block=bool(narrow & 2))
+            seen_modes.add(narrow & 2)
+    assert seen_modes == {0, 2}                               # both ways of dealing a layer out occur in the domain
     # a layer with more column blocks than the grid has warps cannot be one pass of the step
     assert query("stack", 128, 128 * 4000, k, 1)[7] == 0
 
