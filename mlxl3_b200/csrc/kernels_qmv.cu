@@ -63,11 +63,11 @@ QmvPlan plan_qmv(int in, int out, int k, int64_t rows) {
     const int resident = r <= 8 ? g_ctas_per_sm.load() : 1;
     const int forced = g_force_grid.load();
     int64_t grid = forced > 0 ? forced : static_cast<int64_t>(sm_count()) * resident;
-    // keep at least four tiles per warp so a warp is not all prologue and epilogue
-    grid = std::max<int64_t>(1, std::min(grid, total / (kQmvWarps * 4)));
+    // the layer is dealt out in whole rows of 8 tiles: no more warps than rows
+    const int64_t rb = tiles_k, rt = rb * plan.col_blocks;
+    grid = std::max<int64_t>(1, std::min(grid, rt / kQmvWarps));
     // a warp's range must not exceed one column block (it then touches at most two blocks)
-    const int64_t ub = static_cast<int64_t>(tiles_k) * 8;
-    const int64_t min_warps = (total + ub - 2) / (ub - 1) + 1;
+    const int64_t min_warps = (rt + rb - 2) / (rb - 1) + 1;
     grid = std::max(grid, (min_warps + kQmvWarps - 1) / kQmvWarps);
     plan.grid = static_cast<int>(grid);
     plan.max_pieces = static_cast<int>((grid + plan.col_blocks - 1) / plan.col_blocks + 1);

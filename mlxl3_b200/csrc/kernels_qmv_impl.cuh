@@ -453,23 +453,38 @@ qmv_kernel(const QmvArgs p) {
     const int g = lane >> 2, q = lane & 3;
     const int rows = p.rows;
 
-    // All tiles of the layer are ordered column-block-major (unit = block * UB + tk * 8 + tile-in-row)
-    // and warp w of W owns units [T*w/W, T*(w+1)/W): the same tile count (+-1) for every warp of the
-    // grid, whatever the shape.  A warp's range may cross into the next 128-column block (it then has
-    // a segment in each).  The eight warps of a CTA walk the same list of blocks, add their tiles up in
-    // shared memory, and CTAs that share a block ("pieces") meet in global memory.
+    // All tiles of the layer are ordered column-block-major (unit = block * UB + tk * 8 + tile-in-row) and dealt out to
+    // the W warps of the grid in whole rows of 8 tiles, so that no row is copied by two warps and no row is decoded with
+    // a test per tile: warp w owns rows [RT*w/W, RT*(w+1)/W) of the RT rows (the same count +-1 for every warp, whatever
+    // the shape) -- or, when that does not raise the largest share, every column block goes to a whole number of warps
+    // (block c to warps [c W / C, (c + 1) W / C), which share its rows evenly), so that no warp works on two blocks (such
+    // a warp stages, arrives and rotates activations twice; measured in the decode-step kernel: it finishes 1-2 us after
+    // the others).  The eight warps of a CTA walk the same list of blocks, add their tiles up in shared memory, and CTAs
+    // that share a block ("pieces") meet in global memory.
     // (the layer has fewer than 2^31 tiles; only the products with the warp count need 64 bits)
     const int W = static_cast<int>(gridDim.x) * WARPS;
     const int wid = static_cast<int>(blockIdx.x) * WARPS + warp;
     const int UB = p.tiles_k * 8;
-    const int T = UB * (p.out >> 7);
+    const int C = p.out >> 7;
+    const int T = UB * C;
+    const int RB = p.tiles_k, RT = RB * C;
     // a * b / d with a * b below (T + 1) * W: 32-bit when that fits (64-bit division is emulated and slow)
     const bool narrow = static_cast<unsigned long long>(T + 1) * static_cast<unsigned long long>(W) < 0xffffffffull;
-    auto muldiv = [narrow](unsigned int a, unsigned int b, unsigned int d) -> int {
-        return narrow ? static_cast<int>(a * b / d) : static_cast<int>(static_cast<unsigned long long>(a) * b / d);
+    const int per_block = W / C;
+    const bool aligned = per_block >= 1 && (RB + per_block - 1) / per_block <= (RT + W - 1) / W &&
+                         static_cast<unsigned long long>(W + 1) * static_cast<unsigned long long>(C + 1) < 0xffffffffull;
+    auto unit_begin = [=](int w) -> int {                    // first unit (tile) of warp w
+        if (w >= W) return T;
+        if (aligned) {
+            const unsigned int c = ((static_cast<unsigned int>(w) + 1u) * C - 1u) / W;
+            const unsigned int first = c * W / C, count = (c + 1u) * W / C - first;
+            return 8 * static_cast<int>(c * RB + RB * (w - first) / count);
+        }
+        return 8 * (narrow ? static_cast<int>(static_cast<unsigned int>(RT) * static_cast<unsigned int>(w) / static_cast<unsigned int>(W))
+                           : static_cast<int>(static_cast<unsigned long long>(RT) * w / W));
     };
-    const int w0 = muldiv(T, wid, W);
-    const int w1 = muldiv(T, wid + 1, W);
+    const int w0 = unit_begin(wid);
+    const int w1 = unit_begin(wid + 1);
 
     unsigned char* mine = smem_raw + static_cast<size_t>(warp) * p.warp_smem;
     uint32_t* ring = reinterpret_cast<uint32_t*>(mine);                  // SLOTS chunks of R rows of packed words
@@ -485,7 +500,7 @@ qmv_kernel(const QmvArgs p) {
     __shared__ int s_begin[WARPS + 1];
     __shared__ unsigned int s_arrived[WARPS + 2];            // per visited block: warps that staged their tile
     if (threadIdx.x <= WARPS)
-        s_begin[threadIdx.x] = muldiv(T, blockIdx.x * WARPS + threadIdx.x, W);
+        s_begin[threadIdx.x] = unit_begin(static_cast<int>(blockIdx.x) * WARPS + static_cast<int>(threadIdx.x));
     if (threadIdx.x < WARPS + 2) s_arrived[threadIdx.x] = 0;
     if (lane == 0) {
 #pragma unroll
@@ -543,7 +558,6 @@ qmv_kernel(const QmvArgs p) {
         }
         {
             const int tk_first = u0 >> 3, tk_last = (u1 - 1) >> 3;
-            const int lo_first = u0 & 7, hi_last = ((u1 - 1) & 7) + 1;
 
             float acc[8][NB][4];
 #pragma unroll
@@ -629,8 +643,8 @@ qmv_kernel(const QmvArgs p) {
                         xfrag[nb] = reinterpret_cast<const uint32_t*>(p.xhat + grp * p.xhat_group_stride + static_cast<int64_t>(row) * p.in + tk0 * 16) + q;
                 }
                 // The rows of the stretch are walked run by run (a run = the part of one chunk inside the stretch): the
-                // barrier wait and the hand-back of the slot happen once per chunk, and a run without a partial row takes
-                // the loop that tests nothing per tile.  Lanes whose activation row does not exist multiply the last
+                // barrier wait and the hand-back of the slot happen once per chunk, and the row loop tests nothing per
+                // tile (a warp's range is whole rows).  Lanes whose activation row does not exist multiply the last
                 // row again: column n of the product depends on column n of the activations only, and is never stored.
                 auto fragments = [&](int r, uint32_t (&bx)[NB][4]) {
 #pragma unroll
@@ -651,24 +665,12 @@ qmv_kernel(const QmvArgs p) {
                     const int run = min(R - ri, nrows - r);
                     if (ri == 0 && !copy_lost && !mbar_wait(bars + slot, parity)) copy_lost = true;
                     const uint32_t* row_words = ring + (slot * R + ri) * kRowWords;
-                    const bool partial = (tk == tk_first && lo_first != 0) || (tk + run - 1 == tk_last && hi_last != 8);
-                    if (!partial) {
 #pragma unroll 1
-                        for (int j = 0; j < run; ++j) {
-                            uint32_t bx[NB][4];
-                            fragments(r + j, bx);
-                            qmv_row<K, CB, NB, MODE, true>(row_words, geom, 0, 8, bx, acc);
-                            row_words += kRowWords;
-                        }
-                    } else {
-#pragma unroll 1
-                        for (int j = 0; j < run; ++j) {
-                            uint32_t bx[NB][4];
-                            fragments(r + j, bx);
-                            const int lo = tk + j == tk_first ? lo_first : 0, hi = tk + j == tk_last ? hi_last : 8;
-                            qmv_row<K, CB, NB, MODE, false>(row_words, geom, lo, hi, bx, acc);
-                            row_words += kRowWords;
-                        }
+                    for (int j = 0; j < run; ++j) {
+                        uint32_t bx[NB][4];
+                        fragments(r + j, bx);
+                        qmv_row<K, CB, NB, MODE, true>(row_words, geom, 0, 8, bx, acc);
+                        row_words += kRowWords;
                     }
                     r += run;
                     if (ri + run == R || tk0 + r > tk_last) {                   // the chunk is consumed: its slot takes the next one
@@ -717,11 +719,18 @@ qmv_kernel(const QmvArgs p) {
         if (tracing) p.trace[blockIdx.x * 8 + 4] = global_ns();
         if (prev + 1 == static_cast<unsigned int>(__popc(mask))) {
             __threadfence_block();
-            // CTA holding unit x: (ceil((x+1)*W/T) - 1) / WARPS
-            const int i_first = narrow ? static_cast<int>(((static_cast<unsigned int>(cblock * UB + 1) * W - 1u) / T) / WARPS)
-                                       : static_cast<int>((((static_cast<int64_t>(cblock) * UB + 1) * W - 1) / T) / WARPS);
-            const int i_last = narrow ? static_cast<int>(((static_cast<unsigned int>((cblock + 1) * UB) * W - 1u) / T) / WARPS)
-                                      : static_cast<int>(((static_cast<int64_t>(cblock + 1) * UB * W - 1) / T) / WARPS);
+            // first and last CTA with rows of this block: the inverse of unit_begin (warp holding row x: ceil((x+1)*W/RT) - 1)
+            int i_first, i_last;
+            if (aligned) {
+                i_first = static_cast<int>(static_cast<unsigned int>(cblock) * W / C) / WARPS;
+                i_last = (static_cast<int>(static_cast<unsigned int>(cblock + 1) * W / C) - 1) / WARPS;
+            } else if (narrow) {
+                i_first = static_cast<int>(((static_cast<unsigned int>(cblock * RB + 1) * W - 1u) / RT) / WARPS);
+                i_last = static_cast<int>(((static_cast<unsigned int>((cblock + 1) * RB) * W - 1u) / RT) / WARPS);
+            } else {
+                i_first = static_cast<int>((((static_cast<int64_t>(cblock) * RB + 1) * W - 1) / RT) / WARPS);
+                i_last = static_cast<int>(((static_cast<int64_t>(cblock + 1) * RB * W - 1) / RT) / WARPS);
+            }
             qmv_finish_block(p, cblock, mask, second, i_last - i_first + 1, static_cast<int>(blockIdx.x) - i_first, smem_raw,
                              lane);
             if (tracing) p.trace[blockIdx.x * 8 + 5] = global_ns();

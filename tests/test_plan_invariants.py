@@ -3,9 +3,10 @@ arithmetic).  The reference proves the corresponding properties of its own split
 (native/src/contracts.rs:1995-2012, 1051-1069); here every shape of the domain is simply checked.
 
 Invariants:
-* fused kernel and decode-step kernel (warp-level stream-K): a warp's range of tiles never exceeds one 128-column
-  block's worth (so it touches at most two blocks and owns two staging buffers), the stated bound on the CTAs that
-  share a column block holds for every block, every tile belongs to exactly one warp;
+* fused kernel and decode-step kernel (warp-level stream-K, a layer dealt out in whole rows of 8 tiles): a warp's range
+  never exceeds one 128-column block's worth (so it touches at most two blocks and owns two staging buffers), the
+  stated bound on the CTAs that share a column block holds for every block, every tile belongs to exactly one warp;
+  where every block goes to a whole number of warps, no warp works on two blocks and the largest share did not grow;
 * tensor-core product: every input split keeps at least 8 stages of 64 inputs (or there is one split), the token
   tiles cover the rows, the small shape is used up to 64 rows.
 """
@@ -65,7 +66,12 @@ def test_fused_kernel_partition(k):
                 grid, max_pieces, col_blocks, warps_per_cta, smem, fused = query("qmv", n_in, n_out, k, rows)[:6]
                 assert col_blocks == n_out // 128 and grid >= 1 and smem <= 200 * 1024
                 assert fused == (1 if rows <= 2 else 0)
-                assert partition_ok(n_in // 16, col_blocks, grid * warps_per_cta, warps_per_cta, max_pieces)
+                # the kernel derives the way a layer is dealt out from the launch itself: whole warps per column block
+                # when that does not raise the largest share of rows
+                warps, rb = grid * warps_per_cta, n_in // 16
+                per_block = warps // col_blocks
+                whole = per_block >= 1 and -(-rb // per_block) <= -(-(rb * col_blocks) // warps)
+                assert partition_ok(rb, col_blocks, warps, warps_per_cta, max_pieces, whole_rows=True, whole_warps_per_block=whole)
 
 
 @pytest.mark.parametrize("k", [2, 4, 6])
