@@ -315,6 +315,12 @@ typedef struct {
     const void* d_x;                 /* [rows, in] */
     void* d_y[8];                    /* one [rows, out] pointer per member (a plain layer uses d_y[0]) */
     b200exl3_tp* tp;                 /* NULL, or the exchange context of a row-parallel layer */
+    /* NULL, or the operators fused around the layer as in b200exl3_linear_forward_fused / b200exl3_group_forward_fused
+     * (fp16 steps): prologue kind 2 (SwiGLU) or 3 (RMSNorm from the block sums the layer before left), epilogue 1
+     * (residual add + block sums; plain layers) or 2 (rotary embedding + cache append; a [q | k | v] group, one row).
+     * Kind 1 is not taken: it needs the whole input row before the first block.  With these a decoder block's
+     * o, [gate | up], down and the next block's [q | k | v] are one step. */
+    const b200exl3_prologue* fused;
 } b200exl3_stack_op;
 int b200exl3_stack_create(const b200exl3_stack_op* ops, int count, int x_dtype, int64_t rows, b200exl3_stack** out);
 void b200exl3_stack_free(b200exl3_stack* handle);

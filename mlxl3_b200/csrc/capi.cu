@@ -798,8 +798,11 @@ int b200exl3_stack_create(const b200exl3_stack_op* ops, int count, int x_dtype, 
         if (c.k != first->k || c.cb != first->cb || ((c.flags ^ first->flags) & B200EXL3_EXACT_WEIGHTS))
             return fail("layer %d: every layer of a step must share bit width, codebook and weight mode", i);
         if (!src.d_x || !aligned16(src.d_x)) return fail("layer %d: input pointer is NULL or not 16-byte aligned", i);
-        for (int g = 0; g < c.groups; ++g)
-            if (!src.d_y[g] || !aligned16(src.d_y[g])) return fail("layer %d: output pointer %d is NULL or not 16-byte aligned", i, g);
+        for (int g = 0; g < c.groups; ++g) {
+            // the residual epilogue stores through its own pointer, the rotary one writes k and v into the caches
+            const bool unused = src.fused && ((src.fused->epilogue == 1) || (src.fused->epilogue == 2 && g > 0));
+            if ((!src.d_y[g] && !unused) || !aligned16(src.d_y[g])) return fail("layer %d: output pointer %d is NULL or not 16-byte aligned", i, g);
+        }
         if (src.tp) {
             if (c.groups != 1) return fail("layer %d: a grouped layer cannot be a row shard", i);
             if (tp && tp != src.tp) return fail("layer %d: a step uses one exchange context", i);
@@ -813,6 +816,27 @@ int b200exl3_stack_create(const b200exl3_stack_op* ops, int count, int x_dtype, 
         o.groups = c.groups; o.in = c.in; o.out = c.out;
         for (int g = 0; g < c.groups; ++g) { o.gy[g] = src.d_y[g]; o.gcol0[g] = c.gcol0[g]; o.gout[g] = c.gout[g]; }
         o.tp_unit0 = src.tp ? 0 : -1;
+        if (src.fused && (src.fused->kind != 0 || src.fused->epilogue != 0)) {
+            const b200exl3_prologue* f = src.fused;
+            if (x_dtype != kF16) return fail("layer %d: fused operators need an fp16 step", i);
+            if (check_prologue(f, src.d_x, rows)) return -1;
+            if (f->kind == 1) return fail("layer %d: a step takes the RMSNorm prologue from block sums (kind 3), not kind 1", i);
+            if (f->epilogue == 1 && c.groups != 1) return fail("layer %d: the residual epilogue belongs to plain layers", i);
+            if (f->epilogue == 2 && (c.groups != 3 || c.gout[1] != c.gout[2] || c.gout[0] % 128 || c.gout[1] % 128))
+                return fail("layer %d: the rotary epilogue needs a group of three members [q | k | v] with 128-wide heads", i);
+            o.prologue = f->kind; o.epilogue = f->epilogue;
+            o.pro_aux = reinterpret_cast<const __half*>(f->d_aux);
+            o.pro_weight = reinterpret_cast<const __half*>(f->d_weight);
+            o.pro_sumsq = f->d_sumsq; o.pro_eps = f->eps;
+            o.epi_residual = reinterpret_cast<const __half*>(f->d_residual);
+            o.epi_sum = reinterpret_cast<__half*>(f->d_residual_out);
+            o.epi_sumsq = f->d_sumsq_out;
+            if (f->epilogue == 2) {
+                o.epi_pos = f->d_pos; o.epi_log2_theta = log2f(f->theta); o.epi_max_ctx = f->max_ctx;
+                o.epi_k_cache = reinterpret_cast<__half*>(f->d_k_cache);
+                o.epi_v_cache = reinterpret_cast<__half*>(f->d_v_cache);
+            }
+        }
     }
     b200exl3_stack* h = new (std::nothrow) b200exl3_stack{};
     if (!h) return fail("out of host memory");
@@ -851,6 +875,7 @@ int b200exl3_stack_create(const b200exl3_stack_op* ops, int count, int x_dtype, 
     a.piece_words[1] = reinterpret_cast<unsigned long long*>(h->scratch + h->sync_bytes + max_words);
     a.warp_smem = h->plan.warp_smem; a.xs_offset = h->plan.xs_offset; a.stage_offset = h->plan.stage_offset;
     a.table_offset = h->plan.table_offset; a.x_blocks = h->plan.x_blocks;
+    for (const StackOp& o : table) a.fused |= (o.prologue != 0 || o.epilogue != 0) ? 1 : 0;
     a.wait_ns = static_cast<unsigned long long>(g_stack_wait_ms.load()) * 1000000ull;
     if (tp) a.tp = tp_peers(tp);
     *out_handle = h;

@@ -185,6 +185,21 @@ struct StackOp {               // one layer of the step; lives in device memory
     int narrow;                // bit 0: (tiles + 1) * warps fits 32 bits; bit 1: whole warps per column block (see stack_unit_begin)
     int max_pieces;            // bound on the CTAs that share one column block
     int tp_unit0;              // >= 0: row shard of a tensor-parallel layer, first exchange unit; -1: none
+    // operators fused around the layer (fp16 steps; the arithmetic of the per-layer kernel's prologues and epilogues)
+    int prologue;              // 0 none, 2 SwiGLU (x = gate rows, pro_aux = up rows), 3 RMSNorm from block sums of squares
+    int epilogue;              // 0 none, 1 residual add + block sums of squares, 2 rotary embedding + cache append ([q|k|v])
+    const __half* pro_aux;
+    const __half* pro_weight;  // [in] norm weight
+    const float* pro_sumsq;    // [rows, in / 128]
+    float pro_eps;
+    const __half* epi_residual;// [rows, out]
+    __half* epi_sum;           // [rows, out] (may be epi_residual)
+    float* epi_sumsq;          // [rows, out / 128]
+    const int* epi_pos;
+    float epi_log2_theta;
+    int epi_max_ctx;
+    __half* epi_k_cache;
+    __half* epi_v_cache;
 };
 
 // What every warp needs at a layer boundary, staged in shared memory at kernel start so that the weight cursor
@@ -197,6 +212,7 @@ struct StackOpLite {
     const __half* bias;
     void* y0;                  // output of a plain layer (grouped layers read their outputs from the full table)
     int tiles_k, tiles_n, col_blocks, warps, narrow, in, groups, max_pieces, tp_unit0, gout0;
+    int prologue, epilogue;    // the rest of a fused layer's description is read from the full table
 };
 constexpr int kStackMaxOps = 256;    // layers per launch: the staged table takes 88 bytes per layer
 
@@ -214,6 +230,7 @@ struct StackArgs {
     unsigned long long* trace; // optional [n_ops, grid, kStackTraceSlots] stamps; warp 0: boundary passed, rotated, main loop done, block carried on; the warp that
                                // carries a block on: start, after the atomic, pieces added, stored and counted; then every warp: its tiles done
     int table_offset;          // offset of the staged layer table in dynamic shared memory
+    int fused;                 // 1: some layer of the step has a fused prologue or epilogue (a kernel of its own)
     TpPeers tp;
 };
 

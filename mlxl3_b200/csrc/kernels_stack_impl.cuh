@@ -229,6 +229,66 @@ __device__ __forceinline__ void stack_rotate_chunk(const void* x, int x_dtype, c
     __syncwarp();
 }
 
+// The same rotation with an operator fused in front of the input scales (fp16 steps; the arithmetic of the per-layer
+// kernel's prologues, statement by statement): kind 3 = RMSNorm of the input row from the sums of squares per 128-block
+// that the layer before left (the row's 1 / rms is added up by every warp from those 32-112 floats, in a fixed order);
+// kind 2 = SwiGLU, x = gate rows and aux = up rows.  All loads of a row go out before the first use.
+__device__ __forceinline__ void stack_rotate_chunk_fused(const StackOp& f, const uint2 (&sv)[kQmvXBlocks], int rows, int kb0, int nblk,
+                                                         int kXsHalves, __half* xs, int lane) {
+    const __half* x = reinterpret_cast<const __half*>(f.x);
+    constexpr int kBatch = 3;                                  // blocks whose loads are in flight together (registers)
+#pragma unroll 1
+    for (int row = 0; row < rows; ++row) {
+        float inv = 0.0f;
+        if (f.prologue == 3) {
+            float acc = 0.0f;
+            for (int b = lane; b < (f.in >> 7); b += 32) acc += __ldcg(f.pro_sumsq + row * (f.in >> 7) + b);
+#pragma unroll
+            for (int d = 16; d >= 1; d >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
+            inv = rsqrtf(acc / static_cast<float>(f.in) + f.pro_eps);
+        }
+#pragma unroll
+        for (int b0 = 0; b0 < kQmvXBlocks; b0 += kBatch) {
+            if (b0 >= nblk) break;
+            const int64_t at = static_cast<int64_t>(row) * f.in + (kb0 + b0) * 128 + lane * 4;
+            uint2 raw[kBatch], aux[kBatch];
+#pragma unroll
+            for (int b = 0; b < kBatch; ++b)
+                if (b0 + b < nblk) {
+                    raw[b] = __ldcg(reinterpret_cast<const uint2*>(x + at + b * 128));
+                    aux[b] = f.prologue == 3 ? __ldg(reinterpret_cast<const uint2*>(f.pro_weight + (kb0 + b0 + b) * 128 + lane * 4))
+                                             : __ldcg(reinterpret_cast<const uint2*>(f.pro_aux + at + b * 128));
+                }
+#pragma unroll
+            for (int b = 0; b < kBatch; ++b)
+                if (b0 + b < nblk) {
+                    const __half2* xh = reinterpret_cast<const __half2*>(&raw[b]);
+                    const __half2* ah = reinterpret_cast<const __half2*>(&aux[b]);
+                    __half2 v[2];
+                    if (f.prologue == 3) {
+                        const float2 f0 = __half22float2(xh[0]), f1 = __half22float2(xh[1]);
+                        v[0] = __hmul2_rn(ah[0], __floats2half2_rn(f0.x * inv, f0.y * inv));
+                        v[1] = __hmul2_rn(ah[1], __floats2half2_rn(f1.x * inv, f1.y * inv));
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) {
+                            const float2 g = __half22float2(xh[j]);
+                            const __half2 sg = __floats2half2_rn(1.0f / (1.0f + expf(-g.x)), 1.0f / (1.0f + expf(-g.y)));
+                            v[j] = __hmul2_rn(__hmul2_rn(xh[j], sg), ah[j]);
+                        }
+                    }
+                    const __half2* sh = reinterpret_cast<const __half2*>(&sv[b0 + b]);
+                    __align__(8) __half h[4];
+                    *reinterpret_cast<__half2*>(h) = __hmul2_rn(v[0], sh[0]);
+                    *reinterpret_cast<__half2*>(h + 2) = __hmul2_rn(v[1], sh[1]);
+                    warp_hadamard128_f16(h, lane);
+                    *reinterpret_cast<uint2*>(xs + row * kXsHalves + (b0 + b) * 128 + lane * 4) = *reinterpret_cast<uint2*>(h);
+                }
+        }
+    }
+    __syncwarp();
+}
+
 __device__ __forceinline__ int stack_group_of(const StackOp& o, int cblock) {
     int grp = 0;
 #pragma unroll 1
@@ -242,6 +302,7 @@ __device__ __forceinline__ int stack_group_of(const StackOp& o, int cblock) {
 // it with the other ranks (row shard), rotates, stores, and counts the block as done.  Everything the last steps need
 // from memory (output scales, bias, the output pointer of a grouped layer) is requested at the start, so that the
 // chain of memory round trips is: pieces out, pieces in, result out.
+template <bool FUSED>
 __device__ __forceinline__ void stack_finish_block(const StackArgs& a, const StackOpLite& o, int op, int cblock,
                                                    unsigned int warp_mask, unsigned int second_mask, int pieces, int piece,
                                                    uint32_t tag, const unsigned char* smem_base, int lane) {
@@ -363,6 +424,52 @@ __device__ __forceinline__ void stack_finish_block(const StackArgs& a, const Sta
                     out[j] = __hmul_rn(h[j], sv[j]);
                     if (bias) out[j] = __hadd_rn(out[j], bias[j]);
                 }
+                if (FUSED && o.epilogue == 1) {
+                    // residual add and the block's sum of squares for the next RMSNorm (fixed shuffle order)
+                    const StackOp& f = a.ops[op];
+                    const int64_t at = static_cast<int64_t>(row) * f.out + col;
+                    const uint2 rv = __ldcg(reinterpret_cast<const uint2*>(f.epi_residual + at));
+                    const __half* rh = reinterpret_cast<const __half*>(&rv);
+                    float sq = 0.0f;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        out[j] = __hadd_rn(rh[j], out[j]);
+                        const float v1 = __half2float(out[j]);
+                        sq = fmaf(v1, v1, sq);
+                    }
+                    *reinterpret_cast<uint2*>(f.epi_sum + at) = *reinterpret_cast<const uint2*>(out);
+#pragma unroll
+                    for (int d = 16; d >= 1; d >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, d);
+                    if (lane == 0) f.epi_sumsq[row * (f.out >> 7) + cblock] = sq;
+                    continue;
+                }
+                if (FUSED && o.epilogue == 2) {
+                    // [q | k | v] with 128-wide heads: this block is one head.  Rotary embedding of q and k heads (pairs
+                    // (i, i + 64): lane L holds columns 4L..4L+3, its partner is lane L ^ 16); keys and values go straight
+                    // into row `pos` of the caches.
+                    const StackOp& f = a.ops[op];
+                    const int grp = stack_group_of(f, cblock);
+                    int pos = __ldg(f.epi_pos);
+                    pos = pos < 0 ? 0 : (pos >= f.epi_max_ctx ? f.epi_max_ctx - 1 : pos);
+                    if (grp < 2) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const float mine = __half2float(out[j]);
+                            const float other = __shfl_xor_sync(0xffffffffu, mine, 16);
+                            const int i = (lane & 15) * 4 + j;
+                            const float inv_freq = exp2f(-f.epi_log2_theta * static_cast<float>(2 * i) / 128.0f);
+                            float sn, cs;
+                            sincosf(static_cast<float>(pos) * inv_freq, &sn, &cs);
+                            const float a0 = lane < 16 ? mine : other, b0 = lane < 16 ? other : mine;
+                            out[j] = __float2half_rn(lane < 16 ? a0 * cs - b0 * sn : a0 * sn + b0 * cs);
+                        }
+                    }
+                    __half* dst = grp == 0 ? reinterpret_cast<__half*>(f.gy[0]) + gcol
+                                           : (grp == 1 ? f.epi_k_cache : f.epi_v_cache) +
+                                                 (static_cast<int64_t>(gcol >> 7) * f.epi_max_ctx + pos) * 128 + lane * 4;
+                    *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(out);
+                    continue;
+                }
                 *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(y) + static_cast<int64_t>(row) * gout + gcol) =
                     *reinterpret_cast<const uint2*>(out);
             } else {
@@ -389,7 +496,9 @@ __device__ __forceinline__ void stack_fragment(uint32_t p0, uint32_t p1, uint32_
     }
 }
 
-template <int K, int CB, int MODE>
+// FUSED: the step contains layers with a fused prologue or epilogue.  A kernel of its own, so that the plain step keeps
+// its registers (with that code compiled in, the plain step spilled and ran 11 % slower).
+template <int K, int CB, int MODE, bool FUSED>
 __global__ void __launch_bounds__(kStackWarps * 32, kStackCtasPerSm)
 stack_kernel(const StackArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -425,6 +534,7 @@ stack_kernel(const StackArgs a) {
         l.tiles_k = o.tiles_k; l.tiles_n = o.tiles_n; l.col_blocks = o.col_blocks; l.warps = o.warps; l.narrow = o.narrow;
         l.in = o.in; l.groups = o.groups; l.max_pieces = o.max_pieces; l.tp_unit0 = o.tp_unit0; l.gout0 = o.gout[0];
         l.svh = o.svh; l.bias = o.bias; l.y0 = o.gy[0];
+        l.prologue = o.prologue; l.epilogue = o.epilogue;
         lite[i] = l;
     }
     if (threadIdx.x < WARPS + 2) s_arrived[threadIdx.x] = 0;
@@ -506,7 +616,7 @@ stack_kernel(const StackArgs a) {
                     i_first = static_cast<int>((((static_cast<int64_t>(cblock) * RB + 1) * Wop - 1) / RT) / WARPS);
                     i_last = static_cast<int>(((static_cast<int64_t>(cblock + 1) * RB * Wop - 1) / RT) / WARPS);
                 }
-                stack_finish_block(a, o, op, cblock, mask, second, i_last - i_first + 1, static_cast<int>(blockIdx.x) - i_first, tag,
+                stack_finish_block<FUSED>(a, o, op, cblock, mask, second, i_last - i_first + 1, static_cast<int>(blockIdx.x) - i_first, tag,
                                    smem_raw, lane);
             }
             if (tracing) stamp[3] = global_ns();
@@ -539,7 +649,8 @@ stack_kernel(const StackArgs a) {
                         waited = true;
                         if (tracing) stamp[0] = global_ns();
                     }
-                    stack_rotate_chunk(o.x, a.x_dtype, sv, o.in, rows, kb0, nblk, kXsHalves, xs, lane);
+                    if (FUSED && o.prologue != 0) stack_rotate_chunk_fused(a.ops[op], sv, rows, kb0, nblk, kXsHalves, xs, lane);
+                    else stack_rotate_chunk(o.x, a.x_dtype, sv, o.in, rows, kb0, nblk, kXsHalves, xs, lane);
                     if (tracing && first_chunk) stamp[1] = global_ns();
                     const uint32_t* xfrag =
                         reinterpret_cast<const uint32_t*>(xs + min(g, rows - 1) * kXsHalves + (tk0 * 16 - kb0 * 128)) + q;
@@ -610,9 +721,9 @@ stack_kernel(const StackArgs a) {
     }
 }
 
-template <int K, int CB, int MODE>
+template <int K, int CB, int MODE, bool FUSED>
 cudaError_t stack_launch_one(const StackArgs& a, const StackPlan& plan, cudaStream_t stream) {
-    auto kernel = stack_kernel<K, CB, MODE>;
+    auto kernel = stack_kernel<K, CB, MODE, FUSED>;
     static PerDeviceOnce attribute;
     if (attribute.needed()) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kStackMaxSmemBytes);
@@ -634,9 +745,14 @@ cudaError_t stack_launch_one(const StackArgs& a, const StackPlan& plan, cudaStre
 
 template <int K>
 cudaError_t stack_launch_k(const StackArgs& a, int cb, bool exact, const StackPlan& plan, cudaStream_t stream) {
-    if (cb == 2) return stack_launch_one<K, 2, 1>(a, plan, stream);
-    if (cb == 0) return exact ? stack_launch_one<K, 0, 1>(a, plan, stream) : stack_launch_one<K, 0, 0>(a, plan, stream);
-    return exact ? stack_launch_one<K, 1, 1>(a, plan, stream) : stack_launch_one<K, 1, 0>(a, plan, stream);
+    if (a.fused) {
+        if (cb == 2) return stack_launch_one<K, 2, 1, true>(a, plan, stream);
+        if (cb == 0) return exact ? stack_launch_one<K, 0, 1, true>(a, plan, stream) : stack_launch_one<K, 0, 0, true>(a, plan, stream);
+        return exact ? stack_launch_one<K, 1, 1, true>(a, plan, stream) : stack_launch_one<K, 1, 0, true>(a, plan, stream);
+    }
+    if (cb == 2) return stack_launch_one<K, 2, 1, false>(a, plan, stream);
+    if (cb == 0) return exact ? stack_launch_one<K, 0, 1, false>(a, plan, stream) : stack_launch_one<K, 0, 0, false>(a, plan, stream);
+    return exact ? stack_launch_one<K, 1, 1, false>(a, plan, stream) : stack_launch_one<K, 1, 0, false>(a, plan, stream);
 }
 
 }  // namespace b200exl3

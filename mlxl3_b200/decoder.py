@@ -191,6 +191,8 @@ class DenseDecoder:
         self.graph = None
         self.store_logits = False
         self.fused = True            # norms, residual adds and SwiGLU run inside the projections' kernels; False: as kernels of their own
+        self.stacked = False         # True (with fused): o, [gate|up], down and the next block's [q|k|v] are ONE persistent launch
+        self.stacks = None
         self.hidden_name = "h"       # buffer that holds the residual stream after a step
         self.launches_per_step = 0
 
@@ -215,7 +217,46 @@ class DenseDecoder:
         else:
             op.forward_device(d_x, F16, 1, d_y, self.ws, self.stream)
 
+    def _build_stacks(self) -> None:
+        """One decode-step object per block: o (+ residual), [gate|up] (RMSNorm from block sums), down (SwiGLU, + residual)
+        and the NEXT block's [q|k|v] (RMSNorm from block sums, rotary embedding, cache append)."""
+        from .stack import Exl3Stack
+        c, b = self.config, self.buf
+        h, sq = b["h"].ptr, self.sumsq.ptr
+        self.stacks = []
+        for l, e in enumerate(self.layers):
+            ops = [(e["o"], b["att"].ptr, 0, self.tp, Prologue.plain().with_residual(h, h, sq)),
+                   (e["gu"], h, [b["gate"].ptr, b["up"].ptr], None, Prologue.rms_norm_from_blocks(e["mlp_norm"].ptr, c.eps, sq)),
+                   (e["down"], b["gate"].ptr, 0, self.tp, Prologue.swiglu(b["up"].ptr).with_residual(h, h, sq))]
+            if l + 1 < len(self.layers):
+                n = self.layers[l + 1]
+                ops.append((n["qkv"], h, [b["q"].ptr, 0, 0], None,
+                            Prologue.rms_norm_from_blocks(n["attn_norm"].ptr, c.eps, sq).with_rope(self.d_pos.ptr, c.theta, c.max_ctx,
+                                                                                                   n["k_cache"].ptr, n["v_cache"].ptr)))
+            self.stacks.append(Exl3Stack(ops, F16, 1))
+
+    def _launch_stacked(self) -> None:
+        c, b, s = self.config, self.buf, self.stream
+        if self.stacks is None:
+            self._build_stacks()
+        h = b["h"].ptr
+        embed(self.embed_table.ptr, self.d_token.ptr, 1, c.vocab, c.hidden, h, s)
+        e0 = self.layers[0]
+        e0["qkv"].forward_fused_device(Prologue.rms_norm(e0["attn_norm"].ptr, c.eps).with_rope(self.d_pos.ptr, c.theta, c.max_ctx, e0["k_cache"].ptr,
+                                                                                             e0["v_cache"].ptr), h, 1, [b["q"].ptr, 0, 0], self.ws, s)
+        for e, stack in zip(self.layers, self.stacks):
+            attention_decode(b["q"].ptr, e["k_cache"].ptr, e["v_cache"].ptr, self.heads, self.kv_heads, c.head_dim, self.d_pos.ptr, c.max_ctx,
+                             c.head_dim ** -0.5, b["att"].ptr, self.attn_ws, s)
+            stack.forward(s)
+        rms_norm(h, 0, self.final_norm.ptr, 1, c.hidden, c.eps, 0, b["xn"].ptr, s)
+        self.hidden_name = "h"
+        head_argmax(b["xn"].ptr, self.head_weight.ptr, self.vocab, c.hidden, self.rank * self.vocab, b["logits"].ptr if self.store_logits else 0,
+                    self.d_best_value.ptr, self.d_best_index.ptr, self.head_ws, s)
+        self.launches_per_step = 2 * len(self.layers) + 5
+
     def _launch(self) -> None:
+        if self.fused and self.stacked and self.config.head_dim == 128:
+            return self._launch_stacked()
         if self.fused:
             return self._launch_fused()
         c, b, s = self.config, self.buf, self.stream

@@ -39,6 +39,8 @@ def main(argv=None) -> None:
                     help="> 0: time one decode step of a Llama-3-8B-shaped dense decoder with this many layers at --context keys")
     ap.add_argument("--context", type=int, default=2048)
     ap.add_argument("--unfused", action="store_true", help="with --decoder-layers: norms and SwiGLU as kernels of their own")
+    ap.add_argument("--stacked", action="store_true",
+                    help="with --decoder-layers: o, [gate|up], down and the next block's [q|k|v] as one persistent launch per block")
     ap.add_argument("--trace", action="store_true", help="with --step-layers: print the per-layer phase stamps of one step")
     ap.add_argument("--step-plain", action="store_true",
                     help="with --step-layers: that many plain layers of --in x --out instead of decoder blocks (chained when square)")
@@ -188,6 +190,7 @@ def decoder_main(args) -> None:
     config = DecoderConfig(layers=args.decoder_layers, k_bits=args.k, codebook=args.cb, max_ctx=args.context)
     model = DenseDecoder(config, SyntheticWeights(config, seed=1))
     model.fused = not args.unfused
+    model.stacked = args.stacked
     model.fill_cache(args.context - 1)
     model.set_input(17, args.context - 1)
     if not args.no_graph:

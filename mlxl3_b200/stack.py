@@ -14,14 +14,17 @@ from .runtime import DEFAULT_STREAM, Stream
 
 
 class _StackOp(ctypes.Structure):
-    _fields_ = [("linear", c_void_p), ("group", c_void_p), ("d_x", c_void_p), ("d_y", c_void_p * 8), ("tp", c_void_p)]
+    _fields_ = [("linear", c_void_p), ("group", c_void_p), ("d_x", c_void_p), ("d_y", c_void_p * 8), ("tp", c_void_p),
+                ("fused", c_void_p)]
 
 
 class Exl3Stack:
-    """``Exl3Stack(ops, dtype, rows)`` with ``ops`` a list of ``(layer, d_x, d_ys)`` or ``(layer, d_x, d_ys, tp_context)``:
-    ``layer`` an ``Exl3Linear`` or ``Exl3Group``, ``d_x`` the device address of its ``[rows, in]`` input, ``d_ys`` one
-    device address (or a list, one per member of a group) for its outputs.  ``forward()`` runs every layer in order;
-    layer i+1 may read what layer i wrote."""
+    """``Exl3Stack(ops, dtype, rows)`` with ``ops`` a list of ``(layer, d_x, d_ys)``, ``(layer, d_x, d_ys, tp_context)`` or
+    ``(layer, d_x, d_ys, tp_context_or_None, prologue)``: ``layer`` an ``Exl3Linear`` or ``Exl3Group``, ``d_x`` the device
+    address of its ``[rows, in]`` input, ``d_ys`` one device address (or a list, one per member of a group) for its
+    outputs, ``prologue`` a ``linear.Prologue`` with the operators fused around the layer (SwiGLU or RMSNorm-from-block-sums
+    in front, residual add or rotary embedding + cache append behind).  ``forward()`` runs every layer in order; layer
+    i+1 may read what layer i wrote."""
 
     def __init__(self, ops, dtype: int, rows: int = 1):
         ops = list(ops)
@@ -43,6 +46,10 @@ class Exl3Stack:
             for i, y in enumerate(ys):
                 entry.d_y[i] = y
             entry.tp = tp.handle if tp is not None else None
+            fused = op[4] if len(op) > 4 else None
+            if fused is not None:
+                entry.fused = ctypes.addressof(fused)
+                self._keep.append(fused)
             self._keep.append(layer)
         handle = c_void_p()
         _lib.call("b200exl3_stack_create", ctypes.cast(table, c_void_p), len(ops), dtype, rows, byref(handle))

@@ -315,3 +315,37 @@ def test_rotary_epilogue_matches_the_separate_kernel(gpu):
         group.forward_fused_device(Prologue.plain().with_rope(d_pos.ptr, theta, max_ctx, kc1.ptr, vc1.ptr), d_x.ptr, 2, [q1.ptr, 0, 0], ws, stream)
     with pytest.raises(gpu.B200Exl3Error, match="belongs to a"):
         members[0].forward_fused_device(Prologue.plain().with_rope(d_pos.ptr, theta, max_ctx, kc1.ptr, vc1.ptr), d_x.ptr, 1, q1.ptr, ws, stream)
+
+
+def test_small_decoder_with_one_persistent_launch_per_block(gpu):
+    """o, [gate|up], down and the next block's [q|k|v] -- with their fused norms, SwiGLU, residual adds, rotary embedding
+    and cache append -- as ONE decode-step launch per block: same bar against the oracle, and step by step against the
+    per-layer form (other summation order inside a projection, so not the same bits)."""
+    from mlxl3_b200.decoder import DenseDecoder
+    config, weights = _small()
+    model, linear = _oracle_model(config, weights)
+    dec, ref = DenseDecoder(config, weights), DenseDecoder(config, weights)
+    dec.store_logits, dec.stacked = True, True
+    ref.store_logits = True
+    kc = [np.zeros((config.kv_heads, config.max_ctx, config.head_dim), np.float16) for _ in range(config.layers)]
+    vc = [np.zeros((config.kv_heads, config.max_ctx, config.head_dim), np.float16) for _ in range(config.layers)]
+    for d in (dec, ref):
+        for e in d.layers:
+            e["k_cache"].fill(0, d.stream), e["v_cache"].fill(0, d.stream)
+    for pos, token in enumerate([3, 700, 41, 9]):
+        for d in (dec, ref):
+            d.set_input(token, pos)
+            d.step()
+        _, index = dec.result()
+        logits, hidden = dec.download("logits"), dec.download("h")
+        want_logits, want_best, want_h = od.dense_decoder_step(model, token, pos, kc, vc, linear)
+        bar_l = 3e-2 * np.abs(want_logits.astype(np.float32)).max()
+        assert np.abs(hidden.astype(np.float32) - want_h.astype(np.float32).ravel()).max() <= 3e-2 * np.abs(want_h.astype(np.float32)).max()
+        assert np.abs(logits.astype(np.float32) - want_logits.astype(np.float32)).max() <= bar_l
+        assert float(want_logits[want_best]) - float(want_logits[index]) <= bar_l
+        assert np.abs(logits.astype(np.float32) - ref.download("logits").astype(np.float32)).max() <= 1e-2 * np.abs(want_logits.astype(np.float32)).max()
+        for a, b in zip(dec.layers, ref.layers):          # the caches were appended by the fused epilogue
+            ka = a["k_cache"].download((config.kv_heads, config.max_ctx, config.head_dim), np.float16, dec.stream)
+            kb = b["k_cache"].download((config.kv_heads, config.max_ctx, config.head_dim), np.float16, ref.stream)
+            assert np.abs(ka.astype(np.float32) - kb.astype(np.float32)).max() <= 2e-2 * max(1.0, np.abs(kb.astype(np.float32)).max())
+    assert all(s.status() == 0 for s in dec.stacks) and dec.launches_per_step == 2 * config.layers + 5
