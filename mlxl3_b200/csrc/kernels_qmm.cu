@@ -45,7 +45,7 @@ constexpr uint32_t kRawBytes = 16 * 1024;
 constexpr int kGroupWarps = 8;        // decoder warps of a group: (tile row of the stage, quad of the 8-tile row)
 // Warp roles.  The single-thread roles take the lowest warp numbers: the scheduler favours older warps, and a
 // producer starved by spinning decoder warps stalls the whole pipeline.
-constexpr int kMmaWarp = 0, kActWarp = 1, kWeightWarp = 2, kFirstDecoder = 4;
+constexpr int kMmaWarp = 0, kActWarp = 1, kWeightWarp = 2, kWatchWarp = 3, kFirstDecoder = 4;
 constexpr uint32_t kAStageBytes = 128 * 128;           // 128 rows x 64 fp16
 
 // Two shapes of the same kernel.  Large (more than 64 rows): a CTA holds up to 512 tokens (two accumulator
@@ -155,6 +155,25 @@ __device__ __forceinline__ bool qmm_wait(uint64_t* bar, uint32_t parity, volatil
         if ((i & 255) == 0 && (*cta_failed || global_ns() - t0 > 250000000ull)) { *cta_failed = 1; return false; }
     }
 }
+__device__ __forceinline__ uint32_t ld_acquire_shared(const uint32_t* ptr) {
+    uint32_t v;
+    asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(smem_addr(ptr)) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_shared(uint32_t* ptr, uint32_t v) {
+    asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_addr(ptr)), "r"(v) : "memory");
+}
+// Bounded wait of one thread until the watcher's count has passed `it` (a shared-memory load answers in tens of
+// cycles, a barrier test in a few hundred).
+__device__ __forceinline__ bool qmm_wait_count(const uint32_t* count, int it, volatile int* cta_failed) {
+    for (int i = 0; i < 16384; ++i)
+        if (ld_acquire_shared(count) > static_cast<uint32_t>(it)) return true;
+    const unsigned long long t0 = global_ns();
+    for (int i = 1;; ++i) {
+        if (ld_acquire_shared(count) > static_cast<uint32_t>(it)) return true;
+        if ((i & 255) == 0 && (*cta_failed || global_ns() - t0 > 250000000ull)) { *cta_failed = 1; return false; }
+    }
+}
 // The same wait for a whole warp: one lane polls (32 lanes polling one barrier flood the shared-memory
 // pipe that the copies, the stores and the MMA issue also need), then every lane observes the completed
 // phase itself, which makes the data the barrier guards visible to it.
@@ -178,6 +197,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap xmap, const QmmArgs p) {
     __shared__ __align__(8) uint64_t full_a[kStages], done[kStages], full_b[S::kBSlots], accum_bar;
     __shared__ __align__(8) uint64_t raw_full[kRawDepthMax], raw_empty[kRawDepthMax];
     __shared__ uint32_t tmem_base_slot;
+    __shared__ uint32_t s_mma_ready;      // written by the watcher warp: product stages whose operands are in place
     __shared__ volatile int s_failed;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -215,6 +235,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap xmap, const QmmArgs p) {
         mbar_init(&accum_bar, 1);
         for (int d = 0; d < kRawDepth; ++d) { mbar_init(&raw_full[d], 1); mbar_init(&raw_empty[d], kGroupWarps); }
         s_failed = 0;
+        s_mma_ready = 0;
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == kMmaWarp) tmem_alloc(&tmem_base_slot, tmem_cols);
@@ -235,9 +256,20 @@ qmm_kernel(const __grid_constant__ CUtensorMap xmap, const QmmArgs p) {
         const uint32_t* my_quad = raw_base + (trow * 2 + quad) * kQuadWords;
         // A barrier test takes a few hundred cycles to answer, so the tests for the warp's next stage are
         // issued before the current stage is decoded and their answer is only looked at afterwards.
+        // Large shape: lane 0 tests the packed words and lane 1 the A stage in ONE instruction, so the warp stalls
+        // once, not twice (the warp barrier below orders the other lanes' reads after the two observations).  With two
+        // small CTAs per SM that was measured slower than every lane testing both.
         auto stage_ready = [&](int it) -> bool {
-            return mbar_test_wait(&raw_full[it % kRawDepth], (it / kRawDepth) & 1u) &
-                   mbar_test_wait(&done[it % kStages], ((it / kStages) & 1u) ^ 1u);
+            if constexpr (SMALL) {
+                return mbar_test_wait(&raw_full[it % kRawDepth], (it / kRawDepth) & 1u) &
+                       mbar_test_wait(&done[it % kStages], ((it / kStages) & 1u) ^ 1u);
+            } else {
+                uint64_t* bar = lane == 0 ? &raw_full[it % kRawDepth] : &done[it % kStages];
+                const uint32_t par = lane == 0 ? (it / kRawDepth) & 1u : ((it / kStages) & 1u) ^ 1u;
+                bool ok = true;
+                if (lane < 2) ok = mbar_test_wait(bar, par);
+                return ok;
+            }
         };
         bool ready = group < nst && stage_ready(group);
         for (int it = group; it < nst; it += S::kDecoderGroups) {
@@ -248,6 +280,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap xmap, const QmmArgs p) {
                         qmm_wait(&done[s], ((it / kStages) & 1u) ^ 1u, &s_failed);
                 if (!__all_sync(0xffffffffu, ready)) break;
             }
+            if constexpr (!SMALL) __syncwarp();
             unsigned char* a_stage = a_base + s * kAStageBytes;
             const uint4* qw = reinterpret_cast<const uint4*>(my_quad + rslot * kRawStageWords);
             const uint4 W2 = qw[geom.i2];
@@ -281,22 +314,21 @@ qmm_kernel(const __grid_constant__ CUtensorMap xmap, const QmmArgs p) {
         if (tr && threadIdx.x == 32 * kFirstDecoder) tr[2] = global_ns();
     } else if (warp == kActWarp) {
         // ================= activation producer: one tensor copy per half and stage =================
-        if (lane == 0) {
-            // a slot is free once the MMAs of the stage that used it last are done
-            int slot = 0;
+        if (lane < halves) {
+            // Lane h copies half h: the two halves' barrier tests (a few hundred cycles each) run side by side.
+            // A slot is free once the MMAs of the stage that used it last are done.
+            const int h = lane;
             for (int it = 0; it < nst && !s_failed; ++it) {
-                for (int h = 0; h < halves; ++h) {
-                    const int before = it * halves + h - S::kBSlots;     // the use of this slot one lap earlier
-                    if (before >= 0) {
-                        const int st = before / halves;
-                        if (!qmm_wait(&done[st % kStages], (st / kStages) & 1u, &s_failed)) break;
-                    }
-                    mbar_expect_tx(&full_b[slot], S::kBSlotBytes);
-                    tma_load_2d(b_base + slot * S::kBSlotBytes, &xmap, (st0 + it) * 64, brow0 + h * S::kTokHalf, &full_b[slot]);
-                    if (++slot == S::kBSlots) slot = 0;
+                const int u = it * halves + h, slot = u % S::kBSlots;
+                const int before = u - S::kBSlots;                       // the use of this slot one lap earlier
+                if (before >= 0) {
+                    const int st = before / halves;
+                    if (!qmm_wait(&done[st % kStages], (st / kStages) & 1u, &s_failed)) break;
                 }
+                mbar_expect_tx(&full_b[slot], S::kBSlotBytes);
+                tma_load_2d(b_base + slot * S::kBSlotBytes, &xmap, (st0 + it) * 64, brow0 + h * S::kTokHalf, &full_b[slot]);
             }
-            if (tr) tr[7] = global_ns();
+            if (tr && lane == 0) tr[7] = global_ns();
         }
     } else if (warp == kWeightWarp) {
         // ================= weight producer: one bulk copy (4 tile rows x 8 tiles, contiguous) per stage =================
@@ -311,30 +343,61 @@ qmm_kernel(const __grid_constant__ CUtensorMap xmap, const QmmArgs p) {
                 if (++slot == kRawDepth) { slot = 0; par ^= 1u; }
             }
         }
+    } else if (!SMALL && warp == kWatchWarp) {
+        // ================= watcher: all barriers of the next product stage in ONE test instruction =================
+        // A barrier test answers after a few hundred cycles and the thread that reads the answer stalls that long.
+        // Up to three tests in a row per stage (A stage, one or two activation slots) cost the issuing thread more
+        // time than issuing the stage's products: it, not the tensor pipe, set the pace.  Here lane 0 looks at the A
+        // stage and lanes 1, 2 at the activation slots, one instruction tests them all, and the count of stages whose
+        // operands are in place is published in shared memory, where the issuing thread reads it in tens of cycles.
+        // (Large shape only: with two small CTAs per SM the decoders set the pace and a second polling warp costs more
+        // than it saves -- measured.)
+        const uint32_t mask = halves == 2 ? 7u : 3u;
+        int idle = 0;
+        unsigned long long t0 = 0;
+        for (int it = 0; it < nst;) {
+            uint64_t* bar = nullptr;
+            uint32_t par = 0;
+            if (lane == 0) {
+                bar = &full_a[it % kStages]; par = (it / kStages) & 1u;
+            } else if (lane <= halves) {
+                const int u = it * halves + lane - 1;
+                bar = &full_b[u % S::kBSlots]; par = (u / S::kBSlots) & 1u;
+            }
+            bool ok = false;
+            if (bar != nullptr) ok = mbar_test_wait(bar, par);
+            if ((__ballot_sync(0xffffffffu, ok) & mask) == mask) {
+                ++it;
+                idle = 0;
+                if (lane == 0) st_release_shared(&s_mma_ready, static_cast<uint32_t>(it));
+                continue;
+            }
+            if ((++idle & 1023) == 0) {                                   // bounded like every other wait of the kernel
+                int give_up = 0;
+                if (lane == 0) {
+                    if (idle == 1024) t0 = global_ns();
+                    give_up = s_failed || global_ns() - t0 > 250000000ull;
+                    if (give_up) s_failed = 1;
+                }
+                if (__shfl_sync(0xffffffffu, give_up, 0)) break;
+            }
+        }
     } else if (warp == kMmaWarp) {
         // ================= MMA issuer =================
         if (lane == 0) {
-            // all barrier tests of a stage are issued together (each takes a few hundred cycles to answer)
+            // small shape: the thread tests the barriers itself, all tests of the next stage right after the commit
             auto stage_ready = [&](int it) -> bool {
-                bool ok = mbar_test_wait(&full_a[it % kStages], (it / kStages) & 1u);
-                for (int h = 0; h < halves; ++h) {
-                    const int u = it * halves + h;
-                    ok &= mbar_test_wait(&full_b[u % S::kBSlots], (u / S::kBSlots) & 1u);
-                }
-                return ok;
+                return mbar_test_wait(&full_a[it % kStages], (it / kStages) & 1u) &
+                       mbar_test_wait(&full_b[it % S::kBSlots], (it / S::kBSlots) & 1u);
             };
-            bool ready = nst > 0 && stage_ready(0);
+            bool ready = SMALL && nst > 0 && stage_ready(0);
             for (int it = 0; it < nst && !s_failed; ++it) {
                 const int s = it % kStages;
-                if (!ready) {
-                    if (!qmm_wait(&full_a[s], (it / kStages) & 1u, &s_failed)) break;
-                    bool ok = true;
-                    for (int h = 0; h < halves && ok; ++h) {
-                        const int u = it * halves + h;
-                        ok = qmm_wait(&full_b[u % S::kBSlots], (u / S::kBSlots) & 1u, &s_failed);
-                    }
-                    if (!ok) break;
-                }
+                if constexpr (SMALL) {
+                    if (!ready && (!qmm_wait(&full_a[s], (it / kStages) & 1u, &s_failed) ||
+                                   !qmm_wait(&full_b[it % S::kBSlots], (it / S::kBSlots) & 1u, &s_failed)))
+                        break;
+                } else if (!qmm_wait_count(&s_mma_ready, it, &s_failed)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t a_addr = smem_addr(a_base + s * kAStageBytes);
                 for (int h = 0; h < halves; ++h) {
@@ -345,7 +408,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap xmap, const QmmArgs p) {
                                  (it > 0 || kk > 0) ? 1u : 0u);
                 }
                 umma_commit(&done[s]);                                  // A stage and B slots free once these MMAs have read them
-                ready = it + 1 < nst && stage_ready(it + 1);
+                if constexpr (SMALL) ready = it + 1 < nst && stage_ready(it + 1);
             }
             umma_commit(&accum_bar);                                    // accumulator complete
             if (tr) tr[3] = global_ns();
