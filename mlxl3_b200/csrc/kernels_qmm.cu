@@ -459,17 +459,27 @@ qmm_kernel(const __grid_constant__ CUtensorMap xmap, const QmmArgs p) {
 #pragma unroll
                 for (int i = 0; i < 32; ++i) stage[i * 128 + lq * 32 + lane] = __float2half_rn(__uint_as_float(r[i]));
                 asm volatile("bar.sync %0, %1;" ::"r"(1 + cpart), "r"(128) : "memory");
-#pragma unroll 1
-                for (int j = 0; j < 8; ++j) {
+#pragma unroll 2
+                for (int j = 0; j < 8; ++j) {                            // two rows' shuffle chains in flight
                     const int t = lq * 8 + j, tok = tok0 + c + t;
                     if (tok >= p.rows) break;
                     __align__(8) __half h[4];
                     *reinterpret_cast<uint2*>(h) = *reinterpret_cast<const uint2*>(stage + t * 128 + lane * 4);
                     warp_hadamard128_f16(h, lane);
+                    if (p.y_dtype == kF16) {                            // one 8-byte store per lane
 #pragma unroll
-                    for (int e = 0; e < 4; ++e)
-                        store_from_half(p.y, p.y_dtype, static_cast<int64_t>(tok) * p.out + cblock * 128 + lane * 4 + e,
-                                        __hmul_rn(h[e], sv[e]), bias, lane * 4 + e);
+                        for (int e = 0; e < 4; ++e) {
+                            h[e] = __hmul_rn(h[e], sv[e]);
+                            if (bias) h[e] = __hadd_rn(h[e], bias[lane * 4 + e]);
+                        }
+                        *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(p.y) + static_cast<int64_t>(tok) * p.out + cblock * 128 +
+                                                  lane * 4) = *reinterpret_cast<const uint2*>(h);
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            store_from_half(p.y, p.y_dtype, static_cast<int64_t>(tok) * p.out + cblock * 128 + lane * 4 + e,
+                                            __hmul_rn(h[e], sv[e]), bias, lane * 4 + e);
+                    }
                 }
                 buf ^= 1;
             }
