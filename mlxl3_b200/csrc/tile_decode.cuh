@@ -97,12 +97,15 @@ __device__ __forceinline__ void lane_weights_exact(uint32_t w2, uint32_t w1, uin
         };
         a0 = pair(b[0], b[1]); a1 = pair(b[4], b[5]); a2 = pair(b[2], b[3]); a3 = pair(b[6], b[7]);
     } else {
+        // a weight is the fp16 sum of the two halves of its masked hash: two scalar adds that select their halves
+        // (no repacking before them) and one merge -- one logic-pipe instruction less per pair than packing
+        // (lo, lo) and (hi, hi) first
         auto pair = [&](uint32_t x, uint32_t y) {
             x = lop3_and_xor(x, 0x8fff8fffu, 0x3b603b60u);
             y = lop3_and_xor(y, 0x8fff8fffu, 0x3b603b60u);
-            uint32_t lo2 = prmt(x, y, 0x5410), hi2 = prmt(x, y, 0x7632);
-            __half2 w = __hadd2_rn(*reinterpret_cast<__half2*>(&lo2), *reinterpret_cast<__half2*>(&hi2));
-            return *reinterpret_cast<uint32_t*>(&w);
+            const __half2 hx = *reinterpret_cast<__half2*>(&x), hy = *reinterpret_cast<__half2*>(&y);
+            const __half2 w = __halves2half2(__hadd_rn(__low2half(hx), __high2half(hx)), __hadd_rn(__low2half(hy), __high2half(hy)));
+            return *reinterpret_cast<const uint32_t*>(&w);
         };
         a0 = pair(b[0], b[1]); a1 = pair(b[4], b[5]); a2 = pair(b[2], b[3]); a3 = pair(b[6], b[7]);
     }
