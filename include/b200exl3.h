@@ -247,13 +247,15 @@ int b200exl3_moe_forward(const b200exl3_moe* handle, const void* d_x, int x_dtyp
                          const uint32_t* d_selected, const void* d_scores, int score_dtype, void* d_y,
                          void* d_workspace, size_t workspace_bytes, b200exl3_stream stream);
 
-/* ---- layers with a fused prologue (fp16, 1 or 2 rows: decode) ---------------------------------------------------
+/* ---- layers with a fused prologue (fp16; 1 to 8 rows, the SwiGLU prologue alone any number of rows) --------------
  * The reference fuses the operators around a projection into its prologue kernels where dispatch count matters
  * (flash_up_finish_swiglu_prepare and its neighbours, native/shaders/exl3.metal:240-291).  Here the layer kernel's own
  * input rotation takes the operator in front of it:
  *   kind 1  RMSNorm: s = half(x + aux) (aux = residual rows or NULL), input = weight * half(s * rsqrt(mean(s^2) + eps));
  *           s is also stored to d_sum when that is not NULL (it must not be x: other warps still read x);
- *   kind 2  SwiGLU: input = half(half(x * half(sigmoid(x))) * aux), x = gate rows, aux = up rows.
+ *   kind 2  SwiGLU: input = half(half(x * half(sigmoid(x))) * aux), x = gate rows, aux = up rows.  With more than 8
+ *           rows (prefill: the tensor-core product) it is applied by the input-rotation kernel, so a dense MLP block
+ *           is [gate | up] -> down with no kernel between them.
  * Same arithmetic as b200exl3_rms_norm / b200exl3_swiglu followed by the plain forward; the row sum of the norm is added
  * in another order, so the last fp32 bit of 1/rms may differ from the stand-alone kernel's.  Kind 1 makes every warp
  * add up the whole row; the cheaper pairing is the residual EPILOGUE of the layer before (which already holds each

@@ -426,6 +426,13 @@ static int forward_common(const LayerCore& c, const void* d_x, int x_dtype, cons
     const bool exact = (c.flags & B200EXL3_EXACT_WEIGHTS) != 0;
     const size_t x_size = dtype_size(x_dtype);
     const __half* xhat = reinterpret_cast<const __half*>(d_xhat);
+    // more rows than the fused kernel rotates itself: the input rotation is a kernel of its own, and the SwiGLU
+    // prologue (the only one taken with that many rows) is applied there
+    const __half* glu_up = nullptr;
+    if (pro && pro->kind == 2 && rows > kQmvFusedRows) {
+        glu_up = reinterpret_cast<const __half*>(pro->d_aux);
+        pro = nullptr;
+    }
     if (rows >= kQmmMinRows && ys && !d_xhat && g_qmm_enabled) {
         // many rows: input rotation -> tensor-core product (fp32 partials per input split) -> output rotation.
         // A group runs member by member (each member has its own input scales, so its own rotated rows); a row shard
@@ -438,7 +445,7 @@ static int forward_common(const LayerCore& c, const void* d_x, int x_dtype, cons
             const __half* svh = c.svh + c.gcol0[g];
             const __half* bias = c.bias ? c.bias + c.gcol0[g] : nullptr;
             const int ld = c.out / 16, col0 = c.gcol0[g] / 16;
-            B200_TRY(launch_prepare(d_x, x_dtype, c.suh + static_cast<size_t>(g) * c.in, 1, rows, c.in, buf, stream), "prepare");
+            B200_TRY(launch_prepare(d_x, x_dtype, c.suh + static_cast<size_t>(g) * c.in, 1, rows, c.in, buf, stream, glu_up), "prepare");
             if (tp) {
                 qp.splits = 1;
                 B200_TRY(launch_qmm(c.wq, c.in, c.gout[g], c.k, c.cb, buf, rows, qp, partials, status, nullptr, nullptr, nullptr, 0, stream, ld, col0),
@@ -465,7 +472,7 @@ static int forward_common(const LayerCore& c, const void* d_x, int x_dtype, cons
         __half* buf = reinterpret_cast<__half*>(base + kCounterBytes + qmv_partial_bytes(first, c.out, rows));
         for (int g = 0; g < c.groups; ++g)
             B200_TRY(launch_prepare(d_x, x_dtype, c.suh + static_cast<size_t>(g) * c.in, 1, rows, c.in,
-                                    buf + static_cast<size_t>(g) * rows * c.in, stream), "prepare");
+                                    buf + static_cast<size_t>(g) * rows * c.in, stream, glu_up), "prepare");
         xhat = buf;
     }
     for (int64_t r0 = 0; r0 < rows; r0 += kMaxBatchRows) {
@@ -574,7 +581,10 @@ int b200exl3_linear_decode(const b200exl3_linear* h, uint16_t* d_w, b200exl3_str
 
 static int check_prologue(const b200exl3_prologue* pro, const void* d_x, int64_t rows) {
     if (!pro) return fail("NULL argument");
-    if (rows < 1 || rows > kQmvFusedRows) return fail("a fused prologue takes 1 or %d rows, got %lld", kQmvFusedRows, static_cast<long long>(rows));
+    // any number of rows for the SwiGLU prologue alone (with many rows it is applied by the input-rotation kernel)
+    const bool glu_only = pro->kind == 2 && pro->epilogue == 0;
+    if (rows < 1 || (rows > kQmvFusedRows && !glu_only))
+        return fail("a fused prologue takes 1 to %d rows (the SwiGLU prologue alone: any number), got %lld", kQmvFusedRows, static_cast<long long>(rows));
     if (pro->kind < 0 || pro->kind > 3) return fail("unknown prologue kind %d", pro->kind);
     if ((pro->kind == 1 || pro->kind == 3) && (!pro->d_weight || !(pro->eps >= 0.0f)))
         return fail("the RMSNorm prologue needs a weight and a non-negative epsilon");

@@ -44,7 +44,7 @@ cudaError_t launch_reconstruct(const uint16_t* trellis, int tiles_k, int tiles_n
 // ---- rotations (kernels_rotate.cu) ----------------------------------------------------------------
 // xhat[r, :] = H128(half(half(x[r, :]) * suh[(r % scale_rows), :])); scale_rows is 1 or rows.
 cudaError_t launch_prepare(const void* x, int x_dtype, const __half* suh, int64_t scale_rows, int64_t rows, int in,
-                           __half* xhat, cudaStream_t stream);
+                           __half* xhat, cudaStream_t stream, const __half* glu_up = nullptr);
 // y = half(H128(half(sum_s partials[s, r, :]))) * svh (+ bias), written in y_dtype.
 cudaError_t launch_finish(const float* partials, int splits, int64_t split_stride, const __half* svh,
                           int64_t scale_rows, const __half* bias, int64_t rows, int out, int y_dtype, void* y,

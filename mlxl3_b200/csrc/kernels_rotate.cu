@@ -8,7 +8,7 @@ namespace b200exl3 {
 
 __global__ void __launch_bounds__(256)
 prepare_kernel(const void* __restrict__ x, int x_dtype, const __half* __restrict__ suh, int64_t scale_rows,
-               int64_t rows, int in, __half* __restrict__ xhat) {
+               int64_t rows, int in, __half* __restrict__ xhat, const __half* __restrict__ glu_up) {
     const int lane = threadIdx.x & 31;
     const int blocks_per_row = in >> 7;
     const int64_t total = rows * blocks_per_row;
@@ -18,8 +18,25 @@ prepare_kernel(const void* __restrict__ x, int x_dtype, const __half* __restrict
         const int col = static_cast<int>(unit % blocks_per_row) * 128 + lane * 4;
         const __half* s = suh + (scale_rows == 1 ? 0 : row * in) + col;
         __align__(8) __half h[4];
+        if (glu_up != nullptr) {
+            // SwiGLU of two fp16 row sets as the input (x = gate rows): half(gate * sigmoid(gate)) * up, each product
+            // rounded to half, the arithmetic of the stand-alone SwiGLU kernel and of the small-batch prologue
+            const uint2 gv = *reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(x) + row * in + col);
+            const uint2 uv = *reinterpret_cast<const uint2*>(glu_up + row * in + col);
+            const __half2* gh = reinterpret_cast<const __half2*>(&gv);
+            const __half2* uh = reinterpret_cast<const __half2*>(&uv);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) h[j] = __hmul_rn(load_as_half(x, x_dtype, row * in + col + j), s[j]);
+            for (int j = 0; j < 2; ++j) {
+                const float2 f = __half22float2(gh[j]);
+                const __half2 sg = __floats2half2_rn(1.0f / (1.0f + expf(-f.x)), 1.0f / (1.0f + expf(-f.y)));
+                const __half2 v = __hmul2_rn(__hmul2_rn(gh[j], sg), uh[j]);
+                h[2 * j] = __hmul_rn(__low2half(v), s[2 * j]);
+                h[2 * j + 1] = __hmul_rn(__high2half(v), s[2 * j + 1]);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) h[j] = __hmul_rn(load_as_half(x, x_dtype, row * in + col + j), s[j]);
+        }
         warp_hadamard128_f16(h, lane);
         *reinterpret_cast<uint2*>(xhat + row * in + col) = *reinterpret_cast<uint2*>(h);
     }
@@ -65,9 +82,10 @@ static unsigned grid_for(int64_t units) {
 }
 
 cudaError_t launch_prepare(const void* x, int x_dtype, const __half* suh, int64_t scale_rows, int64_t rows, int in,
-                           __half* xhat, cudaStream_t stream) {
+                           __half* xhat, cudaStream_t stream, const __half* glu_up) {
     if (rows == 0) return cudaSuccess;
-    prepare_kernel<<<grid_for(rows * (in / 128)), 256, 0, stream>>>(x, x_dtype, suh, scale_rows, rows, in, xhat);
+    if (glu_up != nullptr && x_dtype != kF16) return cudaErrorInvalidValue;
+    prepare_kernel<<<grid_for(rows * (in / 128)), 256, 0, stream>>>(x, x_dtype, suh, scale_rows, rows, in, xhat, glu_up);
     return cudaGetLastError();
 }
 

@@ -351,17 +351,17 @@ class DenseMlp:
 
     def _ensure(self, rows: int) -> None:
         if rows > self._rows:
-            self._bufs = [DeviceBuffer(rows * self.ffn * 2) for _ in range(3)]
+            self._bufs = [DeviceBuffer(rows * self.ffn * 2) for _ in range(2)]
             self._ws = new_workspace(max(self.group.workspace_bytes(rows), self.down.workspace_bytes(rows)))
             self._rows = rows
 
     def forward_device(self, d_x: int, rows: int, d_y: int, stream: Stream = DEFAULT_STREAM) -> None:
         """fp16 rows in, fp16 rows out, no host copies."""
         self._ensure(rows)
-        gate, up, act = self._bufs
+        gate, up = self._bufs
         self.group.forward_device(d_x, F16, rows, [gate.ptr, up.ptr], self._ws, stream)
-        swiglu(gate.ptr, up.ptr, rows * self.ffn, act.ptr, stream)
-        self.down.forward_device(act.ptr, F16, rows, d_y, self._ws, stream)
+        # SwiGLU is the prologue of the down projection's input rotation (any number of rows)
+        self.down.forward_fused_device(Prologue.swiglu(up.ptr), gate.ptr, rows, d_y, self._ws, stream)
 
     def forward(self, x: np.ndarray, stream: Stream = DEFAULT_STREAM) -> np.ndarray:
         x = np.ascontiguousarray(x, np.float16)

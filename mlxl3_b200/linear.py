@@ -74,7 +74,7 @@ def static_status(clear: bool = False) -> int:
 
 class Prologue(ctypes.Structure):
     """``b200exl3_prologue``: the operators fused in front of a layer's input rotation and behind its output rotation
-    (fp16, 1 or 2 rows)."""
+    (fp16; 1 to 8 rows, the SwiGLU prologue alone any number of rows)."""
     _fields_ = [("kind", ctypes.c_int), ("d_aux", c_void_p), ("d_weight", c_void_p), ("d_sum", c_void_p), ("eps", ctypes.c_float),
                 ("d_sumsq", c_void_p), ("epilogue", ctypes.c_int), ("d_residual", c_void_p), ("d_residual_out", c_void_p),
                 ("d_sumsq_out", c_void_p), ("d_pos", c_void_p), ("theta", ctypes.c_float), ("max_ctx", ctypes.c_int),

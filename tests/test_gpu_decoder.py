@@ -250,8 +250,20 @@ def test_fused_prologues_match_the_separate_kernels(gpu):
         nxt.forward_fused_device(Prologue.rms_norm_from_blocks(d_wn.ptr, 1e-5, d_sq.ptr), d_h.ptr, rows, z1.ptr, ws2, stream)
         za, zb = z0.download((rows, 256), np.float16, stream).astype(np.float32), z1.download((rows, 256), np.float16, stream).astype(np.float32)
         assert np.abs(za - zb).max() <= 2e-3 * np.abs(za).max()
-    with pytest.raises(gpu.B200Exl3Error, match="1 or 2 rows"):
-        layer.forward_fused_device(Prologue.swiglu(d_u.ptr), d_g.ptr, 3, y1.ptr, ws, stream)
+    with pytest.raises(gpu.B200Exl3Error, match="1 to 2 rows"):
+        layer.forward_fused_device(Prologue.rms_norm(d_w.ptr, 1e-5), d_x.ptr, 3, y1.ptr, ws, stream)
+    # the SwiGLU prologue alone takes any number of rows: from 3 rows on the input-rotation kernel applies it (fused
+    # small-batch kernel up to 8 rows, tensor-core product from 9), bit-identical to the stand-alone kernel + plain layer
+    for rows in (3, 12, 70):
+        g, u = (rng.standard_normal((rows, n_in)) * 2).astype(np.float16), rng.standard_normal((rows, n_in)).astype(np.float16)
+        d_g, d_u, d_a = DeviceBuffer.from_numpy(g), DeviceBuffer.from_numpy(u), DeviceBuffer(g.nbytes)
+        y0, y1 = DeviceBuffer(rows * n_out * 2), DeviceBuffer(rows * n_out * 2)
+        ws = gpu.new_workspace(layer.workspace_bytes(rows))
+        dec.swiglu(d_g.ptr, d_u.ptr, g.size, d_a.ptr, stream)
+        layer.forward_device(d_a.ptr, gpu.F16, rows, y0.ptr, ws, stream)
+        layer.forward_fused_device(Prologue.swiglu(d_u.ptr), d_g.ptr, rows, y1.ptr, ws, stream)
+        assert np.array_equal(bits(y0.download((rows, n_out), np.float16, stream)), bits(y1.download((rows, n_out), np.float16, stream)))
+        assert gpu.workspace_status(ws) == 0
     with pytest.raises(gpu.B200Exl3Error, match="over its own input"):
         layer.forward_fused_device(Prologue.rms_norm(d_w.ptr, 1e-5, d_r.ptr, d_x.ptr), d_x.ptr, 1, y1.ptr, ws, stream)
 
