@@ -178,8 +178,8 @@ route_plan_kernel(const uint32_t* __restrict__ selected, int64_t slots, int expe
     // One warp per expert walks the slots in order, 32 at a time: a slot's position among its expert's rows is the
     // number of earlier slots with the same expert (ballot + population count), so the plan (and with it the
     // summation order of every row's products, which depends on the segment a row lands in) is the same on every call.
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     {
-        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
         for (int e = warp; e < experts; e += warps) {
             int pos = 0;
             for (int64_t s0 = 0; s0 < slots; s0 += 32) {
@@ -193,11 +193,25 @@ route_plan_kernel(const uint32_t* __restrict__ selected, int64_t slots, int expe
         }
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        int at = 0;
-        for (int e = 0; e < experts; ++e) { base[e] = at; at += (count[e] + seg_rows - 1) / seg_rows; }
-        base[experts] = at;
-        seg_count[0] = min(at, max_segments);
+    if (warp == 0) {
+        // first segment of every expert: a running sum of the experts' segment counts, 32 experts per step of one warp
+        int carry = 0;
+        for (int e0 = 0; e0 < experts; e0 += 32) {
+            const int e = e0 + lane;
+            const int segs = e < experts ? (count[e] + seg_rows - 1) / seg_rows : 0;
+            int incl = segs;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int up = __shfl_up_sync(0xffffffffu, incl, d);
+                if (lane >= d) incl += up;
+            }
+            if (e < experts) base[e] = carry + incl - segs;
+            carry += __shfl_sync(0xffffffffu, incl, 31);
+        }
+        if (lane == 0) {
+            base[experts] = carry;
+            seg_count[0] = min(carry, max_segments);
+        }
     }
     __syncthreads();
     for (int e = threadIdx.x; e < experts; e += blockDim.x)
@@ -228,6 +242,9 @@ route_plan_grouped_kernel(const uint32_t* __restrict__ selected, int64_t slots, 
     int* base = s_mem + experts;        // [experts + 1] first segment of each expert
     unsigned short* table = reinterpret_cast<unsigned short*>(s_mem + 2 * experts + 1);   // [groups][experts]: counts, then positions
     const int groups = static_cast<int>((slots + 31) / 32);
+    // every slot's expert and its rank inside its group stay in shared memory between the passes
+    unsigned short* slot_expert = table + static_cast<size_t>(groups) * experts;         // [groups * 32]
+    unsigned char* slot_rank = reinterpret_cast<unsigned char*>(slot_expert + static_cast<size_t>(groups) * 32);   // [groups * 32]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     for (int i = threadIdx.x; i < groups * experts; i += blockDim.x) table[i] = 0;
     for (int64_t r = threadIdx.x; r < static_cast<int64_t>(max_segments) * seg_rows; r += blockDim.x) row_slot[r] = kNoSlot;
@@ -238,7 +255,8 @@ route_plan_grouped_kernel(const uint32_t* __restrict__ selected, int64_t slots, 
         const unsigned int same = __match_any_sync(0xffffffffu, e);
         const int rank = __popc(same & ((1u << lane) - 1u));
         if (s < slots) {
-            slot_row[s] = static_cast<uint32_t>(rank);                      // rank inside the group, for pass 3
+            slot_expert[s] = static_cast<unsigned short>(e);
+            slot_rank[s] = static_cast<unsigned char>(rank);                // rank inside the group, for pass 3
             if (rank == 0) table[g * experts + e] = static_cast<unsigned short>(__popc(same));
         }
     }
@@ -253,18 +271,32 @@ route_plan_grouped_kernel(const uint32_t* __restrict__ selected, int64_t slots, 
         count[e] = running;
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        int at = 0;
-        for (int e = 0; e < experts; ++e) { base[e] = at; at += (count[e] + seg_rows - 1) / seg_rows; }
-        base[experts] = at;
-        seg_count[0] = min(at, max_segments);
+    if (warp == 0) {
+        // first segment of every expert: a running sum of the experts' segment counts, 32 experts per step of one warp
+        int carry = 0;
+        for (int e0 = 0; e0 < experts; e0 += 32) {
+            const int e = e0 + lane;
+            const int segs = e < experts ? (count[e] + seg_rows - 1) / seg_rows : 0;
+            int incl = segs;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int up = __shfl_up_sync(0xffffffffu, incl, d);
+                if (lane >= d) incl += up;
+            }
+            if (e < experts) base[e] = carry + incl - segs;
+            carry += __shfl_sync(0xffffffffu, incl, 31);
+        }
+        if (lane == 0) {
+            base[experts] = carry;
+            seg_count[0] = min(carry, max_segments);
+        }
     }
     __syncthreads();
     for (int e = threadIdx.x; e < experts; e += blockDim.x)
         for (int s = base[e]; s < base[e + 1] && s < max_segments; ++s) seg_expert[s] = static_cast<uint32_t>(e);
     for (int64_t s = threadIdx.x; s < slots; s += blockDim.x) {
-        const int e = static_cast<int>(min(selected[s], static_cast<uint32_t>(experts - 1)));
-        const int pos = table[(s >> 5) * experts + e] + static_cast<int>(slot_row[s]);
+        const int e = slot_expert[s];
+        const int pos = table[(s >> 5) * experts + e] + static_cast<int>(slot_rank[s]);
         const int64_t row = static_cast<int64_t>(base[e] + pos / seg_rows) * seg_rows + pos % seg_rows;
         slot_row[s] = static_cast<uint32_t>(row);
         if (row < static_cast<int64_t>(max_segments) * seg_rows) row_slot[row] = static_cast<uint32_t>(s);
@@ -397,7 +429,8 @@ cudaError_t launch_route_plan(const uint32_t* selected, int64_t slots, int exper
                               uint32_t* seg_expert, uint32_t* row_slot, uint32_t* slot_row, cudaStream_t stream) {
     if (experts > 65535 || slots >= 65535) return cudaErrorInvalidValue;              // positions are kept in 16 bits
     const size_t groups = static_cast<size_t>((slots + 31) / 32);
-    const size_t grouped = (2 * static_cast<size_t>(experts) + 1) * sizeof(int) + groups * experts * sizeof(unsigned short);
+    const size_t grouped = (2 * static_cast<size_t>(experts) + 1) * sizeof(int) + groups * experts * sizeof(unsigned short) +
+                           groups * 32 * (sizeof(unsigned short) + sizeof(unsigned char));
     if (grouped <= 48 * 1024) {
         return launch_dependent(route_plan_grouped_kernel, dim3(1), dim3(1024), grouped, stream, selected, slots, experts, max_segments,
                                 seg_rows, seg_count, seg_expert, row_slot, slot_row);
