@@ -191,7 +191,7 @@ class DenseDecoder:
         self.graph = None
         self.store_logits = False
         self.fused = True            # norms, residual adds and SwiGLU run inside the projections' kernels; False: as kernels of their own
-        self.stacked = False         # True (with fused): o, [gate|up], down and the next block's [q|k|v] are ONE persistent launch
+        self.stacked = False         # True (with fused, one GPU): o, [gate|up], down and the next block's [q|k|v] are ONE persistent launch
         self.stacks = None
         self.hidden_name = "h"       # buffer that holds the residual stream after a step
         self.launches_per_step = 0
@@ -255,7 +255,8 @@ class DenseDecoder:
         self.launches_per_step = 2 * len(self.layers) + 5
 
     def _launch(self) -> None:
-        if self.fused and self.stacked and self.config.head_dim == 128:
+        # one persistent launch per block: single GPU only (with tensor parallelism the per-layer kernels run)
+        if self.fused and self.stacked and self.config.head_dim == 128 and self.tp is None:
             return self._launch_stacked()
         if self.fused:
             return self._launch_fused()
