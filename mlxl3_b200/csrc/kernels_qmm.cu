@@ -189,6 +189,11 @@ template <int K, int CB, bool SMALL>
 __global__ void __launch_bounds__(QmmShape<SMALL>::kThreads, QmmShape<SMALL>::kMinBlocks)
 qmm_kernel(const __grid_constant__ CUtensorMap xmap, const QmmArgs p) {
     using S = QmmShape<SMALL>;
+    // Dependent launch: this kernel may be scheduled under the tail of the kernel before it (the input rotation, the
+    // glue of the expert block); everything it reads from global memory -- rotated rows, the segment table -- was written
+    // by that kernel, so it waits here before its first read.
+    pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int kQuadWords = 32 * K;                       // four interleaved tiles
     constexpr int kRawStageWords = 8 * kQuadWords;           // 4 tile rows x 2 quads
@@ -526,8 +531,7 @@ cudaError_t qmm_launch_shape(const CUtensorMap& map, const QmmArgs& p, dim3 grid
         if (e != cudaSuccess) return e;
         attribute.mark();
     }
-    kernel<<<grid, S::kThreads, smem, stream>>>(map, p);
-    return cudaGetLastError();
+    return launch_dependent(kernel, grid, dim3(S::kThreads), smem, stream, map, p);
 }
 
 template <int K, int CB>

@@ -9,6 +9,8 @@ namespace b200exl3 {
 __global__ void __launch_bounds__(256)
 prepare_kernel(const void* __restrict__ x, int x_dtype, const __half* __restrict__ suh, int64_t scale_rows,
                int64_t rows, int in, __half* __restrict__ xhat, const __half* __restrict__ glu_up) {
+    pdl_launch_dependents();                    // the kernel after this one may start; it waits for our memory itself
+    pdl_wait();                                 // what the kernel before this one wrote is visible from here on
     const int lane = threadIdx.x & 31;
     const int blocks_per_row = in >> 7;
     const int64_t total = rows * blocks_per_row;
@@ -46,6 +48,8 @@ __global__ void __launch_bounds__(256)
 finish_kernel(const float* __restrict__ partials, int splits, int64_t split_stride, const __half* __restrict__ svh,
               int64_t scale_rows, const __half* __restrict__ bias, int64_t rows, int out, int y_dtype,
               void* __restrict__ y) {
+    pdl_launch_dependents();                    // the kernel after this one may start; it waits for our memory itself
+    pdl_wait();                                 // what the kernel before this one wrote is visible from here on
     const int lane = threadIdx.x & 31;
     const int blocks_per_row = out >> 7;
     const int64_t total = rows * blocks_per_row;
@@ -85,17 +89,16 @@ cudaError_t launch_prepare(const void* x, int x_dtype, const __half* suh, int64_
                            __half* xhat, cudaStream_t stream, const __half* glu_up) {
     if (rows == 0) return cudaSuccess;
     if (glu_up != nullptr && x_dtype != kF16) return cudaErrorInvalidValue;
-    prepare_kernel<<<grid_for(rows * (in / 128)), 256, 0, stream>>>(x, x_dtype, suh, scale_rows, rows, in, xhat, glu_up);
-    return cudaGetLastError();
+    return launch_dependent(prepare_kernel, dim3(grid_for(rows * (in / 128))), dim3(256), 0, stream, x, x_dtype, suh, scale_rows, rows, in, xhat,
+                            glu_up);
 }
 
 cudaError_t launch_finish(const float* partials, int splits, int64_t split_stride, const __half* svh,
                           int64_t scale_rows, const __half* bias, int64_t rows, int out, int y_dtype, void* y,
                           cudaStream_t stream) {
     if (rows == 0) return cudaSuccess;
-    finish_kernel<<<grid_for(rows * (out / 128)), 256, 0, stream>>>(partials, splits, split_stride, svh, scale_rows, bias,
-                                                                    rows, out, y_dtype, y);
-    return cudaGetLastError();
+    return launch_dependent(finish_kernel, dim3(grid_for(rows * (out / 128))), dim3(256), 0, stream, partials, splits, split_stride, svh,
+                            scale_rows, bias, rows, out, y_dtype, y);
 }
 
 }  // namespace b200exl3
