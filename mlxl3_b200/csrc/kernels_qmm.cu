@@ -190,10 +190,13 @@ __global__ void __launch_bounds__(QmmShape<SMALL>::kThreads, QmmShape<SMALL>::kM
 qmm_kernel(const __grid_constant__ CUtensorMap xmap, const QmmArgs p) {
     using S = QmmShape<SMALL>;
     // Dependent launch: this kernel may be scheduled under the tail of the kernel before it (the input rotation, the
-    // glue of the expert block); everything it reads from global memory -- rotated rows, the segment table -- was written
-    // by that kernel, so it waits here before its first read.
+    // glue of the expert block).  The packed weights are nobody's output, so the barriers, the tensor memory and the
+    // first weight copies do not wait; what that kernel wrote -- the rotated rows, the segment table -- is read only
+    // after griddepcontrol.wait (expert-mapped mode: at once, the table is read first; otherwise by the activation
+    // producer before its first copy), and nothing is stored to global memory before it either (the decoders wait
+    // before the epilogue).
     pdl_launch_dependents();
-    pdl_wait();
+    if (p.map_expert != nullptr) pdl_wait();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int kQuadWords = 32 * K;                       // four interleaved tiles
     constexpr int kRawStageWords = 8 * kQuadWords;           // 4 tile rows x 2 quads
@@ -323,6 +326,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap xmap, const QmmArgs p) {
             // Lane h copies half h: the two halves' barrier tests (a few hundred cycles each) run side by side.
             // A slot is free once the MMAs of the stage that used it last are done.
             const int h = lane;
+            pdl_wait();
             for (int it = 0; it < nst && !s_failed; ++it) {
                 const int u = it * halves + h, slot = u % S::kBSlots;
                 const int before = u - S::kBSlots;                       // the use of this slot one lap earlier
@@ -422,6 +426,7 @@ qmm_kernel(const __grid_constant__ CUtensorMap xmap, const QmmArgs p) {
 
     // ================= epilogue: accumulator -> fp32 partial products =================
     if (dec >= 0) {
+        pdl_wait();                                                     // returns at once: the kernel before ended long ago
         if (nst > 0) {
             qmm_wait_warp(&accum_bar, 0, &s_failed, lane);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -500,7 +505,10 @@ qmm_kernel(const __grid_constant__ CUtensorMap xmap, const QmmArgs p) {
         while (global_ns() - t0 < 2000000ull) __nanosleep(1000);
     }
     if (warp == kMmaWarp) tmem_dealloc(tmem, tmem_cols);
-    if (threadIdx.x == 0 && s_failed) atomicExch(p.error, 3u);
+    if (threadIdx.x == 0 && s_failed) {
+        pdl_wait();
+        atomicExch(p.error, 3u);
+    }
 }
 
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
