@@ -338,26 +338,58 @@ head_kernel(const __half* __restrict__ x, const __half* __restrict__ w, int64_t 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float best_v = -INFINITY;
     int64_t best_i = INT64_MAX;
-    for (int64_t row = static_cast<int64_t>(blockIdx.x) * kHeadWarps + warp; row < vocab; row += static_cast<int64_t>(gridDim.x) * kHeadWarps) {
-        const uint4* wr = reinterpret_cast<const uint4*>(w + row * hidden);
-        float acc = 0.0f;
-        for (int i = lane; i < hidden / 8; i += 32) {
-            const uint4 wv = __ldcs(wr + i);
-            const uint4 xv = reinterpret_cast<const uint4*>(s_x)[i];
-            const __half2* wh = reinterpret_cast<const __half2*>(&wv);
-            const __half2* xh = reinterpret_cast<const __half2*>(&xv);
+    // Two rows per round and eight loads per lane in flight: the kernel streams 1 GB, so what counts is how many bytes
+    // each warp keeps on their way.  Every row's sum is still added in the same order (lane-strided, then the warp sum).
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * kHeadWarps;
+    const int steps = hidden / 8;
+    for (int64_t row = static_cast<int64_t>(blockIdx.x) * kHeadWarps + warp; row < vocab; row += 2 * stride) {
+        const bool two = row + stride < vocab;
+        const uint4* wr0 = reinterpret_cast<const uint4*>(w + row * hidden);
+        const uint4* wr1 = reinterpret_cast<const uint4*>(w + (two ? row + stride : row) * hidden);
+        float acc0 = 0.0f, acc1 = 0.0f;
+        int i = lane;
+        for (; i + 96 < steps; i += 128) {
+            uint4 wa[4], wb[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float2 a = __half22float2(wh[j]), b = __half22float2(xh[j]);
-                acc = fmaf(a.x, b.x, acc);
-                acc = fmaf(a.y, b.y, acc);
+            for (int u = 0; u < 4; ++u) { wa[u] = __ldcs(wr0 + i + 32 * u); wb[u] = __ldcs(wr1 + i + 32 * u); }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const uint4 xv = reinterpret_cast<const uint4*>(s_x)[i + 32 * u];
+                const __half2* xh = reinterpret_cast<const __half2*>(&xv);
+                const __half2* ah = reinterpret_cast<const __half2*>(&wa[u]);
+                const __half2* bh = reinterpret_cast<const __half2*>(&wb[u]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 b = __half22float2(xh[j]), a0 = __half22float2(ah[j]), a1 = __half22float2(bh[j]);
+                    acc0 = fmaf(a0.x, b.x, acc0); acc0 = fmaf(a0.y, b.y, acc0);
+                    acc1 = fmaf(a1.x, b.x, acc1); acc1 = fmaf(a1.y, b.y, acc1);
+                }
             }
         }
-        acc = warp_sum(acc);
-        const __half rounded = __float2half_rn(acc);
-        if (lane == 0 && logits != nullptr) logits[row] = rounded;
-        const float v = __half2float(rounded);
-        if (better(v, row + index_offset, best_v, best_i)) { best_v = v; best_i = row + index_offset; }
+        for (; i < steps; i += 32) {
+            const uint4 va = __ldcs(wr0 + i), vb = __ldcs(wr1 + i);
+            const uint4 xv = reinterpret_cast<const uint4*>(s_x)[i];
+            const __half2* xh = reinterpret_cast<const __half2*>(&xv);
+            const __half2* ah = reinterpret_cast<const __half2*>(&va);
+            const __half2* bh = reinterpret_cast<const __half2*>(&vb);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 b = __half22float2(xh[j]), a0 = __half22float2(ah[j]), a1 = __half22float2(bh[j]);
+                acc0 = fmaf(a0.x, b.x, acc0); acc0 = fmaf(a0.y, b.y, acc0);
+                acc1 = fmaf(a1.x, b.x, acc1); acc1 = fmaf(a1.y, b.y, acc1);
+            }
+        }
+        acc0 = warp_sum(acc0);
+        acc1 = warp_sum(acc1);
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            if (r == 1 && !two) break;
+            const int64_t at = row + r * stride;
+            const __half rounded = __float2half_rn(r == 0 ? acc0 : acc1);
+            if (lane == 0 && logits != nullptr) logits[at] = rounded;
+            const float v = __half2float(rounded);
+            if (better(v, at + index_offset, best_v, best_i)) { best_v = v; best_i = at + index_offset; }
+        }
     }
     if (lane == 0) { s_v[warp] = best_v; s_i[warp] = best_i; }
     __syncthreads();
