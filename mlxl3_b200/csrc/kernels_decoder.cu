@@ -183,13 +183,22 @@ attention_decode_kernel(const __half* __restrict__ q, const __half* __restrict__
     }
     const __half* kbase = k_cache + static_cast<int64_t>(kvh) * max_ctx * kAttnDim + j * 16;
     const __half* vbase = v_cache + static_cast<int64_t>(kvh) * max_ctx * kAttnDim + j * 16;
+    // the rows of the NEXT round are requested before this round's arithmetic: a chunk is three or four rounds, and a
+    // round that waits for its own loads costs a trip to memory each time
+    uint4 nka, nkb, nva, nvb;
+    auto request = [&](int first) {
+        const int key = first + kg;
+        const int64_t at = static_cast<int64_t>(key < key1 ? key : key1 - 1) * kAttnDim;
+        nka = __ldcs(reinterpret_cast<const uint4*>(kbase + at)); nkb = __ldcs(reinterpret_cast<const uint4*>(kbase + at + 8));
+        nva = __ldcs(reinterpret_cast<const uint4*>(vbase + at)); nvb = __ldcs(reinterpret_cast<const uint4*>(vbase + at + 8));
+    };
+    if (key0 + warp * 4 < key1) request(key0 + warp * 4);
 #pragma unroll 1
     for (int first = key0 + warp * 4; first < key1; first += kAttnWarps * 4) {
         const int key = first + kg;
         const bool valid = key < key1;
-        const int64_t at = static_cast<int64_t>(valid ? key : key1 - 1) * kAttnDim;
-        const uint4 ka = __ldcs(reinterpret_cast<const uint4*>(kbase + at)), kb = __ldcs(reinterpret_cast<const uint4*>(kbase + at + 8));
-        const uint4 va = __ldcs(reinterpret_cast<const uint4*>(vbase + at)), vb = __ldcs(reinterpret_cast<const uint4*>(vbase + at + 8));
+        const uint4 ka = nka, kb = nkb, va = nva, vb = nvb;
+        if (first + kAttnWarps * 4 < key1) request(first + kAttnWarps * 4);
         float kf[16], vf[16];
         {
             const __half2* h0 = reinterpret_cast<const __half2*>(&ka);
@@ -275,7 +284,7 @@ attention_decode_kernel(const __half* __restrict__ q, const __half* __restrict__
     if (!s_last) return;
     __threadfence();
     // warp h merges query head h: lane i weighs splits i and i + 32 (at most 64 splits), then every lane adds its four
-    // dimensions over the splits in split order, eight loads in flight
+    // dimensions over the splits in split order, sixteen loads in flight
     if (warp < nheads) {
         const int64_t base = static_cast<int64_t>(head0 + warp) * splits;
         const float2 ml0 = lane < splits ? __ldcg(&part_ml[base + lane]) : make_float2(-INFINITY, 0.0f);
@@ -288,13 +297,13 @@ attention_decode_kernel(const __half* __restrict__ q, const __half* __restrict__
         float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
         const float* acc_base = part_acc + base * kAttnDim + lane * 4;
 #pragma unroll 1
-        for (int s0 = 0; s0 < splits; s0 += 8) {
-            float4 part[8];
+        for (int s0 = 0; s0 < splits; s0 += 16) {
+            float4 part[16];
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
+            for (int i = 0; i < 16; ++i)
                 if (s0 + i < splits) part[i] = __ldcg(reinterpret_cast<const float4*>(acc_base + static_cast<int64_t>(s0 + i) * kAttnDim));
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
+            for (int i = 0; i < 16; ++i) {
                 const int sp = s0 + i;                                              // uniform over the warp
                 const float c = __shfl_sync(0xffffffffu, sp < 32 ? c0 : c1, sp & 31);
                 const float l_s = __shfl_sync(0xffffffffu, sp < 32 ? ml0.y : ml1.y, sp & 31);
