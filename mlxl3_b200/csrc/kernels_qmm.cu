@@ -11,17 +11,18 @@
 //  * one CTA owns 128 output columns (the 128 lanes of tensor memory), up to 512 tokens (all 512 fp32
 //    columns of tensor memory, as two halves of 256) and a contiguous range of 64-input stages
 //    (split-K across CTAs), so a batch of up to 512 rows decodes every weight exactly once;
-//  * A operand = decoded weights, [128 out, 64 in] fp16, K-major with the 128-byte swizzle.  Eight
-//    decoder warps each own four tiles (one interleaved quad) of one 16-input tile row of the stage:
-//    a warp streams its packed quads with TMA bulk copies into its own ring, decodes the tiles
-//    bit-exactly in registers (the lane's eight weights are two 4-byte pairs for rows g and g+8 of the
-//    A tile) and stores them with the swizzle applied;
+//  * A operand = decoded weights, [128 out, 64 in] fp16, K-major with the 128-byte swizzle.  One thread streams the
+//    packed stages (4 tile rows x 8 tiles, contiguous in the quad layout) with bulk copies into a ring; eight
+//    decoder warps each own four tiles (one interleaved quad) of one 16-input tile row of the stage, decode them
+//    bit-exactly in registers (the lane's eight weights are two 4-byte pairs for rows g and g+8 of the A tile) and
+//    store them with the swizzle applied;
 //  * B operand = rotated activations, [256 token, 64 in] fp16 per half, K-major, loaded by one TMA
 //    tensor copy per half and stage with the 128-byte swizzle (rows past the batch are zero-filled);
 //    the B ring is decoupled from the A ring;
-//  * one thread issues four tcgen05.mma (M=128, N=256, K=16) per half and stage, commits each B slot
-//    and each A stage back to its producers; after the last stage the decoder warps read the
-//    accumulator with tcgen05.ld and store the partial products.
+//  * one thread issues four tcgen05.mma (M=128, N=256, K=16) per half and stage and one commit per stage, which
+//    frees the A stage and the B slots; in the large shape a watcher warp tests the barriers for it (one lane per
+//    barrier, one instruction) and publishes a count; after the last stage the decoder warps read the accumulator
+//    with tcgen05.ld and either store partial products or rotate and store the outputs.
 // Every wait on an mbarrier is bounded in time; a wait that gives up sets the status word and the
 // kernel still releases its tensor memory.
 #include <cuda.h>
