@@ -36,6 +36,13 @@
 #include "tile_decode.cuh"
 #include "kernels.h"
 
+// The operators fused around a layer are compiled into instantiations of their own (kFused): 0 = none, 1 = those of
+// a dense decoder (prologues 1..3, epilogues 1..2), 2 = all (the expert block's prologue 4 and epilogue 3 too).  With all
+// of that code in it the plain kernel spilled 56 bytes and a 4096 -> 14336 layer took 22.4 instead of 21.2 us; the dense
+// set alone does not spill, the expert set does (32..64 bytes).
+#define QMV_PRO(p) ((kFused == 2 || (kFused == 1 && (p).prologue <= 3)) ? (p).prologue : 0)
+#define QMV_EPI(p) ((kFused == 2 || (kFused == 1 && (p).epilogue <= 2)) ? (p).epilogue : 0)
+
 namespace b200exl3 {
 
 // One tile: decode the lane's eight weights and issue the MMAs against the activation fragments.
@@ -192,6 +199,7 @@ __device__ __forceinline__ void qmv_row_inv_rms(const __half* x, const __half* r
 }
 
 // qmv_rotate_chunk with a fused prologue in front of the input scales: RMSNorm (after an optional residual add) or SwiGLU.
+template <int kFused>
 __device__ __forceinline__ void qmv_rotate_chunk_fused(const QmvArgs& p, const __half* suh, const float (&inv)[kQmvFusedRows], int rows, int kb0,
                                                        int nblk, bool store_sum, __half* xs, int lane) {
     constexpr int kXsHalves = kQmvXBlocks * 128;
@@ -206,17 +214,17 @@ __device__ __forceinline__ void qmv_rotate_chunk_fused(const QmvArgs& p, const _
             const uint2 sv = *reinterpret_cast<const uint2*>(suh + col);
             const __half2* xh = reinterpret_cast<const __half2*>(&xv);
             __align__(8) __half2 v[2];
-            if (p.prologue == 1 || p.prologue == 3) {
+            if (QMV_PRO(p) == 1 || QMV_PRO(p) == 3) {
                 const uint2 wv = *reinterpret_cast<const uint2*>(p.pro_weight + col);
                 const __half2* wh = reinterpret_cast<const __half2*>(&wv);
                 __half2 s0 = xh[0], s1 = xh[1];
-                if (p.prologue == 1 && p.pro_aux != nullptr) {
+                if (QMV_PRO(p) == 1 && p.pro_aux != nullptr) {
                     const uint2 rv = __ldcg(reinterpret_cast<const uint2*>(p.pro_aux + at));
                     const __half2* rh = reinterpret_cast<const __half2*>(&rv);
                     s0 = __hadd2_rn(s0, rh[0]);
                     s1 = __hadd2_rn(s1, rh[1]);
                 }
-                if (p.prologue == 1 && store_sum && p.pro_sum != nullptr) {
+                if (QMV_PRO(p) == 1 && store_sum && p.pro_sum != nullptr) {
                     __align__(8) __half2 keep[2] = {s0, s1};
                     *reinterpret_cast<uint2*>(p.pro_sum + at) = *reinterpret_cast<const uint2*>(keep);
                 }
@@ -248,6 +256,7 @@ __device__ __forceinline__ void qmv_rotate_chunk_fused(const QmvArgs& p, const _
 // had work in the block (warp_mask) in warp order; if other CTAs share the block, publishes the
 // sum as this CTA's piece and counts arrivals; the last CTA adds the pieces in piece order.  Whoever
 // holds the complete sum applies the output rotation (or stores the raw sum).
+template <int kFused>
 __device__ __forceinline__ void qmv_finish_block(const QmvArgs& p, int cblock, unsigned int warp_mask, unsigned int second_mask,
                                               int pieces, int piece, const unsigned char* smem_base, int lane) {
     const int rows = p.rows;
@@ -305,7 +314,7 @@ __device__ __forceinline__ void qmv_finish_block(const QmvArgs& p, int cblock, u
                 continue;
             }
             const int col = cblock * 128 + lane * 4;              // column in the concatenated output space
-            if (p.yhat != nullptr && p.epilogue == 3) {
+            if (p.yhat != nullptr && QMV_EPI(p) == 3) {
                 // Expert-mapped down product, one row per slot: virtual block = (slot, block j of the expert's columns).
                 // The block is rotated, scaled by the expert's output scales and the slot's routing weight and parked in
                 // yhat; the last of a token's top_k slots to arrive adds them in slot order (the arithmetic and the order
@@ -374,7 +383,7 @@ __device__ __forceinline__ void qmv_finish_block(const QmvArgs& p, int cblock, u
                 warp_hadamard128_f16(h, lane);
                 __align__(8) __half sv[4];
                 *reinterpret_cast<uint2*>(sv) = *reinterpret_cast<const uint2*>(p.svh + col);
-                if (p.epilogue == 1) {
+                if (QMV_EPI(p) == 1) {
                     // residual add and the block's sum of squares for the next RMSNorm (fixed shuffle order)
                     const int64_t at = static_cast<int64_t>(row) * p.out + col;
                     const uint2 rv = __ldcg(reinterpret_cast<const uint2*>(p.epi_residual + at));
@@ -397,7 +406,7 @@ __device__ __forceinline__ void qmv_finish_block(const QmvArgs& p, int cblock, u
                 }
                 const int grp = qmv_group_of(p, cblock);
                 const int gcol = col - p.gcol0[grp];
-                if (p.epilogue == 2) {
+                if (QMV_EPI(p) == 2) {
                     // [q | k | v] with 128-wide heads: this block is one head.  Rotary embedding of q and k heads (pairs
                     // (i, i + 64): lane L holds columns 4L..4L+3, its partner is lane L ^ 16), keys and values go
                     // straight into row `pos` of the caches.
@@ -437,7 +446,7 @@ __device__ __forceinline__ void qmv_finish_block(const QmvArgs& p, int cblock, u
     }
 }
 
-template <int K, int CB, int NB, int MODE>
+template <int K, int CB, int NB, int MODE, int kFused>
 __global__ void __launch_bounds__(kQmvWarps * 32, NB == 1 ? 2 : 1)
 qmv_kernel(const QmvArgs p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -603,14 +612,14 @@ qmv_kernel(const QmvArgs p) {
 
                 // ---- phase 1: rotate this chunk's activations into the warp's shared memory ------------
                 if (p.xhat == nullptr) {
-                    if (p.prologue == 4) {
+                    if (QMV_PRO(p) == 4) {
                         qmv_rotate_chunk_glu(p, map_slot, map_expert, kb0, ((tk_end - 1) >> 3) - kb0 + 1, xs, lane);
-                    } else if (p.prologue != 0) {
-                        if (!have_inv && p.prologue == 1) {
+                    } else if (QMV_PRO(p) != 0) {
+                        if (!have_inv && QMV_PRO(p) == 1) {
                             qmv_row_inv_rms(reinterpret_cast<const __half*>(p.x), p.pro_aux, p.in, rows, p.pro_eps, lane, inv_rms);
                             have_inv = true;
                         }
-                        if (!have_inv && p.prologue == 3) {
+                        if (!have_inv && QMV_PRO(p) == 3) {
                             // the layer before left the sum of squares of every 128-block: add them in a fixed order
 #pragma unroll
                             for (int row = 0; row < kQmvFusedRows; ++row)
@@ -623,7 +632,7 @@ qmv_kernel(const QmvArgs p) {
                                 }
                             have_inv = true;
                         }
-                        qmv_rotate_chunk_fused(p, p.suh + suh_row * p.in, inv_rms, rows, kb0, ((tk_end - 1) >> 3) - kb0 + 1, cblock == 0, xs, lane);
+                        qmv_rotate_chunk_fused<kFused>(p, p.suh + suh_row * p.in, inv_rms, rows, kb0, ((tk_end - 1) >> 3) - kb0 + 1, cblock == 0, xs, lane);
                     } else {
                         qmv_rotate_chunk(x_rows, p.x_dtype, p.suh + suh_row * p.in, p.in, rows, kb0,
                                          ((tk_end - 1) >> 3) - kb0 + 1, xs, lane);
@@ -731,7 +740,7 @@ qmv_kernel(const QmvArgs p) {
                 i_first = static_cast<int>((((static_cast<int64_t>(cblock) * RB + 1) * W - 1) / RT) / WARPS);
                 i_last = static_cast<int>(((static_cast<int64_t>(cblock + 1) * RB * W - 1) / RT) / WARPS);
             }
-            qmv_finish_block(p, cblock, mask, second, i_last - i_first + 1, static_cast<int>(blockIdx.x) - i_first, smem_raw,
+            qmv_finish_block<kFused>(p, cblock, mask, second, i_last - i_first + 1, static_cast<int>(blockIdx.x) - i_first, smem_raw,
                              lane);
             if (tracing) p.trace[blockIdx.x * 8 + 5] = global_ns();
         }
@@ -739,9 +748,9 @@ qmv_kernel(const QmvArgs p) {
     if (copy_lost && lane == 0) atomicExch(p.error, 1u);
 }
 
-template <int K, int CB, int NB, int MODE>
+template <int K, int CB, int NB, int MODE, int FUSED>
 cudaError_t qmv_launch_one(const QmvArgs& p, const QmvPlan& plan, cudaStream_t stream) {
-    auto kernel = qmv_kernel<K, CB, NB, MODE>;
+    auto kernel = qmv_kernel<K, CB, NB, MODE, FUSED>;
     static PerDeviceOnce attribute;                         // once per kernel and device: allow the largest carve-out
     if (attribute.needed()) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kQmvMaxSmemBytes);
@@ -763,8 +772,13 @@ cudaError_t qmv_launch_one(const QmvArgs& p, const QmvPlan& plan, cudaStream_t s
 
 template <int K, int CB, int MODE>
 cudaError_t qmv_launch_nb(const QmvArgs& p, const QmvPlan& plan, cudaStream_t stream) {
-    if (p.rows <= 8) return qmv_launch_one<K, CB, 1, MODE>(p, plan, stream);
-    return qmv_launch_one<K, CB, 2, MODE>(p, plan, stream);
+    const int fused = (p.prologue == 4 || p.epilogue == 3) ? 2 : ((p.prologue != 0 || p.epilogue != 0) ? 1 : 0);
+    if (p.rows <= 8) {
+        if (fused == 2) return qmv_launch_one<K, CB, 1, MODE, 2>(p, plan, stream);
+        return fused ? qmv_launch_one<K, CB, 1, MODE, 1>(p, plan, stream) : qmv_launch_one<K, CB, 1, MODE, 0>(p, plan, stream);
+    }
+    if (fused == 2) return qmv_launch_one<K, CB, 2, MODE, 2>(p, plan, stream);
+    return fused ? qmv_launch_one<K, CB, 2, MODE, 1>(p, plan, stream) : qmv_launch_one<K, CB, 2, MODE, 0>(p, plan, stream);
 }
 
 template <int K>
