@@ -66,8 +66,8 @@ def test_switch_glu_matches_oracle(gpu, k, cb, experts, top_k, n_in, hidden, row
 
 
 def test_switch_glu_many_rows_and_repeated_experts(gpu):
-    """More than 32 slots: the expert-sorted form (segments of 8 rows per expert), several passes, every
-    expert chosen many times, and experts that nobody chose."""
+    """600 slots over 12 experts (50 per expert): the expert-sorted form with segments of 64 rows through the
+    tensor-core product, every expert chosen many times, and experts that nobody chose."""
     rng = np.random.default_rng(77)
     experts, top_k, n_in, hidden, k, cb, rows = 12, 4, 256, 256, 3, 1, 150
     bank = make_bank(rng, experts, n_in, hidden, k)
